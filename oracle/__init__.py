@@ -1,0 +1,9 @@
+"""CPU oracle for the paged-decode hot path (test infrastructure only).
+
+Only tests, the smoke check and the CPU-baseline leg of the bench may import this package; the
+product library never does.  `pa_oracle.c` restates the reference's CPU golden
+(tests/apitest/kernelstest/mix/test_paged_attention_common.py:229-366 and
+tests/apitest/kernelstest/mix/test_reshape_and_cache.py:45-68 of the reference) and is pinned
+against outputs of those Python functions stored under tests/golden/.
+"""
+from .oracle import build, load, paged_attention, reshape_and_cache, num_threads  # noqa: F401

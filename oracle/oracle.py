@@ -1,0 +1,100 @@
+"""ctypes front end of liboracle.so (see pa_oracle.c).  Arrays are numpy; bf16 travels as uint16 bits."""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+FP16, BF16, INT8 = 0, 1, 2
+_DT = {"fp16": FP16, "bf16": BF16, "int8": INT8}
+
+
+def build(force=False):
+    """Compile pa_oracle.c with gcc (OpenMP) into oracle/liboracle.so."""
+    so = os.path.join(_HERE, "liboracle.so")
+    src = os.path.join(_HERE, "pa_oracle.c")
+    if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", _HERE, "-B", "liboracle.so"], stdout=subprocess.DEVNULL)
+    return so
+
+
+def load():
+    global _LIB
+    if _LIB is None:
+        so = os.path.join(_HERE, "liboracle.so")
+        if not os.path.exists(so):
+            build()
+        lib = ctypes.CDLL(so)
+        vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_float
+        lib.oracle_paged_attention.restype = ctypes.c_int
+        lib.oracle_paged_attention.argtypes = [vp] * 11 + [i32] * 10 + [f32, i32]
+        lib.oracle_reshape_and_cache.restype = ctypes.c_int
+        lib.oracle_reshape_and_cache.argtypes = [vp] * 5 + [i32, i64, i64, i64]
+        lib.oracle_num_threads.restype = ctypes.c_int
+        _LIB = lib
+    return _LIB
+
+
+def _ptr(a):
+    if a is None:
+        return None
+    assert a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def num_threads():
+    return int(load().oracle_num_threads())
+
+
+def paged_attention(q, k_cache, v_cache, block_tables, context_lens, scale, q_dtype, kv_dtype=None, dv=None,
+                    k_descale=None, v_descale=None, k_offset=None, v_offset=None, out=None, want_high=False,
+                    nthreads=0):
+    """Decode attention golden.  `v_cache=None` means the MLA combined cache (V = K[..., :dv]).
+
+    q: [B,H,Dk] (float16, or uint16 holding bf16 bits); caches [NB,BS,Hkv,D] in the same encoding or
+    int8.  Returns out [B,H,Dv] in q's encoding (rows of zero-length sequences keep `out`'s
+    previous contents, zeros if `out` is None) and optionally the fp32 high-precision output.
+    """
+    lib = load()
+    kv_dtype = kv_dtype or q_dtype
+    B, H, Dk = q.shape
+    NB, BS, Hkv, Dk2 = k_cache.shape
+    assert Dk == Dk2
+    if v_cache is None:
+        v_cache, dv_row = k_cache, Dk
+        assert dv is not None
+    else:
+        dv_row = v_cache.shape[3]
+        dv = dv or dv_row
+    block_tables = np.ascontiguousarray(block_tables, dtype=np.int32)
+    context_lens = np.ascontiguousarray(context_lens, dtype=np.int32)
+    if out is None:
+        out = np.zeros((B, H, dv), dtype=q.dtype)
+    high = np.zeros((B, H, dv), dtype=np.float32) if want_high else None
+    f32 = lambda a: None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+    i32 = lambda a: None if a is None else np.ascontiguousarray(a, dtype=np.int32)
+    kd, vd, ko, vo = f32(k_descale), f32(v_descale), i32(k_offset), i32(v_offset)
+    rc = lib.oracle_paged_attention(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(context_lens),
+                                    _ptr(kd), _ptr(vd), _ptr(ko), _ptr(vo), _ptr(out), _ptr(high), B, H, Hkv, Dk,
+                                    dv, dv_row, BS, block_tables.shape[1], _DT[q_dtype], _DT[kv_dtype],
+                                    float(scale), int(nthreads))
+    if rc != 0:
+        raise ValueError("oracle_paged_attention rejected its arguments")
+    return (out, high) if want_high else out
+
+
+def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping):
+    """In-place scatter golden; `value`/`value_cache` may be None (K-only variant)."""
+    lib = load()
+    slot_mapping = np.ascontiguousarray(slot_mapping, dtype=np.int32)
+    n = slot_mapping.shape[0]
+    krow = key[0].nbytes if key is not None and n else 0
+    vrow = value[0].nbytes if value is not None and n else 0
+    nslots = key_cache.shape[0] * key_cache.shape[1]
+    rc = lib.oracle_reshape_and_cache(_ptr(key), _ptr(value), _ptr(key_cache), _ptr(value_cache), _ptr(slot_mapping),
+                                      n, krow, vrow, nslots)
+    if rc != 0:
+        raise ValueError("oracle_reshape_and_cache rejected its arguments")

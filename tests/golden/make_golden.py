@@ -1,0 +1,175 @@
+"""Generates the golden fixtures in this directory from the REFERENCE's own CPU golden code.
+
+Run where the reference checkout is available:
+
+    python tests/golden/make_golden.py /path/to/ascend-transformer-boost
+
+It imports, unmodified, the golden functions of the reference test-suite
+  tests/apitest/kernelstest/mix/test_paged_attention_common.py   (TestPagedAttention:
+      ref_single_query_cached_kv_attention / ref_masked_attention / group_mm_torch)
+  tests/apitest/opstest/python/operations/paged_attention/test_paged_attention_operation_mla.py
+      (TestPagedAttentionMLA: same functions for the combined K/V cache)
+  tests/apitest/kernelstest/mix/test_reshape_and_cache.py        (generate_test_data)
+with the NPU-only imports (`torch_npu`, `op_test`, `operation_test`) replaced by empty stubs, feeds
+them this repository's seeded inputs, and stores the outputs as small .npz files.  The inputs are
+not stored: they are regenerated from the seed and checked against the stored SHA-256.
+"""
+import hashlib
+import importlib.util
+import os
+import sys
+import types
+import unittest
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, HERE)
+
+from golden_cases import GOLDEN_PA_CASES, GOLDEN_RAC_CASES, load_workloads, rac_inputs  # noqa: E402
+
+wl = load_workloads()
+
+
+def _stub_modules():
+    class _Any(unittest.TestCase):
+        def runTest(self):
+            pass
+
+    def _decorator_factory(*a, **k):
+        if len(a) == 1 and callable(a[0]) and not k:
+            return a[0]
+        return lambda f: f
+
+    for name, cls in (("op_test", "OpTest"), ("operation_test", "OperationTest")):
+        m = types.ModuleType(name)
+        setattr(m, cls, _Any)
+        m.__getattr__ = lambda attr: _decorator_factory
+        sys.modules[name] = m
+    sys.modules["torch_npu"] = types.ModuleType("torch_npu")
+
+
+def _load(path, name):
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def to_torch(a, dtype):
+    if dtype == "bf16":
+        return torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16)
+    return torch.from_numpy(np.ascontiguousarray(a))
+
+
+def from_torch(t, dtype):
+    if dtype == "bf16":
+        return t.to(torch.bfloat16).contiguous().view(torch.int16).numpy().view(np.uint16)
+    if dtype == "fp16":
+        return t.to(torch.float16).contiguous().numpy()
+    return t.contiguous().numpy()
+
+
+def digest(d):
+    h = hashlib.sha256()
+    for k in sorted(d):
+        v = d[k]
+        if isinstance(v, np.ndarray):
+            h.update(k.encode())
+            h.update(np.ascontiguousarray(v).tobytes())
+    return h.hexdigest()
+
+
+def run_pa_case(ref_root, case, cls_common, cls_mla):
+    d = wl.make_host_inputs(case)
+    tdt = {"fp16": torch.float16, "bf16": torch.bfloat16}[case.q_dtype]
+    q = to_torch(d["q"], case.q_dtype)
+    kc = to_torch(d["k_cache"], case.kvd)
+    if case.mla or case.dk != case.dv:
+        # the MLA golden class reads K and V widths separately, so it also serves Dk != Dv
+        t = cls_mla()
+        t.compressHead = False
+        t.is_int8_flag = False
+        t.num_heads, t.kv_heads, t.num_tokens = case.heads, case.kv_heads, case.batch
+        t.head_size_qk, t.head_size_vo = case.dk, case.dv
+        vc = kc[:, :, :, :case.dv] if case.mla else to_torch(d["v_cache"], case.kvd)
+        out = torch.zeros((case.batch, case.heads, case.dv), dtype=torch.float32)
+        high = torch.zeros_like(out)
+        # the reference packs outputs of non-empty sequences; golden cases for MLA have none empty
+        t.ref_single_query_cached_kv_attention(out, high, q, kc, vc, d["block_tables"].tolist(),
+                                               d["context_lens"].tolist(), None, mask_dim=0,
+                                               mask_data_type=tdt)
+    else:
+        t = cls_common()
+        t.compressHead = False
+        t.is_int8_flag = case.kvd == "int8"
+        t.is_quant_flag = 0
+        t.has_bias = case.offsets
+        t.scaleType = 0
+        t.num_heads, t.kv_heads, t.num_tokens, t.head_size = case.heads, case.kv_heads, case.batch, case.dk
+        if t.is_int8_flag:
+            t.de_scale1_fp32 = torch.from_numpy(d["k_descale"])
+            t.de_scale2_fp32 = torch.from_numpy(d["v_descale"])
+            if case.offsets:
+                t.offset1 = torch.from_numpy(d["k_offset"])
+                t.offset2 = torch.from_numpy(d["v_offset"])
+        vc = to_torch(d["v_cache"], case.kvd)
+        out = torch.zeros((case.batch, case.heads, case.dv), dtype=torch.float32)
+        high = torch.zeros_like(out)
+        assert (d["context_lens"] > 0).all(), "the reference golden packs rows when a length is 0"
+        t.ref_single_query_cached_kv_attention(out, high, q, kc, vc, d["block_tables"].tolist(),
+                                               d["context_lens"].tolist(), None, None, False, mask_dim=0,
+                                               mask_data_type=tdt)
+    return {"out": from_torch(out, case.q_dtype), "out_high": high.numpy(),
+            "input_sha256": np.frombuffer(digest(d).encode(), dtype=np.uint8)}
+
+
+def run_rac_case(rac_mod, spec):
+    inp = rac_inputs(spec)
+    # generate_test_data of the reference reads these attributes of the test object
+    t = rac_mod.TestReshapeAndCache() if hasattr(rac_mod, "TestReshapeAndCache") else None
+    if t is None:
+        cls = [v for v in vars(rac_mod).values() if isinstance(v, type) and hasattr(v, "generate_test_data")][0]
+        t = cls()
+    t.num_tokens, t.num_heads = spec["tokens"], spec["heads"]
+    t.head_size_k, t.head_size_v = spec["dk"], spec["dv"]
+    t.block_size, t.num_blocks = spec["block_size"], spec["num_blocks"]
+    t.dtype = {"fp16": "float16", "bf16": "bfloat16", "int8": "int8"}[spec["dtype"]]
+    # the reference holds bf16 test data as float32 values; decode ours the same way
+    t.key = wl.to_f32(inp["key"], spec["dtype"]) if spec["dtype"] == "bf16" else inp["key"]
+    t.value = wl.to_f32(inp["value"], spec["dtype"]) if spec["dtype"] == "bf16" else inp["value"]
+    t.slot_mapping = inp["slot_mapping"]
+    kexp, vexp = t.generate_test_data()   # caches start from zeros in the reference golden
+    if spec["dtype"] == "bf16":
+        kexp, vexp = wl.f32_to_bf16_bits(kexp), wl.f32_to_bf16_bits(vexp)
+    return {"key_cache": kexp, "value_cache": vexp,
+            "input_sha256": np.frombuffer(digest(inp).encode(), dtype=np.uint8)}
+
+
+def main():
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    _stub_modules()
+    kt = os.path.join(ref_root, "tests/apitest/kernelstest")
+    sys.path.insert(0, kt)
+    sys.path.insert(0, os.path.join(kt, "mix"))
+    cwd = os.getcwd()
+    os.chdir(os.path.join(kt, "mix"))
+    common = _load(os.path.join(kt, "mix/test_paged_attention_common.py"), "ref_pa_common")
+    rac = _load(os.path.join(kt, "mix/test_reshape_and_cache.py"), "ref_rac")
+    mla = _load(os.path.join(ref_root, "tests/apitest/opstest/python/operations/paged_attention/"
+                                       "test_paged_attention_operation_mla.py"), "ref_pa_mla")
+    os.chdir(cwd)
+    for case in GOLDEN_PA_CASES:
+        res = run_pa_case(ref_root, case, common.TestPagedAttention, mla.TestPagedAttentionMLA)
+        np.savez_compressed(os.path.join(HERE, f"pa_{case.name}.npz"), **res)
+        print("wrote", case.name, res["out"].shape)
+    for spec in GOLDEN_RAC_CASES:
+        res = run_rac_case(rac, spec)
+        np.savez_compressed(os.path.join(HERE, f"rac_{spec['name']}.npz"), **res)
+        print("wrote", spec["name"])
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,70 @@
+"""Pins the C oracle against outputs of the reference's own Python golden (tests/golden/*.npz)."""
+import hashlib
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from golden_cases import GOLDEN_PA_CASES, GOLDEN_RAC_CASES, HERE, load_workloads, rac_inputs
+
+wl = load_workloads()
+
+
+def _digest(d):
+    h = hashlib.sha256()
+    for k in sorted(d):
+        v = d[k]
+        if isinstance(v, np.ndarray):
+            h.update(k.encode())
+            h.update(np.ascontiguousarray(v).tobytes())
+    return h.hexdigest()
+
+
+def ulp(dtype):
+    return 2.0 ** -10 if dtype == "fp16" else 2.0 ** -7
+
+
+@pytest.mark.parametrize("case", GOLDEN_PA_CASES, ids=lambda c: c.name)
+def test_oracle_matches_reference_golden(case):
+    fx = np.load(os.path.join(HERE, f"pa_{case.name}.npz"))
+    d = wl.make_host_inputs(case)
+    assert _digest(d) == bytes(fx["input_sha256"]).decode(), "seeded inputs changed; regenerate the fixtures"
+    out, high = oracle.paged_attention(
+        d["q"], d["k_cache"], d["v_cache"], d["block_tables"], d["context_lens"], case.qk_scale, case.q_dtype,
+        kv_dtype=case.kvd, dv=case.dv, k_descale=d.get("k_descale"), v_descale=d.get("v_descale"),
+        k_offset=d.get("k_offset"), v_offset=d.get("v_offset"), want_high=True)
+    ref_high = fx["out_high"]
+    # fp32 path: only summation order differs between torch.matmul and the C loops
+    np.testing.assert_allclose(high, ref_high, rtol=2e-4, atol=2e-5)
+    got = wl.to_f32(out, case.q_dtype)
+    ref = wl.to_f32(fx["out"], case.q_dtype)
+    # rounded output: a couple of units in the last place (a 1-ulp fp32 difference in exp() can flip the
+    # rounding of one probability, which moves the output by ulp(P) * |v|)
+    tol = 2 * ulp(case.q_dtype) * np.maximum(np.abs(ref), 2.0 ** -6)
+    assert np.all(np.abs(got - ref) <= tol), float(np.max(np.abs(got - ref)))
+    # and nearly all elements bit-identical
+    same = np.mean(out.view(np.uint16) == fx["out"].view(np.uint16))
+    assert same > 0.97, same
+
+
+@pytest.mark.parametrize("spec", GOLDEN_RAC_CASES, ids=lambda s: s["name"])
+def test_oracle_reshape_and_cache_bit_exact(spec):
+    fx = np.load(os.path.join(HERE, f"rac_{spec['name']}.npz"))
+    inp = rac_inputs(spec)
+    assert _digest(inp) == bytes(fx["input_sha256"]).decode()
+    kdt = fx["key_cache"].dtype
+    kc = np.zeros((spec["num_blocks"], spec["block_size"], spec["heads"], spec["dk"]), dtype=kdt)
+    vc = np.zeros((spec["num_blocks"], spec["block_size"], spec["heads"], spec["dv"]), dtype=kdt)
+    oracle.reshape_and_cache(inp["key"].view(kdt), inp["value"].view(kdt), kc, vc, inp["slot_mapping"])
+    assert np.array_equal(kc.view(np.uint8), fx["key_cache"].view(np.uint8))
+    assert np.array_equal(vc.view(np.uint8), fx["value_cache"].view(np.uint8))
+
+
+def test_oracle_skips_empty_sequences():
+    case = wl.Case("z", batch=3, heads=4, kv_heads=2, q_dtype="fp16", ctx=("list", [0, 5, 0]), seed=5)
+    d = wl.make_host_inputs(case)
+    out = np.full((3, 4, 128), 7.0, dtype=np.float16)
+    oracle.paged_attention(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], d["context_lens"],
+                           case.qk_scale, "fp16", out=out)
+    assert np.all(out[0] == 7.0) and np.all(out[2] == 7.0) and not np.all(out[1] == 7.0)
