@@ -1,0 +1,71 @@
+"""Builds libatb_b200.so (CUDA kernels + C ABI + the atb:: C++ operator layer) in-tree with nvcc for sm_100a."""
+import os
+import subprocess
+import sys
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(PKG)
+CSRC = os.path.join(PKG, "csrc")
+OUT = os.path.join(PKG, "libatb_b200.so")
+
+CU_SOURCES = ["reshape_and_cache.cu", "pa_generic.cu", "pa_combine.cu", "pa_tma_mma.cu", "atb_scale_convert.cu"]
+CPP_SOURCES = ["pa_planner.cpp", "c_api.cpp", "atb_operation_base.cpp", "atb_paged_attention.cpp",
+               "atb_reshape_and_cache.cpp", "atb_c_wrappers.cpp"]
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC,-fvisibility=default", "--expt-relaxed-constexpr",
+              "-I" + os.path.join(ROOT, "include"), "-I" + CSRC]
+
+
+def sources():
+    return [os.path.join(CSRC, s) for s in CU_SOURCES + CPP_SOURCES]
+
+
+def stale():
+    if not os.path.exists(OUT):
+        return True
+    t = os.path.getmtime(OUT)
+    deps = sources() + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
+    deps += [os.path.join(ROOT, "include", "atb_b200.h")]
+    deps += [os.path.join(ROOT, "include", "atb", f) for f in os.listdir(os.path.join(ROOT, "include", "atb"))]
+    return any(os.path.getmtime(d) > t for d in deps)
+
+
+def build(force=False, verbose=False):
+    """Compile every source with nvcc and link the shared library.  Objects go to csrc/build/."""
+    if not force and not stale():
+        return OUT
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    objdir = os.path.join(CSRC, "build")
+    os.makedirs(objdir, exist_ok=True)
+    procs = []
+    objs = []
+    for src in sources():
+        obj = os.path.join(objdir, os.path.basename(src) + ".o")
+        objs.append(obj)
+        if not force and os.path.exists(obj) and not _obj_stale(obj, src):
+            continue
+        cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-x", "cu", "-c", src, "-o", obj]
+        procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    failed = False
+    for src, p in procs:
+        out, _ = p.communicate()
+        if p.returncode != 0 or verbose:
+            sys.stderr.write(f"--- {os.path.basename(src)}\n{out}\n")
+        failed |= p.returncode != 0
+    if failed:
+        raise RuntimeError("nvcc failed")
+    subprocess.check_call([nvcc, "-shared", "-Wno-deprecated-gpu-targets", "-o", OUT] + objs + ["-cudart", "shared" if os.environ.get("ATB_B200_SHARED_CUDART") else "static"])
+    return OUT
+
+
+def _obj_stale(obj, src):
+    t = os.path.getmtime(obj)
+    deps = [src] + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
+    deps += [os.path.join(ROOT, "include", "atb_b200.h")]
+    deps += [os.path.join(ROOT, "include", "atb", f) for f in os.listdir(os.path.join(ROOT, "include", "atb"))]
+    return any(os.path.getmtime(d) > t for d in deps)
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -1,0 +1,382 @@
+"""ctypes bindings of libatb_b200.so (the declarations of include/atb_b200.h) and thin torch helpers.
+
+The library is the product; this module is the Python-side mirror of the reference's test harness
+entry (`OperationTorch.set_param / execute`, tests/apitest/opstest/python/operations/operation_test.py:66-110
+of the reference).  There is no fallback: if the shared library is missing, importing fails.
+"""
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libatb_b200.so")
+
+FP16, BF16, INT8 = 0, 1, 2
+KERNEL_AUTO, KERNEL_GENERIC, KERNEL_TMA_MMA, KERNEL_MLA_TC5 = 0, 1, 2, 3
+DTYPE_CODE = {"fp16": FP16, "bf16": BF16, "int8": INT8}
+
+# aclDataType / aclFormat values (include/acl/acl.h)
+ACL_FLOAT, ACL_FLOAT16, ACL_INT8, ACL_INT32, ACL_INT64, ACL_BF16 = 0, 1, 2, 3, 9, 27
+ACL_FORMAT_ND = 2
+
+# atb::ErrorType (include/atb/types.h)
+NO_ERROR = 0
+ERROR_INVALID_PARAM = 1
+ERROR_RT_FAIL = 4
+ERROR_INVALID_IN_TENSOR_NUM = 5
+ERROR_INVALID_TENSOR_DIM = 8
+ERROR_INVALID_TENSOR_SIZE = 9
+ERROR_INVALID_TENSOR_INI_MATCH = 13
+ERROR_INVALID_TENSOR_ADDR = 14
+ERROR_INVALID_TENSOR_DIM_NUM = 16
+
+
+class PaDesc(ctypes.Structure):
+    _fields_ = [("batch", ctypes.c_int32), ("num_heads", ctypes.c_int32), ("kv_heads", ctypes.c_int32),
+                ("head_dim_k", ctypes.c_int32), ("head_dim_v", ctypes.c_int32), ("v_row_dim", ctypes.c_int32),
+                ("block_size", ctypes.c_int32), ("num_blocks", ctypes.c_int32),
+                ("max_blocks_per_seq", ctypes.c_int32), ("q_dtype", ctypes.c_int32), ("kv_dtype", ctypes.c_int32),
+                ("qk_scale", ctypes.c_float), ("kernel", ctypes.c_int32), ("sm_count", ctypes.c_int32),
+                ("reserved", ctypes.c_int32 * 4)]
+
+
+class PaTensors(ctypes.Structure):
+    _fields_ = [("q", ctypes.c_void_p), ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p),
+                ("block_tables", ctypes.c_void_p), ("k_descale", ctypes.c_void_p), ("v_descale", ctypes.c_void_p),
+                ("k_offset", ctypes.c_void_p), ("v_offset", ctypes.c_void_p), ("out", ctypes.c_void_p)]
+
+
+class PaPlanInfo(ctypes.Structure):
+    _fields_ = [("kernel", ctypes.c_int32), ("num_ctas", ctypes.c_int32), ("num_items", ctypes.c_int32),
+                ("num_partials", ctypes.c_int32), ("num_combine_seqs", ctypes.c_int32),
+                ("tile_tokens", ctypes.c_int32), ("workspace_bytes", ctypes.c_uint64),
+                ("plan_bytes", ctypes.c_uint64)]
+
+
+class AtbTensor(ctypes.Structure):
+    _fields_ = [("dtype", ctypes.c_int32), ("format", ctypes.c_int32), ("dims", ctypes.c_int64 * 8),
+                ("dim_num", ctypes.c_uint64), ("device_data", ctypes.c_void_p), ("host_data", ctypes.c_void_p),
+                ("data_size", ctypes.c_uint64)]
+
+
+class PagedAttentionParam(ctypes.Structure):
+    """Byte layout of atb::infer::PagedAttentionParam (120 bytes)."""
+    _fields_ = [("headNum", ctypes.c_int32), ("qkScale", ctypes.c_float), ("kvHeadNum", ctypes.c_int32),
+                ("maskType", ctypes.c_int32), ("batchRunStatusEnable", ctypes.c_bool), ("quantType", ctypes.c_int32),
+                ("outDataType", ctypes.c_int32), ("hasQuantOffset", ctypes.c_bool), ("compressType", ctypes.c_int32),
+                ("calcType", ctypes.c_int32), ("scaleType", ctypes.c_int32), ("inputLayout", ctypes.c_int32),
+                ("mlaVHeadSize", ctypes.c_uint32), ("qScale", ctypes.c_float), ("rsv", ctypes.c_uint8 * 64)]
+
+    def __init__(self, **kw):
+        super().__init__()
+        self.qkScale = 1.0
+        self.outDataType = -1
+        for k, v in kw.items():
+            setattr(self, k, v)
+
+
+class ReshapeAndCacheParam(ctypes.Structure):
+    """Byte layout of atb::infer::ReshapeAndCacheParam (24 bytes)."""
+    _fields_ = [("compressType", ctypes.c_int32), ("kvCacheCfg", ctypes.c_int32), ("rsv", ctypes.c_uint8 * 16)]
+
+
+# every symbol include/atb_b200.h declares
+EXPORTS = [
+    "atb_b200_pa_plan_create", "atb_b200_pa_plan_update", "atb_b200_pa_plan_get_info", "atb_b200_pa_plan_dump",
+    "atb_b200_pa_plan_destroy", "atb_b200_pa_launch", "atb_b200_reshape_and_cache",
+    "atb_b200_pa_plan_device_status", "atb_b200_pa_plan_set_profiling", "atb_b200_pa_plan_last_kernel_ms",
+    "atb_b200_context_create", "atb_b200_context_set_stream", "atb_b200_context_destroy",
+    "atb_b200_operation_create_paged_attention", "atb_b200_operation_create_reshape_and_cache",
+    "atb_b200_operation_input_num", "atb_b200_operation_output_num", "atb_b200_operation_infer_shape",
+    "atb_b200_operation_setup", "atb_b200_operation_execute", "atb_b200_operation_destroy", "atb_b200_version",
+]
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: build it with `python {_PKG}/build.py` "
+                              "(there is no CPU or PyTorch fallback)")
+        L = ctypes.CDLL(LIB_PATH)
+        vp, i32, i64, u32, u64 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_uint32, ctypes.c_uint64
+        P = ctypes.POINTER
+        L.atb_b200_pa_plan_create.argtypes = [P(PaDesc), vp, P(vp)]
+        L.atb_b200_pa_plan_update.argtypes = [vp, vp]
+        L.atb_b200_pa_plan_get_info.argtypes = [vp, P(PaPlanInfo)]
+        L.atb_b200_pa_plan_dump.argtypes = [vp, vp, i32, vp, i32]
+        L.atb_b200_pa_plan_destroy.argtypes = [vp]
+        L.atb_b200_pa_plan_destroy.restype = None
+        L.atb_b200_pa_launch.argtypes = [vp, P(PaTensors), vp, u64, vp]
+        L.atb_b200_reshape_and_cache.argtypes = [vp, vp, vp, vp, vp, i32, i64, i64, i64, vp]
+        L.atb_b200_pa_plan_device_status.argtypes = [vp, vp, vp, P(i32)]
+        L.atb_b200_pa_plan_set_profiling.argtypes = [vp, ctypes.c_int]
+        L.atb_b200_pa_plan_last_kernel_ms.argtypes = [vp, P(ctypes.c_float)]
+        L.atb_b200_context_create.argtypes = [P(vp)]
+        L.atb_b200_context_set_stream.argtypes = [vp, vp]
+        L.atb_b200_context_destroy.argtypes = [vp]
+        L.atb_b200_operation_create_paged_attention.argtypes = [vp, u64, P(vp)]
+        L.atb_b200_operation_create_reshape_and_cache.argtypes = [vp, u64, P(vp)]
+        L.atb_b200_operation_input_num.argtypes = [vp, P(u32)]
+        L.atb_b200_operation_output_num.argtypes = [vp, P(u32)]
+        L.atb_b200_operation_infer_shape.argtypes = [vp, P(AtbTensor), u32, P(AtbTensor), u32]
+        L.atb_b200_operation_setup.argtypes = [vp, P(AtbTensor), u32, P(AtbTensor), u32, P(u64), vp]
+        L.atb_b200_operation_execute.argtypes = [vp, P(AtbTensor), u32, P(AtbTensor), u32, vp, u64, vp]
+        L.atb_b200_operation_destroy.argtypes = [vp]
+        L.atb_b200_version.restype = ctypes.c_char_p
+        _lib = L
+    return _lib
+
+
+class AtbError(RuntimeError):
+    def __init__(self, what, code):
+        super().__init__(f"{what} failed with atb::ErrorType {code}")
+        self.code = code
+
+
+def _check(rc, what):
+    if rc != 0:
+        raise AtbError(what, rc)
+
+
+# ------------------------------------------------------------------ kernel level
+
+def make_desc(batch, num_heads, kv_heads, dk, dv, block_size, num_blocks, max_blocks, q_dtype, kv_dtype=None,
+              qk_scale=1.0, v_row_dim=None, kernel=KERNEL_AUTO, sm_count=0):
+    d = PaDesc()
+    d.batch, d.num_heads, d.kv_heads = batch, num_heads, kv_heads
+    d.head_dim_k, d.head_dim_v, d.v_row_dim = dk, dv, (v_row_dim or dv)
+    d.block_size, d.num_blocks, d.max_blocks_per_seq = block_size, num_blocks, max_blocks
+    d.q_dtype = DTYPE_CODE[q_dtype] if isinstance(q_dtype, str) else q_dtype
+    kv = kv_dtype or q_dtype
+    d.kv_dtype = DTYPE_CODE[kv] if isinstance(kv, str) else kv
+    d.qk_scale, d.kernel, d.sm_count = qk_scale, kernel, sm_count
+    return d
+
+
+class PaPlan:
+    """Owns an atb_b200_pa_plan.  `context_lens` is a host int32 numpy array."""
+
+    def __init__(self, desc, context_lens):
+        import numpy as np
+        self._lens = np.ascontiguousarray(context_lens, dtype=np.int32)
+        self.desc = desc
+        self.handle = ctypes.c_void_p()
+        _check(lib().atb_b200_pa_plan_create(ctypes.byref(desc), self._lens.ctypes.data, ctypes.byref(self.handle)),
+               "atb_b200_pa_plan_create")
+
+    def update(self, context_lens):
+        import numpy as np
+        self._lens = np.ascontiguousarray(context_lens, dtype=np.int32)
+        _check(lib().atb_b200_pa_plan_update(self.handle, self._lens.ctypes.data), "atb_b200_pa_plan_update")
+
+    @property
+    def info(self):
+        info = PaPlanInfo()
+        _check(lib().atb_b200_pa_plan_get_info(self.handle, ctypes.byref(info)), "atb_b200_pa_plan_get_info")
+        return info
+
+    def dump(self):
+        import numpy as np
+        info = self.info
+        items = np.zeros((max(info.num_items, 1), 4), dtype=np.int32)
+        groups = np.zeros(info.num_ctas + 2, dtype=np.int32)
+        _check(lib().atb_b200_pa_plan_dump(self.handle, items.ctypes.data, items.shape[0], groups.ctypes.data,
+                                           groups.shape[0]), "atb_b200_pa_plan_dump")
+        return items[:info.num_items], groups
+
+    def launch(self, tensors, workspace_ptr, workspace_bytes, stream_ptr):
+        _check(lib().atb_b200_pa_launch(self.handle, ctypes.byref(tensors), workspace_ptr, workspace_bytes,
+                                        stream_ptr), "atb_b200_pa_launch")
+
+    def device_status(self, workspace_ptr, stream_ptr):
+        st = ctypes.c_int32(-1)
+        _check(lib().atb_b200_pa_plan_device_status(self.handle, workspace_ptr, stream_ptr, ctypes.byref(st)),
+               "atb_b200_pa_plan_device_status")
+        return st.value
+
+    def set_profiling(self, on=True):
+        _check(lib().atb_b200_pa_plan_set_profiling(self.handle, 1 if on else 0), "atb_b200_pa_plan_set_profiling")
+
+    def last_kernel_ms(self):
+        ms = ctypes.c_float(0)
+        _check(lib().atb_b200_pa_plan_last_kernel_ms(self.handle, ctypes.byref(ms)),
+               "atb_b200_pa_plan_last_kernel_ms")
+        return ms.value
+
+    def close(self):
+        if self.handle:
+            lib().atb_b200_pa_plan_destroy(self.handle)
+            self.handle = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def torch_stream_ptr():
+    import torch
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def pa_tensors(q, k_cache, v_cache, block_tables, out, k_descale=None, v_descale=None, k_offset=None, v_offset=None):
+    t = PaTensors()
+    t.q, t.k_cache = _ptr(q), _ptr(k_cache)
+    t.v_cache = _ptr(v_cache if v_cache is not None else k_cache)
+    t.block_tables, t.out = _ptr(block_tables), _ptr(out)
+    t.k_descale, t.v_descale, t.k_offset, t.v_offset = _ptr(k_descale), _ptr(v_descale), _ptr(k_offset), _ptr(v_offset)
+    return t
+
+
+def paged_attention(q, k_cache, v_cache, block_tables, context_lens_host, qk_scale, dv=None, k_descale=None,
+                    v_descale=None, k_offset=None, v_offset=None, out=None, kernel=KERNEL_AUTO, plan=None,
+                    workspace=None, return_plan=False):
+    """One decode step on torch CUDA tensors through the kernel-level C ABI (plan + launch).
+
+    v_cache=None selects the combined (MLA) cache: V = K[..., :dv].
+    """
+    import torch
+    name = {torch.float16: "fp16", torch.bfloat16: "bf16", torch.int8: "int8"}
+    B, H, Dk = q.shape
+    NB, BS, Hkv, _ = k_cache.shape
+    if v_cache is None:
+        v_row, dv = Dk, dv
+    else:
+        v_row = v_cache.shape[3]
+        dv = dv or v_row
+    if out is None:
+        out = torch.zeros((B, H, dv), dtype=q.dtype, device=q.device)
+    if plan is None:
+        desc = make_desc(B, H, Hkv, Dk, dv, BS, NB, block_tables.shape[1], name[q.dtype], name[k_cache.dtype],
+                         qk_scale, v_row_dim=v_row, kernel=kernel)
+        plan = PaPlan(desc, context_lens_host)
+    info = plan.info
+    if workspace is None or workspace.numel() < info.workspace_bytes:
+        workspace = torch.empty(max(int(info.workspace_bytes), 256), dtype=torch.uint8, device=q.device)
+    t = pa_tensors(q, k_cache, v_cache, block_tables, out, k_descale, v_descale, k_offset, v_offset)
+    plan.launch(t, ctypes.c_void_p(workspace.data_ptr()), workspace.numel(), torch_stream_ptr())
+    if return_plan:
+        return out, plan, workspace
+    return out
+
+
+def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping):
+    """In-place scatter of the new tokens into the caches (value / value_cache may be None)."""
+    n = key.shape[0]
+    krow = key[0].numel() * key.element_size() if n else 0
+    vrow = value[0].numel() * value.element_size() if (value is not None and n) else 0
+    nslots = key_cache.shape[0] * key_cache.shape[1]
+    _check(lib().atb_b200_reshape_and_cache(_ptr(key), _ptr(value), _ptr(key_cache), _ptr(value_cache),
+                                            _ptr(slot_mapping), n, krow, vrow, nslots, torch_stream_ptr()),
+           "atb_b200_reshape_and_cache")
+
+
+# ------------------------------------------------------------------ operator level
+
+def atb_tensor(t=None, *, dtype=None, shape=None, host=None, device_ptr=None, fmt=ACL_FORMAT_ND):
+    """Builds an atb::Tensor view of a torch tensor (or of an explicit dtype/shape for negative tests)."""
+    a = AtbTensor()
+    if t is not None:
+        import torch
+        code = {torch.float16: ACL_FLOAT16, torch.bfloat16: ACL_BF16, torch.int8: ACL_INT8, torch.int32: ACL_INT32,
+                torch.float32: ACL_FLOAT, torch.int64: ACL_INT64}[t.dtype]
+        shape = tuple(t.shape)
+        a.dtype = code if dtype is None else dtype
+        a.device_data = t.data_ptr() if t.is_cuda else None
+        a.data_size = t.numel() * t.element_size()
+        if not t.is_cuda:
+            a.host_data = t.data_ptr()
+    else:
+        a.dtype = dtype
+        size = {ACL_FLOAT16: 2, ACL_BF16: 2, ACL_INT8: 1, ACL_INT32: 4, ACL_FLOAT: 4, ACL_INT64: 8}.get(dtype, 1)
+        n = 1
+        for s in shape:
+            n *= s
+        a.data_size = n * size
+        a.device_data = device_ptr
+    a.format = fmt
+    a.dim_num = len(shape)
+    for i, s in enumerate(shape):
+        a.dims[i] = s
+    if host is not None:
+        a.host_data = host.ctypes.data
+    return a
+
+
+class Context:
+    def __init__(self, stream_ptr=None):
+        self.handle = ctypes.c_void_p()
+        _check(lib().atb_b200_context_create(ctypes.byref(self.handle)), "atb_b200_context_create")
+        if stream_ptr is not None:
+            self.set_stream(stream_ptr)
+
+    def set_stream(self, stream_ptr):
+        _check(lib().atb_b200_context_set_stream(self.handle, stream_ptr), "atb_b200_context_set_stream")
+
+    def __del__(self):
+        try:
+            if self.handle:
+                lib().atb_b200_context_destroy(self.handle)
+        except Exception:
+            pass
+
+
+class Operation:
+    """atb::Operation behind the C wrappers: create from a param struct, then setup() / execute()."""
+
+    def __init__(self, param):
+        self.handle = ctypes.c_void_p()
+        if isinstance(param, PagedAttentionParam):
+            fn, what = lib().atb_b200_operation_create_paged_attention, "CreateOperation(PagedAttentionParam)"
+        else:
+            fn, what = lib().atb_b200_operation_create_reshape_and_cache, "CreateOperation(ReshapeAndCacheParam)"
+        _check(fn(ctypes.byref(param), ctypes.sizeof(param), ctypes.byref(self.handle)), what)
+
+    @property
+    def input_num(self):
+        n = ctypes.c_uint32()
+        _check(lib().atb_b200_operation_input_num(self.handle, ctypes.byref(n)), "GetInputNum")
+        return n.value
+
+    @property
+    def output_num(self):
+        n = ctypes.c_uint32()
+        _check(lib().atb_b200_operation_output_num(self.handle, ctypes.byref(n)), "GetOutputNum")
+        return n.value
+
+    @staticmethod
+    def _arr(tensors):
+        arr = (AtbTensor * max(len(tensors), 1))()
+        for i, t in enumerate(tensors):
+            arr[i] = t
+        return arr
+
+    def infer_shape(self, ins, n_out):
+        outs = (AtbTensor * n_out)()
+        _check(lib().atb_b200_operation_infer_shape(self.handle, self._arr(ins), len(ins), outs, n_out), "InferShape")
+        return [tuple(outs[i].dims[k] for k in range(outs[i].dim_num)) for i in range(n_out)]
+
+    def setup(self, ins, outs, ctx):
+        ws = ctypes.c_uint64(0)
+        _check(lib().atb_b200_operation_setup(self.handle, self._arr(ins), len(ins), self._arr(outs), len(outs),
+                                              ctypes.byref(ws), ctx.handle if ctx is not None else None), "Setup")
+        return ws.value
+
+    def execute(self, ins, outs, workspace_ptr, workspace_bytes, ctx):
+        _check(lib().atb_b200_operation_execute(self.handle, self._arr(ins), len(ins), self._arr(outs), len(outs),
+                                                workspace_ptr, workspace_bytes,
+                                                ctx.handle if ctx is not None else None), "Execute")
+
+    def __del__(self):
+        try:
+            if self.handle:
+                lib().atb_b200_operation_destroy(self.handle)
+        except Exception:
+            pass

@@ -1,0 +1,425 @@
+// atb::CreateOperation<infer::PagedAttentionParam> and the PagedAttentionOperation behind it.
+// Parameter rules, tensor order and shape checks follow
+// src/ops/ops_infer/paged_attention/paged_attention_operation.cpp of the reference
+// (CreateOperation :92-143, *ParamCheck :145-365, GetInputNum :408-444, InferShapeImpl :451-472,
+//  SetupCheckImpl :492-525, KVCacheDimCheck910B :585-632, SetupDimCheck :926-963); features that
+// need other inputs (masks, batchRunStatus, parallel decoding, logN, head compression, QKV
+// quantisation, BNSD layout) are rejected at CreateOperation with ERROR_INVALID_PARAM.
+#include <cmath>
+#include <cstdlib>
+#include <new>
+#include "../../include/atb_b200.h"
+#include "atb_operation_base.h"
+
+namespace atb {
+namespace {
+
+using Param = infer::PagedAttentionParam;
+
+bool ParamCheck(const Param &p)
+{
+    if (p.headNum <= 0) {
+        ATB_B200_LOG(ERROR, "headNum should be greater than zero");
+        return false;
+    }
+    if (p.kvHeadNum < 0) {
+        ATB_B200_LOG(ERROR, "kvHeadNum should be no less than zero");
+        return false;
+    }
+    if (p.kvHeadNum != 0 && p.headNum % p.kvHeadNum != 0) {
+        ATB_B200_LOG(ERROR, "headNum mod kvHeadNum should be zero");
+        return false;
+    }
+    if (p.compressType >= Param::COMPRESS_TYPE_MAX || p.compressType < Param::COMPRESS_TYPE_UNDEFINED ||
+        p.scaleType >= Param::SCALE_TYPE_MAX || p.scaleType < Param::SCALE_TYPE_TOR) {
+        ATB_B200_LOG(ERROR, "enum parameter out of range");
+        return false;
+    }
+    if (p.quantType == Param::TYPE_DEQUANT_FUSION && p.calcType != Param::CALC_TYPE_UNDEFINED) {
+        ATB_B200_LOG(ERROR, "dequant only supports calcType CALC_TYPE_UNDEFINED");
+        return false;
+    }
+    if (p.mlaVHeadSize > 0) {
+        if (p.maskType == Param::MASK_TYPE_ALIBI || p.compressType != Param::COMPRESS_TYPE_UNDEFINED ||
+            p.quantType == Param::TYPE_DEQUANT_FUSION || p.scaleType != Param::SCALE_TYPE_TOR ||
+            p.inputLayout != infer::TYPE_BSND) {
+            ATB_B200_LOG(ERROR, "mla mode does not support alibi, compress, dequant_fusion, logN or BNSD");
+            return false;
+        }
+        if (p.kvHeadNum != 1) {
+            ATB_B200_LOG(ERROR, "kvHeadNum should be 1, mla mode only supports MQA");
+            return false;
+        }
+        if (p.mlaVHeadSize > 576) {
+            ATB_B200_LOG(ERROR, "mlaVHeadSize should be no greater than 576");
+            return false;
+        }
+    }
+    // Features outside the decode hot path of this build.
+    if (p.maskType != Param::UNDEFINED || p.batchRunStatusEnable || p.compressType != Param::COMPRESS_TYPE_UNDEFINED ||
+        p.calcType != Param::CALC_TYPE_UNDEFINED || p.scaleType != Param::SCALE_TYPE_TOR ||
+        p.inputLayout != infer::TYPE_BSND ||
+        (p.quantType != Param::TYPE_QUANT_UNQUANT && p.quantType != Param::TYPE_DEQUANT_FUSION)) {
+        ATB_B200_LOG(ERROR, "PagedAttention: mask / batchRunStatus / compress / SPEC / logN / BNSD / QKV-quant "
+                            "are not supported by this build");
+        return false;
+    }
+    return true;
+}
+
+int ToKernelDtype(aclDataType t)
+{
+    switch (t) {
+        case ACL_FLOAT16:
+            return ATB_B200_FP16;
+        case ACL_BF16:
+            return ATB_B200_BF16;
+        case ACL_INT8:
+            return ATB_B200_INT8;
+        default:
+            return -1;
+    }
+}
+
+class PagedAttentionOperation : public OperationBase {
+public:
+    explicit PagedAttentionOperation(const Param &p) : OperationBase("PagedAttentionOperation"), param_(p)
+    {
+        const bool mla = p.mlaVHeadSize > 0;
+        const aclDataType halfs[2] = {ACL_FLOAT16, ACL_BF16};
+        for (aclDataType h : halfs) {
+            if (p.quantType == Param::TYPE_DEQUANT_FUSION) {
+                // descale tensors: fp32, the int64-packed fp32 encoding, or (extension) fp16
+                for (aclDataType sc : {ACL_FLOAT, ACL_INT64, ACL_FLOAT16}) {
+                    DtypeComb c = {h, ACL_INT8, ACL_INT8, ACL_INT32, ACL_INT32, sc};
+                    if (p.hasQuantOffset) {
+                        c.push_back(ACL_INT32);
+                    }
+                    c.push_back(sc);
+                    if (p.hasQuantOffset) {
+                        c.push_back(ACL_INT32);
+                    }
+                    c.push_back(h);
+                    combs_.push_back(c);
+                }
+            } else if (mla) {
+                combs_.push_back({h, h, ACL_INT32, ACL_INT32, h});
+            } else {
+                combs_.push_back({h, h, h, ACL_INT32, ACL_INT32, h});
+            }
+        }
+    }
+    ~PagedAttentionOperation() override
+    {
+        if (plan_ != nullptr) {
+            atb_b200_pa_plan_destroy(plan_);
+        }
+        for (void *p : scratch_) {
+            FreeDevice(p);
+        }
+    }
+
+    uint32_t GetInputNum() const override
+    {
+        uint32_t n = 5; // query, keyCache, valueCache, blockTables, contextLens
+        if (param_.quantType == Param::TYPE_DEQUANT_FUSION) {
+            n += param_.hasQuantOffset ? 4 : 2;
+        }
+        if (param_.mlaVHeadSize > 0) {
+            n -= 1; // no valueCache
+        }
+        return n;
+    }
+    uint32_t GetOutputNum() const override { return 1; }
+
+protected:
+    const std::vector<DtypeComb> &DtypeCombs() const override { return combs_; }
+
+    Status InferShapeCheckImpl(const SVector<TensorDesc> &in) const override
+    {
+        const bool mla = param_.mlaVHeadSize > 0;
+        const size_t btPos = mla ? 2 : 3, clPos = mla ? 3 : 4;
+        if (!mla && in.at(2).shape.dimNum != 4) {
+            return ERROR_INVALID_TENSOR_DIM_NUM;
+        }
+        if (in.at(0).shape.dimNum != 3 || in.at(1).shape.dimNum != 4 || in.at(btPos).shape.dimNum != 2 ||
+            in.at(clPos).shape.dimNum != 1) {
+            ATB_B200_LOG(ERROR, "PagedAttention: invalid intensor dimNum");
+            return ERROR_INVALID_TENSOR_DIM_NUM;
+        }
+        const Dims &q = in.at(0).shape, &k = in.at(1).shape;
+        if (q.dims[1] != param_.headNum) {
+            ATB_B200_LOG(ERROR, "PagedAttention: query dim 1 should equal headNum");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        const int64_t kvHeads = param_.kvHeadNum == 0 ? param_.headNum : param_.kvHeadNum;
+        if (k.dims[2] != kvHeads) {
+            ATB_B200_LOG(ERROR, "PagedAttention: keyCache dim 2 should equal kvHeadNum");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (in.at(btPos).shape.dims[0] != q.dims[0] || in.at(clPos).shape.dims[0] != q.dims[0]) {
+            ATB_B200_LOG(ERROR, "PagedAttention: blockTables / contextLens rows should equal query tokens");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (!mla) {
+            const Dims &v = in.at(2).shape;
+            if (k.dims[0] != v.dims[0] || k.dims[1] != v.dims[1] || k.dims[2] != v.dims[2]) {
+                ATB_B200_LOG(ERROR, "PagedAttention: keyCache and valueCache block dims should be the same");
+                return ERROR_INVALID_TENSOR_DIM;
+            }
+        }
+        const int64_t headSize = k.dims[3], blockSize = k.dims[1];
+        if (headSize != q.dims[2]) {
+            ATB_B200_LOG(ERROR, "PagedAttention: headSize of keyCache and query should be same");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (param_.quantType == Param::TYPE_DEQUANT_FUSION) {
+            if (headSize != in.at(2).shape.dims[3]) {
+                return ERROR_INVALID_TENSOR_DIM;
+            }
+            if (headSize > 256 || headSize * blockSize > 128 * 128) {
+                ATB_B200_LOG(ERROR, "PagedAttention: head_size <= 256 and block_size * head_size <= 128*128 required");
+                return ERROR_INVALID_TENSOR_DIM;
+            }
+            const int64_t want = kvHeads * headSize;
+            for (size_t i = 5; i < in.size(); ++i) {
+                if (in.at(i).shape.dimNum != 1 || in.at(i).shape.dims[0] != want) {
+                    ATB_B200_LOG(ERROR, "PagedAttention: descale / offset should have kvHeadNum*headSize elements");
+                    return ERROR_INVALID_TENSOR_DIM;
+                }
+            }
+        } else {
+            if (param_.mlaVHeadSize > headSize) {
+                ATB_B200_LOG(ERROR, "PagedAttention: mlaVHeadSize should be no greater than headSizeK");
+                return ERROR_INVALID_TENSOR_DIM;
+            }
+            const int64_t headSizeV = mla ? param_.mlaVHeadSize : in.at(2).shape.dims[3];
+            if (headSize > 576 || headSizeV > 576) {
+                return ERROR_INVALID_TENSOR_DIM;
+            }
+            if (mla && q.dims[0] > 8192) {
+                return ERROR_INVALID_TENSOR_DIM;
+            }
+            if ((headSize > 256 || headSizeV > 256) && blockSize > 128) {
+                return ERROR_INVALID_TENSOR_DIM;
+            }
+            if (headSize % 4 != 0 || headSizeV % 4 != 0) {
+                ATB_B200_LOG(ERROR, "PagedAttention: head sizes must be multiples of 4");
+                return ERROR_INVALID_TENSOR_DIM;
+            }
+        }
+        return NO_ERROR;
+    }
+
+    Status InferShapeImpl(const SVector<TensorDesc> &in, SVector<TensorDesc> &out) const override
+    {
+        out.at(0) = in.at(0);
+        out.at(0).shape.dims[2] = param_.mlaVHeadSize > 0 ? param_.mlaVHeadSize : in.at(2).shape.dims[3];
+        return NO_ERROR;
+    }
+
+    Status SetupCheckImpl(const SVector<Tensor> &inTensors, const SVector<Tensor> &outTensors) const override
+    {
+        if (inTensors.at(1).desc.shape.dimNum != 4) {
+            return ERROR_INVALID_TENSOR_DIM_NUM;
+        }
+        SVector<TensorDesc> descs;
+        for (size_t i = 0; i < inTensors.size(); ++i) {
+            descs.push_back(inTensors.at(i).desc);
+        }
+        Status st = InferShapeCheckImpl(descs);
+        if (st != NO_ERROR) {
+            return st;
+        }
+        const Dims &o = outTensors.at(0).desc.shape, &q = inTensors.at(0).desc.shape;
+        const int64_t dv = param_.mlaVHeadSize > 0 ? param_.mlaVHeadSize : inTensors.at(2).desc.shape.dims[3];
+        if (o.dimNum != 3 || o.dims[2] != dv) {
+            ATB_B200_LOG(ERROR, "PagedAttention: headSize of attnOut error");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (o.dims[0] != q.dims[0] || o.dims[1] != q.dims[1]) {
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        return NO_ERROR;
+    }
+
+    Status PlanImpl(const VariantPack &vp, uint64_t &workspaceSize) override
+    {
+        const bool mla = param_.mlaVHeadSize > 0;
+        const size_t btPos = mla ? 2 : 3, clPos = mla ? 3 : 4;
+        const Tensor &cl = vp.inTensors.at(clPos);
+        if (cl.hostData == nullptr) {
+            ATB_B200_LOG(ERROR, "PagedAttention: contextLens hostData is null");
+            return ERROR_INVALID_PARAM;
+        }
+        const Dims &q = vp.inTensors.at(0).desc.shape, &k = vp.inTensors.at(1).desc.shape;
+        atb_b200_pa_desc d{};
+        d.batch = static_cast<int32_t>(q.dims[0]);
+        d.num_heads = param_.headNum;
+        d.kv_heads = param_.kvHeadNum == 0 ? param_.headNum : param_.kvHeadNum;
+        d.head_dim_k = static_cast<int32_t>(k.dims[3]);
+        d.head_dim_v = mla ? static_cast<int32_t>(param_.mlaVHeadSize)
+                           : static_cast<int32_t>(vp.inTensors.at(2).desc.shape.dims[3]);
+        d.v_row_dim = mla ? d.head_dim_k : d.head_dim_v;
+        d.block_size = static_cast<int32_t>(k.dims[1]);
+        d.num_blocks = static_cast<int32_t>(k.dims[0]);
+        d.max_blocks_per_seq = static_cast<int32_t>(vp.inTensors.at(btPos).desc.shape.dims[1]);
+        d.q_dtype = ToKernelDtype(vp.inTensors.at(0).desc.dtype);
+        d.kv_dtype = ToKernelDtype(vp.inTensors.at(1).desc.dtype);
+        float scale = param_.qkScale;
+        if (std::fabs(param_.qScale) > 1e-6f && std::fabs(param_.qScale - 1.f) > 1e-6f) {
+            scale *= param_.qScale; // the reference multiplies Q by qScale in a separate node
+        }
+        d.qk_scale = scale;
+        d.kernel = ATB_B200_KERNEL_AUTO;
+        if (const char *force = std::getenv("ATB_B200_FORCE_KERNEL")) {
+            d.kernel = std::atoi(force);
+        }
+        d.sm_count = 0; // the current device's SM count; ATB_B200_SM_COUNT overrides (planning without a GPU)
+        if (const char *sm = std::getenv("ATB_B200_SM_COUNT")) {
+            d.sm_count = std::atoi(sm);
+        }
+        const int32_t *lens = static_cast<const int32_t *>(cl.hostData);
+        int rc;
+        if (plan_ != nullptr && SameDesc(d)) {
+            rc = atb_b200_pa_plan_update(plan_, lens);
+        } else {
+            if (plan_ != nullptr) {
+                atb_b200_pa_plan_destroy(plan_);
+                plan_ = nullptr;
+            }
+            rc = atb_b200_pa_plan_create(&d, lens, &plan_);
+            desc_ = d;
+        }
+        if (rc != 0) {
+            return rc;
+        }
+        atb_b200_pa_plan_info info{};
+        atb_b200_pa_plan_get_info(plan_, &info);
+        workspaceSize = info.workspace_bytes + 256; // room to align the caller's pointer
+        return NO_ERROR;
+    }
+
+    Status LaunchImpl(const VariantPack &vp, uint8_t *workspace, uint64_t workspaceSize, aclrtStream stream) override
+    {
+        const bool mla = param_.mlaVHeadSize > 0;
+        const size_t btPos = mla ? 2 : 3;
+        atb_b200_pa_tensors t{};
+        t.q = vp.inTensors.at(0).deviceData;
+        t.k_cache = vp.inTensors.at(1).deviceData;
+        t.v_cache = mla ? t.k_cache : vp.inTensors.at(2).deviceData;
+        t.block_tables = static_cast<const int32_t *>(vp.inTensors.at(btPos).deviceData);
+        t.out = vp.outTensors.at(0).deviceData;
+        if (param_.quantType == Param::TYPE_DEQUANT_FUSION) {
+            // runner order: kDescale, [kOffset], vDescale, [vOffset]
+            size_t i = 5;
+            const Tensor &ks = vp.inTensors.at(i++);
+            const Tensor *ko = param_.hasQuantOffset ? &vp.inTensors.at(i++) : nullptr;
+            const Tensor &vs = vp.inTensors.at(i++);
+            const Tensor *vo = param_.hasQuantOffset ? &vp.inTensors.at(i++) : nullptr;
+            Status st = ScaleAsFloat(ks, 0, stream, &t.k_descale);
+            if (st != NO_ERROR) {
+                return st;
+            }
+            st = ScaleAsFloat(vs, 1, stream, &t.v_descale);
+            if (st != NO_ERROR) {
+                return st;
+            }
+            t.k_offset = ko ? static_cast<const int32_t *>(ko->deviceData) : nullptr;
+            t.v_offset = vo ? static_cast<const int32_t *>(vo->deviceData) : nullptr;
+        }
+        if (t.q == nullptr || t.k_cache == nullptr || t.v_cache == nullptr || t.block_tables == nullptr ||
+            t.out == nullptr) {
+            return ERROR_INVALID_PARAM;
+        }
+        uint8_t *ws = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255));
+        const uint64_t usable = workspaceSize - static_cast<uint64_t>(ws - workspace);
+        const int rc = atb_b200_pa_launch(plan_, &t, ws, usable, stream);
+        return rc == 0 ? NO_ERROR : (rc == ERROR_INVALID_PARAM ? ERROR_INVALID_PARAM : ERROR_RT_FAIL);
+    }
+
+private:
+    bool SameDesc(const atb_b200_pa_desc &d) const
+    {
+        return d.batch == desc_.batch && d.num_heads == desc_.num_heads && d.kv_heads == desc_.kv_heads &&
+               d.head_dim_k == desc_.head_dim_k && d.head_dim_v == desc_.head_dim_v && d.v_row_dim == desc_.v_row_dim &&
+               d.block_size == desc_.block_size && d.num_blocks == desc_.num_blocks &&
+               d.max_blocks_per_seq == desc_.max_blocks_per_seq && d.q_dtype == desc_.q_dtype &&
+               d.kv_dtype == desc_.kv_dtype && d.qk_scale == desc_.qk_scale && d.kernel == desc_.kernel;
+    }
+    // fp32 scales are used in place; the int64-packed and fp16 encodings are converted once per
+    // launch into a small device buffer owned by the operation.
+    Status ScaleAsFloat(const Tensor &t, int which, aclrtStream stream, const float **out);
+    static void FreeDevice(void *p);
+
+    Param param_;
+    std::vector<DtypeComb> combs_;
+    atb_b200_pa_plan *plan_ = nullptr;
+    atb_b200_pa_desc desc_{};
+    void *scratch_[2] = {nullptr, nullptr};
+    uint64_t scratchElems_[2] = {0, 0};
+};
+
+} // namespace
+
+// implemented in atb_scale_convert.cu (needs device code)
+extern "C" int atb_b200_internal_convert_scales(const void *src, int src_kind, float *dst, uint64_t n, void *stream);
+extern "C" int atb_b200_internal_device_alloc(void **p, uint64_t bytes);
+extern "C" void atb_b200_internal_device_free(void *p);
+
+namespace {
+Status PagedAttentionOperation::ScaleAsFloat(const Tensor &t, int which, aclrtStream stream, const float **out)
+{
+    if (t.deviceData == nullptr) {
+        return ERROR_INVALID_PARAM;
+    }
+    if (t.desc.dtype == ACL_FLOAT) {
+        *out = static_cast<const float *>(t.deviceData);
+        return NO_ERROR;
+    }
+    const uint64_t n = Utils::GetTensorNumel(t.desc);
+    if (scratchElems_[which] < n) {
+        FreeDevice(scratch_[which]);
+        scratch_[which] = nullptr;
+        if (atb_b200_internal_device_alloc(&scratch_[which], n * sizeof(float)) != 0) {
+            scratchElems_[which] = 0;
+            return ERROR_OUT_OF_DEVICE_MEMORY;
+        }
+        scratchElems_[which] = n;
+    }
+    const int kind = t.desc.dtype == ACL_INT64 ? 1 : 2; // 1: fp32 bits in int64 words, 2: fp16
+    if (atb_b200_internal_convert_scales(t.deviceData, kind, static_cast<float *>(scratch_[which]), n, stream) != 0) {
+        return ERROR_RT_FAIL;
+    }
+    *out = static_cast<const float *>(scratch_[which]);
+    return NO_ERROR;
+}
+
+void PagedAttentionOperation::FreeDevice(void *p)
+{
+    if (p != nullptr) {
+        atb_b200_internal_device_free(p);
+    }
+}
+} // namespace
+
+template <> Status CreateOperation(const infer::PagedAttentionParam &opParam, Operation **operation)
+{
+    if (operation == nullptr) {
+        return ERROR_INVALID_PARAM;
+    }
+    if (!RsvIsZero(opParam.rsv, sizeof(opParam.rsv))) {
+        ATB_B200_LOG(ERROR, "PagedAttentionParam.rsv must be zero");
+        return ERROR_INVALID_PARAM;
+    }
+    if (!ParamCheck(opParam)) {
+        return ERROR_INVALID_PARAM;
+    }
+    *operation = new (std::nothrow) PagedAttentionOperation(opParam);
+    if (*operation == nullptr) {
+        return ERROR_OUT_OF_HOST_MEMORY;
+    }
+    return NO_ERROR;
+}
+
+} // namespace atb

@@ -1,0 +1,297 @@
+// extern "C" boundary of libatb_b200.so (see include/atb_b200.h).
+#include <cuda_runtime.h>
+#include <cmath>
+#include <cstring>
+#include <new>
+#include "../../include/atb_b200.h"
+#include "kernels.h"
+#include "pa_planner.h"
+
+using namespace atb_b200;
+
+namespace {
+constexpr int kErrInvalidParam = 1; // atb::ERROR_INVALID_PARAM
+constexpr int kErrRtFail = 4;       // atb::ERROR_RT_FAIL
+constexpr int kErrOutOfHostMemory = 27;
+} // namespace
+
+struct atb_b200_pa_plan {
+    HostPlan hp;
+    uint8_t *staging = nullptr; // pinned copy of the plan blob
+    size_t staging_cap = 0;
+    cudaEvent_t uploaded = nullptr;
+    bool upload_pending = false;
+    bool profile = false;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    int32_t *status_host = nullptr;
+};
+
+extern "C" {
+
+const char *atb_b200_version(void) { return "atb-b200 0.1 (API level of ascend-transformer-boost 8.5.0)"; }
+
+int atb_b200_pa_plan_create(const atb_b200_pa_desc *desc, const int32_t *context_lens_host, atb_b200_pa_plan **plan)
+{
+    if (desc == nullptr || plan == nullptr) {
+        return kErrInvalidParam;
+    }
+    int sm = desc->sm_count;
+    if (sm <= 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm <= 0) {
+            return kErrRtFail;
+        }
+    }
+    atb_b200_pa_plan *p = new (std::nothrow) atb_b200_pa_plan();
+    if (p == nullptr) {
+        return kErrOutOfHostMemory;
+    }
+    int rc;
+    try {
+        rc = plan_paged_attention(*desc, context_lens_host, sm, &p->hp);
+    } catch (...) {
+        rc = kErrOutOfHostMemory;
+    }
+    if (rc != 0) {
+        delete p;
+        return rc;
+    }
+    *plan = p;
+    return ATB_B200_OK;
+}
+
+int atb_b200_pa_plan_update(atb_b200_pa_plan *plan, const int32_t *context_lens_host)
+{
+    if (plan == nullptr) {
+        return kErrInvalidParam;
+    }
+    try {
+        const atb_b200_pa_desc d = plan->hp.desc;
+        return plan_paged_attention(d, context_lens_host, plan->hp.sm_count, &plan->hp);
+    } catch (...) {
+        return kErrOutOfHostMemory;
+    }
+}
+
+int atb_b200_pa_plan_get_info(const atb_b200_pa_plan *plan, atb_b200_pa_plan_info *info)
+{
+    if (plan == nullptr || info == nullptr) {
+        return kErrInvalidParam;
+    }
+    const HostPlan &h = plan->hp;
+    info->kernel = h.kernel;
+    info->num_ctas = h.n_cta_groups * h.cols;
+    info->num_items = (int32_t)h.items.size();
+    info->num_partials = h.n_partials;
+    info->num_combine_seqs = (int32_t)h.combine_seqs.size();
+    info->tile_tokens = kTileTokens;
+    info->workspace_bytes = h.workspace_bytes;
+    info->plan_bytes = h.blob_bytes;
+    return ATB_B200_OK;
+}
+
+int atb_b200_pa_plan_dump(const atb_b200_pa_plan *plan, int32_t *items, int32_t max_items, int32_t *group_begin,
+                          int32_t max_groups)
+{
+    if (plan == nullptr) {
+        return kErrInvalidParam;
+    }
+    const HostPlan &h = plan->hp;
+    if (items != nullptr) {
+        if ((size_t)max_items < h.items.size()) {
+            return kErrInvalidParam;
+        }
+        std::memcpy(items, h.items.data(), h.items.size() * sizeof(PaItem));
+    }
+    if (group_begin != nullptr) {
+        if ((size_t)max_groups < h.group_begin.size()) {
+            return kErrInvalidParam;
+        }
+        std::memcpy(group_begin, h.group_begin.data(), h.group_begin.size() * sizeof(int32_t));
+    }
+    return ATB_B200_OK;
+}
+
+void atb_b200_pa_plan_destroy(atb_b200_pa_plan *plan)
+{
+    if (plan == nullptr) {
+        return;
+    }
+    if (plan->uploaded != nullptr) {
+        cudaEventSynchronize(plan->uploaded);
+        cudaEventDestroy(plan->uploaded);
+    }
+    if (plan->ev0 != nullptr) {
+        cudaEventDestroy(plan->ev0);
+        cudaEventDestroy(plan->ev1);
+    }
+    if (plan->staging != nullptr) {
+        cudaFreeHost(plan->staging);
+    }
+    if (plan->status_host != nullptr) {
+        cudaFreeHost(plan->status_host);
+    }
+    delete plan;
+}
+
+int atb_b200_pa_plan_set_profiling(atb_b200_pa_plan *plan, int enable)
+{
+    if (plan == nullptr) {
+        return kErrInvalidParam;
+    }
+    if (enable && plan->ev0 == nullptr) {
+        if (cudaEventCreate(&plan->ev0) != cudaSuccess || cudaEventCreate(&plan->ev1) != cudaSuccess) {
+            return kErrRtFail;
+        }
+    }
+    plan->profile = enable != 0;
+    return ATB_B200_OK;
+}
+
+int atb_b200_pa_plan_last_kernel_ms(atb_b200_pa_plan *plan, float *ms)
+{
+    if (plan == nullptr || ms == nullptr || plan->ev0 == nullptr) {
+        return kErrInvalidParam;
+    }
+    if (cudaEventSynchronize(plan->ev1) != cudaSuccess || cudaEventElapsedTime(ms, plan->ev0, plan->ev1) != cudaSuccess) {
+        return kErrRtFail;
+    }
+    return ATB_B200_OK;
+}
+
+int atb_b200_pa_launch(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, void *workspace, uint64_t workspace_bytes,
+                       void *stream_v)
+{
+    if (plan == nullptr || t == nullptr || t->q == nullptr || t->k_cache == nullptr || t->v_cache == nullptr ||
+        t->block_tables == nullptr || t->out == nullptr) {
+        return kErrInvalidParam;
+    }
+    HostPlan &h = plan->hp;
+    if (workspace_bytes < h.workspace_bytes || (h.workspace_bytes > 0 && workspace == nullptr) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) {
+        return kErrInvalidParam;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    if (h.items.empty()) {
+        return ATB_B200_OK; // every sequence is empty: outputs stay untouched
+    }
+    // ---- upload the plan (pinned staging, one async copy)
+    if (plan->staging_cap < h.blob_bytes) {
+        if (plan->upload_pending) {
+            cudaEventSynchronize(plan->uploaded);
+            plan->upload_pending = false;
+        }
+        if (plan->staging != nullptr) {
+            cudaFreeHost(plan->staging);
+            plan->staging = nullptr;
+        }
+        const size_t cap = (size_t)h.blob_bytes * 2;
+        if (cudaHostAlloc(reinterpret_cast<void **>(&plan->staging), cap, cudaHostAllocDefault) != cudaSuccess) {
+            plan->staging_cap = 0;
+            return kErrOutOfHostMemory;
+        }
+        plan->staging_cap = cap;
+    }
+    if (plan->uploaded == nullptr && cudaEventCreateWithFlags(&plan->uploaded, cudaEventDisableTiming) != cudaSuccess) {
+        return kErrRtFail;
+    }
+    if (plan->upload_pending) {
+        cudaEventSynchronize(plan->uploaded); // the previous copy out of the staging buffer must be done
+    }
+    h.write_blob(plan->staging);
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
+    if (cudaMemcpyAsync(ws, plan->staging, h.blob_bytes, cudaMemcpyHostToDevice, stream) != cudaSuccess) {
+        return kErrRtFail;
+    }
+    cudaEventRecord(plan->uploaded, stream);
+    plan->upload_pending = true;
+
+    const atb_b200_pa_desc &d = h.desc;
+    PaArgs a{};
+    a.q = t->q;
+    a.k_cache = t->k_cache;
+    a.v_cache = t->v_cache;
+    a.block_tables = t->block_tables;
+    a.k_descale = t->k_descale;
+    a.v_descale = t->v_descale;
+    a.k_offset = t->k_offset;
+    a.v_offset = t->v_offset;
+    a.out = t->out;
+    a.plan.group_begin = reinterpret_cast<const int32_t *>(ws + h.off_group_begin);
+    a.plan.items = reinterpret_cast<const PaItem *>(ws + h.off_items);
+    a.plan.seq_part_base = reinterpret_cast<const int32_t *>(ws + h.off_part_base);
+    a.plan.seq_nparts = reinterpret_cast<const int32_t *>(ws + h.off_nparts);
+    a.plan.combine_seqs = reinterpret_cast<const int32_t *>(ws + h.off_combine);
+    a.plan.part_o = reinterpret_cast<float *>(ws + h.off_part_o);
+    a.plan.part_lse = reinterpret_cast<float *>(ws + h.off_lse);
+    a.plan.status = reinterpret_cast<int32_t *>(ws + h.off_status);
+    a.plan.n_cta_groups = h.n_cta_groups;
+    a.plan.cols = h.cols;
+    a.batch = d.batch;
+    a.num_heads = d.num_heads;
+    a.kv_heads = d.kv_heads;
+    a.group = d.num_heads / d.kv_heads;
+    a.dk = d.head_dim_k;
+    a.dv = d.head_dim_v;
+    a.v_row_dim = d.v_row_dim;
+    a.block_size = d.block_size;
+    a.max_blocks = d.max_blocks_per_seq;
+    a.heads_per_cta = h.heads_per_cta;
+    a.chunks_per_kvh = h.chunks_per_kvh;
+    a.scale_log2 = d.qk_scale * 1.4426950408889634f;
+
+    if (plan->profile) {
+        cudaEventRecord(plan->ev0, stream);
+    }
+    cudaError_t e;
+    if (h.kernel == ATB_B200_KERNEL_TMA_MMA) {
+        e = launch_pa_tma_mma(a, d.q_dtype, d.kv_dtype, d.num_blocks, stream);
+    } else {
+        e = launch_pa_generic(a, d.q_dtype, d.kv_dtype, stream);
+    }
+    if (plan->profile) {
+        cudaEventRecord(plan->ev1, stream);
+    }
+    if (e != cudaSuccess) {
+        return kErrRtFail;
+    }
+    e = launch_pa_combine(a, (int)h.combine_seqs.size(), d.q_dtype, stream);
+    return e == cudaSuccess ? ATB_B200_OK : kErrRtFail;
+}
+
+int atb_b200_pa_plan_device_status(atb_b200_pa_plan *plan, void *workspace, void *stream_v, int32_t *status)
+{
+    if (plan == nullptr || status == nullptr || workspace == nullptr) {
+        return kErrInvalidParam;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    if (plan->status_host == nullptr &&
+        cudaHostAlloc(reinterpret_cast<void **>(&plan->status_host), 64, cudaHostAllocDefault) != cudaSuccess) {
+        return kErrOutOfHostMemory;
+    }
+    const uint8_t *ws = static_cast<const uint8_t *>(workspace);
+    if (cudaMemcpyAsync(plan->status_host, ws + plan->hp.off_status, sizeof(int32_t), cudaMemcpyDeviceToHost, stream) !=
+            cudaSuccess ||
+        cudaStreamSynchronize(stream) != cudaSuccess) {
+        return kErrRtFail;
+    }
+    *status = *plan->status_host;
+    return ATB_B200_OK;
+}
+
+int atb_b200_reshape_and_cache(const void *key, const void *value, void *key_cache, void *value_cache,
+                               const int32_t *slot_mapping, int32_t num_tokens, int64_t k_row_bytes,
+                               int64_t v_row_bytes, int64_t num_slots, void *stream)
+{
+    if (slot_mapping == nullptr || num_tokens < 0 || k_row_bytes < 0 || v_row_bytes < 0 || num_slots < 0 ||
+        ((key == nullptr) != (key_cache == nullptr)) || ((value == nullptr) != (value_cache == nullptr)) ||
+        (key == nullptr && value == nullptr)) {
+        return kErrInvalidParam;
+    }
+    cudaError_t e = launch_reshape_and_cache(key, value, key_cache, value_cache, slot_mapping, num_tokens, k_row_bytes,
+                                             v_row_bytes, num_slots, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? ATB_B200_OK : kErrRtFail;
+}
+
+} // extern "C"

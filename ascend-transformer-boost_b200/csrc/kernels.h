@@ -1,0 +1,28 @@
+// Host-side launchers of the CUDA kernels (internal to the library).
+#ifndef ATB_B200_KERNELS_H
+#define ATB_B200_KERNELS_H
+#include <cuda_runtime.h>
+#include "pa_plan.h"
+
+namespace atb_b200 {
+
+enum DType : int { kFp16 = 0, kBf16 = 1, kInt8 = 2 };
+
+cudaError_t launch_reshape_and_cache(const void *key, const void *value, void *key_cache, void *value_cache,
+                                     const int32_t *slot_mapping, int32_t num_tokens, int64_t k_row_bytes,
+                                     int64_t v_row_bytes, int64_t num_slots, cudaStream_t stream);
+
+// CUDA-core decode attention for any head size / block size / head grouping.
+bool pa_generic_supported(int dk, int dv, int q_dtype, int kv_dtype);
+int pa_generic_heads_per_cta(int dk, int dv);
+cudaError_t launch_pa_generic(const PaArgs &args, int q_dtype, int kv_dtype, cudaStream_t stream);
+
+// TMA page gather + mma.sync tiles: D = 128, block_size = 128, up to 8 query heads per kv head.
+bool pa_tma_mma_supported(int dk, int dv, int v_row_dim, int block_size, int group, int q_dtype, int kv_dtype);
+cudaError_t launch_pa_tma_mma(const PaArgs &args, int q_dtype, int kv_dtype, int num_blocks, cudaStream_t stream);
+
+// Merges the split-KV partials of every split sequence into the output.
+cudaError_t launch_pa_combine(const PaArgs &args, int n_combine_seqs, int q_dtype, cudaStream_t stream);
+
+} // namespace atb_b200
+#endif

@@ -1,0 +1,68 @@
+// Split-KV combine: merges the partial results of every sequence that was cut into several token
+// ranges.  Each partial holds a normalised fp32 output and the log2-domain log-sum-exp of its
+// range; the merge weight of partial i is 2^(lse_i - lse_max) / sum_j 2^(lse_j - lse_max), the
+// same LSE merge as CombineScale in the reference
+// (src/kernels/mixkernels/pagedattention/op_kernel/paged_attention_decoder_nd_common.cce:6568-6700).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace atb_b200 {
+namespace {
+
+constexpr int kMaxPartsShared = 512;
+
+template <typename TQ>
+__global__ void __launch_bounds__(128) pa_combine_kernel(const PaArgs a)
+{
+    __shared__ float w[kMaxPartsShared];
+    const int seq = a.plan.combine_seqs[blockIdx.x];
+    const int h = blockIdx.y;
+    const int base = a.plan.seq_part_base[seq];
+    const int n = a.plan.seq_nparts[seq];
+    const float *lse = a.plan.part_lse + (int64_t)base * a.num_heads + h;
+    float mx = -INFINITY;
+    for (int i = 0; i < n; ++i) {
+        mx = fmaxf(mx, lse[(int64_t)i * a.num_heads]);
+    }
+    float sum = 0.f;
+    for (int i = 0; i < n; ++i) {
+        sum += exp2f(lse[(int64_t)i * a.num_heads] - mx);
+    }
+    const float inv = 1.f / sum;
+    const bool use_shared = n <= kMaxPartsShared;
+    if (use_shared) {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            w[i] = exp2f(lse[(int64_t)i * a.num_heads] - mx) * inv;
+        }
+        __syncthreads();
+    }
+    TQ *out = static_cast<TQ *>(a.out) + ((int64_t)seq * a.num_heads + h) * a.dv;
+    const float *po = a.plan.part_o + ((int64_t)base * a.num_heads + h) * a.dv;
+    const int64_t stride = (int64_t)a.num_heads * a.dv;
+    for (int d = threadIdx.x; d < a.dv; d += blockDim.x) {
+        float acc = 0.f;
+        for (int i = 0; i < n; ++i) {
+            const float wi = use_shared ? w[i] : exp2f(lse[(int64_t)i * a.num_heads] - mx) * inv;
+            acc = fmaf(wi, po[i * stride + d], acc);
+        }
+        out[d] = Elem<TQ>::from_float(acc);
+    }
+}
+
+} // namespace
+
+cudaError_t launch_pa_combine(const PaArgs &args, int n_combine_seqs, int q_dtype, cudaStream_t stream)
+{
+    if (n_combine_seqs <= 0) {
+        return cudaSuccess;
+    }
+    dim3 grid(n_combine_seqs, args.num_heads);
+    if (q_dtype == kFp16) {
+        pa_combine_kernel<__half><<<grid, 128, 0, stream>>>(args);
+    } else {
+        pa_combine_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(args);
+    }
+    return cudaGetLastError();
+}
+
+} // namespace atb_b200

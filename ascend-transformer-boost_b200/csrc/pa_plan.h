@@ -1,0 +1,64 @@
+// Work decomposition shared by the host planner and the device kernels.
+//
+// The attention grid is n_cta_groups x cols CTAs.  A column is one kv head (or one chunk of the
+// query heads of one kv head); a CTA group owns a contiguous slice of the global sequence of
+// 128-token tiles, cut so that every group streams the same number of tiles (split-KV with exact
+// balance).  All columns of a group walk the same token ranges, so the 8 kv-head slices of one
+// cache page are read at about the same time.  A sequence cut into several ranges yields one fp32
+// partial result per range, merged by the combine kernel with their log-sum-exp weights.
+//
+// Stands in for the core-split / split-KV tiling of the reference
+// (src/kernels/mixkernels/pagedattention/tiling/paged_attention_tiling_dependency.cpp:186-212, 406-521).
+#ifndef ATB_B200_PA_PLAN_H
+#define ATB_B200_PA_PLAN_H
+#include <stdint.h>
+
+namespace atb_b200 {
+
+constexpr int kTileTokens = 128;
+
+// One contiguous token range of one sequence.  `slot` is the index of the partial result the range
+// writes, or -1 when the range is the whole sequence and the kernel writes the final output.
+struct PaItem {
+    int32_t seq;
+    int32_t tok_begin;
+    int32_t tok_end;
+    int32_t slot;
+};
+
+// Device view of a plan, passed by value to the kernels.
+struct PaDevPlan {
+    const int32_t *group_begin;   // [n_cta_groups + 1] offsets into items
+    const PaItem *items;          // [n_items]
+    const int32_t *seq_part_base; // [batch] first partial slot of a split sequence
+    const int32_t *seq_nparts;    // [batch] 0 (empty), 1 (direct) or the number of partials
+    const int32_t *combine_seqs;  // [n_combine_seqs] sequences with nparts > 1
+    float *part_o;                // [n_partials, num_heads, dv] normalised partial outputs
+    float *part_lse;              // [n_partials, num_heads] log2-domain log-sum-exp
+    int32_t *status;              // device status word (0 = ok)
+    int32_t n_cta_groups;
+    int32_t cols;
+};
+
+// Kernel arguments common to all attention kernels.
+struct PaArgs {
+    const void *q;
+    const void *k_cache;
+    const void *v_cache;
+    const int32_t *block_tables;
+    const float *k_descale;
+    const float *v_descale;
+    const int32_t *k_offset;
+    const int32_t *v_offset;
+    void *out;
+    PaDevPlan plan;
+    int32_t batch, num_heads, kv_heads, group; // group = num_heads / kv_heads
+    int32_t dk, dv, v_row_dim, block_size, max_blocks;
+    int32_t heads_per_cta, chunks_per_kvh;     // generic kernel: head chunking inside a kv head
+    float scale_log2;                          // qk_scale * log2(e)
+};
+
+enum PaDeviceStatus : int32_t { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusBadBlockId = 2 };
+
+} // namespace atb_b200
+#endif

@@ -1,0 +1,182 @@
+#include "pa_planner.h"
+#include <algorithm>
+#include <cstring>
+#include "kernels.h"
+
+namespace atb_b200 {
+namespace {
+constexpr int kErrInvalidParam = 1;     // atb::ERROR_INVALID_PARAM
+constexpr int kErrInvalidTensorDim = 8; // atb::ERROR_INVALID_TENSOR_DIM
+
+uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+} // namespace
+
+void HostPlan::write_blob(uint8_t *dst) const
+{
+    std::memset(dst, 0, blob_bytes);
+    std::memcpy(dst + off_group_begin, group_begin.data(), group_begin.size() * sizeof(int32_t));
+    if (!items.empty()) {
+        std::memcpy(dst + off_items, items.data(), items.size() * sizeof(PaItem));
+    }
+    std::memcpy(dst + off_part_base, seq_part_base.data(), seq_part_base.size() * sizeof(int32_t));
+    std::memcpy(dst + off_nparts, seq_nparts.data(), seq_nparts.size() * sizeof(int32_t));
+    if (!combine_seqs.empty()) {
+        std::memcpy(dst + off_combine, combine_seqs.data(), combine_seqs.size() * sizeof(int32_t));
+    }
+}
+
+int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens, int sm_count, HostPlan *p)
+{
+    if (p == nullptr || (context_lens == nullptr && d.batch > 0) || sm_count <= 0) {
+        return kErrInvalidParam;
+    }
+    if (d.batch < 0 || d.num_heads <= 0 || d.kv_heads <= 0 || d.num_heads % d.kv_heads != 0 || d.head_dim_k <= 0 ||
+        d.head_dim_v <= 0 || d.v_row_dim < d.head_dim_v || d.block_size <= 0 || d.num_blocks <= 0 ||
+        d.max_blocks_per_seq <= 0) {
+        return kErrInvalidParam;
+    }
+    for (int r : d.reserved) {
+        if (r != 0) {
+            return kErrInvalidParam;
+        }
+    }
+    const int group = d.num_heads / d.kv_heads;
+    const bool tma_ok = pa_tma_mma_supported(d.head_dim_k, d.head_dim_v, d.v_row_dim, d.block_size, group, d.q_dtype,
+                                             d.kv_dtype);
+    const bool gen_ok = pa_generic_supported(d.head_dim_k, d.head_dim_v, d.q_dtype, d.kv_dtype);
+    int kernel = d.kernel;
+    if (kernel == ATB_B200_KERNEL_AUTO) {
+        kernel = tma_ok ? ATB_B200_KERNEL_TMA_MMA : ATB_B200_KERNEL_GENERIC;
+    }
+    if ((kernel == ATB_B200_KERNEL_TMA_MMA && !tma_ok) || (kernel == ATB_B200_KERNEL_GENERIC && !gen_ok) ||
+        (kernel != ATB_B200_KERNEL_TMA_MMA && kernel != ATB_B200_KERNEL_GENERIC)) {
+        return kErrInvalidTensorDim;
+    }
+
+    p->desc = d;
+    p->kernel = kernel;
+    p->sm_count = sm_count;
+    if (kernel == ATB_B200_KERNEL_TMA_MMA) {
+        p->heads_per_cta = 8;
+        p->chunks_per_kvh = 1;
+        p->ctas_per_sm = 2;
+    } else {
+        p->heads_per_cta = pa_generic_heads_per_cta(d.head_dim_k, d.head_dim_v);
+        p->chunks_per_kvh = (group + p->heads_per_cta - 1) / p->heads_per_cta;
+        p->ctas_per_sm = 4;
+    }
+    p->cols = d.kv_heads * p->chunks_per_kvh;
+
+    // ---- balanced cut of the global tile sequence into CTA groups
+    const int64_t max_ctx = (int64_t)d.max_blocks_per_seq * d.block_size;
+    int64_t total_tiles = 0;
+    for (int b = 0; b < d.batch; ++b) {
+        const int64_t ctx = context_lens[b];
+        if (ctx < 0 || ctx > max_ctx) {
+            return kErrInvalidParam; // a length the block table cannot describe
+        }
+        total_tiles += (ctx + kTileTokens - 1) / kTileTokens;
+    }
+    const int slots = sm_count * p->ctas_per_sm;
+    int64_t n_groups = std::max<int64_t>(1, slots / p->cols);
+    if (n_groups < 4) {
+        n_groups = 4; // many columns: still cut long sequences a little for balance
+    }
+    n_groups = std::min<int64_t>(n_groups, std::max<int64_t>(total_tiles, 1));
+
+    // Group j owns the global tile positions [cut[j], cut[j+1]).  The ideal cut j*total/n is moved
+    // onto a sequence boundary when that is at most one tile away (a one-tile fragment costs about
+    // as much in per-range overhead as it saves in balance); cuts are absolute positions, so the
+    // rounding never accumulates and every group stays within ~one tile of the mean.
+    std::vector<int64_t> seq_start(d.batch + 1, 0);
+    for (int b = 0; b < d.batch; ++b) {
+        seq_start[b + 1] = seq_start[b] + ((int64_t)context_lens[b] + kTileTokens - 1) / kTileTokens;
+    }
+    const int64_t snap = (total_tiles / n_groups >= 8) ? 1 : 0;
+    std::vector<int64_t> cut(n_groups + 1, 0);
+    cut[n_groups] = total_tiles;
+    {
+        int b = 0;
+        for (int64_t j = 1; j < n_groups; ++j) {
+            int64_t pos = (j * total_tiles) / n_groups;
+            while (b < d.batch && seq_start[b + 1] <= pos) {
+                ++b;
+            }
+            if (b < d.batch && pos > seq_start[b]) {
+                if (pos - seq_start[b] <= snap) {
+                    pos = seq_start[b];
+                } else if (seq_start[b + 1] - pos <= snap) {
+                    pos = seq_start[b + 1];
+                }
+            }
+            cut[j] = std::max(pos, cut[j - 1]);
+        }
+    }
+
+    p->items.clear();
+    p->group_begin.assign(1, 0);
+    p->seq_part_base.assign(d.batch, 0);
+    p->seq_nparts.assign(d.batch, 0);
+    p->combine_seqs.clear();
+    p->n_partials = 0;
+    {
+        int b = 0;
+        for (int64_t j = 0; j < n_groups; ++j) {
+            int64_t pos = cut[j];
+            const int64_t end = cut[j + 1];
+            while (pos < end) {
+                while (seq_start[b + 1] <= pos) {
+                    ++b;
+                }
+                const int64_t stop = std::min(end, seq_start[b + 1]);
+                PaItem item;
+                item.seq = b;
+                item.tok_begin = (int32_t)((pos - seq_start[b]) * kTileTokens);
+                item.tok_end = (int32_t)std::min<int64_t>(context_lens[b], (stop - seq_start[b]) * kTileTokens);
+                item.slot = -1;
+                p->items.push_back(item);
+                p->seq_nparts[b] += 1;
+                pos = stop;
+            }
+            p->group_begin.push_back((int32_t)p->items.size());
+        }
+    }
+    // items of one sequence are consecutive in the list: number its partial slots
+    for (size_t i = 0; i < p->items.size();) {
+        const int b = p->items[i].seq;
+        const int nparts = p->seq_nparts[b];
+        if (nparts > 1) {
+            p->seq_part_base[b] = p->n_partials;
+            for (int k = 0; k < nparts; ++k) {
+                p->items[i + k].slot = p->n_partials + k;
+            }
+            p->n_partials += nparts;
+            p->combine_seqs.push_back(b);
+        }
+        i += nparts;
+    }
+    p->n_cta_groups = (int)p->group_begin.size() - 1;
+
+    // ---- workspace layout
+    uint64_t off = 0;
+    p->off_group_begin = off;
+    off = align_up(off + p->group_begin.size() * sizeof(int32_t), 16);
+    p->off_items = off;
+    off = align_up(off + p->items.size() * sizeof(PaItem), 16);
+    p->off_part_base = off;
+    off = align_up(off + (uint64_t)d.batch * sizeof(int32_t), 16);
+    p->off_nparts = off;
+    off = align_up(off + (uint64_t)d.batch * sizeof(int32_t), 16);
+    p->off_combine = off;
+    off = align_up(off + p->combine_seqs.size() * sizeof(int32_t), 16);
+    p->off_status = off; // zeroed by every upload
+    off += 16;
+    p->blob_bytes = align_up(off, 256);
+    p->off_lse = p->blob_bytes;
+    p->off_part_o = align_up(p->off_lse + (uint64_t)p->n_partials * d.num_heads * sizeof(float), 256);
+    p->workspace_bytes =
+        align_up(p->off_part_o + (uint64_t)p->n_partials * d.num_heads * d.head_dim_v * sizeof(float), 256);
+    return 0;
+}
+
+} // namespace atb_b200

@@ -1,0 +1,70 @@
+// Parameter structs of the two operators on the decode path, byte-compatible with
+// include/atb/infer_op_params.h of the reference: ReshapeAndCacheParam :488-526 (24 bytes),
+// PagedAttentionParam :1859-1963 (120 bytes); sizes pinned by tests/unittest/ops/test_op_param_size.cpp:47,51.
+#ifndef ATB_INFER_OP_PARAMS_H
+#define ATB_INFER_OP_PARAMS_H
+#include <cstdint>
+#include <acl/acl.h>
+
+namespace atb {
+namespace infer {
+enum InputLayout : int { TYPE_BSND = 0, TYPE_BNSD };
+
+struct ReshapeAndCacheParam {
+    enum CompressType : int { COMPRESS_TYPE_UNDEFINED = 0, COMPRESS_TYPE_KVHEAD, COMPRESS_TYPE_KVHEAD_ROPE };
+    enum KvCacheCfg : int {
+        K_CACHE_V_CACHE = 0, // key/value + both caches (5 inputs, 2 outputs)
+        K_CACHE_V_BYPASS,    // key + key cache only (3 inputs, 1 output), e.g. the MLA combined cache
+        K_CACHE_V_CACHE_NZ   // fractal layout of another SoC; rejected here
+    };
+    CompressType compressType = COMPRESS_TYPE_UNDEFINED;
+    KvCacheCfg kvCacheCfg = K_CACHE_V_CACHE;
+    uint8_t rsv[16] = {0};
+};
+
+struct PagedAttentionParam {
+    int32_t headNum = 0;   // query heads
+    float qkScale = 1.0;   // multiplies Q*K^T
+    int32_t kvHeadNum = 0; // 0 = same as headNum
+    enum MaskType : int {
+        UNDEFINED = 0,
+        MASK_TYPE_NORM,
+        MASK_TYPE_ALIBI,
+        MASK_TYPE_SPEC,
+        MASK_TYPE_MASK_FREE,
+        MASK_TYPE_NORM_COMPRESS
+    };
+    MaskType maskType = UNDEFINED;
+    bool batchRunStatusEnable = false;
+    enum QuantType : int {
+        TYPE_QUANT_UNDEFINED = 0,
+        TYPE_QUANT_UNQUANT = 0,
+        TYPE_DEQUANT_FUSION = 1, // int8 K/V cache with per-channel descale (+ optional offset) inputs
+        TYPE_QUANT_QKV_OFFLINE = 2,
+        TYPE_QUANT_QKV_ONLINE = 3
+    };
+    QuantType quantType = TYPE_QUANT_UNQUANT;
+    aclDataType outDataType = ACL_DT_UNDEFINED;
+    bool hasQuantOffset = false;
+    enum CompressType : int {
+        COMPRESS_TYPE_UNDEFINED = 0,
+        COMPRESS_TYPE_KVHEAD,
+        COMPRESS_TYPE_KVHEAD_ROPE,
+        COMPRESS_TYPE_MAX
+    };
+    CompressType compressType = COMPRESS_TYPE_UNDEFINED;
+    enum CalcType : int { CALC_TYPE_UNDEFINED = 0, CALC_TYPE_SPEC };
+    CalcType calcType = CALC_TYPE_UNDEFINED;
+    enum ScaleType : int { SCALE_TYPE_TOR = 0, SCALE_TYPE_LOGN, SCALE_TYPE_MAX };
+    ScaleType scaleType = SCALE_TYPE_TOR;
+    InputLayout inputLayout = TYPE_BSND;
+    uint32_t mlaVHeadSize = 0; // >0: combined K/V cache, V = first mlaVHeadSize columns of each K row
+    float qScale = 0;
+    uint8_t rsv[64] = {0};
+};
+
+static_assert(sizeof(ReshapeAndCacheParam) == 24, "ABI: ReshapeAndCacheParam is 24 bytes");
+static_assert(sizeof(PagedAttentionParam) == 120, "ABI: PagedAttentionParam is 120 bytes");
+} // namespace infer
+} // namespace atb
+#endif

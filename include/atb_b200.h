@@ -1,0 +1,165 @@
+/*
+ * C ABI of libatb_b200.so: the boundary a foreign-function binding targets.  Plain pointers and
+ * sizes only.  Every function returns 0 (ATB_B200_OK) or an atb::ErrorType value.
+ *
+ * Two levels:
+ *   1. kernel level  - plan on the host from context_lens, then enqueue the CUDA kernels; this is
+ *      what the reference's kernel-host layer does in PagedAttentionTiling + kernel launch.
+ *   2. operator level - handles around the C++ atb::Operation objects, mirroring the reference's
+ *      C-style wrappers (include/atb/atb_acl.h) for callers that cannot use the C++ classes.
+ *
+ * All device pointers are CUDA device memory of the current device; `stream` is a cudaStream_t.
+ * Launch functions only enqueue work; completion is the caller's stream synchronisation.
+ */
+#ifndef ATB_B200_H
+#define ATB_B200_H
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ATB_B200_OK 0
+
+/* element types of query / cache tensors */
+enum { ATB_B200_FP16 = 0, ATB_B200_BF16 = 1, ATB_B200_INT8 = 2 };
+
+/* kernel families; AUTO lets the planner choose */
+enum {
+    ATB_B200_KERNEL_AUTO = 0,
+    ATB_B200_KERNEL_GENERIC = 1, /* CUDA-core kernel, any shape */
+    ATB_B200_KERNEL_TMA_MMA = 2, /* TMA page gather + warp-level tensor-core tiles, D = 128 */
+    ATB_B200_KERNEL_MLA_TC5 = 3  /* TMA + tcgen05/TMEM tiles for the 576/512 latent cache */
+};
+
+/*
+ * Shape of one paged-attention decode call (one query token per sequence).
+ * Replaces AtbOps::OpParam::PagedAttention (src/kernels/include/atbops/params/pagedattention.h:21-87
+ * of the reference) plus the shapes its tiling reads from the tensors
+ * (src/kernels/mixkernels/pagedattention/tiling/paged_attention_tiling.cpp:194-244).
+ */
+typedef struct atb_b200_pa_desc {
+    int32_t batch;          /* sequences = query tokens */
+    int32_t num_heads;      /* query heads */
+    int32_t kv_heads;       /* key/value heads; num_heads % kv_heads == 0 */
+    int32_t head_dim_k;     /* width of a query / key row */
+    int32_t head_dim_v;     /* width of the output row (MLA: mlaVHeadSize) */
+    int32_t v_row_dim;      /* allocated width of a value-cache row (MLA combined cache: head_dim_k) */
+    int32_t block_size;     /* tokens per cache block */
+    int32_t num_blocks;     /* blocks in the cache */
+    int32_t max_blocks_per_seq; /* row length of block_tables */
+    int32_t q_dtype;        /* ATB_B200_FP16 | ATB_B200_BF16; also the output type */
+    int32_t kv_dtype;       /* same as q_dtype, or ATB_B200_INT8 */
+    float qk_scale;         /* multiplies Q*K^T */
+    int32_t kernel;         /* ATB_B200_KERNEL_*; AUTO unless forcing a path */
+    int32_t sm_count;       /* 0 = query the current device (148 on B200) */
+    int32_t reserved[4];    /* must be 0 */
+} atb_b200_pa_desc;
+
+/* Device pointers of one call.  v_cache == k_cache for the MLA combined cache. */
+typedef struct atb_b200_pa_tensors {
+    const void *q;              /* [batch, num_heads, head_dim_k] */
+    const void *k_cache;        /* [num_blocks, block_size, kv_heads, head_dim_k] */
+    const void *v_cache;        /* [num_blocks, block_size, kv_heads, v_row_dim] */
+    const int32_t *block_tables; /* [batch, max_blocks_per_seq] */
+    const float *k_descale;     /* [kv_heads*head_dim_k] fp32, int8 cache only, may be NULL (=1) */
+    const float *v_descale;     /* [kv_heads*head_dim_v] */
+    const int32_t *k_offset;    /* optional int32 offsets added before scaling */
+    const int32_t *v_offset;
+    void *out;                  /* [batch, num_heads, head_dim_v], q_dtype */
+} atb_b200_pa_tensors;
+
+typedef struct atb_b200_pa_plan atb_b200_pa_plan; /* opaque */
+
+typedef struct atb_b200_pa_plan_info {
+    int32_t kernel;          /* family chosen */
+    int32_t num_ctas;        /* grid of the attention kernel */
+    int32_t num_items;       /* (sequence, token-range) work items */
+    int32_t num_partials;    /* split-KV partial results written to the workspace */
+    int32_t num_combine_seqs; /* sequences merged by the combine kernel */
+    int32_t tile_tokens;     /* scheduling granule */
+    uint64_t workspace_bytes;
+    uint64_t plan_bytes;     /* bytes uploaded per launch */
+} atb_b200_pa_plan_info;
+
+/*
+ * Host-only planning: splits the sequences into balanced token ranges (split-KV) from the host
+ * copy of context_lens.  No CUDA call is made unless desc->sm_count == 0.
+ * Replaces PagedAttentionTiling (tiling/paged_attention_tiling.cpp:419-470 of the reference).
+ */
+int atb_b200_pa_plan_create(const atb_b200_pa_desc *desc, const int32_t *context_lens_host, atb_b200_pa_plan **plan);
+/* Re-plan in place for new context_lens of the same batch (one decode step later). */
+int atb_b200_pa_plan_update(atb_b200_pa_plan *plan, const int32_t *context_lens_host);
+int atb_b200_pa_plan_get_info(const atb_b200_pa_plan *plan, atb_b200_pa_plan_info *info);
+/* Copies the plan's work items (4 int32 each: seq, tok_begin, tok_end, partial slot or -1) and the
+ * per-CTA-group item offsets into caller arrays (either may be NULL); for tests and debugging. */
+int atb_b200_pa_plan_dump(const atb_b200_pa_plan *plan, int32_t *items, int32_t max_items, int32_t *group_begin,
+                          int32_t max_groups);
+void atb_b200_pa_plan_destroy(atb_b200_pa_plan *plan);
+
+/*
+ * Enqueue plan upload + attention kernel (+ combine kernel when any sequence was split).
+ * `workspace` must hold plan->workspace_bytes, 256-byte aligned.  Replaces the launch of
+ * paged_attention_mask / paged_multi_latent_attention_mask
+ * (src/kernels/mixkernels/pagedattention/op_kernel/paged_attention_mask_mix.cce:24,
+ *  paged_MLAttention_combine_cache_mask_mix.cce:24 of the reference).
+ */
+int atb_b200_pa_launch(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *tensors, void *workspace,
+                       uint64_t workspace_bytes, void *stream);
+
+/*
+ * ReshapeAndCache: cache[slot_mapping[i]] = key[i] (and value) for slot >= 0; byte-exact copy.
+ * row bytes = heads * head_dim * sizeof(elem).  value/value_cache NULL = K-only variant.
+ * Replaces the reshape_and_cache / reshape_and_cache_siso kernels
+ * (src/kernels/mixkernels/reshape_and_cache/op_kernel/reshape_and_cache_nd.cpp:146,
+ *  reshape_and_cache_nd_siso.cpp:80 of the reference).
+ */
+int atb_b200_reshape_and_cache(const void *key, const void *value, void *key_cache, void *value_cache,
+                               const int32_t *slot_mapping, int32_t num_tokens, int64_t k_row_bytes,
+                               int64_t v_row_bytes, int64_t num_slots, void *stream);
+
+/* Device-side status word of the last launch into `workspace` (0 = ok; 1 = a bounded wait in a
+ * kernel gave up).  Synchronises `stream`. */
+int atb_b200_pa_plan_device_status(atb_b200_pa_plan *plan, void *workspace, void *stream, int32_t *status);
+
+/* Optional timing of the attention kernel alone: when enabled, every launch records CUDA events on
+ * the launch stream around that kernel; last_kernel_ms synchronises on the second event. */
+int atb_b200_pa_plan_set_profiling(atb_b200_pa_plan *plan, int enable);
+int atb_b200_pa_plan_last_kernel_ms(atb_b200_pa_plan *plan, float *ms);
+
+/* ---------------------------------------------------------------- operator level */
+
+/* Mirrors atb::Tensor (include/atb/types.h:118-127 of the reference). */
+typedef struct atb_b200_tensor {
+    int32_t dtype;      /* aclDataType value */
+    int32_t format;     /* aclFormat value */
+    int64_t dims[8];
+    uint64_t dim_num;
+    void *device_data;
+    void *host_data;
+    uint64_t data_size;
+} atb_b200_tensor;
+
+int atb_b200_context_create(void **context);
+int atb_b200_context_set_stream(void *context, void *stream);
+int atb_b200_context_destroy(void *context);
+
+/* `param` points at an atb::infer::PagedAttentionParam (120 bytes) / ReshapeAndCacheParam (24 bytes). */
+int atb_b200_operation_create_paged_attention(const void *param, uint64_t param_bytes, void **operation);
+int atb_b200_operation_create_reshape_and_cache(const void *param, uint64_t param_bytes, void **operation);
+int atb_b200_operation_input_num(void *operation, uint32_t *n);
+int atb_b200_operation_output_num(void *operation, uint32_t *n);
+int atb_b200_operation_infer_shape(void *operation, const atb_b200_tensor *in, uint32_t n_in, atb_b200_tensor *out,
+                                   uint32_t n_out);
+int atb_b200_operation_setup(void *operation, const atb_b200_tensor *in, uint32_t n_in, const atb_b200_tensor *out,
+                             uint32_t n_out, uint64_t *workspace_bytes, void *context);
+int atb_b200_operation_execute(void *operation, const atb_b200_tensor *in, uint32_t n_in, const atb_b200_tensor *out,
+                               uint32_t n_out, void *workspace, uint64_t workspace_bytes, void *context);
+int atb_b200_operation_destroy(void *operation);
+
+const char *atb_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

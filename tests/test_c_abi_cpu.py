@@ -1,0 +1,282 @@
+"""CPU-only checks: the library loads and exports its C ABI, the host planner's invariants, and the
+error behaviour of the operator layer (no kernel is launched here)."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+from helpers import ROOT, capi, wl
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "atb_b200.h")).read()
+    declared = set(re.findall(r"\b(atb_b200_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations parsed"
+    assert declared == set(capi.EXPORTS)
+    lib = ctypes.CDLL(capi.LIB_PATH)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert b"atb-b200" in capi.lib().atb_b200_version()
+
+
+def test_param_struct_sizes_match_reference_abi():
+    # tests/unittest/ops/test_op_param_size.cpp:47,51 of the reference
+    assert ctypes.sizeof(capi.PagedAttentionParam) == 120
+    assert ctypes.sizeof(capi.ReshapeAndCacheParam) == 24
+
+
+def _plan(case, lens=None, kernel=0, sm=148):
+    lens = wl.context_lens(case) if lens is None else np.asarray(lens, dtype=np.int32)
+    need = int(((lens.astype(np.int64) + case.block_size - 1) // case.block_size).max()) if len(lens) else 1
+    d = capi.make_desc(case.batch, case.heads, case.kv_heads, case.dk, case.dv, case.block_size, 1 << 20,
+                       max(need, 1), case.q_dtype, case.kvd, case.qk_scale,
+                       v_row_dim=case.dk if case.mla else case.dv, kernel=kernel, sm_count=sm)
+    return capi.PaPlan(d, lens), lens
+
+
+@pytest.mark.parametrize("case", wl.CONFIGS + wl.SMALL_CASES, ids=lambda c: c.name)
+def test_plan_covers_every_token_exactly_once(case):
+    plan, lens = _plan(case)
+    info = plan.info
+    items, groups = plan.dump()
+    cols = info.num_ctas // max(1, (info.num_ctas // max(1, _cols(case, info))))
+    covered = {}
+    for seq, b, e, slot in items:
+        assert 0 <= b < e <= lens[seq]
+        assert b % 128 == 0
+        covered.setdefault(seq, []).append((b, e, slot))
+    n_partials = 0
+    for seq in range(case.batch):
+        parts = sorted(covered.get(seq, []))
+        if lens[seq] == 0:
+            assert not parts
+            continue
+        assert parts[0][0] == 0 and parts[-1][1] == lens[seq]
+        for (b0, e0, _), (b1, e1, _) in zip(parts, parts[1:]):
+            assert e0 == b1
+        if len(parts) == 1:
+            assert parts[0][2] == -1
+        else:
+            slots = [p[2] for p in parts]
+            assert slots == list(range(slots[0], slots[0] + len(parts)))
+            n_partials += len(parts)
+    assert n_partials == info.num_partials
+    n_groups = len([g for g in groups if True]) and (info.num_ctas // _cols(case, info))
+    assert groups[0] == 0 and groups[n_groups] == info.num_items
+    assert np.all(np.diff(groups[:n_groups + 1]) >= 0)
+
+
+def _cols(case, info):
+    if info.kernel == capi.KERNEL_TMA_MMA:
+        return case.kv_heads
+    dmax = max(case.dk, case.dv)
+    gh = 8 if dmax <= 128 else (4 if dmax <= 256 else 2)
+    group = case.heads // case.kv_heads
+    return case.kv_heads * ((group + gh - 1) // gh)
+
+
+@pytest.mark.parametrize("idx", [1, 2, 3])
+def test_plan_is_balanced_on_benchmark_configs(idx):
+    case = wl.CONFIGS[idx]
+    plan, lens = _plan(case)
+    info = plan.info
+    items, groups = plan.dump()
+    n_groups = info.num_ctas // _cols(case, info)
+    per_sm = 2 if info.kernel == capi.KERNEL_TMA_MMA else 4
+    assert info.num_ctas <= 148 * per_sm, "the grid must fit one wave of resident CTAs"
+    tiles = [sum((e - b + 127) // 128 for _, b, e, _ in items[groups[g]:groups[g + 1]]) for g in range(n_groups)]
+    assert max(tiles) <= np.mean(tiles) * 1.06 + 1
+
+
+def test_plan_update_replans_in_place():
+    case = wl.CONFIGS[1]
+    plan, lens = _plan(case)
+    before = plan.dump()[0].copy()
+    plan.update(lens + 1)
+    after = plan.dump()[0]
+    assert after[:, 2].max() == (lens + 1).max()
+    assert before.shape[0] > 0
+
+
+def test_plan_rejects_bad_arguments():
+    case = wl.CONFIGS[1]
+    lens = wl.context_lens(case)
+    d = capi.make_desc(case.batch, 32, 5, 128, 128, 128, 1000, 32, "bf16", sm_count=148)  # 32 % 5 != 0
+    with pytest.raises(capi.AtbError) as e:
+        capi.PaPlan(d, lens)
+    assert e.value.code == capi.ERROR_INVALID_PARAM
+    d = capi.make_desc(case.batch, 32, 8, 128, 128, 128, 1000, 4, "bf16", sm_count=148)  # lens exceed 4 blocks
+    with pytest.raises(capi.AtbError) as e:
+        capi.PaPlan(d, lens)
+    assert e.value.code == capi.ERROR_INVALID_PARAM
+    d = capi.make_desc(case.batch, 32, 8, 128, 128, 128, 1000, 32, "bf16", sm_count=148)
+    d.reserved[1] = 7
+    with pytest.raises(capi.AtbError):
+        capi.PaPlan(d, lens)
+    # a kernel that does not support the shape
+    d = capi.make_desc(4, 8, 8, 96, 96, 16, 1000, 64, "fp16", kernel=capi.KERNEL_TMA_MMA, sm_count=148)
+    with pytest.raises(capi.AtbError) as e:
+        capi.PaPlan(d, np.array([5, 6, 7, 8], dtype=np.int32))
+    assert e.value.code == capi.ERROR_INVALID_TENSOR_DIM
+
+
+def test_kernel_selection():
+    assert _plan(wl.CONFIGS[1])[0].info.kernel == capi.KERNEL_TMA_MMA
+    assert _plan(wl.CONFIGS[0])[0].info.kernel == capi.KERNEL_TMA_MMA
+    small = {c.name: c for c in wl.SMALL_CASES}
+    assert _plan(small["ragged_d96_bs16_fp16"])[0].info.kernel == capi.KERNEL_GENERIC
+    assert _plan(small["gqa127_fp16"])[0].info.kernel == capi.KERNEL_GENERIC
+
+
+# ---------------------------------------------------------------- operator layer, error behaviour
+
+def _pa_param(**kw):
+    base = dict(headNum=8, kvHeadNum=2, qkScale=0.1)
+    base.update(kw)
+    return capi.PagedAttentionParam(**base)
+
+
+def _expect(code, fn, *a, **k):
+    with pytest.raises(capi.AtbError) as e:
+        fn(*a, **k)
+    assert e.value.code == code, e.value.code
+
+
+def test_create_operation_param_checks():
+    capi.Operation(_pa_param())
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, _pa_param(headNum=0))
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, _pa_param(kvHeadNum=-1))
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, _pa_param(headNum=8, kvHeadNum=3))
+    p = _pa_param()
+    p.rsv[5] = 1
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, p)
+    # MLA rules: one kv head, no dequant fusion, width <= 576
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, _pa_param(mlaVHeadSize=512, kvHeadNum=2))
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, _pa_param(mlaVHeadSize=512, kvHeadNum=1, quantType=1))
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, _pa_param(mlaVHeadSize=600, kvHeadNum=1))
+    capi.Operation(_pa_param(mlaVHeadSize=512, kvHeadNum=1))
+    # dequant needs calcType UNDEFINED
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, _pa_param(quantType=1, calcType=1))
+    rp = capi.ReshapeAndCacheParam()
+    capi.Operation(rp)
+    rp2 = capi.ReshapeAndCacheParam()
+    rp2.kvCacheCfg = 7
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, rp2)
+    rp3 = capi.ReshapeAndCacheParam()
+    rp3.rsv[0] = 1
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, rp3)
+
+
+def test_input_output_counts():
+    assert capi.Operation(_pa_param()).input_num == 5
+    assert capi.Operation(_pa_param(quantType=1)).input_num == 7
+    assert capi.Operation(_pa_param(quantType=1, hasQuantOffset=True)).input_num == 9
+    assert capi.Operation(_pa_param(mlaVHeadSize=512, kvHeadNum=1)).input_num == 4
+    assert capi.Operation(capi.ReshapeAndCacheParam()).input_num == 5
+    siso = capi.ReshapeAndCacheParam()
+    siso.kvCacheCfg = 1
+    op = capi.Operation(siso)
+    assert (op.input_num, op.output_num) == (3, 1)
+
+
+def _pa_tensors(batch=3, heads=8, kvh=2, d=128, bs=128, nb=16, maxb=4, dtype=capi.ACL_FLOAT16, lens=None):
+    T = capi.atb_tensor
+    lens = np.array([5, 130, 400], dtype=np.int32) if lens is None else lens
+    fake = 0x1000
+    ins = [T(dtype=dtype, shape=(batch, heads, d), device_ptr=fake), T(dtype=dtype, shape=(nb, bs, kvh, d), device_ptr=fake),
+           T(dtype=dtype, shape=(nb, bs, kvh, d), device_ptr=fake), T(dtype=capi.ACL_INT32, shape=(batch, maxb), device_ptr=fake),
+           T(dtype=capi.ACL_INT32, shape=(batch,), device_ptr=fake, host=lens)]
+    outs = [T(dtype=dtype, shape=(batch, heads, d), device_ptr=fake)]
+    return ins, outs, lens
+
+
+def test_setup_checks_and_plan_without_gpu(monkeypatch):
+    monkeypatch.setenv("ATB_B200_SM_COUNT", "148")
+    op = capi.Operation(_pa_param())
+    ctx = capi.Context()
+    ins, outs, lens = _pa_tensors()
+    assert op.infer_shape(ins, 1) == [(3, 8, 128)]
+    ws = op.setup(ins, outs, ctx)
+    assert ws >= 256
+    # wrong tensor count
+    _expect(capi.ERROR_INVALID_IN_TENSOR_NUM, op.setup, ins[:4], outs, ctx)
+    # dtype combination not allowed (int8 cache without dequant fusion)
+    bad = list(ins)
+    bad[1] = capi.atb_tensor(dtype=capi.ACL_INT8, shape=(16, 128, 2, 128), device_ptr=0x1000)
+    _expect(capi.ERROR_INVALID_TENSOR_INI_MATCH, op.setup, bad, outs, ctx)
+    # key cache must be 4-D
+    bad = list(ins)
+    bad[1] = capi.atb_tensor(dtype=capi.ACL_FLOAT16, shape=(16, 128, 256), device_ptr=0x1000)
+    _expect(capi.ERROR_INVALID_TENSOR_DIM_NUM, op.setup, bad, outs, ctx)
+    # head size mismatch between query and key cache
+    bad = list(ins)
+    bad[0] = capi.atb_tensor(dtype=capi.ACL_FLOAT16, shape=(3, 8, 64), device_ptr=0x1000)
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, bad, outs, ctx)
+    # output head size must equal the value head size
+    bad_out = [capi.atb_tensor(dtype=capi.ACL_FLOAT16, shape=(3, 8, 64), device_ptr=0x1000)]
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, ins, bad_out, ctx)
+    # contextLens without hostData
+    bad = list(ins)
+    bad[4] = capi.atb_tensor(dtype=capi.ACL_INT32, shape=(3,), device_ptr=0x1000)
+    _expect(capi.ERROR_INVALID_PARAM, op.setup, bad, outs, ctx)
+    # null context
+    _expect(capi.ERROR_INVALID_PARAM, op.setup, ins, outs, None)
+    # zero-sized dim
+    bad = list(ins)
+    bad[3] = capi.atb_tensor(dtype=capi.ACL_INT32, shape=(3, 0), device_ptr=0x1000)
+    _expect(capi.ERROR_INVALID_TENSOR_SIZE, op.setup, bad, outs, ctx)
+
+
+def test_execute_contract_without_gpu(monkeypatch):
+    monkeypatch.setenv("ATB_B200_SM_COUNT", "148")
+    op = capi.Operation(_pa_param())
+    ctx = capi.Context()
+    ins, outs, _ = _pa_tensors()
+    # Execute before Setup
+    _expect(capi.ERROR_INVALID_PARAM, op.execute, ins, outs, None, 0, ctx)
+    ws = op.setup(ins, outs, ctx)
+    # the context has no stream yet
+    _expect(capi.ERROR_INVALID_PARAM, op.execute, ins, outs, 0x2000, ws, ctx)
+    ctx.set_stream(0x3000)
+    # another context than the one given to Setup
+    other = capi.Context(0x3000)
+    _expect(capi.ERROR_INVALID_PARAM, op.execute, ins, outs, 0x2000, ws, other)
+    # workspace smaller than Setup asked for / null workspace
+    _expect(capi.ERROR_INVALID_PARAM, op.execute, ins, outs, 0x2000, ws - 1, ctx)
+    _expect(capi.ERROR_INVALID_PARAM, op.execute, ins, outs, None, ws, ctx)
+    # dataSize differs from Setup's
+    bad = list(ins)
+    bad[0] = capi.atb_tensor(dtype=capi.ACL_FLOAT16, shape=(3, 8, 128), device_ptr=0x1000)
+    bad[0].data_size -= 2
+    _expect(capi.ERROR_INVALID_PARAM, op.execute, bad, outs, 0x2000, ws, ctx)
+    # a tensor with neither device nor host data
+    bad = list(ins)
+    bad[0] = capi.atb_tensor(dtype=capi.ACL_FLOAT16, shape=(3, 8, 128), device_ptr=None)
+    _expect(capi.ERROR_INVALID_PARAM, op.execute, bad, outs, 0x2000, ws, ctx)
+
+
+def test_reshape_and_cache_setup_checks():
+    T = capi.atb_tensor
+    op = capi.Operation(capi.ReshapeAndCacheParam())
+    ctx = capi.Context()
+    f = 0x1000
+    ins = [T(dtype=capi.ACL_BF16, shape=(4, 8, 128), device_ptr=f), T(dtype=capi.ACL_BF16, shape=(4, 8, 64), device_ptr=f),
+           T(dtype=capi.ACL_BF16, shape=(10, 128, 8, 128), device_ptr=f), T(dtype=capi.ACL_BF16, shape=(10, 128, 8, 64), device_ptr=f),
+           T(dtype=capi.ACL_INT32, shape=(4,), device_ptr=f)]
+    outs = [ins[2], ins[3]]
+    assert op.setup(ins, outs, ctx) == 0
+    assert op.infer_shape(ins, 2) == [(10, 128, 8, 128), (10, 128, 8, 64)]
+    bad = list(ins)
+    bad[1] = T(dtype=capi.ACL_BF16, shape=(5, 8, 64), device_ptr=f)
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, bad, outs, ctx)
+    bad = list(ins)
+    bad[2] = T(dtype=capi.ACL_BF16, shape=(10, 128, 8 * 128), device_ptr=f)
+    _expect(capi.ERROR_INVALID_TENSOR_DIM_NUM, op.setup, bad, [bad[2], ins[3]], ctx)
+    # outputs must describe the caches
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, ins, [ins[3], ins[3]], ctx)
+    # mixed dtypes
+    bad = list(ins)
+    bad[0] = T(dtype=capi.ACL_FLOAT16, shape=(4, 8, 128), device_ptr=f)
+    _expect(capi.ERROR_INVALID_TENSOR_INI_MATCH, op.setup, bad, outs, ctx)

@@ -1,0 +1,189 @@
+"""Parity of the CUDA path against the CPU oracle and the reference-golden fixtures, through the C ABI.
+
+Tolerances (max-abs error against the reference golden): fp16 2e-3, bf16 8e-3, int8 cache 1e-2;
+ReshapeAndCache must be bit-exact.
+"""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from golden_cases import GOLDEN_PA_CASES, GOLDEN_RAC_CASES, HERE as GOLDEN_DIR, rac_inputs
+from helpers import capi, host_inputs_to_device, max_abs_err, oracle_out, run_gpu_case, to_dev, tol_for, wl
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+def _kernels_for(case):
+    ks = [capi.KERNEL_AUTO]
+    group = case.heads // case.kv_heads
+    if (case.dk == 128 and case.dv == 128 and case.block_size == 128 and group <= 8 and not case.mla
+            and case.kvd != "int8"):
+        ks.append(capi.KERNEL_GENERIC)
+    return ks
+
+
+# ------------------------------------------------------------------ golden fixtures
+@pytest.mark.parametrize("case", GOLDEN_PA_CASES, ids=lambda c: c.name)
+def test_attention_matches_reference_golden(case):
+    fx = np.load(os.path.join(GOLDEN_DIR, f"pa_{case.name}.npz"))
+    h = wl.make_host_inputs(case)
+    for kernel in _kernels_for(case):
+        out, info = run_gpu_case(case, h, kernel=kernel)
+        err = max_abs_err(out, fx["out"], case.q_dtype)
+        assert err <= tol_for(case), (kernel, info.kernel, err)
+
+
+@pytest.mark.parametrize("spec", GOLDEN_RAC_CASES, ids=lambda s: s["name"])
+def test_reshape_and_cache_matches_reference_golden(spec):
+    fx = np.load(os.path.join(GOLDEN_DIR, f"rac_{spec['name']}.npz"))
+    inp = rac_inputs(spec)
+    dt = spec["dtype"]
+    key, value = to_dev(inp["key"], dt), to_dev(inp["value"], dt)
+    tdt = wl.torch_dtype(dt)
+    kc = torch.zeros((spec["num_blocks"], spec["block_size"], spec["heads"], spec["dk"]), dtype=tdt, device="cuda")
+    vc = torch.zeros((spec["num_blocks"], spec["block_size"], spec["heads"], spec["dv"]), dtype=tdt, device="cuda")
+    capi.reshape_and_cache(key, value, kc, vc, torch.from_numpy(inp["slot_mapping"]).cuda())
+    torch.cuda.synchronize()
+    assert np.array_equal(wl.torch_to_host(kc, dt).view(np.uint8), fx["key_cache"].view(np.uint8))
+    assert np.array_equal(wl.torch_to_host(vc, dt).view(np.uint8), fx["value_cache"].view(np.uint8))
+
+
+# ------------------------------------------------------------------ seeded cases vs the oracle
+@pytest.mark.parametrize("case", wl.SMALL_CASES, ids=lambda c: c.name)
+def test_attention_matches_oracle_small(case):
+    h = wl.make_host_inputs(case)
+    ref = oracle_out(case, h, out=np.full((case.batch, case.heads, case.dv), 0, dtype=h["q"].dtype))
+    for kernel in _kernels_for(case):
+        out, info = run_gpu_case(case, h, kernel=kernel, out_fill=0.0)
+        err = max_abs_err(out, ref, case.q_dtype)
+        assert err <= tol_for(case), (kernel, info.kernel, err)
+
+
+def test_empty_sequences_leave_output_untouched():
+    case = [c for c in wl.SMALL_CASES if c.name == "zero_and_one_ctx"][0]
+    h = wl.make_host_inputs(case)
+    out, _ = run_gpu_case(case, h, out_fill=3.0)
+    f = wl.to_f32(out, case.q_dtype)
+    lens = h["context_lens"]
+    for b in range(case.batch):
+        if lens[b] == 0:
+            assert np.all(f[b] == 3.0)
+        else:
+            assert not np.all(f[b] == 3.0)
+    # ctx == 1: the output is exactly the single V row
+    b = int(np.where(lens == 1)[0][0])
+    blk = h["block_tables"][b, 0]
+    v = wl.to_f32(h["v_cache"][blk, 0], case.q_dtype)      # [kv_heads, D]
+    group = case.heads // case.kv_heads
+    assert np.array_equal(f[b], np.repeat(v, group, axis=0))
+
+
+@pytest.mark.parametrize("idx", [0, 1, 2, 3, 4], ids=lambda i: wl.CONFIGS[i].name)
+def test_benchmark_config_full_size_matches_oracle(idx):
+    case = wl.CONFIGS[idx]
+    d = wl.make_device_inputs(case, "cuda")
+    lens = d["context_lens_host"]
+    # ReshapeAndCache of the step's new tokens first, as a serving step does
+    capi.reshape_and_cache(d["new_k"], d["new_v"], d["k_cache"], d["v_cache"], d["slot_mapping"])
+    out = capi.paged_attention(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], lens, case.qk_scale,
+                               dv=case.dv, k_descale=d.get("k_descale"), v_descale=d.get("v_descale"))
+    torch.cuda.synchronize()
+    hk = wl.torch_to_host(d["k_cache"], case.kvd)
+    hv = None if case.mla else wl.torch_to_host(d["v_cache"], case.kvd)
+    # the scatter is checked bit-exactly through its effect: the new rows sit at their slots
+    nk = wl.torch_to_host(d["new_k"], case.kvd)
+    slots = d["slot_mapping_host"]
+    flat = hk.reshape(-1, case.kv_heads, case.dk)
+    assert np.array_equal(flat[slots[slots >= 0]], nk[slots >= 0])
+    ref = oracle.paged_attention(wl.torch_to_host(d["q"], case.q_dtype), hk, hv, d["block_tables_host"], lens,
+                                 case.qk_scale, case.q_dtype, kv_dtype=case.kvd, dv=case.dv,
+                                 k_descale=None if "k_descale" not in d else d["k_descale"].cpu().numpy(),
+                                 v_descale=None if "v_descale" not in d else d["v_descale"].cpu().numpy())
+    err = max_abs_err(wl.torch_to_host(out, case.q_dtype), ref, case.q_dtype)
+    assert err <= tol_for(case), err
+
+
+# ------------------------------------------------------------------ size-independent properties
+def test_block_permutation_invariance_is_bit_exact():
+    """Moving the pages in memory and permuting block_tables accordingly must not change a bit."""
+    case = wl.CONFIGS[1]
+    d = wl.make_device_inputs(case, "cuda")
+    lens = d["context_lens_host"]
+    out1 = capi.paged_attention(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], lens, case.qk_scale)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    nb = d["k_cache"].shape[0]
+    perm = torch.randperm(nb, generator=g, device="cuda")
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(nb, device="cuda")
+    k2, v2 = d["k_cache"][perm].contiguous(), d["v_cache"][perm].contiguous()   # new[i] = old[perm[i]]
+    bt = d["block_tables"].long()
+    bt2 = torch.where(bt >= 0, inv[bt.clamp(min=0)], bt).int().contiguous()
+    out2 = capi.paged_attention(d["q"], k2, v2, bt2, lens, case.qk_scale)
+    torch.cuda.synchronize()
+    assert torch.equal(out1.view(torch.int16), out2.view(torch.int16))
+
+
+def test_constant_value_rows_give_that_constant():
+    """softmax weights sum to 1: with V[t, :] = c for every token the output is c (up to rounding)."""
+    case = wl.CONFIGS[3]
+    case = wl.Case("c4_small", batch=32, heads=64, kv_heads=8, q_dtype="bf16",
+                   ctx=("lognormal", 7.6, 1.0, 16, 32768), seed=1004)
+    d = wl.make_device_inputs(case, "cuda")
+    c = torch.linspace(-2, 2, 128, device="cuda").to(torch.bfloat16)
+    d["v_cache"][:] = c
+    out = capi.paged_attention(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], d["context_lens_host"],
+                               case.qk_scale)
+    torch.cuda.synchronize()
+    err = (out.float() - c.float()).abs().max().item()
+    assert err <= 8e-3 * 2, err
+
+
+def test_split_and_unsplit_agree():
+    """The same long sequences planned for 148 SMs (split-KV + combine) and for 1 SM (few cuts)."""
+    case = wl.Case("long", batch=3, heads=32, kv_heads=8, q_dtype="fp16", ctx=("list", [9000, 130, 20000]), seed=31)
+    h = wl.make_host_inputs(case)
+    d = host_inputs_to_device(case, h)
+    outs = []
+    for sm in (148, 1):
+        desc = capi.make_desc(case.batch, case.heads, case.kv_heads, 128, 128, 128, h["num_blocks"],
+                              h["block_tables"].shape[1], "fp16", qk_scale=case.qk_scale, sm_count=sm)
+        plan = capi.PaPlan(desc, h["context_lens"])
+        out = capi.paged_attention(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], h["context_lens"],
+                                   case.qk_scale, plan=plan)
+        torch.cuda.synchronize()
+        outs.append(out.float().cpu().numpy())
+    assert np.abs(outs[0] - outs[1]).max() <= 1e-3
+    ref = wl.to_f32(oracle_out(case, h), "fp16")
+    assert np.abs(outs[0] - ref).max() <= 2e-3
+
+
+def test_plan_reuse_over_decode_steps():
+    """A plan updated in place for growing context_lens keeps giving oracle results."""
+    case = wl.Case("steps", batch=5, heads=16, kv_heads=4, q_dtype="bf16", ctx=("list", [126, 127, 128, 255, 600]),
+                   seed=33, pool_blocks=40)
+    h = wl.make_host_inputs(case)
+    # give every sequence room for three more tokens
+    h["block_tables"] = np.concatenate([h["block_tables"], np.full((5, 1), -1, np.int32)], axis=1)
+    used = set(h["block_tables"][h["block_tables"] >= 0].tolist())
+    free = [b for b in range(h["num_blocks"]) if b not in used]
+    for b in range(5):
+        n = (h["context_lens"][b] + 127) // 128
+        h["block_tables"][b, n] = free.pop()
+    d = host_inputs_to_device(case, h)
+    lens = h["context_lens"].copy()
+    plan, ws = None, None
+    for step in range(3):
+        out, plan, ws = capi.paged_attention(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], lens,
+                                             case.qk_scale, plan=plan, workspace=ws, return_plan=True)
+        torch.cuda.synchronize()
+        hh = dict(h, context_lens=lens)
+        ref = oracle_out(case, hh)
+        assert max_abs_err(wl.torch_to_host(out, "bf16"), ref, "bf16") <= 8e-3
+        lens = lens + 1
+        plan.update(lens)
