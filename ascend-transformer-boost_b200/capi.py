@@ -83,7 +83,7 @@ class ReshapeAndCacheParam(ctypes.Structure):
 EXPORTS = [
     "atb_b200_pa_plan_create", "atb_b200_pa_plan_update", "atb_b200_pa_plan_get_info", "atb_b200_pa_plan_dump",
     "atb_b200_pa_plan_destroy", "atb_b200_pa_launch", "atb_b200_reshape_and_cache",
-    "atb_b200_pa_plan_device_status", "atb_b200_pa_plan_set_profiling", "atb_b200_pa_plan_last_kernel_ms",
+    "atb_b200_pa_plan_device_status", "atb_b200_pa_plan_set_profiling", "atb_b200_pa_plan_kernel_ms",
     "atb_b200_context_create", "atb_b200_context_set_stream", "atb_b200_context_destroy",
     "atb_b200_operation_create_paged_attention", "atb_b200_operation_create_reshape_and_cache",
     "atb_b200_operation_input_num", "atb_b200_operation_output_num", "atb_b200_operation_infer_shape",
@@ -112,7 +112,7 @@ def lib():
         L.atb_b200_reshape_and_cache.argtypes = [vp, vp, vp, vp, vp, i32, i64, i64, i64, vp]
         L.atb_b200_pa_plan_device_status.argtypes = [vp, vp, vp, P(i32)]
         L.atb_b200_pa_plan_set_profiling.argtypes = [vp, ctypes.c_int]
-        L.atb_b200_pa_plan_last_kernel_ms.argtypes = [vp, P(ctypes.c_float)]
+        L.atb_b200_pa_plan_kernel_ms.argtypes = [vp, i32, P(ctypes.c_float)]
         L.atb_b200_context_create.argtypes = [P(vp)]
         L.atb_b200_context_set_stream.argtypes = [vp, vp]
         L.atb_b200_context_destroy.argtypes = [vp]
@@ -202,7 +202,7 @@ class PaPlan:
     def last_kernel_ms(self):
         ms = ctypes.c_float(0)
         _check(lib().atb_b200_pa_plan_last_kernel_ms(self.handle, ctypes.byref(ms)),
-               "atb_b200_pa_plan_last_kernel_ms")
+               "atb_b200_pa_plan_kernel_ms")
         return ms.value
 
     def close(self):

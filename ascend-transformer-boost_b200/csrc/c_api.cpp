@@ -21,8 +21,11 @@ struct atb_b200_pa_plan {
     size_t staging_cap = 0;
     cudaEvent_t uploaded = nullptr;
     bool upload_pending = false;
+    // optional timing of the attention kernel: a ring of event pairs, one pair per launch
+    static constexpr int kProfRing = 256;
     bool profile = false;
-    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    cudaEvent_t ev0[kProfRing] = {}, ev1[kProfRing] = {};
+    uint64_t launches = 0;
     int32_t *status_host = nullptr;
 };
 
@@ -122,9 +125,11 @@ void atb_b200_pa_plan_destroy(atb_b200_pa_plan *plan)
         cudaEventSynchronize(plan->uploaded);
         cudaEventDestroy(plan->uploaded);
     }
-    if (plan->ev0 != nullptr) {
-        cudaEventDestroy(plan->ev0);
-        cudaEventDestroy(plan->ev1);
+    for (int i = 0; i < atb_b200_pa_plan::kProfRing; ++i) {
+        if (plan->ev0[i] != nullptr) {
+            cudaEventDestroy(plan->ev0[i]);
+            cudaEventDestroy(plan->ev1[i]);
+        }
     }
     if (plan->staging != nullptr) {
         cudaFreeHost(plan->staging);
@@ -140,21 +145,27 @@ int atb_b200_pa_plan_set_profiling(atb_b200_pa_plan *plan, int enable)
     if (plan == nullptr) {
         return kErrInvalidParam;
     }
-    if (enable && plan->ev0 == nullptr) {
-        if (cudaEventCreate(&plan->ev0) != cudaSuccess || cudaEventCreate(&plan->ev1) != cudaSuccess) {
-            return kErrRtFail;
+    if (enable && plan->ev0[0] == nullptr) {
+        for (int i = 0; i < atb_b200_pa_plan::kProfRing; ++i) {
+            if (cudaEventCreate(&plan->ev0[i]) != cudaSuccess || cudaEventCreate(&plan->ev1[i]) != cudaSuccess) {
+                return kErrRtFail;
+            }
         }
     }
     plan->profile = enable != 0;
+    plan->launches = 0;
     return ATB_B200_OK;
 }
 
-int atb_b200_pa_plan_last_kernel_ms(atb_b200_pa_plan *plan, float *ms)
+int atb_b200_pa_plan_kernel_ms(atb_b200_pa_plan *plan, int32_t launches_back, float *ms)
 {
-    if (plan == nullptr || ms == nullptr || plan->ev0 == nullptr) {
+    if (plan == nullptr || ms == nullptr || plan->ev0[0] == nullptr || launches_back < 0 ||
+        launches_back >= atb_b200_pa_plan::kProfRing || (uint64_t)launches_back >= plan->launches) {
         return kErrInvalidParam;
     }
-    if (cudaEventSynchronize(plan->ev1) != cudaSuccess || cudaEventElapsedTime(ms, plan->ev0, plan->ev1) != cudaSuccess) {
+    const int i = (int)((plan->launches - 1 - (uint64_t)launches_back) % atb_b200_pa_plan::kProfRing);
+    if (cudaEventSynchronize(plan->ev1[i]) != cudaSuccess ||
+        cudaEventElapsedTime(ms, plan->ev0[i], plan->ev1[i]) != cudaSuccess) {
         return kErrRtFail;
     }
     return ATB_B200_OK;
@@ -241,8 +252,9 @@ int atb_b200_pa_launch(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, voi
     a.chunks_per_kvh = h.chunks_per_kvh;
     a.scale_log2 = d.qk_scale * 1.4426950408889634f;
 
+    const int prof_i = (int)(plan->launches % atb_b200_pa_plan::kProfRing);
     if (plan->profile) {
-        cudaEventRecord(plan->ev0, stream);
+        cudaEventRecord(plan->ev0[prof_i], stream);
     }
     cudaError_t e;
     if (h.kernel == ATB_B200_KERNEL_TMA_MMA) {
@@ -251,7 +263,8 @@ int atb_b200_pa_launch(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, voi
         e = launch_pa_generic(a, d.q_dtype, d.kv_dtype, stream);
     }
     if (plan->profile) {
-        cudaEventRecord(plan->ev1, stream);
+        cudaEventRecord(plan->ev1[prof_i], stream);
+        plan->launches++;
     }
     if (e != cudaSuccess) {
         return kErrRtFail;

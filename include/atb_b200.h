@@ -122,10 +122,12 @@ int atb_b200_reshape_and_cache(const void *key, const void *value, void *key_cac
  * kernel gave up).  Synchronises `stream`. */
 int atb_b200_pa_plan_device_status(atb_b200_pa_plan *plan, void *workspace, void *stream, int32_t *status);
 
-/* Optional timing of the attention kernel alone: when enabled, every launch records CUDA events on
- * the launch stream around that kernel; last_kernel_ms synchronises on the second event. */
+/* Optional timing of the attention kernel alone: when enabled, every launch records a pair of
+ * CUDA events on the launch stream around that kernel (a ring of 256 pairs).  kernel_ms returns
+ * the duration of the launch `launches_back` launches ago (0 = the latest) and synchronises on
+ * its second event. */
 int atb_b200_pa_plan_set_profiling(atb_b200_pa_plan *plan, int enable);
-int atb_b200_pa_plan_last_kernel_ms(atb_b200_pa_plan *plan, float *ms);
+int atb_b200_pa_plan_kernel_ms(atb_b200_pa_plan *plan, int32_t launches_back, float *ms);
 
 /* ---------------------------------------------------------------- operator level */
 

@@ -12,6 +12,17 @@ from helpers import capi, host_inputs_to_device, max_abs_err, oracle_out, to_dev
 pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 
+_STREAMS = []
+
+
+def _new_ctx():
+    """A context with its own (non-null) stream, as the reference requires; inputs made on torch's
+    default stream are synchronised first."""
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    _STREAMS.append(s)
+    return capi.Context(s.cuda_stream)
+
 
 def _run_pa_op(case, h, param, scale_encoding="fp32"):
     d = host_inputs_to_device(case, h)
@@ -42,8 +53,7 @@ def _run_pa_op(case, h, param, scale_encoding="fp32"):
     outs = [T(out)]
     op = capi.Operation(param)
     assert op.input_num == len(ins)
-    stream = torch.cuda.current_stream().cuda_stream
-    ctx = capi.Context(stream)
+    ctx = _new_ctx()
     ws_bytes = op.setup(ins, outs, ctx)
     ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device="cuda")
     op.execute(ins, outs, ws.data_ptr(), ws_bytes, ctx)
@@ -64,7 +74,7 @@ def test_c1_reshape_and_cache_then_paged_attention():
     nk, nv = to_dev(h["new_k"], case.kvd), to_dev(h["new_v"], case.kvd)
     slots = torch.from_numpy(h["slot_mapping"]).cuda()
     rac = capi.Operation(capi.ReshapeAndCacheParam())
-    ctx = capi.Context(torch.cuda.current_stream().cuda_stream)
+    ctx = _new_ctx()
     ins = [T(nk), T(nv), T(d["k_cache"]), T(d["v_cache"]), T(slots)]
     outs = [T(d["k_cache"]), T(d["v_cache"])]          # outputs alias the caches
     assert rac.setup(ins, outs, ctx) == 0
@@ -89,7 +99,7 @@ def test_reshape_and_cache_outputs_must_alias():
     p = capi.ReshapeAndCacheParam()
     p.kvCacheCfg = 1
     op = capi.Operation(p)
-    ctx = capi.Context(torch.cuda.current_stream().cuda_stream)
+    ctx = _new_ctx()
     op.setup([T(k), T(kc), T(slots)], [T(other)], ctx)
     with pytest.raises(capi.AtbError) as e:
         op.execute([T(k), T(kc), T(slots)], [T(other)], None, 0, ctx)
@@ -107,7 +117,7 @@ def test_siso_reshape_and_cache_mla_row():
     p = capi.ReshapeAndCacheParam()
     p.kvCacheCfg = 1
     op = capi.Operation(p)
-    ctx = capi.Context(torch.cuda.current_stream().cuda_stream)
+    ctx = _new_ctx()
     op.setup([T(key), T(kc), T(slots)], [T(kc)], ctx)
     op.execute([T(key), T(kc), T(slots)], [T(kc)], None, 0, ctx)
     torch.cuda.synchronize()
