@@ -199,9 +199,10 @@ class PaPlan:
     def set_profiling(self, on=True):
         _check(lib().atb_b200_pa_plan_set_profiling(self.handle, 1 if on else 0), "atb_b200_pa_plan_set_profiling")
 
-    def last_kernel_ms(self):
+    def kernel_ms(self, launches_back=0):
+        """Duration of the attention kernel `launches_back` launches ago (profiling must be on)."""
         ms = ctypes.c_float(0)
-        _check(lib().atb_b200_pa_plan_last_kernel_ms(self.handle, ctypes.byref(ms)),
+        _check(lib().atb_b200_pa_plan_kernel_ms(self.handle, launches_back, ctypes.byref(ms)),
                "atb_b200_pa_plan_kernel_ms")
         return ms.value
 

@@ -1,0 +1,382 @@
+"""Benchmark of the paged-decode hot path (ReshapeAndCache + PagedAttention) on 1..8 B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--config i]
+
+One step = one decode step over the whole batch: scatter the step's new K/V tokens into the paged
+cache, then attention of every sequence's query token over its cached context.  The workload is
+benchmark configuration 2 (GQA decode, Llama-3-8B attention shape: bf16, batch 64, 32 q / 8 kv
+heads, head_dim 128, block_size 128, context_lens uniform in [2048,4096]) with seeded synthetic
+tensors.  With N > 1 the kv heads are sharded over the ranks (strong scaling, one process per GPU)
+and the per-shard outputs are all-gathered with NCCL.
+
+Prints ONE JSON line: `value` is whole-job KV GB/s with all inputs resident in HBM (device-timed),
+`e2e` the same metric through the atb operator API with host buffers (H2D of the step's inputs,
+re-planning, D2H of the output inside the timed region), `roofline` the attention kernel's achieved
+HBM bandwidth against the measured copy peak, `cpu_baseline` the CPU oracle on the host cores.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import __graft_entry__ as entry  # noqa: E402
+
+METRIC = "paged_decode_kv_bandwidth"
+UNIT = "GB/s"
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def ncu_traffic_bytes(case_name):
+    """Per-launch DRAM traffic of the attention kernel from the committed ncu summary, if any."""
+    p = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(p):
+        try:
+            return json.load(open(p)).get(case_name)
+        except Exception:
+            return None
+    return None
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def run_reference_arm(args, case, wl):
+    """The reference's own CPU implementation of the path = its Python/torch golden, restated in C with
+    OpenMP (oracle/pa_oracle.c) because the reference's C++ cannot be built without CANN; timed on
+    all host threads on a bounded sample of the same workload."""
+    import oracle
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    oracle.build()
+    threads = oracle.num_threads()
+    lens = wl.context_lens(case)
+    # bounded sample: the first sequences of the batch, at most ~64k tokens, so a step stays ~1 s
+    budget, take = 65536 * 4, 0
+    while take < case.batch and lens[:take + 1].sum() <= budget:
+        take += 1
+    take = max(take, 1)
+    sub = wl.Case(case.name + f"/first{take}", batch=take, heads=case.heads, kv_heads=case.kv_heads, dk=case.dk,
+                  dv=case.dv, block_size=case.block_size, q_dtype=case.q_dtype, kv_dtype=case.kv_dtype,
+                  ctx=("list", [int(x) for x in lens[:take]]), mla=case.mla, seed=case.seed)
+    h = wl.make_host_inputs(sub)
+    kvb = wl.kv_bytes(sub, h["context_lens"])
+
+    def step():
+        oracle.reshape_and_cache(h["new_k"], h["new_v"], h["k_cache"], h["v_cache"], h["slot_mapping"])
+        oracle.paged_attention(h["q"], h["k_cache"], h["v_cache"], h["block_tables"], h["context_lens"],
+                               sub.qk_scale, sub.q_dtype, kv_dtype=sub.kvd, dv=sub.dv,
+                               k_descale=h.get("k_descale"), v_descale=h.get("v_descale"))
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    gbs = kvb / dt / 1e9
+    sample = f"first {take} of {case.batch} sequences ({int(h['context_lens'].sum())} tokens) per step"
+    line = {"impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": case.q_dtype, "data": "synthetic",
+            "config": {"workload": case.name, "sample": sample},
+            "tokens_per_s": take / dt,
+            "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def cpu_baseline(case, wl, d, lens):
+    """The CPU oracle on the host cores over the whole workload (a few seconds), inputs from the GPU run."""
+    import oracle
+    threads = oracle.num_threads()
+    hk = wl.torch_to_host(d["k_cache"], case.kvd)
+    hv = None if case.mla else wl.torch_to_host(d["v_cache"], case.kvd)
+    hq = wl.torch_to_host(d["q"], case.q_dtype)
+    kd = d["k_descale"].cpu().numpy() if "k_descale" in d else None
+    vd = d["v_descale"].cpu().numpy() if "v_descale" in d else None
+    bt = d["block_tables_host"]
+    reps, t_total = 0, 0.0
+    out = None
+    while reps < 3 or (t_total < 10.0 and reps < 20):
+        t0 = time.perf_counter()
+        out = oracle.paged_attention(hq, hk, hv, bt, lens, case.qk_scale, case.q_dtype, kv_dtype=case.kvd, dv=case.dv,
+                                     k_descale=kd, v_descale=vd)
+        t_total += time.perf_counter() - t0
+        reps += 1
+    dt = t_total / reps
+    return {"value": wl.kv_bytes(case, lens) / dt / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"whole workload, mean of {reps} runs ({dt * 1e3:.0f} ms each)"}, out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--config", type=int, default=1, help="index into the benchmark configurations (default 1)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    pkg = entry.load_package()
+    wl, capi = pkg.workloads, pkg.capi
+    case = wl.CONFIGS[args.config]
+    if args.impl == "reference":
+        run_reference_arm(args, case, wl)
+        return
+
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    capi.lib()
+
+    shard = case.shard_heads(rank, world) if world > 1 else case
+    d = wl.make_device_inputs(shard, dev)
+    lens = d["context_lens_host"]
+    kv_bytes_global = wl.kv_bytes(case, lens)
+    B, H_local, Dv = shard.batch, shard.heads, shard.dv
+
+    stream = torch.cuda.Stream()
+    out = torch.zeros((B, H_local, Dv), dtype=d["q"].dtype, device=dev)
+    gathered = torch.zeros((world, B, H_local, Dv), dtype=d["q"].dtype, device=dev) if world > 1 else None
+    desc = capi.make_desc(B, shard.heads, shard.kv_heads, shard.dk, Dv, shard.block_size, d["num_blocks"],
+                          d["block_tables"].shape[1], shard.q_dtype, shard.kvd, shard.qk_scale,
+                          v_row_dim=shard.dk if shard.mla else Dv)
+    plan = capi.PaPlan(desc, lens)
+    info = plan.info
+    ws = torch.empty(max(int(info.workspace_bytes), 256), dtype=torch.uint8, device=dev)
+    tens = capi.pa_tensors(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], out, d.get("k_descale"),
+                           d.get("v_descale"))
+    plan.set_profiling(True)
+    launches_per_step = 2 + (1 if info.num_combine_seqs > 0 else 0)
+    torch.cuda.synchronize()
+
+    def step():
+        capi.reshape_and_cache(d["new_k"], d["new_v"], d["k_cache"], d["v_cache"], d["slot_mapping"])
+        plan.launch(tens, ws.data_ptr(), ws.numel(), stream.cuda_stream)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, out)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            step()
+        barrier()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+            time.sleep(0.25)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            step()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1) / args.steps
+        n_prof = min(args.steps, 256)
+        kernel_ms = float(np.mean([plan.kernel_ms(i) for i in range(n_prof)]))
+        clocks = sampler.stop() if rank == 0 else None
+    status = plan.device_status(ws.data_ptr(), stream.cuda_stream)
+    if status != 0:
+        raise RuntimeError(f"device status {status}")
+    if world > 1:
+        t = torch.tensor([ms, kernel_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, kernel_ms = float(t[0]), float(t[1])
+
+    # ---- end to end through the operator API with host buffers (rank-local shard, same step)
+    e2e = run_e2e(args, shard, wl, capi, d, lens, dev, world, gathered)
+    if world > 1:
+        t = torch.tensor([e2e["ms"]], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e["ms"] = float(t[0])
+
+    if rank == 0:
+        peak, peak_kind = measured_peak_gbs()
+        value = kv_bytes_global / (ms * 1e-3) / 1e9
+        achieved = wl.kv_bytes(shard, lens) / (kernel_ms * 1e-3) / 1e9
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": case.q_dtype if case.kvd != "int8" else "int8/" + case.q_dtype,
+                "data": "synthetic",
+                "config": {"workload": case.name, "batch": case.batch, "q_heads": case.heads,
+                           "kv_heads": case.kv_heads, "head_dim": case.dk, "block_size": case.block_size,
+                           "context_tokens": int(lens.sum()), "kv_bytes_per_step": kv_bytes_global,
+                           "parallelism": f"kv-head shard x{world}" if world > 1 else "single GPU",
+                           "l2": "KV cache per GPU (%.0f MB) is larger than the 126 MB L2" %
+                                 (wl.kv_bytes(shard, lens) / 1e6),
+                           "kernel": {1: "generic", 2: "tma_mma", 3: "mla_tc5"}.get(info.kernel, "?"),
+                           "ctas": info.num_ctas, "partials": info.num_partials},
+                "tokens_per_s": case.batch / (ms * 1e-3),
+                "pct_of_8000_gbs": 100.0 * value / (8000.0 * world),
+                "pct_of_measured_peak": 100.0 * value / (peak * world),
+                "gpu_launches": launches_per_step * args.steps,
+                "clocks": clocks,
+                "e2e": {"value": kv_bytes_global / (e2e["ms"] * 1e-3) / 1e9, "unit": UNIT,
+                        "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                        "ms_per_step": e2e["ms"], "tokens_per_s": case.batch / (e2e["ms"] * 1e-3)},
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT,
+                             "frac": achieved / peak, "peak_kind": "of " + peak_kind,
+                             "kernel": "pa attention kernel, per GPU", "kernel_ms": kernel_ms,
+                             "traffic": ncu_traffic_bytes(case.name)}}
+        if world == 1 and not args.no_cpu_baseline:
+            base, ref_out = cpu_baseline(case, wl, d, lens)
+            line["cpu_baseline"] = base
+            err = np.abs(wl.to_f32(wl.torch_to_host(out, case.q_dtype), case.q_dtype) -
+                         wl.to_f32(ref_out, case.q_dtype)).max()
+            line["max_abs_err_vs_oracle"] = float(err)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_e2e(args, case, wl, capi, d, lens, dev, world, gathered):
+    """The same step through atb::Operation Setup/Execute with HOST buffers: every step copies the
+    query, the new K/V tokens, slot_mapping, block_tables and context_lens from pinned host memory,
+    re-plans from the host context_lens, runs ReshapeAndCache + PagedAttention and reads the output
+    back to pinned host memory.  The KV cache itself is the path's resident state and stays in HBM."""
+    import torch
+    import torch.distributed as dist
+    T = capi.atb_tensor
+    stream = torch.cuda.Stream()
+    host = {k: d[k].cpu().pin_memory() for k in ("q", "new_k", "block_tables", "slot_mapping", "context_lens")}
+    if not case.mla:
+        host["new_v"] = d["new_v"].cpu().pin_memory()
+    devb = {k: torch.empty_like(d[k]) for k in host}
+    out = torch.zeros((case.batch, case.heads, case.dv), dtype=d["q"].dtype, device=dev)
+    out_host = torch.empty_like(out, device="cpu").pin_memory()
+    lens_host = host["context_lens"].numpy()
+    ctx = capi.Context(stream.cuda_stream)
+    rac_param = capi.ReshapeAndCacheParam()
+    rac_param.kvCacheCfg = 1 if case.mla else 0
+    rac = capi.Operation(rac_param)
+    pa_kw = dict(headNum=case.heads, kvHeadNum=case.kv_heads, qkScale=case.qk_scale)
+    if case.kvd == "int8":
+        pa_kw["quantType"] = 1
+    if case.mla:
+        pa_kw["mlaVHeadSize"] = case.dv
+    pa = capi.Operation(capi.PagedAttentionParam(**pa_kw))
+    if case.mla:
+        rac_in = [T(devb["new_k"]), T(d["k_cache"]), T(devb["slot_mapping"])]
+        rac_out = [T(d["k_cache"])]
+        pa_in = [T(devb["q"]), T(d["k_cache"]), T(devb["block_tables"]), T(devb["context_lens"], host=lens_host)]
+    else:
+        rac_in = [T(devb["new_k"]), T(devb["new_v"]), T(d["k_cache"]), T(d["v_cache"]), T(devb["slot_mapping"])]
+        rac_out = [T(d["k_cache"]), T(d["v_cache"])]
+        pa_in = [T(devb["q"]), T(d["k_cache"]), T(d["v_cache"]), T(devb["block_tables"]),
+                 T(devb["context_lens"], host=lens_host)]
+    if case.kvd == "int8":
+        pa_in += [T(d["k_descale"]), T(d["v_descale"])]
+    pa_out = [T(out)]
+    ws_bytes = pa.setup(pa_in, pa_out, ctx)
+    ws = torch.empty(max(ws_bytes * 2, 256), dtype=torch.uint8, device=dev)
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    d2h = out.numel() * out.element_size()
+
+    def step():
+        for k in host:
+            devb[k].copy_(host[k], non_blocking=True)
+        rac.setup(rac_in, rac_out, ctx)
+        rac.execute(rac_in, rac_out, None, 0, ctx)
+        need = pa.setup(pa_in, pa_out, ctx)          # re-plans from the host context_lens
+        pa.execute(pa_in, pa_out, ws.data_ptr(), max(need, ws_bytes), ctx)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, out)
+        out_host.copy_(out, non_blocking=True)
+        stream.synchronize()                          # the caller consumes the result every step
+
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            step()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            step()
+        torch.cuda.synchronize()
+        ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    return {"ms": ms, "h2d": h2d, "d2h": d2h}
+
+
+if __name__ == "__main__":
+    main()
