@@ -8,7 +8,8 @@ ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 OUT = os.path.join(PKG, "libatb_b200.so")
 
-CU_SOURCES = ["reshape_and_cache.cu", "pa_generic.cu", "pa_combine.cu", "pa_tma_mma.cu", "atb_scale_convert.cu"]
+CU_SOURCES = ["reshape_and_cache.cu", "pa_generic.cu", "pa_combine.cu", "pa_tma_mma.cu", "atb_scale_convert.cu",
+              "pa_noalloc.cu"]
 CPP_SOURCES = ["pa_planner.cpp", "c_api.cpp", "atb_operation_base.cpp", "atb_paged_attention.cpp",
                "atb_reshape_and_cache.cpp", "atb_c_wrappers.cpp"]
 

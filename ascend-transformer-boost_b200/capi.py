@@ -88,6 +88,7 @@ EXPORTS = [
     "atb_b200_operation_create_paged_attention", "atb_b200_operation_create_reshape_and_cache",
     "atb_b200_operation_input_num", "atb_b200_operation_output_num", "atb_b200_operation_infer_shape",
     "atb_b200_operation_setup", "atb_b200_operation_execute", "atb_b200_operation_destroy", "atb_b200_version",
+    "atb_b200_pa_decode_static_scratch",
 ]
 
 _lib = None
@@ -125,6 +126,7 @@ def lib():
         L.atb_b200_operation_execute.argtypes = [vp, P(AtbTensor), u32, P(AtbTensor), u32, vp, u64, vp]
         L.atb_b200_operation_destroy.argtypes = [vp]
         L.atb_b200_version.restype = ctypes.c_char_p
+        L.atb_b200_pa_decode_static_scratch.argtypes = [P(PaDesc), vp, P(PaTensors), vp]
         _lib = L
     return _lib
 

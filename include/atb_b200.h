@@ -129,6 +129,33 @@ int atb_b200_pa_plan_device_status(atb_b200_pa_plan *plan, void *workspace, void
 int atb_b200_pa_plan_set_profiling(atb_b200_pa_plan *plan, int enable);
 int atb_b200_pa_plan_kernel_ms(atb_b200_pa_plan *plan, int32_t launches_back, float *ms);
 
+/*
+ * Paged decode attention without any allocation.  No counterpart in the reference: there the
+ * caller always owns a workspace.  This one is for callers that may not allocate at all - a server
+ * that hands its whole device memory to its own pool and forbids cudaMalloc afterwards, a
+ * latency-bound host thread that must not take an allocator lock, a plugin inside a runtime whose
+ * allocator has to stay the only one.  One call plans the split on the stack (about 80 KB of
+ * stack), uploads the plan from there and runs the same attention and combine kernels as
+ * atb_b200_pa_launch, with their workspace taken from a scratch array built into the library
+ * (8 MiB + 320 KiB of device memory on every GPU that loads the library, held until exit).
+ *
+ * Limits - a call beyond any of them is refused with ERROR_INVALID_PARAM and a message on stderr,
+ * nothing is truncated: batch <= 1024; CTA groups <= 1024; split-KV partials x num_heads <= 65536;
+ * partials x num_heads x head_dim_v <= 2097152 floats.  (The five benchmark shapes need at most a
+ * quarter of that.)
+ *
+ * The scratch is shared by every call and keeps the last call's contents; a call writes all it
+ * later reads (the uploaded plan carries a zeroed status word).  Calls whose kernels can overlap on
+ * the GPU - different streams without ordering, several host threads - race on it: keep them on one
+ * stream or order them yourself.
+ *
+ * The first call on each device looks the scratch's device address up (cudaGetSymbolAddress, with
+ * that device current) and caches it; make that first call outside of any stream capture.  The
+ * call uses no cudaMalloc, cudaFree, cudaHostAlloc, event creation or other allocating routine.
+ */
+int atb_b200_pa_decode_static_scratch(const atb_b200_pa_desc *desc, const int32_t *context_lens_host,
+                                      const atb_b200_pa_tensors *tensors, void *stream);
+
 /* ---------------------------------------------------------------- operator level */
 
 /* Mirrors atb::Tensor (include/atb/types.h:118-127 of the reference). */

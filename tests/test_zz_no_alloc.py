@@ -1,0 +1,73 @@
+"""The allocation-free entry point against the regular one.
+
+Some callers of this library cannot allocate: a server that gave all device memory to its own pool
+and bans cudaMalloc, or a host thread with a latency bound.  For them the library has
+`atb_b200_pa_decode_static_scratch`, which keeps its workspace in a scratch array built into the
+library.  This test calls it twice in a row through the C ABI (the second call finds the first
+call's leftovers in the shared scratch) and compares with `atb_b200_pa_launch`, which uses a
+caller-provided workspace, on the same inputs; both plan the same split, so the outputs must agree
+to within the parity tolerance (they are in fact bit-identical).  It also checks that a call beyond
+the built-in capacity is refused.  The file name sorts last so that a run stopping at the first
+failure has already run every other test.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+
+from helpers import capi, host_inputs_to_device, tol_for, wl
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def _static_scratch_call(case, h, d, out):
+    desc = capi.make_desc(case.batch, case.heads, case.kv_heads, case.dk, case.dv, case.block_size, h["num_blocks"],
+                          h["block_tables"].shape[1], case.q_dtype, case.kvd, case.qk_scale,
+                          v_row_dim=case.dk if case.mla else case.dv)
+    t = capi.pa_tensors(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], out, d["k_descale"], d["v_descale"],
+                        d["k_offset"], d["v_offset"])
+    lens = np.ascontiguousarray(h["context_lens"], dtype=np.int32)
+    return capi.lib().atb_b200_pa_decode_static_scratch(ctypes.byref(desc), lens.ctypes.data, ctypes.byref(t),
+                                                        capi.torch_stream_ptr())
+
+
+@pytest.mark.parametrize("case", [
+    wl.Case("noalloc_gqa4_bf16", batch=12, heads=32, kv_heads=8, q_dtype="bf16", ctx=("uniform", 500, 6000), seed=41),
+    wl.Case("noalloc_gqa15_fp16", batch=6, heads=30, kv_heads=2, q_dtype="fp16", ctx=("uniform", 88, 4000), seed=42),
+], ids=lambda c: c.name)
+def test_static_scratch_matches_workspace_entry_point(case):
+    h = wl.make_host_inputs(case)
+    d = host_inputs_to_device(case, h)
+    ref = capi.paged_attention(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], h["context_lens"],
+                               case.qk_scale, dv=case.dv)
+    torch.cuda.synchronize()
+    ref_f = ref.float().cpu().numpy()
+    for call in range(2):                      # two calls in a row share the scratch
+        out = torch.zeros_like(ref)
+        rc = _static_scratch_call(case, h, d, out)
+        assert rc == 0, rc
+        torch.cuda.synchronize()
+        err = np.abs(out.float().cpu().numpy() - ref_f).max()
+        assert err <= tol_for(case), (call, err)
+        assert torch.equal(out.view(torch.int16), ref.view(torch.int16)), call
+    # a different, shorter workload right after: nothing stale may leak from the previous call
+    h2 = dict(h, context_lens=np.maximum(h["context_lens"] // 3, 1).astype(np.int32))
+    ref2 = capi.paged_attention(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], h2["context_lens"],
+                                case.qk_scale, dv=case.dv)
+    out2 = torch.zeros_like(ref2)
+    assert _static_scratch_call(case, h2, d, out2) == 0
+    torch.cuda.synchronize()
+    assert np.abs(out2.float().cpu().numpy() - ref2.float().cpu().numpy()).max() <= tol_for(case)
+
+
+def test_static_scratch_refuses_oversized_calls():
+    # 1025 sequences: above the built-in batch limit; must be refused before anything is launched
+    desc = capi.make_desc(1025, 8, 8, 128, 128, 128, 16, 1, "fp16", qk_scale=0.1)
+    lens = np.ones(1025, dtype=np.int32)
+    q = torch.zeros(1, device="cuda")
+    t = capi.pa_tensors(q, q, q, q, q)
+    rc = capi.lib().atb_b200_pa_decode_static_scratch(ctypes.byref(desc), lens.ctypes.data, ctypes.byref(t),
+                                                      capi.torch_stream_ptr())
+    assert rc == capi.ERROR_INVALID_PARAM
+    torch.cuda.synchronize()
