@@ -21,6 +21,10 @@ cudaError_t launch_pa_generic(const PaArgs &args, int q_dtype, int kv_dtype, cud
 bool pa_tma_mma_supported(int dk, int dv, int v_row_dim, int block_size, int group, int q_dtype, int kv_dtype);
 cudaError_t launch_pa_tma_mma(const PaArgs &args, int q_dtype, int kv_dtype, int num_blocks, cudaStream_t stream);
 
+// The same for an int8 cache with per-channel descale (and optional offsets).
+bool pa_tma_mma_i8_supported(int dk, int dv, int v_row_dim, int block_size, int group, int q_dtype, int kv_dtype);
+cudaError_t launch_pa_tma_mma_i8(const PaArgs &args, int q_dtype, int num_blocks, cudaStream_t stream);
+
 // Merges the split-KV partials of every split sequence into the output.
 cudaError_t launch_pa_combine(const PaArgs &args, int n_combine_seqs, int q_dtype, cudaStream_t stream);
 

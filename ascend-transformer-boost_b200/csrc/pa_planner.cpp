@@ -42,7 +42,9 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
     }
     const int group = d.num_heads / d.kv_heads;
     const bool tma_ok = pa_tma_mma_supported(d.head_dim_k, d.head_dim_v, d.v_row_dim, d.block_size, group, d.q_dtype,
-                                             d.kv_dtype);
+                                             d.kv_dtype) ||
+                        pa_tma_mma_i8_supported(d.head_dim_k, d.head_dim_v, d.v_row_dim, d.block_size, group, d.q_dtype,
+                                                d.kv_dtype);
     const bool gen_ok = pa_generic_supported(d.head_dim_k, d.head_dim_v, d.q_dtype, d.kv_dtype);
     int kernel = d.kernel;
     if (kernel == ATB_B200_KERNEL_AUTO) {

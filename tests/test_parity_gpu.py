@@ -21,8 +21,7 @@ torch = pytest.importorskip("torch")
 def _kernels_for(case):
     ks = [capi.KERNEL_AUTO]
     group = case.heads // case.kv_heads
-    if (case.dk == 128 and case.dv == 128 and case.block_size == 128 and group <= 8 and not case.mla
-            and case.kvd != "int8"):
+    if case.dk == 128 and case.dv == 128 and case.block_size == 128 and group <= 8 and not case.mla:
         ks.append(capi.KERNEL_GENERIC)
     return ks
 
