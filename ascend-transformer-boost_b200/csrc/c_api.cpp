@@ -260,6 +260,8 @@ int atb_b200_pa_launch(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, voi
     if (h.kernel == ATB_B200_KERNEL_TMA_MMA) {
         e = d.kv_dtype == kInt8 ? launch_pa_tma_mma_i8(a, d.q_dtype, d.num_blocks, stream)
                                 : launch_pa_tma_mma(a, d.q_dtype, d.kv_dtype, d.num_blocks, stream);
+    } else if (h.kernel == ATB_B200_KERNEL_MLA_TC5) {
+        e = launch_pa_mla_tc5(a, d.q_dtype, d.num_blocks, stream);
     } else {
         e = launch_pa_generic(a, d.q_dtype, d.kv_dtype, stream);
     }

@@ -1,0 +1,569 @@
+// Paged decode attention over the MLA combined latent cache (one kv head, K row = 576 = 512 latent
+// + 64 rope, V = the first 512 columns of the same row) on the 5th-generation tensor cores.
+//
+// One CTA per (CTA group, 64 query heads), one CTA per SM.  Warp roles:
+//   warp 4  - TMA producer: Q tile of the token range (64 heads x 576) once, then 64-token K tiles
+//             (9 boxes of 64 tokens x 64 elements, 128-byte swizzle) into a 2-stage ring;
+//   warp 5  - one elected thread issues tcgen05.mma (M = 64 heads):
+//               S[64 x 64 tokens]  = Q . K^T          36 MMAs, K-major A and B, accumulator in TMEM
+//               O[64 x 512]       += P . V            8 MMAs of N = 256; V is the same shared-memory
+//                                                      tile read MN-major, so the cache row crosses
+//                                                      the memory system once
+//             and owns the TMEM allocation;
+//   warps 0-3 - softmax: tcgen05.ld one S row per thread (no cross-thread reductions), running max /
+//             sum in the exp2 domain, P -> bf16/fp16 into shared memory for the P.V MMA; O stays in
+//             TMEM for the whole token range and is rescaled only when a row's maximum grows by more
+//             than 2^8 (the final division by the row sum absorbs the stale scale).
+// TMEM: an M = 64 accumulator occupies 16 of the 32 lanes of each warp's quadrant, so O (512 columns)
+// lives in the lower half-quadrants and the two S buffers in the upper ones.
+//
+// Replaces MLAttentionDecoderAic / paged_multi_latent_attention_mask of the reference
+// (src/kernels/mixkernels/pagedattention/op_kernel/paged_MLAttention_combine_cache_mask_mix.cce:24-150,
+//  paged_attention_decoder_nd_common.cce:2861-3897), which never splits the KV range
+// (tiling/paged_attention_tiling_dependency.cpp:230); here token ranges are split and merged like the
+// other kernels.  Math as the golden: fp32 scores and softmax, P rounded to the query dtype.
+#include <cuda.h>
+#include <mutex>
+#include <type_traits>
+#include "common.cuh"
+#include "kernels.h"
+
+namespace atb_b200 {
+namespace {
+
+constexpr int kHeadsPerCta = 64;
+constexpr int kTok = 64;                 // tokens per stage
+constexpr int kDk = 576, kDv = 512;
+constexpr int kAtoms = kDk / 64;         // 9 boxes of 64 elements per row
+constexpr int kAtomBytes = 64 * 128;     // 64 rows x 128 B
+constexpr int kTileBytes = kAtoms * kAtomBytes; // 73728
+constexpr int kStages = 2;
+constexpr int kPBytes = 64 * 128;        // P: 64 heads x 64 tokens x 2 B
+constexpr int kNumBars = 16;
+constexpr int kSmemBytes = (1 + kStages) * kTileBytes + kPBytes + kNumBars * 8 + 64 + 1024;
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+
+// ---- tcgen05 wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+                 "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate ? 1u : 0u)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+                   "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+                   "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32])
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+                 "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+                 "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+                 "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
+                 "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
+                 "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_3d(void *smem_dst, const void *tmap, uint64_t *bar, int c0, int c1, int c2)
+{
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+                 "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(smem_dst)),
+                 "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle.  Offsets are in bytes.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3fffu);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
+    d |= (uint64_t)1 << 46; // descriptor version of this architecture
+    d |= (uint64_t)2 << 61; // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor of kind::f16: fp32 accumulate, A/B format (0 fp16, 1 bf16), majors, N, M.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t b_mn_major, uint32_t n, uint32_t m)
+{
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (b_mn_major << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+enum Bar { kQFull = 0, kQEmpty, kKvFull0, kKvFull1, kKvEmpty0, kKvEmpty1, kSFull0, kSFull1, kSEmpty0, kSEmpty1, kPFull, kPvDone };
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap, const PaArgs a)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *q_smem = base;
+    uint8_t *kv_smem = base + kTileBytes;
+    uint8_t *p_smem = kv_smem + kStages * kTileBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(p_smem + kPBytes);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int cols = a.plan.cols;
+    const int grp = blockIdx.x / cols;
+    const int col = blockIdx.x - grp * cols;
+    const int head0 = col * kHeadsPerCta;
+    const int nh = min(kHeadsPerCta, a.num_heads - head0);
+    constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bars[kQFull], 1);
+        mbar_init(&bars[kQEmpty], 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bars[kKvFull0 + s], 1);
+            mbar_init(&bars[kKvEmpty0 + s], 1);
+            mbar_init(&bars[kSFull0 + s], 1);
+            mbar_init(&bars[kSEmpty0 + s], 4);
+        }
+        mbar_init(&bars[kPFull], 4);
+        mbar_init(&bars[kPvDone], 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_o = tmem_base;                 // lanes 0-15 of every quadrant, columns 0..511
+    const uint32_t tmem_s = tmem_base + (16u << 16);   // lanes 16-31 of every quadrant, columns 0..127
+
+    const int item_begin = a.plan.group_begin[grp], item_end = a.plan.group_begin[grp + 1];
+
+    auto wait = [&](int bar, uint32_t parity) -> bool {
+        for (uint32_t i = 0; i < (1u << 21); ++i) {
+            if (mbar_try_wait(&bars[bar], parity)) {
+                return true;
+            }
+            if (i > 32) {
+                __nanosleep(64);
+                if (*abort_flag) {
+                    return false;
+                }
+            }
+        }
+        *abort_flag = 1;
+        atomicExch(a.plan.status, kStatusWaitTimeout);
+        return false;
+    };
+
+    if (warp == 4) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&qmap);
+            tma_prefetch_desc(&kmap);
+        }
+        uint32_t g = 0; // global stage counter
+        bool alive = true;
+        for (int it = item_begin, i = 0; it < item_end && alive; ++it, ++i) {
+            const PaItem item = a.plan.items[it];
+            if (lane == 0) {
+                if (!wait(kQEmpty, (i & 1) ^ 1u)) {
+                    alive = false;
+                } else {
+                    mbar_expect_tx(&bars[kQFull], kTileBytes);
+                    for (int at = 0; at < kAtoms; ++at) {
+                        // rows past num_heads are outside the tensor: filled with zeros
+                        tma_load_3d(q_smem + at * kAtomBytes, &qmap, &bars[kQFull], at * 64, head0, item.seq);
+                    }
+                }
+            }
+            alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
+            const int n_st = (item.tok_end - item.tok_begin + kTok - 1) / kTok;
+            const int32_t *bt = a.block_tables + (int64_t)item.seq * a.max_blocks;
+            for (int st0 = 0; st0 < n_st && alive; st0 += 32) {
+                int blk = 0;
+                if (st0 + lane < n_st) {
+                    blk = bt[(item.tok_begin + (st0 + lane) * kTok) / a.block_size];
+                }
+                const int cnt = min(32, n_st - st0);
+                for (int j = 0; j < cnt && alive; ++j, ++g) {
+                    const int b = __shfl_sync(0xffffffffu, blk, j);
+                    if (lane == 0) {
+                        const int s = g & 1;
+                        if (!wait(kKvEmpty0 + s, ((g >> 1) & 1) ^ 1u)) {
+                            alive = false;
+                        } else {
+                            const int tok_in_blk = (item.tok_begin + (st0 + j) * kTok) % a.block_size;
+                            uint8_t *dst = kv_smem + s * kTileBytes;
+                            mbar_expect_tx(&bars[kKvFull0 + s], kTileBytes);
+                            for (int at = 0; at < kAtoms; ++at) {
+                                tma_load_4d(dst + at * kAtomBytes, &kmap, &bars[kKvFull0 + s], at * 64, 0, tok_in_blk, b);
+                            }
+                        }
+                    }
+                    alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = instr_desc(kFmt, 0, kTok, kHeadsPerCta);
+            constexpr uint32_t idesc_pv = instr_desc(kFmt, 1, 256, kHeadsPerCta);
+            const uint32_t q_addr = smem_u32(q_smem), kv_addr = smem_u32(kv_smem), p_addr = smem_u32(p_smem);
+            uint32_t g = 0;
+            bool alive = true;
+            auto issue_qk = [&](uint32_t gg, bool last_of_item) -> bool {
+                const int s = gg & 1;
+                if (!wait(kKvFull0 + s, (gg >> 1) & 1) || !wait(kSEmpty0 + s, ((gg >> 1) & 1) ^ 1u)) {
+                    return false;
+                }
+                tc_fence_after();
+                const uint32_t kb = kv_addr + s * kTileBytes;
+#pragma unroll 1
+                for (int at = 0; at < kAtoms; ++at) {
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        const uint64_t da = smem_desc(q_addr + at * kAtomBytes + ks * 32, 16, 1024);
+                        const uint64_t db = smem_desc(kb + at * kAtomBytes + ks * 32, 16, 1024);
+                        tc_mma(tmem_s + s * 64, da, db, idesc_qk, (at | ks) != 0);
+                    }
+                }
+                tc_commit(&bars[kSFull0 + s]);
+                if (last_of_item) {
+                    tc_commit(&bars[kQEmpty]);
+                }
+                return true;
+            };
+            for (int it = item_begin, i = 0; it < item_end && alive; ++it, ++i) {
+                const PaItem item = a.plan.items[it];
+                const int n_st = (item.tok_end - item.tok_begin + kTok - 1) / kTok;
+                if (!wait(kQFull, i & 1)) {
+                    break;
+                }
+                alive = issue_qk(g, n_st == 1);
+                for (int st = 0; st < n_st && alive; ++st, ++g) {
+                    if (st + 1 < n_st) {
+                        alive = issue_qk(g + 1, st + 2 == n_st);
+                        if (!alive) {
+                            break;
+                        }
+                    }
+                    if (!wait(kPFull, g & 1)) {
+                        alive = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const int s = g & 1;
+                    const uint32_t vb = kv_addr + s * kTileBytes;
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) {
+                            const uint64_t da = smem_desc(p_addr + ks * 32, 16, 1024);
+                            // V^T operand: 64-element boxes along N are 8192 B apart, 8-token groups 1024 B apart
+                            const uint64_t db = smem_desc(vb + (4 * half) * kAtomBytes + ks * 2048, kAtomBytes, 1024);
+                            tc_mma(tmem_o + half * 256, da, db, idesc_pv, st != 0 || ks != 0);
+                        }
+                    }
+                    tc_commit(&bars[kKvEmpty0 + s]);
+                    tc_commit(&bars[kPvDone]);
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax / epilogue warps 0..3
+        const bool s_lane = lane >= 16;                 // upper half-quadrant: the S rows
+        const int row = warp * 16 + (lane & 15);        // head within the CTA
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        uint32_t g = 0;
+        bool alive = true;
+        for (int it = item_begin; it < item_end && alive; ++it) {
+            const PaItem item = a.plan.items[it];
+            const int n_st = (item.tok_end - item.tok_begin + kTok - 1) / kTok;
+            float m_used = -INFINITY, l = 0.f;
+            for (int st = 0; st < n_st && alive; ++st, ++g) {
+                const int sb = g & 1;
+                const int valid = min(kTok, item.tok_end - (item.tok_begin + st * kTok));
+                if (!wait(kSFull0 + sb, (g >> 1) & 1)) {
+                    alive = false;
+                    break;
+                }
+                tc_fence_after();
+                uint32_t r0[32], r1[32];
+                tmem_ld32(tmem_base + lane_base + sb * 64, r0);
+                tmem_ld32(tmem_base + lane_base + sb * 64 + 32, r1);
+                tmem_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&bars[kSEmpty0 + sb]);
+                }
+                // scores in the exp2 domain, tokens past the end of the range masked
+                float mx = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    float v0 = __uint_as_float(r0[j]) * a.scale_log2;
+                    float v1 = __uint_as_float(r1[j]) * a.scale_log2;
+                    v0 = (j < valid) ? v0 : -INFINITY;
+                    v1 = (j + 32 < valid) ? v1 : -INFINITY;
+                    r0[j] = __float_as_uint(v0);
+                    r1[j] = __float_as_uint(v1);
+                    mx = fmaxf(mx, fmaxf(v0, v1));
+                }
+                // lazy rescale: keep the old reference maximum unless it is exceeded by more than 2^8
+                float factor = 1.f;
+                if (s_lane && mx > m_used + 8.f) {
+                    factor = exp2f(m_used - mx); // 0 on the first tile
+                    m_used = mx;
+                    l *= factor;
+                }
+                const bool rescale_row = s_lane && factor != 1.f && st > 0;
+                const bool rescale_any = __any_sync(0xffffffffu, rescale_row);
+                float lsum = 0.f;
+                uint32_t pk[32];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float p0 = fast_exp2(__uint_as_float(r0[2 * j]) - m_used);
+                    const float p1 = fast_exp2(__uint_as_float(r0[2 * j + 1]) - m_used);
+                    const float p2 = fast_exp2(__uint_as_float(r1[2 * j]) - m_used);
+                    const float p3 = fast_exp2(__uint_as_float(r1[2 * j + 1]) - m_used);
+                    lsum += (p0 + p1) + (p2 + p3);
+                    pk[j] = Elem<T>::pack2(p0, p1);
+                    pk[16 + j] = Elem<T>::pack2(p2, p3);
+                }
+                l += lsum;
+                // P(g) overwrites P(g-1) and a rescale touches O: both need P.V(g-1) to have finished
+                if (g > 0 && !wait(kPvDone, (g - 1) & 1)) {
+                    alive = false;
+                    break;
+                }
+                if (rescale_any) {
+                    // O rows live in lanes 0..15; the multiplier comes from the row's S lane.  The S lanes
+                    // of columns 0..127 are rewritten with their own values, so the next S tile must be
+                    // complete before they are touched.
+                    if (st + 1 < n_st && !wait(kSFull0 + (sb ^ 1), ((g + 1) >> 1) & 1)) {
+                        alive = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const float f_o = __shfl_sync(0xffffffffu, factor, (lane & 15) + 16);
+                    const float mul = s_lane ? 1.f : f_o;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < kDv; c0 += 32) {
+                        uint32_t t[32];
+                        tmem_ld32(tmem_base + lane_base + c0, t);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            t[j] = __float_as_uint(__uint_as_float(t[j]) * mul);
+                        }
+                        tmem_st32(tmem_base + lane_base + c0, t);
+                    }
+                    tmem_wait_st();
+                }
+                if (s_lane) {
+                    // row of P: 64 tokens = 8 chunks of 16 B, 128-byte swizzle
+                    uint8_t *prow = p_smem + row * 128;
+#pragma unroll
+                    for (int ch = 0; ch < 8; ++ch) {
+                        *reinterpret_cast<uint4 *>(prow + ((ch ^ (row & 7)) << 4)) =
+                            make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+                    }
+                }
+                if (valid < kTok) {
+                    // rows of V past the end of the range may hold anything: clear them (0 * NaN != 0)
+                    uint8_t *vt = kv_smem + sb * kTileBytes;
+                    const int rows = kTok - valid;
+                    for (int idx = threadIdx.x; idx < rows * 8 * 8; idx += 128) {
+                        const int at = idx / (rows * 8), rem = idx - at * (rows * 8);
+                        const int rr = valid + (rem >> 3), ch = rem & 7;
+                        *reinterpret_cast<uint4 *>(vt + at * kAtomBytes + rr * 128 + (ch << 4)) = make_uint4(0, 0, 0, 0);
+                    }
+                }
+                fence_proxy_async();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&bars[kPFull]);
+                }
+            }
+            if (!alive) {
+                break;
+            }
+            // ---- end of the token range: O / l -> output row or split-KV partial
+            if (!wait(kPvDone, (g - 1) & 1)) {
+                alive = false;
+                break;
+            }
+            tc_fence_after();
+            const float l_row = __shfl_sync(0xffffffffu, l, (lane & 15) + 16);
+            const float m_row = __shfl_sync(0xffffffffu, m_used, (lane & 15) + 16);
+            const float inv = 1.f / l_row;
+            const int h = head0 + row;
+            const bool writer = !s_lane && row < nh;
+            T *out_row = static_cast<T *>(a.out) + ((int64_t)item.seq * a.num_heads + h) * kDv;
+            float *part_row = a.plan.part_o + ((int64_t)(item.slot < 0 ? 0 : item.slot) * a.num_heads + h) * kDv;
+#pragma unroll 1
+            for (int c0 = 0; c0 < kDv; c0 += 32) {
+                uint32_t t[32];
+                tmem_ld32(tmem_base + lane_base + c0, t);
+                tmem_wait_ld();
+                if (writer) {
+                    if (item.slot < 0) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint4 v;
+                            v.x = Elem<T>::pack2(__uint_as_float(t[8 * j]) * inv, __uint_as_float(t[8 * j + 1]) * inv);
+                            v.y = Elem<T>::pack2(__uint_as_float(t[8 * j + 2]) * inv, __uint_as_float(t[8 * j + 3]) * inv);
+                            v.z = Elem<T>::pack2(__uint_as_float(t[8 * j + 4]) * inv, __uint_as_float(t[8 * j + 5]) * inv);
+                            v.w = Elem<T>::pack2(__uint_as_float(t[8 * j + 6]) * inv, __uint_as_float(t[8 * j + 7]) * inv);
+                            *reinterpret_cast<uint4 *>(out_row + c0 + 8 * j) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            *reinterpret_cast<float4 *>(part_row + c0 + 4 * j) =
+                                make_float4(__uint_as_float(t[4 * j]) * inv, __uint_as_float(t[4 * j + 1]) * inv,
+                                            __uint_as_float(t[4 * j + 2]) * inv, __uint_as_float(t[4 * j + 3]) * inv);
+                        }
+                    }
+                }
+            }
+            if (writer && item.slot >= 0) {
+                a.plan.part_lse[(int64_t)item.slot * a.num_heads + h] = m_row + log2f(l_row);
+            }
+            // the next range's first P.V overwrites O: all reads of O must be done first.  It cannot start
+            // before the next P tile is signalled by these same warps, which orders it after this point.
+            tc_fence_before();
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode_fn()
+{
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeFn>(p);
+        }
+    });
+    return fn;
+}
+
+template <typename T> cudaError_t launch_typed(const PaArgs &args, const CUtensorMap &qm, const CUtensorMap &km, cudaStream_t s)
+{
+    auto kern = pa_mla_tc5_kernel<T>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        if (dev >= 0 && dev < 64) {
+            configured[dev] = true;
+        }
+    }
+    const int grid = args.plan.n_cta_groups * args.plan.cols;
+    kern<<<grid, kThreads, kSmemBytes, s>>>(qm, km, args);
+    return cudaGetLastError();
+}
+
+} // namespace
+
+bool pa_mla_tc5_supported(int dk, int dv, int v_row_dim, int block_size, int kv_heads, int q_dtype, int kv_dtype)
+{
+    return dk == kDk && dv == kDv && v_row_dim == kDk && kv_heads == 1 && block_size >= kTok && block_size % kTok == 0 &&
+           block_size <= 256 && (q_dtype == kFp16 || q_dtype == kBf16) && kv_dtype == q_dtype;
+}
+
+cudaError_t launch_pa_mla_tc5(const PaArgs &args, int q_dtype, int num_blocks, cudaStream_t stream)
+{
+    EncodeFn fn = get_encode_fn();
+    if (fn == nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    const CUtensorMapDataType dt = q_dtype == kBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMap qm, km;
+    {
+        // query [batch][num_heads][576]; box = 64 elements x 64 heads of one sequence
+        cuuint64_t dims[3] = {(cuuint64_t)kDk, (cuuint64_t)args.num_heads, (cuuint64_t)args.batch};
+        cuuint64_t strides[2] = {(cuuint64_t)kDk * 2, (cuuint64_t)args.num_heads * kDk * 2};
+        cuuint32_t box[3] = {64, kHeadsPerCta, 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        if (fn(&qm, dt, 3, const_cast<void *>(args.q), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+            return cudaErrorInvalidValue;
+        }
+    }
+    {
+        // cache [num_blocks][block_size][1][576]; box = 64 elements x 64 tokens of one block
+        cuuint64_t dims[4] = {(cuuint64_t)kDk, 1, (cuuint64_t)args.block_size, (cuuint64_t)num_blocks};
+        cuuint64_t strides[3] = {(cuuint64_t)kDk * 2, (cuuint64_t)kDk * 2, (cuuint64_t)args.block_size * kDk * 2};
+        cuuint32_t box[4] = {64, 1, kTok, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        if (fn(&km, dt, 4, const_cast<void *>(args.k_cache), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+            return cudaErrorInvalidValue;
+        }
+    }
+    return q_dtype == kFp16 ? launch_typed<__half>(args, qm, km, stream) : launch_typed<__nv_bfloat16>(args, qm, km, stream);
+}
+
+} // namespace atb_b200

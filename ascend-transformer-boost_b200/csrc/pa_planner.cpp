@@ -46,12 +46,15 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
                         pa_tma_mma_i8_supported(d.head_dim_k, d.head_dim_v, d.v_row_dim, d.block_size, group, d.q_dtype,
                                                 d.kv_dtype);
     const bool gen_ok = pa_generic_supported(d.head_dim_k, d.head_dim_v, d.q_dtype, d.kv_dtype);
+    const bool mla_ok = pa_mla_tc5_supported(d.head_dim_k, d.head_dim_v, d.v_row_dim, d.block_size, d.kv_heads, d.q_dtype,
+                                             d.kv_dtype);
     int kernel = d.kernel;
     if (kernel == ATB_B200_KERNEL_AUTO) {
-        kernel = tma_ok ? ATB_B200_KERNEL_TMA_MMA : ATB_B200_KERNEL_GENERIC;
+        kernel = tma_ok ? ATB_B200_KERNEL_TMA_MMA : (mla_ok ? ATB_B200_KERNEL_MLA_TC5 : ATB_B200_KERNEL_GENERIC);
     }
     if ((kernel == ATB_B200_KERNEL_TMA_MMA && !tma_ok) || (kernel == ATB_B200_KERNEL_GENERIC && !gen_ok) ||
-        (kernel != ATB_B200_KERNEL_TMA_MMA && kernel != ATB_B200_KERNEL_GENERIC)) {
+        (kernel == ATB_B200_KERNEL_MLA_TC5 && !mla_ok) ||
+        (kernel != ATB_B200_KERNEL_TMA_MMA && kernel != ATB_B200_KERNEL_GENERIC && kernel != ATB_B200_KERNEL_MLA_TC5)) {
         return kErrInvalidTensorDim;
     }
 
@@ -62,6 +65,10 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
         p->heads_per_cta = 8;
         p->chunks_per_kvh = 1;
         p->ctas_per_sm = 2;
+    } else if (kernel == ATB_B200_KERNEL_MLA_TC5) {
+        p->heads_per_cta = 64;
+        p->chunks_per_kvh = (group + 63) / 64;
+        p->ctas_per_sm = 1;
     } else {
         p->heads_per_cta = pa_generic_heads_per_cta(d.head_dim_k, d.head_dim_v);
         p->chunks_per_kvh = (group + p->heads_per_cta - 1) / p->heads_per_cta;

@@ -71,6 +71,8 @@ def test_plan_covers_every_token_exactly_once(case):
 def _cols(case, info):
     if info.kernel == capi.KERNEL_TMA_MMA:
         return case.kv_heads
+    if info.kernel == capi.KERNEL_MLA_TC5:
+        return (case.heads + 63) // 64
     dmax = max(case.dk, case.dv)
     gh = 8 if dmax <= 128 else (4 if dmax <= 256 else 2)
     group = case.heads // case.kv_heads
@@ -84,7 +86,7 @@ def test_plan_is_balanced_on_benchmark_configs(idx):
     info = plan.info
     items, groups = plan.dump()
     n_groups = info.num_ctas // _cols(case, info)
-    per_sm = 2 if info.kernel == capi.KERNEL_TMA_MMA else 4
+    per_sm = {capi.KERNEL_TMA_MMA: 2, capi.KERNEL_MLA_TC5: 1}.get(info.kernel, 4)
     assert info.num_ctas <= 148 * per_sm, "the grid must fit one wave of resident CTAs"
     tiles = [sum((e - b + 127) // 128 for _, b, e, _ in items[groups[g]:groups[g + 1]]) for g in range(n_groups)]
     assert max(tiles) <= np.mean(tiles) * 1.06 + 1
@@ -128,6 +130,9 @@ def test_kernel_selection():
     small = {c.name: c for c in wl.SMALL_CASES}
     assert _plan(small["ragged_d96_bs16_fp16"])[0].info.kernel == capi.KERNEL_GENERIC
     assert _plan(small["gqa127_fp16"])[0].info.kernel == capi.KERNEL_GENERIC
+    assert _plan(small["mla_128h_bf16"])[0].info.kernel == capi.KERNEL_MLA_TC5
+    assert _plan(wl.CONFIGS[2])[0].info.kernel == capi.KERNEL_TMA_MMA      # int8 cache
+    assert _plan(wl.CONFIGS[4])[0].info.kernel == capi.KERNEL_MLA_TC5
 
 
 # ---------------------------------------------------------------- operator layer, error behaviour

@@ -23,6 +23,8 @@ def _kernels_for(case):
     group = case.heads // case.kv_heads
     if case.dk == 128 and case.dv == 128 and case.block_size == 128 and group <= 8 and not case.mla:
         ks.append(capi.KERNEL_GENERIC)
+    if case.mla and case.batch * case.heads <= 4096:
+        ks.append(capi.KERNEL_GENERIC)
     return ks
 
 
