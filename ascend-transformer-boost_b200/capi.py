@@ -49,7 +49,8 @@ class PaPlanInfo(ctypes.Structure):
     _fields_ = [("kernel", ctypes.c_int32), ("num_ctas", ctypes.c_int32), ("num_items", ctypes.c_int32),
                 ("num_partials", ctypes.c_int32), ("num_combine_seqs", ctypes.c_int32),
                 ("tile_tokens", ctypes.c_int32), ("workspace_bytes", ctypes.c_uint64),
-                ("plan_bytes", ctypes.c_uint64)]
+                ("plan_bytes", ctypes.c_uint64), ("kernels_per_launch", ctypes.c_int32),
+                ("reserved", ctypes.c_int32)]
 
 
 class AtbTensor(ctypes.Structure):

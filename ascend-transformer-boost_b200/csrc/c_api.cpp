@@ -91,6 +91,8 @@ int atb_b200_pa_plan_get_info(const atb_b200_pa_plan *plan, atb_b200_pa_plan_inf
     info->tile_tokens = kTileTokens;
     info->workspace_bytes = h.workspace_bytes;
     info->plan_bytes = h.blob_bytes;
+    info->kernels_per_launch = (h.n_partials > 0 && !h.fused_combine) ? 2 : 1;
+    info->reserved = 0;
     return ATB_B200_OK;
 }
 
@@ -237,6 +239,7 @@ int atb_b200_pa_launch(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, voi
     a.plan.part_o = reinterpret_cast<float *>(ws + h.off_part_o);
     a.plan.part_lse = reinterpret_cast<float *>(ws + h.off_lse);
     a.plan.status = reinterpret_cast<int32_t *>(ws + h.off_status);
+    a.plan.counters = (h.fused_combine && h.n_partials > 0) ? reinterpret_cast<int32_t *>(ws + h.off_counters) : nullptr;
     a.plan.n_cta_groups = h.n_cta_groups;
     a.plan.cols = h.cols;
     a.batch = d.batch;
@@ -272,7 +275,9 @@ int atb_b200_pa_launch(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, voi
     if (e != cudaSuccess) {
         return kErrRtFail;
     }
-    e = launch_pa_combine(a, (int)h.combine_seqs.size(), d.q_dtype, stream);
+    if (a.plan.counters == nullptr) {
+        e = launch_pa_combine(a, (int)h.combine_seqs.size(), d.q_dtype, stream);
+    }
     return e == cudaSuccess ? ATB_B200_OK : kErrRtFail;
 }
 

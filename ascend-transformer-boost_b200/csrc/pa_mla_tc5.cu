@@ -250,62 +250,70 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             const uint32_t q_addr = smem_u32(q_smem), kv_addr = smem_u32(kv_smem), p_addr = smem_u32(p_smem);
             uint32_t g = 0;
             bool alive = true;
-            auto issue_qk = [&](uint32_t gg, bool last_of_item) -> bool {
-                const int s = gg & 1;
-                if (!wait(kKvFull0 + s, (gg >> 1) & 1) || !wait(kSEmpty0 + s, ((gg >> 1) & 1) ^ 1u)) {
-                    return false;
-                }
-                tc_fence_after();
-                const uint32_t kb = kv_addr + s * kTileBytes;
-#pragma unroll 1
-                for (int at = 0; at < kAtoms; ++at) {
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        const uint64_t da = smem_desc(q_addr + at * kAtomBytes + ks * 32, 16, 1024);
-                        const uint64_t db = smem_desc(kb + at * kAtomBytes + ks * 32, 16, 1024);
-                        tc_mma(tmem_s + s * 64, da, db, idesc_qk, (at | ks) != 0);
-                    }
-                }
-                tc_commit(&bars[kSFull0 + s]);
-                if (last_of_item) {
-                    tc_commit(&bars[kQEmpty]);
-                }
-                return true;
-            };
+            // Issue order is decided by what is ready, P.V first: a P.V releases its K tile to the
+            // producer, so it must never queue behind a Q.K^T that is still waiting for its tile.
+            auto ready = [&](int bar, uint32_t parity) { return mbar_try_wait(&bars[bar], parity); };
             for (int it = item_begin, i = 0; it < item_end && alive; ++it, ++i) {
                 const PaItem item = a.plan.items[it];
                 const int n_st = (item.tok_end - item.tok_begin + kTok - 1) / kTok;
                 if (!wait(kQFull, i & 1)) {
                     break;
                 }
-                alive = issue_qk(g, n_st == 1);
-                for (int st = 0; st < n_st && alive; ++st, ++g) {
-                    if (st + 1 < n_st) {
-                        alive = issue_qk(g + 1, st + 2 == n_st);
-                        if (!alive) {
+                int next_qk = 0, next_pv = 0;
+                uint32_t idle = 0;
+                while (next_pv < n_st) {
+                    const uint32_t gp = g + next_pv, gq = g + next_qk;
+                    if (next_pv < next_qk && ready(kPFull, gp & 1)) {
+                        tc_fence_after();
+                        const int s = gp & 1;
+                        const uint32_t vb = kv_addr + s * kTileBytes;
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                            for (int ks = 0; ks < 4; ++ks) {
+                                const uint64_t da = smem_desc(p_addr + ks * 32, 16, 1024);
+                                // V^T operand: 64-element boxes along N are 8192 B apart, 8-token groups 1024 B apart
+                                const uint64_t db = smem_desc(vb + (4 * half) * kAtomBytes + ks * 2048, kAtomBytes, 1024);
+                                tc_mma(tmem_o + half * 256, da, db, idesc_pv, next_pv != 0 || ks != 0);
+                            }
+                        }
+                        tc_commit(&bars[kKvEmpty0 + s]);
+                        tc_commit(&bars[kPvDone]);
+                        ++next_pv;
+                        idle = 0;
+                    } else if (next_qk < n_st && next_qk < next_pv + 2 && ready(kKvFull0 + (gq & 1), (gq >> 1) & 1) &&
+                               ready(kSEmpty0 + (gq & 1), ((gq >> 1) & 1) ^ 1u)) {
+                        tc_fence_after();
+                        const int s = gq & 1;
+                        const uint32_t kb = kv_addr + s * kTileBytes;
+#pragma unroll 1
+                        for (int at = 0; at < kAtoms; ++at) {
+#pragma unroll
+                            for (int ks = 0; ks < 4; ++ks) {
+                                const uint64_t da = smem_desc(q_addr + at * kAtomBytes + ks * 32, 16, 1024);
+                                const uint64_t db = smem_desc(kb + at * kAtomBytes + ks * 32, 16, 1024);
+                                tc_mma(tmem_s + s * 64, da, db, idesc_qk, (at | ks) != 0);
+                            }
+                        }
+                        tc_commit(&bars[kSFull0 + s]);
+                        if (next_qk + 1 == n_st) {
+                            tc_commit(&bars[kQEmpty]); // Q of this range is no longer needed
+                        }
+                        ++next_qk;
+                        idle = 0;
+                    } else {
+                        if (++idle > 64) {
+                            __nanosleep(32);
+                        }
+                        if (idle > (1u << 22) || *abort_flag) {
+                            *abort_flag = 1;
+                            atomicExch(a.plan.status, kStatusWaitTimeout);
+                            alive = false;
                             break;
                         }
                     }
-                    if (!wait(kPFull, g & 1)) {
-                        alive = false;
-                        break;
-                    }
-                    tc_fence_after();
-                    const int s = g & 1;
-                    const uint32_t vb = kv_addr + s * kTileBytes;
-#pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-#pragma unroll
-                        for (int ks = 0; ks < 4; ++ks) {
-                            const uint64_t da = smem_desc(p_addr + ks * 32, 16, 1024);
-                            // V^T operand: 64-element boxes along N are 8192 B apart, 8-token groups 1024 B apart
-                            const uint64_t db = smem_desc(vb + (4 * half) * kAtomBytes + ks * 2048, kAtomBytes, 1024);
-                            tc_mma(tmem_o + half * 256, da, db, idesc_pv, st != 0 || ks != 0);
-                        }
-                    }
-                    tc_commit(&bars[kKvEmpty0 + s]);
-                    tc_commit(&bars[kPvDone]);
                 }
+                g += n_st;
             }
         }
     } else {

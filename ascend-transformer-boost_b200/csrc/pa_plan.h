@@ -36,6 +36,8 @@ struct PaDevPlan {
     float *part_o;                // [n_partials, num_heads, dv] normalised partial outputs
     float *part_lse;              // [n_partials, num_heads] log2-domain log-sum-exp
     int32_t *status;              // device status word (0 = ok)
+    int32_t *counters;            // [batch * cols] arrivals per (sequence, column), zero before the launch;
+                                  // non-null = the last range to finish merges the partials itself
     int32_t n_cta_groups;
     int32_t cols;
 };

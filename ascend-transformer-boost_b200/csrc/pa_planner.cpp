@@ -180,6 +180,11 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
     off = align_up(off + p->combine_seqs.size() * sizeof(int32_t), 16);
     p->off_status = off; // zeroed by every upload
     off += 16;
+    p->fused_combine = kernel == ATB_B200_KERNEL_TMA_MMA;
+    p->off_counters = off;
+    if (p->fused_combine && p->n_partials > 0) {
+        off = align_up(off + (uint64_t)d.batch * p->cols * sizeof(int32_t), 16);
+    }
     p->blob_bytes = align_up(off, 256);
     p->off_lse = p->blob_bytes;
     p->off_part_o = align_up(p->off_lse + (uint64_t)p->n_partials * d.num_heads * sizeof(float), 256);

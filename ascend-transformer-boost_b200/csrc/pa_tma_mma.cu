@@ -360,6 +360,57 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 }
             }
         }
+        if (item.slot >= 0 && a.plan.counters != nullptr) {
+            // In-kernel merge: the range that arrives last for this (sequence, kv head) finds every
+            // partial already written (fence + counter) and combines them with their LSE weights.
+            __threadfence();
+            named_bar_sync(1, kConsumerWarps * 32);
+            const int n_parts = a.plan.seq_nparts[item.seq];
+            if (threadIdx.x == 0) {
+                const int old = atomicAdd(&a.plan.counters[item.seq * cols + kvh], 1);
+                sm_l[0] = (old == n_parts - 1) ? 1.f : 0.f;
+            }
+            named_bar_sync(1, kConsumerWarps * 32);
+            const bool last = sm_l[0] != 0.f;
+            if (last) {
+                __threadfence();
+                const int hl = threadIdx.x >> 4;
+                const int d0 = (threadIdx.x & 15) * 8;
+                if (hl < group) {
+                    const int h = kvh * group + hl;
+                    const int pbase = a.plan.seq_part_base[item.seq];
+                    const float *lse = a.plan.part_lse + (int64_t)pbase * a.num_heads + h;
+                    float mx = -INFINITY;
+                    for (int i = 0; i < n_parts; ++i) {
+                        mx = fmaxf(mx, __ldcg(lse + (int64_t)i * a.num_heads));
+                    }
+                    float wsum = 0.f;
+                    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    const float *po = a.plan.part_o + ((int64_t)pbase * a.num_heads + h) * 128 + d0;
+                    for (int i = 0; i < n_parts; ++i) {
+                        const float w = exp2f(__ldcg(lse + (int64_t)i * a.num_heads) - mx);
+                        wsum += w;
+                        const float4 pa = __ldcg(reinterpret_cast<const float4 *>(po + (int64_t)i * a.num_heads * 128));
+                        const float4 pb = __ldcg(reinterpret_cast<const float4 *>(po + (int64_t)i * a.num_heads * 128 + 4));
+                        acc[0] = fmaf(w, pa.x, acc[0]);
+                        acc[1] = fmaf(w, pa.y, acc[1]);
+                        acc[2] = fmaf(w, pa.z, acc[2]);
+                        acc[3] = fmaf(w, pa.w, acc[3]);
+                        acc[4] = fmaf(w, pb.x, acc[4]);
+                        acc[5] = fmaf(w, pb.y, acc[5]);
+                        acc[6] = fmaf(w, pb.z, acc[6]);
+                        acc[7] = fmaf(w, pb.w, acc[7]);
+                    }
+                    const float inv = 1.f / wsum;
+                    uint4 pk;
+                    pk.x = Elem<T>::pack2(acc[0] * inv, acc[1] * inv);
+                    pk.y = Elem<T>::pack2(acc[2] * inv, acc[3] * inv);
+                    pk.z = Elem<T>::pack2(acc[4] * inv, acc[5] * inv);
+                    pk.w = Elem<T>::pack2(acc[6] * inv, acc[7] * inv);
+                    *reinterpret_cast<uint4 *>(static_cast<T *>(a.out) + ((int64_t)item.seq * a.num_heads + h) * 128 + d0) = pk;
+                }
+            }
+        }
         named_bar_sync(1, kConsumerWarps * 32);
     }
 }

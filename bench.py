@@ -219,7 +219,7 @@ def main():
     tens = capi.pa_tensors(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], out, d.get("k_descale"),
                            d.get("v_descale"))
     plan.set_profiling(True)
-    launches_per_step = 2 + (1 if info.num_combine_seqs > 0 else 0)
+    launches_per_step = 1 + info.kernels_per_launch      # ReshapeAndCache + attention (+ combine)
     torch.cuda.synchronize()
 
     def step():

@@ -80,6 +80,8 @@ typedef struct atb_b200_pa_plan_info {
     int32_t tile_tokens;     /* scheduling granule */
     uint64_t workspace_bytes;
     uint64_t plan_bytes;     /* bytes uploaded per launch */
+    int32_t kernels_per_launch; /* 1 = attention only (it merges split sequences itself), 2 = + combine */
+    int32_t reserved;
 } atb_b200_pa_plan_info;
 
 /*

@@ -5,9 +5,9 @@ and bans cudaMalloc, or a host thread with a latency bound.  For them the librar
 `atb_b200_pa_decode_static_scratch`, which keeps its workspace in a scratch array built into the
 library.  This test calls it twice in a row through the C ABI (the second call finds the first
 call's leftovers in the shared scratch) and compares with `atb_b200_pa_launch`, which uses a
-caller-provided workspace, on the same inputs; both plan the same split, so the outputs must agree
-to within the parity tolerance (they are in fact bit-identical).  It also checks that a call beyond
-the built-in capacity is refused.  The file name sorts last so that a run stopping at the first
+caller-provided workspace, on the same inputs; both plan the same split (only the order in which the
+split-KV partials are summed differs), so the outputs must agree to within the parity tolerance.  It
+also checks that a call beyond the built-in capacity is refused.  The file name sorts last so that a run stopping at the first
 failure has already run every other test.
 """
 import ctypes
@@ -50,7 +50,6 @@ def test_static_scratch_matches_workspace_entry_point(case):
         torch.cuda.synchronize()
         err = np.abs(out.float().cpu().numpy() - ref_f).max()
         assert err <= tol_for(case), (call, err)
-        assert torch.equal(out.view(torch.int16), ref.view(torch.int16)), call
     # a different, shorter workload right after: nothing stale may leak from the previous call
     h2 = dict(h, context_lens=np.maximum(h["context_lens"] // 3, 1).astype(np.int32))
     ref2 = capi.paged_attention(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], h2["context_lens"],
