@@ -226,7 +226,7 @@ def main():
         capi.reshape_and_cache(d["new_k"], d["new_v"], d["k_cache"], d["v_cache"], d["slot_mapping"])
         plan.launch(tens, ws.data_ptr(), ws.numel(), stream.cuda_stream)
         if world > 1:
-            dist.all_gather_into_tensor(gathered, out)
+            dist.all_gather_into_tensor(gathered.view(-1), out.view(-1))
 
     def barrier():
         if world > 1:
@@ -357,7 +357,7 @@ def run_e2e(args, case, wl, capi, d, lens, dev, world, gathered):
         need = pa.setup(pa_in, pa_out, ctx)          # re-plans from the host context_lens
         pa.execute(pa_in, pa_out, ws.data_ptr(), max(need, ws_bytes), ctx)
         if world > 1:
-            dist.all_gather_into_tensor(gathered, out)
+            dist.all_gather_into_tensor(gathered.view(-1), out.view(-1))
         out_host.copy_(out, non_blocking=True)
         stream.synchronize()                          # the caller consumes the result every step
 
