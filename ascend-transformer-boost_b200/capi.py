@@ -53,6 +53,12 @@ class PaPlanInfo(ctypes.Structure):
                 ("reserved", ctypes.c_int32)]
 
 
+class PaPeers(ctypes.Structure):
+    _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("total_heads", ctypes.c_int32),
+                ("head_offset", ctypes.c_int32), ("peer_out", ctypes.c_void_p * 8),
+                ("peer_flags", ctypes.c_void_p * 8), ("epoch", ctypes.c_uint32), ("reserved", ctypes.c_uint32)]
+
+
 class AtbTensor(ctypes.Structure):
     _fields_ = [("dtype", ctypes.c_int32), ("format", ctypes.c_int32), ("dims", ctypes.c_int64 * 8),
                 ("dim_num", ctypes.c_uint64), ("device_data", ctypes.c_void_p), ("host_data", ctypes.c_void_p),
@@ -89,7 +95,8 @@ EXPORTS = [
     "atb_b200_operation_create_paged_attention", "atb_b200_operation_create_reshape_and_cache",
     "atb_b200_operation_input_num", "atb_b200_operation_output_num", "atb_b200_operation_infer_shape",
     "atb_b200_operation_setup", "atb_b200_operation_execute", "atb_b200_operation_destroy", "atb_b200_version",
-    "atb_b200_pa_decode_static_scratch",
+    "atb_b200_pa_decode_static_scratch", "atb_b200_pa_launch_gathered", "atb_b200_peer_buffer_create",
+    "atb_b200_peer_buffer_open", "atb_b200_peer_buffer_close", "atb_b200_peer_buffer_destroy",
 ]
 
 _lib = None
@@ -128,6 +135,11 @@ def lib():
         L.atb_b200_operation_destroy.argtypes = [vp]
         L.atb_b200_version.restype = ctypes.c_char_p
         L.atb_b200_pa_decode_static_scratch.argtypes = [P(PaDesc), vp, P(PaTensors), vp]
+        L.atb_b200_pa_launch_gathered.argtypes = [vp, P(PaTensors), P(PaPeers), vp, u64, vp]
+        L.atb_b200_peer_buffer_create.argtypes = [u64, P(vp), ctypes.c_char_p]
+        L.atb_b200_peer_buffer_open.argtypes = [ctypes.c_char_p, P(vp)]
+        L.atb_b200_peer_buffer_close.argtypes = [vp]
+        L.atb_b200_peer_buffer_destroy.argtypes = [vp]
         _lib = L
     return _lib
 
@@ -192,6 +204,11 @@ class PaPlan:
     def launch(self, tensors, workspace_ptr, workspace_bytes, stream_ptr):
         _check(lib().atb_b200_pa_launch(self.handle, ctypes.byref(tensors), workspace_ptr, workspace_bytes,
                                         stream_ptr), "atb_b200_pa_launch")
+
+    def launch_gathered(self, tensors, peers, workspace_ptr, workspace_bytes, stream_ptr):
+        _check(lib().atb_b200_pa_launch_gathered(self.handle, ctypes.byref(tensors), ctypes.byref(peers),
+                                                 workspace_ptr, workspace_bytes, stream_ptr),
+               "atb_b200_pa_launch_gathered")
 
     def device_status(self, workspace_ptr, stream_ptr):
         st = ctypes.c_int32(-1)
@@ -280,6 +297,89 @@ def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping):
     _check(lib().atb_b200_reshape_and_cache(_ptr(key), _ptr(value), _ptr(key_cache), _ptr(value_cache),
                                             _ptr(slot_mapping), n, krow, vrow, nslots, torch_stream_ptr()),
            "atb_b200_reshape_and_cache")
+
+
+class PeerExchange:
+    """Gathered-output buffers and flag arrays shared by the ranks of a node over CUDA IPC.
+
+    Every rank creates `n_buffers` gathered output buffers of `out_bytes` and one flag array, hands
+    the IPC handles to its peers through torch.distributed (any host channel would do) and maps
+    theirs.  `peers(i)` builds the atb_b200_pa_peers argument of the i-th call.
+    """
+
+    def __init__(self, out_bytes, total_heads, head_offset, n_buffers=2):
+        import torch.distributed as dist
+        self.world, self.rank = dist.get_world_size(), dist.get_rank()
+        self.total_heads, self.head_offset = total_heads, head_offset
+        self.local, handles = [], []
+        for _ in range(n_buffers + 1):                       # last one = the flag array
+            ptr = ctypes.c_void_p()
+            h = ctypes.create_string_buffer(64)
+            nbytes = out_bytes if len(self.local) < n_buffers else 256
+            _check(lib().atb_b200_peer_buffer_create(nbytes, ctypes.byref(ptr), h), "atb_b200_peer_buffer_create")
+            self.local.append(ptr.value)
+            handles.append(bytes(h.raw))
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, handles)
+        self.mapped = []                                      # [buffer][rank] -> pointer valid in this process
+        self._opened = []
+        for b in range(n_buffers + 1):
+            row = []
+            for r in range(self.world):
+                if r == self.rank:
+                    row.append(self.local[b])
+                else:
+                    p = ctypes.c_void_p()
+                    _check(lib().atb_b200_peer_buffer_open(everyone[r][b], ctypes.byref(p)),
+                           "atb_b200_peer_buffer_open")
+                    row.append(p.value)
+                    self._opened.append(p.value)
+            self.mapped.append(row)
+        self.n_buffers = n_buffers
+        self.calls = 0
+        self._structs = []
+        for b in range(n_buffers):
+            p = PaPeers()
+            p.world, p.rank, p.total_heads, p.head_offset = self.world, self.rank, self.total_heads, self.head_offset
+            for r in range(self.world):
+                p.peer_out[r] = self.mapped[b][r]
+                p.peer_flags[r] = self.mapped[n_buffers][r]
+            self._structs.append(p)
+        dist.barrier()
+
+    def peers(self):
+        """Argument for the next call: alternates the gathered buffer, advances the epoch.
+        Returns (atb_b200_pa_peers, local pointer of the gathered buffer this call fills)."""
+        b = self.calls % self.n_buffers
+        self.calls += 1
+        p = self._structs[b]
+        p.epoch = self.calls
+        return p, self.local[b]
+
+    def local_tensor(self, ptr, shape, dtype):
+        """A torch view of one of this rank's gathered buffers."""
+        import torch
+        nbytes = 1
+        for s_ in shape:
+            nbytes *= s_
+        nbytes *= torch.empty((), dtype=dtype).element_size()
+
+        class _Raw:
+            pass
+        raw = _Raw()
+        raw.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+        return torch.as_tensor(raw, device="cuda").view(dtype).view(shape)
+
+    def close(self):
+        import torch.distributed as dist
+        dist.barrier()
+        for p in self._opened:
+            lib().atb_b200_peer_buffer_close(p)
+        self._opened = []
+        dist.barrier()
+        for p in self.local:
+            lib().atb_b200_peer_buffer_destroy(p)
+        self.local = []
 
 
 # ------------------------------------------------------------------ operator level

@@ -17,10 +17,14 @@ constexpr int kErrOutOfHostMemory = 27;
 
 struct atb_b200_pa_plan {
     HostPlan hp;
-    uint8_t *staging = nullptr; // pinned copy of the plan blob
+    // Pinned staging of the plan blob: a ring of slots, so the host can enqueue several steps ahead
+    // of the GPU; a slot is rewritten only after the copy that last read it has completed.
+    static constexpr int kStagingRing = 4;
+    uint8_t *staging = nullptr; // kStagingRing slots of staging_cap bytes
     size_t staging_cap = 0;
-    cudaEvent_t uploaded = nullptr;
-    bool upload_pending = false;
+    cudaEvent_t uploaded[kStagingRing] = {};
+    bool upload_pending[kStagingRing] = {};
+    uint64_t uploads = 0;
     // optional timing of the attention kernel: a ring of event pairs, one pair per launch
     static constexpr int kProfRing = 256;
     bool profile = false;
@@ -123,9 +127,11 @@ void atb_b200_pa_plan_destroy(atb_b200_pa_plan *plan)
     if (plan == nullptr) {
         return;
     }
-    if (plan->uploaded != nullptr) {
-        cudaEventSynchronize(plan->uploaded);
-        cudaEventDestroy(plan->uploaded);
+    for (int i = 0; i < atb_b200_pa_plan::kStagingRing; ++i) {
+        if (plan->uploaded[i] != nullptr) {
+            cudaEventSynchronize(plan->uploaded[i]);
+            cudaEventDestroy(plan->uploaded[i]);
+        }
     }
     for (int i = 0; i < atb_b200_pa_plan::kProfRing; ++i) {
         if (plan->ev0[i] != nullptr) {
@@ -173,11 +179,36 @@ int atb_b200_pa_plan_kernel_ms(atb_b200_pa_plan *plan, int32_t launches_back, fl
     return ATB_B200_OK;
 }
 
+static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, const atb_b200_pa_peers *peers,
+                          void *workspace, uint64_t workspace_bytes, void *stream_v);
+
 int atb_b200_pa_launch(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, void *workspace, uint64_t workspace_bytes,
                        void *stream_v)
 {
+    return pa_launch_impl(plan, t, nullptr, workspace, workspace_bytes, stream_v);
+}
+
+int atb_b200_pa_launch_gathered(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, const atb_b200_pa_peers *peers,
+                                void *workspace, uint64_t workspace_bytes, void *stream_v)
+{
+    if (plan == nullptr || peers == nullptr || peers->world < 1 || peers->world > 8 || peers->rank < 0 ||
+        peers->rank >= peers->world || plan->hp.kernel != ATB_B200_KERNEL_TMA_MMA ||
+        peers->head_offset < 0 || peers->head_offset + plan->hp.desc.num_heads > peers->total_heads) {
+        return kErrInvalidParam;
+    }
+    for (int r = 0; r < peers->world; ++r) {
+        if (peers->peer_out[r] == nullptr || peers->peer_flags[r] == nullptr) {
+            return kErrInvalidParam;
+        }
+    }
+    return pa_launch_impl(plan, t, peers, workspace, workspace_bytes, stream_v);
+}
+
+static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, const atb_b200_pa_peers *peers,
+                          void *workspace, uint64_t workspace_bytes, void *stream_v)
+{
     if (plan == nullptr || t == nullptr || t->q == nullptr || t->k_cache == nullptr || t->v_cache == nullptr ||
-        t->block_tables == nullptr || t->out == nullptr) {
+        t->block_tables == nullptr || (t->out == nullptr && peers == nullptr)) {
         return kErrInvalidParam;
     }
     HostPlan &h = plan->hp;
@@ -186,39 +217,46 @@ int atb_b200_pa_launch(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, voi
         return kErrInvalidParam;
     }
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    if (h.items.empty()) {
+    if (h.items.empty() && peers == nullptr) {
         return ATB_B200_OK; // every sequence is empty: outputs stay untouched
     }
-    // ---- upload the plan (pinned staging, one async copy)
+    // ---- upload the plan (pinned staging ring, one async copy)
+    constexpr int kRing = atb_b200_pa_plan::kStagingRing;
     if (plan->staging_cap < h.blob_bytes) {
-        if (plan->upload_pending) {
-            cudaEventSynchronize(plan->uploaded);
-            plan->upload_pending = false;
+        for (int i = 0; i < kRing; ++i) {
+            if (plan->upload_pending[i]) {
+                cudaEventSynchronize(plan->uploaded[i]);
+                plan->upload_pending[i] = false;
+            }
         }
         if (plan->staging != nullptr) {
             cudaFreeHost(plan->staging);
             plan->staging = nullptr;
         }
-        const size_t cap = (size_t)h.blob_bytes * 2;
-        if (cudaHostAlloc(reinterpret_cast<void **>(&plan->staging), cap, cudaHostAllocDefault) != cudaSuccess) {
+        const size_t cap = ((size_t)h.blob_bytes * 2 + 255) / 256 * 256;
+        if (cudaHostAlloc(reinterpret_cast<void **>(&plan->staging), cap * kRing, cudaHostAllocDefault) != cudaSuccess) {
             plan->staging_cap = 0;
             return kErrOutOfHostMemory;
         }
         plan->staging_cap = cap;
     }
-    if (plan->uploaded == nullptr && cudaEventCreateWithFlags(&plan->uploaded, cudaEventDisableTiming) != cudaSuccess) {
+    const int slot = (int)(plan->uploads % kRing);
+    if (plan->uploaded[slot] == nullptr &&
+        cudaEventCreateWithFlags(&plan->uploaded[slot], cudaEventDisableTiming) != cudaSuccess) {
         return kErrRtFail;
     }
-    if (plan->upload_pending) {
-        cudaEventSynchronize(plan->uploaded); // the previous copy out of the staging buffer must be done
+    if (plan->upload_pending[slot]) {
+        cudaEventSynchronize(plan->uploaded[slot]); // the copy that last read this slot must be done
     }
-    h.write_blob(plan->staging);
+    uint8_t *stage = plan->staging + (size_t)slot * plan->staging_cap;
+    h.write_blob(stage);
     uint8_t *ws = static_cast<uint8_t *>(workspace);
-    if (cudaMemcpyAsync(ws, plan->staging, h.blob_bytes, cudaMemcpyHostToDevice, stream) != cudaSuccess) {
+    if (cudaMemcpyAsync(ws, stage, h.blob_bytes, cudaMemcpyHostToDevice, stream) != cudaSuccess) {
         return kErrRtFail;
     }
-    cudaEventRecord(plan->uploaded, stream);
-    plan->upload_pending = true;
+    cudaEventRecord(plan->uploaded[slot], stream);
+    plan->upload_pending[slot] = true;
+    plan->uploads++;
 
     const atb_b200_pa_desc &d = h.desc;
     PaArgs a{};
@@ -239,6 +277,7 @@ int atb_b200_pa_launch(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, voi
     a.plan.part_o = reinterpret_cast<float *>(ws + h.off_part_o);
     a.plan.part_lse = reinterpret_cast<float *>(ws + h.off_lse);
     a.plan.status = reinterpret_cast<int32_t *>(ws + h.off_status);
+    a.plan.done_ctas = reinterpret_cast<int32_t *>(ws + h.off_done);
     a.plan.counters = (h.fused_combine && h.n_partials > 0) ? reinterpret_cast<int32_t *>(ws + h.off_counters) : nullptr;
     a.plan.n_cta_groups = h.n_cta_groups;
     a.plan.cols = h.cols;
@@ -254,6 +293,17 @@ int atb_b200_pa_launch(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, voi
     a.heads_per_cta = h.heads_per_cta;
     a.chunks_per_kvh = h.chunks_per_kvh;
     a.scale_log2 = d.qk_scale * 1.4426950408889634f;
+    if (peers != nullptr) {
+        a.n_out_peers = peers->world;
+        a.out_total_heads = peers->total_heads;
+        a.out_head_offset = peers->head_offset;
+        for (int r = 0; r < peers->world; ++r) {
+            a.out_peers[r] = peers->peer_out[r];
+            a.peer_flags[r] = peers->peer_flags[r];
+        }
+        a.xchg_rank = peers->rank;
+        a.xchg_epoch = peers->epoch;
+    }
 
     const int prof_i = (int)(plan->launches % atb_b200_pa_plan::kProfRing);
     if (plan->profile) {

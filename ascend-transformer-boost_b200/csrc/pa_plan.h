@@ -38,6 +38,8 @@ struct PaDevPlan {
     int32_t *status;              // device status word (0 = ok)
     int32_t *counters;            // [batch * cols] arrivals per (sequence, column), zero before the launch;
                                   // non-null = the last range to finish merges the partials itself
+    int32_t *done_ctas;           // CTAs that have finished (zero before the launch); used by the
+                                  // cross-GPU completion exchange
     int32_t n_cta_groups;
     int32_t cols;
 };
@@ -58,6 +60,14 @@ struct PaArgs {
     int32_t dk, dv, v_row_dim, block_size, max_blocks;
     int32_t heads_per_cta, chunks_per_kvh;     // generic kernel: head chunking inside a kv head
     float scale_log2;                          // qk_scale * log2(e)
+    // kv heads sharded over several GPUs: every rank's gathered output [tokens, out_total_heads, dv]
+    // (peer-mapped memory); 0 peers = write `out` only
+    void *out_peers[8];
+    int32_t n_out_peers, out_total_heads, out_head_offset;
+    // completion exchange: flag array (8 x uint32) of every rank, this rank, the step number
+    uint32_t *peer_flags[8];
+    int32_t xchg_rank;
+    uint32_t xchg_epoch;
 };
 
 enum PaDeviceStatus : int32_t { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusBadBlockId = 2 };

@@ -179,6 +179,7 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
     p->off_combine = off;
     off = align_up(off + p->combine_seqs.size() * sizeof(int32_t), 16);
     p->off_status = off; // zeroed by every upload
+    p->off_done = off + 4;
     off += 16;
     p->fused_combine = kernel == ATB_B200_KERNEL_TMA_MMA;
     p->off_counters = off;

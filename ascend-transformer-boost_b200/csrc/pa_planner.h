@@ -27,6 +27,7 @@ struct HostPlan {
 
     // Byte offsets inside the workspace (all 256-byte aligned).
     uint64_t off_group_begin = 0, off_items = 0, off_part_base = 0, off_nparts = 0, off_combine = 0;
+    uint64_t off_done = 0;        // finished-CTA counter (zeroed by every upload)
     uint64_t off_counters = 0;    // arrival counters of the in-kernel merge (zeroed by every upload)
     bool fused_combine = false;   // the attention kernel merges split sequences itself
     uint64_t blob_bytes = 0;      // uploaded per launch

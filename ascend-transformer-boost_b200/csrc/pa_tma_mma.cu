@@ -20,6 +20,7 @@
 #include <mutex>
 #include "common.cuh"
 #include "kernels.h"
+#include "pa_exchange.cuh"
 
 namespace atb_b200 {
 namespace {
@@ -33,6 +34,22 @@ constexpr int kStageBytes = 4 * kHalfBytes;         // K lo, K hi, V lo, V hi
 constexpr int kXbufFloats = 32 * 32;                // one warp's O fragments
 constexpr int kFinalStride = 132;                   // padded [head][dim] row (floats)
 constexpr int kSmemBytes = kStages * kStageBytes + (kXbufFloats + 8 * kFinalStride + 64) * 4 + 2 * kStages * 8 + 1024;
+
+// Writes 8 output elements of (sequence, local head h) to the output tensor - or, when the heads are
+// sharded over several GPUs, into the gathered [tokens, all heads, 128] buffer of every rank.
+template <typename T>
+__device__ __forceinline__ void store_out_row(const PaArgs &a, int seq, int h, int d0, const uint4 &pk)
+{
+    if (a.n_out_peers == 0) {
+        *reinterpret_cast<uint4 *>(static_cast<T *>(a.out) + ((int64_t)seq * a.num_heads + h) * 128 + d0) = pk;
+    } else {
+        const int64_t off = ((int64_t)seq * a.out_total_heads + a.out_head_offset + h) * 128 + d0;
+#pragma unroll 1
+        for (int r = 0; r < a.n_out_peers; ++r) {
+            *reinterpret_cast<uint4 *>(static_cast<T *>(a.out_peers[r]) + off) = pk;
+        }
+    }
+}
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 2)
@@ -340,7 +357,7 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     pk.y = Elem<T>::pack2(va.z, va.w);
                     pk.z = Elem<T>::pack2(vb.x, vb.y);
                     pk.w = Elem<T>::pack2(vb.z, vb.w);
-                    *reinterpret_cast<uint4 *>(static_cast<T *>(a.out) + ((int64_t)item.seq * a.num_heads + h) * 128 + d0) = pk;
+                    store_out_row<T>(a, item.seq, h, d0, pk);
                 } else {
                     float *dst = a.plan.part_o + ((int64_t)item.slot * a.num_heads + h) * 128 + d0;
                     *reinterpret_cast<float4 *>(dst) = va;
@@ -407,11 +424,20 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     pk.y = Elem<T>::pack2(acc[2] * inv, acc[3] * inv);
                     pk.z = Elem<T>::pack2(acc[4] * inv, acc[5] * inv);
                     pk.w = Elem<T>::pack2(acc[6] * inv, acc[7] * inv);
-                    *reinterpret_cast<uint4 *>(static_cast<T *>(a.out) + ((int64_t)item.seq * a.num_heads + h) * 128 + d0) = pk;
+                    store_out_row<T>(a, item.seq, h, d0, pk);
                 }
             }
         }
         named_bar_sync(1, kConsumerWarps * 32);
+    }
+    if (a.n_out_peers > 0) {
+        // heads sharded over several GPUs: make this CTA's peer stores visible, then let the last CTA
+        // of the grid exchange completion flags with the other ranks
+        __threadfence_system();
+        named_bar_sync(1, kConsumerWarps * 32);
+        if (warp == 0) {
+            exchange_tail(a, lane);
+        }
     }
 }
 

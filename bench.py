@@ -180,6 +180,8 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--config", type=int, default=1, help="index into the benchmark configurations (default 1)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
+                    help="N>1: attention stores into every rank's gathered buffer (p2p) or a separate NCCL all-gather")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -220,13 +222,39 @@ def main():
                            d.get("v_descale"))
     plan.set_profiling(True)
     launches_per_step = 1 + info.kernels_per_launch      # ReshapeAndCache + attention (+ combine)
+    p2p = world > 1 and args.gather == "p2p" and info.kernel == capi.KERNEL_TMA_MMA
+    exchange = None
+    if p2p:
+        exchange = capi.PeerExchange(B * case.heads * Dv * out.element_size(), case.heads, rank * H_local)
     torch.cuda.synchronize()
 
+    # The timed loop calls the C ABI with pre-built arguments: at N = 8 a step lasts tens of
+    # microseconds and per-call Python marshalling would otherwise bound the measurement.
+    import ctypes
+    L = capi.lib()
+    vp = ctypes.c_void_p
+    rac_args = (vp(d["new_k"].data_ptr()), vp(d["new_v"].data_ptr()) if d["new_v"] is not None else None,
+                vp(d["k_cache"].data_ptr()), vp(d["v_cache"].data_ptr()) if d["v_cache"] is not None else None,
+                vp(d["slot_mapping"].data_ptr()), B,
+                d["new_k"][0].numel() * d["new_k"].element_size(),
+                d["new_v"][0].numel() * d["new_v"].element_size() if d["new_v"] is not None else 0,
+                d["k_cache"].shape[0] * d["k_cache"].shape[1], vp(stream.cuda_stream))
+    tens_ref, ws_ptr, ws_bytes, stream_ptr = ctypes.byref(tens), vp(ws.data_ptr()), ws.numel(), vp(stream.cuda_stream)
+    plan_handle = plan.handle
+    gathered_flat = gathered.view(-1) if gathered is not None else None
+    out_flat = out.view(-1)
+
     def step():
-        capi.reshape_and_cache(d["new_k"], d["new_v"], d["k_cache"], d["v_cache"], d["slot_mapping"])
-        plan.launch(tens, ws.data_ptr(), ws.numel(), stream.cuda_stream)
-        if world > 1:
-            dist.all_gather_into_tensor(gathered.view(-1), out.view(-1))
+        rc = L.atb_b200_reshape_and_cache(*rac_args)
+        if p2p:
+            peers, _ = exchange.peers()
+            rc |= L.atb_b200_pa_launch_gathered(plan_handle, tens_ref, ctypes.byref(peers), ws_ptr, ws_bytes, stream_ptr)
+        else:
+            rc |= L.atb_b200_pa_launch(plan_handle, tens_ref, ws_ptr, ws_bytes, stream_ptr)
+            if world > 1:
+                dist.all_gather_into_tensor(gathered_flat, out_flat)
+        if rc != 0:
+            raise RuntimeError(f"C ABI call failed with {rc}")
 
     def barrier():
         if world > 1:
@@ -278,7 +306,9 @@ def main():
                 "config": {"workload": case.name, "batch": case.batch, "q_heads": case.heads,
                            "kv_heads": case.kv_heads, "head_dim": case.dk, "block_size": case.block_size,
                            "context_tokens": int(lens.sum()), "kv_bytes_per_step": kv_bytes_global,
-                           "parallelism": f"kv-head shard x{world}" if world > 1 else "single GPU",
+                           "parallelism": (f"kv-head shard x{world}, outputs gathered by " +
+                                           ("peer stores from the attention kernel" if p2p else "NCCL all-gather"))
+                           if world > 1 else "single GPU",
                            "l2": "KV cache per GPU (%.0f MB) is larger than the 126 MB L2" %
                                  (wl.kv_bytes(shard, lens) / 1e6),
                            "kernel": {1: "generic", 2: "tma_mma", 3: "mla_tc5"}.get(info.kernel, "?"),
@@ -302,6 +332,8 @@ def main():
                          wl.to_f32(ref_out, case.q_dtype)).max()
             line["max_abs_err_vs_oracle"] = float(err)
         print(json.dumps(line))
+    if exchange is not None:
+        exchange.close()
     if world > 1:
         dist.destroy_process_group()
 

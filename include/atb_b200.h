@@ -110,6 +110,45 @@ int atb_b200_pa_launch(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *tensor
                        uint64_t workspace_bytes, void *stream);
 
 /*
+ * KV heads sharded over the GPUs of one node (one process per GPU): every rank computes the query
+ * heads of its kv heads and the outputs are exchanged.  Instead of a separate all-gather
+ * (AllGatherOperation after attention in a reference model graph,
+ * src/ops/ops_infer/all_gather/all_gather_hccl_runner.cpp:47), the attention kernel stores its
+ * output rows into the gathered buffer [batch, total_heads, head_dim_v] of EVERY rank through
+ * peer-mapped memory (plain stores over NVLink), and a one-CTA kernel then publishes / awaits a
+ * per-rank completion flag.  When the call's work has completed on the stream, the local gathered
+ * buffer holds all ranks' heads.
+ *
+ * peer_out[r] / peer_flags[r]: rank r's gathered buffer and flag array (8 x uint32, zero before the
+ * first call) as mapped in THIS process (atb_b200_peer_buffer_*).  `epoch` starts at 1 and grows by
+ * one per call on every rank.  A rank may run one step ahead of a slow peer, so alternate between
+ * two gathered buffers from call to call.  The wait is bounded; a peer that never arrives sets the
+ * status word (atb_b200_pa_plan_device_status) instead of hanging the GPU.  Only the TMA kernels
+ * (head_dim 128) support this path.
+ */
+typedef struct atb_b200_pa_peers {
+    int32_t world;        /* ranks, 1..8 */
+    int32_t rank;         /* this rank */
+    int32_t total_heads;  /* query heads of the whole model */
+    int32_t head_offset;  /* first global head computed by this rank */
+    void *peer_out[8];
+    uint32_t *peer_flags[8];
+    uint32_t epoch;
+    uint32_t reserved;
+} atb_b200_pa_peers;
+
+int atb_b200_pa_launch_gathered(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *tensors,
+                                const atb_b200_pa_peers *peers, void *workspace, uint64_t workspace_bytes,
+                                void *stream);
+
+/* Device buffers other processes of the node can map (CUDA IPC): create returns the local pointer
+ * and a 64-byte handle to hand to the peers (over any host channel); open maps a peer's buffer. */
+int atb_b200_peer_buffer_create(uint64_t bytes, void **local_ptr, uint8_t handle[64]);
+int atb_b200_peer_buffer_open(const uint8_t handle[64], void **peer_ptr);
+int atb_b200_peer_buffer_close(void *peer_ptr);
+int atb_b200_peer_buffer_destroy(void *local_ptr);
+
+/*
  * ReshapeAndCache: cache[slot_mapping[i]] = key[i] (and value) for slot >= 0; byte-exact copy.
  * row bytes = heads * head_dim * sizeof(elem).  value/value_cache NULL = K-only variant.
  * Replaces the reshape_and_cache / reshape_and_cache_siso kernels
