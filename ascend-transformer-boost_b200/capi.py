@@ -97,6 +97,7 @@ EXPORTS = [
     "atb_b200_operation_setup", "atb_b200_operation_execute", "atb_b200_operation_destroy", "atb_b200_version",
     "atb_b200_pa_decode_static_scratch", "atb_b200_pa_launch_gathered", "atb_b200_peer_buffer_create",
     "atb_b200_peer_buffer_open", "atb_b200_peer_buffer_close", "atb_b200_peer_buffer_destroy",
+    "atb_b200_pa_plan_set_trace",
 ]
 
 _lib = None
@@ -140,6 +141,7 @@ def lib():
         L.atb_b200_peer_buffer_open.argtypes = [ctypes.c_char_p, P(vp)]
         L.atb_b200_peer_buffer_close.argtypes = [vp]
         L.atb_b200_peer_buffer_destroy.argtypes = [vp]
+        L.atb_b200_pa_plan_set_trace.argtypes = [vp, vp, u32]
         _lib = L
     return _lib
 
@@ -215,6 +217,9 @@ class PaPlan:
         _check(lib().atb_b200_pa_plan_device_status(self.handle, workspace_ptr, stream_ptr, ctypes.byref(st)),
                "atb_b200_pa_plan_device_status")
         return st.value
+
+    def set_trace(self, device_ptr, capacity):
+        _check(lib().atb_b200_pa_plan_set_trace(self.handle, device_ptr, capacity), "atb_b200_pa_plan_set_trace")
 
     def set_profiling(self, on=True):
         _check(lib().atb_b200_pa_plan_set_profiling(self.handle, 1 if on else 0), "atb_b200_pa_plan_set_profiling")

@@ -25,6 +25,8 @@ struct atb_b200_pa_plan {
     cudaEvent_t uploaded[kStagingRing] = {};
     bool upload_pending[kStagingRing] = {};
     uint64_t uploads = 0;
+    unsigned long long *trace = nullptr; // optional device event buffer (probe)
+    uint32_t trace_cap = 0;
     // optional timing of the attention kernel: a ring of event pairs, one pair per launch
     static constexpr int kProfRing = 256;
     bool profile = false;
@@ -146,6 +148,16 @@ void atb_b200_pa_plan_destroy(atb_b200_pa_plan *plan)
         cudaFreeHost(plan->status_host);
     }
     delete plan;
+}
+
+int atb_b200_pa_plan_set_trace(atb_b200_pa_plan *plan, void *device_events, uint32_t capacity)
+{
+    if (plan == nullptr || (device_events != nullptr && capacity < 2)) {
+        return kErrInvalidParam;
+    }
+    plan->trace = static_cast<unsigned long long *>(device_events);
+    plan->trace_cap = device_events != nullptr ? capacity : 0;
+    return ATB_B200_OK;
 }
 
 int atb_b200_pa_plan_set_profiling(atb_b200_pa_plan *plan, int enable)
@@ -293,6 +305,8 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
     a.heads_per_cta = h.heads_per_cta;
     a.chunks_per_kvh = h.chunks_per_kvh;
     a.scale_log2 = d.qk_scale * 1.4426950408889634f;
+    a.trace = plan->trace;
+    a.trace_cap = plan->trace_cap;
     if (peers != nullptr) {
         a.n_out_peers = peers->world;
         a.out_total_heads = peers->total_heads;

@@ -101,6 +101,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
                  : "memory");
     return ok != 0;
 }
+// Non-blocking probe (try_wait may suspend the thread for a while when the phase is not complete).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(smem_u32(bar)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
 // Bounded wait: gives up after ~2^22 polls (seconds) and returns false so the kernel can record
 // the failure in its status word and leave instead of hanging the GPU.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)

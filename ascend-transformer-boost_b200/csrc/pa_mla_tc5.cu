@@ -2,10 +2,13 @@
 // + 64 rope, V = the first 512 columns of the same row) on the 5th-generation tensor cores.
 //
 // One CTA per (CTA group, 64 query heads), one CTA per SM.  Warp roles:
-//   warp 4  - TMA producer: Q tile of the token range (64 heads x 576) once, then 64-token K tiles
-//             (9 boxes of 64 tokens x 64 elements, 128-byte swizzle) into a 2-stage ring;
+//   warp 4  - TMA producer: 64-token K tiles (9 boxes of 64 tokens x 64 elements, 128-byte swizzle)
+//             into a 3-stage shared-memory ring (3 x 72 KB: the whole shared memory);
 //   warp 5  - one elected thread issues tcgen05.mma (M = 64 heads):
-//               S[64 x 64 tokens]  = Q . K^T          36 MMAs, K-major A and B, accumulator in TMEM
+//               S[64 x 64 tokens]  = Q . K^T          36 MMAs, A = Q read from TENSOR MEMORY (the 64 x 576
+//                                                      query block is stored there once per token range,
+//                                                      which frees 72 KB of shared memory for the third
+//                                                      stage), B = K tile, accumulator in TMEM
 //               O[64 x 512]       += P . V            8 MMAs of N = 256; V is the same shared-memory
 //                                                      tile read MN-major, so the cache row crosses
 //                                                      the memory system once
@@ -14,8 +17,9 @@
 //             sum in the exp2 domain, P -> bf16/fp16 into shared memory for the P.V MMA; O stays in
 //             TMEM for the whole token range and is rescaled only when a row's maximum grows by more
 //             than 2^8 (the final division by the row sum absorbs the stale scale).
-// TMEM: an M = 64 accumulator occupies 16 of the 32 lanes of each warp's quadrant, so O (512 columns)
-// lives in the lower half-quadrants and the two S buffers in the upper ones.
+// TMEM: an M = 64 operand occupies 16 of the 32 lanes of each warp's quadrant, so O (512 columns)
+// lives in the lower half-quadrants; the upper ones hold the two S buffers (columns 0..127) and Q
+// (bf16/fp16 pairs, columns 128..415).
 //
 // Replaces MLAttentionDecoderAic / paged_multi_latent_attention_mask of the reference
 // (src/kernels/mixkernels/pagedattention/op_kernel/paged_MLAttention_combine_cache_mask_mix.cce:24-150,
@@ -37,10 +41,11 @@ constexpr int kDk = 576, kDv = 512;
 constexpr int kAtoms = kDk / 64;         // 9 boxes of 64 elements per row
 constexpr int kAtomBytes = 64 * 128;     // 64 rows x 128 B
 constexpr int kTileBytes = kAtoms * kAtomBytes; // 73728
-constexpr int kStages = 2;
+constexpr int kStages = 3;
 constexpr int kPBytes = 64 * 128;        // P: 64 heads x 64 tokens x 2 B
 constexpr int kNumBars = 16;
-constexpr int kSmemBytes = (1 + kStages) * kTileBytes + kPBytes + kNumBars * 8 + 64 + 1024;
+constexpr int kSmemBytes = kStages * kTileBytes + kPBytes + kNumBars * 8 + 64 + 1024;
+constexpr uint32_t kQCol = 128;          // first TMEM column of Q (upper half-quadrants)
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 512;
 
@@ -71,6 +76,15 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
                  "setp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
                  "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate ? 1u : 0u)
+                 : "memory");
+}
+// A operand from tensor memory
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, bool accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+                 "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate ? 1u : 0u)
                  : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
@@ -126,16 +140,15 @@ __host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t b_mn_ma
     return (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (b_mn_major << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
-enum Bar { kQFull = 0, kQEmpty, kKvFull0, kKvFull1, kKvEmpty0, kKvEmpty1, kSFull0, kSFull1, kSEmpty0, kSEmpty1, kPFull, kPvDone };
+enum Bar { kQFull = 0, kQEmpty, kKvFull0, kKvFull1, kKvFull2, kKvEmpty0, kKvEmpty1, kKvEmpty2, kSFull0, kSFull1, kSEmpty0, kSEmpty1, kPFull, kPvDone };
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
-pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap, const PaArgs a)
+pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const PaArgs a)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t *q_smem = base;
-    uint8_t *kv_smem = base + kTileBytes;
+    uint8_t *kv_smem = base;
     uint8_t *p_smem = kv_smem + kStages * kTileBytes;
     uint64_t *bars = reinterpret_cast<uint64_t *>(p_smem + kPBytes);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
@@ -150,11 +163,13 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
 
     if (threadIdx.x == 0) {
-        mbar_init(&bars[kQFull], 1);
-        mbar_init(&bars[kQEmpty], 1);
-        for (int s = 0; s < 2; ++s) {
+        mbar_init(&bars[kQFull], 4);   // the four softmax warps have stored Q into TMEM
+        mbar_init(&bars[kQEmpty], 1);  // the last Q.K^T of the range has completed
+        for (int s = 0; s < kStages; ++s) {
             mbar_init(&bars[kKvFull0 + s], 1);
             mbar_init(&bars[kKvEmpty0 + s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
             mbar_init(&bars[kSFull0 + s], 1);
             mbar_init(&bars[kSEmpty0 + s], 4);
         }
@@ -196,25 +211,12 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     if (warp == 4) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            tma_prefetch_desc(&qmap);
             tma_prefetch_desc(&kmap);
         }
         uint32_t g = 0; // global stage counter
         bool alive = true;
         for (int it = item_begin, i = 0; it < item_end && alive; ++it, ++i) {
             const PaItem item = a.plan.items[it];
-            if (lane == 0) {
-                if (!wait(kQEmpty, (i & 1) ^ 1u)) {
-                    alive = false;
-                } else {
-                    mbar_expect_tx(&bars[kQFull], kTileBytes);
-                    for (int at = 0; at < kAtoms; ++at) {
-                        // rows past num_heads are outside the tensor: filled with zeros
-                        tma_load_3d(q_smem + at * kAtomBytes, &qmap, &bars[kQFull], at * 64, head0, item.seq);
-                    }
-                }
-            }
-            alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
             const int n_st = (item.tok_end - item.tok_begin + kTok - 1) / kTok;
             const int32_t *bt = a.block_tables + (int64_t)item.seq * a.max_blocks;
             for (int st0 = 0; st0 < n_st && alive; st0 += 32) {
@@ -226,12 +228,13 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 for (int j = 0; j < cnt && alive; ++j, ++g) {
                     const int b = __shfl_sync(0xffffffffu, blk, j);
                     if (lane == 0) {
-                        const int s = g & 1;
-                        if (!wait(kKvEmpty0 + s, ((g >> 1) & 1) ^ 1u)) {
+                        const int s = g % kStages;
+                        if (!wait(kKvEmpty0 + s, ((g / kStages) & 1) ^ 1u)) {
                             alive = false;
                         } else {
                             const int tok_in_blk = (item.tok_begin + (st0 + j) * kTok) % a.block_size;
                             uint8_t *dst = kv_smem + s * kTileBytes;
+                            probe(a, 1, g);
                             mbar_expect_tx(&bars[kKvFull0 + s], kTileBytes);
                             for (int at = 0; at < kAtoms; ++at) {
                                 tma_load_4d(dst + at * kAtomBytes, &kmap, &bars[kKvFull0 + s], at * 64, 0, tok_in_blk, b);
@@ -247,12 +250,13 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         if (lane == 0) {
             constexpr uint32_t idesc_qk = instr_desc(kFmt, 0, kTok, kHeadsPerCta);
             constexpr uint32_t idesc_pv = instr_desc(kFmt, 1, 256, kHeadsPerCta);
-            const uint32_t q_addr = smem_u32(q_smem), kv_addr = smem_u32(kv_smem), p_addr = smem_u32(p_smem);
+            const uint32_t kv_addr = smem_u32(kv_smem), p_addr = smem_u32(p_smem);
+            const uint32_t tmem_q = tmem_base + (16u << 16) + kQCol;
             uint32_t g = 0;
             bool alive = true;
             // Issue order is decided by what is ready, P.V first: a P.V releases its K tile to the
             // producer, so it must never queue behind a Q.K^T that is still waiting for its tile.
-            auto ready = [&](int bar, uint32_t parity) { return mbar_try_wait(&bars[bar], parity); };
+            auto ready = [&](int bar, uint32_t parity) { return mbar_test_wait(&bars[bar], parity); };
             for (int it = item_begin, i = 0; it < item_end && alive; ++it, ++i) {
                 const PaItem item = a.plan.items[it];
                 const int n_st = (item.tok_end - item.tok_begin + kTok - 1) / kTok;
@@ -264,8 +268,9 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 while (next_pv < n_st) {
                     const uint32_t gp = g + next_pv, gq = g + next_qk;
                     if (next_pv < next_qk && ready(kPFull, gp & 1)) {
+                        probe(a, 3, gp);
                         tc_fence_after();
-                        const int s = gp & 1;
+                        const int s = gp % kStages;
                         const uint32_t vb = kv_addr + s * kTileBytes;
 #pragma unroll
                         for (int half = 0; half < 2; ++half) {
@@ -281,18 +286,20 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                         tc_commit(&bars[kPvDone]);
                         ++next_pv;
                         idle = 0;
-                    } else if (next_qk < n_st && next_qk < next_pv + 2 && ready(kKvFull0 + (gq & 1), (gq >> 1) & 1) &&
+                    } else if (next_qk < n_st && next_qk < next_pv + 2 &&
+                               ready(kKvFull0 + (gq % kStages), (gq / kStages) & 1) &&
                                ready(kSEmpty0 + (gq & 1), ((gq >> 1) & 1) ^ 1u)) {
+                        probe(a, 2, gq);
                         tc_fence_after();
-                        const int s = gq & 1;
-                        const uint32_t kb = kv_addr + s * kTileBytes;
+                        const int s = gq & 1;                                   // S buffer
+                        const uint32_t kb = kv_addr + (gq % kStages) * kTileBytes; // K tile slot
 #pragma unroll 1
                         for (int at = 0; at < kAtoms; ++at) {
 #pragma unroll
                             for (int ks = 0; ks < 4; ++ks) {
-                                const uint64_t da = smem_desc(q_addr + at * kAtomBytes + ks * 32, 16, 1024);
+                                // 16 elements of Q = 8 TMEM columns (two 16-bit values per column)
                                 const uint64_t db = smem_desc(kb + at * kAtomBytes + ks * 32, 16, 1024);
-                                tc_mma(tmem_s + s * 64, da, db, idesc_qk, (at | ks) != 0);
+                                tc_mma_ts(tmem_s + s * 64, tmem_q + at * 32 + ks * 8, db, idesc_qk, (at | ks) != 0);
                             }
                         }
                         tc_commit(&bars[kSFull0 + s]);
@@ -302,9 +309,7 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                         ++next_qk;
                         idle = 0;
                     } else {
-                        if (++idle > 64) {
-                            __nanosleep(32);
-                        }
+                        ++idle;
                         if (idle > (1u << 22) || *abort_flag) {
                             *abort_flag = 1;
                             atomicExch(a.plan.status, kStatusWaitTimeout);
@@ -323,9 +328,41 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         uint32_t g = 0;
         bool alive = true;
-        for (int it = item_begin; it < item_end && alive; ++it) {
+        for (int it = item_begin, i = 0; it < item_end && alive; ++it, ++i) {
             const PaItem item = a.plan.items[it];
             const int n_st = (item.tok_end - item.tok_begin + kTok - 1) / kTok;
+            // ---- Q block of this range -> TMEM (upper half-quadrants, two 16-bit values per column).
+            // The previous range's Q.K^T MMAs must be done with the old Q; O is dead here (its first
+            // P.V overwrites it), so the lower lanes of these columns may be written with anything.
+            if (!wait(kQEmpty, (i & 1) ^ 1u)) {
+                alive = false;
+                break;
+            }
+            tc_fence_after();
+            {
+                const bool has_row = s_lane && row < nh;
+                const uint4 *qrow = reinterpret_cast<const uint4 *>(static_cast<const T *>(a.q) +
+                                                                    ((int64_t)item.seq * a.num_heads + head0 + (has_row ? row : 0)) * kDk);
+#pragma unroll 1
+                for (int c = 0; c < kAtoms; ++c) { // 64 elements = 128 B = 32 columns per step
+                    uint32_t t[32];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint4 v = has_row ? __ldg(qrow + c * 8 + j) : make_uint4(0, 0, 0, 0);
+                        t[4 * j] = v.x;
+                        t[4 * j + 1] = v.y;
+                        t[4 * j + 2] = v.z;
+                        t[4 * j + 3] = v.w;
+                    }
+                    tmem_st32(tmem_base + lane_base + kQCol + c * 32, t);
+                }
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&bars[kQFull]);
+                }
+            }
             float m_used = -INFINITY, l = 0.f;
             for (int st = 0; st < n_st && alive; ++st, ++g) {
                 const int sb = g & 1;
@@ -333,6 +370,9 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 if (!wait(kSFull0 + sb, (g >> 1) & 1)) {
                     alive = false;
                     break;
+                }
+                if (threadIdx.x == 16) {
+                    probe(a, 4, g);
                 }
                 tc_fence_after();
                 uint32_t r0[32], r1[32];
@@ -378,10 +418,16 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                     pk[16 + j] = Elem<T>::pack2(p2, p3);
                 }
                 l += lsum;
+                if (threadIdx.x == 16) {
+                    probe(a, 5, g);
+                }
                 // P(g) overwrites P(g-1) and a rescale touches O: both need P.V(g-1) to have finished
                 if (g > 0 && !wait(kPvDone, (g - 1) & 1)) {
                     alive = false;
                     break;
+                }
+                if (threadIdx.x == 16) {
+                    probe(a, 6, g);
                 }
                 if (rescale_any) {
                     // O rows live in lanes 0..15; the multiplier comes from the row's S lane.  The S lanes
@@ -418,7 +464,7 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 }
                 if (valid < kTok) {
                     // rows of V past the end of the range may hold anything: clear them (0 * NaN != 0)
-                    uint8_t *vt = kv_smem + sb * kTileBytes;
+                    uint8_t *vt = kv_smem + (g % kStages) * kTileBytes;
                     const int rows = kTok - valid;
                     for (int idx = threadIdx.x; idx < rows * 8 * 8; idx += 128) {
                         const int at = idx / (rows * 8), rem = idx - at * (rows * 8);
@@ -431,6 +477,9 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(&bars[kPFull]);
+                }
+                if (threadIdx.x == 16) {
+                    probe(a, 7, g);
                 }
             }
             if (!alive) {
@@ -511,7 +560,7 @@ EncodeFn get_encode_fn()
     return fn;
 }
 
-template <typename T> cudaError_t launch_typed(const PaArgs &args, const CUtensorMap &qm, const CUtensorMap &km, cudaStream_t s)
+template <typename T> cudaError_t launch_typed(const PaArgs &args, const CUtensorMap &km, cudaStream_t s)
 {
     auto kern = pa_mla_tc5_kernel<T>;
     static bool configured[64] = {};
@@ -527,7 +576,7 @@ template <typename T> cudaError_t launch_typed(const PaArgs &args, const CUtenso
         }
     }
     const int grid = args.plan.n_cta_groups * args.plan.cols;
-    kern<<<grid, kThreads, kSmemBytes, s>>>(qm, km, args);
+    kern<<<grid, kThreads, kSmemBytes, s>>>(km, args);
     return cudaGetLastError();
 }
 
@@ -546,19 +595,7 @@ cudaError_t launch_pa_mla_tc5(const PaArgs &args, int q_dtype, int num_blocks, c
         return cudaErrorInvalidValue;
     }
     const CUtensorMapDataType dt = q_dtype == kBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUtensorMap qm, km;
-    {
-        // query [batch][num_heads][576]; box = 64 elements x 64 heads of one sequence
-        cuuint64_t dims[3] = {(cuuint64_t)kDk, (cuuint64_t)args.num_heads, (cuuint64_t)args.batch};
-        cuuint64_t strides[2] = {(cuuint64_t)kDk * 2, (cuuint64_t)args.num_heads * kDk * 2};
-        cuuint32_t box[3] = {64, kHeadsPerCta, 1};
-        cuuint32_t estr[3] = {1, 1, 1};
-        if (fn(&qm, dt, 3, const_cast<void *>(args.q), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
-            return cudaErrorInvalidValue;
-        }
-    }
+    CUtensorMap km;
     {
         // cache [num_blocks][block_size][1][576]; box = 64 elements x 64 tokens of one block
         cuuint64_t dims[4] = {(cuuint64_t)kDk, 1, (cuuint64_t)args.block_size, (cuuint64_t)num_blocks};
@@ -571,7 +608,7 @@ cudaError_t launch_pa_mla_tc5(const PaArgs &args, int q_dtype, int num_blocks, c
             return cudaErrorInvalidValue;
         }
     }
-    return q_dtype == kFp16 ? launch_typed<__half>(args, qm, km, stream) : launch_typed<__nv_bfloat16>(args, qm, km, stream);
+    return q_dtype == kFp16 ? launch_typed<__half>(args, km, stream) : launch_typed<__nv_bfloat16>(args, km, stream);
 }
 
 } // namespace atb_b200

@@ -68,7 +68,23 @@ struct PaArgs {
     uint32_t *peer_flags[8];
     int32_t xchg_rank;
     uint32_t xchg_epoch;
+    // optional event probe (CTA 0 only): trace[0] = number of events, then (tag << 56 | index << 40 | cycles)
+    unsigned long long *trace;
+    uint32_t trace_cap;
 };
+
+__device__ __forceinline__ void probe(const PaArgs &a, unsigned tag, unsigned idx)
+{
+#ifdef __CUDA_ARCH__
+    if (a.trace != nullptr && blockIdx.x == 0) {
+        const unsigned long long n = atomicAdd(a.trace, 1ull);
+        if (n + 1 < a.trace_cap) {
+            a.trace[n + 1] = ((unsigned long long)tag << 56) | ((unsigned long long)(idx & 0xffffu) << 40) |
+                             ((unsigned long long)clock64() & 0xffffffffffull);
+        }
+    }
+#endif
+}
 
 enum PaDeviceStatus : int32_t { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusBadBlockId = 2 };
 

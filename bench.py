@@ -340,20 +340,34 @@ def main():
 
 def run_e2e(args, case, wl, capi, d, lens, dev, world, gathered):
     """The same step through atb::Operation Setup/Execute with HOST buffers: every step copies the
-    query, the new K/V tokens, slot_mapping, block_tables and context_lens from pinned host memory,
-    re-plans from the host context_lens, runs ReshapeAndCache + PagedAttention and reads the output
-    back to pinned host memory.  The KV cache itself is the path's resident state and stays in HBM."""
+    query, the new K/V tokens, slot_mapping, block_tables and context_lens from pinned host memory
+    (packed in one staging area, one H2D copy), re-plans from the host context_lens, runs
+    ReshapeAndCache + PagedAttention and reads the output back to pinned host memory, then waits for
+    it.  The KV cache itself is the path's resident state and stays in HBM.  The operator calls use
+    pre-built tensor records (a C++ caller builds its VariantPack once, too)."""
+    import ctypes
     import torch
     import torch.distributed as dist
     T = capi.atb_tensor
     stream = torch.cuda.Stream()
-    host = {k: d[k].cpu().pin_memory() for k in ("q", "new_k", "block_tables", "slot_mapping", "context_lens")}
-    if not case.mla:
-        host["new_v"] = d["new_v"].cpu().pin_memory()
-    devb = {k: torch.empty_like(d[k]) for k in host}
+    names = ["q", "new_k", "block_tables", "slot_mapping", "context_lens"] + ([] if case.mla else ["new_v"])
+    # one pinned staging area and one device area holding all per-step inputs back to back
+    offs, total = {}, 0
+    for k in names:
+        offs[k] = total
+        total += (d[k].numel() * d[k].element_size() + 255) // 256 * 256
+    host_pack = torch.empty(total, dtype=torch.uint8).pin_memory()
+    dev_pack = torch.empty(total, dtype=torch.uint8, device=dev)
+    devb, h2d = {}, 0
+    for k in names:
+        n = d[k].numel() * d[k].element_size()
+        host_pack[offs[k]:offs[k] + n] = d[k].cpu().contiguous().view(torch.uint8).view(-1)
+        devb[k] = dev_pack[offs[k]:offs[k] + n].view(d[k].dtype).view(d[k].shape)
+        h2d += n
+    lens_off = offs["context_lens"]
+    lens_host = host_pack[lens_off:lens_off + 4 * case.batch].view(torch.int32).numpy()
     out = torch.zeros((case.batch, case.heads, case.dv), dtype=d["q"].dtype, device=dev)
     out_host = torch.empty_like(out, device="cpu").pin_memory()
-    lens_host = host["context_lens"].numpy()
     ctx = capi.Context(stream.cuda_stream)
     rac_param = capi.ReshapeAndCacheParam()
     rac_param.kvCacheCfg = 1 if case.mla else 0
@@ -378,18 +392,26 @@ def run_e2e(args, case, wl, capi, d, lens, dev, world, gathered):
     pa_out = [T(out)]
     ws_bytes = pa.setup(pa_in, pa_out, ctx)
     ws = torch.empty(max(ws_bytes * 2, 256), dtype=torch.uint8, device=dev)
-    h2d = sum(t.numel() * t.element_size() for t in host.values())
     d2h = out.numel() * out.element_size()
 
+    L = capi.lib()
+    arr = capi.Operation._arr
+    rac_i, rac_o, pa_i, pa_o = arr(rac_in), arr(rac_out), arr(pa_in), arr(pa_out)
+    n_ri, n_ro, n_pi, n_po = len(rac_in), len(rac_out), len(pa_in), len(pa_out)
+    need = ctypes.c_uint64(0)
+    ws_ptr, ws_len = ctypes.c_void_p(ws.data_ptr()), ws.numel()
+    gathered_flat = gathered.view(-1) if gathered is not None else None
+
     def step():
-        for k in host:
-            devb[k].copy_(host[k], non_blocking=True)
-        rac.setup(rac_in, rac_out, ctx)
-        rac.execute(rac_in, rac_out, None, 0, ctx)
-        need = pa.setup(pa_in, pa_out, ctx)          # re-plans from the host context_lens
-        pa.execute(pa_in, pa_out, ws.data_ptr(), max(need, ws_bytes), ctx)
+        dev_pack.copy_(host_pack, non_blocking=True)
+        rc = L.atb_b200_operation_setup(rac.handle, rac_i, n_ri, rac_o, n_ro, ctypes.byref(need), ctx.handle)
+        rc |= L.atb_b200_operation_execute(rac.handle, rac_i, n_ri, rac_o, n_ro, None, 0, ctx.handle)
+        rc |= L.atb_b200_operation_setup(pa.handle, pa_i, n_pi, pa_o, n_po, ctypes.byref(need), ctx.handle)
+        rc |= L.atb_b200_operation_execute(pa.handle, pa_i, n_pi, pa_o, n_po, ws_ptr, ws_len, ctx.handle)
+        if rc != 0 or need.value > ws_len:
+            raise RuntimeError(f"operator call failed ({rc})")
         if world > 1:
-            dist.all_gather_into_tensor(gathered.view(-1), out.view(-1))
+            dist.all_gather_into_tensor(gathered_flat, out.view(-1))
         out_host.copy_(out, non_blocking=True)
         stream.synchronize()                          # the caller consumes the result every step
 
