@@ -11,8 +11,9 @@ namespace {
 
 constexpr int kMaxPartsShared = 512;
 
+// One CTA per (split sequence, head); thread t owns output elements 4t..4t+3 (dv is a multiple of 4).
 template <typename TQ>
-__global__ void __launch_bounds__(128) pa_combine_kernel(const PaArgs a)
+__global__ void __launch_bounds__(160) pa_combine_kernel(const PaArgs a)
 {
     __shared__ float w[kMaxPartsShared];
     const int seq = a.plan.combine_seqs[blockIdx.x];
@@ -39,13 +40,20 @@ __global__ void __launch_bounds__(128) pa_combine_kernel(const PaArgs a)
     TQ *out = static_cast<TQ *>(a.out) + ((int64_t)seq * a.num_heads + h) * a.dv;
     const float *po = a.plan.part_o + ((int64_t)base * a.num_heads + h) * a.dv;
     const int64_t stride = (int64_t)a.num_heads * a.dv;
-    for (int d = threadIdx.x; d < a.dv; d += blockDim.x) {
-        float acc = 0.f;
+    for (int d = threadIdx.x * 4; d < a.dv; d += blockDim.x * 4) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int i = 0; i < n; ++i) {
             const float wi = use_shared ? w[i] : exp2f(lse[(int64_t)i * a.num_heads] - mx) * inv;
-            acc = fmaf(wi, po[i * stride + d], acc);
+            const float4 v = *reinterpret_cast<const float4 *>(po + i * stride + d);
+            acc.x = fmaf(wi, v.x, acc.x);
+            acc.y = fmaf(wi, v.y, acc.y);
+            acc.z = fmaf(wi, v.z, acc.z);
+            acc.w = fmaf(wi, v.w, acc.w);
         }
-        out[d] = Elem<TQ>::from_float(acc);
+        uint2 pk;
+        pk.x = Elem<TQ>::pack2(acc.x, acc.y);
+        pk.y = Elem<TQ>::pack2(acc.z, acc.w);
+        *reinterpret_cast<uint2 *>(out + d) = pk;
     }
 }
 
@@ -57,10 +65,11 @@ cudaError_t launch_pa_combine(const PaArgs &args, int n_combine_seqs, int q_dtyp
         return cudaSuccess;
     }
     dim3 grid(n_combine_seqs, args.num_heads);
+    const int threads = ((args.dv / 4 + 31) / 32 * 32) > 160 ? 160 : ((args.dv / 4 + 31) / 32 * 32);
     if (q_dtype == kFp16) {
-        pa_combine_kernel<__half><<<grid, 128, 0, stream>>>(args);
+        pa_combine_kernel<__half><<<grid, threads, 0, stream>>>(args);
     } else {
-        pa_combine_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(args);
+        pa_combine_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(args);
     }
     return cudaGetLastError();
 }
