@@ -68,5 +68,17 @@ def _obj_stale(obj, src):
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+def build_cpp_test():
+    """Compiles tests/cpp/atb_cpp_api_test.cpp (a C++ caller of include/atb/) against the library."""
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    src = os.path.join(ROOT, "tests", "cpp", "atb_cpp_api_test.cpp")
+    exe = os.path.join(ROOT, "tests", "cpp", "atb_cpp_api_test")
+    if os.path.exists(exe) and os.path.getmtime(exe) > max(os.path.getmtime(src), os.path.getmtime(OUT)):
+        return exe
+    subprocess.check_call([nvcc, "-std=c++17", "-O2", "-Wno-deprecated-gpu-targets", "-I" + os.path.join(ROOT, "include"),
+                           "-x", "cu", src, "-o", exe, "-L" + PKG, "-latb_b200", "-Xlinker", "-rpath=" + PKG])
+    return exe
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

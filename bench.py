@@ -175,7 +175,7 @@ def cpu_baseline(case, wl, d, lens):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--steps", type=int, default=3000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--config", type=int, default=1, help="index into the benchmark configurations (default 1)")
