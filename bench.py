@@ -324,7 +324,7 @@ def main():
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT,
                              "frac": achieved / peak, "peak_kind": "of " + peak_kind,
                              "kernel": "pa attention kernel, per GPU", "kernel_ms": kernel_ms,
-                             "traffic": ncu_traffic_bytes(case.name)}}
+                             "traffic": ncu_traffic_bytes(case.name) if world == 1 else None}}
         if world == 1 and not args.no_cpu_baseline:
             base, ref_out = cpu_baseline(case, wl, d, lens)
             line["cpu_baseline"] = base

@@ -149,7 +149,9 @@ def run_rac_case(rac_mod, spec):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py /path/to/ascend-transformer-boost")
+    ref_root = sys.argv[1]
     _stub_modules()
     kt = os.path.join(ref_root, "tests/apitest/kernelstest")
     sys.path.insert(0, kt)
