@@ -302,6 +302,7 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
     a.v_row_dim = d.v_row_dim;
     a.block_size = d.block_size;
     a.max_blocks = d.max_blocks_per_seq;
+    a.num_blocks = d.num_blocks;
     a.heads_per_cta = h.heads_per_cta;
     a.chunks_per_kvh = h.chunks_per_kvh;
     a.scale_log2 = d.qk_scale * 1.4426950408889634f;

@@ -94,6 +94,13 @@ __global__ void __launch_bounds__(kWarps * 32) pa_generic_kernel(const PaArgs a)
         const int32_t *bt = a.block_tables + (int64_t)item.seq * a.max_blocks;
         for (int t = item.tok_begin + warp; t < item.tok_end; t += kWarps) {
             const int64_t blk = bt[t / a.block_size];
+            if (blk < 0 || blk >= a.num_blocks) {
+                // a block id outside the cache: record it and leave the token out instead of faulting
+                if (lane == 0) {
+                    atomicExch(a.plan.status, kStatusBadBlockId);
+                }
+                continue;
+            }
             const int64_t row = blk * a.block_size + (t % a.block_size);
             const TKV *kp = kc + (row * a.kv_heads + kvh) * a.dk;
             const TKV *vp = vc + (row * a.kv_heads + kvh) * a.v_row_dim;

@@ -281,6 +281,7 @@ extern "C" int atb_b200_pa_decode_static_scratch(const atb_b200_pa_desc *desc, c
     a.v_row_dim = d.v_row_dim;
     a.block_size = d.block_size;
     a.max_blocks = d.max_blocks_per_seq;
+    a.num_blocks = d.num_blocks;
     a.heads_per_cta = heads_per_cta;
     a.chunks_per_kvh = chunks_per_kvh;
     a.scale_log2 = d.qk_scale * 1.4426950408889634f;

@@ -57,7 +57,7 @@ struct PaArgs {
     void *out;
     PaDevPlan plan;
     int32_t batch, num_heads, kv_heads, group; // group = num_heads / kv_heads
-    int32_t dk, dv, v_row_dim, block_size, max_blocks;
+    int32_t dk, dv, v_row_dim, block_size, max_blocks, num_blocks;
     int32_t heads_per_cta, chunks_per_kvh;     // generic kernel: head chunking inside a kv head
     float scale_log2;                          // qk_scale * log2(e)
     // kv heads sharded over several GPUs: every rank's gathered output [tokens, out_total_heads, dv]

@@ -44,8 +44,10 @@ def measured_peak_gbs():
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the attention kernel, from the ncu
-# captures summarised under profiles/ (pa_tma_mma_c2_gqa_bf16.md); None where no capture exists yet.
-NCU_TRAFFIC_BYTES = {"c2_gqa_bf16_llama3_8b": 805_704_448}
+# captures summarised under profiles/ (pa_tma_mma_c2_gqa_bf16.md, pa_tma_mma_i8_c3_int8kv.md,
+# pa_mla_tc5_c5_mla.md); None where no capture exists.
+NCU_TRAFFIC_BYTES = {"c2_gqa_bf16_llama3_8b": 806_254_592, "c3_int8kv_70b": 1_379_261_000,
+                     "c5_mla_bf16_dsv3": 259_522_048}
 
 
 def ncu_traffic_bytes(case_name):

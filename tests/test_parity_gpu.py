@@ -188,3 +188,28 @@ def test_plan_reuse_over_decode_steps():
         assert max_abs_err(wl.torch_to_host(out, "bf16"), ref, "bf16") <= 8e-3
         lens = lens + 1
         plan.update(lens)
+
+
+def test_bad_block_id_is_reported_not_faulted():
+    """A block id outside the cache (a caller bug) must not fault the GPU: the generic kernel skips the
+    token and sets the status word; the TMA kernels read zeros (out-of-bounds TMA fill)."""
+    case = wl.Case("badblk", batch=2, heads=8, kv_heads=2, dk=96, dv=96, block_size=16, q_dtype="fp16",
+                   ctx=("list", [40, 33]), seed=71)
+    h = wl.make_host_inputs(case)
+    h["block_tables"] = h["block_tables"].copy()
+    h["block_tables"][1, 1] = h["num_blocks"] + 5
+    d = host_inputs_to_device(case, h)
+    out, plan, ws = capi.paged_attention(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], h["context_lens"],
+                                         case.qk_scale, return_plan=True)
+    torch.cuda.synchronize()
+    assert plan.device_status(ws.data_ptr(), capi.torch_stream_ptr()) == 2
+    assert torch.isfinite(out.float()).all()
+    case2 = wl.Case("badblk128", batch=2, heads=8, kv_heads=2, q_dtype="bf16", ctx=("list", [300, 200]), seed=72)
+    h2 = wl.make_host_inputs(case2)
+    h2["block_tables"] = h2["block_tables"].copy()
+    h2["block_tables"][0, 1] = -1
+    d2 = host_inputs_to_device(case2, h2)
+    out2 = capi.paged_attention(d2["q"], d2["k_cache"], d2["v_cache"], d2["block_tables"], h2["context_lens"],
+                                case2.qk_scale)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out2.float()).all()
