@@ -97,7 +97,7 @@ EXPORTS = [
     "atb_b200_operation_setup", "atb_b200_operation_execute", "atb_b200_operation_destroy", "atb_b200_version",
     "atb_b200_pa_decode_static_scratch", "atb_b200_pa_launch_gathered", "atb_b200_peer_buffer_create",
     "atb_b200_peer_buffer_open", "atb_b200_peer_buffer_close", "atb_b200_peer_buffer_destroy",
-    "atb_b200_pa_plan_set_trace",
+    "atb_b200_pa_plan_set_trace", "atb_b200_pa_plan_prefetch",
 ]
 
 _lib = None
@@ -142,6 +142,7 @@ def lib():
         L.atb_b200_peer_buffer_close.argtypes = [vp]
         L.atb_b200_peer_buffer_destroy.argtypes = [vp]
         L.atb_b200_pa_plan_set_trace.argtypes = [vp, vp, u32]
+        L.atb_b200_pa_plan_prefetch.argtypes = [vp, vp]
         _lib = L
     return _lib
 
@@ -217,6 +218,9 @@ class PaPlan:
         _check(lib().atb_b200_pa_plan_device_status(self.handle, workspace_ptr, stream_ptr, ctypes.byref(st)),
                "atb_b200_pa_plan_device_status")
         return st.value
+
+    def prefetch(self, stream_ptr):
+        _check(lib().atb_b200_pa_plan_prefetch(self.handle, stream_ptr), "atb_b200_pa_plan_prefetch")
 
     def set_trace(self, device_ptr, capacity):
         _check(lib().atb_b200_pa_plan_set_trace(self.handle, device_ptr, capacity), "atb_b200_pa_plan_set_trace")

@@ -316,6 +316,9 @@ Status OperationBase::Setup(const VariantPack &variantPack, uint64_t &workspaceS
             setupOutDescs_.push_back(variantPack.outTensors.at(i).desc);
         }
         setupSuccess_ = true;
+        if (context->GetExecuteStream() != nullptr) {
+            AfterPlanImpl(context->GetExecuteStream());
+        }
         return NO_ERROR;
     } catch (...) {
         return ERROR_OUT_OF_HOST_MEMORY;

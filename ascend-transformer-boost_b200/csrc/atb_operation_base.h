@@ -52,6 +52,9 @@ protected:
     virtual const std::vector<DtypeComb> &DtypeCombs() const = 0;
     // Host planning from the tensors' descs and hostData; returns the workspace size.
     virtual Status PlanImpl(const VariantPack &variantPack, uint64_t &workspaceSize) = 0;
+    // Optional: called at the end of a successful Setup when the context already has a stream, so an
+    // operation can start moving its plan to the device before Execute.
+    virtual void AfterPlanImpl(aclrtStream) {}
     // Enqueue on `stream` with the device pointers of this call.
     virtual Status LaunchImpl(const VariantPack &variantPack, uint8_t *workspace, uint64_t workspaceSize,
                               aclrtStream stream) = 0;

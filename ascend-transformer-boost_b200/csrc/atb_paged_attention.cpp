@@ -300,6 +300,12 @@ protected:
         return NO_ERROR;
     }
 
+    void AfterPlanImpl(aclrtStream stream) override
+    {
+        // start uploading the plan now; if this fails Execute uploads it itself
+        (void)atb_b200_pa_plan_prefetch(plan_, stream);
+    }
+
     Status LaunchImpl(const VariantPack &vp, uint8_t *workspace, uint64_t workspaceSize, aclrtStream stream) override
     {
         const bool mla = param_.mlaVHeadSize > 0;

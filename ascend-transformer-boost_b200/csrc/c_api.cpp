@@ -25,6 +25,19 @@ struct atb_b200_pa_plan {
     cudaEvent_t uploaded[kStagingRing] = {};
     bool upload_pending[kStagingRing] = {};
     uint64_t uploads = 0;
+    // Prefetch path: plan-owned device copies of the blob, uploaded on a private stream ahead of
+    // the launch so that the copy leaves the caller's stream (ring: a slot is refilled only after
+    // the kernels that read it have completed).
+    static constexpr int kDevRing = 4;
+    cudaStream_t copy_stream = nullptr;
+    uint8_t *dev_blob = nullptr;
+    size_t dev_cap = 0;
+    cudaEvent_t dev_uploaded[kDevRing] = {}, dev_consumed[kDevRing] = {};
+    bool dev_consumed_pending[kDevRing] = {};
+    int prefetched_slot = -1;
+    void *prefetch_stream = nullptr; // the stream that was made to wait for the prefetched copy
+    uint64_t prefetches = 0;
+    const int32_t *last_status_ptr = nullptr;
     unsigned long long *trace = nullptr; // optional device event buffer (probe)
     uint32_t trace_cap = 0;
     // optional timing of the attention kernel: a ring of event pairs, one pair per launch
@@ -75,6 +88,7 @@ int atb_b200_pa_plan_update(atb_b200_pa_plan *plan, const int32_t *context_lens_
     if (plan == nullptr) {
         return kErrInvalidParam;
     }
+    plan->prefetched_slot = -1; // an upload of the old plan, if any, is simply never used
     try {
         const atb_b200_pa_desc d = plan->hp.desc;
         return plan_paged_attention(d, context_lens_host, plan->hp.sm_count, &plan->hp);
@@ -144,6 +158,22 @@ void atb_b200_pa_plan_destroy(atb_b200_pa_plan *plan)
     if (plan->staging != nullptr) {
         cudaFreeHost(plan->staging);
     }
+    if (plan->copy_stream != nullptr) {
+        cudaStreamSynchronize(plan->copy_stream);
+        for (int i = 0; i < atb_b200_pa_plan::kDevRing; ++i) {
+            if (plan->dev_consumed_pending[i]) {
+                cudaEventSynchronize(plan->dev_consumed[i]);
+            }
+            if (plan->dev_uploaded[i] != nullptr) {
+                cudaEventDestroy(plan->dev_uploaded[i]);
+                cudaEventDestroy(plan->dev_consumed[i]);
+            }
+        }
+        cudaStreamDestroy(plan->copy_stream);
+    }
+    if (plan->dev_blob != nullptr) {
+        cudaFree(plan->dev_blob);
+    }
     if (plan->status_host != nullptr) {
         cudaFreeHost(plan->status_host);
     }
@@ -191,6 +221,112 @@ int atb_b200_pa_plan_kernel_ms(atb_b200_pa_plan *plan, int32_t launches_back, fl
     return ATB_B200_OK;
 }
 
+// Writes the current blob into the next pinned staging slot (waiting, on the host, only for the copy
+// that last read that slot) and returns it; `*slot_out` is the slot whose event the caller records.
+static uint8_t *stage_blob(atb_b200_pa_plan *plan, int *slot_out)
+{
+    HostPlan &h = plan->hp;
+    constexpr int kRing = atb_b200_pa_plan::kStagingRing;
+    if (plan->staging_cap < h.blob_bytes) {
+        for (int i = 0; i < kRing; ++i) {
+            if (plan->upload_pending[i]) {
+                cudaEventSynchronize(plan->uploaded[i]);
+                plan->upload_pending[i] = false;
+            }
+        }
+        if (plan->staging != nullptr) {
+            cudaFreeHost(plan->staging);
+            plan->staging = nullptr;
+        }
+        const size_t cap = ((size_t)h.blob_bytes * 2 + 255) / 256 * 256;
+        if (cudaHostAlloc(reinterpret_cast<void **>(&plan->staging), cap * kRing, cudaHostAllocDefault) != cudaSuccess) {
+            plan->staging_cap = 0;
+            return nullptr;
+        }
+        plan->staging_cap = cap;
+    }
+    const int slot = (int)(plan->uploads % kRing);
+    if (plan->uploaded[slot] == nullptr &&
+        cudaEventCreateWithFlags(&plan->uploaded[slot], cudaEventDisableTiming) != cudaSuccess) {
+        return nullptr;
+    }
+    if (plan->upload_pending[slot]) {
+        cudaEventSynchronize(plan->uploaded[slot]); // the copy that last read this slot must be done
+    }
+    uint8_t *stage = plan->staging + (size_t)slot * plan->staging_cap;
+    h.write_blob(stage);
+    *slot_out = slot;
+    return stage;
+}
+
+int atb_b200_pa_plan_prefetch(atb_b200_pa_plan *plan, void *stream_v)
+{
+    if (plan == nullptr) {
+        return kErrInvalidParam;
+    }
+    HostPlan &h = plan->hp;
+    if (h.items.empty()) {
+        return ATB_B200_OK;
+    }
+    constexpr int kRing = atb_b200_pa_plan::kDevRing;
+    if (plan->copy_stream == nullptr) {
+        if (cudaStreamCreateWithFlags(&plan->copy_stream, cudaStreamNonBlocking) != cudaSuccess) {
+            return kErrRtFail;
+        }
+        for (int i = 0; i < kRing; ++i) {
+            if (cudaEventCreateWithFlags(&plan->dev_uploaded[i], cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&plan->dev_consumed[i], cudaEventDisableTiming) != cudaSuccess) {
+                return kErrRtFail;
+            }
+        }
+    }
+    if (plan->dev_cap < h.blob_bytes) {
+        for (int i = 0; i < kRing; ++i) {
+            if (plan->dev_consumed_pending[i]) {
+                cudaEventSynchronize(plan->dev_consumed[i]);
+                plan->dev_consumed_pending[i] = false;
+            }
+        }
+        cudaStreamSynchronize(plan->copy_stream);
+        if (plan->dev_blob != nullptr) {
+            cudaFree(plan->dev_blob);
+            plan->dev_blob = nullptr;
+        }
+        const size_t cap = ((size_t)h.blob_bytes * 2 + 255) / 256 * 256;
+        if (cudaMalloc(reinterpret_cast<void **>(&plan->dev_blob), cap * kRing) != cudaSuccess) {
+            plan->dev_cap = 0;
+            return 26; // ERROR_OUT_OF_DEVICE_MEMORY
+        }
+        plan->dev_cap = cap;
+    }
+    const int slot = (int)(plan->prefetches % kRing);
+    if (plan->dev_consumed_pending[slot]) {
+        cudaStreamWaitEvent(plan->copy_stream, plan->dev_consumed[slot], 0); // its last readers must be done
+        plan->dev_consumed_pending[slot] = false;
+    }
+    int sslot = 0;
+    uint8_t *stage = stage_blob(plan, &sslot);
+    if (stage == nullptr) {
+        return kErrOutOfHostMemory;
+    }
+    if (cudaMemcpyAsync(plan->dev_blob + (size_t)slot * plan->dev_cap, stage, h.blob_bytes, cudaMemcpyHostToDevice,
+                        plan->copy_stream) != cudaSuccess) {
+        return kErrRtFail;
+    }
+    cudaEventRecord(plan->uploaded[sslot], plan->copy_stream);
+    plan->upload_pending[sslot] = true;
+    plan->uploads++;
+    cudaEventRecord(plan->dev_uploaded[slot], plan->copy_stream);
+    // everything the caller enqueues on `stream` from here on runs after the upload
+    if (cudaStreamWaitEvent(static_cast<cudaStream_t>(stream_v), plan->dev_uploaded[slot], 0) != cudaSuccess) {
+        return kErrRtFail;
+    }
+    plan->prefetched_slot = slot;
+    plan->prefetch_stream = stream_v;
+    plan->prefetches++;
+    return ATB_B200_OK;
+}
+
 static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, const atb_b200_pa_peers *peers,
                           void *workspace, uint64_t workspace_bytes, void *stream_v);
 
@@ -232,43 +368,28 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
     if (h.items.empty() && peers == nullptr) {
         return ATB_B200_OK; // every sequence is empty: outputs stay untouched
     }
-    // ---- upload the plan (pinned staging ring, one async copy)
-    constexpr int kRing = atb_b200_pa_plan::kStagingRing;
-    if (plan->staging_cap < h.blob_bytes) {
-        for (int i = 0; i < kRing; ++i) {
-            if (plan->upload_pending[i]) {
-                cudaEventSynchronize(plan->uploaded[i]);
-                plan->upload_pending[i] = false;
-            }
+    // ---- the plan blob: already on the device (prefetch), or uploaded now into the workspace
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
+    uint8_t *blob = ws;
+    const int dev_slot = plan->prefetched_slot;
+    if (dev_slot >= 0) {
+        blob = plan->dev_blob + (size_t)dev_slot * plan->dev_cap;
+        if (plan->prefetch_stream != stream_v) { // launched on another stream than the one that waited
+            cudaStreamWaitEvent(stream, plan->dev_uploaded[dev_slot], 0);
         }
-        if (plan->staging != nullptr) {
-            cudaFreeHost(plan->staging);
-            plan->staging = nullptr;
-        }
-        const size_t cap = ((size_t)h.blob_bytes * 2 + 255) / 256 * 256;
-        if (cudaHostAlloc(reinterpret_cast<void **>(&plan->staging), cap * kRing, cudaHostAllocDefault) != cudaSuccess) {
-            plan->staging_cap = 0;
+    } else {
+        int sslot = 0;
+        uint8_t *stage = stage_blob(plan, &sslot);
+        if (stage == nullptr) {
             return kErrOutOfHostMemory;
         }
-        plan->staging_cap = cap;
+        if (cudaMemcpyAsync(ws, stage, h.blob_bytes, cudaMemcpyHostToDevice, stream) != cudaSuccess) {
+            return kErrRtFail;
+        }
+        cudaEventRecord(plan->uploaded[sslot], stream);
+        plan->upload_pending[sslot] = true;
+        plan->uploads++;
     }
-    const int slot = (int)(plan->uploads % kRing);
-    if (plan->uploaded[slot] == nullptr &&
-        cudaEventCreateWithFlags(&plan->uploaded[slot], cudaEventDisableTiming) != cudaSuccess) {
-        return kErrRtFail;
-    }
-    if (plan->upload_pending[slot]) {
-        cudaEventSynchronize(plan->uploaded[slot]); // the copy that last read this slot must be done
-    }
-    uint8_t *stage = plan->staging + (size_t)slot * plan->staging_cap;
-    h.write_blob(stage);
-    uint8_t *ws = static_cast<uint8_t *>(workspace);
-    if (cudaMemcpyAsync(ws, stage, h.blob_bytes, cudaMemcpyHostToDevice, stream) != cudaSuccess) {
-        return kErrRtFail;
-    }
-    cudaEventRecord(plan->uploaded[slot], stream);
-    plan->upload_pending[slot] = true;
-    plan->uploads++;
 
     const atb_b200_pa_desc &d = h.desc;
     PaArgs a{};
@@ -281,16 +402,17 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
     a.k_offset = t->k_offset;
     a.v_offset = t->v_offset;
     a.out = t->out;
-    a.plan.group_begin = reinterpret_cast<const int32_t *>(ws + h.off_group_begin);
-    a.plan.items = reinterpret_cast<const PaItem *>(ws + h.off_items);
-    a.plan.seq_part_base = reinterpret_cast<const int32_t *>(ws + h.off_part_base);
-    a.plan.seq_nparts = reinterpret_cast<const int32_t *>(ws + h.off_nparts);
-    a.plan.combine_seqs = reinterpret_cast<const int32_t *>(ws + h.off_combine);
+    a.plan.group_begin = reinterpret_cast<const int32_t *>(blob + h.off_group_begin);
+    a.plan.items = reinterpret_cast<const PaItem *>(blob + h.off_items);
+    a.plan.seq_part_base = reinterpret_cast<const int32_t *>(blob + h.off_part_base);
+    a.plan.seq_nparts = reinterpret_cast<const int32_t *>(blob + h.off_nparts);
+    a.plan.combine_seqs = reinterpret_cast<const int32_t *>(blob + h.off_combine);
     a.plan.part_o = reinterpret_cast<float *>(ws + h.off_part_o);
     a.plan.part_lse = reinterpret_cast<float *>(ws + h.off_lse);
-    a.plan.status = reinterpret_cast<int32_t *>(ws + h.off_status);
-    a.plan.done_ctas = reinterpret_cast<int32_t *>(ws + h.off_done);
-    a.plan.counters = (h.fused_combine && h.n_partials > 0) ? reinterpret_cast<int32_t *>(ws + h.off_counters) : nullptr;
+    a.plan.status = reinterpret_cast<int32_t *>(blob + h.off_status);
+    a.plan.done_ctas = reinterpret_cast<int32_t *>(blob + h.off_done);
+    a.plan.counters = (h.fused_combine && h.n_partials > 0) ? reinterpret_cast<int32_t *>(blob + h.off_counters) : nullptr;
+    plan->last_status_ptr = a.plan.status;
     a.plan.n_cta_groups = h.n_cta_groups;
     a.plan.cols = h.cols;
     a.batch = d.batch;
@@ -343,6 +465,11 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
     if (a.plan.counters == nullptr) {
         e = launch_pa_combine(a, (int)h.combine_seqs.size(), d.q_dtype, stream);
     }
+    if (dev_slot >= 0) {
+        cudaEventRecord(plan->dev_consumed[dev_slot], stream);
+        plan->dev_consumed_pending[dev_slot] = true;
+        plan->prefetched_slot = -1;
+    }
     return e == cudaSuccess ? ATB_B200_OK : kErrRtFail;
 }
 
@@ -357,7 +484,9 @@ int atb_b200_pa_plan_device_status(atb_b200_pa_plan *plan, void *workspace, void
         return kErrOutOfHostMemory;
     }
     const uint8_t *ws = static_cast<const uint8_t *>(workspace);
-    if (cudaMemcpyAsync(plan->status_host, ws + plan->hp.off_status, sizeof(int32_t), cudaMemcpyDeviceToHost, stream) !=
+    const void *src = plan->last_status_ptr != nullptr ? static_cast<const void *>(plan->last_status_ptr)
+                                                      : static_cast<const void *>(ws + plan->hp.off_status);
+    if (cudaMemcpyAsync(plan->status_host, src, sizeof(int32_t), cudaMemcpyDeviceToHost, stream) !=
             cudaSuccess ||
         cudaStreamSynchronize(stream) != cudaSuccess) {
         return kErrRtFail;

@@ -2,7 +2,7 @@
 //
 // The attention grid is n_cta_groups x cols CTAs.  A column is one kv head (or one chunk of the
 // query heads of one kv head); a CTA group owns a contiguous slice of the global sequence of
-// 128-token tiles, cut so that every group streams the same number of tiles (split-KV with exact
+// 64-token tiles, cut so that every group streams the same number of tiles (split-KV with exact
 // balance).  All columns of a group walk the same token ranges, so the 8 kv-head slices of one
 // cache page are read at about the same time.  A sequence cut into several ranges yields one fp32
 // partial result per range, merged by the combine kernel with their log-sum-exp weights.
@@ -15,7 +15,7 @@
 
 namespace atb_b200 {
 
-constexpr int kTileTokens = 128;
+constexpr int kTileTokens = 64; // scheduling granule: token ranges start at multiples of it
 
 // One contiguous token range of one sequence.  `slot` is the index of the partial result the range
 // writes, or -1 when the range is the whole sequence and the kernel writes the final output.

@@ -29,6 +29,7 @@ namespace atb_b200 {
 namespace {
 
 constexpr int kStageTokens = 64;
+constexpr int kBlockTokens = 128;   // cache block size this kernel is built for
 constexpr int kStages = 6;
 constexpr int kConsumerWarps = 4;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
@@ -121,7 +122,7 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
             for (int st0 = 0; st0 < n_st && alive; st0 += 32) {
                 int blk = 0;
                 if (st0 + lane < n_st) {
-                    blk = bt[(item.tok_begin + (st0 + lane) * kStageTokens) / kTileTokens];
+                    blk = bt[(item.tok_begin + (st0 + lane) * kStageTokens) / kBlockTokens];
                 }
                 const int cnt = min(32, n_st - st0);
                 for (int j = 0; j < cnt; ++j) {
@@ -131,7 +132,7 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
                             atomicExch(a.plan.status, kStatusWaitTimeout);
                             alive = false;
                         } else {
-                            const int tok_in_blk = (item.tok_begin + (st0 + j) * kStageTokens) % kTileTokens;
+                            const int tok_in_blk = (item.tok_begin + (st0 + j) * kStageTokens) % kBlockTokens;
                             uint8_t *dst = stages + stage * kStageBytes;
                             mbar_expect_tx(&full[stage], kStageBytes);
                             // a block id outside the cache makes the tile out of bounds: TMA fills zeros
@@ -562,7 +563,7 @@ template <typename T> cudaError_t launch_typed(const PaArgs &args, const CUtenso
 
 bool pa_tma_mma_i8_supported(int dk, int dv, int v_row_dim, int block_size, int group, int q_dtype, int kv_dtype)
 {
-    return dk == 128 && dv == 128 && v_row_dim == 128 && block_size == kTileTokens && group >= 1 && group <= 8 &&
+    return dk == 128 && dv == 128 && v_row_dim == 128 && block_size == kBlockTokens && group >= 1 && group <= 8 &&
            (q_dtype == kFp16 || q_dtype == kBf16) && kv_dtype == kInt8;
 }
 

@@ -247,7 +247,8 @@ def main():
     out_flat = out.view(-1)
 
     def step():
-        rc = L.atb_b200_reshape_and_cache(*rac_args)
+        rc = L.atb_b200_pa_plan_prefetch(plan_handle, stream_ptr)      # plan upload leaves the critical stream
+        rc |= L.atb_b200_reshape_and_cache(*rac_args)
         if p2p:
             peers, _ = exchange.peers()
             rc |= L.atb_b200_pa_launch_gathered(plan_handle, tens_ref, ctypes.byref(peers), ws_ptr, ws_bytes, stream_ptr)
@@ -406,9 +407,11 @@ def run_e2e(args, case, wl, capi, d, lens, dev, world, gathered):
 
     def step():
         dev_pack.copy_(host_pack, non_blocking=True)
+        # Setup of both operators first (host planning; PagedAttention re-plans from the host
+        # context_lens and starts uploading its plan), then the two Executes
         rc = L.atb_b200_operation_setup(rac.handle, rac_i, n_ri, rac_o, n_ro, ctypes.byref(need), ctx.handle)
-        rc |= L.atb_b200_operation_execute(rac.handle, rac_i, n_ri, rac_o, n_ro, None, 0, ctx.handle)
         rc |= L.atb_b200_operation_setup(pa.handle, pa_i, n_pi, pa_o, n_po, ctypes.byref(need), ctx.handle)
+        rc |= L.atb_b200_operation_execute(rac.handle, rac_i, n_ri, rac_o, n_ro, None, 0, ctx.handle)
         rc |= L.atb_b200_operation_execute(pa.handle, pa_i, n_pi, pa_o, n_po, ws_ptr, ws_len, ctx.handle)
         if rc != 0 or need.value > ws_len:
             raise RuntimeError(f"operator call failed ({rc})")

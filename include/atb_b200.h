@@ -110,6 +110,16 @@ int atb_b200_pa_launch(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *tensor
                        uint64_t workspace_bytes, void *stream);
 
 /*
+ * Optional: upload the plan ahead of the launch.  Copies the plan into device memory owned by the plan
+ * on a private stream and makes `stream` wait for that copy at the point of this call, so the copy
+ * overlaps whatever the caller enqueues before it and no longer sits between ReshapeAndCache and the
+ * attention kernel.  Call it after plan_create / plan_update and before the work that precedes the
+ * launch; the next atb_b200_pa_launch on the same stream then uses that copy.  Without it the launch
+ * uploads the plan itself.  (The reference uploads its tiling at Execute: operation_base.cpp:716.)
+ */
+int atb_b200_pa_plan_prefetch(atb_b200_pa_plan *plan, void *stream);
+
+/*
  * KV heads sharded over the GPUs of one node (one process per GPU): every rank computes the query
  * heads of its kv heads and the outputs are exchanged.  Instead of a separate all-gather
  * (AllGatherOperation after attention in a reference model graph,
