@@ -104,6 +104,9 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
         fence_barrier_init();
     }
     __syncthreads();
+    // launched with programmatic stream serialisation: everything above overlapped the tail of the
+    // previous kernel in the stream; wait for it (and its memory) before reading any input
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int item_begin = a.plan.group_begin[grp], item_end = a.plan.group_begin[grp + 1];
     uint32_t stage = 0, phase = 0;
@@ -554,9 +557,17 @@ template <typename T> cudaError_t launch_typed(const PaArgs &args, const CUtenso
             configured[dev] = true;
         }
     }
-    const int grid = args.plan.n_cta_groups * args.plan.cols;
-    kern<<<grid, kThreads, kSmemBytes, s>>>(km, vm, args);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(args.plan.n_cta_groups * args.plan.cols));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, km, vm, args);
 }
 
 } // namespace

@@ -16,6 +16,9 @@ __global__ void __launch_bounds__(256) reshape_and_cache_kernel(const uint8_t *_
                                                                 int64_t k_row_bytes, int64_t v_row_bytes,
                                                                 int64_t num_slots)
 {
+    // lets a dependent kernel launched with programmatic stream serialisation (the attention kernel)
+    // begin its prologue now; it still waits for this grid to finish before it reads the cache
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int token = blockIdx.x;
     const int64_t slot = slot_mapping[token];
     if (slot < 0 || slot >= num_slots) {
