@@ -16,6 +16,9 @@ template <typename TQ>
 __global__ void __launch_bounds__(160) pa_combine_kernel(const PaArgs a)
 {
     __shared__ float w[kMaxPartsShared];
+    // launched with programmatic stream serialisation right behind the attention kernel: wait for its
+    // partials before reading anything
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int seq = a.plan.combine_seqs[blockIdx.x];
     const int h = blockIdx.y;
     const int base = a.plan.seq_part_base[seq];
@@ -66,12 +69,19 @@ cudaError_t launch_pa_combine(const PaArgs &args, int n_combine_seqs, int q_dtyp
     }
     dim3 grid(n_combine_seqs, args.num_heads);
     const int threads = ((args.dv / 4 + 31) / 32 * 32) > 160 ? 160 : ((args.dv / 4 + 31) / 32 * 32);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
     if (q_dtype == kFp16) {
-        pa_combine_kernel<__half><<<grid, threads, 0, stream>>>(args);
-    } else {
-        pa_combine_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(args);
+        return cudaLaunchKernelEx(&cfg, pa_combine_kernel<__half>, args);
     }
-    return cudaGetLastError();
+    return cudaLaunchKernelEx(&cfg, pa_combine_kernel<__nv_bfloat16>, args);
 }
 
 } // namespace atb_b200

@@ -185,6 +185,9 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const PaArgs a)
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // launched with programmatic stream serialisation: the set-up above overlapped the tail of the
+    // previous kernel in the stream; wait for it (and its memory) before reading any input
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_o = tmem_base;                 // lanes 0-15 of every quadrant, columns 0..511
     const uint32_t tmem_s = tmem_base + (16u << 16);   // lanes 16-31 of every quadrant, columns 0..127
@@ -575,9 +578,17 @@ template <typename T> cudaError_t launch_typed(const PaArgs &args, const CUtenso
             configured[dev] = true;
         }
     }
-    const int grid = args.plan.n_cta_groups * args.plan.cols;
-    kern<<<grid, kThreads, kSmemBytes, s>>>(km, args);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(args.plan.n_cta_groups * args.plan.cols));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, km, args);
 }
 
 } // namespace
