@@ -213,3 +213,50 @@ def test_bad_block_id_is_reported_not_faulted():
                                 case2.qk_scale)
     torch.cuda.synchronize()
     assert torch.isfinite(out2.float()).all()
+
+
+def _random_cases(n, seed):
+    """Seeded random shapes around the tile / block / split boundaries of the tiled kernels."""
+    rng = np.random.default_rng(seed)
+    cases = []
+    boundary = [1, 2, 15, 16, 17, 63, 64, 65, 127, 128, 129, 191, 192, 193, 255, 256, 257, 511, 512, 513, 1000, 2047, 2048,
+                2049, 4097]
+    for i in range(n):
+        kind = i % 3
+        kv_heads = int(rng.choice([1, 2, 4, 8]))
+        group = int(rng.choice([1, 2, 3, 4, 5, 8]))
+        batch = int(rng.integers(1, 24))
+        lens = [int(rng.choice(boundary)) if rng.random() < 0.6 else int(rng.integers(1, 6000)) for _ in range(batch)]
+        if rng.random() < 0.3:
+            lens[int(rng.integers(0, batch))] = 0
+        kw = dict(batch=batch, heads=kv_heads * group, kv_heads=kv_heads, ctx=("list", lens), seed=1000 + i)
+        if kind == 0:
+            cases.append(wl.Case(f"rand{i}_bf16", q_dtype="bf16", **kw))
+        elif kind == 1:
+            cases.append(wl.Case(f"rand{i}_fp16", q_dtype="fp16", **kw))
+        else:
+            cases.append(wl.Case(f"rand{i}_int8", q_dtype=str(rng.choice(["fp16", "bf16"])), kv_dtype="int8",
+                                 offsets=bool(rng.random() < 0.5), **kw))
+    return cases
+
+
+@pytest.mark.parametrize("case", _random_cases(24, 2024), ids=lambda c: c.name)
+def test_randomized_shapes_match_oracle(case):
+    h = wl.make_host_inputs(case)
+    ref = oracle_out(case, h, out=np.zeros((case.batch, case.heads, case.dv), dtype=h["q"].dtype))
+    out, info = run_gpu_case(case, h, out_fill=0.0)
+    assert info.kernel == capi.KERNEL_TMA_MMA
+    err = max_abs_err(out, ref, case.q_dtype)
+    assert err <= tol_for(case), err
+
+
+@pytest.mark.parametrize("heads,lens", [(8, [1, 64, 65, 4000]), (128, [300, 6000, 63]), (64, [129, 128, 127]),
+                                         (16, [5000]), (192, [100, 2500])])
+def test_randomized_mla_shapes_match_oracle(heads, lens):
+    case = wl.Case(f"mla_rand_h{heads}", batch=len(lens), heads=heads, kv_heads=1, dk=576, dv=512, q_dtype="bf16",
+                   mla=True, ctx=("list", lens), seed=500 + heads)
+    h = wl.make_host_inputs(case)
+    ref = oracle_out(case, h)
+    out, info = run_gpu_case(case, h)
+    assert info.kernel == capi.KERNEL_MLA_TC5
+    assert max_abs_err(out, ref, "bf16") <= 8e-3
