@@ -1,0 +1,42 @@
+"""Property tests of the host planner over random batches: every token is covered exactly once, work
+is balanced, partial slots are consistent - for any SM count and any column count."""
+import numpy as np
+from hypothesis import given, settings, strategies as st
+
+from helpers import capi
+
+
+@settings(max_examples=150, deadline=None)
+@given(lens=st.lists(st.integers(min_value=0, max_value=40000), min_size=1, max_size=80),
+       kv_heads=st.sampled_from([1, 2, 4, 8, 32]), group=st.sampled_from([1, 4, 8]),
+       sm=st.sampled_from([1, 7, 132, 148]))
+def test_plan_invariants(lens, kv_heads, group, sm):
+    lens = np.asarray(lens, dtype=np.int32)
+    max_blocks = max(1, int((lens.max() + 127) // 128))
+    d = capi.make_desc(len(lens), kv_heads * group, kv_heads, 128, 128, 128, 1 << 20, max_blocks, "bf16", sm_count=sm)
+    plan = capi.PaPlan(d, lens)
+    info = plan.info
+    items, groups = plan.dump()
+    n_groups = info.num_ctas // kv_heads
+    covered = np.zeros(len(lens), dtype=np.int64)
+    parts = np.zeros(len(lens), dtype=np.int64)
+    last_end = {}
+    slots = []
+    for seq, b, e, slot in items:
+        assert 0 <= b < e <= lens[seq] and b % 64 == 0
+        assert last_end.get(seq, 0) == b          # ranges of a sequence are contiguous and in order
+        last_end[seq] = e
+        covered[seq] += e - b
+        parts[seq] += 1
+        if slot >= 0:
+            slots.append(slot)
+    assert np.array_equal(covered, lens.astype(np.int64))
+    assert sorted(slots) == list(range(info.num_partials))
+    assert info.num_partials == int(parts[parts > 1].sum())
+    assert info.num_combine_seqs == int((parts > 1).sum())
+    if info.num_items:
+        tiles = np.array([sum((e - b + 63) // 64 for _, b, e, _ in items[groups[g]:groups[g + 1]])
+                          for g in range(n_groups)])
+        assert groups[n_groups] == info.num_items
+        assert tiles.max() - tiles.mean() <= 2.5  # absolute cuts: never more than ~two tiles above the mean
+    plan.close()
