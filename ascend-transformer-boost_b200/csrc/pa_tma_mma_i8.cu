@@ -1,5 +1,5 @@
 // Paged decode attention over an int8 KV cache with per-channel dequantisation
-// (quantType TYPE_DEQUANT_FUSION), head_dim 128 / block_size 128, up to 8 query heads per kv head.
+// (quantType TYPE_DEQUANT_FUSION), head_dim 128 / block_size 16, 32, 64, 128 or 256, up to 8 query heads per kv head.
 //
 // Same structure as the fp16/bf16 kernel in pa_tma_mma.cu (TMA page gather into a shared-memory
 // ring, four consumer warps with independent online-softmax states, split-KV partials), with the
@@ -29,7 +29,6 @@ namespace atb_b200 {
 namespace {
 
 constexpr int kStageTokens = 64;
-constexpr int kBlockTokens = 128;   // cache block size this kernel is built for
 constexpr int kStages = 6;
 constexpr int kConsumerWarps = 4;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
@@ -122,30 +121,44 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
             const PaItem item = a.plan.items[it];
             const int n_st = (item.tok_end - item.tok_begin + kStageTokens - 1) / kStageTokens;
             const int32_t *bt = a.block_tables + (int64_t)item.seq * a.max_blocks;
-            for (int st0 = 0; st0 < n_st && alive; st0 += 32) {
-                int blk = 0;
-                if (st0 + lane < n_st) {
-                    blk = bt[(item.tok_begin + (st0 + lane) * kStageTokens) / kBlockTokens];
+            // A 64-token stage is one TMA box per operand half when the cache block holds >= 64 tokens,
+            // and 64 / block_size boxes (one per block) otherwise.  The lanes look the block ids of up
+            // to 32 boxes up at once; boxes past the end of the range get id -1 (zero-filled tile).
+            const int box_tok = min(a.block_size, kStageTokens);
+            const int bps = kStageTokens / box_tok;          // boxes per stage: 1, 2 or 4
+            const int box_bytes = box_tok * 128;
+            const int st_per_batch = 32 / bps;
+            for (int st0 = 0; st0 < n_st && alive; st0 += st_per_batch) {
+                int blk = -1;
+                {
+                    const int tok = item.tok_begin + (st0 + lane / bps) * kStageTokens + (lane % bps) * box_tok;
+                    if (tok < item.tok_end) {
+                        blk = bt[tok / a.block_size];
+                    }
                 }
-                const int cnt = min(32, n_st - st0);
+                const int cnt = min(st_per_batch, n_st - st0);
                 for (int j = 0; j < cnt; ++j) {
-                    const int b = __shfl_sync(0xffffffffu, blk, j);
                     if (lane == 0) {
                         if (!mbar_wait(&empty[stage], phase ^ 1u)) {
                             atomicExch(a.plan.status, kStatusWaitTimeout);
                             alive = false;
                         } else {
-                            const int tok_in_blk = (item.tok_begin + (st0 + j) * kStageTokens) % kBlockTokens;
-                            uint8_t *dst = stages + stage * kStageBytes;
                             mbar_expect_tx(&full[stage], kStageBytes);
-                            // a block id outside the cache makes the tile out of bounds: TMA fills zeros
-                            tma_load_4d(dst, &kmap, &full[stage], 0, kvh, tok_in_blk, b);
-                            tma_load_4d(dst + kTileBytes, &vmap, &full[stage], 0, kvh, tok_in_blk, b);
                         }
                     }
                     alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
                     if (!alive) {
                         break;
+                    }
+                    for (int bx = 0; bx < bps; ++bx) {
+                        const int b = __shfl_sync(0xffffffffu, blk, j * bps + bx);
+                        if (lane == 0) {
+                            const int tok_in_blk = (item.tok_begin + (st0 + j) * kStageTokens + bx * box_tok) % a.block_size;
+                            uint8_t *dst = stages + stage * kStageBytes + bx * box_bytes;
+                            // a block id outside the cache makes the tile out of bounds: TMA fills zeros
+                            tma_load_4d(dst, &kmap, &full[stage], 0, kvh, tok_in_blk, b);
+                            tma_load_4d(dst + kTileBytes, &vmap, &full[stage], 0, kvh, tok_in_blk, b);
+                        }
                     }
                     if (++stage == kStages) {
                         stage = 0;
@@ -533,7 +546,7 @@ bool encode_cache_map(CUtensorMap *map, const void *base, int kv_heads, int bloc
     }
     cuuint64_t dims[4] = {128, (cuuint64_t)kv_heads, (cuuint64_t)block_size, (cuuint64_t)num_blocks};
     cuuint64_t strides[3] = {128, (cuuint64_t)kv_heads * 128, (cuuint64_t)block_size * kv_heads * 128};
-    cuuint32_t box[4] = {128, 1, kStageTokens, 1};
+    cuuint32_t box[4] = {128, 1, (cuuint32_t)(block_size < kStageTokens ? block_size : kStageTokens), 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -574,7 +587,7 @@ template <typename T> cudaError_t launch_typed(const PaArgs &args, const CUtenso
 
 bool pa_tma_mma_i8_supported(int dk, int dv, int v_row_dim, int block_size, int group, int q_dtype, int kv_dtype)
 {
-    return dk == 128 && dv == 128 && v_row_dim == 128 && block_size == kBlockTokens && group >= 1 && group <= 8 &&
+    return dk == 128 && dv == 128 && v_row_dim == 128 && (block_size == 16 || block_size == 32 || block_size == 64 || block_size == 128 || block_size == 256) && group >= 1 && group <= 8 &&
            (q_dtype == kFp16 || q_dtype == kBf16) && kv_dtype == kInt8;
 }
 

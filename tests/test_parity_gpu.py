@@ -21,7 +21,7 @@ torch = pytest.importorskip("torch")
 def _kernels_for(case):
     ks = [capi.KERNEL_AUTO]
     group = case.heads // case.kv_heads
-    if case.dk == 128 and case.dv == 128 and case.block_size == 128 and group <= 8 and not case.mla:
+    if case.dk == 128 and case.dv == 128 and case.block_size in (16, 32, 64, 128, 256) and group <= 8 and not case.mla:
         ks.append(capi.KERNEL_GENERIC)
     if case.mla and case.batch * case.heads <= 4096:
         ks.append(capi.KERNEL_GENERIC)
@@ -215,9 +215,10 @@ def test_bad_block_id_is_reported_not_faulted():
     assert torch.isfinite(out2.float()).all()
 
 
-def _random_cases(n, seed):
+def _random_cases(n, seed, block_sizes=(128,)):
     """Seeded random shapes around the tile / block / split boundaries of the tiled kernels."""
     rng = np.random.default_rng(seed)
+    bs_rng = np.random.default_rng(seed + 7)
     cases = []
     boundary = [1, 2, 15, 16, 17, 63, 64, 65, 127, 128, 129, 191, 192, 193, 255, 256, 257, 511, 512, 513, 1000, 2047, 2048,
                 2049, 4097]
@@ -229,18 +230,20 @@ def _random_cases(n, seed):
         lens = [int(rng.choice(boundary)) if rng.random() < 0.6 else int(rng.integers(1, 6000)) for _ in range(batch)]
         if rng.random() < 0.3:
             lens[int(rng.integers(0, batch))] = 0
-        kw = dict(batch=batch, heads=kv_heads * group, kv_heads=kv_heads, ctx=("list", lens), seed=1000 + i)
+        kw = dict(batch=batch, heads=kv_heads * group, kv_heads=kv_heads, ctx=("list", lens), seed=1000 + i,
+                  block_size=int(bs_rng.choice(block_sizes)))
         if kind == 0:
-            cases.append(wl.Case(f"rand{i}_bf16", q_dtype="bf16", **kw))
+            cases.append(wl.Case(f"rand{i}_bs{kw['block_size']}_bf16", q_dtype="bf16", **kw))
         elif kind == 1:
-            cases.append(wl.Case(f"rand{i}_fp16", q_dtype="fp16", **kw))
+            cases.append(wl.Case(f"rand{i}_bs{kw['block_size']}_fp16", q_dtype="fp16", **kw))
         else:
-            cases.append(wl.Case(f"rand{i}_int8", q_dtype=str(rng.choice(["fp16", "bf16"])), kv_dtype="int8",
+            cases.append(wl.Case(f"rand{i}_bs{kw['block_size']}_int8", q_dtype=str(rng.choice(["fp16", "bf16"])), kv_dtype="int8",
                                  offsets=bool(rng.random() < 0.5), **kw))
     return cases
 
 
-@pytest.mark.parametrize("case", _random_cases(24, 2024), ids=lambda c: c.name)
+@pytest.mark.parametrize("case", _random_cases(24, 2024) + _random_cases(24, 4242, (16, 32, 64, 256)),
+                         ids=lambda c: c.name)
 def test_randomized_shapes_match_oracle(case):
     h = wl.make_host_inputs(case)
     ref = oracle_out(case, h, out=np.zeros((case.batch, case.heads, case.dv), dtype=h["q"].dtype))
