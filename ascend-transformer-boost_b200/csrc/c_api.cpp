@@ -1,6 +1,7 @@
 // extern "C" boundary of libatb_b200.so (see include/atb_b200.h).
 #include <cuda_runtime.h>
 #include <cmath>
+#include <cstdio>
 #include <cstring>
 #include <new>
 #include "../../include/atb_b200.h"
@@ -460,10 +461,14 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
         plan->launches++;
     }
     if (e != cudaSuccess) {
+        std::fprintf(stderr, "[atb][ERROR] paged attention kernel launch failed: %s\n", cudaGetErrorString(e));
         return kErrRtFail;
     }
     if (a.plan.counters == nullptr) {
         e = launch_pa_combine(a, (int)h.combine_seqs.size(), d.q_dtype, stream);
+        if (e != cudaSuccess) {
+            std::fprintf(stderr, "[atb][ERROR] split-KV merge kernel launch failed: %s\n", cudaGetErrorString(e));
+        }
     }
     if (dev_slot >= 0) {
         cudaEventRecord(plan->dev_consumed[dev_slot], stream);
