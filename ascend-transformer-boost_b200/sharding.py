@@ -6,7 +6,11 @@ Attention is independent per kv head, so the only exchange is an all-gather of t
 [tokens, heads/R, Dv]; the gathered tensor is rank-major [R, tokens, heads/R, Dv] (the convention of
 ATB's AllGatherOperation, src/ops/ops_infer/all_gather/all_gather_operation.cpp:79-89 of the
 reference) and `gathered_to_full` views it as [tokens, heads, Dv].
-The MLA combined cache has a single kv head and cannot be sharded this way.
+The MLA combined cache has a single kv head (kvHeadNum == 1 is enforced,
+src/ops/ops_infer/paged_attention/paged_attention_operation.cpp:355-358) and cannot be sharded this
+way; it is sharded by sequence instead: rank r owns the contiguous sequences
+[r*B/R, (r+1)*B/R) with their cache blocks (data-parallel attention), and the all-gather of the
+per-rank outputs [B/R, heads, Dv] along the first dimension is already the final [B, heads, Dv].
 """
 import numpy as np
 
@@ -32,6 +36,32 @@ def shard_host_inputs(case, h, rank, world):
         if h.get(name) is not None:
             d[name] = np.ascontiguousarray(h[name].reshape(case.kv_heads, width)[kvs].reshape(-1))
     return d
+
+
+def sequence_slice(batch, rank, world):
+    """Contiguous sequences of one rank when a step is sharded by sequence (MLA)."""
+    if batch % world != 0:
+        raise ValueError(f"{batch} sequences cannot be split evenly over {world} ranks")
+    per = batch // world
+    return slice(rank * per, (rank + 1) * per)
+
+
+def shard_host_inputs_by_sequence(case, h, rank, world):
+    """Slices the numpy inputs of workloads.make_host_inputs down to one rank's sequences.  The block
+    pool stays whole (a real deployment gives each rank only its sequences' blocks; the ids in the
+    block tables are unchanged here, so the result is identical)."""
+    sl = sequence_slice(case.batch, rank, world)
+    d = dict(h)
+    for name in ("q", "block_tables", "context_lens", "slot_mapping", "new_k", "new_v"):
+        if h.get(name) is not None:
+            d[name] = np.ascontiguousarray(h[name][sl])
+    return d
+
+
+def gathered_sequences_to_full(gathered):
+    """[R, B/R, heads, Dv] (rank-major all-gather of sequence shards) -> [B, heads, Dv], a pure view."""
+    r, b, hh, dv = gathered.shape
+    return gathered.reshape(r * b, hh, dv)
 
 
 def gathered_to_full(gathered):

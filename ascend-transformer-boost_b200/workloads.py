@@ -78,6 +78,15 @@ class Case:
         return replace(self, name=f"{self.name}/r{rank}of{world}", heads=self.heads // world,
                        kv_heads=self.kv_heads // world)
 
+    def shard_sequences(self, rank, world):
+        """The slice of this case one rank owns when the sequences are sharded over `world` GPUs
+        (the MLA cache has one kv head, so it is split by sequence): same lengths as the unsharded
+        case, taken in contiguous chunks."""
+        assert self.batch % world == 0
+        per = self.batch // world
+        lens = context_lens(self)[rank * per:(rank + 1) * per]
+        return replace(self, name=f"{self.name}/seq{rank}of{world}", batch=per, ctx=("list", [int(x) for x in lens]))
+
 
 # The benchmark configurations, in order (index 0 is the CPU-runnable golden case).
 CONFIGS = [

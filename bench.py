@@ -7,7 +7,8 @@ cache, then attention of every sequence's query token over its cached context.  
 benchmark configuration 2 (GQA decode, Llama-3-8B attention shape: bf16, batch 64, 32 q / 8 kv
 heads, head_dim 128, block_size 128, context_lens uniform in [2048,4096]) with seeded synthetic
 tensors.  With N > 1 the kv heads are sharded over the ranks (strong scaling, one process per GPU)
-and the per-shard outputs are all-gathered with NCCL.
+and the per-shard outputs are gathered; the MLA configuration has a single kv head and is sharded by
+sequence instead (contiguous chunks of the batch per rank).
 
 Prints ONE JSON line: `value` is whole-job KV GB/s with all inputs resident in HBM (device-timed),
 `e2e` the same metric through the atb operator API with host buffers (H2D of the step's inputs,
@@ -205,10 +206,18 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     capi.lib()
 
-    shard = case.shard_heads(rank, world) if world > 1 else case
+    # kv heads are sharded over the ranks; the MLA cache has one kv head and is sharded by sequence
+    by_sequence = world > 1 and case.kv_heads % world != 0
+    if world == 1:
+        shard = case
+    elif by_sequence:
+        shard = case.shard_sequences(rank, world)
+    else:
+        shard = case.shard_heads(rank, world)
     d = wl.make_device_inputs(shard, dev)
     lens = d["context_lens_host"]
-    kv_bytes_global = wl.kv_bytes(case, lens)
+    global_lens = wl.context_lens(case)
+    kv_bytes_global = wl.kv_bytes(case, global_lens)
     B, H_local, Dv = shard.batch, shard.heads, shard.dv
 
     stream = torch.cuda.Stream()
@@ -315,9 +324,11 @@ def main():
                 "data": "synthetic",
                 "config": {"workload": case.name, "batch": case.batch, "q_heads": case.heads,
                            "kv_heads": case.kv_heads, "head_dim": case.dk, "block_size": case.block_size,
-                           "context_tokens": int(lens.sum()), "kv_bytes_per_step": kv_bytes_global,
-                           "parallelism": (f"kv-head shard x{world}, outputs gathered by " +
-                                           ("peer stores from the attention kernel" if p2p else "NCCL all-gather"))
+                           "context_tokens": int(global_lens.sum()), "kv_bytes_per_step": kv_bytes_global,
+                           "parallelism": ((f"sequence shard x{world} (one kv head: contiguous chunks of the batch per "
+                                            "rank), outputs gathered by NCCL all-gather") if by_sequence else
+                                           (f"kv-head shard x{world}, outputs gathered by " +
+                                            ("peer stores from the attention kernel" if p2p else "NCCL all-gather")))
                            if world > 1 else "single GPU",
                            "l2": "KV cache per GPU (%.0f MB) is larger than the 126 MB L2" %
                                  (wl.kv_bytes(shard, lens) / 1e6),
