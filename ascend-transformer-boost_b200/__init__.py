@@ -8,6 +8,6 @@ The directory name is not a Python identifier; load it with `__graft_entry__.loa
 which registers it as the module `atb_b200`.
 """
 from . import build as _build  # noqa: F401
-from . import capi, sharding, workloads  # noqa: F401
+from . import capi, sharding, torch_atb, workloads  # noqa: F401
 
 build = _build.build

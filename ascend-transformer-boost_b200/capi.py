@@ -97,7 +97,7 @@ EXPORTS = [
     "atb_b200_operation_setup", "atb_b200_operation_execute", "atb_b200_operation_destroy", "atb_b200_version",
     "atb_b200_pa_decode_static_scratch", "atb_b200_pa_launch_gathered", "atb_b200_peer_buffer_create",
     "atb_b200_peer_buffer_open", "atb_b200_peer_buffer_close", "atb_b200_peer_buffer_destroy",
-    "atb_b200_pa_plan_set_trace", "atb_b200_pa_plan_prefetch",
+    "atb_b200_pa_plan_set_trace", "atb_b200_pa_plan_prefetch", "atb_b200_operation_name",
 ]
 
 _lib = None
@@ -134,6 +134,7 @@ def lib():
         L.atb_b200_operation_setup.argtypes = [vp, P(AtbTensor), u32, P(AtbTensor), u32, P(u64), vp]
         L.atb_b200_operation_execute.argtypes = [vp, P(AtbTensor), u32, P(AtbTensor), u32, vp, u64, vp]
         L.atb_b200_operation_destroy.argtypes = [vp]
+        L.atb_b200_operation_name.argtypes = [vp, ctypes.c_char_p, u64]
         L.atb_b200_version.restype = ctypes.c_char_p
         L.atb_b200_pa_decode_static_scratch.argtypes = [P(PaDesc), vp, P(PaTensors), vp]
         L.atb_b200_pa_launch_gathered.argtypes = [vp, P(PaTensors), P(PaPeers), vp, u64, vp]
@@ -463,6 +464,12 @@ class Operation:
         n = ctypes.c_uint32()
         _check(lib().atb_b200_operation_output_num(self.handle, ctypes.byref(n)), "GetOutputNum")
         return n.value
+
+    @property
+    def name(self):
+        buf = ctypes.create_string_buffer(128)
+        _check(lib().atb_b200_operation_name(self.handle, buf, len(buf)), "GetName")
+        return buf.value.decode()
 
     @staticmethod
     def _arr(tensors):

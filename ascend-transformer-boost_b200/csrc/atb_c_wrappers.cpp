@@ -104,6 +104,22 @@ int atb_b200_operation_output_num(void *operation, uint32_t *n)
     return NO_ERROR;
 }
 
+int atb_b200_operation_name(void *operation, char *buf, uint64_t cap)
+{
+    if (operation == nullptr || buf == nullptr || cap == 0) {
+        return ERROR_INVALID_PARAM;
+    }
+    try {
+        const std::string name = static_cast<Operation *>(operation)->GetName();
+        const uint64_t n = name.size() < cap - 1 ? name.size() : cap - 1;
+        std::memcpy(buf, name.data(), n);
+        buf[n] = '\0';
+    } catch (...) {
+        return ERROR_INTERNAL_ERROR;
+    }
+    return NO_ERROR;
+}
+
 int atb_b200_operation_infer_shape(void *operation, const atb_b200_tensor *in, uint32_t n_in, atb_b200_tensor *out,
                                    uint32_t n_out)
 {

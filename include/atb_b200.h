@@ -235,6 +235,9 @@ int atb_b200_operation_create_paged_attention(const void *param, uint64_t param_
 int atb_b200_operation_create_reshape_and_cache(const void *param, uint64_t param_bytes, void **operation);
 int atb_b200_operation_input_num(void *operation, uint32_t *n);
 int atb_b200_operation_output_num(void *operation, uint32_t *n);
+/* Operation::GetName (include/atb/operation.h:46 of the reference): copies the NUL-terminated name into
+ * buf (at most cap bytes, always terminated); ERROR_INVALID_PARAM when buf is null or cap is 0. */
+int atb_b200_operation_name(void *operation, char *buf, uint64_t cap);
 int atb_b200_operation_infer_shape(void *operation, const atb_b200_tensor *in, uint32_t n_in, atb_b200_tensor *out,
                                    uint32_t n_out);
 int atb_b200_operation_setup(void *operation, const atb_b200_tensor *in, uint32_t n_in, const atb_b200_tensor *out,
