@@ -6,7 +6,7 @@ from hypothesis import given, settings, strategies as st
 from helpers import capi
 
 
-@settings(max_examples=150, deadline=None)
+@settings(max_examples=500, deadline=None, derandomize=True)
 @given(lens=st.lists(st.integers(min_value=0, max_value=40000), min_size=1, max_size=80),
        kv_heads=st.sampled_from([1, 2, 4, 8, 32]), group=st.sampled_from([1, 4, 8]),
        sm=st.sampled_from([1, 7, 132, 148]))
@@ -35,8 +35,11 @@ def test_plan_invariants(lens, kv_heads, group, sm):
     assert info.num_partials == int(parts[parts > 1].sum())
     assert info.num_combine_seqs == int((parts > 1).sum())
     if info.num_items:
+        # work is balanced in 64-token tiles (a sequence occupies ceil(len / 64) of them): a cut is the
+        # absolute position j*total/n rounded down, moved by at most one tile onto a sequence boundary,
+        # so a group is less than three tiles (one per end + the rounding) above the mean
         tiles = np.array([sum((e - b + 63) // 64 for _, b, e, _ in items[groups[g]:groups[g + 1]])
                           for g in range(n_groups)])
         assert groups[n_groups] == info.num_items
-        assert tiles.max() - tiles.mean() <= 2.5  # absolute cuts: never more than ~two tiles above the mean
+        assert tiles.max() - tiles.mean() < 3.0
     plan.close()
