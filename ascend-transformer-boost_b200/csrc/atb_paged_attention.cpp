@@ -8,6 +8,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <new>
+#include <vector>
 #include "../../include/atb_b200.h"
 #include "atb_operation_base.h"
 
@@ -56,11 +57,11 @@ bool ParamCheck(const Param &p)
         }
     }
     // Features outside the decode hot path of this build.
-    if (p.maskType != Param::UNDEFINED || p.batchRunStatusEnable || p.compressType != Param::COMPRESS_TYPE_UNDEFINED ||
+    if (p.maskType != Param::UNDEFINED || p.compressType != Param::COMPRESS_TYPE_UNDEFINED ||
         p.calcType != Param::CALC_TYPE_UNDEFINED || p.scaleType != Param::SCALE_TYPE_TOR ||
         p.inputLayout != infer::TYPE_BSND ||
         (p.quantType != Param::TYPE_QUANT_UNQUANT && p.quantType != Param::TYPE_DEQUANT_FUSION)) {
-        ATB_B200_LOG(ERROR, "PagedAttention: mask / batchRunStatus / compress / SPEC / logN / BNSD / QKV-quant "
+        ATB_B200_LOG(ERROR, "PagedAttention: mask / compress / SPEC / logN / BNSD / QKV-quant "
                             "are not supported by this build");
         return false;
     }
@@ -91,7 +92,11 @@ public:
             if (p.quantType == Param::TYPE_DEQUANT_FUSION) {
                 // descale tensors: fp32, the int64-packed fp32 encoding, or (extension) fp16
                 for (aclDataType sc : {ACL_FLOAT, ACL_INT64, ACL_FLOAT16}) {
-                    DtypeComb c = {h, ACL_INT8, ACL_INT8, ACL_INT32, ACL_INT32, sc};
+                    DtypeComb c = {h, ACL_INT8, ACL_INT8, ACL_INT32, ACL_INT32};
+                    if (p.batchRunStatusEnable) {
+                        c.push_back(ACL_INT32);
+                    }
+                    c.push_back(sc);
                     if (p.hasQuantOffset) {
                         c.push_back(ACL_INT32);
                     }
@@ -102,10 +107,18 @@ public:
                     c.push_back(h);
                     combs_.push_back(c);
                 }
-            } else if (mla) {
-                combs_.push_back({h, h, ACL_INT32, ACL_INT32, h});
             } else {
-                combs_.push_back({h, h, h, ACL_INT32, ACL_INT32, h});
+                DtypeComb c = {h, h};
+                if (!mla) {
+                    c.push_back(h);
+                }
+                c.push_back(ACL_INT32);
+                c.push_back(ACL_INT32);
+                if (p.batchRunStatusEnable) {
+                    c.push_back(ACL_INT32);
+                }
+                c.push_back(h);
+                combs_.push_back(c);
             }
         }
     }
@@ -122,6 +135,9 @@ public:
     uint32_t GetInputNum() const override
     {
         uint32_t n = 5; // query, keyCache, valueCache, blockTables, contextLens
+        if (param_.batchRunStatusEnable) {
+            n += 1; // batchRunStatus
+        }
         if (param_.quantType == Param::TYPE_DEQUANT_FUSION) {
             n += param_.hasQuantOffset ? 4 : 2;
         }
@@ -133,6 +149,9 @@ public:
     uint32_t GetOutputNum() const override { return 1; }
 
 protected:
+    // position of kDescale: after contextLens and the optional batchRunStatus
+    size_t ScalePos() const { return param_.batchRunStatusEnable ? 6 : 5; }
+
     const std::vector<DtypeComb> &DtypeCombs() const override { return combs_; }
 
     Status InferShapeCheckImpl(const SVector<TensorDesc> &in) const override
@@ -157,7 +176,17 @@ protected:
             ATB_B200_LOG(ERROR, "PagedAttention: keyCache dim 2 should equal kvHeadNum");
             return ERROR_INVALID_TENSOR_DIM;
         }
-        if (in.at(btPos).shape.dims[0] != q.dims[0] || in.at(clPos).shape.dims[0] != q.dims[0]) {
+        if (param_.batchRunStatusEnable) {
+            // dynamic batch: the control tensors may describe more sequences than there are query tokens
+            if (q.dims[0] > in.at(btPos).shape.dims[0] || q.dims[0] > in.at(clPos).shape.dims[0]) {
+                ATB_B200_LOG(ERROR, "PagedAttention: numTokens in q should be no greater than blockTables and contextLens");
+                return ERROR_INVALID_TENSOR_DIM;
+            }
+            if (in.at(clPos + 1).shape.dimNum != 1 || in.at(clPos + 1).shape.dims[0] < q.dims[0]) {
+                ATB_B200_LOG(ERROR, "PagedAttention: batchRunStatus should hold one value per query token");
+                return ERROR_INVALID_TENSOR_DIM;
+            }
+        } else if (in.at(btPos).shape.dims[0] != q.dims[0] || in.at(clPos).shape.dims[0] != q.dims[0]) {
             ATB_B200_LOG(ERROR, "PagedAttention: blockTables / contextLens rows should equal query tokens");
             return ERROR_INVALID_TENSOR_DIM;
         }
@@ -182,7 +211,7 @@ protected:
                 return ERROR_INVALID_TENSOR_DIM;
             }
             const int64_t want = kvHeads * headSize;
-            for (size_t i = 5; i < in.size(); ++i) {
+            for (size_t i = ScalePos(); i < in.size(); ++i) {
                 if (in.at(i).shape.dimNum != 1 || in.at(i).shape.dims[0] != want) {
                     ATB_B200_LOG(ERROR, "PagedAttention: descale / offset should have kvHeadNum*headSize elements");
                     return ERROR_INVALID_TENSOR_DIM;
@@ -280,6 +309,25 @@ protected:
             d.sm_count = std::atoi(sm);
         }
         const int32_t *lens = static_cast<const int32_t *>(cl.hostData);
+        if (param_.batchRunStatusEnable) {
+            // Dynamic batch: the status tensor is host data like contextLens
+            // (src/ops/ops_infer/paged_attention/param.cpp:39-50 of the reference).  The reference's kernels
+            // skip a sequence through its zero context length; here a sequence whose status is 0 is also
+            // planned as empty, so it is skipped whatever length the caller left in contextLens.
+            const Tensor &status = vp.inTensors.at(clPos + 1);
+            if (status.hostData == nullptr) {
+                ATB_B200_LOG(ERROR, "PagedAttention: batchRunStatus hostData is null");
+                return ERROR_INVALID_PARAM;
+            }
+            const int32_t *run = static_cast<const int32_t *>(status.hostData);
+            effectiveLens_.assign(lens, lens + d.batch);
+            for (int32_t b = 0; b < d.batch; ++b) {
+                if (run[b] == 0) {
+                    effectiveLens_[b] = 0;
+                }
+            }
+            lens = effectiveLens_.data();
+        }
         int rc;
         if (plan_ != nullptr && SameDesc(d)) {
             rc = atb_b200_pa_plan_update(plan_, lens);
@@ -318,7 +366,7 @@ protected:
         t.out = vp.outTensors.at(0).deviceData;
         if (param_.quantType == Param::TYPE_DEQUANT_FUSION) {
             // runner order: kDescale, [kOffset], vDescale, [vOffset]
-            size_t i = 5;
+            size_t i = ScalePos();
             const Tensor &ks = vp.inTensors.at(i++);
             const Tensor *ko = param_.hasQuantOffset ? &vp.inTensors.at(i++) : nullptr;
             const Tensor &vs = vp.inTensors.at(i++);
@@ -361,6 +409,7 @@ private:
     Param param_;
     std::vector<DtypeComb> combs_;
     atb_b200_pa_plan *plan_ = nullptr;
+    std::vector<int32_t> effectiveLens_; // contextLens with the sequences batchRunStatus switches off set to 0
     atb_b200_pa_desc desc_{};
     void *scratch_[2] = {nullptr, nullptr};
     uint64_t scratchElems_[2] = {0, 0};

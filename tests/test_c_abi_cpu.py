@@ -234,6 +234,48 @@ def test_setup_checks_and_plan_without_gpu(monkeypatch):
     _expect(capi.ERROR_INVALID_TENSOR_SIZE, op.setup, bad, outs, ctx)
 
 
+def test_batch_run_status_switches_sequences_off(monkeypatch):
+    """Dynamic batch (batchRunStatusEnable): one more host tensor after contextLens; a sequence whose status is
+    0 is planned as empty.  The plan is observed through the workspace size (split-KV partials need room)."""
+    monkeypatch.setenv("ATB_B200_SM_COUNT", "148")
+    T = capi.atb_tensor
+    ctx = capi.Context()
+    long_lens = np.array([5, 40000, 40000], dtype=np.int32)
+    ins, outs, _ = _pa_tensors(maxb=320, nb=1024, lens=long_lens)
+    plain = capi.Operation(_pa_param())
+    ws_all = plain.setup(ins, outs, ctx)
+    ins0, _, _ = _pa_tensors(maxb=320, nb=1024, lens=np.array([5, 0, 0], dtype=np.int32))
+    ws_first_only = capi.Operation(_pa_param()).setup(ins0, outs, ctx)
+    assert ws_first_only < ws_all
+
+    op = capi.Operation(_pa_param(batchRunStatusEnable=True))
+    assert op.input_num == 6
+    status = np.array([1, 0, 0], dtype=np.int32)
+    with_status = ins + [T(dtype=capi.ACL_INT32, shape=(3,), device_ptr=0x1000, host=status)]
+    assert op.infer_shape(with_status, 1) == [(3, 8, 128)]
+    assert op.setup(with_status, outs, ctx) == ws_first_only
+    status[:] = 1
+    assert op.setup(with_status, outs, ctx) == ws_all
+    # the status tensor must carry host data, one value per query token
+    bad = ins + [T(dtype=capi.ACL_INT32, shape=(3,), device_ptr=0x1000)]
+    _expect(capi.ERROR_INVALID_PARAM, op.setup, bad, outs, ctx)
+    bad = ins + [T(dtype=capi.ACL_INT32, shape=(2,), device_ptr=0x1000, host=status[:2].copy())]
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, bad, outs, ctx)
+    _expect(capi.ERROR_INVALID_IN_TENSOR_NUM, op.setup, ins, outs, ctx)
+    # the control tensors may describe more sequences than there are query tokens, never fewer
+    lens5 = np.array([5, 40000, 40000, 7, 9], dtype=np.int32)
+    more = list(with_status)
+    more[3] = T(dtype=capi.ACL_INT32, shape=(5, 320), device_ptr=0x1000)
+    more[4] = T(dtype=capi.ACL_INT32, shape=(5,), device_ptr=0x1000, host=lens5)
+    assert op.setup(more, outs, ctx) == ws_all
+    fewer = list(with_status)
+    fewer[4] = T(dtype=capi.ACL_INT32, shape=(2,), device_ptr=0x1000, host=lens5[:2].copy())
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, fewer, outs, ctx)
+    # with the int8 cache the scales follow the status tensor
+    q8 = capi.Operation(_pa_param(batchRunStatusEnable=True, quantType=1))
+    assert q8.input_num == 8
+
+
 def test_execute_contract_without_gpu(monkeypatch):
     monkeypatch.setenv("ATB_B200_SM_COUNT", "148")
     op = capi.Operation(_pa_param())
