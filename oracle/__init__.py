@@ -7,3 +7,4 @@ tests/apitest/kernelstest/mix/test_reshape_and_cache.py:45-68 of the reference) 
 against outputs of those Python functions stored under tests/golden/.
 """
 from .oracle import build, load, paged_attention, reshape_and_cache, num_threads  # noqa: F401
+from . import cache_ops  # noqa: F401

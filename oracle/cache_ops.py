@@ -1,0 +1,53 @@
+"""CPU oracle of the cache-management siblings of ReshapeAndCache (test infrastructure only).
+
+Pure byte movement, restated in numpy from the reference's CPU goldens:
+  block_copy         tests/apitest/kernelstest/mix/test_blockcopy.py:65-81  (TestBlockCopy.golden_calc)
+  paged_cache_load   tests/apitest/kernelstest/mix/test_paged_cache_load_nd.py:67-110
+                     (generate_test_data), with the device kernel's row placement
+                     (src/kernels/mixkernels/paged_cache_load/op_kernel/paged_cache_load_nd.cpp:139-160):
+                     token j of sequence i always lands in row start_i + j.
+  reshape_and_cache_with_stride   the same scatter as ReshapeAndCache
+                     (tests/apitest/kernelstest/mix/test_reshape_and_cache.py:45-68) over strided views
+Pinned against outputs of those reference functions stored under tests/golden/.
+"""
+import numpy as np
+
+
+def block_copy(k_cache, v_cache, src_blocks, dst_blocks, cum_sum):
+    """In place: source block i is copied to the destination blocks dst[cum[i-1]:cum[i]] (cum is the
+    running total of destinations per source), in source order, as the golden does."""
+    start = 0
+    for i, src in enumerate(np.asarray(src_blocks)):
+        end = int(cum_sum[i])
+        for j in range(start, end):
+            dst = int(dst_blocks[j])
+            k_cache[dst] = k_cache[int(src)].copy()
+            if v_cache is not None:
+                v_cache[dst] = v_cache[int(src)].copy()
+        start = end
+    return k_cache, v_cache
+
+
+def paged_cache_load(k_cache, v_cache, block_tables, context_lens, key_out, value_out, seq_starts=None,
+                     cumulative=False):
+    """Gathers the cached tokens of every sequence back into contiguous rows (the reverse of
+    ReshapeAndCache).  context_lens holds lengths [B], or with `cumulative` the running totals [B+1];
+    seq_starts (tokens, used in whole blocks) offsets each sequence's walk through its block table.
+    Rows whose block id is negative are left untouched."""
+    block_size = k_cache.shape[1]
+    lens = np.asarray(context_lens).astype(np.int64)
+    if cumulative:
+        starts, ends = lens[:-1], lens[1:]
+    else:
+        ends = np.cumsum(lens)
+        starts = ends - lens
+    for i in range(len(starts)):
+        table_off = 0 if seq_starts is None else int(seq_starts[i]) // block_size
+        for j in range(int(ends[i] - starts[i])):
+            blk = int(block_tables[i, table_off + j // block_size])
+            if blk < 0:
+                continue
+            key_out[starts[i] + j] = k_cache[blk, j % block_size]
+            if v_cache is not None:
+                value_out[starts[i] + j] = v_cache[blk, j % block_size]
+    return key_out, value_out

@@ -68,3 +68,64 @@ def rac_inputs(spec):
         return _wl.encode(rng.standard_normal((n, h, d), dtype=np.float32), spec["dtype"])
 
     return {"key": gen(spec["dk"]), "value": gen(spec["dv"]), "slot_mapping": slots}
+
+
+# ------------------------------------------------------------------ cache-management siblings
+
+GOLDEN_BLOCKCOPY_CASES = [
+    dict(name="fp16_small", blocks=15, block_size=2, heads=2, d=2, n_src=3, n_dst=10, dtype="fp16", seed=301),
+    dict(name="bf16_mid", blocks=40, block_size=16, heads=3, d=24, n_src=7, n_dst=19, dtype="bf16", seed=302),
+    dict(name="int8_one_to_one", blocks=24, block_size=8, heads=2, d=20, n_src=6, n_dst=6, dtype="int8", seed=303),
+]
+
+
+def blockcopy_inputs(spec):
+    """Seeded BlockCopy inputs as the reference test draws them (tests/apitest/kernelstest/mix/
+    test_blockcopy.py:17-55): destinations are distinct blocks that are not sources, cumSum is a
+    sorted running total ending at the number of destinations."""
+    rng = np.random.default_rng(spec["seed"])
+    shape = (spec["blocks"], spec["block_size"], spec["heads"], spec["d"])
+
+    def gen():
+        if spec["dtype"] == "int8":
+            return rng.integers(-127, 128, size=shape, dtype=np.int8)
+        return _wl.encode(rng.standard_normal(shape, dtype=np.float32), spec["dtype"])
+
+    src = rng.integers(0, spec["blocks"], size=spec["n_src"]).astype(np.int32)
+    free = np.setdiff1d(np.arange(spec["blocks"]), src)
+    dst = rng.choice(free, size=spec["n_dst"], replace=False).astype(np.int32)
+    inner = np.sort(rng.choice(np.arange(1, spec["n_dst"]), size=spec["n_src"] - 1, replace=False))
+    cum = np.append(inner, spec["n_dst"]).astype(np.int32)
+    return {"k_cache": gen(), "v_cache": gen(), "src": src, "dst": dst, "cum": cum}
+
+
+GOLDEN_PCL_CASES = [
+    dict(name="fp16_cumsum_starts", batch=5, heads=3, dk=40, dv=24, block_size=16, blocks=20, max_len=70,
+         dtype="fp16", cumulative=True, starts=True, seed=311),
+    dict(name="bf16_cumsum_starts", batch=3, heads=1, dk=144, dv=128, block_size=128, blocks=6, max_len=200,
+         dtype="bf16", cumulative=True, starts=True, seed=312),
+    dict(name="int8_cumsum_starts", batch=6, heads=4, dk=32, dv=32, block_size=8, blocks=30, max_len=50,
+         dtype="int8", cumulative=True, starts=True, seed=313),
+]
+
+
+def pcl_inputs(spec):
+    """Seeded PagedCacheLoad inputs shaped like the reference test's (tests/apitest/kernelstest/mix/
+    test_paged_cache_load_nd.py:25-63): random block tables with four spare columns, cumulative
+    lengths, sequence starts of 0..4 whole blocks."""
+    rng = np.random.default_rng(spec["seed"])
+    bs = spec["block_size"]
+
+    def gen(d):
+        shape = (spec["blocks"], bs, spec["heads"], d)
+        if spec["dtype"] == "int8":
+            return rng.integers(-127, 128, size=shape, dtype=np.int8)
+        return _wl.encode(rng.standard_normal(shape, dtype=np.float32), spec["dtype"])
+
+    lens = rng.integers(1, spec["max_len"] + 1, size=spec["batch"])
+    cols = (int(lens.max()) + bs - 1) // bs + 4
+    tables = rng.integers(0, spec["blocks"], size=(spec["batch"], cols)).astype(np.int32)
+    starts = (rng.integers(0, 5, size=spec["batch"]) * bs).astype(np.int32)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    return {"k_cache": gen(spec["dk"]), "v_cache": gen(spec["dv"]), "block_tables": tables, "cu_lens": cu,
+            "lens": lens.astype(np.int32), "seq_starts": starts}

@@ -10,6 +10,8 @@ It imports, unmodified, the golden functions of the reference test-suite
   tests/apitest/opstest/python/operations/paged_attention/test_paged_attention_operation_mla.py
       (TestPagedAttentionMLA: same functions for the combined K/V cache)
   tests/apitest/kernelstest/mix/test_reshape_and_cache.py        (generate_test_data)
+  tests/apitest/kernelstest/mix/test_blockcopy.py                (TestBlockCopy.golden_calc)
+  tests/apitest/kernelstest/mix/test_paged_cache_load_nd.py      (TestPagedCacheLoad.generate_test_data)
 with the NPU-only imports (`torch_npu`, `op_test`, `operation_test`) replaced by empty stubs, feeds
 them this repository's seeded inputs, and stores the outputs as small .npz files.  The inputs are
 not stored: they are regenerated from the seed and checked against the stored SHA-256.
@@ -28,7 +30,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, HERE)
 
-from golden_cases import GOLDEN_PA_CASES, GOLDEN_RAC_CASES, load_workloads, rac_inputs  # noqa: E402
+from golden_cases import (GOLDEN_BLOCKCOPY_CASES, GOLDEN_PA_CASES, GOLDEN_PCL_CASES, GOLDEN_RAC_CASES,  # noqa: E402
+                          blockcopy_inputs, load_workloads, pcl_inputs, rac_inputs)
 
 wl = load_workloads()
 
@@ -148,6 +151,39 @@ def run_rac_case(rac_mod, spec):
             "input_sha256": np.frombuffer(digest(inp).encode(), dtype=np.uint8)}
 
 
+def _as_ref_values(a, dtype):
+    """The reference tests hold bf16 data as float32 values; fp16 / int8 as they are."""
+    return wl.to_f32(a, dtype) if dtype == "bf16" else a
+
+
+def run_blockcopy_case(mod, spec):
+    inp = blockcopy_inputs(spec)
+    t = mod.TestBlockCopy()
+    t.kCache = _as_ref_values(inp["k_cache"], spec["dtype"]).copy()
+    t.vCache = _as_ref_values(inp["v_cache"], spec["dtype"]).copy()
+    idx = [torch.from_numpy(inp[k]) for k in ("src", "dst", "cum")]
+    kexp, vexp = t.golden_calc([None, None] + idx)
+    if spec["dtype"] == "bf16":
+        kexp, vexp = wl.f32_to_bf16_bits(kexp), wl.f32_to_bf16_bits(vexp)
+    return {"k_cache": kexp, "v_cache": vexp, "input_sha256": np.frombuffer(digest(inp).encode(), dtype=np.uint8)}
+
+
+def run_pcl_case(mod, spec):
+    inp = pcl_inputs(spec)
+    t = mod.TestPagedCacheLoad()
+    t.num_tokens, t.num_heads = spec["batch"], spec["heads"]
+    t.head_size_k, t.head_size_v = spec["dk"], spec["dv"]
+    t.block_size, t.num_blocks = spec["block_size"], spec["blocks"]
+    t.dtype = {"fp16": "float16", "bf16": "bfloat16", "int8": "int8"}[spec["dtype"]]
+    t.key_cache = _as_ref_values(inp["k_cache"], spec["dtype"])
+    t.value_cache = _as_ref_values(inp["v_cache"], spec["dtype"])
+    t.block_tables, t.context_lens, t.seq_starts = inp["block_tables"], inp["cu_lens"], inp["seq_starts"]
+    kexp, vexp = t.generate_test_data()
+    if spec["dtype"] == "bf16":
+        kexp, vexp = wl.f32_to_bf16_bits(kexp), wl.f32_to_bf16_bits(vexp)
+    return {"key": kexp, "value": vexp, "input_sha256": np.frombuffer(digest(inp).encode(), dtype=np.uint8)}
+
+
 def main():
     if len(sys.argv) < 2:
         sys.exit("usage: make_golden.py /path/to/ascend-transformer-boost")
@@ -162,7 +198,17 @@ def main():
     rac = _load(os.path.join(kt, "mix/test_reshape_and_cache.py"), "ref_rac")
     mla = _load(os.path.join(ref_root, "tests/apitest/opstest/python/operations/paged_attention/"
                                        "test_paged_attention_operation_mla.py"), "ref_pa_mla")
+    blockcopy = _load(os.path.join(kt, "mix/test_blockcopy.py"), "ref_blockcopy")
+    pcl = _load(os.path.join(kt, "mix/test_paged_cache_load_nd.py"), "ref_pcl")
     os.chdir(cwd)
+    for spec in GOLDEN_BLOCKCOPY_CASES:
+        np.savez_compressed(os.path.join(HERE, f"blockcopy_{spec['name']}.npz"), **run_blockcopy_case(blockcopy, spec))
+        print("wrote blockcopy", spec["name"])
+    for spec in GOLDEN_PCL_CASES:
+        np.savez_compressed(os.path.join(HERE, f"pcl_{spec['name']}.npz"), **run_pcl_case(pcl, spec))
+        print("wrote pcl", spec["name"])
+    if "--siblings-only" in sys.argv:
+        return
     for case in GOLDEN_PA_CASES:
         res = run_pa_case(ref_root, case, common.TestPagedAttention, mla.TestPagedAttentionMLA)
         np.savez_compressed(os.path.join(HERE, f"pa_{case.name}.npz"), **res)

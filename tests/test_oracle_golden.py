@@ -68,3 +68,40 @@ def test_oracle_skips_empty_sequences():
     oracle.paged_attention(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], d["context_lens"],
                            case.qk_scale, "fp16", out=out)
     assert np.all(out[0] == 7.0) and np.all(out[2] == 7.0) and not np.all(out[1] == 7.0)
+
+
+# ------------------------------------------------------------------ cache-management siblings (bit-exact)
+
+from golden_cases import GOLDEN_BLOCKCOPY_CASES, GOLDEN_PCL_CASES, blockcopy_inputs, pcl_inputs  # noqa: E402
+
+
+def _bits(a):
+    return a.view(np.uint16) if a.dtype == np.float16 else a
+
+
+@pytest.mark.parametrize("spec", GOLDEN_BLOCKCOPY_CASES, ids=lambda s: s["name"])
+def test_block_copy_oracle_matches_reference_golden(spec):
+    fx = np.load(os.path.join(HERE, f"blockcopy_{spec['name']}.npz"))
+    inp = blockcopy_inputs(spec)
+    assert _digest(inp) == bytes(fx["input_sha256"]).decode(), "seeded inputs changed; regenerate the fixtures"
+    k, v = oracle.cache_ops.block_copy(inp["k_cache"].copy(), inp["v_cache"].copy(), inp["src"], inp["dst"], inp["cum"])
+    assert np.array_equal(_bits(k), _bits(fx["k_cache"])) and np.array_equal(_bits(v), _bits(fx["v_cache"]))
+    assert not np.array_equal(_bits(k), _bits(inp["k_cache"]))          # the case does move data
+
+
+@pytest.mark.parametrize("spec", GOLDEN_PCL_CASES, ids=lambda s: s["name"])
+def test_paged_cache_load_oracle_matches_reference_golden(spec):
+    fx = np.load(os.path.join(HERE, f"pcl_{spec['name']}.npz"))
+    inp = pcl_inputs(spec)
+    assert _digest(inp) == bytes(fx["input_sha256"]).decode(), "seeded inputs changed; regenerate the fixtures"
+    total = int(inp["cu_lens"][-1])
+    key = np.zeros((total,) + inp["k_cache"].shape[2:], dtype=inp["k_cache"].dtype)
+    value = np.zeros((total,) + inp["v_cache"].shape[2:], dtype=inp["v_cache"].dtype)
+    oracle.cache_ops.paged_cache_load(inp["k_cache"], inp["v_cache"], inp["block_tables"], inp["cu_lens"], key, value,
+                                      seq_starts=inp["seq_starts"], cumulative=True)
+    assert np.array_equal(_bits(key), _bits(fx["key"])) and np.array_equal(_bits(value), _bits(fx["value"]))
+    # lengths instead of running totals give the same rows
+    key2, value2 = np.zeros_like(key), np.zeros_like(value)
+    oracle.cache_ops.paged_cache_load(inp["k_cache"], inp["v_cache"], inp["block_tables"], inp["lens"], key2, value2,
+                                      seq_starts=inp["seq_starts"], cumulative=False)
+    assert np.array_equal(_bits(key2), _bits(key)) and np.array_equal(_bits(value2), _bits(value))
