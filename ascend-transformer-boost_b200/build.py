@@ -9,9 +9,9 @@ CSRC = os.path.join(PKG, "csrc")
 OUT = os.path.join(PKG, "libatb_b200.so")
 
 CU_SOURCES = ["reshape_and_cache.cu", "pa_generic.cu", "pa_combine.cu", "pa_tma_mma.cu", "atb_scale_convert.cu",
-              "pa_noalloc.cu", "pa_tma_mma_i8.cu", "pa_mla_tc5.cu", "pa_exchange.cu"]
+              "pa_noalloc.cu", "pa_tma_mma_i8.cu", "pa_mla_tc5.cu", "pa_exchange.cu", "cache_ops.cu"]
 CPP_SOURCES = ["pa_planner.cpp", "c_api.cpp", "atb_operation_base.cpp", "atb_paged_attention.cpp",
-               "atb_reshape_and_cache.cpp", "atb_c_wrappers.cpp"]
+               "atb_reshape_and_cache.cpp", "atb_c_wrappers.cpp", "atb_cache_ops.cpp"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=default", "--expt-relaxed-constexpr",
@@ -77,6 +77,31 @@ def build_cpp_test():
         return exe
     subprocess.check_call([nvcc, "-std=c++17", "-O2", "-Wno-deprecated-gpu-targets", "-I" + os.path.join(ROOT, "include"),
                            "-x", "cu", src, "-o", exe, "-L" + PKG, "-latb_b200", "-Xlinker", "-rpath=" + PKG])
+    return exe
+
+
+def build_host_emulation():
+    """Compiles tests/cpp/cache_ops_host_emulation.cpp with g++: the bodies of the cache-management
+    kernels run on the CPU so that the tests can compare them with the oracle and the golden fixtures."""
+    src = os.path.join(ROOT, "tests", "cpp", "cache_ops_host_emulation.cpp")
+    body = os.path.join(CSRC, "cache_ops_body.h")
+    so = os.path.join(ROOT, "tests", "cpp", "libcache_ops_host_emulation.so")
+    if os.path.exists(so) and os.path.getmtime(so) > max(os.path.getmtime(src), os.path.getmtime(body)):
+        return so
+    subprocess.check_call(["g++", "-std=c++17", "-O1", "-g", "-shared", "-fPIC", src, "-o", so])
+    return so
+
+
+def build_body_selftest():
+    """Compiles tests/cpp/cache_ops_body_selftest.cpp with AddressSanitizer and UBSan: randomized and
+    adversarial cases of the same kernel bodies; an out-of-bounds access aborts the executable."""
+    src = os.path.join(ROOT, "tests", "cpp", "cache_ops_body_selftest.cpp")
+    body = os.path.join(CSRC, "cache_ops_body.h")
+    exe = os.path.join(ROOT, "tests", "cpp", "cache_ops_body_selftest")
+    if os.path.exists(exe) and os.path.getmtime(exe) > max(os.path.getmtime(src), os.path.getmtime(body)):
+        return exe
+    subprocess.check_call(["g++", "-std=c++17", "-O1", "-g", "-fsanitize=address,undefined",
+                           "-fno-sanitize-recover=all", src, "-o", exe])
     return exe
 
 

@@ -86,6 +86,17 @@ class ReshapeAndCacheParam(ctypes.Structure):
     _fields_ = [("compressType", ctypes.c_int32), ("kvCacheCfg", ctypes.c_int32), ("rsv", ctypes.c_uint8 * 16)]
 
 
+class BlockCopyParam(ctypes.Structure):
+    """Byte layout of atb::infer::BlockCopyParam (16 bytes)."""
+    _fields_ = [("rsv", ctypes.c_uint8 * 16)]
+
+
+class PagedCacheLoadParam(ctypes.Structure):
+    """Byte layout of atb::infer::PagedCacheLoadParam (64 bytes); kvCacheCfg 1 = ND caches."""
+    _fields_ = [("kvCacheCfg", ctypes.c_int8), ("isSeqLensCumsumMode", ctypes.c_bool), ("hasSeqStarts", ctypes.c_bool),
+                ("rsv", ctypes.c_uint8 * 61)]
+
+
 # every symbol include/atb_b200.h declares
 EXPORTS = [
     "atb_b200_pa_plan_create", "atb_b200_pa_plan_update", "atb_b200_pa_plan_get_info", "atb_b200_pa_plan_dump",
@@ -98,6 +109,8 @@ EXPORTS = [
     "atb_b200_pa_decode_static_scratch", "atb_b200_pa_launch_gathered", "atb_b200_peer_buffer_create",
     "atb_b200_peer_buffer_open", "atb_b200_peer_buffer_close", "atb_b200_peer_buffer_destroy",
     "atb_b200_pa_plan_set_trace", "atb_b200_pa_plan_prefetch", "atb_b200_operation_name",
+    "atb_b200_block_copy", "atb_b200_paged_cache_load", "atb_b200_paged_cache_load_workspace_bytes",
+    "atb_b200_operation_create_block_copy", "atb_b200_operation_create_paged_cache_load",
 ]
 
 _lib = None
@@ -128,6 +141,8 @@ def lib():
         L.atb_b200_context_destroy.argtypes = [vp]
         L.atb_b200_operation_create_paged_attention.argtypes = [vp, u64, P(vp)]
         L.atb_b200_operation_create_reshape_and_cache.argtypes = [vp, u64, P(vp)]
+        L.atb_b200_operation_create_block_copy.argtypes = [vp, u64, P(vp)]
+        L.atb_b200_operation_create_paged_cache_load.argtypes = [vp, u64, P(vp)]
         L.atb_b200_operation_input_num.argtypes = [vp, P(u32)]
         L.atb_b200_operation_output_num.argtypes = [vp, P(u32)]
         L.atb_b200_operation_infer_shape.argtypes = [vp, P(AtbTensor), u32, P(AtbTensor), u32]
@@ -144,6 +159,11 @@ def lib():
         L.atb_b200_peer_buffer_destroy.argtypes = [vp]
         L.atb_b200_pa_plan_set_trace.argtypes = [vp, vp, u32]
         L.atb_b200_pa_plan_prefetch.argtypes = [vp, vp]
+        L.atb_b200_block_copy.argtypes = [vp, vp, vp, vp, vp, i32, i32, i64, i64, i64, vp]
+        L.atb_b200_paged_cache_load_workspace_bytes.argtypes = [i32, i32]
+        L.atb_b200_paged_cache_load_workspace_bytes.restype = u64
+        L.atb_b200_paged_cache_load.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i32, vp,
+                                                u64, vp]
         _lib = L
     return _lib
 
@@ -309,6 +329,31 @@ def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping):
            "atb_b200_reshape_and_cache")
 
 
+def block_copy(k_cache, v_cache, src_blocks, dst_blocks, cum_sum, stream_ptr=None):
+    """In place on torch CUDA tensors: caches [blocks, block_size, heads, D]; int32 index tensors on the device."""
+    kb = k_cache[0].numel() * k_cache.element_size()
+    vb = v_cache[0].numel() * v_cache.element_size() if v_cache is not None else 0
+    _check(lib().atb_b200_block_copy(_ptr(k_cache), _ptr(v_cache), _ptr(src_blocks), _ptr(dst_blocks), _ptr(cum_sum),
+                                     src_blocks.numel(), dst_blocks.numel(), kb, vb, k_cache.shape[0],
+                                     stream_ptr if stream_ptr is not None else torch_stream_ptr()), "atb_b200_block_copy")
+
+
+def paged_cache_load(k_cache, v_cache, block_tables, context_lens, key, value, seq_starts=None, cumulative=False,
+                     stream_ptr=None):
+    """Gathers cached tokens into key / value ([rows, heads, D] torch CUDA tensors)."""
+    import torch
+    batch = context_lens.numel() - (1 if cumulative else 0)
+    ws_bytes = lib().atb_b200_paged_cache_load_workspace_bytes(batch, int(cumulative))
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=key.device)
+    _check(lib().atb_b200_paged_cache_load(
+        _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(context_lens), _ptr(seq_starts), _ptr(key), _ptr(value),
+        batch, block_tables.shape[1], k_cache.shape[1], k_cache[0, 0].numel() * k_cache.element_size(),
+        v_cache[0, 0].numel() * v_cache.element_size() if v_cache is not None else 0, k_cache.shape[0], key.shape[0],
+        int(cumulative), ws.data_ptr(), ws_bytes, stream_ptr if stream_ptr is not None else torch_stream_ptr()),
+        "atb_b200_paged_cache_load")
+    return ws
+
+
 class PeerExchange:
     """Gathered-output buffers and flag arrays shared by the ranks of a node over CUDA IPC.
 
@@ -449,6 +494,10 @@ class Operation:
         self.handle = ctypes.c_void_p()
         if isinstance(param, PagedAttentionParam):
             fn, what = lib().atb_b200_operation_create_paged_attention, "CreateOperation(PagedAttentionParam)"
+        elif isinstance(param, BlockCopyParam):
+            fn, what = lib().atb_b200_operation_create_block_copy, "CreateOperation(BlockCopyParam)"
+        elif isinstance(param, PagedCacheLoadParam):
+            fn, what = lib().atb_b200_operation_create_paged_cache_load, "CreateOperation(PagedCacheLoadParam)"
         else:
             fn, what = lib().atb_b200_operation_create_reshape_and_cache, "CreateOperation(ReshapeAndCacheParam)"
         _check(fn(ctypes.byref(param), ctypes.sizeof(param), ctypes.byref(self.handle)), what)

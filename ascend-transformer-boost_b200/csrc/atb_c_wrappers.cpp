@@ -86,6 +86,32 @@ int atb_b200_operation_create_reshape_and_cache(const void *param, uint64_t para
     return st;
 }
 
+int atb_b200_operation_create_block_copy(const void *param, uint64_t param_bytes, void **operation)
+{
+    if (param == nullptr || operation == nullptr || param_bytes != sizeof(infer::BlockCopyParam)) {
+        return ERROR_INVALID_PARAM;
+    }
+    infer::BlockCopyParam p;
+    std::memcpy(&p, param, sizeof(p));
+    Operation *op = nullptr;
+    Status st = CreateOperation(p, &op);
+    *operation = op;
+    return st;
+}
+
+int atb_b200_operation_create_paged_cache_load(const void *param, uint64_t param_bytes, void **operation)
+{
+    if (param == nullptr || operation == nullptr || param_bytes != sizeof(infer::PagedCacheLoadParam)) {
+        return ERROR_INVALID_PARAM;
+    }
+    infer::PagedCacheLoadParam p;
+    std::memcpy(&p, param, sizeof(p));
+    Operation *op = nullptr;
+    Status st = CreateOperation(p, &op);
+    *operation = op;
+    return st;
+}
+
 int atb_b200_operation_input_num(void *operation, uint32_t *n)
 {
     if (operation == nullptr || n == nullptr) {

@@ -1,0 +1,290 @@
+// atb::CreateOperation<infer::BlockCopyParam> and <infer::PagedCacheLoadParam>: the cache-management
+// operations next to ReshapeAndCache.  Checks follow the reference:
+//   BlockCopy       src/ops/ops_infer/block_copy/block_copy_operation.cpp (CreateOperation :29-46,
+//                   GetInputNum/GetOutputNum :58-67, InferShapeCheckImpl :69-95, SetupCheckImpl :105-150)
+//   PagedCacheLoad  src/ops/ops_infer/paged_cache_load/paged_cache_load_operation.cpp (CreateOperation :51-77,
+//                   GetInputNum :95-102, InferShapeImpl :109-115, SetupCheckImpl :122-146, DimCheck :149-196,
+//                   KVCacheDimCheck910BND :252-297)
+// The fractal-NZ cache layout of PagedCacheLoad belongs to other hardware and is rejected.
+#include <new>
+#include "../../include/atb_b200.h"
+#include "atb_operation_base.h"
+
+namespace atb {
+namespace {
+
+uint64_t ElemSize(aclDataType t) { return t == ACL_INT8 ? 1 : 2; }
+
+bool ShapeEqual(const Dims &a, const Dims &b)
+{
+    if (a.dimNum != b.dimNum) {
+        return false;
+    }
+    for (uint64_t i = 0; i < a.dimNum; ++i) {
+        if (a.dims[i] != b.dims[i]) {
+            return false;
+        }
+    }
+    return true;
+}
+
+// ---------------------------------------------------------------------------------------------------
+class BlockCopyOperation : public OperationBase {
+public:
+    explicit BlockCopyOperation(const infer::BlockCopyParam &p) : OperationBase("BlockCopyOperation"), param_(p)
+    {
+        for (aclDataType t : {ACL_FLOAT16, ACL_BF16, ACL_INT8}) {
+            combs_.push_back({t, t, ACL_INT32, ACL_INT32, ACL_INT32});
+        }
+    }
+    uint32_t GetInputNum() const override { return 5; } // keyCache, valueCache, srcBlockIndices, dstBlockIndices, cumSum
+    uint32_t GetOutputNum() const override { return 0; } // the caches are updated in place
+
+protected:
+    const std::vector<DtypeComb> &DtypeCombs() const override { return combs_; }
+
+    Status InferShapeCheckImpl(const SVector<TensorDesc> &in) const override
+    {
+        const int64_t blockCount = in.at(0).shape.dims[0];
+        if (!ShapeEqual(in.at(0).shape, in.at(1).shape)) {
+            ATB_B200_LOG(ERROR, "BlockCopy: kCache shape is not equal vCache shape");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (in.at(0).shape.dimNum != 4) {
+            ATB_B200_LOG(ERROR, "BlockCopy: cache shape is not 4");
+            return ERROR_INVALID_TENSOR_DIM_NUM;
+        }
+        if (in.at(2).shape.dimNum != 1 || in.at(3).shape.dimNum != 1) {
+            ATB_B200_LOG(ERROR, "BlockCopy: indices shape is not 1");
+            return ERROR_INVALID_TENSOR_DIM_NUM;
+        }
+        if (!ShapeEqual(in.at(4).shape, in.at(2).shape)) {
+            ATB_B200_LOG(ERROR, "BlockCopy: cumSum shape is not equal srcBlockIndices shape");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (in.at(2).shape.dims[0] > blockCount || in.at(3).shape.dims[0] > blockCount) {
+            ATB_B200_LOG(ERROR, "BlockCopy: indices shape[0] is greater than blockCount");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        return NO_ERROR;
+    }
+
+    Status InferShapeImpl(const SVector<TensorDesc> &, SVector<TensorDesc> &) const override { return NO_ERROR; }
+
+    Status SetupCheckImpl(const SVector<Tensor> &inTensors, const SVector<Tensor> &) const override
+    {
+        SVector<TensorDesc> descs;
+        for (size_t i = 0; i < inTensors.size(); ++i) {
+            descs.push_back(inTensors.at(i).desc);
+        }
+        Status st = InferShapeCheckImpl(descs);
+        if (st != NO_ERROR) {
+            return st;
+        }
+        if (!TensorDescEqual(descs.at(0), descs.at(1))) {
+            ATB_B200_LOG(ERROR, "BlockCopy: kCache desc is not equal vCache desc");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (descs.at(0).format != ACL_FORMAT_ND || descs.at(1).format != ACL_FORMAT_ND) {
+            return ERROR_INVALID_TENSOR_FORMAT;
+        }
+        return NO_ERROR;
+    }
+
+    Status PlanImpl(const VariantPack &, uint64_t &workspaceSize) override
+    {
+        workspaceSize = 0;
+        return NO_ERROR;
+    }
+
+    Status LaunchImpl(const VariantPack &vp, uint8_t *, uint64_t, aclrtStream stream) override
+    {
+        const Tensor &kc = vp.inTensors.at(0), &vc = vp.inTensors.at(1);
+        const Tensor &src = vp.inTensors.at(2), &dst = vp.inTensors.at(3), &cum = vp.inTensors.at(4);
+        if (kc.deviceData == nullptr || vc.deviceData == nullptr || src.deviceData == nullptr ||
+            dst.deviceData == nullptr || cum.deviceData == nullptr) {
+            return ERROR_INVALID_PARAM;
+        }
+        const Dims &s = kc.desc.shape;
+        const int64_t blockBytes = s.dims[1] * s.dims[2] * s.dims[3] * static_cast<int64_t>(ElemSize(kc.desc.dtype));
+        const int rc = atb_b200_block_copy(kc.deviceData, vc.deviceData, static_cast<const int32_t *>(src.deviceData),
+                                           static_cast<const int32_t *>(dst.deviceData),
+                                           static_cast<const int32_t *>(cum.deviceData),
+                                           static_cast<int32_t>(src.desc.shape.dims[0]),
+                                           static_cast<int32_t>(dst.desc.shape.dims[0]), blockBytes, blockBytes, s.dims[0],
+                                           stream);
+        return rc == 0 ? NO_ERROR : (rc == ERROR_INVALID_PARAM ? ERROR_INVALID_PARAM : ERROR_RT_FAIL);
+    }
+
+private:
+    infer::BlockCopyParam param_;
+    std::vector<DtypeComb> combs_;
+};
+
+// ---------------------------------------------------------------------------------------------------
+class PagedCacheLoadOperation : public OperationBase {
+public:
+    using Param = infer::PagedCacheLoadParam;
+    explicit PagedCacheLoadOperation(const Param &p) : OperationBase("PagedCacheLoadOperation"), param_(p)
+    {
+        for (aclDataType t : {ACL_FLOAT16, ACL_BF16, ACL_INT8}) {
+            // keyCache, valueCache, blockTables, contextLens, key, value, seqStarts -> key, value
+            combs_.push_back({t, t, ACL_INT32, ACL_INT32, t, t, ACL_INT32, t, t});
+        }
+    }
+    uint32_t GetInputNum() const override { return 7; }
+    uint32_t GetOutputNum() const override { return 2; }
+
+protected:
+    const std::vector<DtypeComb> &DtypeCombs() const override { return combs_; }
+
+    Status InferShapeCheckImpl(const SVector<TensorDesc> &in) const override
+    {
+        if (in.at(0).shape.dimNum != 4 || in.at(1).shape.dimNum != 4 || in.at(2).shape.dimNum != 2 ||
+            in.at(3).shape.dimNum != 1 || in.at(4).shape.dimNum != 3 || in.at(5).shape.dimNum != 3 ||
+            in.at(6).shape.dimNum != 1) {
+            ATB_B200_LOG(ERROR, "PagedCacheLoad: invalid intensor dimNum");
+            return ERROR_INVALID_TENSOR_DIM_NUM;
+        }
+        const Dims &kc = in.at(0).shape, &vc = in.at(1).shape;
+        if (kc.dims[0] != vc.dims[0]) {
+            ATB_B200_LOG(ERROR, "PagedCacheLoad: numBlocks should be same");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (in.at(4).shape.dims[0] != in.at(5).shape.dims[0]) {
+            ATB_B200_LOG(ERROR, "PagedCacheLoad: sumcontextlens should be same");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (kc.dims[1] != vc.dims[1]) {
+            ATB_B200_LOG(ERROR, "PagedCacheLoad: blockSizes should be same");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (kc.dims[2] != vc.dims[2]) {
+            ATB_B200_LOG(ERROR, "PagedCacheLoad: numHeads should be same");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (kc.dims[1] == 0) {
+            ATB_B200_LOG(ERROR, "PagedCacheLoad: blockSize cannot be zero");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        const int64_t batch = in.at(2).shape.dims[0];
+        if (in.at(3).shape.dims[0] != batch + (param_.isSeqLensCumsumMode ? 1 : 0)) {
+            ATB_B200_LOG(ERROR, "PagedCacheLoad: the rows of blockTables should match the length of SeqLens");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        const int64_t alignK = in.at(0).dtype == ACL_INT8 ? 32 : 16, alignV = in.at(1).dtype == ACL_INT8 ? 32 : 16;
+        if (kc.dims[2] * kc.dims[3] % alignK != 0 || vc.dims[2] * vc.dims[3] % alignV != 0) {
+            ATB_B200_LOG(ERROR, "PagedCacheLoad: num_heads*head_size should be aligned to 16 (fp16/bf16) or 32 (int8)");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (param_.hasSeqStarts && in.at(6).shape.dims[0] != batch) {
+            ATB_B200_LOG(ERROR, "PagedCacheLoad: the length of seqStarts should match the rows of blockTables");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        return NO_ERROR;
+    }
+
+    Status InferShapeImpl(const SVector<TensorDesc> &in, SVector<TensorDesc> &out) const override
+    {
+        out.at(0) = in.at(4);
+        out.at(1) = in.at(5);
+        return NO_ERROR;
+    }
+
+    Status SetupCheckImpl(const SVector<Tensor> &inTensors, const SVector<Tensor> &outTensors) const override
+    {
+        SVector<TensorDesc> descs;
+        for (size_t i = 0; i < inTensors.size(); ++i) {
+            descs.push_back(inTensors.at(i).desc);
+        }
+        const Dims &ok = outTensors.at(0).desc.shape, &ov = outTensors.at(1).desc.shape;
+        if (ok.dimNum != 3 || ov.dimNum != 3 || descs.at(0).shape.dimNum != 4 || descs.at(1).shape.dimNum != 4 ||
+            ok.dims[1] != descs.at(0).shape.dims[2] || ok.dims[2] != descs.at(0).shape.dims[3] ||
+            ov.dims[1] != descs.at(1).shape.dims[2] || ov.dims[2] != descs.at(1).shape.dims[3]) {
+            ATB_B200_LOG(ERROR, "PagedCacheLoad: the last dimensions of outTensors need to match the caches");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        return InferShapeCheckImpl(descs);
+    }
+
+    Status PlanImpl(const VariantPack &vp, uint64_t &workspaceSize) override
+    {
+        const int32_t batch = static_cast<int32_t>(vp.inTensors.at(2).desc.shape.dims[0]);
+        workspaceSize = atb_b200_paged_cache_load_workspace_bytes(batch, param_.isSeqLensCumsumMode ? 1 : 0);
+        if (workspaceSize > 0) {
+            workspaceSize += 256; // room to align the caller's pointer
+        }
+        return NO_ERROR;
+    }
+
+    Status LaunchImpl(const VariantPack &vp, uint8_t *workspace, uint64_t workspaceSize, aclrtStream stream) override
+    {
+        const Tensor &kc = vp.inTensors.at(0), &vc = vp.inTensors.at(1), &bt = vp.inTensors.at(2);
+        const Tensor &lens = vp.inTensors.at(3), &starts = vp.inTensors.at(6);
+        const Tensor &key = vp.outTensors.at(0), &value = vp.outTensors.at(1);
+        if (kc.deviceData == nullptr || vc.deviceData == nullptr || bt.deviceData == nullptr ||
+            lens.deviceData == nullptr || key.deviceData == nullptr || value.deviceData == nullptr ||
+            (param_.hasSeqStarts && starts.deviceData == nullptr)) {
+            return ERROR_INVALID_PARAM;
+        }
+        const Dims &k = kc.desc.shape, &v = vc.desc.shape;
+        uint8_t *ws = nullptr;
+        uint64_t usable = 0;
+        if (workspace != nullptr && workspaceSize >= 256) {
+            ws = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255));
+            usable = workspaceSize - static_cast<uint64_t>(ws - workspace);
+        }
+        const int rc = atb_b200_paged_cache_load(
+            kc.deviceData, vc.deviceData, static_cast<const int32_t *>(bt.deviceData),
+            static_cast<const int32_t *>(lens.deviceData),
+            param_.hasSeqStarts ? static_cast<const int32_t *>(starts.deviceData) : nullptr, key.deviceData,
+            value.deviceData, static_cast<int32_t>(bt.desc.shape.dims[0]), static_cast<int32_t>(bt.desc.shape.dims[1]),
+            static_cast<int32_t>(k.dims[1]), k.dims[2] * k.dims[3] * static_cast<int64_t>(ElemSize(kc.desc.dtype)),
+            v.dims[2] * v.dims[3] * static_cast<int64_t>(ElemSize(vc.desc.dtype)), k.dims[0], key.desc.shape.dims[0],
+            param_.isSeqLensCumsumMode ? 1 : 0, ws, usable, stream);
+        return rc == 0 ? NO_ERROR : (rc == ERROR_INVALID_PARAM ? ERROR_INVALID_PARAM : ERROR_RT_FAIL);
+    }
+
+private:
+    Param param_;
+    std::vector<DtypeComb> combs_;
+};
+
+} // namespace
+
+template <> Status CreateOperation(const infer::BlockCopyParam &opParam, Operation **operation)
+{
+    if (operation == nullptr) {
+        return ERROR_INVALID_PARAM;
+    }
+    if (!RsvIsZero(opParam.rsv, sizeof(opParam.rsv))) {
+        ATB_B200_LOG(ERROR, "BlockCopyParam.rsv must be zero");
+        return ERROR_INVALID_PARAM;
+    }
+    *operation = new (std::nothrow) BlockCopyOperation(opParam);
+    return *operation == nullptr ? ERROR_OUT_OF_HOST_MEMORY : NO_ERROR;
+}
+
+template <> Status CreateOperation(const infer::PagedCacheLoadParam &opParam, Operation **operation)
+{
+    using Param = infer::PagedCacheLoadParam;
+    if (operation == nullptr) {
+        return ERROR_INVALID_PARAM;
+    }
+    if (!RsvIsZero(opParam.rsv, sizeof(opParam.rsv))) {
+        ATB_B200_LOG(ERROR, "PagedCacheLoadParam.rsv must be zero");
+        return ERROR_INVALID_PARAM;
+    }
+    if (opParam.kvCacheCfg < Param::K_CACHE_V_CACHE_NZ || opParam.kvCacheCfg > Param::K_CACHE_V_CACHE_ND) {
+        ATB_B200_LOG(ERROR, "wrong kvcache config");
+        return ERROR_INVALID_PARAM;
+    }
+    if (opParam.kvCacheCfg == Param::K_CACHE_V_CACHE_NZ) {
+        ATB_B200_LOG(ERROR, "PagedCacheLoad: the NZ cache layout is not supported by this build");
+        return ERROR_INVALID_PARAM;
+    }
+    *operation = new (std::nothrow) PagedCacheLoadOperation(opParam);
+    return *operation == nullptr ? ERROR_OUT_OF_HOST_MEMORY : NO_ERROR;
+}
+
+} // namespace atb

@@ -63,6 +63,30 @@ struct PagedAttentionParam {
     uint8_t rsv[64] = {0};
 };
 
+// BlockCopy: copy the cache blocks named by srcBlockIndices onto the blocks named by dstBlockIndices
+// (include/atb/infer_op_params.h:1205-1215 of the reference).  Inputs keyCache, valueCache,
+// srcBlockIndices [n], dstBlockIndices [m], cumSum [n] (running total of destinations per source);
+// no outputs, the caches are updated in place.
+struct BlockCopyParam {
+    uint8_t rsv[16] = {0};
+};
+
+// PagedCacheLoad: the reverse of ReshapeAndCache (include/atb/infer_op_params.h:3070-3100 of the
+// reference).  Inputs keyCache, valueCache, blockTables, contextLens, key, value, seqStarts; outputs
+// key, value ([sum of lengths, heads, headSize]).
+struct PagedCacheLoadParam {
+    enum KvCacheCfg : int8_t {
+        K_CACHE_V_CACHE_NZ = 0, // fractal layout of another SoC (the reference's default); rejected here
+        K_CACHE_V_CACHE_ND,     // [numBlocks, blockSize, heads, headSize] caches
+    };
+    KvCacheCfg kvCacheCfg = K_CACHE_V_CACHE_NZ;
+    bool isSeqLensCumsumMode = false; // contextLens holds running totals [batch + 1] instead of lengths
+    bool hasSeqStarts = false;        // seqStarts[i] / blockSize = first block-table column of sequence i
+    uint8_t rsv[61] = {0};
+};
+
+static_assert(sizeof(BlockCopyParam) == 16, "ABI: BlockCopyParam is 16 bytes");
+static_assert(sizeof(PagedCacheLoadParam) == 64, "ABI: PagedCacheLoadParam is 64 bytes");
 static_assert(sizeof(ReshapeAndCacheParam) == 24, "ABI: ReshapeAndCacheParam is 24 bytes");
 static_assert(sizeof(PagedAttentionParam) == 120, "ABI: PagedAttentionParam is 120 bytes");
 } // namespace infer

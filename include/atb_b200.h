@@ -233,6 +233,9 @@ int atb_b200_context_destroy(void *context);
 /* `param` points at an atb::infer::PagedAttentionParam (120 bytes) / ReshapeAndCacheParam (24 bytes). */
 int atb_b200_operation_create_paged_attention(const void *param, uint64_t param_bytes, void **operation);
 int atb_b200_operation_create_reshape_and_cache(const void *param, uint64_t param_bytes, void **operation);
+/* atb::CreateOperation<infer::BlockCopyParam> (16-byte param) and <infer::PagedCacheLoadParam> (64-byte param) */
+int atb_b200_operation_create_block_copy(const void *param, uint64_t param_bytes, void **operation);
+int atb_b200_operation_create_paged_cache_load(const void *param, uint64_t param_bytes, void **operation);
 int atb_b200_operation_input_num(void *operation, uint32_t *n);
 int atb_b200_operation_output_num(void *operation, uint32_t *n);
 /* Operation::GetName (include/atb/operation.h:46 of the reference): copies the NUL-terminated name into
@@ -245,6 +248,32 @@ int atb_b200_operation_setup(void *operation, const atb_b200_tensor *in, uint32_
 int atb_b200_operation_execute(void *operation, const atb_b200_tensor *in, uint32_t n_in, const atb_b200_tensor *out,
                                uint32_t n_out, void *workspace, uint64_t workspace_bytes, void *context);
 int atb_b200_operation_destroy(void *operation);
+
+/* ---- cache-management siblings of ReshapeAndCache (kernel level) ------------------------------------
+ *
+ * BlockCopy: copy whole cache blocks in place, replaces the BlockCopyOperation kernel of the reference
+ * (src/ops/ops_infer/block_copy/block_copy_operation.cpp:58-120, golden tests/apitest/kernelstest/mix/
+ * test_blockcopy.py:65-81).  Source block src_blocks[i] goes to the destinations
+ * dst_blocks[cum_sum[i-1] .. cum_sum[i]) (cum_sum = running total of destinations per source; all three
+ * are device int32 arrays).  v_cache may be null.  Blocks outside [0, num_blocks) are skipped.  The
+ * copies run in parallel: a block must not be both a source and a destination of one call. */
+int atb_b200_block_copy(void *k_cache, void *v_cache, const int32_t *src_blocks, const int32_t *dst_blocks,
+                        const int32_t *cum_sum, int32_t n_src, int32_t n_dst, int64_t k_block_bytes,
+                        int64_t v_block_bytes, int64_t num_blocks, void *stream);
+
+/* PagedCacheLoad (ND caches): gather every sequence's cached tokens into contiguous rows, the reverse of
+ * ReshapeAndCache; replaces src/kernels/mixkernels/paged_cache_load/op_kernel/paged_cache_load_nd.cpp:139-226
+ * of the reference.  context_lens (device int32) holds lengths [batch], or running totals [batch + 1] when
+ * lens_are_cumulative; sequence i fills rows [start_i, start_i + len_i) of key / value ([out_rows, row bytes])
+ * from the blocks block_tables[i][seq_starts[i] / block_size + t].  seq_starts may be null; v_cache and value
+ * may both be null.  Block ids, table columns and rows out of range are skipped.  With plain lengths the call
+ * needs atb_b200_paged_cache_load_workspace_bytes(batch, 0) bytes of device workspace for the running totals. */
+uint64_t atb_b200_paged_cache_load_workspace_bytes(int32_t batch, int32_t lens_are_cumulative);
+int atb_b200_paged_cache_load(const void *k_cache, const void *v_cache, const int32_t *block_tables,
+                              const int32_t *context_lens, const int32_t *seq_starts, void *key, void *value,
+                              int32_t batch, int32_t table_cols, int32_t block_size, int64_t k_row_bytes,
+                              int64_t v_row_bytes, int64_t num_blocks, int64_t out_rows, int32_t lens_are_cumulative,
+                              void *workspace, uint64_t workspace_bytes, void *stream);
 
 const char *atb_b200_version(void);
 

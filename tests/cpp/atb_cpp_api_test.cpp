@@ -99,6 +99,20 @@ static int RunCpu()
     CHECK(atb::CreateOperation(rp, &op) == atb::NO_ERROR);
     CHECK(op->GetInputNum() == 3 && op->GetOutputNum() == 1);
     CHECK(atb::DestroyOperation(op) == atb::NO_ERROR);
+    // the cache-management siblings
+    atb::infer::BlockCopyParam bp;
+    CHECK(atb::CreateOperation(bp, &op) == atb::NO_ERROR);
+    CHECK(op->GetName() == "BlockCopyOperation" && op->GetInputNum() == 5 && op->GetOutputNum() == 0);
+    CHECK(atb::DestroyOperation(op) == atb::NO_ERROR);
+    bp.rsv[0] = 1;
+    CHECK(atb::CreateOperation(bp, &op) == atb::ERROR_INVALID_PARAM);
+    atb::infer::PagedCacheLoadParam lp;
+    CHECK(atb::CreateOperation(lp, &op) == atb::ERROR_INVALID_PARAM); // default = the NZ layout of another SoC
+    lp.kvCacheCfg = atb::infer::PagedCacheLoadParam::K_CACHE_V_CACHE_ND;
+    lp.isSeqLensCumsumMode = true;
+    CHECK(atb::CreateOperation(lp, &op) == atb::NO_ERROR);
+    CHECK(op->GetName() == "PagedCacheLoadOperation" && op->GetInputNum() == 7 && op->GetOutputNum() == 2);
+    CHECK(atb::DestroyOperation(op) == atb::NO_ERROR);
     CHECK(atb::DestroyContext(ctx) == atb::NO_ERROR);
 
     atb::SVector<int> v;

@@ -1,0 +1,201 @@
+"""BlockCopy and PagedCacheLoad without a GPU: the CUDA kernels' per-thread bodies (csrc/cache_ops_body.h)
+run on the CPU over an emulated grid and must reproduce the reference goldens bit for bit; an
+AddressSanitizer build of the same bodies takes randomized and hostile inputs; the C ABI rejects bad
+arguments before any launch."""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+import oracle
+from golden_cases import (GOLDEN_BLOCKCOPY_CASES, GOLDEN_PCL_CASES, HERE as GOLDEN_DIR, blockcopy_inputs, pcl_inputs)
+from helpers import capi, pkg
+
+_emu = None
+
+
+def emu():
+    global _emu
+    if _emu is None:
+        L = ctypes.CDLL(pkg._build.build_host_emulation())
+        vp, i32, i64 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64
+        L.emu_block_copy.argtypes = [vp, vp, vp, vp, vp, i32, i32, i64, i64, i64, i32, i32]
+        L.emu_paged_cache_load.argtypes = [vp] * 7 + [i32, i32, i32, i64, i64, i64, i64, i32, vp, i32, i32]
+        _emu = L
+    return _emu
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+
+
+def _bits(a):
+    return a.view(np.uint16) if a.dtype == np.float16 else a
+
+
+def test_kernel_bodies_survive_address_sanitizer():
+    exe = pkg._build.build_body_selftest()
+    r = subprocess.run([exe, "300"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "0 failures" in r.stdout
+
+
+@pytest.mark.parametrize("chunks,threads", [(0, 4), (1, 1), (3, 5)])
+@pytest.mark.parametrize("spec", GOLDEN_BLOCKCOPY_CASES, ids=lambda s: s["name"])
+def test_block_copy_body_matches_reference_golden(spec, chunks, threads):
+    fx = np.load(os.path.join(GOLDEN_DIR, f"blockcopy_{spec['name']}.npz"))
+    inp = blockcopy_inputs(spec)
+    k, v = inp["k_cache"].copy(), inp["v_cache"].copy()
+    emu().emu_block_copy(_p(k), _p(v), _p(inp["src"]), _p(inp["dst"]), _p(inp["cum"]), len(inp["src"]), len(inp["dst"]),
+                         k[0].nbytes, v[0].nbytes, k.shape[0], chunks, threads)
+    assert np.array_equal(_bits(k), _bits(fx["k_cache"])) and np.array_equal(_bits(v), _bits(fx["v_cache"]))
+
+
+@pytest.mark.parametrize("cumulative", [True, False])
+@pytest.mark.parametrize("chunks,threads", [(0, 3), (2, 1)])
+@pytest.mark.parametrize("spec", GOLDEN_PCL_CASES, ids=lambda s: s["name"])
+def test_paged_cache_load_body_matches_reference_golden(spec, chunks, threads, cumulative):
+    fx = np.load(os.path.join(GOLDEN_DIR, f"pcl_{spec['name']}.npz"))
+    inp = pcl_inputs(spec)
+    kc, vc = inp["k_cache"], inp["v_cache"]
+    total = int(inp["cu_lens"][-1])
+    key = np.zeros((total,) + kc.shape[2:], dtype=kc.dtype)
+    value = np.zeros((total,) + vc.shape[2:], dtype=vc.dtype)
+    lens = inp["cu_lens"] if cumulative else inp["lens"]
+    ws = np.zeros(spec["batch"] + 1, dtype=np.int32)
+    emu().emu_paged_cache_load(_p(kc), _p(vc), _p(inp["block_tables"]), _p(lens), _p(inp["seq_starts"]), _p(key),
+                               _p(value), spec["batch"], inp["block_tables"].shape[1], spec["block_size"],
+                               kc[0, 0].nbytes, vc[0, 0].nbytes, kc.shape[0], total, int(cumulative), _p(ws), chunks,
+                               threads)
+    assert np.array_equal(_bits(key), _bits(fx["key"])) and np.array_equal(_bits(value), _bits(fx["value"]))
+
+
+def test_paged_cache_load_body_against_oracle_with_holes():
+    """Negative block ids and a missing seq_starts: rows of such tokens stay untouched, as in the oracle."""
+    rng = np.random.default_rng(5)
+    kc = rng.integers(-100, 100, size=(9, 4, 2, 24), dtype=np.int8)
+    vc = rng.integers(-100, 100, size=(9, 4, 2, 8), dtype=np.int8)
+    tables = rng.integers(-2, 9, size=(5, 6)).astype(np.int32)
+    lens = np.array([3, 0, 17, 24, 9], dtype=np.int32)
+    total = int(lens.sum())
+    key, value = np.full((total, 2, 24), 7, np.int8), np.full((total, 2, 8), 7, np.int8)
+    ref_k, ref_v = key.copy(), value.copy()
+    oracle.cache_ops.paged_cache_load(kc, vc, tables, lens, ref_k, ref_v)
+    ws = np.zeros(6, dtype=np.int32)
+    emu().emu_paged_cache_load(_p(kc), _p(vc), _p(tables), _p(lens), None, _p(key), _p(value), 5, 6, 4, 48, 16, 9, total,
+                               0, _p(ws), 0, 4)
+    assert np.array_equal(key, ref_k) and np.array_equal(value, ref_v)
+    assert (ref_k == 7).any()                                  # the case does have holes
+
+
+def test_c_abi_rejects_bad_arguments_before_launching():
+    L = capi.lib()
+    fake = ctypes.c_void_p(0x1000)
+    assert L.atb_b200_block_copy(None, fake, fake, fake, fake, 1, 1, 64, 64, 4, None) == capi.ERROR_INVALID_PARAM
+    assert L.atb_b200_block_copy(fake, fake, None, fake, fake, 1, 1, 64, 64, 4, None) == capi.ERROR_INVALID_PARAM
+    assert L.atb_b200_block_copy(fake, fake, fake, fake, fake, 1, 1, 0, 64, 4, None) == capi.ERROR_INVALID_PARAM
+    assert L.atb_b200_block_copy(fake, fake, fake, fake, fake, 0, 0, 64, 64, 4, None) == 0      # nothing to do
+    assert L.atb_b200_paged_cache_load_workspace_bytes(100, 1) == 0
+    assert L.atb_b200_paged_cache_load_workspace_bytes(100, 0) >= 101 * 4
+    args = [fake, fake, fake, fake, None, fake, fake, 4, 8, 16, 64, 64, 10, 100, 0, None, 0, None]
+    assert L.atb_b200_paged_cache_load(*args) == capi.ERROR_INVALID_PARAM                       # no workspace
+    args = [fake, None, fake, fake, None, fake, fake, 4, 8, 16, 64, 64, 10, 100, 1, None, 0, None]
+    assert L.atb_b200_paged_cache_load(*args) == capi.ERROR_INVALID_PARAM                       # value without v_cache
+    args = [fake, fake, fake, fake, None, fake, fake, 0, 8, 16, 64, 64, 10, 100, 1, None, 0, None]
+    assert L.atb_b200_paged_cache_load(*args) == 0                                              # empty batch
+
+
+# ------------------------------------------------------------------ the operations' host side (no GPU)
+
+def _expect(code, fn, *a):
+    with pytest.raises(capi.AtbError) as e:
+        fn(*a)
+    assert e.value.code == code, (e.value.code, code)
+
+
+def _T(dtype, shape, host=None):
+    return capi.atb_tensor(dtype=dtype, shape=shape, device_ptr=0x1000, host=host)
+
+
+def test_block_copy_operation_checks():
+    assert ctypes.sizeof(capi.BlockCopyParam) == 16
+    op = capi.Operation(capi.BlockCopyParam())
+    assert (op.name, op.input_num, op.output_num) == ("BlockCopyOperation", 5, 0)
+    bad = capi.BlockCopyParam()
+    bad.rsv[3] = 1
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, bad)
+    ctx = capi.Context()
+    f16, i32 = capi.ACL_FLOAT16, capi.ACL_INT32
+    cache = (20, 16, 2, 64)
+    ins = [_T(f16, cache), _T(f16, cache), _T(i32, (3,)), _T(i32, (10,)), _T(i32, (3,))]
+    assert op.setup(ins, [], ctx) == 0
+    wrong = list(ins)
+    wrong[1] = _T(f16, (20, 16, 2, 32))
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, wrong, [], ctx)                 # caches differ
+    wrong = list(ins)
+    wrong[4] = _T(i32, (4,))
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, wrong, [], ctx)                 # cumSum vs sources
+    wrong = list(ins)
+    wrong[3] = _T(i32, (21,))
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, wrong, [], ctx)                 # more destinations than blocks
+    wrong = list(ins)
+    wrong[2] = _T(i32, (3, 1))
+    wrong[4] = _T(i32, (3, 1))
+    _expect(capi.ERROR_INVALID_TENSOR_DIM_NUM, op.setup, wrong, [], ctx)
+    wrong = list(ins)
+    wrong[2] = _T(capi.ACL_INT64, (3,))
+    _expect(capi.ERROR_INVALID_TENSOR_INI_MATCH, op.setup, wrong, [], ctx)
+    _expect(capi.ERROR_INVALID_IN_TENSOR_NUM, op.setup, ins[:4], [], ctx)
+
+
+def _pcl_param(**kw):
+    p = capi.PagedCacheLoadParam()
+    p.kvCacheCfg = 1
+    for k, v in kw.items():
+        setattr(p, k, v)
+    return p
+
+
+def test_paged_cache_load_operation_checks():
+    assert ctypes.sizeof(capi.PagedCacheLoadParam) == 64
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, capi.PagedCacheLoadParam())    # the NZ layout (reference default)
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, _pcl_param(kvCacheCfg=2))
+    bad = _pcl_param()
+    bad.rsv[60] = 1
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, bad)
+    op = capi.Operation(_pcl_param(isSeqLensCumsumMode=True, hasSeqStarts=True))
+    assert (op.name, op.input_num, op.output_num) == ("PagedCacheLoadOperation", 7, 2)
+    ctx = capi.Context()
+    bf16, i32 = capi.ACL_BF16, capi.ACL_INT32
+    ins = [_T(bf16, (128, 128, 16, 144)), _T(bf16, (128, 128, 16, 128)), _T(i32, (16, 12)), _T(i32, (17,)),
+           _T(bf16, (900, 16, 144)), _T(bf16, (900, 16, 128)), _T(i32, (16,))]
+    outs = [_T(bf16, (900, 16, 144)), _T(bf16, (900, 16, 128))]
+    assert op.infer_shape(ins, 2) == [(900, 16, 144), (900, 16, 128)]
+    assert op.setup(ins, outs, ctx) == 0                                              # running totals: no workspace
+    plain = capi.Operation(_pcl_param())
+    lens_ins = list(ins)
+    lens_ins[3] = _T(i32, (16,))
+    assert plain.setup(lens_ins, outs, ctx) >= 17 * 4                                 # room for the running totals
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, plain.setup, ins, outs, ctx)              # 17 lengths for 16 sequences
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, lens_ins, outs, ctx)
+    wrong = list(ins)
+    wrong[6] = _T(i32, (15,))
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, wrong, outs, ctx)               # seqStarts per sequence
+    wrong = list(ins)
+    wrong[1] = _T(bf16, (128, 64, 16, 128))
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, wrong, outs, ctx)               # block sizes differ
+    wrong = list(ins)
+    wrong[0] = _T(bf16, (128, 128, 3, 5))
+    wrong[1] = _T(bf16, (128, 128, 3, 5))
+    wrong[4] = _T(bf16, (900, 3, 5))
+    wrong[5] = _T(bf16, (900, 3, 5))
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, wrong, [wrong[4], wrong[5]], ctx)   # heads*headSize % 16
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, ins, [outs[0], _T(bf16, (900, 16, 64))], ctx)
+    wrong = list(ins)
+    wrong[5] = _T(bf16, (901, 16, 128))
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, wrong, [outs[0], wrong[5]], ctx)    # rows of key and value
+    wrong = list(ins)
+    wrong[2] = _T(i32, (16,))
+    _expect(capi.ERROR_INVALID_TENSOR_DIM_NUM, op.setup, wrong, outs, ctx)

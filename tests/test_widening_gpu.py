@@ -53,3 +53,116 @@ def test_dynamic_batch_skips_switched_off_sequences(extra_rows):
     assert max_abs_err(out, ref, case.q_dtype) <= tol_for(case)
     off = [b for b, s in enumerate(status) if s == 0]
     assert np.all(out[off] == np.float16(7.0))   # rows of skipped sequences are left untouched
+
+
+# ------------------------------------------------------------------ BlockCopy / PagedCacheLoad
+
+import os  # noqa: E402
+
+import oracle  # noqa: E402
+from golden_cases import (GOLDEN_BLOCKCOPY_CASES, GOLDEN_PCL_CASES, HERE as GOLDEN_DIR,  # noqa: E402
+                          blockcopy_inputs, pcl_inputs)
+from helpers import to_dev  # noqa: E402
+
+
+def _bits(a):
+    return a.view(np.uint16) if a.dtype == np.float16 else a
+
+
+def _i32(a):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).cuda()
+
+
+@pytest.mark.parametrize("spec", GOLDEN_BLOCKCOPY_CASES, ids=lambda s: s["name"])
+def test_block_copy_matches_reference_golden(spec):
+    fx = np.load(os.path.join(GOLDEN_DIR, f"blockcopy_{spec['name']}.npz"))
+    inp = blockcopy_inputs(spec)
+    k, v = to_dev(inp["k_cache"], spec["dtype"]), to_dev(inp["v_cache"], spec["dtype"])
+    capi.block_copy(k, v, _i32(inp["src"]), _i32(inp["dst"]), _i32(inp["cum"]))
+    torch.cuda.synchronize()
+    assert np.array_equal(_bits(wl.torch_to_host(k, spec["dtype"])), _bits(fx["k_cache"]))
+    assert np.array_equal(_bits(wl.torch_to_host(v, spec["dtype"])), _bits(fx["v_cache"]))
+
+
+def test_block_copy_operation_large_blocks():
+    """Blocks of 256 KB (several chunks per block) through the atb operator API, against the oracle."""
+    rng = np.random.default_rng(91)
+    shape = (24, 128, 8, 128)
+    kc = rng.integers(-30000, 30000, size=shape, dtype=np.int16)
+    vc = rng.integers(-30000, 30000, size=shape, dtype=np.int16)
+    src = np.array([3, 7, 11], dtype=np.int32)
+    dst = np.array([0, 1, 2, 4, 5, 20, 23], dtype=np.int32)
+    cum = np.array([2, 3, 7], dtype=np.int32)
+    ref_k, ref_v = oracle.cache_ops.block_copy(kc.copy(), vc.copy(), src, dst, cum)
+    k = torch.from_numpy(kc).cuda().view(torch.bfloat16)
+    v = torch.from_numpy(vc).cuda().view(torch.bfloat16)
+    s, d, c = _i32(src), _i32(dst), _i32(cum)
+    T = capi.atb_tensor
+    op = capi.Operation(capi.BlockCopyParam())
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    ctx = capi.Context(stream.cuda_stream)
+    ins = [T(k), T(v), T(s), T(d), T(c)]
+    assert op.setup(ins, [], ctx) == 0
+    op.execute(ins, [], None, 0, ctx)
+    torch.cuda.synchronize()
+    assert np.array_equal(k.view(torch.int16).cpu().numpy(), ref_k)
+    assert np.array_equal(v.view(torch.int16).cpu().numpy(), ref_v)
+
+
+@pytest.mark.parametrize("cumulative", [True, False])
+@pytest.mark.parametrize("spec", GOLDEN_PCL_CASES, ids=lambda s: s["name"])
+def test_paged_cache_load_matches_reference_golden(spec, cumulative):
+    fx = np.load(os.path.join(GOLDEN_DIR, f"pcl_{spec['name']}.npz"))
+    inp = pcl_inputs(spec)
+    kc, vc = to_dev(inp["k_cache"], spec["dtype"]), to_dev(inp["v_cache"], spec["dtype"])
+    total = int(inp["cu_lens"][-1])
+    key = torch.zeros((total,) + tuple(kc.shape[2:]), dtype=kc.dtype, device="cuda")
+    value = torch.zeros((total,) + tuple(vc.shape[2:]), dtype=vc.dtype, device="cuda")
+    lens = _i32(inp["cu_lens"] if cumulative else inp["lens"])
+    capi.paged_cache_load(kc, vc, _i32(inp["block_tables"]), lens, key, value, seq_starts=_i32(inp["seq_starts"]),
+                          cumulative=cumulative)
+    torch.cuda.synchronize()
+    assert np.array_equal(_bits(wl.torch_to_host(key, spec["dtype"])), _bits(fx["key"]))
+    assert np.array_equal(_bits(wl.torch_to_host(value, spec["dtype"])), _bits(fx["value"]))
+
+
+def test_paged_cache_load_operation_reference_shape():
+    """The shape of the reference's kernel test (16 sequences, 16 heads, 144 / 128 wide, block 128:
+    tests/apitest/kernelstest/mix/test_paged_cache_load_nd.py:151-178) through the operator API."""
+    rng = np.random.default_rng(92)
+    nb, bs, heads, dk, dv, batch = 32, 128, 16, 144, 128, 16
+    kc = rng.integers(-30000, 30000, size=(nb, bs, heads, dk), dtype=np.int16)
+    vc = rng.integers(-30000, 30000, size=(nb, bs, heads, dv), dtype=np.int16)
+    lens = rng.integers(1, 400, size=batch).astype(np.int32)
+    lens[3] = 300                                           # long enough to reach the hole below
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    cols = (int(lens.max()) + bs - 1) // bs + 4
+    tables = rng.integers(0, nb, size=(batch, cols)).astype(np.int32)
+    tables[3, 1] = -1                                       # a hole: those rows stay as they are
+    starts = (rng.integers(0, 5, size=batch) * bs).astype(np.int32)
+    starts[3] = 0
+    total = int(cu[-1])
+    ref_k = np.full((total, heads, dk), 5, np.int16)
+    ref_v = np.full((total, heads, dv), 5, np.int16)
+    oracle.cache_ops.paged_cache_load(kc, vc, tables, cu, ref_k, ref_v, seq_starts=starts, cumulative=True)
+    T = capi.atb_tensor
+    d_kc, d_vc = torch.from_numpy(kc).cuda().view(torch.float16), torch.from_numpy(vc).cuda().view(torch.float16)
+    key = torch.full((total, heads, dk), 5, dtype=torch.int16, device="cuda").view(torch.float16)
+    value = torch.full((total, heads, dv), 5, dtype=torch.int16, device="cuda").view(torch.float16)
+    d_t, d_cu, d_st = _i32(tables), _i32(cu), _i32(starts)
+    p = capi.PagedCacheLoadParam()
+    p.kvCacheCfg, p.isSeqLensCumsumMode, p.hasSeqStarts = 1, True, True
+    op = capi.Operation(p)
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    ctx = capi.Context(stream.cuda_stream)
+    ins = [T(d_kc), T(d_vc), T(d_t), T(d_cu), T(key), T(value), T(d_st)]
+    outs = [T(key), T(value)]
+    ws_bytes = op.setup(ins, outs, ctx)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device="cuda")
+    op.execute(ins, outs, ws.data_ptr(), ws_bytes, ctx)
+    torch.cuda.synchronize()
+    assert np.array_equal(key.view(torch.int16).cpu().numpy(), ref_k)
+    assert np.array_equal(value.view(torch.int16).cpu().numpy(), ref_v)
+    assert (ref_k == 5).all(axis=(1, 2)).any()              # the hole left rows untouched
