@@ -86,6 +86,11 @@ class ReshapeAndCacheParam(ctypes.Structure):
     _fields_ = [("compressType", ctypes.c_int32), ("kvCacheCfg", ctypes.c_int32), ("rsv", ctypes.c_uint8 * 16)]
 
 
+class ReshapeAndCacheWithStrideParam(ctypes.Structure):
+    """Byte layout of atb::infer::ReshapeAndCacheWithStrideParam (24 bytes)."""
+    _fields_ = [("compressType", ctypes.c_int32), ("kvCacheCfg", ctypes.c_int32), ("rsv", ctypes.c_uint8 * 16)]
+
+
 class BlockCopyParam(ctypes.Structure):
     """Byte layout of atb::infer::BlockCopyParam (16 bytes)."""
     _fields_ = [("rsv", ctypes.c_uint8 * 16)]
@@ -111,6 +116,7 @@ EXPORTS = [
     "atb_b200_pa_plan_set_trace", "atb_b200_pa_plan_prefetch", "atb_b200_operation_name",
     "atb_b200_block_copy", "atb_b200_paged_cache_load", "atb_b200_paged_cache_load_workspace_bytes",
     "atb_b200_operation_create_block_copy", "atb_b200_operation_create_paged_cache_load",
+    "atb_b200_reshape_and_cache_strided", "atb_b200_operation_create_reshape_and_cache_with_stride",
 ]
 
 _lib = None
@@ -142,6 +148,8 @@ def lib():
         L.atb_b200_operation_create_paged_attention.argtypes = [vp, u64, P(vp)]
         L.atb_b200_operation_create_reshape_and_cache.argtypes = [vp, u64, P(vp)]
         L.atb_b200_operation_create_block_copy.argtypes = [vp, u64, P(vp)]
+        L.atb_b200_operation_create_reshape_and_cache_with_stride.argtypes = [vp, u64, P(vp)]
+        L.atb_b200_reshape_and_cache_strided.argtypes = [vp, vp, vp, vp, vp, i32, i64, i64, i64, i64, i64, vp]
         L.atb_b200_operation_create_paged_cache_load.argtypes = [vp, u64, P(vp)]
         L.atb_b200_operation_input_num.argtypes = [vp, P(u32)]
         L.atb_b200_operation_output_num.argtypes = [vp, P(u32)]
@@ -494,6 +502,9 @@ class Operation:
         self.handle = ctypes.c_void_p()
         if isinstance(param, PagedAttentionParam):
             fn, what = lib().atb_b200_operation_create_paged_attention, "CreateOperation(PagedAttentionParam)"
+        elif isinstance(param, ReshapeAndCacheWithStrideParam):
+            fn, what = (lib().atb_b200_operation_create_reshape_and_cache_with_stride,
+                        "CreateOperation(ReshapeAndCacheWithStrideParam)")
         elif isinstance(param, BlockCopyParam):
             fn, what = lib().atb_b200_operation_create_block_copy, "CreateOperation(BlockCopyParam)"
         elif isinstance(param, PagedCacheLoadParam):

@@ -1,11 +1,16 @@
-// atb::CreateOperation<infer::BlockCopyParam> and <infer::PagedCacheLoadParam>: the cache-management
+// atb::CreateOperation<infer::BlockCopyParam>, <infer::PagedCacheLoadParam> and
+// <infer::ReshapeAndCacheWithStrideParam>: the cache-management
 // operations next to ReshapeAndCache.  Checks follow the reference:
 //   BlockCopy       src/ops/ops_infer/block_copy/block_copy_operation.cpp (CreateOperation :29-46,
 //                   GetInputNum/GetOutputNum :58-67, InferShapeCheckImpl :69-95, SetupCheckImpl :105-150)
 //   PagedCacheLoad  src/ops/ops_infer/paged_cache_load/paged_cache_load_operation.cpp (CreateOperation :51-77,
 //                   GetInputNum :95-102, InferShapeImpl :109-115, SetupCheckImpl :122-146, DimCheck :149-196,
 //                   KVCacheDimCheck910BND :252-297)
-// The fractal-NZ cache layout of PagedCacheLoad belongs to other hardware and is rejected.
+//   ReshapeAndCacheWithStride  src/ops/ops_infer/reshape_and_cache_with_stride/
+//                   reshape_and_cache_with_stride_operation.cpp (CreateOperation :51-88, GetInputNum :115-127,
+//                   SetupCheckImpl :164-194, DimCheck :196-232, DimCheckSISO :234-260)
+// The fractal-NZ cache layout of PagedCacheLoad and the head-compression modes belong to other hardware
+// and are rejected.
 #include <new>
 #include "../../include/atb_b200.h"
 #include "atb_operation_base.h"
@@ -250,7 +255,204 @@ private:
     std::vector<DtypeComb> combs_;
 };
 
+// ---------------------------------------------------------------------------------------------------
+// ReshapeAndCacheWithStride: key (and value) are strided views described by host tensors
+// kStrides / vStrides (int64 element strides per dimension) and kOffset / vOffset (int64 element offset
+// from the tensor's address).  As in the reference, only the token stride matters: a token's row of
+// heads x headSize elements is contiguous, and the KEY's token stride is applied to the value as well
+// (tiling/reshape_and_cache_tiling.cpp:64-72, op_kernel/reshape_and_cache_nd.cpp:78-79, 111-112).
+class ReshapeAndCacheWithStrideOperation : public OperationBase {
+public:
+    using Param = infer::ReshapeAndCacheWithStrideParam;
+    explicit ReshapeAndCacheWithStrideOperation(const Param &p)
+        : OperationBase("ReshapeAndCacheWithStrideOperation"), param_(p)
+    {
+        for (aclDataType t : {ACL_FLOAT16, ACL_BF16, ACL_INT8}) {
+            if (siso()) {
+                combs_.push_back({t, t, ACL_INT32, ACL_INT64, ACL_INT64, t});
+            } else {
+                combs_.push_back({t, t, t, t, ACL_INT32, ACL_INT64, ACL_INT64, ACL_INT64, ACL_INT64, t, t});
+            }
+        }
+    }
+    uint32_t GetInputNum() const override { return siso() ? 5 : 9; }
+    uint32_t GetOutputNum() const override { return siso() ? 1 : 2; }
+
+protected:
+    const std::vector<DtypeComb> &DtypeCombs() const override { return combs_; }
+
+    Status InferShapeCheckImpl(const SVector<TensorDesc> &in) const override
+    {
+        if (siso()) {
+            if (in.at(0).shape.dimNum != 3 || in.at(1).shape.dimNum != 4 || in.at(2).shape.dimNum != 1 ||
+                in.at(3).shape.dimNum != 1 || in.at(4).shape.dimNum != 1) {
+                ATB_B200_LOG(ERROR, "ReshapeAndCacheWithStride: invalid intensor dimNum");
+                return ERROR_INVALID_TENSOR_DIM_NUM;
+            }
+            const Dims &k = in.at(0).shape, &kc = in.at(1).shape;
+            if (k.dims[0] != in.at(2).shape.dims[0] || k.dims[1] != kc.dims[2] || k.dims[2] != kc.dims[3]) {
+                ATB_B200_LOG(ERROR, "ReshapeAndCacheWithStride: key, keyCache and slotMapping dims do not match");
+                return ERROR_INVALID_TENSOR_DIM;
+            }
+            return NO_ERROR;
+        }
+        if (in.at(0).shape.dimNum != 3 || in.at(1).shape.dimNum != 3 || in.at(2).shape.dimNum != 4 ||
+            in.at(3).shape.dimNum != 4) {
+            ATB_B200_LOG(ERROR, "ReshapeAndCacheWithStride: invalid intensor dimNum");
+            return ERROR_INVALID_TENSOR_DIM_NUM;
+        }
+        for (size_t i = 4; i < 9; ++i) {
+            if (in.at(i).shape.dimNum != 1) {
+                ATB_B200_LOG(ERROR, "ReshapeAndCacheWithStride: invalid intensor dimNum");
+                return ERROR_INVALID_TENSOR_DIM_NUM;
+            }
+        }
+        const Dims &k = in.at(0).shape, &v = in.at(1).shape, &kc = in.at(2).shape, &vc = in.at(3).shape;
+        if (k.dims[0] != v.dims[0] || k.dims[1] != v.dims[1]) {
+            ATB_B200_LOG(ERROR, "ReshapeAndCacheWithStride: numTokens / numHead of key and value should be same");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (kc.dims[0] != vc.dims[0] || kc.dims[1] != vc.dims[1]) {
+            ATB_B200_LOG(ERROR, "ReshapeAndCacheWithStride: numBlocks / blockSize of the caches should be same");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (k.dims[1] != kc.dims[2] || v.dims[1] != vc.dims[2]) {
+            ATB_B200_LOG(ERROR, "ReshapeAndCacheWithStride: numHeads should be same");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (k.dims[2] != kc.dims[3] || v.dims[2] != vc.dims[3]) {
+            ATB_B200_LOG(ERROR, "ReshapeAndCacheWithStride: key/keyCache and value/valueCache headSize should be same");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (in.at(4).shape.dims[0] != k.dims[0]) {
+            ATB_B200_LOG(ERROR, "ReshapeAndCacheWithStride: slotMapping length should equal numTokens");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        return NO_ERROR;
+    }
+
+    Status InferShapeImpl(const SVector<TensorDesc> &in, SVector<TensorDesc> &out) const override
+    {
+        if (siso()) {
+            out.at(0) = in.at(1);
+        } else {
+            out.at(0) = in.at(2);
+            out.at(1) = in.at(3);
+        }
+        return NO_ERROR;
+    }
+
+    Status SetupCheckImpl(const SVector<Tensor> &inTensors, const SVector<Tensor> &outTensors) const override
+    {
+        SVector<TensorDesc> descs;
+        for (size_t i = 0; i < inTensors.size(); ++i) {
+            descs.push_back(inTensors.at(i).desc);
+        }
+        Status st = InferShapeCheckImpl(descs);
+        if (st != NO_ERROR) {
+            return st;
+        }
+        const size_t kc = siso() ? 1 : 2;
+        if (!TensorDescEqual(descs.at(kc), outTensors.at(0).desc) ||
+            (!siso() && !TensorDescEqual(descs.at(3), outTensors.at(1).desc))) {
+            ATB_B200_LOG(ERROR, "ReshapeAndCacheWithStride: intensor & outtensor descs should be same");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        return NO_ERROR;
+    }
+
+    // The strides and offsets are host data, read at Setup like contextLens of PagedAttention
+    // (reshape_and_cache_with_stride_ops_runner.cpp:79-104 of the reference).
+    Status PlanImpl(const VariantPack &vp, uint64_t &workspaceSize) override
+    {
+        workspaceSize = 0;
+        const Tensor &kStrides = vp.inTensors.at(siso() ? 3 : 5);
+        const Tensor &kOffset = vp.inTensors.at(siso() ? 4 : 7);
+        const Tensor *vOffset = siso() ? nullptr : &vp.inTensors.at(8);
+        const Tensor *vStrides = siso() ? nullptr : &vp.inTensors.at(6);
+        if (kStrides.hostData == nullptr || kOffset.hostData == nullptr ||
+            (!siso() && (vOffset->hostData == nullptr || vStrides->hostData == nullptr))) {
+            ATB_B200_LOG(ERROR, "ReshapeAndCacheWithStride: strides / offsets hostData is null");
+            return ERROR_INVALID_PARAM;
+        }
+        if (kStrides.desc.shape.dims[0] < 1 || kOffset.desc.shape.dims[0] < 1 ||
+            (!siso() && vOffset->desc.shape.dims[0] < 1)) {
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        tokenStride_ = static_cast<const int64_t *>(kStrides.hostData)[0];
+        kOffset_ = static_cast<const int64_t *>(kOffset.hostData)[0];
+        vOffset_ = siso() ? 0 : static_cast<const int64_t *>(vOffset->hostData)[0];
+        if (tokenStride_ < 0 || kOffset_ < 0 || vOffset_ < 0) {
+            ATB_B200_LOG(ERROR, "ReshapeAndCacheWithStride: strides and offsets must not be negative");
+            return ERROR_INVALID_PARAM;
+        }
+        return NO_ERROR;
+    }
+
+    Status LaunchImpl(const VariantPack &vp, uint8_t *, uint64_t, aclrtStream stream) override
+    {
+        const Tensor &key = vp.inTensors.at(0);
+        const Tensor &keyCache = vp.inTensors.at(siso() ? 1 : 2);
+        const Tensor &slots = vp.inTensors.at(siso() ? 2 : 4);
+        const Tensor *value = siso() ? nullptr : &vp.inTensors.at(1);
+        const Tensor *valueCache = siso() ? nullptr : &vp.inTensors.at(3);
+        void *kcOut = vp.outTensors.at(0).deviceData;
+        void *vcOut = siso() ? nullptr : vp.outTensors.at(1).deviceData;
+        if (kcOut != keyCache.deviceData || (!siso() && vcOut != valueCache->deviceData)) {
+            ATB_B200_LOG(ERROR, "ReshapeAndCacheWithStride: the output tensors must alias the cache inputs");
+            return ERROR_INVALID_TENSOR_ADDR;
+        }
+        if (key.deviceData == nullptr || kcOut == nullptr || slots.deviceData == nullptr ||
+            (!siso() && (value->deviceData == nullptr || vcOut == nullptr))) {
+            return ERROR_INVALID_PARAM;
+        }
+        const int64_t es = static_cast<int64_t>(ElemSize(key.desc.dtype));
+        const Dims &k = key.desc.shape, &kc = keyCache.desc.shape;
+        const int64_t kRow = k.dims[1] * k.dims[2] * es;
+        const int64_t vRow = siso() ? 0 : value->desc.shape.dims[1] * value->desc.shape.dims[2] * es;
+        const uint8_t *kPtr = static_cast<const uint8_t *>(key.deviceData) + kOffset_ * es;
+        const uint8_t *vPtr = siso() ? nullptr : static_cast<const uint8_t *>(value->deviceData) + vOffset_ * es;
+        const int rc = atb_b200_reshape_and_cache_strided(kPtr, vPtr, kcOut, vcOut,
+                                                          static_cast<const int32_t *>(slots.deviceData),
+                                                          static_cast<int32_t>(k.dims[0]), kRow, vRow, tokenStride_ * es,
+                                                          tokenStride_ * es, kc.dims[0] * kc.dims[1], stream);
+        return rc == 0 ? NO_ERROR : (rc == ERROR_INVALID_PARAM ? ERROR_INVALID_PARAM : ERROR_RT_FAIL);
+    }
+
+private:
+    bool siso() const { return param_.kvCacheCfg == Param::K_CACHE_V_BYPASS; }
+    Param param_;
+    std::vector<DtypeComb> combs_;
+    int64_t tokenStride_ = 0, kOffset_ = 0, vOffset_ = 0; // elements, from the host tensors at Setup
+};
+
 } // namespace
+
+template <> Status CreateOperation(const infer::ReshapeAndCacheWithStrideParam &opParam, Operation **operation)
+{
+    using Param = infer::ReshapeAndCacheWithStrideParam;
+    if (operation == nullptr) {
+        return ERROR_INVALID_PARAM;
+    }
+    if (!RsvIsZero(opParam.rsv, sizeof(opParam.rsv))) {
+        ATB_B200_LOG(ERROR, "ReshapeAndCacheWithStrideParam.rsv must be zero");
+        return ERROR_INVALID_PARAM;
+    }
+    if (opParam.compressType < Param::COMPRESS_TYPE_UNDEFINED || opParam.compressType > Param::COMPRESS_TYPE_KVHEAD_ROPE) {
+        ATB_B200_LOG(ERROR, "wrong compress head");
+        return ERROR_INVALID_PARAM;
+    }
+    if (opParam.kvCacheCfg < Param::K_CACHE_V_CACHE || opParam.kvCacheCfg > Param::K_CACHE_V_BYPASS) {
+        ATB_B200_LOG(ERROR, "wrong kvcache config");
+        return ERROR_INVALID_PARAM;
+    }
+    if (opParam.compressType != Param::COMPRESS_TYPE_UNDEFINED) {
+        ATB_B200_LOG(ERROR, "ReshapeAndCacheWithStride: head compression is not supported by this build");
+        return ERROR_INVALID_PARAM;
+    }
+    *operation = new (std::nothrow) ReshapeAndCacheWithStrideOperation(opParam);
+    return *operation == nullptr ? ERROR_OUT_OF_HOST_MEMORY : NO_ERROR;
+}
 
 template <> Status CreateOperation(const infer::BlockCopyParam &opParam, Operation **operation)
 {

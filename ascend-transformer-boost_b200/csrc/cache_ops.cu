@@ -1,8 +1,12 @@
-// BlockCopy and PagedCacheLoad: the cache-management siblings of ReshapeAndCache.
+// BlockCopy, PagedCacheLoad and ReshapeAndCache over strided inputs: the cache-management siblings of
+// ReshapeAndCache.
 //   BlockCopy        copies whole cache blocks (beam search / prefix reuse); replaces
 //                    src/kernels/mixkernels/blockcopy of the reference.
 //   PagedCacheLoad   gathers a sequence's cached tokens back into contiguous rows; replaces
 //                    src/kernels/mixkernels/paged_cache_load/op_kernel/paged_cache_load_nd.cpp.
+//   ReshapeAndCache (strided)  the scatter of ReshapeAndCache reading rows that are `stride` apart (K/V
+//                    slices of a fused QKV projection); replaces the strided mode of
+//                    src/kernels/mixkernels/reshape_and_cache/op_kernel/reshape_and_cache_nd.cpp:70-128.
 // HBM-bound byte movement: 16-byte vectors, one CTA per (block, chunk) so that a few hundred KB are
 // in flight per SM.  The per-thread arithmetic lives in cache_ops_body.h, shared with the CPU tests.
 #include <cuda_runtime.h>
@@ -25,6 +29,11 @@ __global__ void __launch_bounds__(kThreads) block_copy_kernel(const BlockCopyArg
 __global__ void __launch_bounds__(kThreads) paged_cache_load_kernel(const PagedCacheLoadArgs a)
 {
     paged_cache_load_body(a, blockIdx.x, threadIdx.x, blockDim.x);
+}
+
+__global__ void __launch_bounds__(kThreads) rac_strided_kernel(const RacStridedArgs a)
+{
+    rac_strided_body(a, blockIdx.x, threadIdx.x, blockDim.x);
 }
 
 __global__ void prefix_lens_kernel(const int32_t *lens, int32_t *cu, int32_t batch)
@@ -141,6 +150,42 @@ int atb_b200_paged_cache_load(const void *k_cache, const void *v_cache, const in
         return kErrInvalidParam;
     }
     paged_cache_load_kernel<<<(unsigned)ctas, kThreads, 0, s>>>(a);
+    return cudaGetLastError() == cudaSuccess ? 0 : kErrRtFail;
+}
+
+int atb_b200_reshape_and_cache_strided(const void *key, const void *value, void *key_cache, void *value_cache,
+                                       const int32_t *slot_mapping, int32_t num_tokens, int64_t k_row_bytes,
+                                       int64_t v_row_bytes, int64_t k_token_stride_bytes, int64_t v_token_stride_bytes,
+                                       int64_t num_slots, void *stream)
+{
+    if (key == nullptr || key_cache == nullptr || slot_mapping == nullptr || num_tokens < 0 || k_row_bytes <= 0 ||
+        k_token_stride_bytes < 0 || num_slots <= 0 || ((value == nullptr) != (value_cache == nullptr)) ||
+        (value != nullptr && (v_row_bytes <= 0 || v_token_stride_bytes < 0))) {
+        return kErrInvalidParam;
+    }
+    if (num_tokens == 0) {
+        return 0;
+    }
+    RacStridedArgs a{};
+    a.key = static_cast<const uint8_t *>(key);
+    a.value = static_cast<const uint8_t *>(value);
+    a.key_cache = static_cast<uint8_t *>(key_cache);
+    a.value_cache = static_cast<uint8_t *>(value_cache);
+    a.slot_mapping = slot_mapping;
+    a.num_tokens = num_tokens;
+    a.k_row_bytes = k_row_bytes;
+    a.v_row_bytes = value != nullptr ? v_row_bytes : 0;
+    a.k_src_stride = k_token_stride_bytes;
+    a.v_src_stride = value != nullptr ? v_token_stride_bytes : 0;
+    a.num_slots = num_slots;
+    a.chunks = chunks_for(k_row_bytes > a.v_row_bytes ? k_row_bytes : a.v_row_bytes);
+    a.vec16 = aligned16(key) && aligned16(value) && aligned16(key_cache) && aligned16(value_cache) &&
+              k_row_bytes % 16 == 0 && a.v_row_bytes % 16 == 0 && a.k_src_stride % 16 == 0 && a.v_src_stride % 16 == 0;
+    const int64_t ctas = (int64_t)num_tokens * a.chunks;
+    if (ctas > 0x7fffffff) {
+        return kErrInvalidParam;
+    }
+    rac_strided_kernel<<<(unsigned)ctas, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
     return cudaGetLastError() == cudaSuccess ? 0 : kErrRtFail;
 }
 

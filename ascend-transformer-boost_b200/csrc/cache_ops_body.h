@@ -154,6 +154,47 @@ ATB_B200_HD void paged_cache_load_body(const PagedCacheLoadArgs &a, int64_t cta,
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// ReshapeAndCache over strided inputs: token t's key row (heads x head size, contiguous) starts
+// `k_src_stride` bytes after token t-1's, e.g. inside the output of a fused QKV projection; the row is
+// scattered to cache slot slot_mapping[t] like ReshapeAndCache does.  One CTA per (token, chunk).
+// Negative slots mean "do not store"; slots past the cache are dropped.
+struct RacStridedArgs {
+    const uint8_t *key, *value;        // first element of token 0's row (any view offset already applied)
+    uint8_t *key_cache, *value_cache;  // value / value_cache may be null
+    const int32_t *slot_mapping;
+    int32_t num_tokens;
+    int64_t k_row_bytes, v_row_bytes;
+    int64_t k_src_stride, v_src_stride; // bytes between consecutive tokens' rows
+    int64_t num_slots;
+    int32_t chunks;
+    bool vec16;
+};
+
+ATB_B200_HD void rac_strided_body(const RacStridedArgs &a, int64_t cta, int tid, int nthreads)
+{
+    const int32_t token = (int32_t)(cta / a.chunks), c = (int32_t)(cta % a.chunks);
+    if (token >= a.num_tokens) {
+        return;
+    }
+    const int64_t slot = a.slot_mapping[token];
+    if (slot < 0 || slot >= a.num_slots) {
+        return;
+    }
+    int64_t begin, end;
+    chunk_range(a.k_row_bytes, a.chunks, c, &begin, &end);
+    if (begin < end) {
+        copy_range(a.key_cache + slot * a.k_row_bytes, a.key + token * a.k_src_stride, begin, end, tid, nthreads, a.vec16);
+    }
+    if (a.value != nullptr && a.value_cache != nullptr) {
+        chunk_range(a.v_row_bytes, a.chunks, c, &begin, &end);
+        if (begin < end) {
+            copy_range(a.value_cache + slot * a.v_row_bytes, a.value + token * a.v_src_stride, begin, end, tid, nthreads,
+                       a.vec16);
+        }
+    }
+}
+
 // Running totals of the sequence lengths (one thread; batch is small): cu[0] = 0, cu[i+1] = cu[i] + lens[i].
 ATB_B200_HD void prefix_lens_body(const int32_t *lens, int32_t *cu, int32_t batch)
 {

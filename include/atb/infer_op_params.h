@@ -63,6 +63,19 @@ struct PagedAttentionParam {
     uint8_t rsv[64] = {0};
 };
 
+// ReshapeAndCache whose key / value are strided views (e.g. slices of a fused QKV projection output):
+// include/atb/infer_op_params.h:531-568 of the reference.  Inputs key, value, keyCache, valueCache,
+// slotMapping, kStrides, vStrides, kOffset, vOffset (the last four int64 host tensors: element strides
+// per dimension and the element offset of the view); K_CACHE_V_BYPASS: key, keyCache, slotMapping,
+// kStrides, kOffset.
+struct ReshapeAndCacheWithStrideParam {
+    enum CompressType : int { COMPRESS_TYPE_UNDEFINED = 0, COMPRESS_TYPE_KVHEAD, COMPRESS_TYPE_KVHEAD_ROPE };
+    enum KvCacheCfg : int { K_CACHE_V_CACHE = 0, K_CACHE_V_BYPASS };
+    CompressType compressType = COMPRESS_TYPE_UNDEFINED;
+    KvCacheCfg kvCacheCfg = K_CACHE_V_CACHE;
+    uint8_t rsv[16] = {0};
+};
+
 // BlockCopy: copy the cache blocks named by srcBlockIndices onto the blocks named by dstBlockIndices
 // (include/atb/infer_op_params.h:1205-1215 of the reference).  Inputs keyCache, valueCache,
 // srcBlockIndices [n], dstBlockIndices [m], cumSum [n] (running total of destinations per source);
@@ -85,6 +98,7 @@ struct PagedCacheLoadParam {
     uint8_t rsv[61] = {0};
 };
 
+static_assert(sizeof(ReshapeAndCacheWithStrideParam) == 24, "ABI: ReshapeAndCacheWithStrideParam is 24 bytes");
 static_assert(sizeof(BlockCopyParam) == 16, "ABI: BlockCopyParam is 16 bytes");
 static_assert(sizeof(PagedCacheLoadParam) == 64, "ABI: PagedCacheLoadParam is 64 bytes");
 static_assert(sizeof(ReshapeAndCacheParam) == 24, "ABI: ReshapeAndCacheParam is 24 bytes");

@@ -236,6 +236,8 @@ int atb_b200_operation_create_reshape_and_cache(const void *param, uint64_t para
 /* atb::CreateOperation<infer::BlockCopyParam> (16-byte param) and <infer::PagedCacheLoadParam> (64-byte param) */
 int atb_b200_operation_create_block_copy(const void *param, uint64_t param_bytes, void **operation);
 int atb_b200_operation_create_paged_cache_load(const void *param, uint64_t param_bytes, void **operation);
+/* atb::CreateOperation<infer::ReshapeAndCacheWithStrideParam> (24-byte param) */
+int atb_b200_operation_create_reshape_and_cache_with_stride(const void *param, uint64_t param_bytes, void **operation);
 int atb_b200_operation_input_num(void *operation, uint32_t *n);
 int atb_b200_operation_output_num(void *operation, uint32_t *n);
 /* Operation::GetName (include/atb/operation.h:46 of the reference): copies the NUL-terminated name into
@@ -274,6 +276,17 @@ int atb_b200_paged_cache_load(const void *k_cache, const void *v_cache, const in
                               int32_t batch, int32_t table_cols, int32_t block_size, int64_t k_row_bytes,
                               int64_t v_row_bytes, int64_t num_blocks, int64_t out_rows, int32_t lens_are_cumulative,
                               void *workspace, uint64_t workspace_bytes, void *stream);
+
+/* ReshapeAndCache reading strided rows: token t's key row (k_row_bytes, contiguous) starts at
+ * key + t * k_token_stride_bytes (value likewise), e.g. the K and V slices of a fused QKV projection output;
+ * the rows are scattered to the cache slots like atb_b200_reshape_and_cache does.  key / value point at the
+ * first element of token 0's row (the caller applies the view's element offset).  Replaces the strided mode
+ * of the reference's ReshapeAndCache kernel (op_kernel/reshape_and_cache_nd.cpp:70-128, tiling
+ * reshape_and_cache_tiling.cpp:60-75).  value and value_cache may both be null. */
+int atb_b200_reshape_and_cache_strided(const void *key, const void *value, void *key_cache, void *value_cache,
+                                       const int32_t *slot_mapping, int32_t num_tokens, int64_t k_row_bytes,
+                                       int64_t v_row_bytes, int64_t k_token_stride_bytes, int64_t v_token_stride_bytes,
+                                       int64_t num_slots, void *stream);
 
 const char *atb_b200_version(void);
 

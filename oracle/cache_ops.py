@@ -51,3 +51,24 @@ def paged_cache_load(k_cache, v_cache, block_tables, context_lens, key_out, valu
             if v_cache is not None:
                 value_out[starts[i] + j] = v_cache[blk, j % block_size]
     return key_out, value_out
+
+
+def reshape_and_cache_with_stride(key_storage, value_storage, key_cache, value_cache, slot_mapping, num_heads, dk, dv,
+                                  token_stride, k_offset, v_offset=0):
+    """ReshapeAndCache reading strided rows: token t's key row is the num_heads*dk elements of the flat
+    array key_storage starting at k_offset + t*token_stride (value: v_offset + t*token_stride, the KEY's
+    token stride, as the reference kernel applies it).  The gathered rows go through the pinned
+    ReshapeAndCache oracle."""
+    from .oracle import reshape_and_cache
+    n = len(slot_mapping)
+    kflat = np.ascontiguousarray(key_storage).reshape(-1)
+    key = np.stack([kflat[k_offset + t * token_stride: k_offset + t * token_stride + num_heads * dk]
+                    for t in range(n)]).reshape(n, num_heads, dk)
+    value = None
+    if value_storage is not None:
+        vflat = np.ascontiguousarray(value_storage).reshape(-1)
+        value = np.stack([vflat[v_offset + t * token_stride: v_offset + t * token_stride + num_heads * dv]
+                          for t in range(n)]).reshape(n, num_heads, dv)
+        value = np.ascontiguousarray(value)
+    reshape_and_cache(np.ascontiguousarray(key), value, key_cache, value_cache, slot_mapping)
+    return key_cache, value_cache

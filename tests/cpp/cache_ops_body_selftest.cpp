@@ -213,6 +213,73 @@ void test_paged_cache_load(int case_id)
     expect(value.n == 0 || std::memcmp(value.p, vref.data(), value.n) == 0, "paged_cache_load value", case_id);
 }
 
+void test_rac_strided(int case_id)
+{
+    const int tokens = rnd_in(1, 12), slots = rnd_in(1, 40);
+    const bool odd = rnd() % 4 == 0, has_v = rnd() % 5 != 0;
+    const int64_t krow = odd ? rnd_in(1, 90) : 16 * rnd_in(1, 10), vrow = odd ? rnd_in(1, 90) : 16 * rnd_in(1, 10);
+    // rows may overlap (stride < row) or be far apart; the storage holds exactly the last row's end
+    const int64_t kstride = odd ? rnd_in(0, 200) : 16 * rnd_in(0, 20), vstride = odd ? rnd_in(0, 200) : 16 * rnd_in(0, 20);
+    Buf ks((size_t)((tokens - 1) * kstride + krow), !odd), vs((size_t)((tokens - 1) * vstride + vrow), !odd);
+    Buf kc((size_t)slots * krow, !odd), vc((size_t)slots * vrow, !odd);
+    std::vector<int32_t> map(tokens);
+    std::vector<int> used(slots, 0);
+    for (int t = 0; t < tokens; ++t) {
+        const uint32_t r = rnd() % 8;
+        if (r == 0) {
+            map[t] = -1 - (int)(rnd() % 3);
+        } else if (r == 1) {
+            map[t] = slots + (int)(rnd() % 3);
+        } else {
+            int sidx = rnd_in(0, slots - 1);
+            while (used[sidx]) { // distinct slots, as a block manager hands them out
+                sidx = (sidx + 1) % slots;
+                if (sidx == 0 && tokens > slots) {
+                    break;
+                }
+            }
+            if (used[sidx]) {
+                map[t] = -1;
+            } else {
+                used[sidx] = 1;
+                map[t] = sidx;
+            }
+        }
+    }
+    std::vector<uint8_t> kref(kc.p, kc.p + kc.n), vref(vc.p, vc.p + vc.n);
+    for (int t = 0; t < tokens; ++t) {
+        if (map[t] < 0 || map[t] >= slots) {
+            continue;
+        }
+        std::memcpy(&kref[(size_t)map[t] * krow], ks.p + t * kstride, krow);
+        if (has_v) {
+            std::memcpy(&vref[(size_t)map[t] * vrow], vs.p + t * vstride, vrow);
+        }
+    }
+    RacStridedArgs a{};
+    a.key = ks.p;
+    a.value = has_v ? vs.p : nullptr;
+    a.key_cache = kc.p;
+    a.value_cache = has_v ? vc.p : nullptr;
+    a.slot_mapping = map.data();
+    a.num_tokens = tokens;
+    a.k_row_bytes = krow;
+    a.v_row_bytes = has_v ? vrow : 0;
+    a.k_src_stride = kstride;
+    a.v_src_stride = has_v ? vstride : 0;
+    a.num_slots = slots;
+    a.chunks = rnd_in(1, 4);
+    a.vec16 = !odd;
+    const int threads = rnd_in(1, 6);
+    for (int64_t cta = 0; cta < (int64_t)tokens * a.chunks; ++cta) {
+        for (int tid = 0; tid < threads; ++tid) {
+            rac_strided_body(a, cta, tid, threads);
+        }
+    }
+    expect(std::memcmp(kc.p, kref.data(), kc.n) == 0, "rac_strided key cache", case_id);
+    expect(std::memcmp(vc.p, vref.data(), vc.n) == 0, "rac_strided value cache", case_id);
+}
+
 } // namespace
 
 int main(int argc, char **argv)
@@ -221,7 +288,8 @@ int main(int argc, char **argv)
     for (int i = 0; i < n; ++i) {
         test_block_copy(i);
         test_paged_cache_load(i);
+        test_rac_strided(i);
     }
-    std::printf("%d cases, %d failures\n", 2 * n, failures);
+    std::printf("%d cases, %d failures\n", 3 * n, failures);
     return failures == 0 ? 0 : 1;
 }

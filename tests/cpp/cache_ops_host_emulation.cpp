@@ -86,4 +86,31 @@ int emu_paged_cache_load(const uint8_t *k_cache, const uint8_t *v_cache, const i
     return a.vec16 ? 16 : 1;
 }
 
+int emu_rac_strided(const uint8_t *key, const uint8_t *value, uint8_t *key_cache, uint8_t *value_cache,
+                    const int32_t *slots, int32_t num_tokens, int64_t k_row_bytes, int64_t v_row_bytes, int64_t k_stride,
+                    int64_t v_stride, int64_t num_slots, int32_t chunks, int32_t threads)
+{
+    RacStridedArgs a{};
+    a.key = key;
+    a.value = value;
+    a.key_cache = key_cache;
+    a.value_cache = value_cache;
+    a.slot_mapping = slots;
+    a.num_tokens = num_tokens;
+    a.k_row_bytes = k_row_bytes;
+    a.v_row_bytes = value ? v_row_bytes : 0;
+    a.k_src_stride = k_stride;
+    a.v_src_stride = value ? v_stride : 0;
+    a.num_slots = num_slots;
+    a.chunks = chunks > 0 ? chunks : (int32_t)chunks_for(k_row_bytes > a.v_row_bytes ? k_row_bytes : a.v_row_bytes);
+    a.vec16 = aligned16(key) && aligned16(value) && aligned16(key_cache) && aligned16(value_cache) &&
+              k_row_bytes % 16 == 0 && a.v_row_bytes % 16 == 0 && a.k_src_stride % 16 == 0 && a.v_src_stride % 16 == 0;
+    for (int64_t cta = 0; cta < (int64_t)num_tokens * a.chunks; ++cta) {
+        for (int tid = 0; tid < threads; ++tid) {
+            rac_strided_body(a, cta, tid, threads);
+        }
+    }
+    return a.vec16 ? 16 : 1;
+}
+
 } // extern "C"

@@ -23,6 +23,7 @@ def emu():
         vp, i32, i64 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64
         L.emu_block_copy.argtypes = [vp, vp, vp, vp, vp, i32, i32, i64, i64, i64, i32, i32]
         L.emu_paged_cache_load.argtypes = [vp] * 7 + [i32, i32, i32, i64, i64, i64, i64, i32, vp, i32, i32]
+        L.emu_rac_strided.argtypes = [vp] * 5 + [i32, i64, i64, i64, i64, i64, i32, i32]
         _emu = L
     return _emu
 
@@ -199,3 +200,89 @@ def test_paged_cache_load_operation_checks():
     wrong = list(ins)
     wrong[2] = _T(i32, (16,))
     _expect(capi.ERROR_INVALID_TENSOR_DIM_NUM, op.setup, wrong, outs, ctx)
+
+
+# ------------------------------------------------------------------ ReshapeAndCache over strided inputs
+
+def _qkv_case(seed, tokens, heads, dk, dv, dtype, block_size=4, blocks=7):
+    """K and V as slices of one fused [tokens, q | k | v] projection output (the case the operation is for)."""
+    rng = np.random.default_rng(seed)
+    width = 3 * dk + heads * dk + heads * dv + 5          # some query columns first, padding at the end
+    fused = rng.integers(-120, 120, size=(tokens, width)).astype(dtype)
+    k_off, v_off = 3 * dk, 3 * dk + heads * dk
+    kc = rng.integers(-120, 120, size=(blocks, block_size, heads, dk)).astype(dtype)
+    vc = rng.integers(-120, 120, size=(blocks, block_size, heads, dv)).astype(dtype)
+    slots = rng.choice(np.arange(0, blocks * block_size), size=tokens, replace=False).astype(np.int32)
+    slots[1] = -3                                          # "do not store"
+    return fused, width, k_off, v_off, kc, vc, slots
+
+
+@pytest.mark.parametrize("dtype,dk,dv", [(np.int16, 16, 8), (np.int8, 32, 48), (np.int16, 5, 3)])
+@pytest.mark.parametrize("chunks,threads", [(0, 4), (3, 2)])
+def test_rac_strided_body_matches_oracle(dtype, dk, dv, chunks, threads):
+    heads, tokens = 3, 9
+    fused, width, k_off, v_off, kc, vc, slots = _qkv_case(7, tokens, heads, dk, dv, dtype)
+    ref_k, ref_v = oracle.cache_ops.reshape_and_cache_with_stride(fused, fused, kc.copy(), vc.copy(), slots, heads, dk, dv,
+                                                                  width, k_off, v_off)
+    es = fused.itemsize
+    flat = fused.reshape(-1)
+    k_view, v_view = flat[k_off:], flat[v_off:]
+    emu().emu_rac_strided(_p(k_view), _p(v_view), _p(kc), _p(vc), _p(slots), tokens, heads * dk * es, heads * dv * es,
+                          width * es, width * es, kc.shape[0] * kc.shape[1], chunks, threads)
+    assert np.array_equal(kc, ref_k) and np.array_equal(vc, ref_v)
+    assert (slots < 0).any()                                # skipped tokens are part of the case
+
+
+def test_reshape_and_cache_with_stride_operation_checks():
+    assert ctypes.sizeof(capi.ReshapeAndCacheWithStrideParam) == 24
+    op = capi.Operation(capi.ReshapeAndCacheWithStrideParam())
+    assert (op.name, op.input_num, op.output_num) == ("ReshapeAndCacheWithStrideOperation", 9, 2)
+    siso_p = capi.ReshapeAndCacheWithStrideParam()
+    siso_p.kvCacheCfg = 1
+    siso = capi.Operation(siso_p)
+    assert (siso.input_num, siso.output_num) == (5, 1)
+    bad = capi.ReshapeAndCacheWithStrideParam()
+    bad.compressType = 1
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, bad)
+    bad = capi.ReshapeAndCacheWithStrideParam()
+    bad.kvCacheCfg = 2
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, bad)
+    ctx = capi.Context()
+    f16, i32, i64 = capi.ACL_FLOAT16, capi.ACL_INT32, capi.ACL_INT64
+    strides = np.array([3 * 8 * 128, 128, 1], dtype=np.int64)
+    koff, voff = np.array([8 * 128], dtype=np.int64), np.array([2 * 8 * 128], dtype=np.int64)
+    ins = [_T(f16, (6, 8, 128)), _T(f16, (6, 8, 128)), _T(f16, (10, 16, 8, 128)), _T(f16, (10, 16, 8, 128)),
+           _T(i32, (6,)), _T(i64, (3,), host=strides), _T(i64, (3,), host=strides), _T(i64, (1,), host=koff),
+           _T(i64, (1,), host=voff)]
+    outs = [ins[2], ins[3]]
+    assert op.infer_shape(ins, 2) == [(10, 16, 8, 128), (10, 16, 8, 128)]
+    assert op.setup(ins, outs, ctx) == 0
+    wrong = list(ins)
+    wrong[5] = _T(i64, (3,))
+    _expect(capi.ERROR_INVALID_PARAM, op.setup, wrong, outs, ctx)                     # strides without host data
+    neg = np.array([-1], dtype=np.int64)
+    wrong = list(ins)
+    wrong[7] = _T(i64, (1,), host=neg)
+    _expect(capi.ERROR_INVALID_PARAM, op.setup, wrong, outs, ctx)                     # negative offset
+    wrong = list(ins)
+    wrong[1] = _T(f16, (5, 8, 128))
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, wrong, outs, ctx)                # tokens of key and value
+    wrong = list(ins)
+    wrong[4] = _T(i32, (7,))
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, wrong, outs, ctx)                # slots per token
+    wrong = list(ins)
+    wrong[5] = _T(i32, (3,), host=strides)
+    _expect(capi.ERROR_INVALID_TENSOR_INI_MATCH, op.setup, wrong, outs, ctx)          # strides must be int64
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, ins, [ins[2], _T(f16, (10, 16, 8, 64))], ctx)
+    _expect(capi.ERROR_INVALID_IN_TENSOR_NUM, op.setup, ins[:5], outs, ctx)
+    s_ins = [ins[0], ins[2], ins[4], ins[5], ins[7]]
+    assert siso.setup(s_ins, [ins[2]], ctx) == 0
+    L = capi.lib()
+    fake = ctypes.c_void_p(0x1000)
+    assert L.atb_b200_reshape_and_cache_strided(None, None, fake, None, fake, 4, 64, 0, 128, 0, 10, None) == \
+        capi.ERROR_INVALID_PARAM
+    assert L.atb_b200_reshape_and_cache_strided(fake, fake, fake, None, fake, 4, 64, 64, 128, 128, 10, None) == \
+        capi.ERROR_INVALID_PARAM                                                      # value without its cache
+    assert L.atb_b200_reshape_and_cache_strided(fake, None, fake, None, fake, 4, 64, 0, -16, 0, 10, None) == \
+        capi.ERROR_INVALID_PARAM
+    assert L.atb_b200_reshape_and_cache_strided(fake, None, fake, None, fake, 0, 64, 0, 128, 0, 10, None) == 0

@@ -166,3 +166,42 @@ def test_paged_cache_load_operation_reference_shape():
     assert np.array_equal(key.view(torch.int16).cpu().numpy(), ref_k)
     assert np.array_equal(value.view(torch.int16).cpu().numpy(), ref_v)
     assert (ref_k == 5).all(axis=(1, 2)).any()              # the hole left rows untouched
+
+
+def test_reshape_and_cache_with_stride_from_fused_qkv():
+    """K and V as column slices of one fused [tokens, q | k | v] tensor, through the operator API, bit-exact
+    against the oracle (which gathers the rows and applies the pinned ReshapeAndCache oracle)."""
+    rng = np.random.default_rng(93)
+    tokens, heads, q_heads, d, bs, nb = 37, 8, 32, 128, 128, 6
+    width = (q_heads + 2 * heads) * d
+    fused_h = rng.integers(-30000, 30000, size=(tokens, width), dtype=np.int16)
+    k_off, v_off = q_heads * d, (q_heads + heads) * d
+    kc_h = rng.integers(-30000, 30000, size=(nb, bs, heads, d), dtype=np.int16)
+    vc_h = rng.integers(-30000, 30000, size=(nb, bs, heads, d), dtype=np.int16)
+    slots_h = rng.choice(np.arange(0, nb * bs), size=tokens, replace=False).astype(np.int32)
+    slots_h[5] = -2                                        # "do not store"
+    ref_k, ref_v = oracle.cache_ops.reshape_and_cache_with_stride(fused_h, fused_h, kc_h.copy(), vc_h.copy(), slots_h,
+                                                                  heads, d, d, width, k_off, v_off)
+    fused = torch.from_numpy(fused_h).cuda().view(torch.bfloat16)
+    kc = torch.from_numpy(kc_h).cuda().view(torch.bfloat16)
+    vc = torch.from_numpy(vc_h).cuda().view(torch.bfloat16)
+    slots = _i32(slots_h)
+    strides = np.array([width, d, 1], dtype=np.int64)
+    koff, voff = np.array([k_off], dtype=np.int64), np.array([v_off], dtype=np.int64)
+    T = capi.atb_tensor
+    # key and value: the fused tensor's address with the logical [tokens, heads, d] shape
+    key_t = T(dtype=capi.ACL_BF16, shape=(tokens, heads, d), device_ptr=fused.data_ptr())
+    val_t = T(dtype=capi.ACL_BF16, shape=(tokens, heads, d), device_ptr=fused.data_ptr())
+    i64 = capi.ACL_INT64
+    ins = [key_t, val_t, T(kc), T(vc), T(slots), T(dtype=i64, shape=(3,), host=strides),
+           T(dtype=i64, shape=(3,), host=strides), T(dtype=i64, shape=(1,), host=koff), T(dtype=i64, shape=(1,), host=voff)]
+    outs = [T(kc), T(vc)]
+    op = capi.Operation(capi.ReshapeAndCacheWithStrideParam())
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    ctx = capi.Context(stream.cuda_stream)
+    assert op.setup(ins, outs, ctx) == 0
+    op.execute(ins, outs, None, 0, ctx)
+    torch.cuda.synchronize()
+    assert np.array_equal(kc.view(torch.int16).cpu().numpy(), ref_k)
+    assert np.array_equal(vc.view(torch.int16).cpu().numpy(), ref_v)
