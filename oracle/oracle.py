@@ -31,6 +31,8 @@ def load():
         vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_float
         lib.oracle_paged_attention.restype = ctypes.c_int
         lib.oracle_paged_attention.argtypes = [vp] * 11 + [i32] * 10 + [f32, i32]
+        lib.oracle_paged_attention_ex.restype = ctypes.c_int
+        lib.oracle_paged_attention_ex.argtypes = [vp] * 11 + [i32] * 10 + [f32, i32, vp, i64, i64, vp]
         lib.oracle_reshape_and_cache.restype = ctypes.c_int
         lib.oracle_reshape_and_cache.argtypes = [vp] * 5 + [i32, i64, i64, i64]
         lib.oracle_num_threads.restype = ctypes.c_int
@@ -51,8 +53,12 @@ def num_threads():
 
 def paged_attention(q, k_cache, v_cache, block_tables, context_lens, scale, q_dtype, kv_dtype=None, dv=None,
                     k_descale=None, v_descale=None, k_offset=None, v_offset=None, out=None, want_high=False,
-                    nthreads=0):
+                    nthreads=0, mask=None, logn=None):
     """Decode attention golden.  `v_cache=None` means the MLA combined cache (V = K[..., :dv]).
+
+    mask: additive fp32 bias of shape [B, H, 1, T] (alibi), [B, 1, T] or [B, T] (plain mask per
+    sequence) or [1, T] / [T] (one row for all), T >= the longest context; logn: [B] fp32 factors of
+    the scale (SCALE_TYPE_LOGN).
 
     q: [B,H,Dk] (float16, or uint16 holding bf16 bits); caches [NB,BS,Hkv,D] in the same encoding or
     int8.  Returns out [B,H,Dv] in q's encoding (rows of zero-length sequences keep `out`'s
@@ -77,10 +83,24 @@ def paged_attention(q, k_cache, v_cache, block_tables, context_lens, scale, q_dt
     f32 = lambda a: None if a is None else np.ascontiguousarray(a, dtype=np.float32)
     i32 = lambda a: None if a is None else np.ascontiguousarray(a, dtype=np.int32)
     kd, vd, ko, vo = f32(k_descale), f32(v_descale), i32(k_offset), i32(v_offset)
-    rc = lib.oracle_paged_attention(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(context_lens),
-                                    _ptr(kd), _ptr(vd), _ptr(ko), _ptr(vo), _ptr(out), _ptr(high), B, H, Hkv, Dk,
-                                    dv, dv_row, BS, block_tables.shape[1], _DT[q_dtype], _DT[kv_dtype],
-                                    float(scale), int(nthreads))
+    mb = mh = 0
+    if mask is not None:
+        mask = np.ascontiguousarray(mask, dtype=np.float32)
+        T = mask.shape[-1]
+        assert T >= int(context_lens.max(initial=0)), "the mask is shorter than the longest context"
+        if mask.ndim == 4:
+            assert mask.shape[:3] == (B, H, 1)
+            mb, mh = H * T, T
+        elif mask.size == T:
+            mb = mh = 0
+        else:
+            assert mask.size == B * T
+            mb, mh = T, 0
+    logn = f32(logn)
+    rc = lib.oracle_paged_attention_ex(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(context_lens),
+                                       _ptr(kd), _ptr(vd), _ptr(ko), _ptr(vo), _ptr(out), _ptr(high), B, H, Hkv, Dk,
+                                       dv, dv_row, BS, block_tables.shape[1], _DT[q_dtype], _DT[kv_dtype],
+                                       float(scale), int(nthreads), _ptr(mask), mb, mh, _ptr(logn))
     if rc != 0:
         raise ValueError("oracle_paged_attention rejected its arguments")
     return (out, high) if want_high else out

@@ -165,17 +165,23 @@ static inline void store_elem(void *p, int64_t idx, int dtype, float v)
  *  out          [batch, num_heads, dv] q_dtype; out_high (nullable) same shape, fp32, with the
  *               un-rounded probabilities (the golden's "true_out")
  *
- * Follows ref_masked_attention: fp32 QK^T, * scale, fp32 softmax (max, exp, sum, divide),
+ *  mask         (nullable) fp32 additive bias, score(b, h, t) += mask[b*mask_batch_stride + h*mask_head_stride + t]:
+ *               the alibi mask [batch, heads, 1, max_ctx] (strides heads*max_ctx, max_ctx), the plain
+ *               mask [batch, 1, max_ctx] (strides max_ctx, 0) or one row for all (strides 0, 0)
+ *  logn         (nullable) [batch] fp32, multiplies the scale of sequence b (SCALE_TYPE_LOGN)
+ *
+ * Follows ref_masked_attention: fp32 QK^T, * scale, + mask, fp32 softmax (max, exp, sum, divide),
  * P rounded to the query dtype, fp32 PV, result rounded to the query dtype.
  * A sequence with context_len == 0 is skipped and its output rows are left untouched.
  * Returns 0, or -1 on a bad argument.
  */
-int oracle_paged_attention(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_tables,
-                           const int32_t *context_lens, const float *k_descale, const float *v_descale,
-                           const int32_t *k_offset, const int32_t *v_offset, void *out, float *out_high,
-                           int32_t batch, int32_t num_heads, int32_t kv_heads, int32_t dk, int32_t dv,
-                           int32_t dv_row, int32_t block_size, int32_t max_blocks, int32_t q_dtype,
-                           int32_t kv_dtype, float scale, int32_t nthreads)
+int oracle_paged_attention_ex(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_tables,
+                              const int32_t *context_lens, const float *k_descale, const float *v_descale,
+                              const int32_t *k_offset, const int32_t *v_offset, void *out, float *out_high,
+                              int32_t batch, int32_t num_heads, int32_t kv_heads, int32_t dk, int32_t dv,
+                              int32_t dv_row, int32_t block_size, int32_t max_blocks, int32_t q_dtype,
+                              int32_t kv_dtype, float scale, int32_t nthreads, const float *mask,
+                              int64_t mask_batch_stride, int64_t mask_head_stride, const float *logn)
 {
     if (!q || !k_cache || !v_cache || !block_tables || !context_lens || !out || batch < 0 || num_heads <= 0 ||
         kv_heads <= 0 || num_heads % kv_heads != 0 || dk <= 0 || dv <= 0 || dv > dv_row || block_size <= 0) {
@@ -262,7 +268,12 @@ int oracle_paged_attention(const void *q, const void *k_cache, const void *v_cac
                     for (int d = 0; d < dk; ++d) {
                         acc += qf[d] * kd[d];
                     }
-                    acc *= scale;
+                    /* scale (times the sequence's logN factor), then the additive mask:
+                     * test_paged_attention_common.py:252-254 and :345-347 of the reference */
+                    acc *= logn ? scale * logn[b] : scale;
+                    if (mask) {
+                        acc += mask[(int64_t)b * mask_batch_stride + (int64_t)h * mask_head_stride + t];
+                    }
                     s[t] = acc;
                     if (acc > m) {
                         m = acc;
@@ -309,6 +320,18 @@ int oracle_paged_attention(const void *q, const void *k_cache, const void *v_cac
         free(ph);
     }
     return 0;
+}
+
+int oracle_paged_attention(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_tables,
+                           const int32_t *context_lens, const float *k_descale, const float *v_descale,
+                           const int32_t *k_offset, const int32_t *v_offset, void *out, float *out_high,
+                           int32_t batch, int32_t num_heads, int32_t kv_heads, int32_t dk, int32_t dv,
+                           int32_t dv_row, int32_t block_size, int32_t max_blocks, int32_t q_dtype,
+                           int32_t kv_dtype, float scale, int32_t nthreads)
+{
+    return oracle_paged_attention_ex(q, k_cache, v_cache, block_tables, context_lens, k_descale, v_descale, k_offset,
+                                     v_offset, out, out_high, batch, num_heads, kv_heads, dk, dv, dv_row, block_size,
+                                     max_blocks, q_dtype, kv_dtype, scale, nthreads, NULL, 0, 0, NULL);
 }
 
 /*

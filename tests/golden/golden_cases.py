@@ -129,3 +129,40 @@ def pcl_inputs(spec):
     cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
     return {"k_cache": gen(spec["dk"]), "v_cache": gen(spec["dv"]), "block_tables": tables, "cu_lens": cu,
             "lens": lens.astype(np.int32), "seq_starts": starts}
+
+
+# ------------------------------------------------------------------ PagedAttention with a mask / logN scale
+
+GOLDEN_PA_FEATURE_CASES = [
+    dict(case=Case("alibi_fp16", batch=3, heads=8, kv_heads=8, q_dtype="fp16", ctx=("list", [70, 130, 257]), seed=121),
+         mask="alibi", logn=False),
+    dict(case=Case("norm_mask_bf16_gqa", batch=4, heads=8, kv_heads=2, q_dtype="bf16", ctx=("list", [33, 129, 200, 64]),
+                   seed=122), mask="norm", logn=False),
+    dict(case=Case("logn_fp16", batch=3, heads=4, kv_heads=4, q_dtype="fp16", ctx=("list", [150, 31, 300]), seed=123),
+         mask=None, logn=True),
+    dict(case=Case("alibi_logn_bf16", batch=2, heads=8, kv_heads=4, q_dtype="bf16", ctx=("list", [140, 90]), seed=124),
+         mask="alibi", logn=True),
+]
+
+
+def pa_mask(spec):
+    """The additive mask of a feature case in the query dtype's encoding, built like the reference test
+    builds it (tests/apitest/kernelstest/mix/test_paged_attention_common.py:488-506): alibi
+    [batch, heads, 1, max_ctx] = slope_h * (position - context_len + 1); plain [batch, 1, max_ctx] with
+    -10000 on the first i positions of sequence i."""
+    case = spec["case"]
+    lens = _wl.context_lens(case)
+    T = int(lens.max())
+    if spec["mask"] == "alibi":
+        h = case.heads
+        slopes = np.exp2(-8.0 * (np.arange(h, dtype=np.float32) + 1) / h).astype(np.float32)
+        m = np.zeros((case.batch, h, 1, T), dtype=np.float32)
+        for i, n in enumerate(lens):
+            m[i, :, 0, :n] = slopes[:, None] * (np.arange(n, dtype=np.float32) - n + 1)[None, :]
+    elif spec["mask"] == "norm":
+        m = np.zeros((case.batch, 1, T), dtype=np.float32)
+        for i in range(case.batch):
+            m[i, :, :i] = -10000.0
+    else:
+        return None
+    return _wl.encode(m, case.q_dtype)

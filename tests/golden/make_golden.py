@@ -30,8 +30,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, HERE)
 
-from golden_cases import (GOLDEN_BLOCKCOPY_CASES, GOLDEN_PA_CASES, GOLDEN_PCL_CASES, GOLDEN_RAC_CASES,  # noqa: E402
-                          blockcopy_inputs, load_workloads, pcl_inputs, rac_inputs)
+from golden_cases import (GOLDEN_BLOCKCOPY_CASES, GOLDEN_PA_CASES, GOLDEN_PA_FEATURE_CASES, GOLDEN_PCL_CASES,  # noqa: E402
+                          GOLDEN_RAC_CASES, blockcopy_inputs, load_workloads, pa_mask, pcl_inputs, rac_inputs)
 
 wl = load_workloads()
 
@@ -151,6 +151,36 @@ def run_rac_case(rac_mod, spec):
             "input_sha256": np.frombuffer(digest(inp).encode(), dtype=np.uint8)}
 
 
+def run_pa_feature_case(common, spec):
+    """PagedAttention with the additive mask (alibi: mask_dim 4, plain: mask_dim 3) and / or the logN scale,
+    through the same golden function as the plain cases."""
+    case = spec["case"]
+    d = wl.make_host_inputs(case)
+    tdt = {"fp16": torch.float16, "bf16": torch.bfloat16}[case.q_dtype]
+    t = common.TestPagedAttention()
+    t.compressHead = False
+    t.is_int8_flag = False
+    t.is_quant_flag = 0
+    t.has_bias = False
+    t.scaleType = common.ScaleType.SCALE_LOGN_FP32.value if spec["logn"] else 0
+    t.num_heads, t.kv_heads, t.num_tokens, t.head_size = case.heads, case.kv_heads, case.batch, case.dk
+    mask_np = pa_mask(spec)
+    mask = None if mask_np is None else to_torch(mask_np, case.q_dtype)
+    mask_dim = {None: 0, "alibi": 4, "norm": 3}[spec["mask"]]
+    out = torch.zeros((case.batch, case.heads, case.dv), dtype=torch.float32)
+    high = torch.zeros_like(out)
+    torch.manual_seed(case.seed)                       # the golden draws logN from torch's generator
+    t.ref_single_query_cached_kv_attention(out, high, to_torch(d["q"], case.q_dtype), to_torch(d["k_cache"], case.kvd),
+                                           to_torch(d["v_cache"], case.kvd), d["block_tables"].tolist(),
+                                           d["context_lens"].tolist(), mask, None, False, mask_dim=mask_dim,
+                                           mask_data_type=tdt)
+    res = {"out": from_torch(out, case.q_dtype), "out_high": high.numpy(),
+           "input_sha256": np.frombuffer(digest(d).encode(), dtype=np.uint8)}
+    if spec["logn"]:
+        res["logn"] = t.logN.numpy().astype(np.float32)
+    return res
+
+
 def _as_ref_values(a, dtype):
     """The reference tests hold bf16 data as float32 values; fp16 / int8 as they are."""
     return wl.to_f32(a, dtype) if dtype == "bf16" else a
@@ -207,6 +237,10 @@ def main():
     for spec in GOLDEN_PCL_CASES:
         np.savez_compressed(os.path.join(HERE, f"pcl_{spec['name']}.npz"), **run_pcl_case(pcl, spec))
         print("wrote pcl", spec["name"])
+    for spec in GOLDEN_PA_FEATURE_CASES:
+        res = run_pa_feature_case(common, spec)
+        np.savez_compressed(os.path.join(HERE, f"pa_{spec['case'].name}.npz"), **res)
+        print("wrote", spec["case"].name, res["out"].shape)
     if "--siblings-only" in sys.argv:
         return
     for case in GOLDEN_PA_CASES:

@@ -105,3 +105,28 @@ def test_paged_cache_load_oracle_matches_reference_golden(spec):
     oracle.cache_ops.paged_cache_load(inp["k_cache"], inp["v_cache"], inp["block_tables"], inp["lens"], key2, value2,
                                       seq_starts=inp["seq_starts"], cumulative=False)
     assert np.array_equal(_bits(key2), _bits(key)) and np.array_equal(_bits(value2), _bits(value))
+
+
+# ------------------------------------------------------------------ PagedAttention with a mask / logN scale
+
+from golden_cases import GOLDEN_PA_FEATURE_CASES, pa_mask  # noqa: E402
+
+
+@pytest.mark.parametrize("spec", GOLDEN_PA_FEATURE_CASES, ids=lambda s: s["case"].name)
+def test_oracle_mask_and_logn_match_reference_golden(spec):
+    case = spec["case"]
+    fx = np.load(os.path.join(HERE, f"pa_{case.name}.npz"))
+    d = wl.make_host_inputs(case)
+    assert _digest(d) == bytes(fx["input_sha256"]).decode(), "seeded inputs changed; regenerate the fixtures"
+    mask = pa_mask(spec)
+    mask_f32 = None if mask is None else wl.to_f32(mask, case.q_dtype)
+    logn = fx["logn"] if spec["logn"] else None
+    out, high = oracle.paged_attention(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], d["context_lens"],
+                                       case.qk_scale, case.q_dtype, want_high=True, mask=mask_f32, logn=logn)
+    np.testing.assert_allclose(high, fx["out_high"], rtol=2e-4, atol=2e-5)
+    got, ref = wl.to_f32(out, case.q_dtype), wl.to_f32(fx["out"], case.q_dtype)
+    assert np.abs(got - ref).max() <= 2 * ulp(case.q_dtype) * max(1.0, float(np.abs(ref).max()))
+    # the feature is not a no-op on this case
+    plain = oracle.paged_attention(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], d["context_lens"],
+                                   case.qk_scale, case.q_dtype)
+    assert np.abs(wl.to_f32(plain, case.q_dtype) - ref).max() > 8 * ulp(case.q_dtype)
