@@ -6,5 +6,6 @@ product library never does.  `pa_oracle.c` restates the reference's CPU golden
 tests/apitest/kernelstest/mix/test_reshape_and_cache.py:45-68 of the reference) and is pinned
 against outputs of those Python functions stored under tests/golden/.
 """
-from .oracle import build, load, paged_attention, reshape_and_cache, num_threads  # noqa: F401
+from .oracle import (build, load, multi_latent_attention, num_threads, paged_attention,  # noqa: F401
+                     reshape_and_cache)
 from . import cache_ops  # noqa: F401

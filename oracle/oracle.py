@@ -118,3 +118,14 @@ def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping):
                                       n, krow, vrow, nslots)
     if rc != 0:
         raise ValueError("oracle_reshape_and_cache rejected its arguments")
+
+
+def multi_latent_attention(q_nope, q_rope, ct_kv, k_rope, block_tables, context_lens, scale, q_dtype, **kw):
+    """MultiLatentAttention decode golden with the split cache (cacheMode 1 of the reference): the
+    latent part [.., 512] and the rope part [.., 64] of the query and of the cache are separate
+    tensors; V is the latent part.  The reference's golden computes on the joined tensors and splits
+    them afterwards (tests/apitest/opstest/python/operations/multi_latent_attention/
+    test_multi_latent_attention.py:330-347), so this joins them and runs the combined-cache golden."""
+    q = np.ascontiguousarray(np.concatenate([q_nope, q_rope], axis=-1))
+    cache = np.ascontiguousarray(np.concatenate([ct_kv, k_rope], axis=-1))
+    return paged_attention(q, cache, None, block_tables, context_lens, scale, q_dtype, dv=ct_kv.shape[-1], **kw)

@@ -130,3 +130,20 @@ def test_oracle_mask_and_logn_match_reference_golden(spec):
     plain = oracle.paged_attention(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], d["context_lens"],
                                    case.qk_scale, case.q_dtype)
     assert np.abs(wl.to_f32(plain, case.q_dtype) - ref).max() > 8 * ulp(case.q_dtype)
+
+
+@pytest.mark.parametrize("case", [c for c in GOLDEN_PA_CASES if c.mla], ids=lambda c: c.name)
+def test_split_cache_mla_oracle_matches_reference_golden(case):
+    """MultiLatentAttention with the split cache: the reference's golden is the combined-cache one with
+    query and cache split [512, 64] afterwards, so the same fixtures pin it."""
+    fx = np.load(os.path.join(HERE, f"pa_{case.name}.npz"))
+    d = wl.make_host_inputs(case)
+    q, kc = d["q"], d["k_cache"]
+    out = oracle.multi_latent_attention(np.ascontiguousarray(q[..., :512]), np.ascontiguousarray(q[..., 512:]),
+                                        np.ascontiguousarray(kc[..., :512]), np.ascontiguousarray(kc[..., 512:]),
+                                        d["block_tables"], d["context_lens"], case.qk_scale, case.q_dtype)
+    combined = oracle.paged_attention(q, kc, None, d["block_tables"], d["context_lens"], case.qk_scale, case.q_dtype,
+                                      dv=case.dv)
+    assert np.array_equal(out.view(np.uint16), combined.view(np.uint16))
+    got, ref = wl.to_f32(out, case.q_dtype), wl.to_f32(fx["out"], case.q_dtype)
+    assert np.all(np.abs(got - ref) <= 2 * ulp(case.q_dtype) * np.maximum(np.abs(ref), 2.0 ** -6))
