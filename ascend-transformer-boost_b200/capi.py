@@ -91,6 +91,19 @@ class ReshapeAndCacheWithStrideParam(ctypes.Structure):
     _fields_ = [("compressType", ctypes.c_int32), ("kvCacheCfg", ctypes.c_int32), ("rsv", ctypes.c_uint8 * 16)]
 
 
+class NormRopeReshapeParam(ctypes.Structure):
+    """Byte layout of atb::infer::NormRopeReshapeParam (28 bytes)."""
+    _fields_ = [("precisionMode", ctypes.c_uint32), ("rotaryCoeff", ctypes.c_uint32), ("epsilon", ctypes.c_float),
+                ("rsv", ctypes.c_uint8 * 16)]
+
+    def __init__(self, **kw):
+        super().__init__()
+        self.rotaryCoeff = 2
+        self.epsilon = 1e-5
+        for k, v in kw.items():
+            setattr(self, k, v)
+
+
 class BlockCopyParam(ctypes.Structure):
     """Byte layout of atb::infer::BlockCopyParam (16 bytes)."""
     _fields_ = [("rsv", ctypes.c_uint8 * 16)]
@@ -117,6 +130,7 @@ EXPORTS = [
     "atb_b200_block_copy", "atb_b200_paged_cache_load", "atb_b200_paged_cache_load_workspace_bytes",
     "atb_b200_operation_create_block_copy", "atb_b200_operation_create_paged_cache_load",
     "atb_b200_reshape_and_cache_strided", "atb_b200_operation_create_reshape_and_cache_with_stride",
+    "atb_b200_norm_rope_reshape", "atb_b200_operation_create_norm_rope_reshape",
 ]
 
 _lib = None
@@ -148,6 +162,8 @@ def lib():
         L.atb_b200_operation_create_paged_attention.argtypes = [vp, u64, P(vp)]
         L.atb_b200_operation_create_reshape_and_cache.argtypes = [vp, u64, P(vp)]
         L.atb_b200_operation_create_block_copy.argtypes = [vp, u64, P(vp)]
+        L.atb_b200_operation_create_norm_rope_reshape.argtypes = [vp, u64, P(vp)]
+        L.atb_b200_norm_rope_reshape.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, ctypes.c_float, i64, vp]
         L.atb_b200_operation_create_reshape_and_cache_with_stride.argtypes = [vp, u64, P(vp)]
         L.atb_b200_reshape_and_cache_strided.argtypes = [vp, vp, vp, vp, vp, i32, i64, i64, i64, i64, i64, vp]
         L.atb_b200_operation_create_paged_cache_load.argtypes = [vp, u64, P(vp)]
@@ -505,6 +521,8 @@ class Operation:
         elif isinstance(param, ReshapeAndCacheWithStrideParam):
             fn, what = (lib().atb_b200_operation_create_reshape_and_cache_with_stride,
                         "CreateOperation(ReshapeAndCacheWithStrideParam)")
+        elif isinstance(param, NormRopeReshapeParam):
+            fn, what = lib().atb_b200_operation_create_norm_rope_reshape, "CreateOperation(NormRopeReshapeParam)"
         elif isinstance(param, BlockCopyParam):
             fn, what = lib().atb_b200_operation_create_block_copy, "CreateOperation(BlockCopyParam)"
         elif isinstance(param, PagedCacheLoadParam):

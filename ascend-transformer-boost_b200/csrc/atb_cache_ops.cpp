@@ -426,7 +426,150 @@ private:
     int64_t tokenStride_ = 0, kOffset_ = 0, vOffset_ = 0; // elements, from the host tensors at Setup
 };
 
+// ---------------------------------------------------------------------------------------------------
+// NormRopeReshape: RMSNorm of the latent row, RoPE of the rope row, both written into the token's slot of
+// the MLA latent cache (src/ops/ops_infer/norm_rope_reshape/norm_rope_reshape_operation.cpp of the
+// reference: CreateOperation :35-55, GetInputNum/GetOutputNum :66-74, InferShapeImpl :76-81,
+// InferShapeCheckImpl :83-98, SetupCheckImpl :100-113, CheckDim910B :122-135, NormRopeReshapeCheckImpl910B :137-184).
+class NormRopeReshapeOperation : public OperationBase {
+public:
+    using Param = infer::NormRopeReshapeParam;
+    explicit NormRopeReshapeOperation(const Param &p) : OperationBase("NormRopeReshapeOperation"), param_(p)
+    {
+        for (aclDataType t : {ACL_FLOAT16, ACL_BF16}) {
+            // x, gamma, keyRope, cos, sin, slotMapping, keyCacheIn -> keyCacheOut
+            combs_.push_back({t, t, t, t, t, ACL_INT32, t, t});
+        }
+    }
+    uint32_t GetInputNum() const override { return 7; }
+    uint32_t GetOutputNum() const override { return 1; }
+
+protected:
+    const std::vector<DtypeComb> &DtypeCombs() const override { return combs_; }
+
+    Status InferShapeCheckImpl(const SVector<TensorDesc> &in) const override
+    {
+        if (in.at(0).shape.dimNum != 3 || in.at(1).shape.dimNum != 1 || in.at(2).shape.dimNum != 2 ||
+            in.at(3).shape.dimNum != 2 || in.at(4).shape.dimNum != 2 || in.at(5).shape.dimNum != 1 ||
+            in.at(6).shape.dimNum != 4) {
+            ATB_B200_LOG(ERROR, "NormRopeReshape: invalid intensor dimNum");
+            return ERROR_INVALID_TENSOR_DIM_NUM;
+        }
+        const Dims &x = in.at(0).shape, &g = in.at(1).shape, &kr = in.at(2).shape, &c = in.at(3).shape;
+        const Dims &s = in.at(4).shape, &slots = in.at(5).shape, &kc = in.at(6).shape;
+        if (g.dims[0] != x.dims[2]) {
+            ATB_B200_LOG(ERROR, "NormRopeReshape: gamma should have as many elements as a row of x");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (x.dims[0] != kr.dims[0] || x.dims[0] != c.dims[0] || x.dims[0] != s.dims[0] || x.dims[0] != slots.dims[0]) {
+            ATB_B200_LOG(ERROR, "NormRopeReshape: x, keyRope, cos, sin and slotMapping should have one row per token");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (kr.dims[1] != c.dims[1] || kr.dims[1] != s.dims[1]) {
+            ATB_B200_LOG(ERROR, "NormRopeReshape: keyRope, cos and sin should have the same width");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (kc.dims[3] != x.dims[2] + kr.dims[1]) {
+            ATB_B200_LOG(ERROR, "NormRopeReshape: the cache row should be as wide as x plus keyRope");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (x.dims[2] % 16 != 0) {
+            ATB_B200_LOG(ERROR, "NormRopeReshape: the last dimension of x should be a multiple of 16");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (x.dims[1] != 1 || kc.dims[2] != 1 || kr.dims[1] % 2 != 0) {
+            ATB_B200_LOG(ERROR, "NormRopeReshape: one latent head per token and an even rope width are required");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        return NO_ERROR;
+    }
+
+    Status InferShapeImpl(const SVector<TensorDesc> &in, SVector<TensorDesc> &out) const override
+    {
+        out.at(0) = in.at(6);
+        return NO_ERROR;
+    }
+
+    Status SetupCheckImpl(const SVector<Tensor> &inTensors, const SVector<Tensor> &outTensors) const override
+    {
+        SVector<TensorDesc> descs;
+        for (size_t i = 0; i < inTensors.size(); ++i) {
+            descs.push_back(inTensors.at(i).desc);
+        }
+        const TensorDesc &o = outTensors.at(0).desc;
+        if (o.dtype != descs.at(6).dtype) {
+            return ERROR_INVALID_TENSOR_DTYPE;
+        }
+        if (o.format != descs.at(6).format) {
+            return ERROR_INVALID_TENSOR_FORMAT;
+        }
+        if (!ShapeEqual(o.shape, descs.at(6).shape)) {
+            ATB_B200_LOG(ERROR, "NormRopeReshape: keyCacheOut should have the shape of keyCacheIn");
+            return o.shape.dimNum != descs.at(6).shape.dimNum ? ERROR_INVALID_TENSOR_SIZE : ERROR_INVALID_TENSOR_DIM;
+        }
+        return InferShapeCheckImpl(descs);
+    }
+
+    Status PlanImpl(const VariantPack &, uint64_t &workspaceSize) override
+    {
+        workspaceSize = 0;
+        return NO_ERROR;
+    }
+
+    Status LaunchImpl(const VariantPack &vp, uint8_t *, uint64_t, aclrtStream stream) override
+    {
+        const Tensor &cacheIn = vp.inTensors.at(6);
+        void *cacheOut = vp.outTensors.at(0).deviceData;
+        if (cacheOut != cacheIn.deviceData) {
+            ATB_B200_LOG(ERROR, "NormRopeReshape: the output tensor must alias keyCacheIn (only the tokens' slots are written)");
+            return ERROR_INVALID_TENSOR_ADDR;
+        }
+        for (size_t i = 0; i < 6; ++i) {
+            if (vp.inTensors.at(i).deviceData == nullptr) {
+                return ERROR_INVALID_PARAM;
+            }
+        }
+        if (cacheOut == nullptr) {
+            return ERROR_INVALID_PARAM;
+        }
+        const Dims &x = vp.inTensors.at(0).desc.shape, &kc = cacheIn.desc.shape;
+        const int rc = atb_b200_norm_rope_reshape(
+            vp.inTensors.at(0).deviceData, vp.inTensors.at(1).deviceData, vp.inTensors.at(2).deviceData,
+            vp.inTensors.at(3).deviceData, vp.inTensors.at(4).deviceData,
+            static_cast<const int32_t *>(vp.inTensors.at(5).deviceData), cacheOut, static_cast<int32_t>(x.dims[0]),
+            static_cast<int32_t>(x.dims[2]), static_cast<int32_t>(vp.inTensors.at(2).desc.shape.dims[1]),
+            vp.inTensors.at(0).desc.dtype == ACL_BF16 ? ATB_B200_BF16 : ATB_B200_FP16, param_.epsilon,
+            kc.dims[0] * kc.dims[1], stream);
+        return rc == 0 ? NO_ERROR : (rc == ERROR_INVALID_PARAM ? ERROR_INVALID_PARAM : ERROR_RT_FAIL);
+    }
+
+private:
+    Param param_;
+    std::vector<DtypeComb> combs_;
+};
+
 } // namespace
+
+template <> Status CreateOperation(const infer::NormRopeReshapeParam &opParam, Operation **operation)
+{
+    if (operation == nullptr) {
+        return ERROR_INVALID_PARAM;
+    }
+    if (!RsvIsZero(opParam.rsv, sizeof(opParam.rsv))) {
+        ATB_B200_LOG(ERROR, "NormRopeReshapeParam.rsv must be zero");
+        return ERROR_INVALID_PARAM;
+    }
+    if (!(opParam.epsilon > 0.f)) {
+        ATB_B200_LOG(ERROR, "NormRopeReshape: invalid epsilon, it should be a positive value");
+        return ERROR_INVALID_PARAM;
+    }
+    if (opParam.rotaryCoeff != 2 || opParam.precisionMode != 0) {
+        ATB_B200_LOG(ERROR, "NormRopeReshape: only rotaryCoeff 2 and precisionMode 0 are supported");
+        return ERROR_INVALID_PARAM;
+    }
+    *operation = new (std::nothrow) NormRopeReshapeOperation(opParam);
+    return *operation == nullptr ? ERROR_OUT_OF_HOST_MEMORY : NO_ERROR;
+}
 
 template <> Status CreateOperation(const infer::ReshapeAndCacheWithStrideParam &opParam, Operation **operation)
 {

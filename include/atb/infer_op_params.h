@@ -76,6 +76,16 @@ struct ReshapeAndCacheWithStrideParam {
     uint8_t rsv[16] = {0};
 };
 
+// Fused RMSNorm + RoPE + ReshapeAndCache of the MLA latent cache (include/atb/infer_op_params.h:2697-2716 of
+// the reference).  Inputs x [tokens, 1, dx], gamma [dx], keyRope [tokens, dr], cos [tokens, dr],
+// sin [tokens, dr], slotMapping [tokens], keyCacheIn [blocks, blockSize, 1, dx + dr]; output keyCacheOut.
+struct NormRopeReshapeParam {
+    uint32_t precisionMode = 0;
+    uint32_t rotaryCoeff = 2; // 2: rotate halves (the only mode of the reference kernel and of this one)
+    float epsilon = 1e-5;
+    uint8_t rsv[16] = {0};
+};
+
 // BlockCopy: copy the cache blocks named by srcBlockIndices onto the blocks named by dstBlockIndices
 // (include/atb/infer_op_params.h:1205-1215 of the reference).  Inputs keyCache, valueCache,
 // srcBlockIndices [n], dstBlockIndices [m], cumSum [n] (running total of destinations per source);
@@ -99,6 +109,7 @@ struct PagedCacheLoadParam {
 };
 
 static_assert(sizeof(ReshapeAndCacheWithStrideParam) == 24, "ABI: ReshapeAndCacheWithStrideParam is 24 bytes");
+static_assert(sizeof(NormRopeReshapeParam) == 28, "ABI: NormRopeReshapeParam is 28 bytes");
 static_assert(sizeof(BlockCopyParam) == 16, "ABI: BlockCopyParam is 16 bytes");
 static_assert(sizeof(PagedCacheLoadParam) == 64, "ABI: PagedCacheLoadParam is 64 bytes");
 static_assert(sizeof(ReshapeAndCacheParam) == 24, "ABI: ReshapeAndCacheParam is 24 bytes");

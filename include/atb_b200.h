@@ -238,6 +238,8 @@ int atb_b200_operation_create_block_copy(const void *param, uint64_t param_bytes
 int atb_b200_operation_create_paged_cache_load(const void *param, uint64_t param_bytes, void **operation);
 /* atb::CreateOperation<infer::ReshapeAndCacheWithStrideParam> (24-byte param) */
 int atb_b200_operation_create_reshape_and_cache_with_stride(const void *param, uint64_t param_bytes, void **operation);
+/* atb::CreateOperation<infer::NormRopeReshapeParam> (28-byte param) */
+int atb_b200_operation_create_norm_rope_reshape(const void *param, uint64_t param_bytes, void **operation);
 int atb_b200_operation_input_num(void *operation, uint32_t *n);
 int atb_b200_operation_output_num(void *operation, uint32_t *n);
 /* Operation::GetName (include/atb/operation.h:46 of the reference): copies the NUL-terminated name into
@@ -287,6 +289,17 @@ int atb_b200_reshape_and_cache_strided(const void *key, const void *value, void 
                                        const int32_t *slot_mapping, int32_t num_tokens, int64_t k_row_bytes,
                                        int64_t v_row_bytes, int64_t k_token_stride_bytes, int64_t v_token_stride_bytes,
                                        int64_t num_slots, void *stream);
+
+/* Fused RMSNorm + RoPE + cache write of the MLA latent cache (NormRopeReshapeOperation of the reference,
+ * src/ops/ops_infer/norm_rope_reshape/norm_rope_reshape_operation.cpp; golden tests/apitest/kernelstest/mix/
+ * test_rms_norm_and_rope_and_reshape_and_cache.py:24-72): token t's cache row (slot slot_mapping[t], dx + dr wide)
+ * becomes [ x[t] * rsqrt(mean(x[t]^2) + epsilon) * gamma | key_rope[t] * cos[t] + rotate_half(key_rope[t]) * sin[t] ].
+ * x [tokens, dx], gamma [dx], key_rope / cos_table / sin_table [tokens, dr], all of `dtype` (ATB_B200_FP16 | BF16);
+ * negative slots are skipped, slots >= num_slots dropped. */
+int atb_b200_norm_rope_reshape(const void *x, const void *gamma, const void *key_rope, const void *cos_table,
+                               const void *sin_table, const int32_t *slot_mapping, void *key_cache,
+                               int32_t num_tokens, int32_t dx, int32_t dr, int32_t dtype, float epsilon,
+                               int64_t num_slots, void *stream);
 
 const char *atb_b200_version(void);
 

@@ -8,6 +8,8 @@ Pure byte movement, restated in numpy from the reference's CPU goldens:
                      token j of sequence i always lands in row start_i + j.
   reshape_and_cache_with_stride   the same scatter as ReshapeAndCache
                      (tests/apitest/kernelstest/mix/test_reshape_and_cache.py:45-68) over strided views
+  norm_rope_reshape  tests/apitest/kernelstest/mix/test_rms_norm_and_rope_and_reshape_and_cache.py:24-72
+                     (rmsnorm_golden, rope_golden, rac_golden, golden_calc) and its _bf16 twin
 Pinned against outputs of those reference functions stored under tests/golden/.
 """
 import numpy as np
@@ -72,3 +74,41 @@ def reshape_and_cache_with_stride(key_storage, value_storage, key_cache, value_c
         value = np.ascontiguousarray(value)
     reshape_and_cache(np.ascontiguousarray(key), value, key_cache, value_cache, slot_mapping)
     return key_cache, value_cache
+
+
+def _round_to(a32, dtype):
+    """fp32 -> the storage encoding: float16, or bf16 bits (round to nearest even) as uint16."""
+    if dtype == "fp16":
+        return a32.astype(np.float16)
+    bits = np.ascontiguousarray(a32, dtype=np.float32).view(np.uint32)
+    return ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def _to_f32(a, dtype):
+    if dtype == "fp16":
+        return a.astype(np.float32)
+    return (a.astype(np.uint32) << 16).view(np.float32)
+
+
+def norm_rope_reshape(x, gamma, key_rope, cos, sin, slot_mapping, key_cache, epsilon, dtype):
+    """Fused RMSNorm(x) * gamma | RoPE(key_rope) -> cache row (the MLA latent cache update), in place.
+
+    x [T, 1, Dx], gamma [Dx], key_rope / cos / sin [T, Dr], key_cache [blocks, block_size, 1, Dx + Dr], all in
+    `dtype` encoding (float16, or uint16 holding bf16 bits).  fp32 arithmetic in the golden's order:
+    rms = 1 / sqrt(sum(x^2) / Dx + eps); norm = (rms * x) * gamma; rope = k * cos + rotate_half(k) * sin with
+    rotate_half(k) = (-k[Dr/2:], k[:Dr/2]); each rounded once to the storage type.  Negative slots are skipped."""
+    xf = _to_f32(np.asarray(x), dtype).reshape(x.shape[0], -1)
+    gf = _to_f32(np.asarray(gamma), dtype)
+    square_sum = np.sum(np.square(xf), axis=-1, keepdims=True)
+    rms = (1.0 / np.sqrt(square_sum / np.float32(xf.shape[-1]) + np.float32(epsilon))).astype(np.float32)
+    norm = rms * xf * gf
+    kf, cf, sf = (_to_f32(np.asarray(t), dtype) for t in (key_rope, cos, sin))
+    first, second = np.split(kf, 2, axis=1)
+    rope = kf * cf + np.concatenate((-second, first), axis=1) * sf
+    rows = np.concatenate((_round_to(norm.astype(np.float32), dtype), _round_to(rope.astype(np.float32), dtype)), axis=-1)
+    block_size = key_cache.shape[1]
+    for i, slot in enumerate(np.asarray(slot_mapping)):
+        if slot < 0:
+            continue
+        key_cache[slot // block_size, slot % block_size, 0] = rows[i]
+    return key_cache

@@ -166,3 +166,27 @@ def pa_mask(spec):
     else:
         return None
     return _wl.encode(m, case.q_dtype)
+
+
+# ------------------------------------------------------------------ fused RMSNorm + RoPE + cache write
+
+GOLDEN_NRR_CASES = [
+    dict(name="fp16_mla", tokens=40, dx=512, dr=64, block_size=16, blocks=4, dtype="fp16", eps=1e-5, seed=401),
+    dict(name="bf16_mla", tokens=33, dx=512, dr=64, block_size=8, blocks=6, dtype="bf16", eps=1e-6, seed=402),
+    dict(name="fp16_small", tokens=9, dx=32, dr=16, block_size=4, blocks=5, dtype="fp16", eps=1e-5, seed=403),
+]
+
+
+def nrr_inputs(spec):
+    """Seeded inputs of the fused op, value ranges of a real layer (x ~ N(0,1) * 3, gamma ~ U(0.5, 1.5), cos /
+    sin of random angles) rather than the reference test's U(-100, 100); distinct slots, some negative."""
+    rng = np.random.default_rng(spec["seed"])
+    t, dx, dr = spec["tokens"], spec["dx"], spec["dr"]
+    enc = lambda a: _wl.encode(a.astype(np.float32), spec["dtype"])
+    angle = rng.uniform(0, 2 * np.pi, size=(t, dr // 2)).astype(np.float32)
+    cos = np.concatenate([np.cos(angle), np.cos(angle)], axis=1)
+    sin = np.concatenate([np.sin(angle), np.sin(angle)], axis=1)
+    slots = rng.choice(np.arange(spec["blocks"] * spec["block_size"]), size=t, replace=False).astype(np.int32)
+    slots[2] = -1
+    return {"x": enc(3.0 * rng.standard_normal((t, 1, dx))), "gamma": enc(rng.uniform(0.5, 1.5, size=dx)),
+            "key_rope": enc(rng.standard_normal((t, dr))), "cos": enc(cos), "sin": enc(sin), "slot_mapping": slots}

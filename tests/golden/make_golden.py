@@ -12,6 +12,8 @@ It imports, unmodified, the golden functions of the reference test-suite
   tests/apitest/kernelstest/mix/test_reshape_and_cache.py        (generate_test_data)
   tests/apitest/kernelstest/mix/test_blockcopy.py                (TestBlockCopy.golden_calc)
   tests/apitest/kernelstest/mix/test_paged_cache_load_nd.py      (TestPagedCacheLoad.generate_test_data)
+  tests/apitest/kernelstest/mix/test_rms_norm_and_rope_and_reshape_and_cache{,_bf16}.py
+                                                                 (rmsnorm_golden, rope_golden, rac_golden)
 with the NPU-only imports (`torch_npu`, `op_test`, `operation_test`) replaced by empty stubs, feeds
 them this repository's seeded inputs, and stores the outputs as small .npz files.  The inputs are
 not stored: they are regenerated from the seed and checked against the stored SHA-256.
@@ -31,7 +33,8 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, HERE)
 
 from golden_cases import (GOLDEN_BLOCKCOPY_CASES, GOLDEN_PA_CASES, GOLDEN_PA_FEATURE_CASES, GOLDEN_PCL_CASES,  # noqa: E402
-                          GOLDEN_RAC_CASES, blockcopy_inputs, load_workloads, pa_mask, pcl_inputs, rac_inputs)
+                          GOLDEN_NRR_CASES, GOLDEN_RAC_CASES, blockcopy_inputs, load_workloads, nrr_inputs, pa_mask,
+                          pcl_inputs, rac_inputs)
 
 wl = load_workloads()
 
@@ -181,6 +184,23 @@ def run_pa_feature_case(common, spec):
     return res
 
 
+def run_nrr_case(mod_fp16, mod_bf16, spec):
+    """The fused RMSNorm + RoPE + cache write: the reference's three golden functions in golden_calc's order.
+    fp16: rounded float16 rows; bf16: the reference keeps float32 rows (stored as such)."""
+    inp = nrr_inputs(spec)
+    mod = mod_fp16 if spec["dtype"] == "fp16" else mod_bf16
+    t = mod.TestRmsNormAndRopeAndReshapeAndCacheOperation()
+    val = lambda a: (a if spec["dtype"] == "fp16" else wl.to_f32(a, "bf16"))
+    x, gamma, kr, cos, sin = (val(inp[k]) for k in ("x", "gamma", "key_rope", "cos", "sin"))
+    cache = np.zeros((spec["blocks"], spec["block_size"], 1, spec["dx"] + spec["dr"]),
+                     dtype=np.float16 if spec["dtype"] == "fp16" else np.float32)
+    norm = t.rmsnorm_golden(x, gamma, spec["eps"])
+    rope = t.rope_golden(kr, sin, cos).reshape(sin.shape[0], -1, sin.shape[-1])
+    rows = np.concatenate((norm, rope), axis=-1)
+    out = t.rac_golden(spec["block_size"], rows, inp["slot_mapping"], cache)
+    return {"key_cache": out, "input_sha256": np.frombuffer(digest(inp).encode(), dtype=np.uint8)}
+
+
 def _as_ref_values(a, dtype):
     """The reference tests hold bf16 data as float32 values; fp16 / int8 as they are."""
     return wl.to_f32(a, dtype) if dtype == "bf16" else a
@@ -230,7 +250,12 @@ def main():
                                        "test_paged_attention_operation_mla.py"), "ref_pa_mla")
     blockcopy = _load(os.path.join(kt, "mix/test_blockcopy.py"), "ref_blockcopy")
     pcl = _load(os.path.join(kt, "mix/test_paged_cache_load_nd.py"), "ref_pcl")
+    nrr16 = _load(os.path.join(kt, "mix/test_rms_norm_and_rope_and_reshape_and_cache.py"), "ref_nrr_fp16")
+    nrrbf = _load(os.path.join(kt, "mix/test_rms_norm_and_rope_and_reshape_and_cache_bf16.py"), "ref_nrr_bf16")
     os.chdir(cwd)
+    for spec in GOLDEN_NRR_CASES:
+        np.savez_compressed(os.path.join(HERE, f"nrr_{spec['name']}.npz"), **run_nrr_case(nrr16, nrrbf, spec))
+        print("wrote nrr", spec["name"])
     for spec in GOLDEN_BLOCKCOPY_CASES:
         np.savez_compressed(os.path.join(HERE, f"blockcopy_{spec['name']}.npz"), **run_blockcopy_case(blockcopy, spec))
         print("wrote blockcopy", spec["name"])

@@ -286,3 +286,50 @@ def test_reshape_and_cache_with_stride_operation_checks():
     assert L.atb_b200_reshape_and_cache_strided(fake, None, fake, None, fake, 4, 64, 0, -16, 0, 10, None) == \
         capi.ERROR_INVALID_PARAM
     assert L.atb_b200_reshape_and_cache_strided(fake, None, fake, None, fake, 0, 64, 0, 128, 0, 10, None) == 0
+
+
+# ------------------------------------------------------------------ fused RMSNorm + RoPE + cache write
+
+def test_norm_rope_reshape_operation_checks():
+    assert ctypes.sizeof(capi.NormRopeReshapeParam) == 28
+    op = capi.Operation(capi.NormRopeReshapeParam())
+    assert (op.name, op.input_num, op.output_num) == ("NormRopeReshapeOperation", 7, 1)
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, capi.NormRopeReshapeParam(epsilon=0.0))
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, capi.NormRopeReshapeParam(rotaryCoeff=4))
+    bad = capi.NormRopeReshapeParam()
+    bad.rsv[15] = 1
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, bad)
+    ctx = capi.Context()
+    bf, i32 = capi.ACL_BF16, capi.ACL_INT32
+    ins = [_T(bf, (32, 1, 512)), _T(bf, (512,)), _T(bf, (32, 64)), _T(bf, (32, 64)), _T(bf, (32, 64)), _T(i32, (32,)),
+           _T(bf, (10, 128, 1, 576))]
+    outs = [ins[6]]
+    assert op.infer_shape(ins, 1) == [(10, 128, 1, 576)]
+    assert op.setup(ins, outs, ctx) == 0
+    wrong = list(ins)
+    wrong[1] = _T(bf, (256,))
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, wrong, outs, ctx)                # gamma vs x
+    wrong = list(ins)
+    wrong[3] = _T(bf, (32, 32))
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, wrong, outs, ctx)                # cos vs keyRope
+    wrong = list(ins)
+    wrong[6] = _T(bf, (10, 128, 1, 512))
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, wrong, [wrong[6]], ctx)          # cache row width
+    wrong = list(ins)
+    wrong[5] = _T(i32, (31,))
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, wrong, outs, ctx)                # one slot per token
+    wrong = list(ins)
+    wrong[0] = _T(bf, (32, 512))
+    _expect(capi.ERROR_INVALID_TENSOR_DIM_NUM, op.setup, wrong, outs, ctx)
+    wrong = list(ins)
+    wrong[1] = _T(capi.ACL_FLOAT16, (512,))
+    _expect(capi.ERROR_INVALID_TENSOR_INI_MATCH, op.setup, wrong, outs, ctx)          # mixed dtypes
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, ins, [_T(bf, (10, 64, 1, 576))], ctx)
+    L = capi.lib()
+    fake = ctypes.c_void_p(0x1000)
+    ok = [fake] * 7 + [4, 512, 64, 1, 1e-5, 1280, None]
+    assert L.atb_b200_norm_rope_reshape(*([fake] * 7 + [0, 512, 64, 1, 1e-5, 1280, None])) == 0     # no tokens
+    for pos, val in [(0, None), (9, 63), (10, 2), (11, 0.0), (12, 0)]:
+        args = list(ok)
+        args[pos] = val
+        assert L.atb_b200_norm_rope_reshape(*args) == capi.ERROR_INVALID_PARAM, pos

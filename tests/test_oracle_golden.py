@@ -147,3 +147,27 @@ def test_split_cache_mla_oracle_matches_reference_golden(case):
     assert np.array_equal(out.view(np.uint16), combined.view(np.uint16))
     got, ref = wl.to_f32(out, case.q_dtype), wl.to_f32(fx["out"], case.q_dtype)
     assert np.all(np.abs(got - ref) <= 2 * ulp(case.q_dtype) * np.maximum(np.abs(ref), 2.0 ** -6))
+
+
+# ------------------------------------------------------------------ fused RMSNorm + RoPE + cache write
+
+from golden_cases import GOLDEN_NRR_CASES, nrr_inputs  # noqa: E402
+
+
+@pytest.mark.parametrize("spec", GOLDEN_NRR_CASES, ids=lambda s: s["name"])
+def test_norm_rope_reshape_oracle_matches_reference_golden(spec):
+    fx = np.load(os.path.join(HERE, f"nrr_{spec['name']}.npz"))
+    inp = nrr_inputs(spec)
+    assert _digest(inp) == bytes(fx["input_sha256"]).decode(), "seeded inputs changed; regenerate the fixtures"
+    store = np.float16 if spec["dtype"] == "fp16" else np.uint16
+    cache = np.zeros((spec["blocks"], spec["block_size"], 1, spec["dx"] + spec["dr"]), dtype=store)
+    oracle.cache_ops.norm_rope_reshape(inp["x"], inp["gamma"], inp["key_rope"], inp["cos"], inp["sin"],
+                                       inp["slot_mapping"], cache, spec["eps"], spec["dtype"])
+    if spec["dtype"] == "fp16":
+        # the reference rounds to float16 itself: bit-exact
+        assert np.array_equal(cache.view(np.uint16), fx["key_cache"].view(np.uint16))
+    else:
+        # the reference keeps float32 rows for bf16 inputs: ours are those rows rounded to bf16 (half an ulp)
+        got, ref = wl.to_f32(cache, "bf16"), fx["key_cache"]
+        assert np.all(np.abs(got - ref) <= 2.0 ** -8 * np.maximum(np.abs(ref), 2.0 ** -20))
+    assert np.count_nonzero(cache) > 0

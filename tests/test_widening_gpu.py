@@ -205,3 +205,41 @@ def test_reshape_and_cache_with_stride_from_fused_qkv():
     torch.cuda.synchronize()
     assert np.array_equal(kc.view(torch.int16).cpu().numpy(), ref_k)
     assert np.array_equal(vc.view(torch.int16).cpu().numpy(), ref_v)
+
+
+# ------------------------------------------------------------------ fused RMSNorm + RoPE + cache write
+
+from golden_cases import GOLDEN_NRR_CASES, nrr_inputs  # noqa: E402
+
+
+@pytest.mark.parametrize("spec", GOLDEN_NRR_CASES, ids=lambda s: s["name"])
+def test_norm_rope_reshape_matches_oracle(spec):
+    """Through the operator API against the oracle (itself pinned on the reference golden).  The tolerance is
+    the reference test's own for this operation (test_rms_norm_and_rope_and_reshape_and_cache.py:74-86:
+    |diff| <= 2^-8 * max(1, |golden|)); the kernel's summation order, emulated on the CPU, reproduces the
+    oracle bit for bit on these cases, so nearly all elements must also be identical."""
+    inp = nrr_inputs(spec)
+    dt = spec["dtype"]
+    shape = (spec["blocks"], spec["block_size"], 1, spec["dx"] + spec["dr"])
+    rng = np.random.default_rng(spec["seed"] + 1)
+    cache_h = wl.encode(rng.standard_normal(shape).astype(np.float32), dt)        # other slots must survive
+    ref = cache_h.copy()
+    oracle.cache_ops.norm_rope_reshape(inp["x"], inp["gamma"], inp["key_rope"], inp["cos"], inp["sin"],
+                                       inp["slot_mapping"], ref, spec["eps"], dt)
+    d = {k: to_dev(inp[k], dt) for k in ("x", "gamma", "key_rope", "cos", "sin")}
+    slots = _i32(inp["slot_mapping"])
+    cache = to_dev(cache_h, dt)
+    T = capi.atb_tensor
+    op = capi.Operation(capi.NormRopeReshapeParam(epsilon=spec["eps"]))
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    ctx = capi.Context(stream.cuda_stream)
+    ins = [T(d["x"]), T(d["gamma"]), T(d["key_rope"]), T(d["cos"]), T(d["sin"]), T(slots), T(cache)]
+    outs = [T(cache)]
+    assert op.setup(ins, outs, ctx) == 0
+    op.execute(ins, outs, None, 0, ctx)
+    torch.cuda.synchronize()
+    got_bits = wl.torch_to_host(cache, dt)
+    got, want = wl.to_f32(got_bits, dt), wl.to_f32(ref, dt)
+    assert np.all(np.abs(got - want) <= 2.0 ** -8 * np.maximum(1.0, np.abs(want)))
+    assert np.mean(got_bits.view(np.uint16) == ref.view(np.uint16)) > 0.99
