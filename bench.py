@@ -10,6 +10,9 @@ tensors.  With N > 1 the kv heads are sharded over the ranks (strong scaling, on
 and the per-shard outputs are gathered; the MLA configuration has a single kv head and is sharded by
 sequence instead (contiguous chunks of the batch per rank).
 
+`--op block_copy | paged_cache_load | norm_rope_reshape` times one of the cache-management kernels instead
+(1 GPU, its own JSON line with the achieved HBM bandwidth); the default is the decode hot path.
+
 Prints ONE JSON line: `value` is whole-job KV GB/s with all inputs resident in HBM (device-timed),
 `e2e` the same metric through the atb operator API with host buffers (H2D of the step's inputs,
 re-planning, D2H of the output inside the timed region), `roofline` the attention kernel's achieved
@@ -185,11 +188,16 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
                     help="N>1: attention stores into every rank's gathered buffer (p2p) or a separate NCCL all-gather")
+    ap.add_argument("--op", default="decode", choices=["decode", "block_copy", "paged_cache_load", "norm_rope_reshape"],
+                    help="decode (default): the hot path; the others time one cache-management kernel on 1 GPU")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
     pkg = entry.load_package()
     wl, capi = pkg.workloads, pkg.capi
+    if args.op != "decode":
+        run_cache_op_bench(args, capi)
+        return
     case = wl.CONFIGS[args.config]
     if args.impl == "reference":
         run_reference_arm(args, case, wl)
@@ -357,6 +365,92 @@ def main():
         exchange.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_cache_op_bench(args, capi):
+    """Times one cache-management kernel (1 GPU, device-resident inputs larger than L2, CUDA events on the
+    launching stream) and prints its achieved HBM bandwidth: algorithmic bytes = bytes read + bytes written."""
+    import torch
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    capi.lib()
+    rng = np.random.default_rng(2024)
+    stream = torch.cuda.Stream()
+    heads, d, bs = 8, 128, 128                         # the cache geometry of benchmark configuration 2
+    steps = min(args.steps, 200)
+    if args.op == "block_copy":
+        nb = 4096                                      # 2 x 1 GiB of cache
+        kc = torch.empty((nb, bs, heads, d), dtype=torch.bfloat16, device=dev).normal_()
+        vc = torch.empty_like(kc).normal_()
+        n_src, per = 512, 3                            # 512 sources copied to 3 blocks each
+        perm = rng.permutation(nb)
+        src = torch.from_numpy(perm[:n_src].astype(np.int32)).to(dev)
+        dst = torch.from_numpy(perm[n_src:n_src + n_src * per].astype(np.int32)).to(dev)
+        cum = torch.from_numpy((np.arange(1, n_src + 1) * per).astype(np.int32)).to(dev)
+        block_bytes = kc[0].numel() * kc.element_size()
+        moved = 2 * 2 * n_src * per * block_bytes      # K and V, read + write
+        workload = f"{n_src} source blocks x {per} copies, block {block_bytes >> 10} KiB, K and V"
+
+        def step():
+            capi.block_copy(kc, vc, src, dst, cum, stream_ptr=stream.cuda_stream)
+    elif args.op == "paged_cache_load":
+        batch, ctx = 64, 3072
+        blocks_per_seq = ctx // bs
+        nb = 2 * batch * blocks_per_seq
+        kc = torch.empty((nb, bs, heads, d), dtype=torch.bfloat16, device=dev).normal_()
+        vc = torch.empty_like(kc).normal_()
+        tables = torch.from_numpy(rng.permutation(nb)[:batch * blocks_per_seq].reshape(batch, -1).astype(np.int32)).to(dev)
+        cu = torch.from_numpy((np.arange(batch + 1) * ctx).astype(np.int32)).to(dev)
+        key = torch.empty((batch * ctx, heads, d), dtype=torch.bfloat16, device=dev)
+        value = torch.empty_like(key)
+        moved = 2 * 2 * key.numel() * key.element_size()
+        workload = f"{batch} sequences x {ctx} tokens, {heads} heads x {d}, bf16, K and V"
+
+        def step():
+            capi.paged_cache_load(kc, vc, tables, cu, key, value, cumulative=True, stream_ptr=stream.cuda_stream)
+    else:
+        tokens, dx, dr, nb = 4096, 512, 64, 4096       # a prefill-sized batch of new tokens: decode is latency-bound
+        x = torch.empty((tokens, 1, dx), dtype=torch.bfloat16, device=dev).normal_()
+        gamma = torch.empty(dx, dtype=torch.bfloat16, device=dev).uniform_(0.5, 1.5)
+        kr = torch.empty((tokens, dr), dtype=torch.bfloat16, device=dev).normal_()
+        cos, sin = torch.empty_like(kr).uniform_(-1, 1), torch.empty_like(kr).uniform_(-1, 1)
+        slots = torch.from_numpy(rng.permutation(nb * bs)[:tokens].astype(np.int32)).to(dev)
+        cache = torch.zeros((nb, bs, 1, dx + dr), dtype=torch.bfloat16, device=dev)
+        moved = tokens * ((dx + 3 * dr) * 2 + (dx + dr) * 2 + 4) + dx * 2
+        workload = f"{tokens} new tokens, latent {dx} + rope {dr}, bf16"
+        L = capi.lib()
+
+        def step():
+            rc = L.atb_b200_norm_rope_reshape(x.data_ptr(), gamma.data_ptr(), kr.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                              slots.data_ptr(), cache.data_ptr(), tokens, dx, dr, 1, 1e-6, nb * bs,
+                                              stream.cuda_stream)
+            if rc != 0:
+                raise RuntimeError(f"C ABI call failed with {rc}")
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            step()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(0)
+        sampler.start()
+        time.sleep(0.25)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            step()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        clocks = sampler.stop()
+    peak, peak_kind = measured_peak_gbs()
+    achieved = moved / (ms * 1e-3) / 1e9
+    print(json.dumps({"metric": "cache_op_bandwidth", "value": achieved, "unit": UNIT, "n_gpus": 1, "steps": steps,
+                      "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "data": "synthetic",
+                      "config": {"workload": f"{args.op}: {workload}",
+                                 "l2": "working set larger than the 126 MB L2" if moved > 252e6 else "fits in L2: latency-bound"},
+                      "gpu_launches": steps, "clocks": clocks,
+                      "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
+                                   "peak_kind": "of " + peak_kind, "kernel": args.op, "kernel_ms": ms, "traffic": None}}))
 
 
 def run_e2e(args, case, wl, capi, d, lens, dev, world, gathered):
