@@ -68,7 +68,8 @@ struct PaArgs {
     uint32_t *peer_flags[8];
     int32_t xchg_rank;
     uint32_t xchg_epoch;
-    // optional event probe (CTA 0 only): trace[0] = number of events, then (tag << 56 | index << 40 | cycles)
+    // optional event probe of one CTA (CTA number = trace_cap >> 24, capacity = its low 24 bits):
+    // trace[0] = number of events, then (tag << 56 | index << 40 | cycles)
     unsigned long long *trace;
     uint32_t trace_cap;
 };
@@ -76,9 +77,9 @@ struct PaArgs {
 __device__ __forceinline__ void probe(const PaArgs &a, unsigned tag, unsigned idx)
 {
 #ifdef __CUDA_ARCH__
-    if (a.trace != nullptr && blockIdx.x == 0) {
+    if (a.trace != nullptr && blockIdx.x == (a.trace_cap >> 24)) {
         const unsigned long long n = atomicAdd(a.trace, 1ull);
-        if (n + 1 < a.trace_cap) {
+        if (n + 1 < (a.trace_cap & 0xffffffu)) {
             a.trace[n + 1] = ((unsigned long long)tag << 56) | ((unsigned long long)(idx & 0xffffu) << 40) |
                              ((unsigned long long)clock64() & 0xffffffffffull);
         }

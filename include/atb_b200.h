@@ -174,9 +174,9 @@ int atb_b200_reshape_and_cache(const void *key, const void *value, void *key_cac
 int atb_b200_pa_plan_device_status(atb_b200_pa_plan *plan, void *workspace, void *stream, int32_t *status);
 
 /* Optional event probe for kernel tuning (the role of the reference's Probe hooks,
- * src/atb/utils/probe.h:19-58): `device_events` is a zeroed device array of `capacity` uint64; CTA 0 of
- * the MLA kernel appends (tag << 56 | index << 40 | SM cycle counter) records, element 0 counts them.
- * NULL switches it off. */
+ * src/atb/utils/probe.h:19-58): `device_events` is a zeroed device array of (capacity & 0xffffff) uint64;
+ * CTA number (capacity >> 24) of the MLA kernel appends (tag << 56 | index << 40 | SM cycle counter) records,
+ * element 0 counts them.  NULL switches it off. */
 int atb_b200_pa_plan_set_trace(atb_b200_pa_plan *plan, void *device_events, uint32_t capacity);
 
 /* Optional timing of the attention kernel alone: when enabled, every launch records a pair of
