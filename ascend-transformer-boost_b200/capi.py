@@ -36,13 +36,14 @@ class PaDesc(ctypes.Structure):
                 ("block_size", ctypes.c_int32), ("num_blocks", ctypes.c_int32),
                 ("max_blocks_per_seq", ctypes.c_int32), ("q_dtype", ctypes.c_int32), ("kv_dtype", ctypes.c_int32),
                 ("qk_scale", ctypes.c_float), ("kernel", ctypes.c_int32), ("sm_count", ctypes.c_int32),
-                ("reserved", ctypes.c_int32 * 4)]
+                ("rope_dim", ctypes.c_int32), ("reserved", ctypes.c_int32 * 3)]
 
 
 class PaTensors(ctypes.Structure):
     _fields_ = [("q", ctypes.c_void_p), ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p),
                 ("block_tables", ctypes.c_void_p), ("k_descale", ctypes.c_void_p), ("v_descale", ctypes.c_void_p),
-                ("k_offset", ctypes.c_void_p), ("v_offset", ctypes.c_void_p), ("out", ctypes.c_void_p)]
+                ("k_offset", ctypes.c_void_p), ("v_offset", ctypes.c_void_p), ("out", ctypes.c_void_p),
+                ("q_rope", ctypes.c_void_p), ("k_rope_cache", ctypes.c_void_p)]
 
 
 class PaPlanInfo(ctypes.Structure):
@@ -206,8 +207,9 @@ def _check(rc, what):
 # ------------------------------------------------------------------ kernel level
 
 def make_desc(batch, num_heads, kv_heads, dk, dv, block_size, num_blocks, max_blocks, q_dtype, kv_dtype=None,
-              qk_scale=1.0, v_row_dim=None, kernel=KERNEL_AUTO, sm_count=0):
+              qk_scale=1.0, v_row_dim=None, kernel=KERNEL_AUTO, sm_count=0, rope_dim=0):
     d = PaDesc()
+    d.rope_dim = rope_dim
     d.batch, d.num_heads, d.kv_heads = batch, num_heads, kv_heads
     d.head_dim_k, d.head_dim_v, d.v_row_dim = dk, dv, (v_row_dim or dv)
     d.block_size, d.num_blocks, d.max_blocks_per_seq = block_size, num_blocks, max_blocks
@@ -301,8 +303,10 @@ def torch_stream_ptr():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def pa_tensors(q, k_cache, v_cache, block_tables, out, k_descale=None, v_descale=None, k_offset=None, v_offset=None):
+def pa_tensors(q, k_cache, v_cache, block_tables, out, k_descale=None, v_descale=None, k_offset=None, v_offset=None,
+               q_rope=None, k_rope_cache=None):
     t = PaTensors()
+    t.q_rope, t.k_rope_cache = _ptr(q_rope), _ptr(k_rope_cache)
     t.q, t.k_cache = _ptr(q), _ptr(k_cache)
     t.v_cache = _ptr(v_cache if v_cache is not None else k_cache)
     t.block_tables, t.out = _ptr(block_tables), _ptr(out)

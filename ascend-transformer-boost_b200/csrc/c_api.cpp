@@ -357,7 +357,8 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
                           void *workspace, uint64_t workspace_bytes, void *stream_v)
 {
     if (plan == nullptr || t == nullptr || t->q == nullptr || t->k_cache == nullptr || t->v_cache == nullptr ||
-        t->block_tables == nullptr || (t->out == nullptr && peers == nullptr)) {
+        t->block_tables == nullptr || (t->out == nullptr && peers == nullptr) ||
+        (plan->hp.desc.rope_dim != 0 && (t->q_rope == nullptr || t->k_rope_cache == nullptr))) {
         return kErrInvalidParam;
     }
     HostPlan &h = plan->hp;
@@ -403,6 +404,11 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
     a.k_offset = t->k_offset;
     a.v_offset = t->v_offset;
     a.out = t->out;
+    a.q_rope = d.rope_dim != 0 ? t->q_rope : nullptr;
+    a.k_rope = d.rope_dim != 0 ? t->k_rope_cache : nullptr;
+    if (d.rope_dim != 0 && (a.q_rope == nullptr || a.k_rope == nullptr)) {
+        return kErrInvalidParam;
+    }
     a.plan.group_begin = reinterpret_cast<const int32_t *>(blob + h.off_group_begin);
     a.plan.items = reinterpret_cast<const PaItem *>(blob + h.off_items);
     a.plan.seq_part_base = reinterpret_cast<const int32_t *>(blob + h.off_part_base);

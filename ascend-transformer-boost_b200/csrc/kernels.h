@@ -26,7 +26,8 @@ bool pa_tma_mma_i8_supported(int dk, int dv, int v_row_dim, int block_size, int 
 cudaError_t launch_pa_tma_mma_i8(const PaArgs &args, int q_dtype, int num_blocks, cudaStream_t stream);
 
 // MLA combined cache (Dk 576, Dv 512, one kv head): TMA + tcgen05/TMEM, 64 query heads per CTA.
-bool pa_mla_tc5_supported(int dk, int dv, int v_row_dim, int block_size, int kv_heads, int q_dtype, int kv_dtype);
+bool pa_mla_tc5_supported(int dk, int dv, int v_row_dim, int rope_dim, int block_size, int kv_heads, int q_dtype,
+                          int kv_dtype);
 cudaError_t launch_pa_mla_tc5(const PaArgs &args, int q_dtype, int num_blocks, cudaStream_t stream);
 
 // Merges the split-KV partials of every split sequence into the output.

@@ -144,7 +144,7 @@ enum Bar { kQFull = 0, kQEmpty, kKvFull0, kKvFull1, kKvFull2, kKvEmpty0, kKvEmpt
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
-pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const PaArgs a)
+pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap rmap, const PaArgs a)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -215,7 +215,11 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const PaArgs a)
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             tma_prefetch_desc(&kmap);
+            tma_prefetch_desc(&rmap);
         }
+        // The rope part of a row (elements 512..575) is either the tail of the combined cache row or, with the
+        // split cache, a row of a tensor of its own; rmap describes whichever holds it.
+        const int rope_x0 = a.k_rope != nullptr ? 0 : kDv;
         uint32_t g = 0; // global stage counter
         bool alive = true;
         for (int it = item_begin, i = 0; it < item_end && alive; ++it, ++i) {
@@ -239,9 +243,10 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const PaArgs a)
                             uint8_t *dst = kv_smem + s * kTileBytes;
                             probe(a, 1, g);
                             mbar_expect_tx(&bars[kKvFull0 + s], kTileBytes);
-                            for (int at = 0; at < kAtoms; ++at) {
+                            for (int at = 0; at < kAtoms - 1; ++at) {
                                 tma_load_4d(dst + at * kAtomBytes, &kmap, &bars[kKvFull0 + s], at * 64, 0, tok_in_blk, b);
                             }
+                            tma_load_4d(dst + (kAtoms - 1) * kAtomBytes, &rmap, &bars[kKvFull0 + s], rope_x0, 0, tok_in_blk, b);
                         }
                     }
                     alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
@@ -344,14 +349,19 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const PaArgs a)
             tc_fence_after();
             {
                 const bool has_row = s_lane && row < nh;
-                const uint4 *qrow = reinterpret_cast<const uint4 *>(static_cast<const T *>(a.q) +
-                                                                    ((int64_t)item.seq * a.num_heads + head0 + (has_row ? row : 0)) * kDk);
+                const int64_t qidx = (int64_t)item.seq * a.num_heads + head0 + (has_row ? row : 0);
+                // combined rows: 576 elements; split cache: 512 latent elements here, 64 rope elements in q_rope
+                const bool split = a.q_rope != nullptr;
+                const uint4 *qrow = reinterpret_cast<const uint4 *>(static_cast<const T *>(a.q) + qidx * (split ? kDv : kDk));
+                const uint4 *qrope = split ? reinterpret_cast<const uint4 *>(static_cast<const T *>(a.q_rope) + qidx * (kDk - kDv))
+                                           : qrow + kDv / 8;
 #pragma unroll 1
                 for (int c = 0; c < kAtoms; ++c) { // 64 elements = 128 B = 32 columns per step
+                    const uint4 *src = c < kAtoms - 1 ? qrow + c * 8 : qrope;
                     uint32_t t[32];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        const uint4 v = has_row ? __ldg(qrow + c * 8 + j) : make_uint4(0, 0, 0, 0);
+                        const uint4 v = has_row ? __ldg(src + j) : make_uint4(0, 0, 0, 0);
                         t[4 * j] = v.x;
                         t[4 * j + 1] = v.y;
                         t[4 * j + 2] = v.z;
@@ -563,7 +573,8 @@ EncodeFn get_encode_fn()
     return fn;
 }
 
-template <typename T> cudaError_t launch_typed(const PaArgs &args, const CUtensorMap &km, cudaStream_t s)
+template <typename T>
+cudaError_t launch_typed(const PaArgs &args, const CUtensorMap &km, const CUtensorMap &rm, cudaStream_t s)
 {
     auto kern = pa_mla_tc5_kernel<T>;
     static bool configured[64] = {};
@@ -588,14 +599,17 @@ template <typename T> cudaError_t launch_typed(const PaArgs &args, const CUtenso
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, km, args);
+    return cudaLaunchKernelEx(&cfg, kern, km, rm, args);
 }
 
 } // namespace
 
-bool pa_mla_tc5_supported(int dk, int dv, int v_row_dim, int block_size, int kv_heads, int q_dtype, int kv_dtype)
+bool pa_mla_tc5_supported(int dk, int dv, int v_row_dim, int rope_dim, int block_size, int kv_heads, int q_dtype,
+                          int kv_dtype)
 {
-    return dk == kDk && dv == kDv && v_row_dim == kDk && kv_heads == 1 && block_size >= kTok && block_size % kTok == 0 &&
+    // combined cache: rows of 576; split cache: latent rows of 512 plus rope rows of 64 in a tensor of their own
+    const bool rows_ok = (rope_dim == 0 && v_row_dim == kDk) || (rope_dim == kDk - kDv && v_row_dim == kDv);
+    return dk == kDk && dv == kDv && rows_ok && kv_heads == 1 && block_size >= kTok && block_size % kTok == 0 &&
            block_size <= 256 && (q_dtype == kFp16 || q_dtype == kBf16) && kv_dtype == q_dtype;
 }
 
@@ -606,20 +620,23 @@ cudaError_t launch_pa_mla_tc5(const PaArgs &args, int q_dtype, int num_blocks, c
         return cudaErrorInvalidValue;
     }
     const CUtensorMapDataType dt = q_dtype == kBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUtensorMap km;
-    {
-        // cache [num_blocks][block_size][1][576]; box = 64 elements x 64 tokens of one block
-        cuuint64_t dims[4] = {(cuuint64_t)kDk, 1, (cuuint64_t)args.block_size, (cuuint64_t)num_blocks};
-        cuuint64_t strides[3] = {(cuuint64_t)kDk * 2, (cuuint64_t)kDk * 2, (cuuint64_t)args.block_size * kDk * 2};
+    // cache [num_blocks][block_size][1][row]; box = 64 elements x 64 tokens of one block
+    auto encode = [&](CUtensorMap *map, const void *base, int row) {
+        cuuint64_t dims[4] = {(cuuint64_t)row, 1, (cuuint64_t)args.block_size, (cuuint64_t)num_blocks};
+        cuuint64_t strides[3] = {(cuuint64_t)row * 2, (cuuint64_t)row * 2, (cuuint64_t)args.block_size * row * 2};
         cuuint32_t box[4] = {64, 1, kTok, 1};
         cuuint32_t estr[4] = {1, 1, 1, 1};
-        if (fn(&km, dt, 4, const_cast<void *>(args.k_cache), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
-            return cudaErrorInvalidValue;
-        }
+        return fn(map, dt, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    };
+    const bool split = args.k_rope != nullptr;
+    CUtensorMap km, rm;
+    if (!encode(&km, args.k_cache, split ? kDv : kDk) ||
+        !encode(&rm, split ? args.k_rope : args.k_cache, split ? kDk - kDv : kDk)) {
+        return cudaErrorInvalidValue;
     }
-    return q_dtype == kFp16 ? launch_typed<__half>(args, km, stream) : launch_typed<__nv_bfloat16>(args, km, stream);
+    return q_dtype == kFp16 ? launch_typed<__half>(args, km, rm, stream) : launch_typed<__nv_bfloat16>(args, km, rm, stream);
 }
 
 } // namespace atb_b200

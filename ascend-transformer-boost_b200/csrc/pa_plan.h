@@ -68,6 +68,9 @@ struct PaArgs {
     uint32_t *peer_flags[8];
     int32_t xchg_rank;
     uint32_t xchg_epoch;
+    // split MLA cache: rope parts of the query rows and of the cache rows (null = combined rows)
+    const void *q_rope;
+    const void *k_rope;
     // optional event probe of one CTA (CTA number = trace_cap >> 24, capacity = its low 24 bits):
     // trace[0] = number of events, then (tag << 56 | index << 40 | cycles)
     unsigned long long *trace;

@@ -46,9 +46,18 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
                         pa_tma_mma_i8_supported(d.head_dim_k, d.head_dim_v, d.v_row_dim, d.block_size, group, d.q_dtype,
                                                 d.kv_dtype);
     const bool gen_ok = pa_generic_supported(d.head_dim_k, d.head_dim_v, d.q_dtype, d.kv_dtype);
-    const bool mla_ok = pa_mla_tc5_supported(d.head_dim_k, d.head_dim_v, d.v_row_dim, d.block_size, d.kv_heads, d.q_dtype,
+    const bool mla_ok = pa_mla_tc5_supported(d.head_dim_k, d.head_dim_v, d.v_row_dim, d.rope_dim, d.block_size, d.kv_heads, d.q_dtype,
                                              d.kv_dtype);
+    if (d.rope_dim != 0 && !mla_ok) {
+        return kErrInvalidTensorDim; // the split latent / rope cache exists for the tcgen05 MLA kernel only
+    }
     int kernel = d.kernel;
+    if (d.rope_dim != 0) {
+        if (kernel != ATB_B200_KERNEL_AUTO && kernel != ATB_B200_KERNEL_MLA_TC5) {
+            return kErrInvalidTensorDim;
+        }
+        kernel = ATB_B200_KERNEL_MLA_TC5;
+    }
     if (kernel == ATB_B200_KERNEL_AUTO) {
         kernel = tma_ok ? ATB_B200_KERNEL_TMA_MMA : (mla_ok ? ATB_B200_KERNEL_MLA_TC5 : ATB_B200_KERNEL_GENERIC);
     }

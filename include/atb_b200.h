@@ -53,7 +53,11 @@ typedef struct atb_b200_pa_desc {
     float qk_scale;         /* multiplies Q*K^T */
     int32_t kernel;         /* ATB_B200_KERNEL_*; AUTO unless forcing a path */
     int32_t sm_count;       /* 0 = query the current device (148 on B200) */
-    int32_t reserved[4];    /* must be 0 */
+    int32_t rope_dim;       /* 0, or 64 for the split MLA cache (MultiLatentAttention, cacheMode KROPE_CTKV of the
+                               reference): the last rope_dim elements of every query / key row live in the separate
+                               tensors q_rope / k_rope_cache, q and k_cache hold the first head_dim_k - rope_dim
+                               (= head_dim_v = v_row_dim) elements */
+    int32_t reserved[3];    /* must be 0 */
 } atb_b200_pa_desc;
 
 /* Device pointers of one call.  v_cache == k_cache for the MLA combined cache. */
@@ -67,6 +71,8 @@ typedef struct atb_b200_pa_tensors {
     const int32_t *k_offset;    /* optional int32 offsets added before scaling */
     const int32_t *v_offset;
     void *out;                  /* [batch, num_heads, head_dim_v], q_dtype */
+    const void *q_rope;         /* rope_dim > 0 only: [batch, num_heads, rope_dim] */
+    const void *k_rope_cache;   /* rope_dim > 0 only: [num_blocks, block_size, kv_heads, rope_dim] */
 } atb_b200_pa_tensors;
 
 typedef struct atb_b200_pa_plan atb_b200_pa_plan; /* opaque */

@@ -243,3 +243,56 @@ def test_norm_rope_reshape_matches_oracle(spec):
     got, want = wl.to_f32(got_bits, dt), wl.to_f32(ref, dt)
     assert np.all(np.abs(got - want) <= 2.0 ** -8 * np.maximum(1.0, np.abs(want)))
     assert np.mean(got_bits.view(np.uint16) == ref.view(np.uint16)) > 0.99
+
+
+# ------------------------------------------------------------------ MLA with the split latent / rope cache
+
+def _run_split_mla(case, h):
+    """The kernel-level C ABI with rope_dim = 64: query and cache given as latent [.., 512] and rope [.., 64] tensors."""
+    dt = case.q_dtype
+    q, kc = to_dev(h["q"], dt), to_dev(h["k_cache"], dt)
+    q_nope, q_rope = q[..., :512].contiguous(), q[..., 512:].contiguous()
+    ct_kv, k_rope = kc[..., :512].contiguous(), kc[..., 512:].contiguous()
+    bt = torch.from_numpy(h["block_tables"]).cuda()
+    out = torch.zeros((case.batch, case.heads, 512), dtype=q.dtype, device="cuda")
+    desc = capi.make_desc(case.batch, case.heads, 1, 576, 512, case.block_size, kc.shape[0], bt.shape[1], dt,
+                          qk_scale=case.qk_scale, v_row_dim=512, rope_dim=64)
+    plan = capi.PaPlan(desc, h["context_lens"])
+    assert plan.info.kernel == capi.KERNEL_MLA_TC5
+    ws = torch.empty(max(int(plan.info.workspace_bytes), 256), dtype=torch.uint8, device="cuda")
+    tens = capi.pa_tensors(q_nope, ct_kv, ct_kv, bt, out, q_rope=q_rope, k_rope_cache=k_rope)
+    plan.launch(tens, ws.data_ptr(), ws.numel(), capi.torch_stream_ptr())
+    torch.cuda.synchronize()
+    assert plan.device_status(ws.data_ptr(), capi.torch_stream_ptr()) == 0
+    return wl.torch_to_host(out, dt)
+
+
+@pytest.mark.parametrize("name", ["mla_8h_fp16", "mla_8h_bf16", "mla_128h_bf16"])
+def test_split_cache_mla_kernel_matches_oracle_and_combined_cache(name):
+    case = [c for c in wl.SMALL_CASES if c.name == name][0]
+    h = wl.make_host_inputs(case)
+    got = _run_split_mla(case, h)
+    ref = oracle.multi_latent_attention(np.ascontiguousarray(h["q"][..., :512]), np.ascontiguousarray(h["q"][..., 512:]),
+                                        np.ascontiguousarray(h["k_cache"][..., :512]),
+                                        np.ascontiguousarray(h["k_cache"][..., 512:]), h["block_tables"], h["context_lens"],
+                                        case.qk_scale, case.q_dtype)
+    assert max_abs_err(got, ref, case.q_dtype) <= tol_for(case)
+    from helpers import run_gpu_case
+    combined, info = run_gpu_case(case, h)
+    assert info.kernel == capi.KERNEL_MLA_TC5
+    assert np.array_equal(got.view(np.uint16), combined.view(np.uint16))      # same kernel, same arithmetic
+
+
+def test_split_cache_needs_both_rope_tensors():
+    case = [c for c in wl.SMALL_CASES if c.name == "mla_8h_bf16"][0]
+    h = wl.make_host_inputs(case)
+    desc = capi.make_desc(case.batch, case.heads, 1, 576, 512, case.block_size, h["k_cache"].shape[0],
+                          h["block_tables"].shape[1], "bf16", qk_scale=case.qk_scale, v_row_dim=512, rope_dim=64)
+    plan = capi.PaPlan(desc, h["context_lens"])
+    fake = torch.zeros(16, dtype=torch.uint8, device="cuda")
+    ws = torch.empty(max(int(plan.info.workspace_bytes), 256), dtype=torch.uint8, device="cuda")
+    tens = capi.pa_tensors(fake, fake, fake, fake, fake)                      # no rope tensors
+    with pytest.raises(capi.AtbError):
+        plan.launch(tens, ws.data_ptr(), ws.numel(), capi.torch_stream_ptr())
+    with pytest.raises(capi.AtbError):                                       # other shapes have no split form
+        capi.PaPlan(capi.make_desc(2, 8, 2, 128, 128, 128, 8, 4, "bf16", rope_dim=64), h["context_lens"][:2])
