@@ -92,6 +92,19 @@ class ReshapeAndCacheWithStrideParam(ctypes.Structure):
     _fields_ = [("compressType", ctypes.c_int32), ("kvCacheCfg", ctypes.c_int32), ("rsv", ctypes.c_uint8 * 16)]
 
 
+class MultiLatentAttentionParam(ctypes.Structure):
+    """Byte layout of atb::infer::MultiLatentAttentionParam (64 bytes); cacheMode 1 = separate latent / rope caches."""
+    _fields_ = [("headNum", ctypes.c_int32), ("qkScale", ctypes.c_float), ("kvHeadNum", ctypes.c_int32),
+                ("maskType", ctypes.c_int32), ("calcType", ctypes.c_int32), ("cacheMode", ctypes.c_uint8),
+                ("windowSize", ctypes.c_uint32), ("maskUseStatusType", ctypes.c_int32), ("rsv", ctypes.c_uint8 * 32)]
+
+    def __init__(self, **kw):
+        super().__init__()
+        self.qkScale = 1.0
+        for k, v in kw.items():
+            setattr(self, k, v)
+
+
 class NormRopeReshapeParam(ctypes.Structure):
     """Byte layout of atb::infer::NormRopeReshapeParam (28 bytes)."""
     _fields_ = [("precisionMode", ctypes.c_uint32), ("rotaryCoeff", ctypes.c_uint32), ("epsilon", ctypes.c_float),
@@ -132,6 +145,7 @@ EXPORTS = [
     "atb_b200_operation_create_block_copy", "atb_b200_operation_create_paged_cache_load",
     "atb_b200_reshape_and_cache_strided", "atb_b200_operation_create_reshape_and_cache_with_stride",
     "atb_b200_norm_rope_reshape", "atb_b200_operation_create_norm_rope_reshape",
+    "atb_b200_operation_create_multi_latent_attention",
 ]
 
 _lib = None
@@ -163,6 +177,7 @@ def lib():
         L.atb_b200_operation_create_paged_attention.argtypes = [vp, u64, P(vp)]
         L.atb_b200_operation_create_reshape_and_cache.argtypes = [vp, u64, P(vp)]
         L.atb_b200_operation_create_block_copy.argtypes = [vp, u64, P(vp)]
+        L.atb_b200_operation_create_multi_latent_attention.argtypes = [vp, u64, P(vp)]
         L.atb_b200_operation_create_norm_rope_reshape.argtypes = [vp, u64, P(vp)]
         L.atb_b200_norm_rope_reshape.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, ctypes.c_float, i64, vp]
         L.atb_b200_operation_create_reshape_and_cache_with_stride.argtypes = [vp, u64, P(vp)]
@@ -525,6 +540,9 @@ class Operation:
         elif isinstance(param, ReshapeAndCacheWithStrideParam):
             fn, what = (lib().atb_b200_operation_create_reshape_and_cache_with_stride,
                         "CreateOperation(ReshapeAndCacheWithStrideParam)")
+        elif isinstance(param, MultiLatentAttentionParam):
+            fn, what = (lib().atb_b200_operation_create_multi_latent_attention,
+                        "CreateOperation(MultiLatentAttentionParam)")
         elif isinstance(param, NormRopeReshapeParam):
             fn, what = lib().atb_b200_operation_create_norm_rope_reshape, "CreateOperation(NormRopeReshapeParam)"
         elif isinstance(param, BlockCopyParam):

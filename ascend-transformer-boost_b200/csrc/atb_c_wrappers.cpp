@@ -112,6 +112,19 @@ int atb_b200_operation_create_reshape_and_cache_with_stride(const void *param, u
     return st;
 }
 
+int atb_b200_operation_create_multi_latent_attention(const void *param, uint64_t param_bytes, void **operation)
+{
+    if (param == nullptr || operation == nullptr || param_bytes != sizeof(infer::MultiLatentAttentionParam)) {
+        return ERROR_INVALID_PARAM;
+    }
+    infer::MultiLatentAttentionParam p;
+    std::memcpy(&p, param, sizeof(p));
+    Operation *op = nullptr;
+    Status st = CreateOperation(p, &op);
+    *operation = op;
+    return st;
+}
+
 int atb_b200_operation_create_norm_rope_reshape(const void *param, uint64_t param_bytes, void **operation)
 {
     if (param == nullptr || operation == nullptr || param_bytes != sizeof(infer::NormRopeReshapeParam)) {

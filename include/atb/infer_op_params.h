@@ -76,6 +76,41 @@ struct ReshapeAndCacheWithStrideParam {
     uint8_t rsv[16] = {0};
 };
 
+// MultiLatentAttention (include/atb/infer_op_params.h:2899-2950 of the reference): attention over the MLA latent
+// cache given as separate latent (512) and rope (64) tensors.  Decode form built here: inputs qNope [tokens, heads,
+// 512], qRope [tokens, heads, 64], ctKV [blocks, 128, 1, 512], kRope [blocks, 128, 1, 64], blockTables, contextLens
+// (host data mandatory); output attnOut [tokens, heads, 512].
+struct MultiLatentAttentionParam {
+    int32_t headNum = 0;
+    float qkScale = 1.0;
+    int32_t kvHeadNum = 0;
+    enum MaskType : int { UNDEFINED = 0, MASK_TYPE_SPEC, MASK_TYPE_MASK_FREE, MASK_TYPE_CAUSAL_MASK, MASK_TYPE_SWA_NORM };
+    MaskType maskType = UNDEFINED;
+    enum CalcType : int {
+        CALC_TYPE_UNDEFINED = 0, // decode, one query token per sequence
+        CALC_TYPE_SPEC,          // several query tokens per sequence (parallel decoding)
+        CALC_TYPE_RING,          // also returns the log-sum-exp
+        CALC_TYPE_SPEC_AND_RING,
+        CALC_TYPE_PREFILL,
+    };
+    CalcType calcType = CALC_TYPE_UNDEFINED;
+    enum CacheMode : uint8_t {
+        KVCACHE = 0,  // combined cache (not supported by the reference either)
+        KROPE_CTKV,   // separate latent and rope caches
+        INT8_NZCACHE, // layouts of another SoC
+        NZCACHE,
+    };
+    CacheMode cacheMode = KVCACHE;
+    uint32_t windowSize = 0;
+    enum MaskUseStatusType : int {
+        MASK_USE_STATUS_TYPE_UNDEFINED = 0,
+        MASK_USE_STATUS_TYPE_BATCH_MASK,
+        MASK_USE_STATUS_TYPE_MAX
+    };
+    MaskUseStatusType maskUseStatusType = MASK_USE_STATUS_TYPE_UNDEFINED;
+    uint8_t rsv[32] = {0};
+};
+
 // Fused RMSNorm + RoPE + ReshapeAndCache of the MLA latent cache (include/atb/infer_op_params.h:2697-2716 of
 // the reference).  Inputs x [tokens, 1, dx], gamma [dx], keyRope [tokens, dr], cos [tokens, dr],
 // sin [tokens, dr], slotMapping [tokens], keyCacheIn [blocks, blockSize, 1, dx + dr]; output keyCacheOut.
@@ -109,6 +144,7 @@ struct PagedCacheLoadParam {
 };
 
 static_assert(sizeof(ReshapeAndCacheWithStrideParam) == 24, "ABI: ReshapeAndCacheWithStrideParam is 24 bytes");
+static_assert(sizeof(MultiLatentAttentionParam) == 64, "ABI: MultiLatentAttentionParam is 64 bytes");
 static_assert(sizeof(NormRopeReshapeParam) == 28, "ABI: NormRopeReshapeParam is 28 bytes");
 static_assert(sizeof(BlockCopyParam) == 16, "ABI: BlockCopyParam is 16 bytes");
 static_assert(sizeof(PagedCacheLoadParam) == 64, "ABI: PagedCacheLoadParam is 64 bytes");

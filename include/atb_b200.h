@@ -244,6 +244,8 @@ int atb_b200_operation_create_block_copy(const void *param, uint64_t param_bytes
 int atb_b200_operation_create_paged_cache_load(const void *param, uint64_t param_bytes, void **operation);
 /* atb::CreateOperation<infer::ReshapeAndCacheWithStrideParam> (24-byte param) */
 int atb_b200_operation_create_reshape_and_cache_with_stride(const void *param, uint64_t param_bytes, void **operation);
+/* atb::CreateOperation<infer::MultiLatentAttentionParam> (64-byte param; tests/unittest/ops/test_op_param_size.cpp:68) */
+int atb_b200_operation_create_multi_latent_attention(const void *param, uint64_t param_bytes, void **operation);
 /* atb::CreateOperation<infer::NormRopeReshapeParam> (28-byte param) */
 int atb_b200_operation_create_norm_rope_reshape(const void *param, uint64_t param_bytes, void **operation);
 int atb_b200_operation_input_num(void *operation, uint32_t *n);

@@ -113,6 +113,16 @@ static int RunCpu()
     CHECK(atb::CreateOperation(lp, &op) == atb::NO_ERROR);
     CHECK(op->GetName() == "PagedCacheLoadOperation" && op->GetInputNum() == 7 && op->GetOutputNum() == 2);
     CHECK(atb::DestroyOperation(op) == atb::NO_ERROR);
+    // MLA decode attention over the split latent / rope cache
+    atb::infer::MultiLatentAttentionParam mp;
+    mp.headNum = 128;
+    mp.kvHeadNum = 1;
+    mp.qkScale = 0.0417f;
+    CHECK(atb::CreateOperation(mp, &op) == atb::ERROR_INVALID_PARAM); // default cacheMode KVCACHE has no kernel
+    mp.cacheMode = atb::infer::MultiLatentAttentionParam::KROPE_CTKV;
+    CHECK(atb::CreateOperation(mp, &op) == atb::NO_ERROR);
+    CHECK(op->GetName() == "MultiLatentAttentionOperation" && op->GetInputNum() == 6 && op->GetOutputNum() == 1);
+    CHECK(atb::DestroyOperation(op) == atb::NO_ERROR);
     CHECK(atb::DestroyContext(ctx) == atb::NO_ERROR);
 
     atb::SVector<int> v;

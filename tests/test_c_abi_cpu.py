@@ -327,3 +327,68 @@ def test_reshape_and_cache_setup_checks():
     bad = list(ins)
     bad[0] = T(dtype=capi.ACL_FLOAT16, shape=(4, 8, 128), device_ptr=f)
     _expect(capi.ERROR_INVALID_TENSOR_INI_MATCH, op.setup, bad, outs, ctx)
+
+
+# ------------------------------------------------------------------ MultiLatentAttentionOperation
+
+def _mla_param(**kw):
+    base = dict(headNum=128, kvHeadNum=1, qkScale=0.0417, cacheMode=1)
+    base.update(kw)
+    return capi.MultiLatentAttentionParam(**base)
+
+
+def _mla_tensors(batch=3, heads=128, nb=16, maxb=4, dtype=capi.ACL_BF16, lens=None):
+    T = capi.atb_tensor
+    lens = np.array([5, 130, 400], dtype=np.int32) if lens is None else lens
+    fake = 0x1000
+    ins = [T(dtype=dtype, shape=(batch, heads, 512), device_ptr=fake), T(dtype=dtype, shape=(batch, heads, 64), device_ptr=fake),
+           T(dtype=dtype, shape=(nb, 128, 1, 512), device_ptr=fake), T(dtype=dtype, shape=(nb, 128, 1, 64), device_ptr=fake),
+           T(dtype=capi.ACL_INT32, shape=(batch, maxb), device_ptr=fake),
+           T(dtype=capi.ACL_INT32, shape=(batch,), device_ptr=fake, host=lens)]
+    outs = [T(dtype=dtype, shape=(batch, heads, 512), device_ptr=fake)]
+    return ins, outs
+
+
+def test_multi_latent_attention_param_checks():
+    # tests/unittest/ops/test_op_param_size.cpp:68 of the reference
+    assert ctypes.sizeof(capi.MultiLatentAttentionParam) == 64
+    op = capi.Operation(_mla_param())
+    assert (op.name, op.input_num, op.output_num) == ("MultiLatentAttentionOperation", 6, 1)
+    for bad in (dict(qkScale=0.0), dict(qkScale=1.5), dict(headNum=24), dict(kvHeadNum=2), dict(cacheMode=0),
+                dict(cacheMode=9), dict(maskType=7), dict(calcType=9),
+                # forms of the reference this build does not carry
+                dict(calcType=1), dict(calcType=2), dict(calcType=4), dict(maskType=1, calcType=1),
+                dict(cacheMode=2), dict(cacheMode=3), dict(maskUseStatusType=1)):
+        _expect(capi.ERROR_INVALID_PARAM, capi.Operation, _mla_param(**bad))
+    p = _mla_param()
+    p.rsv[31] = 1
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, p)
+
+
+def test_multi_latent_attention_setup_checks(monkeypatch):
+    monkeypatch.setenv("ATB_B200_SM_COUNT", "148")
+    op = capi.Operation(_mla_param())
+    ctx = capi.Context()
+    ins, outs = _mla_tensors()
+    assert op.infer_shape(ins, 1) == [(3, 128, 512)]
+    assert op.setup(ins, outs, ctx) >= 256
+    T = capi.atb_tensor
+
+    def swapped(i, **kw):
+        bad = list(ins)
+        bad[i] = T(device_ptr=0x1000, **kw)
+        return bad
+    bf = capi.ACL_BF16
+    _expect(capi.ERROR_INVALID_IN_TENSOR_NUM, op.setup, ins[:5], outs, ctx)
+    _expect(capi.ERROR_INVALID_TENSOR_INI_MATCH, op.setup, swapped(1, dtype=capi.ACL_FLOAT16, shape=(3, 128, 64)), outs, ctx)
+    _expect(capi.ERROR_INVALID_TENSOR_DIM_NUM, op.setup, swapped(2, dtype=bf, shape=(16, 128, 512)), outs, ctx)
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, swapped(2, dtype=bf, shape=(16, 64, 1, 512)), outs, ctx)   # block size
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, swapped(3, dtype=bf, shape=(15, 128, 1, 64)), outs, ctx)   # block count
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, swapped(0, dtype=bf, shape=(3, 64, 512)), outs, ctx)       # heads
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, swapped(1, dtype=bf, shape=(3, 128, 32)), outs, ctx)       # rope width
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, swapped(0, dtype=bf, shape=(4, 128, 512)), outs, ctx)      # tokens != batch
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, ins, [T(dtype=bf, shape=(3, 128, 576), device_ptr=0x1000)], ctx)
+    _expect(capi.ERROR_INVALID_PARAM, op.setup, swapped(5, dtype=capi.ACL_INT32, shape=(3,)), outs, ctx)        # no host lens
+    # execute before a successful setup of these tensors is refused without touching the device
+    op2 = capi.Operation(_mla_param())
+    _expect(capi.ERROR_INVALID_PARAM, op2.execute, ins, outs, 0x1000, 1 << 20, ctx)

@@ -296,3 +296,38 @@ def test_split_cache_needs_both_rope_tensors():
         plan.launch(tens, ws.data_ptr(), ws.numel(), capi.torch_stream_ptr())
     with pytest.raises(capi.AtbError):                                       # other shapes have no split form
         capi.PaPlan(capi.make_desc(2, 8, 2, 128, 128, 128, 8, 4, "bf16", rope_dim=64), h["context_lens"][:2])
+
+
+# ------------------------------------------------------------------ MultiLatentAttentionOperation (atb operator API)
+
+@pytest.mark.parametrize("name", ["mla_8h_fp16", "mla_8h_bf16", "mla_128h_bf16"])
+def test_multi_latent_attention_operation_matches_oracle(name):
+    case = [c for c in wl.SMALL_CASES if c.name == name][0]
+    h = wl.make_host_inputs(case)
+    dt = case.q_dtype
+    q, kc = to_dev(h["q"], dt), to_dev(h["k_cache"], dt)
+    q_nope, q_rope = q[..., :512].contiguous(), q[..., 512:].contiguous()
+    ct_kv, k_rope = kc[..., :512].contiguous(), kc[..., 512:].contiguous()
+    bt = torch.from_numpy(h["block_tables"]).cuda()
+    lens_dev = torch.from_numpy(h["context_lens"]).cuda()
+    out = torch.full((case.batch, case.heads, 512), 7.0, dtype=q.dtype, device="cuda")
+    T = capi.atb_tensor
+    ins = [T(q_nope), T(q_rope), T(ct_kv), T(k_rope), T(bt), T(lens_dev, host=h["context_lens"])]
+    outs = [T(out)]
+    op = capi.Operation(capi.MultiLatentAttentionParam(headNum=case.heads, kvHeadNum=1, qkScale=case.qk_scale, cacheMode=1))
+    assert op.infer_shape(ins, 1) == [tuple(out.shape)]
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    ctx = capi.Context(stream.cuda_stream)
+    for lens in (h["context_lens"], np.maximum(h["context_lens"] // 2, 1).astype(np.int32)):   # second Setup re-plans
+        ins[5] = T(lens_dev, host=lens)
+        ws_bytes = op.setup(ins, outs, ctx)
+        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device="cuda")
+        op.execute(ins, outs, ws.data_ptr(), ws_bytes, ctx)
+        torch.cuda.synchronize()
+        got = wl.torch_to_host(out, dt)
+        ref = oracle.multi_latent_attention(np.ascontiguousarray(h["q"][..., :512]), np.ascontiguousarray(h["q"][..., 512:]),
+                                            np.ascontiguousarray(h["k_cache"][..., :512]),
+                                            np.ascontiguousarray(h["k_cache"][..., 512:]), h["block_tables"], lens,
+                                            case.qk_scale, dt)
+        assert max_abs_err(got, ref, dt) <= tol_for(case)
