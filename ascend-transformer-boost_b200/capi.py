@@ -36,14 +36,19 @@ class PaDesc(ctypes.Structure):
                 ("block_size", ctypes.c_int32), ("num_blocks", ctypes.c_int32),
                 ("max_blocks_per_seq", ctypes.c_int32), ("q_dtype", ctypes.c_int32), ("kv_dtype", ctypes.c_int32),
                 ("qk_scale", ctypes.c_float), ("kernel", ctypes.c_int32), ("sm_count", ctypes.c_int32),
-                ("rope_dim", ctypes.c_int32), ("reserved", ctypes.c_int32 * 3)]
+                ("rope_dim", ctypes.c_int32), ("score_mods", ctypes.c_int32), ("reserved", ctypes.c_int32 * 2)]
 
 
 class PaTensors(ctypes.Structure):
     _fields_ = [("q", ctypes.c_void_p), ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p),
                 ("block_tables", ctypes.c_void_p), ("k_descale", ctypes.c_void_p), ("v_descale", ctypes.c_void_p),
                 ("k_offset", ctypes.c_void_p), ("v_offset", ctypes.c_void_p), ("out", ctypes.c_void_p),
-                ("q_rope", ctypes.c_void_p), ("k_rope_cache", ctypes.c_void_p)]
+                ("q_rope", ctypes.c_void_p), ("k_rope_cache", ctypes.c_void_p),
+                ("mask", ctypes.c_void_p), ("mask_batch_stride", ctypes.c_int64), ("mask_head_stride", ctypes.c_int64),
+                ("mask_tokens", ctypes.c_int64), ("logn", ctypes.c_void_p)]
+
+
+SCORE_MASK, SCORE_LOGN = 1, 2
 
 
 class PaPlanInfo(ctypes.Structure):
@@ -222,9 +227,9 @@ def _check(rc, what):
 # ------------------------------------------------------------------ kernel level
 
 def make_desc(batch, num_heads, kv_heads, dk, dv, block_size, num_blocks, max_blocks, q_dtype, kv_dtype=None,
-              qk_scale=1.0, v_row_dim=None, kernel=KERNEL_AUTO, sm_count=0, rope_dim=0):
+              qk_scale=1.0, v_row_dim=None, kernel=KERNEL_AUTO, sm_count=0, rope_dim=0, score_mods=0):
     d = PaDesc()
-    d.rope_dim = rope_dim
+    d.rope_dim, d.score_mods = rope_dim, score_mods
     d.batch, d.num_heads, d.kv_heads = batch, num_heads, kv_heads
     d.head_dim_k, d.head_dim_v, d.v_row_dim = dk, dv, (v_row_dim or dv)
     d.block_size, d.num_blocks, d.max_blocks_per_seq = block_size, num_blocks, max_blocks
@@ -319,8 +324,11 @@ def torch_stream_ptr():
 
 
 def pa_tensors(q, k_cache, v_cache, block_tables, out, k_descale=None, v_descale=None, k_offset=None, v_offset=None,
-               q_rope=None, k_rope_cache=None):
+               q_rope=None, k_rope_cache=None, mask=None, mask_strides=(0, 0), mask_tokens=0, logn=None):
+    """`mask_strides` = (batch, head) element strides of the additive mask, `mask_tokens` its last dimension."""
     t = PaTensors()
+    t.mask, t.logn = _ptr(mask), _ptr(logn)
+    t.mask_batch_stride, t.mask_head_stride, t.mask_tokens = int(mask_strides[0]), int(mask_strides[1]), int(mask_tokens)
     t.q_rope, t.k_rope_cache = _ptr(q_rope), _ptr(k_rope_cache)
     t.q, t.k_cache = _ptr(q), _ptr(k_cache)
     t.v_cache = _ptr(v_cache if v_cache is not None else k_cache)

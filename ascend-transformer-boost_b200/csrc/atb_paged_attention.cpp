@@ -56,12 +56,18 @@ bool ParamCheck(const Param &p)
             return false;
         }
     }
-    // Features outside the decode hot path of this build.
-    if (p.maskType != Param::UNDEFINED || p.compressType != Param::COMPRESS_TYPE_UNDEFINED ||
-        p.calcType != Param::CALC_TYPE_UNDEFINED || p.scaleType != Param::SCALE_TYPE_TOR ||
+    if (p.scaleType == Param::SCALE_TYPE_LOGN &&
+        (p.quantType != Param::TYPE_QUANT_UNQUANT || p.calcType != Param::CALC_TYPE_UNDEFINED ||
+         p.compressType != Param::COMPRESS_TYPE_UNDEFINED)) {
+        ATB_B200_LOG(ERROR, "logN func does not support quant, calcType or compressType features");
+        return false;
+    }
+    // Features outside the decode path of this build.
+    if ((p.maskType != Param::UNDEFINED && p.maskType != Param::MASK_TYPE_NORM && p.maskType != Param::MASK_TYPE_ALIBI) ||
+        p.compressType != Param::COMPRESS_TYPE_UNDEFINED || p.calcType != Param::CALC_TYPE_UNDEFINED ||
         p.inputLayout != infer::TYPE_BSND ||
         (p.quantType != Param::TYPE_QUANT_UNQUANT && p.quantType != Param::TYPE_DEQUANT_FUSION)) {
-        ATB_B200_LOG(ERROR, "PagedAttention: mask / compress / SPEC / logN / BNSD / QKV-quant "
+        ATB_B200_LOG(ERROR, "PagedAttention: SPEC / MASK_FREE / NORM_COMPRESS masks, compress, SPEC, BNSD and QKV-quant "
                             "are not supported by this build");
         return false;
     }
@@ -93,6 +99,9 @@ public:
                 // descale tensors: fp32, the int64-packed fp32 encoding, or (extension) fp16
                 for (aclDataType sc : {ACL_FLOAT, ACL_INT64, ACL_FLOAT16}) {
                     DtypeComb c = {h, ACL_INT8, ACL_INT8, ACL_INT32, ACL_INT32};
+                    if (p.maskType != Param::UNDEFINED) {
+                        c.push_back(h);
+                    }
                     if (p.batchRunStatusEnable) {
                         c.push_back(ACL_INT32);
                     }
@@ -114,8 +123,14 @@ public:
                 }
                 c.push_back(ACL_INT32);
                 c.push_back(ACL_INT32);
+                if (p.maskType != Param::UNDEFINED) {
+                    c.push_back(h);
+                }
                 if (p.batchRunStatusEnable) {
                     c.push_back(ACL_INT32);
+                }
+                if (p.scaleType == Param::SCALE_TYPE_LOGN) {
+                    c.push_back(ACL_FLOAT);
                 }
                 c.push_back(h);
                 combs_.push_back(c);
@@ -135,6 +150,12 @@ public:
     uint32_t GetInputNum() const override
     {
         uint32_t n = 5; // query, keyCache, valueCache, blockTables, contextLens
+        if (param_.maskType != Param::UNDEFINED) {
+            n += 1; // mask
+        }
+        if (param_.scaleType == Param::SCALE_TYPE_LOGN) {
+            n += 1; // logN, always the last input
+        }
         if (param_.batchRunStatusEnable) {
             n += 1; // batchRunStatus
         }
@@ -149,8 +170,45 @@ public:
     uint32_t GetOutputNum() const override { return 1; }
 
 protected:
-    // position of kDescale: after contextLens and the optional batchRunStatus
-    size_t ScalePos() const { return param_.batchRunStatusEnable ? 6 : 5; }
+    // optional inputs follow contextLens in the reference's order: mask, batchRunStatus, kDescale ..., logN (last)
+    bool HasMask() const { return param_.maskType != Param::UNDEFINED; }
+    size_t ClPos() const { return param_.mlaVHeadSize > 0 ? 3 : 4; }
+    size_t MaskPos() const { return ClPos() + 1; }
+    size_t StatusPos() const { return ClPos() + 1 + (HasMask() ? 1 : 0); }
+    size_t ScalePos() const { return StatusPos() + (param_.batchRunStatusEnable ? 1 : 0); }
+
+    // The mask shapes of the reference's documentation for this SoC class: plain [batch, 1, tokens] or [1, tokens];
+    // alibi [batch, heads, 1, tokens] or [heads, 1, tokens].  Fills the element strides the kernels index with.
+    Status MaskLayout(const Dims &m, int64_t qTokens, int64_t *batchStride, int64_t *headStride, int64_t *tokens) const
+    {
+        const int64_t len = m.dims[m.dimNum - 1];
+        *tokens = len;
+        if (param_.maskType == Param::MASK_TYPE_NORM) {
+            *headStride = 0;
+            if (m.dimNum == 3 && m.dims[1] == 1 && m.dims[0] >= qTokens) {
+                *batchStride = len;
+                return NO_ERROR;
+            }
+            if (m.dimNum == 2 && m.dims[0] == 1) {
+                *batchStride = 0;
+                return NO_ERROR;
+            }
+            ATB_B200_LOG(ERROR, "PagedAttention: norm mask should be [batch, 1, max_seq_len] or [1, max_seq_len]");
+            return m.dimNum == 2 || m.dimNum == 3 ? ERROR_INVALID_TENSOR_DIM : ERROR_INVALID_TENSOR_DIM_NUM;
+        }
+        *headStride = len;
+        if (m.dimNum == 4 && m.dims[1] == param_.headNum && m.dims[2] == 1 && m.dims[0] >= qTokens) {
+            *batchStride = static_cast<int64_t>(param_.headNum) * len;
+            return NO_ERROR;
+        }
+        if (m.dimNum == 3 && m.dims[0] == param_.headNum && m.dims[1] == 1) {
+            *batchStride = 0;
+            return NO_ERROR;
+        }
+        ATB_B200_LOG(ERROR, "PagedAttention: alibi mask should be [batch, head_num, 1, max_seq_len] or "
+                            "[head_num, 1, max_seq_len]");
+        return m.dimNum == 3 || m.dimNum == 4 ? ERROR_INVALID_TENSOR_DIM : ERROR_INVALID_TENSOR_DIM_NUM;
+    }
 
     const std::vector<DtypeComb> &DtypeCombs() const override { return combs_; }
 
@@ -176,13 +234,31 @@ protected:
             ATB_B200_LOG(ERROR, "PagedAttention: keyCache dim 2 should equal kvHeadNum");
             return ERROR_INVALID_TENSOR_DIM;
         }
+        if (HasMask()) {
+            int64_t bs = 0, hs = 0, len = 0;
+            const Status st = MaskLayout(in.at(MaskPos()).shape, q.dims[0], &bs, &hs, &len);
+            if (st != NO_ERROR) {
+                return st;
+            }
+        }
+        if (param_.scaleType == Param::SCALE_TYPE_LOGN) {
+            const Dims &ln = in.at(in.size() - 1).shape;
+            if (ln.dimNum != 1) {
+                ATB_B200_LOG(ERROR, "PagedAttention: invalid logN intensor dimNum");
+                return ERROR_INVALID_TENSOR_DIM_NUM;
+            }
+            if (ln.dims[0] != in.at(clPos).shape.dims[0]) {
+                ATB_B200_LOG(ERROR, "PagedAttention: intensor contextLens and intensor logn has different batch size");
+                return ERROR_INVALID_TENSOR_DIM;
+            }
+        }
         if (param_.batchRunStatusEnable) {
             // dynamic batch: the control tensors may describe more sequences than there are query tokens
             if (q.dims[0] > in.at(btPos).shape.dims[0] || q.dims[0] > in.at(clPos).shape.dims[0]) {
                 ATB_B200_LOG(ERROR, "PagedAttention: numTokens in q should be no greater than blockTables and contextLens");
                 return ERROR_INVALID_TENSOR_DIM;
             }
-            if (in.at(clPos + 1).shape.dimNum != 1 || in.at(clPos + 1).shape.dims[0] < q.dims[0]) {
+            if (in.at(StatusPos()).shape.dimNum != 1 || in.at(StatusPos()).shape.dims[0] < q.dims[0]) {
                 ATB_B200_LOG(ERROR, "PagedAttention: batchRunStatus should hold one value per query token");
                 return ERROR_INVALID_TENSOR_DIM;
             }
@@ -211,7 +287,7 @@ protected:
                 return ERROR_INVALID_TENSOR_DIM;
             }
             const int64_t want = kvHeads * headSize;
-            for (size_t i = ScalePos(); i < in.size(); ++i) {
+            for (size_t i = ScalePos(); i < ScalePos() + (param_.hasQuantOffset ? 4u : 2u); ++i) {
                 if (in.at(i).shape.dimNum != 1 || in.at(i).shape.dims[0] != want) {
                     ATB_B200_LOG(ERROR, "PagedAttention: descale / offset should have kvHeadNum*headSize elements");
                     return ERROR_INVALID_TENSOR_DIM;
@@ -308,13 +384,25 @@ protected:
         if (const char *sm = std::getenv("ATB_B200_SM_COUNT")) {
             d.sm_count = std::atoi(sm);
         }
+        d.score_mods = (HasMask() ? ATB_B200_SCORE_MASK : 0) |
+                       (param_.scaleType == Param::SCALE_TYPE_LOGN ? ATB_B200_SCORE_LOGN : 0);
         const int32_t *lens = static_cast<const int32_t *>(cl.hostData);
+        if (HasMask()) {
+            int64_t bs = 0, hs = 0, len = 0;
+            (void)MaskLayout(vp.inTensors.at(MaskPos()).desc.shape, q.dims[0], &bs, &hs, &len);
+            for (int32_t b = 0; b < d.batch; ++b) {
+                if (lens[b] > len) {
+                    ATB_B200_LOG(ERROR, "PagedAttention: the mask is shorter than a sequence's context");
+                    return ERROR_INVALID_TENSOR_DIM;
+                }
+            }
+        }
         if (param_.batchRunStatusEnable) {
             // Dynamic batch: the status tensor is host data like contextLens
             // (src/ops/ops_infer/paged_attention/param.cpp:39-50 of the reference).  The reference's kernels
             // skip a sequence through its zero context length; here a sequence whose status is 0 is also
             // planned as empty, so it is skipped whatever length the caller left in contextLens.
-            const Tensor &status = vp.inTensors.at(clPos + 1);
+            const Tensor &status = vp.inTensors.at(StatusPos());
             if (status.hostData == nullptr) {
                 ATB_B200_LOG(ERROR, "PagedAttention: batchRunStatus hostData is null");
                 return ERROR_INVALID_PARAM;
@@ -382,8 +470,18 @@ protected:
             t.k_offset = ko ? static_cast<const int32_t *>(ko->deviceData) : nullptr;
             t.v_offset = vo ? static_cast<const int32_t *>(vo->deviceData) : nullptr;
         }
+        if (HasMask()) {
+            const Tensor &m = vp.inTensors.at(MaskPos());
+            t.mask = m.deviceData;
+            (void)MaskLayout(m.desc.shape, vp.inTensors.at(0).desc.shape.dims[0], &t.mask_batch_stride,
+                             &t.mask_head_stride, &t.mask_tokens);
+        }
+        if (param_.scaleType == Param::SCALE_TYPE_LOGN) {
+            t.logn = static_cast<const float *>(vp.inTensors.at(vp.inTensors.size() - 1).deviceData);
+        }
         if (t.q == nullptr || t.k_cache == nullptr || t.v_cache == nullptr || t.block_tables == nullptr ||
-            t.out == nullptr) {
+            t.out == nullptr || (HasMask() && t.mask == nullptr) ||
+            (param_.scaleType == Param::SCALE_TYPE_LOGN && t.logn == nullptr)) {
             return ERROR_INVALID_PARAM;
         }
         uint8_t *ws = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255));
@@ -399,7 +497,8 @@ private:
                d.head_dim_k == desc_.head_dim_k && d.head_dim_v == desc_.head_dim_v && d.v_row_dim == desc_.v_row_dim &&
                d.block_size == desc_.block_size && d.num_blocks == desc_.num_blocks &&
                d.max_blocks_per_seq == desc_.max_blocks_per_seq && d.q_dtype == desc_.q_dtype &&
-               d.kv_dtype == desc_.kv_dtype && d.qk_scale == desc_.qk_scale && d.kernel == desc_.kernel;
+               d.kv_dtype == desc_.kv_dtype && d.qk_scale == desc_.qk_scale && d.kernel == desc_.kernel &&
+               d.score_mods == desc_.score_mods;
     }
     // fp32 scales are used in place; the int64-packed and fp16 encodings are converted once per
     // launch into a small device buffer owned by the operation.

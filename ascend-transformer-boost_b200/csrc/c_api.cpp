@@ -362,6 +362,13 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
         return kErrInvalidParam;
     }
     HostPlan &h = plan->hp;
+    if ((h.desc.score_mods & ATB_B200_SCORE_MASK) != 0 &&
+        (t->mask == nullptr || t->mask_tokens < h.max_context || t->mask_batch_stride < 0 || t->mask_head_stride < 0)) {
+        return kErrInvalidParam; // no mask, or one shorter than the longest context
+    }
+    if ((h.desc.score_mods & ATB_B200_SCORE_LOGN) != 0 && t->logn == nullptr) {
+        return kErrInvalidParam;
+    }
     if (workspace_bytes < h.workspace_bytes || (h.workspace_bytes > 0 && workspace == nullptr) ||
         (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) {
         return kErrInvalidParam;
@@ -409,6 +416,12 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
     if (d.rope_dim != 0 && (a.q_rope == nullptr || a.k_rope == nullptr)) {
         return kErrInvalidParam;
     }
+    if ((d.score_mods & ATB_B200_SCORE_MASK) != 0) {
+        a.mask = t->mask;
+        a.mask_bs = t->mask_batch_stride;
+        a.mask_hs = t->mask_head_stride;
+    }
+    a.logn = (d.score_mods & ATB_B200_SCORE_LOGN) != 0 ? t->logn : nullptr;
     a.plan.group_begin = reinterpret_cast<const int32_t *>(blob + h.off_group_begin);
     a.plan.items = reinterpret_cast<const PaItem *>(blob + h.off_items);
     a.plan.seq_part_base = reinterpret_cast<const int32_t *>(blob + h.off_part_base);

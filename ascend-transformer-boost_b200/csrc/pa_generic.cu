@@ -92,6 +92,10 @@ __global__ void __launch_bounds__(kWarps * 32) pa_generic_kernel(const PaArgs a)
             }
         }
         const int32_t *bt = a.block_tables + (int64_t)item.seq * a.max_blocks;
+        // SCALE_TYPE_LOGN: the sequence's factor multiplies the scale; additive mask in the query dtype
+        const float scale_l2 = a.logn != nullptr ? a.scale_log2 * __ldg(a.logn + item.seq) : a.scale_log2;
+        const TQ *mrow = a.mask == nullptr ? nullptr
+                                           : static_cast<const TQ *>(a.mask) + (int64_t)item.seq * a.mask_bs + (int64_t)head0 * a.mask_hs;
         for (int t = item.tok_begin + warp; t < item.tok_end; t += kWarps) {
             const int64_t blk = bt[t / a.block_size];
             if (blk < 0 || blk >= a.num_blocks) {
@@ -150,7 +154,11 @@ __global__ void __launch_bounds__(kWarps * 32) pa_generic_kernel(const PaArgs a)
                     }
                 }
                 acc = warp_sum(acc);
-                const float s = acc * a.scale_log2;
+                float s = acc * scale_l2;
+                if (mrow != nullptr && g < nh) {
+                    // a mask of -inf must not turn the running maximum into -inf (exp2(-inf - -inf) = NaN)
+                    s = fmaxf(s + 1.4426950408889634f * Elem<TQ>::to_float(mrow[(int64_t)g * a.mask_hs + t]), -1e30f);
+                }
                 const float m_new = fmaxf(m[g], s);
                 const float corr = exp2f(m[g] - m_new);
                 const float pr = exp2f(s - m_new);

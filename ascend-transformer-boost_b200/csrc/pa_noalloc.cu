@@ -105,8 +105,9 @@ extern "C" int atb_b200_pa_decode_static_scratch(const atb_b200_pa_desc *desc, c
             return kErrInvalidParam;
         }
     }
-    if (d.rope_dim != 0) {
-        return kErrInvalidTensorDim; // the split latent / rope cache is served by the planned entry points only
+    if (d.rope_dim != 0 || d.score_mods != 0) {
+        return kErrInvalidTensorDim; // the split latent / rope cache, masks and logN scaling are served by the
+                                     // planned entry points only
     }
     if (d.batch > kMaxBatch) {
         return refuse("batch", d.batch, kMaxBatch);

@@ -71,6 +71,11 @@ struct PaArgs {
     // split MLA cache: rope parts of the query rows and of the cache rows (null = combined rows)
     const void *q_rope;
     const void *k_rope;
+    // additive mask in the query dtype (score(b, h, t) += mask[b * mask_bs + h * mask_hs + t]) and per-sequence
+    // factors of the scale; both null on the plain path
+    const void *mask;
+    int64_t mask_bs, mask_hs;
+    const float *logn;
     // optional event probe of one CTA (CTA number = trace_cap >> 24, capacity = its low 24 bits):
     // trace[0] = number of events, then (tag << 56 | index << 40 | cycles)
     unsigned long long *trace;

@@ -58,6 +58,19 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
         }
         kernel = ATB_B200_KERNEL_MLA_TC5;
     }
+    if (d.score_mods != 0) {
+        // masks and logN scaling live in the fp16 / bf16 D = 128 kernel and in the CUDA-core kernel
+        if ((d.score_mods & ~(ATB_B200_SCORE_MASK | ATB_B200_SCORE_LOGN)) != 0 || d.rope_dim != 0) {
+            return kErrInvalidParam;
+        }
+        const bool tma_plain = tma_ok && d.kv_dtype != kInt8;
+        if (kernel == ATB_B200_KERNEL_AUTO) {
+            kernel = tma_plain ? ATB_B200_KERNEL_TMA_MMA : ATB_B200_KERNEL_GENERIC;
+        }
+        if (kernel == ATB_B200_KERNEL_MLA_TC5 || (kernel == ATB_B200_KERNEL_TMA_MMA && !tma_plain)) {
+            return kErrInvalidTensorDim;
+        }
+    }
     if (kernel == ATB_B200_KERNEL_AUTO) {
         kernel = tma_ok ? ATB_B200_KERNEL_TMA_MMA : (mla_ok ? ATB_B200_KERNEL_MLA_TC5 : ATB_B200_KERNEL_GENERIC);
     }
@@ -87,14 +100,16 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
 
     // ---- balanced cut of the global tile sequence into CTA groups
     const int64_t max_ctx = (int64_t)d.max_blocks_per_seq * d.block_size;
-    int64_t total_tiles = 0;
+    int64_t total_tiles = 0, longest = 0;
     for (int b = 0; b < d.batch; ++b) {
         const int64_t ctx = context_lens[b];
         if (ctx < 0 || ctx > max_ctx) {
             return kErrInvalidParam; // a length the block table cannot describe
         }
         total_tiles += (ctx + kTileTokens - 1) / kTileTokens;
+        longest = std::max(longest, ctx);
     }
+    p->max_context = longest;
     const int slots = sm_count * p->ctas_per_sm;
     int64_t n_groups = std::max<int64_t>(1, slots / p->cols);
     if (n_groups < 4) {

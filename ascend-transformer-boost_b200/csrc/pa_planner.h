@@ -19,6 +19,7 @@ struct HostPlan {
     int sm_count = 148;
     int n_cta_groups = 0;
     int n_partials = 0;
+    int64_t max_context = 0; // longest context of the planned batch (tokens)
     std::vector<PaItem> items;
     std::vector<int32_t> group_begin;   // n_cta_groups + 1
     std::vector<int32_t> seq_part_base; // batch

@@ -51,7 +51,9 @@ __device__ __forceinline__ void store_out_row(const PaArgs &a, int seq, int h, i
     }
 }
 
-template <typename T>
+// kMods: the variant that applies an additive mask and / or per-sequence logN factors to the scores; the plain
+// variant carries none of that code.
+template <typename T, bool kMods>
 __global__ void __launch_bounds__(kThreads, 2)
 pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const PaArgs a)
 {
@@ -172,6 +174,18 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         }
         float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
+        float scale_l2 = a.scale_log2;
+        const T *mrow0 = nullptr, *mrow1 = nullptr; // mask rows of this thread's two heads (columns 2c, 2c + 1)
+        if (kMods) {
+            if (a.logn != nullptr) {
+                scale_l2 *= __ldg(a.logn + item.seq);
+            }
+            if (a.mask != nullptr) {
+                const T *mb = static_cast<const T *>(a.mask) + (int64_t)item.seq * a.mask_bs;
+                mrow0 = mb + (int64_t)(kvh * group + min(2 * c, group - 1)) * a.mask_hs;     // padding heads read
+                mrow1 = mb + (int64_t)(kvh * group + min(2 * c + 1, group - 1)) * a.mask_hs; // a real head's row
+            }
+        }
         const int n_st = (item.tok_end - item.tok_begin + kStageTokens - 1) / kStageTokens;
         for (int st = 0; st < n_st; ++st) {
             const int valid_tokens = item.tok_end - (item.tok_begin + st * kStageTokens + warp * 16);
@@ -219,7 +233,21 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 float s[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    s[i] = (s0[i] + s1[i]) * a.scale_log2;
+                    s[i] = (s0[i] + s1[i]) * scale_l2;
+                }
+                if (kMods && mrow0 != nullptr) {
+                    // tokens past the end are not read; a mask of -inf is kept finite so that a fully masked
+                    // start of a sequence cannot turn the running maximum into -inf
+                    constexpr float kLog2e = 1.4426950408889634f;
+                    const int64_t t0 = (int64_t)item.tok_begin + st * kStageTokens + warp * 16 + g;
+                    if (g < valid_tokens) {
+                        s[0] = fmaxf(s[0] + kLog2e * Elem<T>::to_float(mrow0[t0]), -1e30f);
+                        s[1] = fmaxf(s[1] + kLog2e * Elem<T>::to_float(mrow1[t0]), -1e30f);
+                    }
+                    if (g + 8 < valid_tokens) {
+                        s[2] = fmaxf(s[2] + kLog2e * Elem<T>::to_float(mrow0[t0 + 8]), -1e30f);
+                        s[3] = fmaxf(s[3] + kLog2e * Elem<T>::to_float(mrow1[t0 + 8]), -1e30f);
+                    }
                 }
                 if (g >= valid_tokens) {
                     s[0] = s[1] = -INFINITY;
@@ -498,8 +526,10 @@ bool encode_cache_map(CUtensorMap *map, const void *base, int elem_dtype, int kv
 
 template <typename T> cudaError_t launch_typed(const PaArgs &args, const CUtensorMap &km, const CUtensorMap &vm, cudaStream_t s)
 {
-    auto kern = pa_tma_mma_kernel<T>;
-    static bool configured[64] = {};
+    const bool mods = args.mask != nullptr || args.logn != nullptr;
+    auto kern = mods ? pa_tma_mma_kernel<T, true> : pa_tma_mma_kernel<T, false>;
+    static bool configured_plain[64] = {}, configured_mods[64] = {};
+    bool *configured = mods ? configured_mods : configured_plain;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {

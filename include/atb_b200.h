@@ -57,8 +57,15 @@ typedef struct atb_b200_pa_desc {
                                reference): the last rope_dim elements of every query / key row live in the separate
                                tensors q_rope / k_rope_cache, q and k_cache hold the first head_dim_k - rope_dim
                                (= head_dim_v = v_row_dim) elements */
-    int32_t reserved[3];    /* must be 0 */
+    int32_t score_mods;     /* ATB_B200_SCORE_* bits: what is applied to Q*K^T besides qk_scale (PagedAttentionParam
+                               maskType NORM / ALIBI, scaleType SCALE_TYPE_LOGN of the reference) */
+    int32_t reserved[2];    /* must be 0 */
 } atb_b200_pa_desc;
+
+enum {
+    ATB_B200_SCORE_MASK = 1, /* score(b, h, t) += mask[b * mask_batch_stride + h * mask_head_stride + t] */
+    ATB_B200_SCORE_LOGN = 2  /* the scale of sequence b is qk_scale * logn[b] */
+};
 
 /* Device pointers of one call.  v_cache == k_cache for the MLA combined cache. */
 typedef struct atb_b200_pa_tensors {
@@ -73,6 +80,15 @@ typedef struct atb_b200_pa_tensors {
     void *out;                  /* [batch, num_heads, head_dim_v], q_dtype */
     const void *q_rope;         /* rope_dim > 0 only: [batch, num_heads, rope_dim] */
     const void *k_rope_cache;   /* rope_dim > 0 only: [num_blocks, block_size, kv_heads, rope_dim] */
+    /* ATB_B200_SCORE_MASK only: additive mask in q_dtype, indexed in elements as stated at the enum.  The alibi mask
+       [batch, heads, 1, tokens] has strides (heads*tokens, tokens), [heads, 1, tokens] (0, tokens); the plain mask
+       [batch, 1, tokens] (tokens, 0), [1, tokens] (0, 0).  mask_tokens = its last dimension, at least the longest
+       context of the plan. */
+    const void *mask;
+    int64_t mask_batch_stride;
+    int64_t mask_head_stride;
+    int64_t mask_tokens;
+    const float *logn;          /* ATB_B200_SCORE_LOGN only: [batch] fp32 */
 } atb_b200_pa_tensors;
 
 typedef struct atb_b200_pa_plan atb_b200_pa_plan; /* opaque */

@@ -392,3 +392,82 @@ def test_multi_latent_attention_setup_checks(monkeypatch):
     # execute before a successful setup of these tensors is refused without touching the device
     op2 = capi.Operation(_mla_param())
     _expect(capi.ERROR_INVALID_PARAM, op2.execute, ins, outs, 0x1000, 1 << 20, ctx)
+
+
+# ------------------------------------------------------------------ masks and logN scaling
+
+def test_mask_and_logn_param_rules():
+    assert capi.Operation(_pa_param(maskType=1)).input_num == 6            # NORM
+    assert capi.Operation(_pa_param(maskType=2)).input_num == 6            # ALIBI
+    assert capi.Operation(_pa_param(scaleType=1)).input_num == 6           # logN
+    assert capi.Operation(_pa_param(maskType=2, scaleType=1, batchRunStatusEnable=True)).input_num == 8
+    assert capi.Operation(_pa_param(maskType=1, quantType=1, hasQuantOffset=True)).input_num == 10
+    for bad in (dict(maskType=3), dict(maskType=4), dict(maskType=5),      # SPEC, MASK_FREE, NORM_COMPRESS
+                dict(scaleType=1, quantType=1), dict(scaleType=2),
+                dict(mlaVHeadSize=512, kvHeadNum=1, maskType=2), dict(mlaVHeadSize=512, kvHeadNum=1, scaleType=1)):
+        _expect(capi.ERROR_INVALID_PARAM, capi.Operation, _pa_param(**bad))
+
+
+def test_mask_and_logn_setup_checks(monkeypatch):
+    monkeypatch.setenv("ATB_B200_SM_COUNT", "148")
+    T = capi.atb_tensor
+    ctx = capi.Context()
+    f16, fake = capi.ACL_FLOAT16, 0x1000
+    ins, outs, lens = _pa_tensors()                                        # batch 3, 8 heads, longest context 400
+
+    def with_extra(*extra):
+        return list(ins) + list(extra)
+    norm = capi.Operation(_pa_param(maskType=1))
+    assert norm.setup(with_extra(T(dtype=f16, shape=(3, 1, 512), device_ptr=fake)), outs, ctx) >= 256
+    assert norm.setup(with_extra(T(dtype=f16, shape=(1, 400), device_ptr=fake)), outs, ctx) >= 256
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, norm.setup, with_extra(T(dtype=f16, shape=(3, 1, 399), device_ptr=fake)), outs, ctx)
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, norm.setup, with_extra(T(dtype=f16, shape=(2, 1, 512), device_ptr=fake)), outs, ctx)
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, norm.setup, with_extra(T(dtype=f16, shape=(512, 512), device_ptr=fake)), outs, ctx)
+    _expect(capi.ERROR_INVALID_TENSOR_DIM_NUM, norm.setup, with_extra(T(dtype=f16, shape=(3, 8, 1, 512), device_ptr=fake)), outs, ctx)
+    _expect(capi.ERROR_INVALID_TENSOR_INI_MATCH, norm.setup,
+            with_extra(T(dtype=capi.ACL_BF16, shape=(3, 1, 512), device_ptr=fake)), outs, ctx)   # mask dtype = query dtype
+    _expect(capi.ERROR_INVALID_IN_TENSOR_NUM, norm.setup, ins, outs, ctx)
+    alibi = capi.Operation(_pa_param(maskType=2))
+    assert alibi.setup(with_extra(T(dtype=f16, shape=(3, 8, 1, 400), device_ptr=fake)), outs, ctx) >= 256
+    assert alibi.setup(with_extra(T(dtype=f16, shape=(8, 1, 400), device_ptr=fake)), outs, ctx) >= 256
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, alibi.setup, with_extra(T(dtype=f16, shape=(3, 4, 1, 400), device_ptr=fake)), outs, ctx)
+    _expect(capi.ERROR_INVALID_TENSOR_DIM_NUM, alibi.setup, with_extra(T(dtype=f16, shape=(1, 400), device_ptr=fake)), outs, ctx)
+    logn = capi.Operation(_pa_param(scaleType=1))
+    assert logn.setup(with_extra(T(dtype=capi.ACL_FLOAT, shape=(3,), device_ptr=fake)), outs, ctx) >= 256
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, logn.setup, with_extra(T(dtype=capi.ACL_FLOAT, shape=(4,), device_ptr=fake)), outs, ctx)
+    _expect(capi.ERROR_INVALID_TENSOR_INI_MATCH, logn.setup, with_extra(T(dtype=f16, shape=(3,), device_ptr=fake)), outs, ctx)
+    both = capi.Operation(_pa_param(maskType=2, scaleType=1))
+    assert both.setup(with_extra(T(dtype=f16, shape=(8, 1, 400), device_ptr=fake),
+                                 T(dtype=capi.ACL_FLOAT, shape=(3,), device_ptr=fake)), outs, ctx) >= 256
+
+
+def test_planner_routes_score_modifiers():
+    lens = np.array([100, 900], dtype=np.int32)
+
+    def plan(dk=128, kv="bf16", mods=capi.SCORE_MASK, kernel=0, **kw):
+        d = capi.make_desc(2, 8, 2, dk, dk, 128, 64, 8, "bf16", kv, sm_count=148, score_mods=mods, kernel=kernel, **kw)
+        return capi.PaPlan(d, lens).info.kernel
+    assert plan() == capi.KERNEL_TMA_MMA
+    assert plan(mods=capi.SCORE_LOGN | capi.SCORE_MASK) == capi.KERNEL_TMA_MMA
+    assert plan(dk=64) == capi.KERNEL_GENERIC
+    assert plan(kv="int8") == capi.KERNEL_GENERIC                          # the int8 TMA kernel carries no mask code
+    assert plan(kernel=capi.KERNEL_GENERIC) == capi.KERNEL_GENERIC
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, kv="int8", kernel=capi.KERNEL_TMA_MMA)
+    _expect(capi.ERROR_INVALID_PARAM, plan, mods=4)
+    with pytest.raises(capi.AtbError):                                     # no mask on the split MLA cache
+        capi.PaPlan(capi.make_desc(2, 8, 1, 576, 512, 128, 64, 8, "bf16", sm_count=148, v_row_dim=512, rope_dim=64,
+                                   score_mods=1), lens)
+
+
+def test_launch_refuses_missing_or_short_mask_before_touching_the_device():
+    lens = np.array([100, 900], dtype=np.int32)
+    d = capi.make_desc(2, 8, 2, 128, 128, 128, 64, 8, "bf16", sm_count=148, score_mods=capi.SCORE_MASK | capi.SCORE_LOGN)
+    plan = capi.PaPlan(d, lens)
+    t = capi.PaTensors()
+    for f in ("q", "k_cache", "v_cache", "block_tables", "out"):
+        setattr(t, f, 0x1000)
+    _expect(capi.ERROR_INVALID_PARAM, plan.launch, t, 0x1000, 1 << 30, None)          # no mask
+    t.mask, t.mask_tokens = 0x1000, 899
+    _expect(capi.ERROR_INVALID_PARAM, plan.launch, t, 0x1000, 1 << 30, None)          # shorter than the longest context
+    t.mask_tokens = 900
+    _expect(capi.ERROR_INVALID_PARAM, plan.launch, t, 0x1000, 1 << 30, None)          # no logN factors

@@ -331,3 +331,99 @@ def test_multi_latent_attention_operation_matches_oracle(name):
                                             np.ascontiguousarray(h["k_cache"][..., 512:]), h["block_tables"], lens,
                                             case.qk_scale, dt)
         assert max_abs_err(got, ref, dt) <= tol_for(case)
+
+
+# ------------------------------------------------------------------ masks (NORM, ALIBI) and logN scaling
+
+from golden_cases import GOLDEN_PA_FEATURE_CASES, pa_mask  # noqa: E402
+
+
+def _run_pa_op(case, h, param_kw, mask=None, logn=None, lens=None):
+    """PagedAttention through the atb operator API with the optional mask (after contextLens) and logN (last) inputs."""
+    d = host_inputs_to_device(case, h)
+    T = capi.atb_tensor
+    lens = h["context_lens"] if lens is None else lens
+    out = torch.full((case.batch, case.heads, case.dv), 7.0, dtype=wl.torch_dtype(case.q_dtype), device="cuda")
+    lens_dev = torch.from_numpy(lens).cuda()
+    ins = [T(d["q"]), T(d["k_cache"]), T(d["v_cache"]), T(d["block_tables"]), T(lens_dev, host=lens)]
+    keep = [lens_dev]
+    if mask is not None:
+        keep.append(to_dev(mask, case.q_dtype))
+        ins.append(T(keep[-1]))
+    if logn is not None:
+        keep.append(torch.from_numpy(np.ascontiguousarray(logn, dtype=np.float32)).cuda())
+        ins.append(T(keep[-1]))
+    outs = [T(out)]
+    op = capi.Operation(capi.PagedAttentionParam(headNum=case.heads, kvHeadNum=case.kv_heads, qkScale=case.qk_scale,
+                                                 **param_kw))
+    assert op.input_num == len(ins)
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    ctx = capi.Context(stream.cuda_stream)
+    ws_bytes = op.setup(ins, outs, ctx)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device="cuda")
+    op.execute(ins, outs, ws.data_ptr(), ws_bytes, ctx)
+    torch.cuda.synchronize()
+    return wl.torch_to_host(out, case.q_dtype)
+
+
+def _feature_param(spec):
+    kw = {}
+    if spec["mask"] is not None:
+        kw["maskType"] = 2 if spec["mask"] == "alibi" else 1
+    if spec["logn"]:
+        kw["scaleType"] = 1
+    return kw
+
+
+@pytest.mark.parametrize("kernel", [capi.KERNEL_TMA_MMA, capi.KERNEL_GENERIC], ids=["tma_mma", "generic"])
+@pytest.mark.parametrize("spec", GOLDEN_PA_FEATURE_CASES, ids=lambda s: s["case"].name)
+def test_mask_and_logn_match_reference_golden(spec, kernel, monkeypatch):
+    case = spec["case"]
+    fx = np.load(os.path.join(GOLDEN_DIR, f"pa_{case.name}.npz"))
+    h = wl.make_host_inputs(case)
+    monkeypatch.setenv("ATB_B200_FORCE_KERNEL", str(kernel))
+    got = _run_pa_op(case, h, _feature_param(spec), mask=pa_mask(spec), logn=fx["logn"] if spec["logn"] else None)
+    assert max_abs_err(got, fx["out"], case.q_dtype) <= tol_for(case)
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_shared_alibi_rows_split_sequences_and_masked_out_prefix(dtype):
+    """Long sequences (split over several CTAs and merged), the alibi mask given once for all sequences
+    ([heads, 1, tokens]), logN factors, and - in a second run - a norm mask that removes a whole prefix with -inf,
+    longer than one CTA's first tile, which must neither produce NaN nor let the removed tokens through."""
+    case = wl.Case(f"feat_long_{dtype}", batch=5, heads=16, kv_heads=4, q_dtype=dtype,
+                   ctx=("list", [4000, 37, 2100, 640, 1]), seed=77)
+    h = wl.make_host_inputs(case)
+    lens = h["context_lens"]
+    tmax = int(lens.max())
+    rng = np.random.default_rng(5)
+    slopes = np.exp2(-8.0 * (np.arange(case.heads, dtype=np.float32) + 1) / case.heads)
+    alibi = (slopes[:, None, None] * (np.arange(tmax, dtype=np.float32) - tmax + 1)[None, None, :]).astype(np.float32)
+    alibi_enc = wl.encode(alibi, dtype)
+    logn = rng.uniform(0.8, 1.6, size=case.batch).astype(np.float32)
+    got = _run_pa_op(case, h, dict(maskType=2, scaleType=1), mask=alibi_enc, logn=logn)
+    mask_f32 = np.broadcast_to(wl.to_f32(alibi_enc, dtype)[None], (case.batch, case.heads, 1, tmax))
+    ref = oracle.paged_attention(h["q"], h["k_cache"], h["v_cache"], h["block_tables"], lens, case.qk_scale, dtype,
+                                 mask=np.ascontiguousarray(mask_f32), logn=logn)
+    assert max_abs_err(got, ref, dtype) <= tol_for(case)
+
+    norm = np.zeros((case.batch, 1, tmax), dtype=np.float32)
+    cut = [300, 5, 0, 639, 0]                                  # tokens removed at the start of each sequence
+    for b, n in enumerate(cut):
+        norm[b, 0, :n] = -np.inf
+    got = _run_pa_op(case, h, dict(maskType=1), mask=wl.encode(norm, dtype))
+    assert np.isfinite(wl.to_f32(got, dtype)).all()
+    ref = oracle.paged_attention(h["q"], h["k_cache"], h["v_cache"], h["block_tables"], lens, case.qk_scale, dtype,
+                                 mask=np.maximum(norm, -60000.0))
+    assert max_abs_err(got, ref, dtype) <= tol_for(case)
+
+
+def test_mask_shorter_than_a_context_is_refused():
+    spec = GOLDEN_PA_FEATURE_CASES[1]
+    case = spec["case"]
+    h = wl.make_host_inputs(case)
+    short = pa_mask(spec)[..., : int(h["context_lens"].max()) - 1]
+    with pytest.raises(capi.AtbError) as e:
+        _run_pa_op(case, h, dict(maskType=1), mask=np.ascontiguousarray(short))
+    assert e.value.code == capi.ERROR_INVALID_TENSOR_DIM
