@@ -36,7 +36,7 @@ class PaDesc(ctypes.Structure):
                 ("block_size", ctypes.c_int32), ("num_blocks", ctypes.c_int32),
                 ("max_blocks_per_seq", ctypes.c_int32), ("q_dtype", ctypes.c_int32), ("kv_dtype", ctypes.c_int32),
                 ("qk_scale", ctypes.c_float), ("kernel", ctypes.c_int32), ("sm_count", ctypes.c_int32),
-                ("rope_dim", ctypes.c_int32), ("score_mods", ctypes.c_int32), ("reserved", ctypes.c_int32 * 2)]
+                ("rope_dim", ctypes.c_int32), ("score_mods", ctypes.c_int32), ("kv_layout", ctypes.c_int32), ("reserved", ctypes.c_int32 * 1)]
 
 
 class PaTensors(ctypes.Structure):
@@ -227,9 +227,9 @@ def _check(rc, what):
 # ------------------------------------------------------------------ kernel level
 
 def make_desc(batch, num_heads, kv_heads, dk, dv, block_size, num_blocks, max_blocks, q_dtype, kv_dtype=None,
-              qk_scale=1.0, v_row_dim=None, kernel=KERNEL_AUTO, sm_count=0, rope_dim=0, score_mods=0):
+              qk_scale=1.0, v_row_dim=None, kernel=KERNEL_AUTO, sm_count=0, rope_dim=0, score_mods=0, kv_layout=0):
     d = PaDesc()
-    d.rope_dim, d.score_mods = rope_dim, score_mods
+    d.rope_dim, d.score_mods, d.kv_layout = rope_dim, score_mods, kv_layout
     d.batch, d.num_heads, d.kv_heads = batch, num_heads, kv_heads
     d.head_dim_k, d.head_dim_v, d.v_row_dim = dk, dv, (v_row_dim or dv)
     d.block_size, d.num_blocks, d.max_blocks_per_seq = block_size, num_blocks, max_blocks

@@ -62,12 +62,21 @@ bool ParamCheck(const Param &p)
         ATB_B200_LOG(ERROR, "logN func does not support quant, calcType or compressType features");
         return false;
     }
+    if (p.inputLayout == infer::TYPE_BNSD &&
+        (p.calcType != Param::CALC_TYPE_UNDEFINED || p.compressType != Param::COMPRESS_TYPE_UNDEFINED ||
+         p.quantType != Param::TYPE_QUANT_UNQUANT || p.scaleType != Param::SCALE_TYPE_TOR)) {
+        ATB_B200_LOG(ERROR, "BNSD feature cannot coexist with calcType, compressType, quantType or scaleType features");
+        return false;
+    }
+    if (p.inputLayout != infer::TYPE_BSND && p.inputLayout != infer::TYPE_BNSD) {
+        ATB_B200_LOG(ERROR, "inputLayout should be TYPE_BSND or TYPE_BNSD");
+        return false;
+    }
     // Features outside the decode path of this build.
     if ((p.maskType != Param::UNDEFINED && p.maskType != Param::MASK_TYPE_NORM && p.maskType != Param::MASK_TYPE_ALIBI) ||
         p.compressType != Param::COMPRESS_TYPE_UNDEFINED || p.calcType != Param::CALC_TYPE_UNDEFINED ||
-        p.inputLayout != infer::TYPE_BSND ||
         (p.quantType != Param::TYPE_QUANT_UNQUANT && p.quantType != Param::TYPE_DEQUANT_FUSION)) {
-        ATB_B200_LOG(ERROR, "PagedAttention: SPEC / MASK_FREE / NORM_COMPRESS masks, compress, SPEC, BNSD and QKV-quant "
+        ATB_B200_LOG(ERROR, "PagedAttention: SPEC / MASK_FREE / NORM_COMPRESS masks, compress, SPEC and QKV-quant "
                             "are not supported by this build");
         return false;
     }
@@ -230,8 +239,11 @@ protected:
             return ERROR_INVALID_TENSOR_DIM;
         }
         const int64_t kvHeads = param_.kvHeadNum == 0 ? param_.headNum : param_.kvHeadNum;
-        if (k.dims[2] != kvHeads) {
-            ATB_B200_LOG(ERROR, "PagedAttention: keyCache dim 2 should equal kvHeadNum");
+        // TYPE_BNSD: cache blocks are [kv_heads, block_size, head_size] instead of [block_size, kv_heads, head_size]
+        const bool bnsd = param_.inputLayout == infer::TYPE_BNSD;
+        const int hDim = bnsd ? 1 : 2, sDim = bnsd ? 2 : 1;
+        if (k.dims[hDim] != kvHeads) {
+            ATB_B200_LOG(ERROR, "PagedAttention: the head dim of keyCache should equal kvHeadNum");
             return ERROR_INVALID_TENSOR_DIM;
         }
         if (HasMask()) {
@@ -273,7 +285,7 @@ protected:
                 return ERROR_INVALID_TENSOR_DIM;
             }
         }
-        const int64_t headSize = k.dims[3], blockSize = k.dims[1];
+        const int64_t headSize = k.dims[3], blockSize = k.dims[sDim];
         if (headSize != q.dims[2]) {
             ATB_B200_LOG(ERROR, "PagedAttention: headSize of keyCache and query should be same");
             return ERROR_INVALID_TENSOR_DIM;
@@ -366,7 +378,8 @@ protected:
         d.head_dim_v = mla ? static_cast<int32_t>(param_.mlaVHeadSize)
                            : static_cast<int32_t>(vp.inTensors.at(2).desc.shape.dims[3]);
         d.v_row_dim = mla ? d.head_dim_k : d.head_dim_v;
-        d.block_size = static_cast<int32_t>(k.dims[1]);
+        d.kv_layout = param_.inputLayout == infer::TYPE_BNSD ? ATB_B200_KV_BNSD : ATB_B200_KV_BSND;
+        d.block_size = static_cast<int32_t>(k.dims[d.kv_layout == ATB_B200_KV_BNSD ? 2 : 1]);
         d.num_blocks = static_cast<int32_t>(k.dims[0]);
         d.max_blocks_per_seq = static_cast<int32_t>(vp.inTensors.at(btPos).desc.shape.dims[1]);
         d.q_dtype = ToKernelDtype(vp.inTensors.at(0).desc.dtype);
@@ -498,7 +511,7 @@ private:
                d.block_size == desc_.block_size && d.num_blocks == desc_.num_blocks &&
                d.max_blocks_per_seq == desc_.max_blocks_per_seq && d.q_dtype == desc_.q_dtype &&
                d.kv_dtype == desc_.kv_dtype && d.qk_scale == desc_.qk_scale && d.kernel == desc_.kernel &&
-               d.score_mods == desc_.score_mods;
+               d.score_mods == desc_.score_mods && d.kv_layout == desc_.kv_layout;
     }
     // fp32 scales are used in place; the int64-packed and fp16 encodings are converted once per
     // launch into a small device buffer owned by the operation.

@@ -422,6 +422,7 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
         a.mask_hs = t->mask_head_stride;
     }
     a.logn = (d.score_mods & ATB_B200_SCORE_LOGN) != 0 ? t->logn : nullptr;
+    a.kv_bnsd = d.kv_layout == ATB_B200_KV_BNSD ? 1 : 0;
     a.plan.group_begin = reinterpret_cast<const int32_t *>(blob + h.off_group_begin);
     a.plan.items = reinterpret_cast<const PaItem *>(blob + h.off_items);
     a.plan.seq_part_base = reinterpret_cast<const int32_t *>(blob + h.off_part_base);

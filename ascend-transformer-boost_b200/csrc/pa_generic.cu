@@ -105,9 +105,11 @@ __global__ void __launch_bounds__(kWarps * 32) pa_generic_kernel(const PaArgs a)
                 }
                 continue;
             }
-            const int64_t row = blk * a.block_size + (t % a.block_size);
-            const TKV *kp = kc + (row * a.kv_heads + kvh) * a.dk;
-            const TKV *vp = vc + (row * a.kv_heads + kvh) * a.v_row_dim;
+            // row of (block, token, kv head): token-major blocks, or heads-major ones (BNSD)
+            const int64_t row = a.kv_bnsd ? (blk * a.kv_heads + kvh) * a.block_size + (t % a.block_size)
+                                          : (blk * a.block_size + (t % a.block_size)) * a.kv_heads + kvh;
+            const TKV *kp = kc + row * a.dk;
+            const TKV *vp = vc + row * a.v_row_dim;
             float kf[NPK][4], vf[NPV][4];
 #pragma unroll
             for (int p = 0; p < NPK; ++p) {

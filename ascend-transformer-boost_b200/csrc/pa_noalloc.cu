@@ -105,9 +105,9 @@ extern "C" int atb_b200_pa_decode_static_scratch(const atb_b200_pa_desc *desc, c
             return kErrInvalidParam;
         }
     }
-    if (d.rope_dim != 0 || d.score_mods != 0) {
-        return kErrInvalidTensorDim; // the split latent / rope cache, masks and logN scaling are served by the
-                                     // planned entry points only
+    if (d.rope_dim != 0 || d.score_mods != 0 || d.kv_layout != 0) {
+        return kErrInvalidTensorDim; // the split latent / rope cache, masks, logN scaling and the heads-major
+                                     // cache layout are served by the planned entry points only
     }
     if (d.batch > kMaxBatch) {
         return refuse("batch", d.batch, kMaxBatch);

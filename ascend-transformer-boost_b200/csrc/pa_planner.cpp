@@ -71,6 +71,18 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
             return kErrInvalidTensorDim;
         }
     }
+    if (d.kv_layout != ATB_B200_KV_BSND) {
+        // heads-major cache blocks: fp16 / bf16 caches in the D = 128 kernel and in the CUDA-core kernel
+        if (d.kv_layout != ATB_B200_KV_BNSD || d.rope_dim != 0 || d.kv_dtype == kInt8 || d.v_row_dim != d.head_dim_v) {
+            return kErrInvalidParam;
+        }
+        if (kernel == ATB_B200_KERNEL_AUTO) {
+            kernel = tma_ok ? ATB_B200_KERNEL_TMA_MMA : ATB_B200_KERNEL_GENERIC;
+        }
+        if (kernel == ATB_B200_KERNEL_MLA_TC5) {
+            return kErrInvalidTensorDim;
+        }
+    }
     if (kernel == ATB_B200_KERNEL_AUTO) {
         kernel = tma_ok ? ATB_B200_KERNEL_TMA_MMA : (mla_ok ? ATB_B200_KERNEL_MLA_TC5 : ATB_B200_KERNEL_GENERIC);
     }

@@ -133,10 +133,12 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             const int tok_in_blk = (item.tok_begin + (st0 + j) * kStageTokens + bx * box_tok) % a.block_size;
                             uint8_t *dst = stages + stage * kStageBytes + bx * box_bytes;
                             // a block id outside the cache makes the tile out of bounds: TMA fills zeros
-                            tma_load_4d(dst, &kmap, &full[stage], 0, kvh, tok_in_blk, b);
-                            tma_load_4d(dst + kHalfBytes, &kmap, &full[stage], 64, kvh, tok_in_blk, b);
-                            tma_load_4d(dst + 2 * kHalfBytes, &vmap, &full[stage], 0, kvh, tok_in_blk, b);
-                            tma_load_4d(dst + 3 * kHalfBytes, &vmap, &full[stage], 64, kvh, tok_in_blk, b);
+                            // coordinates (dim, kv head, token, block); heads-major blocks swap the middle two
+                            const int c1 = a.kv_bnsd ? tok_in_blk : kvh, c2 = a.kv_bnsd ? kvh : tok_in_blk;
+                            tma_load_4d(dst, &kmap, &full[stage], 0, c1, c2, b);
+                            tma_load_4d(dst + kHalfBytes, &kmap, &full[stage], 64, c1, c2, b);
+                            tma_load_4d(dst + 2 * kHalfBytes, &vmap, &full[stage], 0, c1, c2, b);
+                            tma_load_4d(dst + 3 * kHalfBytes, &vmap, &full[stage], 64, c1, c2, b);
                         }
                     }
                     if (++stage == kStages) {
@@ -507,7 +509,8 @@ EncodeFn get_encode_fn()
 
 // 4-D view [num_blocks][block_size][kv_heads][128] of a cache; one box = 64 tokens x 64 elements
 // of one kv head (128-byte rows, 128-byte swizzle).
-bool encode_cache_map(CUtensorMap *map, const void *base, int elem_dtype, int kv_heads, int block_size, int num_blocks)
+bool encode_cache_map(CUtensorMap *map, const void *base, int elem_dtype, int kv_heads, int block_size, int num_blocks,
+                      bool bnsd)
 {
     EncodeFn fn = get_encode_fn();
     if (fn == nullptr) {
@@ -517,6 +520,16 @@ bool encode_cache_map(CUtensorMap *map, const void *base, int elem_dtype, int kv
     cuuint64_t dims[4] = {128, (cuuint64_t)kv_heads, (cuuint64_t)block_size, (cuuint64_t)num_blocks};
     cuuint64_t strides[3] = {128 * es, (cuuint64_t)kv_heads * 128 * es, (cuuint64_t)block_size * kv_heads * 128 * es};
     cuuint32_t box[4] = {64, 1, (cuuint32_t)(block_size < kStageTokens ? block_size : kStageTokens), 1};
+    if (bnsd) {
+        // [num_blocks][kv_heads][block_size][128]: coordinates (dim, token, kv head, block), strides still ascending;
+        // a box is the same 64-element x box_tokens tile in shared memory
+        dims[1] = (cuuint64_t)block_size;
+        dims[2] = (cuuint64_t)kv_heads;
+        strides[0] = 128 * es;
+        strides[1] = (cuuint64_t)block_size * 128 * es;
+        box[1] = box[2];
+        box[2] = 1;
+    }
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = fn(map, elem_dtype == kBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                     const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -567,8 +580,8 @@ cudaError_t launch_pa_tma_mma(const PaArgs &args, int q_dtype, int kv_dtype, int
 {
     (void)kv_dtype;
     CUtensorMap km, vm;
-    if (!encode_cache_map(&km, args.k_cache, q_dtype, args.kv_heads, args.block_size, num_blocks) ||
-        !encode_cache_map(&vm, args.v_cache, q_dtype, args.kv_heads, args.block_size, num_blocks)) {
+    if (!encode_cache_map(&km, args.k_cache, q_dtype, args.kv_heads, args.block_size, num_blocks, args.kv_bnsd != 0) ||
+        !encode_cache_map(&vm, args.v_cache, q_dtype, args.kv_heads, args.block_size, num_blocks, args.kv_bnsd != 0)) {
         return cudaErrorInvalidValue;
     }
     return q_dtype == kFp16 ? launch_typed<__half>(args, km, vm, stream) : launch_typed<__nv_bfloat16>(args, km, vm, stream);

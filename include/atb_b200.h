@@ -59,8 +59,13 @@ typedef struct atb_b200_pa_desc {
                                (= head_dim_v = v_row_dim) elements */
     int32_t score_mods;     /* ATB_B200_SCORE_* bits: what is applied to Q*K^T besides qk_scale (PagedAttentionParam
                                maskType NORM / ALIBI, scaleType SCALE_TYPE_LOGN of the reference) */
-    int32_t reserved[2];    /* must be 0 */
+    int32_t kv_layout;      /* ATB_B200_KV_BSND (0): caches [num_blocks, block_size, kv_heads, dim];
+                               ATB_B200_KV_BNSD (1): [num_blocks, kv_heads, block_size, dim] (inputLayout TYPE_BNSD of
+                               the reference; fp16 / bf16 caches, no split MLA cache) */
+    int32_t reserved[1];    /* must be 0 */
 } atb_b200_pa_desc;
+
+enum { ATB_B200_KV_BSND = 0, ATB_B200_KV_BNSD = 1 };
 
 enum {
     ATB_B200_SCORE_MASK = 1, /* score(b, h, t) += mask[b * mask_batch_stride + h * mask_head_stride + t] */

@@ -114,7 +114,7 @@ def test_plan_rejects_bad_arguments():
         capi.PaPlan(d, lens)
     assert e.value.code == capi.ERROR_INVALID_PARAM
     d = capi.make_desc(case.batch, 32, 8, 128, 128, 128, 1000, 32, "bf16", sm_count=148)
-    d.reserved[1] = 7
+    d.reserved[0] = 7
     with pytest.raises(capi.AtbError):
         capi.PaPlan(d, lens)
     # a kernel that does not support the shape
@@ -471,3 +471,32 @@ def test_launch_refuses_missing_or_short_mask_before_touching_the_device():
     _expect(capi.ERROR_INVALID_PARAM, plan.launch, t, 0x1000, 1 << 30, None)          # shorter than the longest context
     t.mask_tokens = 900
     _expect(capi.ERROR_INVALID_PARAM, plan.launch, t, 0x1000, 1 << 30, None)          # no logN factors
+
+
+def test_bnsd_layout_rules(monkeypatch):
+    monkeypatch.setenv("ATB_B200_SM_COUNT", "148")
+    T = capi.atb_tensor
+    ctx = capi.Context()
+    f16, fake = capi.ACL_FLOAT16, 0x1000
+    op = capi.Operation(_pa_param(inputLayout=1))
+    for bad in (dict(inputLayout=1, quantType=1), dict(inputLayout=1, scaleType=1), dict(inputLayout=1, calcType=1),
+                dict(inputLayout=2), dict(inputLayout=1, mlaVHeadSize=512, kvHeadNum=1)):
+        _expect(capi.ERROR_INVALID_PARAM, capi.Operation, _pa_param(**bad))
+    lens = np.array([5, 130, 400], dtype=np.int32)
+    ins = [T(dtype=f16, shape=(3, 8, 128), device_ptr=fake), T(dtype=f16, shape=(16, 2, 64, 128), device_ptr=fake),
+           T(dtype=f16, shape=(16, 2, 64, 128), device_ptr=fake), T(dtype=capi.ACL_INT32, shape=(3, 8), device_ptr=fake),
+           T(dtype=capi.ACL_INT32, shape=(3,), device_ptr=fake, host=lens)]
+    outs = [T(dtype=f16, shape=(3, 8, 128), device_ptr=fake)]
+    assert op.setup(ins, outs, ctx) >= 256
+    bad = list(ins)                                                        # token-major blocks given to a BNSD operation
+    bad[1] = bad[2] = T(dtype=f16, shape=(16, 64, 2, 128), device_ptr=fake)
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, bad, outs, ctx)
+    # kernel level: heads-major blocks exist for fp16 / bf16 caches without the split MLA cache
+    d = capi.make_desc(3, 8, 2, 128, 128, 64, 16, 8, "fp16", sm_count=148, kv_layout=1)
+    assert capi.PaPlan(d, lens).info.kernel == capi.KERNEL_TMA_MMA
+    assert capi.PaPlan(capi.make_desc(3, 8, 2, 96, 96, 64, 16, 8, "fp16", sm_count=148, kv_layout=1),
+                       lens).info.kernel == capi.KERNEL_GENERIC
+    _expect(capi.ERROR_INVALID_PARAM, capi.PaPlan, capi.make_desc(3, 8, 2, 128, 128, 64, 16, 8, "fp16", "int8", sm_count=148,
+                                                                   kv_layout=1), lens)
+    _expect(capi.ERROR_INVALID_PARAM, capi.PaPlan, capi.make_desc(3, 8, 2, 128, 128, 64, 16, 8, "fp16", sm_count=148,
+                                                                   kv_layout=2), lens)

@@ -427,3 +427,40 @@ def test_mask_shorter_than_a_context_is_refused():
     with pytest.raises(capi.AtbError) as e:
         _run_pa_op(case, h, dict(maskType=1), mask=np.ascontiguousarray(short))
     assert e.value.code == capi.ERROR_INVALID_TENSOR_DIM
+
+
+# ------------------------------------------------------------------ heads-major cache blocks (inputLayout TYPE_BNSD)
+
+@pytest.mark.parametrize("kernel", [capi.KERNEL_TMA_MMA, capi.KERNEL_GENERIC], ids=["tma_mma", "generic"])
+@pytest.mark.parametrize("name,block_size", [("zero_and_one_ctx", 128), ("mha_fp16_no_mask", 16), ("gqa4_bf16_mid", 32)])
+def test_bnsd_cache_layout_matches_token_major_result(name, block_size, kernel, monkeypatch):
+    """The same cache contents with blocks stored [kv_heads, block_size, head_size] give the same output bits as the
+    token-major layout (same kernel, same arithmetic), which the hot-path tests pin to the oracle."""
+    import dataclasses
+    base = [c for c in wl.SMALL_CASES if c.name == name][0]
+    case = dataclasses.replace(base, block_size=block_size)
+    h = wl.make_host_inputs(case)
+    from helpers import run_gpu_case
+    want, info = run_gpu_case(case, h, kernel=kernel)
+    assert info.kernel == kernel
+    assert max_abs_err(want, oracle_out(case, h), case.q_dtype) <= tol_for(case)
+    d = host_inputs_to_device(case, h)
+    T = capi.atb_tensor
+    kc = d["k_cache"].permute(0, 2, 1, 3).contiguous()
+    vc = d["v_cache"].permute(0, 2, 1, 3).contiguous()
+    out = torch.full((case.batch, case.heads, case.dv), 7.0, dtype=kc.dtype, device="cuda")
+    lens_dev = torch.from_numpy(h["context_lens"]).cuda()
+    ins = [T(d["q"]), T(kc), T(vc), T(d["block_tables"]), T(lens_dev, host=h["context_lens"])]
+    outs = [T(out)]
+    monkeypatch.setenv("ATB_B200_FORCE_KERNEL", str(kernel))
+    op = capi.Operation(capi.PagedAttentionParam(headNum=case.heads, kvHeadNum=case.kv_heads, qkScale=case.qk_scale,
+                                                 inputLayout=1))
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    ctx = capi.Context(stream.cuda_stream)
+    ws_bytes = op.setup(ins, outs, ctx)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device="cuda")
+    op.execute(ins, outs, ws.data_ptr(), ws_bytes, ctx)
+    torch.cuda.synchronize()
+    got = wl.torch_to_host(out, case.q_dtype)
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
