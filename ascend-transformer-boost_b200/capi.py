@@ -48,7 +48,7 @@ class PaTensors(ctypes.Structure):
                 ("mask_tokens", ctypes.c_int64), ("logn", ctypes.c_void_p)]
 
 
-SCORE_MASK, SCORE_LOGN = 1, 2
+SCORE_MASK, SCORE_LOGN, SCORE_ROWS = 1, 2, 4
 
 
 class PaPlanInfo(ctypes.Structure):
@@ -136,7 +136,7 @@ class PagedCacheLoadParam(ctypes.Structure):
 
 # every symbol include/atb_b200.h declares
 EXPORTS = [
-    "atb_b200_pa_plan_create", "atb_b200_pa_plan_update", "atb_b200_pa_plan_get_info", "atb_b200_pa_plan_dump",
+    "atb_b200_pa_plan_create", "atb_b200_pa_plan_update", "atb_b200_pa_plan_set_rows", "atb_b200_pa_plan_get_info", "atb_b200_pa_plan_dump",
     "atb_b200_pa_plan_destroy", "atb_b200_pa_launch", "atb_b200_reshape_and_cache",
     "atb_b200_pa_plan_device_status", "atb_b200_pa_plan_set_profiling", "atb_b200_pa_plan_kernel_ms",
     "atb_b200_context_create", "atb_b200_context_set_stream", "atb_b200_context_destroy",
@@ -167,6 +167,7 @@ def lib():
         P = ctypes.POINTER
         L.atb_b200_pa_plan_create.argtypes = [P(PaDesc), vp, P(vp)]
         L.atb_b200_pa_plan_update.argtypes = [vp, vp]
+        L.atb_b200_pa_plan_set_rows.argtypes = [vp, vp, ctypes.c_int32, vp, ctypes.c_int64]
         L.atb_b200_pa_plan_get_info.argtypes = [vp, P(PaPlanInfo)]
         L.atb_b200_pa_plan_dump.argtypes = [vp, vp, i32, vp, i32]
         L.atb_b200_pa_plan_destroy.argtypes = [vp]
@@ -255,6 +256,15 @@ class PaPlan:
         import numpy as np
         self._lens = np.ascontiguousarray(context_lens, dtype=np.int32)
         _check(lib().atb_b200_pa_plan_update(self.handle, self._lens.ctypes.data), "atb_b200_pa_plan_update")
+
+    def set_rows(self, bt_rows, bt_row_count, mask_rows=None, mask_row_count=0):
+        """SCORE_ROWS plans: the block-table row and the mask row of every query token (host int32 arrays)."""
+        import numpy as np
+        bt = np.ascontiguousarray(bt_rows, dtype=np.int32)
+        mr = None if mask_rows is None else np.ascontiguousarray(mask_rows, dtype=np.int32)
+        _check(lib().atb_b200_pa_plan_set_rows(self.handle, bt.ctypes.data, int(bt_row_count),
+                                               None if mr is None else mr.ctypes.data, int(mask_row_count)),
+               "atb_b200_pa_plan_set_rows")
 
     @property
     def info(self):

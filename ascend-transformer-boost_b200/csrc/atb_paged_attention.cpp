@@ -72,11 +72,33 @@ bool ParamCheck(const Param &p)
         ATB_B200_LOG(ERROR, "inputLayout should be TYPE_BSND or TYPE_BNSD");
         return false;
     }
+    if (p.calcType != Param::CALC_TYPE_UNDEFINED && p.calcType != Param::CALC_TYPE_SPEC) {
+        ATB_B200_LOG(ERROR, "calcType should be in the range of its enum value");
+        return false;
+    }
+    if (p.calcType == Param::CALC_TYPE_SPEC) {
+        if (p.batchRunStatusEnable) {
+            ATB_B200_LOG(ERROR, "SPEC func does not support dynamic batch");
+            return false;
+        }
+        if (p.mlaVHeadSize == 0 && p.maskType != Param::MASK_TYPE_NORM && p.maskType != Param::MASK_TYPE_SPEC) {
+            ATB_B200_LOG(ERROR, "SPEC func only support norm mask and spec mask");
+            return false;
+        }
+        if (p.mlaVHeadSize > 0) {
+            ATB_B200_LOG(ERROR, "PagedAttention: parallel decoding over the MLA cache is not supported by this build");
+            return false;
+        }
+    } else if (p.maskType == Param::MASK_TYPE_SPEC) {
+        ATB_B200_LOG(ERROR, "MASK_TYPE_SPEC needs calcType CALC_TYPE_SPEC");
+        return false;
+    }
     // Features outside the decode path of this build.
-    if ((p.maskType != Param::UNDEFINED && p.maskType != Param::MASK_TYPE_NORM && p.maskType != Param::MASK_TYPE_ALIBI) ||
-        p.compressType != Param::COMPRESS_TYPE_UNDEFINED || p.calcType != Param::CALC_TYPE_UNDEFINED ||
+    if ((p.maskType != Param::UNDEFINED && p.maskType != Param::MASK_TYPE_NORM && p.maskType != Param::MASK_TYPE_ALIBI &&
+         p.maskType != Param::MASK_TYPE_SPEC) ||
+        p.compressType != Param::COMPRESS_TYPE_UNDEFINED ||
         (p.quantType != Param::TYPE_QUANT_UNQUANT && p.quantType != Param::TYPE_DEQUANT_FUSION)) {
-        ATB_B200_LOG(ERROR, "PagedAttention: SPEC / MASK_FREE / NORM_COMPRESS masks, compress, SPEC and QKV-quant "
+        ATB_B200_LOG(ERROR, "PagedAttention: MASK_FREE / NORM_COMPRESS masks, compress and QKV-quant "
                             "are not supported by this build");
         return false;
     }
@@ -138,6 +160,9 @@ public:
                 if (p.batchRunStatusEnable) {
                     c.push_back(ACL_INT32);
                 }
+                if (p.calcType == Param::CALC_TYPE_SPEC) {
+                    c.push_back(ACL_INT32); // qSeqLens
+                }
                 if (p.scaleType == Param::SCALE_TYPE_LOGN) {
                     c.push_back(ACL_FLOAT);
                 }
@@ -165,6 +190,9 @@ public:
         if (param_.scaleType == Param::SCALE_TYPE_LOGN) {
             n += 1; // logN, always the last input
         }
+        if (param_.calcType == Param::CALC_TYPE_SPEC) {
+            n += 1; // qSeqLens
+        }
         if (param_.batchRunStatusEnable) {
             n += 1; // batchRunStatus
         }
@@ -185,6 +213,9 @@ protected:
     size_t MaskPos() const { return ClPos() + 1; }
     size_t StatusPos() const { return ClPos() + 1 + (HasMask() ? 1 : 0); }
     size_t ScalePos() const { return StatusPos() + (param_.batchRunStatusEnable ? 1 : 0); }
+    bool Spec() const { return param_.calcType == Param::CALC_TYPE_SPEC; }
+    // qSeqLens follows the quantisation tensors (none of which exist together with SPEC in this build)
+    size_t QLensPos() const { return ScalePos(); }
 
     // The mask shapes of the reference's documentation for this SoC class: plain [batch, 1, tokens] or [1, tokens];
     // alibi [batch, heads, 1, tokens] or [heads, 1, tokens].  Fills the element strides the kernels index with.
@@ -192,6 +223,19 @@ protected:
     {
         const int64_t len = m.dims[m.dimNum - 1];
         *tokens = len;
+        if (Spec()) {
+            // parallel decoding: MASK_TYPE_SPEC [num_tokens, max_seq_len], one row per query token; MASK_TYPE_NORM the
+            // square causal mask [max_seq_len, max_seq_len], a token reads row contextLen - qSeqLen + j
+            *headStride = 0;
+            *batchStride = len;
+            const bool ok = m.dimNum == 2 && (param_.maskType == Param::MASK_TYPE_SPEC ? m.dims[0] >= qTokens : m.dims[0] == len);
+            if (!ok) {
+                ATB_B200_LOG(ERROR, "PagedAttention: with CALC_TYPE_SPEC the mask should be [num_tokens, max_seq_len] "
+                                    "(spec mask) or [max_seq_len, max_seq_len] (norm mask)");
+                return m.dimNum == 2 ? ERROR_INVALID_TENSOR_DIM : ERROR_INVALID_TENSOR_DIM_NUM;
+            }
+            return NO_ERROR;
+        }
         if (param_.maskType == Param::MASK_TYPE_NORM) {
             *headStride = 0;
             if (m.dimNum == 3 && m.dims[1] == 1 && m.dims[0] >= qTokens) {
@@ -272,6 +316,19 @@ protected:
             }
             if (in.at(StatusPos()).shape.dimNum != 1 || in.at(StatusPos()).shape.dims[0] < q.dims[0]) {
                 ATB_B200_LOG(ERROR, "PagedAttention: batchRunStatus should hold one value per query token");
+                return ERROR_INVALID_TENSOR_DIM;
+            }
+        } else if (Spec()) {
+            // several query tokens per sequence: the control tensors have one row per sequence
+            const int64_t batch = in.at(clPos).shape.dims[0];
+            const Dims &ql = in.at(QLensPos()).shape;
+            if (ql.dimNum != 1 || ql.dims[0] != batch || in.at(btPos).shape.dims[0] != batch || q.dims[0] < batch) {
+                ATB_B200_LOG(ERROR, "PagedAttention: blockTables, contextLens and qSeqLens should have one row per "
+                                    "sequence, and the query at least one token per sequence");
+                return ERROR_INVALID_TENSOR_DIM;
+            }
+            if (k.dims[sDim] > 128) {
+                ATB_B200_LOG(ERROR, "PagedAttention: blockSize should be no greater than 128 with CALC_TYPE_SPEC");
                 return ERROR_INVALID_TENSOR_DIM;
             }
         } else if (in.at(btPos).shape.dims[0] != q.dims[0] || in.at(clPos).shape.dims[0] != q.dims[0]) {
@@ -398,8 +455,40 @@ protected:
             d.sm_count = std::atoi(sm);
         }
         d.score_mods = (HasMask() ? ATB_B200_SCORE_MASK : 0) |
-                       (param_.scaleType == Param::SCALE_TYPE_LOGN ? ATB_B200_SCORE_LOGN : 0);
+                       (param_.scaleType == Param::SCALE_TYPE_LOGN ? ATB_B200_SCORE_LOGN : 0) |
+                       (Spec() ? ATB_B200_SCORE_ROWS : 0);
         const int32_t *lens = static_cast<const int32_t *>(cl.hostData);
+        if (Spec()) {
+            // Parallel decoding: every query token becomes a planned row of its own, with its sequence's length and
+            // block-table row (qSeqLens is host data: src/ops/ops_infer/paged_attention/param.cpp of the reference).
+            const Tensor &ql = vp.inTensors.at(QLensPos());
+            if (ql.hostData == nullptr) {
+                ATB_B200_LOG(ERROR, "PagedAttention: qSeqLens hostData is null");
+                return ERROR_INVALID_PARAM;
+            }
+            const int32_t *qLens = static_cast<const int32_t *>(ql.hostData);
+            const int64_t batch = cl.desc.shape.dims[0];
+            const bool normMask = param_.maskType == Param::MASK_TYPE_NORM;
+            effectiveLens_.clear();
+            btRows_.clear();
+            maskRows_.clear();
+            for (int64_t b = 0; b < batch; ++b) {
+                if (qLens[b] < 0 || (normMask && qLens[b] > lens[b])) {
+                    ATB_B200_LOG(ERROR, "PagedAttention: qSeqLens should be in [0, contextLens]");
+                    return ERROR_INVALID_PARAM;
+                }
+                for (int32_t j = 0; j < qLens[b]; ++j) {
+                    maskRows_.push_back(normMask ? lens[b] - qLens[b] + j : static_cast<int32_t>(effectiveLens_.size()));
+                    effectiveLens_.push_back(lens[b]);
+                    btRows_.push_back(static_cast<int32_t>(b));
+                }
+            }
+            if (static_cast<int64_t>(effectiveLens_.size()) != q.dims[0]) {
+                ATB_B200_LOG(ERROR, "PagedAttention: the sum of qSeqLens should equal the query tokens");
+                return ERROR_INVALID_PARAM;
+            }
+            lens = effectiveLens_.data();
+        }
         if (HasMask()) {
             int64_t bs = 0, hs = 0, len = 0;
             (void)MaskLayout(vp.inTensors.at(MaskPos()).desc.shape, q.dims[0], &bs, &hs, &len);
@@ -442,6 +531,14 @@ protected:
         }
         if (rc != 0) {
             return rc;
+        }
+        if (Spec()) {
+            const Dims &m = vp.inTensors.at(MaskPos()).desc.shape;
+            rc = atb_b200_pa_plan_set_rows(plan_, btRows_.data(), static_cast<int32_t>(cl.desc.shape.dims[0]),
+                                           maskRows_.data(), m.dims[0]);
+            if (rc != 0) {
+                return rc;
+            }
         }
         atb_b200_pa_plan_info info{};
         atb_b200_pa_plan_get_info(plan_, &info);
@@ -521,7 +618,9 @@ private:
     Param param_;
     std::vector<DtypeComb> combs_;
     atb_b200_pa_plan *plan_ = nullptr;
-    std::vector<int32_t> effectiveLens_; // contextLens with the sequences batchRunStatus switches off set to 0
+    // contextLens with the sequences batchRunStatus switches off set to 0; with CALC_TYPE_SPEC one entry per query token
+    std::vector<int32_t> effectiveLens_;
+    std::vector<int32_t> btRows_, maskRows_; // CALC_TYPE_SPEC: block-table row and mask row of every query token
     atb_b200_pa_desc desc_{};
     void *scratch_[2] = {nullptr, nullptr};
     uint64_t scratchElems_[2] = {0, 0};

@@ -98,6 +98,35 @@ int atb_b200_pa_plan_update(atb_b200_pa_plan *plan, const int32_t *context_lens_
     }
 }
 
+int atb_b200_pa_plan_set_rows(atb_b200_pa_plan *plan, const int32_t *bt_rows, int32_t bt_row_count,
+                              const int32_t *mask_rows, int64_t mask_row_count)
+{
+    if (plan == nullptr || bt_rows == nullptr || (plan->hp.desc.score_mods & ATB_B200_SCORE_ROWS) == 0) {
+        return kErrInvalidParam;
+    }
+    HostPlan &h = plan->hp;
+    const bool masked = (h.desc.score_mods & ATB_B200_SCORE_MASK) != 0;
+    if (masked && mask_rows == nullptr) {
+        return kErrInvalidParam;
+    }
+    const int batch = h.desc.batch;
+    for (int b = 0; b < batch; ++b) {
+        if (bt_rows[b] < 0 || bt_rows[b] >= bt_row_count ||
+            (masked && (mask_rows[b] < 0 || mask_rows[b] >= mask_row_count))) {
+            return kErrInvalidParam;
+        }
+    }
+    if (h.bt_rows.size() != (size_t)batch) {
+        return kErrInvalidParam; // planned without the rows: the blob has no room for them
+    }
+    for (int b = 0; b < batch; ++b) {
+        h.bt_rows[b] = bt_rows[b];
+        h.mask_rows[b] = masked ? mask_rows[b] : 0;
+    }
+    plan->prefetched_slot = -1; // an upload made before the rows were set is not used
+    return ATB_B200_OK;
+}
+
 int atb_b200_pa_plan_get_info(const atb_b200_pa_plan *plan, atb_b200_pa_plan_info *info)
 {
     if (plan == nullptr || info == nullptr) {
@@ -423,6 +452,10 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
     }
     a.logn = (d.score_mods & ATB_B200_SCORE_LOGN) != 0 ? t->logn : nullptr;
     a.kv_bnsd = d.kv_layout == ATB_B200_KV_BNSD ? 1 : 0;
+    if ((d.score_mods & ATB_B200_SCORE_ROWS) != 0) {
+        a.bt_rows = reinterpret_cast<const int32_t *>(blob + h.off_rows);
+        a.mask_rows = a.bt_rows + d.batch;
+    }
     a.plan.group_begin = reinterpret_cast<const int32_t *>(blob + h.off_group_begin);
     a.plan.items = reinterpret_cast<const PaItem *>(blob + h.off_items);
     a.plan.seq_part_base = reinterpret_cast<const int32_t *>(blob + h.off_part_base);

@@ -91,11 +91,13 @@ __global__ void __launch_bounds__(kWarps * 32) pa_generic_kernel(const PaArgs a)
                 o[g][p][0] = o[g][p][1] = o[g][p][2] = o[g][p][3] = 0.f;
             }
         }
-        const int32_t *bt = a.block_tables + (int64_t)item.seq * a.max_blocks;
+        const int32_t *bt = a.block_tables + (int64_t)(a.bt_rows != nullptr ? a.bt_rows[item.seq] : item.seq) * a.max_blocks;
         // SCALE_TYPE_LOGN: the sequence's factor multiplies the scale; additive mask in the query dtype
         const float scale_l2 = a.logn != nullptr ? a.scale_log2 * __ldg(a.logn + item.seq) : a.scale_log2;
         const TQ *mrow = a.mask == nullptr ? nullptr
-                                           : static_cast<const TQ *>(a.mask) + (int64_t)item.seq * a.mask_bs + (int64_t)head0 * a.mask_hs;
+                                           : static_cast<const TQ *>(a.mask) +
+                                                 (int64_t)(a.mask_rows != nullptr ? a.mask_rows[item.seq] : item.seq) * a.mask_bs +
+                                                 (int64_t)head0 * a.mask_hs;
         for (int t = item.tok_begin + warp; t < item.tok_end; t += kWarps) {
             const int64_t blk = bt[t / a.block_size];
             if (blk < 0 || blk >= a.num_blocks) {

@@ -76,6 +76,9 @@ struct PaArgs {
     const void *mask;
     int64_t mask_bs, mask_hs;
     const float *logn;
+    // parallel decoding: the block-table row and the mask row of every query token (null: the token's own index)
+    const int32_t *bt_rows;
+    const int32_t *mask_rows;
     int32_t kv_bnsd; // 1: caches laid out [num_blocks, kv_heads, block_size, dim]
     // optional event probe of one CTA (CTA number = trace_cap >> 24, capacity = its low 24 bits):
     // trace[0] = number of events, then (tag << 56 | index << 40 | cycles)

@@ -23,6 +23,10 @@ void HostPlan::write_blob(uint8_t *dst) const
     if (!combine_seqs.empty()) {
         std::memcpy(dst + off_combine, combine_seqs.data(), combine_seqs.size() * sizeof(int32_t));
     }
+    if (!bt_rows.empty()) {
+        std::memcpy(dst + off_rows, bt_rows.data(), bt_rows.size() * sizeof(int32_t));
+        std::memcpy(dst + off_rows + bt_rows.size() * sizeof(int32_t), mask_rows.data(), mask_rows.size() * sizeof(int32_t));
+    }
 }
 
 int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens, int sm_count, HostPlan *p)
@@ -60,7 +64,7 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
     }
     if (d.score_mods != 0) {
         // masks and logN scaling live in the fp16 / bf16 D = 128 kernel and in the CUDA-core kernel
-        if ((d.score_mods & ~(ATB_B200_SCORE_MASK | ATB_B200_SCORE_LOGN)) != 0 || d.rope_dim != 0) {
+        if ((d.score_mods & ~(ATB_B200_SCORE_MASK | ATB_B200_SCORE_LOGN | ATB_B200_SCORE_ROWS)) != 0 || d.rope_dim != 0) {
             return kErrInvalidParam;
         }
         const bool tma_plain = tma_ok && d.kv_dtype != kInt8;
@@ -221,6 +225,21 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
     p->off_counters = off;
     if (p->fused_combine && p->n_partials > 0) {
         off = align_up(off + (uint64_t)d.batch * p->cols * sizeof(int32_t), 16);
+    }
+    if ((d.score_mods & ATB_B200_SCORE_ROWS) != 0) {
+        // rows set for this batch size stay; otherwise token b reads row b
+        if (p->bt_rows.size() != (size_t)d.batch) {
+            p->bt_rows.resize(d.batch);
+            p->mask_rows.resize(d.batch);
+            for (int b = 0; b < d.batch; ++b) {
+                p->bt_rows[b] = p->mask_rows[b] = b;
+            }
+        }
+        p->off_rows = off;
+        off = align_up(off + 2 * (uint64_t)d.batch * sizeof(int32_t), 16);
+    } else {
+        p->bt_rows.clear();
+        p->mask_rows.clear();
     }
     p->blob_bytes = align_up(off, 256);
     p->off_lse = p->blob_bytes;

@@ -97,7 +97,8 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         for (int it = item_begin; it < item_end && alive; ++it) {
             const PaItem item = a.plan.items[it];
             const int n_st = (item.tok_end - item.tok_begin + kStageTokens - 1) / kStageTokens;
-            const int32_t *bt = a.block_tables + (int64_t)item.seq * a.max_blocks;
+            const int bt_row = (kMods && a.bt_rows != nullptr) ? a.bt_rows[item.seq] : item.seq;
+            const int32_t *bt = a.block_tables + (int64_t)bt_row * a.max_blocks;
             // A 64-token stage is one TMA box per operand half when the cache block holds >= 64 tokens,
             // and 64 / block_size boxes (one per block) otherwise.  The lanes look the block ids of up
             // to 32 boxes up at once; boxes past the end of the range get id -1 (zero-filled tile).
@@ -183,7 +184,8 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 scale_l2 *= __ldg(a.logn + item.seq);
             }
             if (a.mask != nullptr) {
-                const T *mb = static_cast<const T *>(a.mask) + (int64_t)item.seq * a.mask_bs;
+                const T *mb = static_cast<const T *>(a.mask) +
+                              (int64_t)(a.mask_rows != nullptr ? a.mask_rows[item.seq] : item.seq) * a.mask_bs;
                 mrow0 = mb + (int64_t)(kvh * group + min(2 * c, group - 1)) * a.mask_hs;     // padding heads read
                 mrow1 = mb + (int64_t)(kvh * group + min(2 * c + 1, group - 1)) * a.mask_hs; // a real head's row
             }
@@ -539,7 +541,7 @@ bool encode_cache_map(CUtensorMap *map, const void *base, int elem_dtype, int kv
 
 template <typename T> cudaError_t launch_typed(const PaArgs &args, const CUtensorMap &km, const CUtensorMap &vm, cudaStream_t s)
 {
-    const bool mods = args.mask != nullptr || args.logn != nullptr;
+    const bool mods = args.mask != nullptr || args.logn != nullptr || args.bt_rows != nullptr;
     auto kern = mods ? pa_tma_mma_kernel<T, true> : pa_tma_mma_kernel<T, false>;
     static bool configured_plain[64] = {}, configured_mods[64] = {};
     bool *configured = mods ? configured_mods : configured_plain;

@@ -69,7 +69,11 @@ enum { ATB_B200_KV_BSND = 0, ATB_B200_KV_BNSD = 1 };
 
 enum {
     ATB_B200_SCORE_MASK = 1, /* score(b, h, t) += mask[b * mask_batch_stride + h * mask_head_stride + t] */
-    ATB_B200_SCORE_LOGN = 2  /* the scale of sequence b is qk_scale * logn[b] */
+    ATB_B200_SCORE_LOGN = 2, /* the scale of sequence b is qk_scale * logn[b] */
+    ATB_B200_SCORE_ROWS = 4  /* query token b reads row bt_rows[b] of block_tables and (with a mask) row mask_rows[b]
+                                of the mask instead of row b: parallel decoding (CALC_TYPE_SPEC of the reference),
+                                where several query tokens share one sequence's cache.  The rows are set with
+                                atb_b200_pa_plan_set_rows; until then they are the identity. */
 };
 
 /* Device pointers of one call.  v_cache == k_cache for the MLA combined cache. */
@@ -119,6 +123,16 @@ typedef struct atb_b200_pa_plan_info {
 int atb_b200_pa_plan_create(const atb_b200_pa_desc *desc, const int32_t *context_lens_host, atb_b200_pa_plan **plan);
 /* Re-plan in place for new context_lens of the same batch (one decode step later). */
 int atb_b200_pa_plan_update(atb_b200_pa_plan *plan, const int32_t *context_lens_host);
+/*
+ * ATB_B200_SCORE_ROWS only: which row of block_tables (bt_rows[b] in [0, bt_row_count)) and of the mask
+ * (mask_rows[b] in [0, mask_row_count); may be NULL without a mask) query token b uses; both host arrays of
+ * desc->batch entries, copied.  Call after plan_create / plan_update and before plan_prefetch / launch of the step.
+ * The caller passes block_tables with bt_row_count rows and a mask with mask_row_count rows of mask_tokens elements
+ * (mask_batch_stride = the row length).  Replaces the qSeqLens handling of the reference's tiling
+ * (paged_attention_tiling.cpp; qSeqLens is host data there too, ops_infer/paged_attention/param.cpp).
+ */
+int atb_b200_pa_plan_set_rows(atb_b200_pa_plan *plan, const int32_t *bt_rows, int32_t bt_row_count,
+                              const int32_t *mask_rows, int64_t mask_row_count);
 int atb_b200_pa_plan_get_info(const atb_b200_pa_plan *plan, atb_b200_pa_plan_info *info);
 /* Copies the plan's work items (4 int32 each: seq, tok_begin, tok_end, partial slot or -1) and the
  * per-CTA-group item offsets into caller arrays (either may be NULL); for tests and debugging. */

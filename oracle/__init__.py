@@ -7,5 +7,5 @@ tests/apitest/kernelstest/mix/test_reshape_and_cache.py:45-68 of the reference) 
 against outputs of those Python functions stored under tests/golden/.
 """
 from .oracle import (build, load, multi_latent_attention, num_threads, paged_attention,  # noqa: F401
-                     reshape_and_cache)
+                     paged_attention_spec, reshape_and_cache)
 from . import cache_ops  # noqa: F401

@@ -120,6 +120,29 @@ def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping):
         raise ValueError("oracle_reshape_and_cache rejected its arguments")
 
 
+def paged_attention_spec(q, k_cache, v_cache, block_tables, q_lens, context_lens, scale, q_dtype, mask, mask_rows_are_tokens,
+                         nthreads=0):
+    """Parallel decoding (PagedAttentionParam::CALC_TYPE_SPEC): sequence b owns q_lens[b] consecutive query tokens,
+    each of which attends to all context_lens[b] cached tokens of that sequence plus a row of `mask` (fp32):
+    row = the token's index for MASK_TYPE_SPEC ([tokens, T]; `mask_rows_are_tokens`), row = ctx - q_len + j of the
+    square causal mask [T, T] for MASK_TYPE_NORM.  Restates ref_single_query_cached_kv_attention of
+    tests/apitest/kernelstest/mix/test_paged_attention_lookahead.py:97-140 by expanding every query token into a
+    sequence of its own (its sequence's block-table row and length, its mask row) for `paged_attention`."""
+    q_lens = np.asarray(q_lens, dtype=np.int64)
+    context_lens = np.asarray(context_lens, dtype=np.int32)
+    tokens = int(q_lens.sum())
+    assert q.shape[0] == tokens and len(q_lens) == len(context_lens) == block_tables.shape[0]
+    owner = np.repeat(np.arange(len(q_lens)), q_lens)
+    within = np.arange(tokens) - np.repeat(np.cumsum(q_lens) - q_lens, q_lens)
+    lens = context_lens[owner]
+    mask = np.asarray(mask, dtype=np.float32)
+    rows = np.arange(tokens) if mask_rows_are_tokens else lens.astype(np.int64) - q_lens[owner] + within
+    assert rows.min(initial=0) >= 0 and rows.max(initial=0) < mask.shape[0]
+    per_token = np.ascontiguousarray(mask[rows][:, None, :])                     # [tokens, 1, T]
+    return paged_attention(q, k_cache, v_cache, np.ascontiguousarray(block_tables[owner]), lens, scale, q_dtype,
+                           nthreads=nthreads, mask=per_token)
+
+
 def multi_latent_attention(q_nope, q_rope, ct_kv, k_rope, block_tables, context_lens, scale, q_dtype, **kw):
     """MultiLatentAttention decode golden with the split cache (cacheMode 1 of the reference): the
     latent part [.., 512] and the rope part [.., 64] of the query and of the cache are separate

@@ -168,6 +168,41 @@ def pa_mask(spec):
     return _wl.encode(m, case.q_dtype)
 
 
+# ------------------------------------------------------------------ PagedAttention, parallel decoding (CALC_TYPE_SPEC)
+
+GOLDEN_PA_SPEC_CASES = [
+    dict(case=Case("spec_mask_fp16", batch=4, heads=8, kv_heads=8, q_dtype="fp16", ctx=("list", [10, 64, 64, 64]),
+                   seed=131), q_lens=[1, 15, 30, 6], mask="spec"),
+    dict(case=Case("spec_norm_mask_gqa_fp16", batch=3, heads=8, kv_heads=2, q_dtype="fp16", ctx=("list", [140, 33, 257]),
+                   seed=132), q_lens=[4, 2, 5], mask="norm"),
+]
+
+
+def spec_inputs(spec):
+    """Inputs of a parallel-decoding case: the caches, block tables and context lengths of `case` (one row per
+    sequence), a query with sum(q_lens) tokens, and the mask built like the reference test builds it
+    (tests/apitest/kernelstest/mix/test_paged_attention_lookahead.py:176-191): MASK_TYPE_SPEC
+    [tokens, max_ctx] with the causal triangle of every sequence in its last q_len columns; MASK_TYPE_NORM the
+    square causal mask [max_ctx, max_ctx] (a token reads row ctx - q_len + j)."""
+    case = spec["case"]
+    d = _wl.make_host_inputs(case)
+    q_lens = np.asarray(spec["q_lens"], dtype=np.int32)
+    tokens, T = int(q_lens.sum()), int(d["context_lens"].max())
+    rng = np.random.default_rng(case.seed + 29)
+    d["q"] = _wl.encode(rng.standard_normal((tokens, case.heads, case.dk)).astype(np.float32), case.q_dtype)
+    if spec["mask"] == "spec":
+        m = np.zeros((tokens, T), dtype=np.float32)
+        pre = 0
+        for n in q_lens:
+            m[pre:pre + n, T - n:] = np.triu(np.ones((n, n), dtype=np.float32), 1) * -10000.0
+            pre += n
+    else:
+        m = np.triu(np.ones((T, T), dtype=np.float32), 1) * -10000.0
+    d["mask"] = _wl.encode(m, case.q_dtype)
+    d["q_lens"] = q_lens
+    return d
+
+
 # ------------------------------------------------------------------ fused RMSNorm + RoPE + cache write
 
 GOLDEN_NRR_CASES = [

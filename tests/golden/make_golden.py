@@ -32,8 +32,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, HERE)
 
-from golden_cases import (GOLDEN_BLOCKCOPY_CASES, GOLDEN_PA_CASES, GOLDEN_PA_FEATURE_CASES, GOLDEN_PCL_CASES,  # noqa: E402
-                          GOLDEN_NRR_CASES, GOLDEN_RAC_CASES, blockcopy_inputs, load_workloads, nrr_inputs, pa_mask,
+from golden_cases import (GOLDEN_BLOCKCOPY_CASES, GOLDEN_PA_CASES, GOLDEN_PA_FEATURE_CASES, GOLDEN_PA_SPEC_CASES, GOLDEN_PCL_CASES,  # noqa: E402
+                          GOLDEN_NRR_CASES, GOLDEN_RAC_CASES, blockcopy_inputs, load_workloads, nrr_inputs, pa_mask, spec_inputs,
                           pcl_inputs, rac_inputs)
 
 wl = load_workloads()
@@ -184,6 +184,21 @@ def run_pa_feature_case(common, spec):
     return res
 
 
+def run_pa_spec_case(lookahead, spec):
+    """Parallel decoding through the golden function of the reference's lookahead test (numpy, fp16; mask_type 3 =
+    MASK_TYPE_SPEC rows per token, 0 = rows of the square causal mask)."""
+    case = spec["case"]
+    assert case.q_dtype == "fp16"
+    d = spec_inputs(spec)
+    t = lookahead.TestUnpadPagedAttention()
+    out = np.zeros((d["q"].shape[0], case.heads, case.dv), dtype=np.float16)
+    t.ref_single_query_cached_kv_attention(out, d["q"], d["k_cache"], d["v_cache"], d["block_tables"].tolist(),
+                                           d["q_lens"].tolist(), d["context_lens"].tolist(), d["mask"],
+                                           3 if spec["mask"] == "spec" else 0)
+    dig = {k: v for k, v in d.items() if isinstance(v, np.ndarray)}
+    return {"out": out, "input_sha256": np.frombuffer(digest(dig).encode(), dtype=np.uint8)}
+
+
 def run_nrr_case(mod_fp16, mod_bf16, spec):
     """The fused RMSNorm + RoPE + cache write: the reference's three golden functions in golden_calc's order.
     fp16: rounded float16 rows; bf16: the reference keeps float32 rows (stored as such)."""
@@ -252,7 +267,14 @@ def main():
     pcl = _load(os.path.join(kt, "mix/test_paged_cache_load_nd.py"), "ref_pcl")
     nrr16 = _load(os.path.join(kt, "mix/test_rms_norm_and_rope_and_reshape_and_cache.py"), "ref_nrr_fp16")
     nrrbf = _load(os.path.join(kt, "mix/test_rms_norm_and_rope_and_reshape_and_cache_bf16.py"), "ref_nrr_bf16")
+    lookahead = _load(os.path.join(kt, "mix/test_paged_attention_lookahead.py"), "ref_pa_lookahead")
     os.chdir(cwd)
+    for spec in GOLDEN_PA_SPEC_CASES:
+        res = run_pa_spec_case(lookahead, spec)
+        np.savez_compressed(os.path.join(HERE, f"pa_{spec['case'].name}.npz"), **res)
+        print("wrote", spec["case"].name, res["out"].shape)
+    if "--spec-only" in sys.argv:
+        return
     for spec in GOLDEN_NRR_CASES:
         np.savez_compressed(os.path.join(HERE, f"nrr_{spec['name']}.npz"), **run_nrr_case(nrr16, nrrbf, spec))
         print("wrote nrr", spec["name"])

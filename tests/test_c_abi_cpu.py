@@ -453,7 +453,7 @@ def test_planner_routes_score_modifiers():
     assert plan(kv="int8") == capi.KERNEL_GENERIC                          # the int8 TMA kernel carries no mask code
     assert plan(kernel=capi.KERNEL_GENERIC) == capi.KERNEL_GENERIC
     _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, kv="int8", kernel=capi.KERNEL_TMA_MMA)
-    _expect(capi.ERROR_INVALID_PARAM, plan, mods=4)
+    _expect(capi.ERROR_INVALID_PARAM, plan, mods=8)
     with pytest.raises(capi.AtbError):                                     # no mask on the split MLA cache
         capi.PaPlan(capi.make_desc(2, 8, 1, 576, 512, 128, 64, 8, "bf16", sm_count=148, v_row_dim=512, rope_dim=64,
                                    score_mods=1), lens)
@@ -500,3 +500,56 @@ def test_bnsd_layout_rules(monkeypatch):
                                                                    kv_layout=1), lens)
     _expect(capi.ERROR_INVALID_PARAM, capi.PaPlan, capi.make_desc(3, 8, 2, 128, 128, 64, 16, 8, "fp16", sm_count=148,
                                                                    kv_layout=2), lens)
+
+
+# ------------------------------------------------------------------ parallel decoding (CALC_TYPE_SPEC)
+
+def test_parallel_decoding_param_and_setup_rules(monkeypatch):
+    monkeypatch.setenv("ATB_B200_SM_COUNT", "148")
+    T = capi.atb_tensor
+    ctx = capi.Context()
+    f16, i32, fake = capi.ACL_FLOAT16, capi.ACL_INT32, 0x1000
+    assert capi.Operation(_pa_param(calcType=1, maskType=3)).input_num == 7
+    assert capi.Operation(_pa_param(calcType=1, maskType=1)).input_num == 7
+    for bad in (dict(calcType=1), dict(calcType=1, maskType=2), dict(calcType=1, maskType=3, batchRunStatusEnable=True),
+                dict(maskType=3), dict(calcType=2, maskType=3), dict(calcType=1, maskType=3, scaleType=1),
+                dict(calcType=1, maskType=3, inputLayout=1), dict(calcType=1, maskType=3, quantType=1)):
+        _expect(capi.ERROR_INVALID_PARAM, capi.Operation, _pa_param(**bad))
+    lens = np.array([40, 300], dtype=np.int32)
+    qlens = np.array([3, 2], dtype=np.int32)
+
+    def tensors(tokens=5, mask_shape=(5, 300), qlens=qlens, bs=128):
+        ins = [T(dtype=f16, shape=(tokens, 8, 128), device_ptr=fake), T(dtype=f16, shape=(16, bs, 2, 128), device_ptr=fake),
+               T(dtype=f16, shape=(16, bs, 2, 128), device_ptr=fake), T(dtype=i32, shape=(2, 4), device_ptr=fake),
+               T(dtype=i32, shape=(2,), device_ptr=fake, host=lens), T(dtype=f16, shape=mask_shape, device_ptr=fake),
+               T(dtype=i32, shape=(2,), device_ptr=fake, host=qlens)]
+        return ins, [T(dtype=f16, shape=(tokens, 8, 128), device_ptr=fake)]
+    spec = capi.Operation(_pa_param(calcType=1, maskType=3))
+    assert spec.setup(*tensors(), ctx) >= 256
+    _expect(capi.ERROR_INVALID_PARAM, spec.setup, *tensors(tokens=6, mask_shape=(6, 300)), ctx)       # sum(qSeqLens) != tokens
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, spec.setup, *tensors(mask_shape=(4, 300)), ctx)            # a mask row per token
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, spec.setup, *tensors(mask_shape=(5, 299)), ctx)            # shorter than a context
+    _expect(capi.ERROR_INVALID_TENSOR_DIM_NUM, spec.setup, *tensors(mask_shape=(5, 1, 300)), ctx)
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, spec.setup, *tensors(bs=256), ctx)
+    ins, outs = tensors()
+    ins[6] = T(dtype=i32, shape=(2,), device_ptr=fake)                                                # qSeqLens without host data
+    _expect(capi.ERROR_INVALID_PARAM, spec.setup, ins, outs, ctx)
+    norm = capi.Operation(_pa_param(calcType=1, maskType=1))
+    assert norm.setup(*tensors(mask_shape=(512, 512)), ctx) >= 256
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, norm.setup, *tensors(mask_shape=(5, 512)), ctx)            # must be square
+    _expect(capi.ERROR_INVALID_PARAM, norm.setup, *tensors(tokens=43, mask_shape=(512, 512),
+                                                            qlens=np.array([41, 2], dtype=np.int32)), ctx)  # q_len > ctx
+
+
+def test_plan_rows_contract():
+    lens = np.array([40, 40, 40, 300, 300], dtype=np.int32)
+    d = capi.make_desc(5, 8, 2, 128, 128, 128, 16, 4, "fp16", sm_count=148, score_mods=capi.SCORE_ROWS | capi.SCORE_MASK)
+    plan = capi.PaPlan(d, lens)
+    plan.set_rows([0, 0, 0, 1, 1], 2, [0, 1, 2, 3, 4], 5)
+    _expect(capi.ERROR_INVALID_PARAM, plan.set_rows, [0, 0, 0, 1, 2], 2, [0, 1, 2, 3, 4], 5)       # block-table row out of range
+    _expect(capi.ERROR_INVALID_PARAM, plan.set_rows, [0, 0, 0, 1, 1], 2, [0, 1, 2, 3, 5], 5)       # mask row out of range
+    _expect(capi.ERROR_INVALID_PARAM, plan.set_rows, [0, 0, 0, 1, 1], 2, None, 0)                  # masked plan needs mask rows
+    plain = capi.PaPlan(capi.make_desc(5, 8, 2, 128, 128, 128, 16, 4, "fp16", sm_count=148), lens)
+    _expect(capi.ERROR_INVALID_PARAM, plain.set_rows, [0, 0, 0, 1, 1], 2)                          # not a SCORE_ROWS plan
+    plan.update(lens + 1)                                                                          # rows survive a re-plan
+    assert plan.info.plan_bytes > plain.info.plan_bytes - 256

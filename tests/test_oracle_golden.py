@@ -171,3 +171,29 @@ def test_norm_rope_reshape_oracle_matches_reference_golden(spec):
         got, ref = wl.to_f32(cache, "bf16"), fx["key_cache"]
         assert np.all(np.abs(got - ref) <= 2.0 ** -8 * np.maximum(np.abs(ref), 2.0 ** -20))
     assert np.count_nonzero(cache) > 0
+
+
+# ------------------------------------------------------------------ PagedAttention, parallel decoding
+
+from golden_cases import GOLDEN_PA_SPEC_CASES, spec_inputs  # noqa: E402
+
+
+@pytest.mark.parametrize("spec", GOLDEN_PA_SPEC_CASES, ids=lambda s: s["case"].name)
+def test_oracle_parallel_decoding_matches_reference_golden(spec):
+    """The reference's lookahead golden rounds the scores and the output to fp16 between its steps, so it is matched
+    at that test's own threshold, 2^-8 * max(1, |golden|)
+    (tests/apitest/kernelstest/mix/test_paged_attention_lookahead.py:49-55)."""
+    case = spec["case"]
+    fx = np.load(os.path.join(HERE, f"pa_{case.name}.npz"))
+    d = spec_inputs(spec)
+    assert _digest(d) == bytes(fx["input_sha256"]).decode(), "seeded inputs changed; regenerate the fixtures"
+    out = oracle.paged_attention_spec(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], d["q_lens"],
+                                      d["context_lens"], case.qk_scale, case.q_dtype, wl.to_f32(d["mask"], case.q_dtype),
+                                      mask_rows_are_tokens=spec["mask"] == "spec")
+    got, ref = wl.to_f32(out, case.q_dtype), wl.to_f32(fx["out"], case.q_dtype)
+    assert np.all(np.abs(got - ref) <= 2.0 ** -8 * np.maximum(1.0, np.abs(ref)))
+    # the mask matters: without it the later tokens of a sequence would see their successors
+    owner = np.repeat(np.arange(case.batch), d["q_lens"])
+    unmasked = oracle.paged_attention(d["q"], d["k_cache"], d["v_cache"], d["block_tables"][owner],
+                                      d["context_lens"][owner], case.qk_scale, case.q_dtype)
+    assert np.abs(wl.to_f32(unmasked, case.q_dtype) - ref).max() > 2.0 ** -5

@@ -464,3 +464,59 @@ def test_bnsd_cache_layout_matches_token_major_result(name, block_size, kernel, 
     torch.cuda.synchronize()
     got = wl.torch_to_host(out, case.q_dtype)
     assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+# ------------------------------------------------------------------ parallel decoding (CALC_TYPE_SPEC)
+
+from golden_cases import GOLDEN_PA_SPEC_CASES, spec_inputs  # noqa: E402
+
+
+def _run_spec_op(case, d, mask_kind, q_lens, lens):
+    dt = case.q_dtype
+    T = capi.atb_tensor
+    q, kc, vc = to_dev(d["q"], dt), to_dev(d["k_cache"], dt), to_dev(d["v_cache"], dt)
+    bt = torch.from_numpy(d["block_tables"]).cuda()
+    mask = to_dev(d["mask"], dt)
+    lens_dev, ql_dev = torch.from_numpy(lens).cuda(), torch.from_numpy(q_lens).cuda()
+    out = torch.full((q.shape[0], case.heads, case.dv), 7.0, dtype=q.dtype, device="cuda")
+    ins = [T(q), T(kc), T(vc), T(bt), T(lens_dev, host=lens), T(mask), T(ql_dev, host=q_lens)]
+    outs = [T(out)]
+    op = capi.Operation(capi.PagedAttentionParam(headNum=case.heads, kvHeadNum=case.kv_heads, qkScale=case.qk_scale,
+                                                 calcType=1, maskType=3 if mask_kind == "spec" else 1))
+    assert op.infer_shape(ins, 1) == [tuple(out.shape)]
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    ctx = capi.Context(stream.cuda_stream)
+    ws_bytes = op.setup(ins, outs, ctx)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device="cuda")
+    op.execute(ins, outs, ws.data_ptr(), ws_bytes, ctx)
+    torch.cuda.synchronize()
+    return wl.torch_to_host(out, dt)
+
+
+@pytest.mark.parametrize("kernel", [capi.KERNEL_TMA_MMA, capi.KERNEL_GENERIC], ids=["tma_mma", "generic"])
+@pytest.mark.parametrize("spec", GOLDEN_PA_SPEC_CASES, ids=lambda s: s["case"].name)
+def test_parallel_decoding_matches_reference_golden(spec, kernel, monkeypatch):
+    case = spec["case"]
+    fx = np.load(os.path.join(GOLDEN_DIR, f"pa_{case.name}.npz"))
+    d = spec_inputs(spec)
+    monkeypatch.setenv("ATB_B200_FORCE_KERNEL", str(kernel))
+    got = _run_spec_op(case, d, spec["mask"], d["q_lens"], d["context_lens"])
+    ref = oracle.paged_attention_spec(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], d["q_lens"], d["context_lens"],
+                                      case.qk_scale, case.q_dtype, wl.to_f32(d["mask"], case.q_dtype),
+                                      mask_rows_are_tokens=spec["mask"] == "spec")
+    assert max_abs_err(got, ref, case.q_dtype) <= tol_for(case)
+    # and the reference's own golden at that test's threshold (it rounds scores and output to fp16 on the way)
+    g, r = wl.to_f32(got, case.q_dtype), wl.to_f32(fx["out"], case.q_dtype)
+    assert np.all(np.abs(g - r) <= 2.0 ** -8 * np.maximum(1.0, np.abs(r)))
+
+
+def test_parallel_decoding_long_sequences_bf16():
+    """Multi-token queries over sequences long enough to be split over CTAs, a sequence with no query token, bf16."""
+    case = wl.Case("spec_long_bf16", batch=4, heads=16, kv_heads=4, q_dtype="bf16", ctx=("list", [5000, 700, 64, 2300]), seed=91)
+    spec = dict(case=case, q_lens=[4, 0, 3, 2], mask="norm")
+    d = spec_inputs(spec)
+    got = _run_spec_op(case, d, "norm", d["q_lens"], d["context_lens"])
+    ref = oracle.paged_attention_spec(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], d["q_lens"], d["context_lens"],
+                                      case.qk_scale, "bf16", wl.to_f32(d["mask"], "bf16"), mask_rows_are_tokens=False)
+    assert max_abs_err(got, ref, "bf16") <= tol_for(case)
