@@ -97,6 +97,11 @@ class ReshapeAndCacheWithStrideParam(ctypes.Structure):
     _fields_ = [("compressType", ctypes.c_int32), ("kvCacheCfg", ctypes.c_int32), ("rsv", ctypes.c_uint8 * 16)]
 
 
+class KvCacheParam(ctypes.Structure):
+    """Byte layout of atb::infer::KvCacheParam (8 bytes)."""
+    _fields_ = [("rsv", ctypes.c_uint8 * 8)]
+
+
 class MultiLatentAttentionParam(ctypes.Structure):
     """Byte layout of atb::infer::MultiLatentAttentionParam (64 bytes); cacheMode 1 = separate latent / rope caches."""
     _fields_ = [("headNum", ctypes.c_int32), ("qkScale", ctypes.c_float), ("kvHeadNum", ctypes.c_int32),
@@ -151,6 +156,7 @@ EXPORTS = [
     "atb_b200_reshape_and_cache_strided", "atb_b200_operation_create_reshape_and_cache_with_stride",
     "atb_b200_norm_rope_reshape", "atb_b200_operation_create_norm_rope_reshape",
     "atb_b200_operation_create_multi_latent_attention",
+    "atb_b200_kv_cache", "atb_b200_operation_create_kv_cache",
 ]
 
 _lib = None
@@ -184,6 +190,9 @@ def lib():
         L.atb_b200_operation_create_reshape_and_cache.argtypes = [vp, u64, P(vp)]
         L.atb_b200_operation_create_block_copy.argtypes = [vp, u64, P(vp)]
         L.atb_b200_operation_create_multi_latent_attention.argtypes = [vp, u64, P(vp)]
+        L.atb_b200_operation_create_kv_cache.argtypes = [vp, u64, P(vp)]
+        L.atb_b200_kv_cache.argtypes = [vp, vp, vp, vp, vp, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                        ctypes.c_int64, vp]
         L.atb_b200_operation_create_norm_rope_reshape.argtypes = [vp, u64, P(vp)]
         L.atb_b200_norm_rope_reshape.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, ctypes.c_float, i64, vp]
         L.atb_b200_operation_create_reshape_and_cache_with_stride.argtypes = [vp, u64, P(vp)]
@@ -399,6 +408,15 @@ def block_copy(k_cache, v_cache, src_blocks, dst_blocks, cum_sum, stream_ptr=Non
                                      stream_ptr if stream_ptr is not None else torch_stream_ptr()), "atb_b200_block_copy")
 
 
+def kv_cache(new_kv, layer_id, past, token_offset, seq_len, stream_ptr=None):
+    """In place on torch CUDA tensors: past [layers, batch, max_seqlen, hidden] receives the rows of new_kv
+    [tokens, hidden]; layer_id [1], token_offset [batch], seq_len [batch] are int32 device tensors."""
+    _check(lib().atb_b200_kv_cache(_ptr(new_kv), _ptr(layer_id), _ptr(past), _ptr(token_offset), _ptr(seq_len),
+                                   new_kv.shape[0], past.shape[0], past.shape[1], past.shape[2],
+                                   past.shape[3] * past.element_size(),
+                                   stream_ptr if stream_ptr is not None else torch_stream_ptr()), "atb_b200_kv_cache")
+
+
 def paged_cache_load(k_cache, v_cache, block_tables, context_lens, key, value, seq_starts=None, cumulative=False,
                      stream_ptr=None):
     """Gathers cached tokens into key / value ([rows, heads, D] torch CUDA tensors)."""
@@ -558,6 +576,8 @@ class Operation:
         elif isinstance(param, ReshapeAndCacheWithStrideParam):
             fn, what = (lib().atb_b200_operation_create_reshape_and_cache_with_stride,
                         "CreateOperation(ReshapeAndCacheWithStrideParam)")
+        elif isinstance(param, KvCacheParam):
+            fn, what = lib().atb_b200_operation_create_kv_cache, "CreateOperation(KvCacheParam)"
         elif isinstance(param, MultiLatentAttentionParam):
             fn, what = (lib().atb_b200_operation_create_multi_latent_attention,
                         "CreateOperation(MultiLatentAttentionParam)")

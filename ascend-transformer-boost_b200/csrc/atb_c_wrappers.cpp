@@ -86,6 +86,19 @@ int atb_b200_operation_create_reshape_and_cache(const void *param, uint64_t para
     return st;
 }
 
+int atb_b200_operation_create_kv_cache(const void *param, uint64_t param_bytes, void **operation)
+{
+    if (param == nullptr || operation == nullptr || param_bytes != sizeof(infer::KvCacheParam)) {
+        return ERROR_INVALID_PARAM;
+    }
+    infer::KvCacheParam p;
+    std::memcpy(&p, param, sizeof(p));
+    Operation *op = nullptr;
+    Status st = CreateOperation(p, &op);
+    *operation = op;
+    return st;
+}
+
 int atb_b200_operation_create_block_copy(const void *param, uint64_t param_bytes, void **operation)
 {
     if (param == nullptr || operation == nullptr || param_bytes != sizeof(infer::BlockCopyParam)) {

@@ -548,7 +548,107 @@ private:
     std::vector<DtypeComb> combs_;
 };
 
+// ---------------------------------------------------------------------------------------------------
+// KvCache: appends the new K (or V) rows of every sequence to a contiguous per-layer cache.  Rules of
+// src/ops/ops_infer/kv_cache/kv_cache_operation.cpp:42-141 of the reference (ND layout).
+class KvCacheOperation : public OperationBase {
+public:
+    explicit KvCacheOperation(const infer::KvCacheParam &p) : OperationBase("KvCacheOperation"), param_(p)
+    {
+        for (aclDataType t : {ACL_FLOAT16, ACL_BF16, ACL_INT8}) {
+            combs_.push_back({t, ACL_INT32, t, ACL_INT32, ACL_INT32});
+        }
+    }
+    uint32_t GetInputNum() const override { return 5; } // newKv, layerId, past, tokenOffset, seqLen
+    uint32_t GetOutputNum() const override { return 0; } // past is updated in place
+
+protected:
+    const std::vector<DtypeComb> &DtypeCombs() const override { return combs_; }
+
+    Status DimCheck(const SVector<TensorDesc> &in, Status dimNumError) const
+    {
+        if ((in.at(0).shape.dimNum != 2 && in.at(0).shape.dimNum != 4) || in.at(1).shape.dimNum != 1 ||
+            in.at(2).shape.dimNum != 4 || in.at(3).shape.dimNum != 1 || in.at(4).shape.dimNum != 1) {
+            ATB_B200_LOG(ERROR, "KvCache: invalid intensor dimNums");
+            return dimNumError;
+        }
+        const Dims &kv = in.at(0).shape, &past = in.at(2).shape;
+        const int64_t hiddenSize = past.dims[3];
+        if (in.at(2).dtype == ACL_INT8 ? hiddenSize % 32 != 0 : hiddenSize % 16 != 0) {
+            ATB_B200_LOG(ERROR, "KvCache: hiddenSize should be a multiple of 16 (int8: 32)");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (hiddenSize != (kv.dimNum == 2 ? kv.dims[1] : kv.dims[2] * kv.dims[3])) {
+            ATB_B200_LOG(ERROR, "KvCache: hiddenSizes should be same");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (past.dims[1] != in.at(3).shape.dims[0] || past.dims[1] != in.at(4).shape.dims[0]) {
+            ATB_B200_LOG(ERROR, "KvCache: batches should be same");
+            return ERROR_INVALID_TENSOR_DIM;
+        }
+        return NO_ERROR;
+    }
+
+    Status InferShapeCheckImpl(const SVector<TensorDesc> &in) const override
+    {
+        return DimCheck(in, ERROR_INVALID_TENSOR_DIM_NUM);
+    }
+
+    Status InferShapeImpl(const SVector<TensorDesc> &, SVector<TensorDesc> &) const override { return NO_ERROR; }
+
+    Status SetupCheckImpl(const SVector<Tensor> &inTensors, const SVector<Tensor> &) const override
+    {
+        SVector<TensorDesc> descs;
+        for (size_t i = 0; i < inTensors.size(); ++i) {
+            descs.push_back(inTensors.at(i).desc);
+        }
+        return DimCheck(descs, ERROR_INVALID_TENSOR_DIM); // the reference's Setup reports the dim count this way
+    }
+
+    Status PlanImpl(const VariantPack &, uint64_t &workspaceSize) override
+    {
+        workspaceSize = 0;
+        return NO_ERROR;
+    }
+
+    Status LaunchImpl(const VariantPack &vp, uint8_t *, uint64_t, aclrtStream stream) override
+    {
+        const Tensor &kv = vp.inTensors.at(0), &layer = vp.inTensors.at(1), &past = vp.inTensors.at(2);
+        const Tensor &off = vp.inTensors.at(3), &len = vp.inTensors.at(4);
+        if (kv.deviceData == nullptr || layer.deviceData == nullptr || past.deviceData == nullptr ||
+            off.deviceData == nullptr || len.deviceData == nullptr) {
+            return ERROR_INVALID_PARAM;
+        }
+        const Dims &k = kv.desc.shape, &p = past.desc.shape;
+        const int64_t tokens = k.dimNum == 2 ? k.dims[0] : k.dims[0] * k.dims[1];
+        const int rc = atb_b200_kv_cache(kv.deviceData, static_cast<const int32_t *>(layer.deviceData), past.deviceData,
+                                         static_cast<const int32_t *>(off.deviceData),
+                                         static_cast<const int32_t *>(len.deviceData), tokens,
+                                         static_cast<int32_t>(p.dims[0]), static_cast<int32_t>(p.dims[1]),
+                                         static_cast<int32_t>(p.dims[2]),
+                                         p.dims[3] * static_cast<int64_t>(ElemSize(past.desc.dtype)), stream);
+        return rc == 0 ? NO_ERROR : (rc == ERROR_INVALID_PARAM ? ERROR_INVALID_PARAM : ERROR_RT_FAIL);
+    }
+
+private:
+    infer::KvCacheParam param_;
+    std::vector<DtypeComb> combs_;
+};
+
 } // namespace
+
+template <> Status CreateOperation(const infer::KvCacheParam &opParam, Operation **operation)
+{
+    if (operation == nullptr) {
+        return ERROR_INVALID_PARAM;
+    }
+    if (!RsvIsZero(opParam.rsv, sizeof(opParam.rsv))) {
+        ATB_B200_LOG(ERROR, "KvCacheParam.rsv must be zero");
+        return ERROR_INVALID_PARAM;
+    }
+    *operation = new (std::nothrow) KvCacheOperation(opParam);
+    return *operation == nullptr ? ERROR_OUT_OF_HOST_MEMORY : NO_ERROR;
+}
 
 template <> Status CreateOperation(const infer::NormRopeReshapeParam &opParam, Operation **operation)
 {

@@ -36,6 +36,11 @@ __global__ void __launch_bounds__(kThreads) rac_strided_kernel(const RacStridedA
     rac_strided_body(a, blockIdx.x, threadIdx.x, blockDim.x);
 }
 
+__global__ void __launch_bounds__(kThreads) kv_cache_kernel(const KvCacheArgs a)
+{
+    kv_cache_body(a, blockIdx.x, threadIdx.x, blockDim.x);
+}
+
 __global__ void prefix_lens_kernel(const int32_t *lens, int32_t *cu, int32_t batch)
 {
     if (blockIdx.x == 0 && threadIdx.x == 0) {
@@ -186,6 +191,40 @@ int atb_b200_reshape_and_cache_strided(const void *key, const void *value, void 
         return kErrInvalidParam;
     }
     rac_strided_kernel<<<(unsigned)ctas, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    return cudaGetLastError() == cudaSuccess ? 0 : kErrRtFail;
+}
+
+int atb_b200_kv_cache(const void *new_kv, const int32_t *layer_id, void *past, const int32_t *token_offset,
+                      const int32_t *seq_len, int64_t num_tokens, int32_t layers, int32_t batch, int32_t max_seqlen,
+                      int64_t row_bytes, void *stream)
+{
+    if (new_kv == nullptr || layer_id == nullptr || past == nullptr || token_offset == nullptr || seq_len == nullptr ||
+        num_tokens < 0 || layers <= 0 || batch < 0 || max_seqlen <= 0 || row_bytes <= 0) {
+        return kErrInvalidParam;
+    }
+    if (batch == 0 || num_tokens == 0) {
+        return 0;
+    }
+    KvCacheArgs a{};
+    a.new_kv = static_cast<const uint8_t *>(new_kv);
+    a.past = static_cast<uint8_t *>(past);
+    a.layer_id = layer_id;
+    a.token_offset = token_offset;
+    a.seq_len = seq_len;
+    a.layers = layers;
+    a.batch = batch;
+    a.max_seqlen = max_seqlen;
+    a.row_bytes = row_bytes;
+    a.n_tokens = num_tokens;
+    // the longest run a sequence can have: every row of new_kv, or a full cache row
+    const int64_t longest = (num_tokens < max_seqlen ? num_tokens : (int64_t)max_seqlen) * row_bytes;
+    a.chunks = chunks_for(longest);
+    a.vec16 = aligned16(new_kv) && aligned16(past) && row_bytes % 16 == 0;
+    const int64_t ctas = (int64_t)batch * a.chunks;
+    if (ctas > 0x7fffffff) {
+        return kErrInvalidParam;
+    }
+    kv_cache_kernel<<<(unsigned)ctas, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
     return cudaGetLastError() == cudaSuccess ? 0 : kErrRtFail;
 }
 

@@ -195,6 +195,48 @@ ATB_B200_HD void rac_strided_body(const RacStridedArgs &a, int64_t cta, int tid,
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// KvCache (contiguous, per-layer cache [layers, batch, max_seqlen, hidden]): sequence b's seq_len[b] new rows,
+// which follow those of the sequences before it in new_kv [tokens, hidden], go to positions
+// [token_offset[b] - seq_len[b], token_offset[b]) of past[layer_id[0]][b] - one contiguous run on both sides.
+// One CTA per (sequence, chunk).  A layer outside the cache, a negative length, a run that would start before
+// position 0 or end past max_seqlen, and rows past the end of new_kv are skipped, never dereferenced.
+struct KvCacheArgs {
+    const uint8_t *new_kv;
+    uint8_t *past;
+    const int32_t *layer_id, *token_offset, *seq_len;
+    int32_t layers, batch, max_seqlen;
+    int64_t row_bytes;   // hidden size x element size
+    int64_t n_tokens;    // rows of new_kv
+    int32_t chunks;
+    bool vec16;
+};
+
+ATB_B200_HD void kv_cache_body(const KvCacheArgs &a, int64_t cta, int tid, int nthreads)
+{
+    const int32_t b = (int32_t)(cta / a.chunks), c = (int32_t)(cta % a.chunks);
+    if (b >= a.batch) {
+        return;
+    }
+    const int64_t layer = a.layer_id[0], n = a.seq_len[b], off = a.token_offset[b];
+    if (layer < 0 || layer >= a.layers || n <= 0 || off < n || off > a.max_seqlen) {
+        return;
+    }
+    int64_t prefix = 0; // rows of the sequences before b (batch is small)
+    for (int32_t i = 0; i < b; ++i) {
+        prefix += a.seq_len[i] > 0 ? a.seq_len[i] : 0;
+    }
+    if (prefix + n > a.n_tokens) {
+        return;
+    }
+    int64_t begin, end;
+    chunk_range(n * a.row_bytes, a.chunks, c, &begin, &end);
+    if (begin < end) {
+        copy_range(a.past + ((layer * a.batch + b) * a.max_seqlen + off - n) * a.row_bytes, a.new_kv + prefix * a.row_bytes,
+                   begin, end, tid, nthreads, a.vec16);
+    }
+}
+
 // Running totals of the sequence lengths (one thread; batch is small): cu[0] = 0, cu[i+1] = cu[i] + lens[i].
 ATB_B200_HD void prefix_lens_body(const int32_t *lens, int32_t *cu, int32_t batch)
 {

@@ -76,6 +76,13 @@ struct ReshapeAndCacheWithStrideParam {
     uint8_t rsv[16] = {0};
 };
 
+// KvCache (include/atb/infer_op_params.h:423-431 of the reference): appends new K or V rows to a contiguous per-layer
+// cache.  Inputs newKv [tokens, hidden] (or [batch, seq, heads, headSize]), layerId [1], past [layers, batch, maxSeqLen,
+// hidden], tokenOffset [batch], seqLen [batch] (all int32 device tensors); no outputs, past is updated in place.
+struct KvCacheParam {
+    uint8_t rsv[8] = {0};
+};
+
 // MultiLatentAttention (include/atb/infer_op_params.h:2899-2950 of the reference): attention over the MLA latent
 // cache given as separate latent (512) and rope (64) tensors.  Decode form built here: inputs qNope [tokens, heads,
 // 512], qRope [tokens, heads, 64], ctKV [blocks, 128, 1, 512], kRope [blocks, 128, 1, 64], blockTables, contextLens
@@ -144,6 +151,7 @@ struct PagedCacheLoadParam {
 };
 
 static_assert(sizeof(ReshapeAndCacheWithStrideParam) == 24, "ABI: ReshapeAndCacheWithStrideParam is 24 bytes");
+static_assert(sizeof(KvCacheParam) == 8, "ABI: KvCacheParam is 8 bytes");
 static_assert(sizeof(MultiLatentAttentionParam) == 64, "ABI: MultiLatentAttentionParam is 64 bytes");
 static_assert(sizeof(NormRopeReshapeParam) == 28, "ABI: NormRopeReshapeParam is 28 bytes");
 static_assert(sizeof(BlockCopyParam) == 16, "ABI: BlockCopyParam is 16 bytes");

@@ -279,6 +279,18 @@ int atb_b200_operation_create_block_copy(const void *param, uint64_t param_bytes
 int atb_b200_operation_create_paged_cache_load(const void *param, uint64_t param_bytes, void **operation);
 /* atb::CreateOperation<infer::ReshapeAndCacheWithStrideParam> (24-byte param) */
 int atb_b200_operation_create_reshape_and_cache_with_stride(const void *param, uint64_t param_bytes, void **operation);
+/*
+ * KvCache (src/kernels/mixkernels/kvcache of the reference; golden tests/apitest/kernelstest/mix/test_kvcache.py:65-78):
+ * the contiguous per-layer cache past [layers, batch, max_seqlen, hidden] receives, for every sequence b, its seq_len[b]
+ * rows of new_kv [num_tokens, hidden] (sequences back to back) at positions [token_offset[b] - seq_len[b],
+ * token_offset[b]) of layer layer_id[0].  layer_id, token_offset, seq_len are device int32 arrays; row_bytes = hidden x
+ * element size.  Runs that do not fit the cache or new_kv are skipped.
+ */
+int atb_b200_kv_cache(const void *new_kv, const int32_t *layer_id, void *past, const int32_t *token_offset,
+                      const int32_t *seq_len, int64_t num_tokens, int32_t layers, int32_t batch, int32_t max_seqlen,
+                      int64_t row_bytes, void *stream);
+/* atb::CreateOperation<infer::KvCacheParam> (8-byte param; tests/unittest/ops/test_op_param_size.cpp:36) */
+int atb_b200_operation_create_kv_cache(const void *param, uint64_t param_bytes, void **operation);
 /* atb::CreateOperation<infer::MultiLatentAttentionParam> (64-byte param; tests/unittest/ops/test_op_param_size.cpp:68) */
 int atb_b200_operation_create_multi_latent_attention(const void *param, uint64_t param_bytes, void **operation);
 /* atb::CreateOperation<infer::NormRopeReshapeParam> (28-byte param) */

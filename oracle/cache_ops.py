@@ -112,3 +112,16 @@ def norm_rope_reshape(x, gamma, key_rope, cos, sin, slot_mapping, key_cache, eps
             continue
         key_cache[slot // block_size, slot % block_size, 0] = rows[i]
     return key_cache
+
+
+def kv_cache(new_kv, layer_id, past, token_offset, seq_len):
+    """KvCache on numpy arrays, in place on `past` [layers, batch, max_seqlen, hidden]: sequence i's seq_len[i] rows of
+    new_kv [tokens, hidden] (sequences back to back) go to positions [token_offset[i] - seq_len[i], token_offset[i]) of
+    past[layer_id].  Follows golden_calc of tests/apitest/kernelstest/mix/test_kvcache.py:65-78 of the reference."""
+    prefix = 0
+    for i in range(past.shape[1]):
+        n, off = int(seq_len[i]), int(token_offset[i])
+        for j in range(n):
+            past[int(layer_id), i, off - n + j, :] = new_kv[prefix + j, :]
+        prefix += n
+    return past

@@ -113,6 +113,10 @@ static int RunCpu()
     CHECK(atb::CreateOperation(lp, &op) == atb::NO_ERROR);
     CHECK(op->GetName() == "PagedCacheLoadOperation" && op->GetInputNum() == 7 && op->GetOutputNum() == 2);
     CHECK(atb::DestroyOperation(op) == atb::NO_ERROR);
+    atb::infer::KvCacheParam kp;
+    CHECK(atb::CreateOperation(kp, &op) == atb::NO_ERROR);
+    CHECK(op->GetName() == "KvCacheOperation" && op->GetInputNum() == 5 && op->GetOutputNum() == 0);
+    CHECK(atb::DestroyOperation(op) == atb::NO_ERROR);
     // MLA decode attention over the split latent / rope cache
     atb::infer::MultiLatentAttentionParam mp;
     mp.headNum = 128;

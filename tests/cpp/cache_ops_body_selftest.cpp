@@ -280,6 +280,55 @@ void test_rac_strided(int case_id)
     expect(std::memcmp(vc.p, vref.data(), vc.n) == 0, "rac_strided value cache", case_id);
 }
 
+void test_kv_cache(int case_id)
+{
+    const int layers = rnd_in(1, 3), batch = rnd_in(1, 6), max_seqlen = rnd_in(1, 20);
+    const bool odd = rnd() % 4 == 0;
+    const int64_t row = odd ? rnd_in(1, 70) : 16 * rnd_in(1, 6);
+    std::vector<int32_t> len(batch), off(batch);
+    int64_t tokens = 0;
+    for (int b = 0; b < batch; ++b) {
+        const uint32_t r = rnd() % 10;
+        len[b] = r == 0 ? -1 : (r == 1 ? 0 : rnd_in(1, max_seqlen));
+        off[b] = r == 2 ? len[b] - 1 : (r == 3 ? max_seqlen + 1 : rnd_in(len[b] > 0 ? len[b] : 0, max_seqlen));
+        tokens += len[b] > 0 ? len[b] : 0;
+    }
+    const bool short_input = rnd() % 6 == 0 && tokens > 1; // new_kv holds fewer rows than the lengths add up to
+    const int64_t have = short_input ? tokens - 1 : tokens;
+    int32_t layer = (rnd() % 8 == 0) ? layers : rnd_in(0, layers - 1); // sometimes past the cache
+    Buf kv((size_t)(have > 0 ? have : 1) * row, !odd), past((size_t)layers * batch * max_seqlen * row, !odd);
+    std::vector<uint8_t> ref(past.p, past.p + past.n);
+    int64_t prefix = 0;
+    for (int b = 0; b < batch; ++b) {
+        const int64_t n = len[b];
+        if (layer < layers && n > 0 && off[b] >= n && off[b] <= max_seqlen && prefix + n <= have) {
+            std::memcpy(&ref[(size_t)(((int64_t)layer * batch + b) * max_seqlen + off[b] - n) * row], kv.p + prefix * row,
+                        (size_t)(n * row));
+        }
+        prefix += n > 0 ? n : 0;
+    }
+    KvCacheArgs a{};
+    a.new_kv = kv.p;
+    a.past = past.p;
+    a.layer_id = &layer;
+    a.token_offset = off.data();
+    a.seq_len = len.data();
+    a.layers = layers;
+    a.batch = batch;
+    a.max_seqlen = max_seqlen;
+    a.row_bytes = row;
+    a.n_tokens = have;
+    a.chunks = rnd_in(1, 4);
+    a.vec16 = !odd;
+    const int threads = rnd_in(1, 6);
+    for (int64_t cta = 0; cta < (int64_t)batch * a.chunks; ++cta) {
+        for (int tid = 0; tid < threads; ++tid) {
+            kv_cache_body(a, cta, tid, threads);
+        }
+    }
+    expect(std::memcmp(past.p, ref.data(), past.n) == 0, "kv_cache past", case_id);
+}
+
 } // namespace
 
 int main(int argc, char **argv)
@@ -289,7 +338,8 @@ int main(int argc, char **argv)
         test_block_copy(i);
         test_paged_cache_load(i);
         test_rac_strided(i);
+        test_kv_cache(i);
     }
-    std::printf("%d cases, %d failures\n", 3 * n, failures);
+    std::printf("%d cases, %d failures\n", 4 * n, failures);
     return failures == 0 ? 0 : 1;
 }

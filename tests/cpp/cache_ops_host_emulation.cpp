@@ -113,4 +113,30 @@ int emu_rac_strided(const uint8_t *key, const uint8_t *value, uint8_t *key_cache
     return a.vec16 ? 16 : 1;
 }
 
+int emu_kv_cache(const uint8_t *new_kv, const int32_t *layer_id, uint8_t *past, const int32_t *token_offset,
+                 const int32_t *seq_len, int64_t n_tokens, int32_t layers, int32_t batch, int32_t max_seqlen,
+                 int64_t row_bytes, int32_t chunks, int32_t threads)
+{
+    KvCacheArgs a{};
+    a.new_kv = new_kv;
+    a.past = past;
+    a.layer_id = layer_id;
+    a.token_offset = token_offset;
+    a.seq_len = seq_len;
+    a.layers = layers;
+    a.batch = batch;
+    a.max_seqlen = max_seqlen;
+    a.row_bytes = row_bytes;
+    a.n_tokens = n_tokens;
+    a.chunks = chunks > 0 ? chunks
+                          : (int32_t)chunks_for((n_tokens < max_seqlen ? n_tokens : (int64_t)max_seqlen) * row_bytes);
+    a.vec16 = aligned16(new_kv) && aligned16(past) && row_bytes % 16 == 0;
+    for (int64_t cta = 0; cta < (int64_t)batch * a.chunks; ++cta) {
+        for (int tid = 0; tid < threads; ++tid) {
+            kv_cache_body(a, cta, tid, threads);
+        }
+    }
+    return a.vec16 ? 16 : 1;
+}
+
 } // extern "C"

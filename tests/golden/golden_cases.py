@@ -131,6 +131,36 @@ def pcl_inputs(spec):
             "lens": lens.astype(np.int32), "seq_starts": starts}
 
 
+GOLDEN_KVCACHE_CASES = [
+    dict(name="fp16_prefill", layers=3, layer_id=1, batch=4, max_seqlen=24, hidden=32, dtype="fp16", decode=False, seed=501),
+    dict(name="bf16_decode", layers=2, layer_id=0, batch=5, max_seqlen=16, hidden=48, dtype="bf16", decode=True, seed=502),
+    dict(name="int8_mixed", layers=2, layer_id=1, batch=3, max_seqlen=20, hidden=64, dtype="int8", decode=False, seed=503),
+]
+
+
+def kvcache_inputs(spec):
+    """Seeded KvCache inputs in the manner of the reference test (tests/apitest/kernelstest/mix/test_kvcache.py:
+    95-108): prefill has token_offset = seq_len, decode one new row per sequence at a random position.  `past`
+    starts as zeros, as the reference golden assumes."""
+    rng = np.random.default_rng(spec["seed"])
+    b, s = spec["batch"], spec["max_seqlen"]
+    if spec["decode"]:
+        seq_len = np.ones(b, dtype=np.int32)
+        token_offset = rng.integers(1, s + 1, size=b).astype(np.int32)
+    else:
+        seq_len = rng.integers(1, s // 2, size=b).astype(np.int32)
+        token_offset = seq_len.copy()
+        token_offset[-1] += 3                      # one sequence appends behind three cached tokens
+    n = int(seq_len.sum())
+    if spec["dtype"] == "int8":
+        new_kv = rng.integers(-127, 128, size=(n, spec["hidden"]), dtype=np.int8)
+    else:
+        new_kv = _wl.encode(rng.uniform(-5, 5, size=(n, spec["hidden"])).astype(np.float32), spec["dtype"])
+    past = np.zeros((spec["layers"], b, s, spec["hidden"]), dtype=new_kv.dtype)
+    return {"new_kv": new_kv, "layer_id": np.array([spec["layer_id"]], dtype=np.int32), "past": past,
+            "token_offset": token_offset, "seq_len": seq_len}
+
+
 # ------------------------------------------------------------------ PagedAttention with a mask / logN scale
 
 GOLDEN_PA_FEATURE_CASES = [

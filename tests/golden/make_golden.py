@@ -32,8 +32,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, HERE)
 
-from golden_cases import (GOLDEN_BLOCKCOPY_CASES, GOLDEN_PA_CASES, GOLDEN_PA_FEATURE_CASES, GOLDEN_PA_SPEC_CASES, GOLDEN_PCL_CASES,  # noqa: E402
-                          GOLDEN_NRR_CASES, GOLDEN_RAC_CASES, blockcopy_inputs, load_workloads, nrr_inputs, pa_mask, spec_inputs,
+from golden_cases import (GOLDEN_BLOCKCOPY_CASES, GOLDEN_PA_CASES, GOLDEN_KVCACHE_CASES, GOLDEN_PA_FEATURE_CASES, GOLDEN_PA_SPEC_CASES, GOLDEN_PCL_CASES,  # noqa: E402
+                          GOLDEN_NRR_CASES, GOLDEN_RAC_CASES, blockcopy_inputs, load_workloads, nrr_inputs, kvcache_inputs, pa_mask, spec_inputs,
                           pcl_inputs, rac_inputs)
 
 wl = load_workloads()
@@ -233,6 +233,24 @@ def run_blockcopy_case(mod, spec):
     return {"k_cache": kexp, "v_cache": vexp, "input_sha256": np.frombuffer(digest(inp).encode(), dtype=np.uint8)}
 
 
+def run_kvcache_case(mod, spec):
+    """KvCache through golden_calc of the reference's kernel test (values as that test holds them: fp16 / int8 numpy;
+    bf16 as float32 numpy, exact)."""
+    inp = kvcache_inputs(spec)
+    t = mod.TestKvcache()
+    t.format_nd, t.format_nz = 2, 29                   # ACL_FORMAT_ND / FRACTAL_NZ, attributes of the stubbed base class
+    t.case_param_gen({"format": t.format_nd, "layer": spec["layers"], "layer_id": spec["layer_id"], "batch": spec["batch"],
+                      "max_seqlen": spec["max_seqlen"], "hidden_size": spec["hidden"]})
+    t.newkv = _as_ref_values(inp["new_kv"], spec["dtype"])
+    t.token_offset, t.seqlen = inp["token_offset"], inp["seq_len"]
+    (out,) = t.golden_calc(None)
+    out = out.numpy()
+    if spec["dtype"] == "bf16":
+        out = wl.f32_to_bf16_bits(out)
+    return {"past": out.astype(inp["new_kv"].dtype) if spec["dtype"] != "bf16" else out,
+            "input_sha256": np.frombuffer(digest(inp).encode(), dtype=np.uint8)}
+
+
 def run_pcl_case(mod, spec):
     inp = pcl_inputs(spec)
     t = mod.TestPagedCacheLoad()
@@ -267,12 +285,16 @@ def main():
     pcl = _load(os.path.join(kt, "mix/test_paged_cache_load_nd.py"), "ref_pcl")
     nrr16 = _load(os.path.join(kt, "mix/test_rms_norm_and_rope_and_reshape_and_cache.py"), "ref_nrr_fp16")
     nrrbf = _load(os.path.join(kt, "mix/test_rms_norm_and_rope_and_reshape_and_cache_bf16.py"), "ref_nrr_bf16")
+    kvcache = _load(os.path.join(kt, "mix/test_kvcache.py"), "ref_kvcache")
     lookahead = _load(os.path.join(kt, "mix/test_paged_attention_lookahead.py"), "ref_pa_lookahead")
     os.chdir(cwd)
     for spec in GOLDEN_PA_SPEC_CASES:
         res = run_pa_spec_case(lookahead, spec)
         np.savez_compressed(os.path.join(HERE, f"pa_{spec['case'].name}.npz"), **res)
         print("wrote", spec["case"].name, res["out"].shape)
+    for spec in GOLDEN_KVCACHE_CASES:
+        np.savez_compressed(os.path.join(HERE, f"kvcache_{spec['name']}.npz"), **run_kvcache_case(kvcache, spec))
+        print("wrote kvcache", spec["name"])
     if "--spec-only" in sys.argv:
         return
     for spec in GOLDEN_NRR_CASES:

@@ -10,7 +10,8 @@ import numpy as np
 import pytest
 
 import oracle
-from golden_cases import (GOLDEN_BLOCKCOPY_CASES, GOLDEN_PCL_CASES, HERE as GOLDEN_DIR, blockcopy_inputs, pcl_inputs)
+from golden_cases import (GOLDEN_BLOCKCOPY_CASES, GOLDEN_KVCACHE_CASES, GOLDEN_PCL_CASES, HERE as GOLDEN_DIR, blockcopy_inputs,
+                          kvcache_inputs, pcl_inputs)
 from helpers import capi, pkg
 
 _emu = None
@@ -24,6 +25,7 @@ def emu():
         L.emu_block_copy.argtypes = [vp, vp, vp, vp, vp, i32, i32, i64, i64, i64, i32, i32]
         L.emu_paged_cache_load.argtypes = [vp] * 7 + [i32, i32, i32, i64, i64, i64, i64, i32, vp, i32, i32]
         L.emu_rac_strided.argtypes = [vp] * 5 + [i32, i64, i64, i64, i64, i64, i32, i32]
+        L.emu_kv_cache.argtypes = [vp] * 5 + [i64, i32, i32, i32, i64, i32, i32]
         _emu = L
     return _emu
 
@@ -333,3 +335,80 @@ def test_norm_rope_reshape_operation_checks():
         args = list(ok)
         args[pos] = val
         assert L.atb_b200_norm_rope_reshape(*args) == capi.ERROR_INVALID_PARAM, pos
+
+
+# ------------------------------------------------------------------ KvCache
+
+def _run_emu_kv_cache(inp, past, chunks, threads):
+    return emu().emu_kv_cache(_p(inp["new_kv"]), _p(inp["layer_id"]), _p(past), _p(inp["token_offset"]), _p(inp["seq_len"]),
+                              inp["new_kv"].shape[0], past.shape[0], past.shape[1], past.shape[2], past[0, 0, 0].nbytes,
+                              chunks, threads)
+
+
+@pytest.mark.parametrize("chunks,threads", [(0, 4), (1, 1), (3, 5)])
+@pytest.mark.parametrize("spec", GOLDEN_KVCACHE_CASES, ids=lambda s: s["name"])
+def test_kv_cache_oracle_and_body_match_reference_golden(spec, chunks, threads):
+    fx = np.load(os.path.join(GOLDEN_DIR, f"kvcache_{spec['name']}.npz"))
+    inp = kvcache_inputs(spec)
+    want = oracle.cache_ops.kv_cache(inp["new_kv"], inp["layer_id"][0], inp["past"].copy(), inp["token_offset"], inp["seq_len"])
+    assert np.array_equal(_bits(want), _bits(fx["past"]))
+    assert np.any(_bits(want) != 0)
+    past = inp["past"].copy()
+    _run_emu_kv_cache(inp, past, chunks, threads)
+    assert np.array_equal(_bits(past), _bits(fx["past"]))
+
+
+def test_kv_cache_body_keeps_other_rows_and_skips_runs_that_do_not_fit():
+    rng = np.random.default_rng(9)
+    spec = GOLDEN_KVCACHE_CASES[0]
+    inp = kvcache_inputs(spec)
+    before = rng.integers(1, 2 ** 15, size=inp["past"].shape).astype(np.uint16).view(np.float16)
+    want = oracle.cache_ops.kv_cache(inp["new_kv"], inp["layer_id"][0], before.copy(), inp["token_offset"], inp["seq_len"])
+    past = before.copy()
+    _run_emu_kv_cache(inp, past, 0, 7)
+    assert np.array_equal(_bits(past), _bits(want))                       # everything not written is untouched
+    for field, b, value in (("token_offset", 1, 0), ("token_offset", 2, spec["max_seqlen"] + 1), ("seq_len", 0, -3),
+                            ("layer_id", 0, spec["layers"]), ("layer_id", 0, -1)):
+        hostile = {k: v.copy() for k, v in inp.items()}
+        hostile[field][b] = value
+        past = before.copy()
+        _run_emu_kv_cache(hostile, past, 2, 3)                            # must not write outside `past` (ASan build checks too)
+        if field == "layer_id":
+            assert np.array_equal(_bits(past), _bits(before))
+        else:
+            assert np.array_equal(_bits(past[:, b]), _bits(before[:, b]))  # the offending sequence is skipped
+
+
+def test_kv_cache_operation_checks():
+    assert ctypes.sizeof(capi.KvCacheParam) == 8                          # tests/unittest/ops/test_op_param_size.cpp:36
+    op = capi.Operation(capi.KvCacheParam())
+    assert (op.name, op.input_num, op.output_num) == ("KvCacheOperation", 5, 0)
+    bad = capi.KvCacheParam()
+    bad.rsv[7] = 1
+    _expect(capi.ERROR_INVALID_PARAM, capi.Operation, bad)
+    ctx = capi.Context()
+    f16, i32, i8 = capi.ACL_FLOAT16, capi.ACL_INT32, capi.ACL_INT8
+    ins = [_T(f16, (37, 1024)), _T(i32, (1,)), _T(f16, (28, 16, 384, 1024)), _T(i32, (16,)), _T(i32, (16,))]
+    assert op.infer_shape(ins, 0) == []
+    assert op.setup(ins, [], ctx) == 0
+    four_d = list(ins)
+    four_d[0] = _T(f16, (16, 2, 8, 128))                                   # [batch, seq, heads, headSize]
+    assert op.setup(four_d, [], ctx) == 0
+
+    def swapped(i, t):
+        w = list(ins)
+        w[i] = t
+        return w
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, swapped(0, _T(f16, (37, 512))), [], ctx)          # hidden sizes differ
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, swapped(3, _T(i32, (15,))), [], ctx)              # batches differ
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, swapped(0, _T(f16, (37, 8, 128))), [], ctx)       # 3-D newKv
+    _expect(capi.ERROR_INVALID_TENSOR_DIM_NUM, op.infer_shape, swapped(0, _T(f16, (37, 8, 128))), 0)
+    _expect(capi.ERROR_INVALID_TENSOR_INI_MATCH, op.setup, swapped(0, _T(capi.ACL_BF16, (37, 1024))), [], ctx)
+    odd = [_T(f16, (37, 1000)), ins[1], _T(f16, (28, 16, 384, 1000)), ins[3], ins[4]]
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, odd, [], ctx)                                     # hidden % 16
+    int8 = [_T(i8, (37, 48)), ins[1], _T(i8, (28, 16, 384, 48)), ins[3], ins[4]]
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, int8, [], ctx)                                    # int8: hidden % 32
+    lib = capi.lib()
+    assert lib.atb_b200_kv_cache(None, 0x1000, 0x1000, 0x1000, 0x1000, 4, 1, 1, 8, 64, None) == capi.ERROR_INVALID_PARAM
+    assert lib.atb_b200_kv_cache(0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 4, 0, 1, 8, 64, None) == capi.ERROR_INVALID_PARAM
+    assert lib.atb_b200_kv_cache(0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0, 1, 1, 8, 64, None) == 0    # nothing to copy

@@ -520,3 +520,46 @@ def test_parallel_decoding_long_sequences_bf16():
     ref = oracle.paged_attention_spec(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], d["q_lens"], d["context_lens"],
                                       case.qk_scale, "bf16", wl.to_f32(d["mask"], "bf16"), mask_rows_are_tokens=False)
     assert max_abs_err(got, ref, "bf16") <= tol_for(case)
+
+
+# ------------------------------------------------------------------ KvCache (contiguous per-layer cache)
+
+from golden_cases import GOLDEN_KVCACHE_CASES, kvcache_inputs  # noqa: E402
+
+
+@pytest.mark.parametrize("spec", GOLDEN_KVCACHE_CASES, ids=lambda s: s["name"])
+def test_kv_cache_matches_reference_golden(spec):
+    fx = np.load(os.path.join(GOLDEN_DIR, f"kvcache_{spec['name']}.npz"))
+    inp = kvcache_inputs(spec)
+    dt = spec["dtype"]
+    T = capi.atb_tensor
+    dev = {k: (to_dev(v, dt) if k in ("new_kv", "past") else torch.from_numpy(v).cuda()) for k, v in inp.items()}
+    ins = [T(dev["new_kv"]), T(dev["layer_id"]), T(dev["past"]), T(dev["token_offset"]), T(dev["seq_len"])]
+    op = capi.Operation(capi.KvCacheParam())
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    ctx = capi.Context(stream.cuda_stream)
+    assert op.setup(ins, [], ctx) == 0
+    op.execute(ins, [], None, 0, ctx)
+    torch.cuda.synchronize()
+    got = wl.torch_to_host(dev["past"], dt)
+    bits = lambda a: a.view(np.uint16) if a.dtype == np.float16 else a
+    assert np.array_equal(bits(got), bits(fx["past"]))
+
+
+def test_kv_cache_large_rows_keep_the_rest_of_the_cache():
+    rng = np.random.default_rng(17)
+    layers, batch, max_seqlen, hidden = 3, 9, 300, 1024                  # 2 KB rows, runs of up to 600 KB (many chunks)
+    seq_len = rng.integers(0, 290, size=batch).astype(np.int32)
+    seq_len[3] = 0
+    token_offset = (seq_len + rng.integers(0, 10, size=batch)).astype(np.int32)
+    new_kv = rng.integers(0, 2 ** 15, size=(int(seq_len.sum()), hidden)).astype(np.uint16)
+    before = rng.integers(0, 2 ** 15, size=(layers, batch, max_seqlen, hidden)).astype(np.uint16)
+    want = oracle.cache_ops.kv_cache(new_kv, 2, before.copy(), token_offset, seq_len)
+    past = torch.from_numpy(before.view(np.int16)).cuda().view(torch.bfloat16)
+    kv = torch.from_numpy(new_kv.view(np.int16)).cuda().view(torch.bfloat16)
+    capi.kv_cache(kv, torch.tensor([2], dtype=torch.int32, device="cuda"), past, torch.from_numpy(token_offset).cuda(),
+                  torch.from_numpy(seq_len).cuda())
+    torch.cuda.synchronize()
+    got = past.view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got, want)
