@@ -45,7 +45,7 @@ class PaTensors(ctypes.Structure):
                 ("k_offset", ctypes.c_void_p), ("v_offset", ctypes.c_void_p), ("out", ctypes.c_void_p),
                 ("q_rope", ctypes.c_void_p), ("k_rope_cache", ctypes.c_void_p),
                 ("mask", ctypes.c_void_p), ("mask_batch_stride", ctypes.c_int64), ("mask_head_stride", ctypes.c_int64),
-                ("mask_tokens", ctypes.c_int64), ("logn", ctypes.c_void_p)]
+                ("mask_tokens", ctypes.c_int64), ("logn", ctypes.c_void_p), ("lse_out", ctypes.c_void_p)]
 
 
 SCORE_MASK, SCORE_LOGN, SCORE_ROWS = 1, 2, 4
@@ -343,10 +343,10 @@ def torch_stream_ptr():
 
 
 def pa_tensors(q, k_cache, v_cache, block_tables, out, k_descale=None, v_descale=None, k_offset=None, v_offset=None,
-               q_rope=None, k_rope_cache=None, mask=None, mask_strides=(0, 0), mask_tokens=0, logn=None):
+               q_rope=None, k_rope_cache=None, mask=None, mask_strides=(0, 0), mask_tokens=0, logn=None, lse_out=None):
     """`mask_strides` = (batch, head) element strides of the additive mask, `mask_tokens` its last dimension."""
     t = PaTensors()
-    t.mask, t.logn = _ptr(mask), _ptr(logn)
+    t.mask, t.logn, t.lse_out = _ptr(mask), _ptr(logn), _ptr(lse_out)
     t.mask_batch_stride, t.mask_head_stride, t.mask_tokens = int(mask_strides[0]), int(mask_strides[1]), int(mask_tokens)
     t.q_rope, t.k_rope_cache = _ptr(q_rope), _ptr(k_rope_cache)
     t.q, t.k_cache = _ptr(q), _ptr(k_cache)

@@ -5,8 +5,9 @@
 // (CreateOperation :58-91, ParamCheck :93-146, ParamRangeCheck :148-170, GetInputNum/GetOutputNum :240-270,
 //  InferShapeImpl :272-286, QKVDimCheck :337-379, DimCheck :579-640) and its host-tensor handling
 // (multi_latent_attention/param.cpp: contextLens is host data).  Built here: calcType UNDEFINED (one query token per
-// sequence), cacheMode KROPE_CTKV, no mask; parallel decoding, ring attention (LSE output), prefill and the NZ / int8
-// caches are rejected.  The device path is the tcgen05 MLA kernel with a second tensor map for the rope rows.
+// sequence) and CALC_TYPE_RING (the same with the log-sum-exp as a second output), cacheMode KROPE_CTKV, no mask;
+// parallel decoding, prefill and the NZ / int8 caches are rejected.  The device path is the tcgen05 MLA kernel with a
+// second tensor map for the rope rows.
 #include <cmath>
 #include <cstdlib>
 #include <new>
@@ -23,8 +24,12 @@ public:
     explicit MultiLatentAttentionOperation(const Param &p) : OperationBase("MultiLatentAttentionOperation"), param_(p)
     {
         for (aclDataType h : {ACL_FLOAT16, ACL_BF16}) {
-            // qNope, qRope, ctKV, kRope, blockTables, contextLens -> attnOut
-            combs_.push_back({h, h, h, h, ACL_INT32, ACL_INT32, h});
+            // qNope, qRope, ctKV, kRope, blockTables, contextLens -> attnOut [, lse]
+            if (Ring()) {
+                combs_.push_back({h, h, h, h, ACL_INT32, ACL_INT32, h, h});
+            } else {
+                combs_.push_back({h, h, h, h, ACL_INT32, ACL_INT32, h});
+            }
         }
     }
     ~MultiLatentAttentionOperation() override
@@ -34,9 +39,12 @@ public:
         }
     }
     uint32_t GetInputNum() const override { return 6; }
-    uint32_t GetOutputNum() const override { return 1; }
+    uint32_t GetOutputNum() const override { return Ring() ? 2 : 1; }
 
 protected:
+    // CALC_TYPE_RING: the log-sum-exp of every (token, head) is a second output [tokens, heads, 1]
+    bool Ring() const { return param_.calcType == Param::CALC_TYPE_RING; }
+
     const std::vector<DtypeComb> &DtypeCombs() const override { return combs_; }
 
     Status InferShapeCheckImpl(const SVector<TensorDesc> &in) const override
@@ -95,6 +103,10 @@ protected:
     {
         out.at(0) = in.at(0);
         out.at(0).dtype = in.at(1).dtype;
+        if (Ring()) {
+            out.at(1) = out.at(0);
+            out.at(1).shape.dims[2] = 1;
+        }
         return NO_ERROR;
     }
 
@@ -112,6 +124,13 @@ protected:
         if (o.dimNum != 3 || o.dims[0] != q.dims[0] || o.dims[1] != q.dims[1] || o.dims[2] != q.dims[2]) {
             ATB_B200_LOG(ERROR, "MultiLatentAttention: attnOut should have the shape of query");
             return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (Ring()) {
+            const Dims &l = outTensors.at(1).desc.shape;
+            if (l.dimNum != 3 || l.dims[0] != q.dims[0] || l.dims[1] != q.dims[1] || l.dims[2] != 1) {
+                ATB_B200_LOG(ERROR, "MultiLatentAttention: lse should be [tokens, heads, 1]");
+                return ERROR_INVALID_TENSOR_DIM;
+            }
         }
         return NO_ERROR;
     }
@@ -177,6 +196,12 @@ protected:
         t.k_rope_cache = vp.inTensors.at(3).deviceData;
         t.block_tables = static_cast<const int32_t *>(vp.inTensors.at(4).deviceData);
         t.out = vp.outTensors.at(0).deviceData;
+        if (Ring()) {
+            t.lse_out = vp.outTensors.at(1).deviceData;
+            if (t.lse_out == nullptr) {
+                return ERROR_INVALID_PARAM;
+            }
+        }
         if (t.q == nullptr || t.q_rope == nullptr || t.k_cache == nullptr || t.k_rope_cache == nullptr ||
             t.block_tables == nullptr || t.out == nullptr) {
             return ERROR_INVALID_PARAM;
@@ -228,9 +253,10 @@ template <> Status CreateOperation(const infer::MultiLatentAttentionParam &opPar
         opParam.maskUseStatusType >= Param::MASK_USE_STATUS_TYPE_MAX) {
         return ERROR_INVALID_PARAM;
     }
-    if (opParam.calcType != Param::CALC_TYPE_UNDEFINED || opParam.maskType != Param::UNDEFINED ||
+    if ((opParam.calcType != Param::CALC_TYPE_UNDEFINED && opParam.calcType != Param::CALC_TYPE_RING) ||
+        opParam.maskType != Param::UNDEFINED ||
         opParam.cacheMode != Param::KROPE_CTKV || opParam.maskUseStatusType != Param::MASK_USE_STATUS_TYPE_UNDEFINED) {
-        ATB_B200_LOG(ERROR, "MultiLatentAttention: parallel decoding, ring attention, prefill, masks and the NZ / int8 "
+        ATB_B200_LOG(ERROR, "MultiLatentAttention: parallel decoding, prefill, masks and the NZ / int8 "
                             "caches are not supported by this build");
         return ERROR_INVALID_PARAM;
     }

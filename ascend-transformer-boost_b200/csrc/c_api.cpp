@@ -452,6 +452,10 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
     }
     a.logn = (d.score_mods & ATB_B200_SCORE_LOGN) != 0 ? t->logn : nullptr;
     a.kv_bnsd = d.kv_layout == ATB_B200_KV_BNSD ? 1 : 0;
+    if (t->lse_out != nullptr && h.kernel != ATB_B200_KERNEL_MLA_TC5) {
+        return kErrInvalidParam; // only the MLA kernel writes the log-sum-exp
+    }
+    a.lse_out = t->lse_out;
     if ((d.score_mods & ATB_B200_SCORE_ROWS) != 0) {
         a.bt_rows = reinterpret_cast<const int32_t *>(blob + h.off_rows);
         a.mask_rows = a.bt_rows + d.batch;

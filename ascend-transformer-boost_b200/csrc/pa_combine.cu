@@ -33,6 +33,11 @@ __global__ void __launch_bounds__(160) pa_combine_kernel(const PaArgs a)
         sum += exp2f(lse[(int64_t)i * a.num_heads] - mx);
     }
     const float inv = 1.f / sum;
+    if (a.lse_out != nullptr && threadIdx.x == 0) {
+        // log-sum-exp of the whole sequence from its ranges' (log2 domain), written as a natural log
+        static_cast<TQ *>(a.lse_out)[(int64_t)seq * a.num_heads + h] =
+            Elem<TQ>::from_float((mx + log2f(sum)) * 0.6931471805599453f);
+    }
     const bool use_shared = n <= kMaxPartsShared;
     if (use_shared) {
         for (int i = threadIdx.x; i < n; i += blockDim.x) {

@@ -539,6 +539,10 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             }
             if (writer && item.slot >= 0) {
                 a.plan.part_lse[(int64_t)item.slot * a.num_heads + h] = m_row + log2f(l_row);
+            } else if (writer && a.lse_out != nullptr) {
+                // whole sequence in this range: its log-sum-exp, natural log (m_row is in the log2 domain)
+                static_cast<T *>(a.lse_out)[(int64_t)item.seq * a.num_heads + h] =
+                    Elem<T>::from_float((m_row + log2f(l_row)) * 0.6931471805599453f);
             }
             // the next range's first P.V overwrites O: all reads of O must be done first.  It cannot start
             // before the next P tile is signalled by these same warps, which orders it after this point.

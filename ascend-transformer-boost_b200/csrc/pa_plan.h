@@ -79,6 +79,7 @@ struct PaArgs {
     // parallel decoding: the block-table row and the mask row of every query token (null: the token's own index)
     const int32_t *bt_rows;
     const int32_t *mask_rows;
+    void *lse_out;   // optional [batch, num_heads] natural-log LSE in the query dtype (MLA kernel + combine)
     int32_t kv_bnsd; // 1: caches laid out [num_blocks, kv_heads, block_size, dim]
     // optional event probe of one CTA (CTA number = trace_cap >> 24, capacity = its low 24 bits):
     // trace[0] = number of events, then (tag << 56 | index << 40 | cycles)

@@ -98,6 +98,9 @@ typedef struct atb_b200_pa_tensors {
     int64_t mask_head_stride;
     int64_t mask_tokens;
     const float *logn;          /* ATB_B200_SCORE_LOGN only: [batch] fp32 */
+    void *lse_out;              /* optional, MLA kernel only: [batch, num_heads] in q_dtype, the natural-log
+                                   log-sum-exp of the scaled scores of every (token, head) (the second output of
+                                   MultiLatentAttention with CALC_TYPE_RING); NULL = not wanted */
 } atb_b200_pa_tensors;
 
 typedef struct atb_b200_pa_plan atb_b200_pa_plan; /* opaque */

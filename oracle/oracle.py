@@ -120,6 +120,46 @@ def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping):
         raise ValueError("oracle_reshape_and_cache rejected its arguments")
 
 
+def _to_f32(a, dtype):
+    """This module's encodings (float16 arrays; bf16 as uint16 bits) to float32."""
+    a = np.asarray(a)
+    if dtype == "bf16":
+        return (a.astype(np.uint32) << 16).view(np.float32)
+    return a.astype(np.float32)
+
+
+def _from_f32(a, dtype):
+    """float32 to this module's encodings, round to nearest even."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    if dtype == "bf16":
+        u = a.view(np.uint32)
+        return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    return a.astype(np.float16)
+
+
+def attention_lse(q, k_cache, block_tables, context_lens, scale, q_dtype):
+    """Natural-log log-sum-exp of the scaled scores of every (token, head), rounded to the query dtype: the second
+    output of MultiLatentAttention with CALC_TYPE_RING.  Follows softmax_numpy (row_max + log(row_sum), fp32) and the
+    cast in ref_masked_attention of tests/apitest/kernelstest/mix/test_paged_attention_mla_split.py:124-132, 171-175
+    of the reference.  q [B, H, Dk] and k_cache [blocks, block_size, kv_heads, Dk] in this module's encodings;
+    sequences of length 0 keep 0."""
+    qf, kf = _to_f32(q, q_dtype), _to_f32(k_cache, q_dtype)
+    B, H, _ = qf.shape
+    kvh, bs = kf.shape[2], kf.shape[1]
+    out = np.zeros((B, H, 1), dtype=np.float32)
+    for b in range(B):
+        n = int(context_lens[b])
+        if n == 0:
+            continue
+        rows = [kf[int(block_tables[b, t // bs]), t % bs] for t in range(n)]
+        keys = np.stack(rows, axis=0)                                       # [n, kv_heads, Dk]
+        for h in range(H):
+            s = (keys[:, h // (H // kvh), :] @ qf[b, h]).astype(np.float32) * np.float32(scale)
+            mx = s.max()
+            out[b, h, 0] = mx + np.log(np.exp(s - mx).sum(dtype=np.float32))
+    return _from_f32(out, q_dtype)
+
+
 def paged_attention_spec(q, k_cache, v_cache, block_tables, q_lens, context_lens, scale, q_dtype, mask, mask_rows_are_tokens,
                          nthreads=0):
     """Parallel decoding (PagedAttentionParam::CALC_TYPE_SPEC): sequence b owns q_lens[b] consecutive query tokens,

@@ -233,6 +233,27 @@ def run_blockcopy_case(mod, spec):
     return {"k_cache": kexp, "v_cache": vexp, "input_sha256": np.frombuffer(digest(inp).encode(), dtype=np.uint8)}
 
 
+def run_mla_lse_case(mla_split, case):
+    """The log-sum-exp output of MultiLatentAttention (ring form) for an MLA case, through ref_masked_attention of the
+    reference's split-cache kernel test, sequence by sequence as its gather loop calls it (mask None)."""
+    d = wl.make_host_inputs(case)
+    tdt = {"fp16": torch.float16, "bf16": torch.bfloat16}[case.q_dtype]
+    t = mla_split.TestPagedAttentionMLA()
+    t.is_int8_flag = False
+    q, kc = to_torch(d["q"], case.q_dtype), to_torch(d["k_cache"], case.q_dtype)
+    lse = torch.zeros((case.batch, case.heads, 1), dtype=tdt)
+    for b in range(case.batch):
+        n = int(d["context_lens"][b])
+        if n == 0:
+            continue
+        keys = torch.stack([kc[int(d["block_tables"][b, j // case.block_size]), j % case.block_size] for j in range(n)], 0)
+        values = keys[..., :case.dv]
+        _, _, _, lse_b = t.ref_masked_attention(q[b].view(1, case.heads, case.dk), keys, values, np.float32(case.qk_scale),
+                                                None, tdt)
+        lse[b] = lse_b.reshape(case.heads, 1).to(tdt)
+    return {"lse": from_torch(lse, case.q_dtype), "input_sha256": np.frombuffer(digest(d).encode(), dtype=np.uint8)}
+
+
 def run_kvcache_case(mod, spec):
     """KvCache through golden_calc of the reference's kernel test (values as that test holds them: fp16 / int8 numpy;
     bf16 as float32 numpy, exact)."""
@@ -286,12 +307,17 @@ def main():
     nrr16 = _load(os.path.join(kt, "mix/test_rms_norm_and_rope_and_reshape_and_cache.py"), "ref_nrr_fp16")
     nrrbf = _load(os.path.join(kt, "mix/test_rms_norm_and_rope_and_reshape_and_cache_bf16.py"), "ref_nrr_bf16")
     kvcache = _load(os.path.join(kt, "mix/test_kvcache.py"), "ref_kvcache")
+    mla_split = _load(os.path.join(kt, "mix/test_paged_attention_mla_split.py"), "ref_pa_mla_split")
     lookahead = _load(os.path.join(kt, "mix/test_paged_attention_lookahead.py"), "ref_pa_lookahead")
     os.chdir(cwd)
     for spec in GOLDEN_PA_SPEC_CASES:
         res = run_pa_spec_case(lookahead, spec)
         np.savez_compressed(os.path.join(HERE, f"pa_{spec['case'].name}.npz"), **res)
         print("wrote", spec["case"].name, res["out"].shape)
+    for case in GOLDEN_PA_CASES:
+        if case.mla:
+            np.savez_compressed(os.path.join(HERE, f"mla_lse_{case.name}.npz"), **run_mla_lse_case(mla_split, case))
+            print("wrote mla_lse", case.name)
     for spec in GOLDEN_KVCACHE_CASES:
         np.savez_compressed(os.path.join(HERE, f"kvcache_{spec['name']}.npz"), **run_kvcache_case(kvcache, spec))
         print("wrote kvcache", spec["name"])

@@ -357,7 +357,7 @@ def test_multi_latent_attention_param_checks():
     for bad in (dict(qkScale=0.0), dict(qkScale=1.5), dict(headNum=24), dict(kvHeadNum=2), dict(cacheMode=0),
                 dict(cacheMode=9), dict(maskType=7), dict(calcType=9),
                 # forms of the reference this build does not carry
-                dict(calcType=1), dict(calcType=2), dict(calcType=4), dict(maskType=1, calcType=1),
+                dict(calcType=1), dict(calcType=3), dict(calcType=4), dict(maskType=1, calcType=1),
                 dict(cacheMode=2), dict(cacheMode=3), dict(maskUseStatusType=1)):
         _expect(capi.ERROR_INVALID_PARAM, capi.Operation, _mla_param(**bad))
     p = _mla_param()
@@ -389,6 +389,16 @@ def test_multi_latent_attention_setup_checks(monkeypatch):
     _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, swapped(0, dtype=bf, shape=(4, 128, 512)), outs, ctx)      # tokens != batch
     _expect(capi.ERROR_INVALID_TENSOR_DIM, op.setup, ins, [T(dtype=bf, shape=(3, 128, 576), device_ptr=0x1000)], ctx)
     _expect(capi.ERROR_INVALID_PARAM, op.setup, swapped(5, dtype=capi.ACL_INT32, shape=(3,)), outs, ctx)        # no host lens
+    # CALC_TYPE_RING: the log-sum-exp [tokens, heads, 1] is a second output
+    ring = capi.Operation(_mla_param(calcType=2))
+    assert (ring.input_num, ring.output_num) == (6, 2)
+    assert ring.infer_shape(ins, 2) == [(3, 128, 512), (3, 128, 1)]
+    lse = T(dtype=bf, shape=(3, 128, 1), device_ptr=0x1000)
+    assert ring.setup(ins, outs + [lse], ctx) >= 256
+    _expect(capi.ERROR_INVALID_IN_TENSOR_NUM, ring.setup, ins, outs, ctx)            # wrong tensor count
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, ring.setup, ins, outs + [T(dtype=bf, shape=(3, 128, 512), device_ptr=0x1000)], ctx)
+    _expect(capi.ERROR_INVALID_TENSOR_INI_MATCH, ring.setup, ins,
+            outs + [T(dtype=capi.ACL_FLOAT, shape=(3, 128, 1), device_ptr=0x1000)], ctx)
     # execute before a successful setup of these tensors is refused without touching the device
     op2 = capi.Operation(_mla_param())
     _expect(capi.ERROR_INVALID_PARAM, op2.execute, ins, outs, 0x1000, 1 << 20, ctx)

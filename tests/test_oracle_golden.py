@@ -197,3 +197,17 @@ def test_oracle_parallel_decoding_matches_reference_golden(spec):
     unmasked = oracle.paged_attention(d["q"], d["k_cache"], d["v_cache"], d["block_tables"][owner],
                                       d["context_lens"][owner], case.qk_scale, case.q_dtype)
     assert np.abs(wl.to_f32(unmasked, case.q_dtype) - ref).max() > 2.0 ** -5
+
+
+@pytest.mark.parametrize("case", [c for c in GOLDEN_PA_CASES if c.mla], ids=lambda c: c.name)
+def test_oracle_lse_matches_reference_golden(case):
+    """The log-sum-exp output of MultiLatentAttention (CALC_TYPE_RING) against ref_masked_attention of the reference's
+    split-cache kernel test: same fp32 arithmetic up to summation order, so at most one unit in the last place."""
+    fx = np.load(os.path.join(HERE, f"mla_lse_{case.name}.npz"))
+    d = wl.make_host_inputs(case)
+    assert _digest(d) == bytes(fx["input_sha256"]).decode(), "seeded inputs changed; regenerate the fixtures"
+    lse = oracle.attention_lse(d["q"], d["k_cache"], d["block_tables"], d["context_lens"], case.qk_scale, case.q_dtype)
+    got, ref = wl.to_f32(lse, case.q_dtype), wl.to_f32(fx["lse"], case.q_dtype)
+    assert got.shape == (case.batch, case.heads, 1)
+    assert np.all(np.abs(got - ref) <= ulp(case.q_dtype) * np.maximum(np.abs(ref), 1.0))
+    assert np.mean(got == ref) > 0.9

@@ -314,8 +314,11 @@ def test_multi_latent_attention_operation_matches_oracle(name):
     T = capi.atb_tensor
     ins = [T(q_nope), T(q_rope), T(ct_kv), T(k_rope), T(bt), T(lens_dev, host=h["context_lens"])]
     outs = [T(out)]
-    op = capi.Operation(capi.MultiLatentAttentionParam(headNum=case.heads, kvHeadNum=1, qkScale=case.qk_scale, cacheMode=1))
-    assert op.infer_shape(ins, 1) == [tuple(out.shape)]
+    lse = torch.full((case.batch, case.heads, 1), 7.0, dtype=q.dtype, device="cuda")
+    outs.append(T(lse))                                                   # CALC_TYPE_RING: log-sum-exp as second output
+    op = capi.Operation(capi.MultiLatentAttentionParam(headNum=case.heads, kvHeadNum=1, qkScale=case.qk_scale, cacheMode=1,
+                                                       calcType=2))
+    assert op.infer_shape(ins, 2) == [tuple(out.shape), tuple(lse.shape)]
     torch.cuda.synchronize()
     stream = torch.cuda.Stream()
     ctx = capi.Context(stream.cuda_stream)
@@ -331,6 +334,10 @@ def test_multi_latent_attention_operation_matches_oracle(name):
                                             np.ascontiguousarray(h["k_cache"][..., 512:]), h["block_tables"], lens,
                                             case.qk_scale, dt)
         assert max_abs_err(got, ref, dt) <= tol_for(case)
+        want_lse = wl.to_f32(oracle.attention_lse(h["q"], h["k_cache"], h["block_tables"], lens, case.qk_scale, dt), dt)
+        got_lse = wl.to_f32(wl.torch_to_host(lse, dt), dt)
+        unit = 2.0 ** (-10 if dt == "fp16" else -7)
+        assert np.all(np.abs(got_lse - want_lse) <= 2 * unit * np.maximum(np.abs(want_lse), 1.0))
 
 
 # ------------------------------------------------------------------ masks (NORM, ALIBI) and logN scaling
