@@ -545,6 +545,7 @@ def atb_tensor(t=None, *, dtype=None, shape=None, host=None, device_ptr=None, fm
         a.dims[i] = s
     if host is not None:
         a.host_data = host.ctypes.data
+    a._keep_alive = (t, host)   # the record holds raw addresses: keep the arrays they point into alive with it
     return a
 
 

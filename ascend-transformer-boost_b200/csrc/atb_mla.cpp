@@ -4,9 +4,10 @@
 // src/ops/ops_infer/multi_latent_attention/multi_latent_attention_operation.cpp of the reference
 // (CreateOperation :58-91, ParamCheck :93-146, ParamRangeCheck :148-170, GetInputNum/GetOutputNum :240-270,
 //  InferShapeImpl :272-286, QKVDimCheck :337-379, DimCheck :579-640) and its host-tensor handling
-// (multi_latent_attention/param.cpp: contextLens is host data).  Built here: calcType UNDEFINED (one query token per
-// sequence) and CALC_TYPE_RING (the same with the log-sum-exp as a second output), cacheMode KROPE_CTKV, no mask;
-// parallel decoding, prefill and the NZ / int8 caches are rejected.  The device path is the tcgen05 MLA kernel with a
+// (multi_latent_attention/param.cpp: contextLens is host data).  Built here: cacheMode KROPE_CTKV with calcType
+// UNDEFINED (one query token per sequence), CALC_TYPE_SPEC (several: MTP; no mask, MASK_TYPE_SPEC or MASK_TYPE_MASK_FREE)
+// and the _RING forms of both (log-sum-exp as a second output); prefill, the other masks and the NZ / int8 caches are
+// rejected.  The device path is the tcgen05 MLA kernel with a
 // second tensor map for the rope rows.
 #include <cmath>
 #include <cstdlib>
@@ -24,12 +25,19 @@ public:
     explicit MultiLatentAttentionOperation(const Param &p) : OperationBase("MultiLatentAttentionOperation"), param_(p)
     {
         for (aclDataType h : {ACL_FLOAT16, ACL_BF16}) {
-            // qNope, qRope, ctKV, kRope, blockTables, contextLens -> attnOut [, lse]
-            if (Ring()) {
-                combs_.push_back({h, h, h, h, ACL_INT32, ACL_INT32, h, h});
-            } else {
-                combs_.push_back({h, h, h, h, ACL_INT32, ACL_INT32, h});
+            // qNope, qRope, ctKV, kRope, blockTables, contextLens [, mask] [, qSeqLens] -> attnOut [, lse]
+            DtypeComb c = {h, h, h, h, ACL_INT32, ACL_INT32};
+            if (HasMask()) {
+                c.push_back(h);
             }
+            if (Spec()) {
+                c.push_back(ACL_INT32);
+            }
+            c.push_back(h);
+            if (Ring()) {
+                c.push_back(h);
+            }
+            combs_.push_back(c);
         }
     }
     ~MultiLatentAttentionOperation() override
@@ -38,12 +46,23 @@ public:
             atb_b200_pa_plan_destroy(plan_);
         }
     }
-    uint32_t GetInputNum() const override { return 6; }
+    uint32_t GetInputNum() const override { return 6u + (HasMask() ? 1u : 0u) + (Spec() ? 1u : 0u); }
     uint32_t GetOutputNum() const override { return Ring() ? 2 : 1; }
 
 protected:
     // CALC_TYPE_RING: the log-sum-exp of every (token, head) is a second output [tokens, heads, 1]
-    bool Ring() const { return param_.calcType == Param::CALC_TYPE_RING; }
+    bool Ring() const
+    {
+        return param_.calcType == Param::CALC_TYPE_RING || param_.calcType == Param::CALC_TYPE_SPEC_AND_RING;
+    }
+    // CALC_TYPE_SPEC: several query tokens per sequence (MTP), qSeqLens as host data after the optional mask
+    bool Spec() const
+    {
+        return param_.calcType == Param::CALC_TYPE_SPEC || param_.calcType == Param::CALC_TYPE_SPEC_AND_RING;
+    }
+    bool HasMask() const { return param_.maskType != Param::UNDEFINED; }
+    size_t MaskPos() const { return 6; }
+    size_t QLensPos() const { return 6 + (HasMask() ? 1 : 0); }
 
     const std::vector<DtypeComb> &DtypeCombs() const override { return combs_; }
 
@@ -60,9 +79,33 @@ protected:
             ATB_B200_LOG(ERROR, "MultiLatentAttention: batch should be <= 8192");
             return ERROR_INVALID_TENSOR_DIM;
         }
-        if (numTokens != batch) {
+        if (!Spec() && numTokens != batch) {
             ATB_B200_LOG(ERROR, "MultiLatentAttention: numTokens and batch should be same in decoder stage");
             return ERROR_INVALID_TENSOR_DIM;
+        }
+        if (Spec()) {
+            const Dims &ql = in.at(QLensPos()).shape;
+            if (ql.dimNum != 1) {
+                ATB_B200_LOG(ERROR, "MultiLatentAttention: invalid qSeqlen dimNum");
+                return ERROR_INVALID_TENSOR_DIM_NUM;
+            }
+            if (ql.dims[0] != batch || numTokens < batch) {
+                ATB_B200_LOG(ERROR, "MultiLatentAttention: dim 0 of qSeqlen should be equal to dim 0 of contextLens");
+                return ERROR_INVALID_TENSOR_DIM;
+            }
+        }
+        if (HasMask()) {
+            // MASK_TYPE_SPEC: one row per query token [num_tokens, max_seq_len]; MASK_TYPE_MASK_FREE: the reference's
+            // fixed causal pattern, any 2-D tensor (its content is implied, it is not read)
+            const Dims &m = in.at(MaskPos()).shape;
+            if (m.dimNum != 2) {
+                ATB_B200_LOG(ERROR, "MultiLatentAttention: invalid mask dimNum");
+                return ERROR_INVALID_TENSOR_DIM_NUM;
+            }
+            if (param_.maskType == Param::MASK_TYPE_SPEC && m.dims[0] < numTokens) {
+                ATB_B200_LOG(ERROR, "MultiLatentAttention: the spec mask should have one row per query token");
+                return ERROR_INVALID_TENSOR_DIM;
+            }
         }
         if (in.at(5).shape.dims[0] != batch) {
             ATB_B200_LOG(ERROR, "MultiLatentAttention: dim 0 of block_tables and contextLens should be same");
@@ -163,9 +206,53 @@ protected:
             d.sm_count = std::atoi(sm);
         }
         const int32_t *lens = static_cast<const int32_t *>(cl.hostData);
+        const bool specMask = param_.maskType == Param::MASK_TYPE_SPEC;
+        if (Spec()) {
+            // Every query token becomes a planned row of its own with its sequence's block-table row.  Without a mask
+            // it sees the whole context; MASK_FREE is the causal rule (token j of q sees ctx - (q - 1 - j) tokens),
+            // expressed through the row's length; MASK_TYPE_SPEC adds the caller's mask row of that token.
+            const Tensor &ql = vp.inTensors.at(QLensPos());
+            if (ql.hostData == nullptr) {
+                ATB_B200_LOG(ERROR, "MultiLatentAttention: qSeqlen hostData is null");
+                return ERROR_INVALID_PARAM;
+            }
+            const int32_t *qLens = static_cast<const int32_t *>(ql.hostData);
+            const int64_t batch = cl.desc.shape.dims[0];
+            const bool causal = param_.maskType == Param::MASK_TYPE_MASK_FREE;
+            tokenLens_.clear();
+            btRows_.clear();
+            maskRows_.clear();
+            for (int64_t b = 0; b < batch; ++b) {
+                if (qLens[b] < 0 || lens[b] < 0 || (causal && qLens[b] > lens[b])) {
+                    ATB_B200_LOG(ERROR, "MultiLatentAttention: qSeqlen should be in [0, contextLens]");
+                    return ERROR_INVALID_PARAM;
+                }
+                for (int32_t j = 0; j < qLens[b]; ++j) {
+                    maskRows_.push_back(static_cast<int32_t>(tokenLens_.size()));
+                    tokenLens_.push_back(causal ? lens[b] - (qLens[b] - 1 - j) : lens[b]);
+                    btRows_.push_back(static_cast<int32_t>(b));
+                }
+            }
+            if (static_cast<int64_t>(tokenLens_.size()) != q.dims[0]) {
+                ATB_B200_LOG(ERROR, "MultiLatentAttention: the sum of qSeqlen should equal the query tokens");
+                return ERROR_INVALID_PARAM;
+            }
+            lens = tokenLens_.data();
+            d.score_mods = ATB_B200_SCORE_ROWS | (specMask ? ATB_B200_SCORE_MASK : 0);
+            if (specMask) {
+                const int64_t maskLen = vp.inTensors.at(MaskPos()).desc.shape.dims[1];
+                for (int32_t t = 0; t < d.batch; ++t) {
+                    if (lens[t] > maskLen) {
+                        ATB_B200_LOG(ERROR, "MultiLatentAttention: the mask is shorter than a sequence's context");
+                        return ERROR_INVALID_TENSOR_DIM;
+                    }
+                }
+            }
+        }
         int rc;
         if (plan_ != nullptr && d.batch == desc_.batch && d.num_blocks == desc_.num_blocks &&
-            d.max_blocks_per_seq == desc_.max_blocks_per_seq && d.q_dtype == desc_.q_dtype && d.sm_count == desc_.sm_count) {
+            d.max_blocks_per_seq == desc_.max_blocks_per_seq && d.q_dtype == desc_.q_dtype && d.sm_count == desc_.sm_count &&
+            d.score_mods == desc_.score_mods) {
             rc = atb_b200_pa_plan_update(plan_, lens);
         } else {
             if (plan_ != nullptr) {
@@ -177,6 +264,14 @@ protected:
         }
         if (rc != 0) {
             return rc;
+        }
+        if (Spec()) {
+            rc = atb_b200_pa_plan_set_rows(plan_, btRows_.data(), static_cast<int32_t>(cl.desc.shape.dims[0]),
+                                           specMask ? maskRows_.data() : nullptr,
+                                           specMask ? vp.inTensors.at(MaskPos()).desc.shape.dims[0] : 0);
+            if (rc != 0) {
+                return rc;
+            }
         }
         atb_b200_pa_plan_info info{};
         atb_b200_pa_plan_get_info(plan_, &info);
@@ -196,6 +291,16 @@ protected:
         t.k_rope_cache = vp.inTensors.at(3).deviceData;
         t.block_tables = static_cast<const int32_t *>(vp.inTensors.at(4).deviceData);
         t.out = vp.outTensors.at(0).deviceData;
+        if (Spec() && param_.maskType == Param::MASK_TYPE_SPEC) {
+            const Tensor &m = vp.inTensors.at(MaskPos());
+            t.mask = m.deviceData;
+            t.mask_batch_stride = m.desc.shape.dims[1];
+            t.mask_head_stride = 0;
+            t.mask_tokens = m.desc.shape.dims[1];
+            if (t.mask == nullptr) {
+                return ERROR_INVALID_PARAM;
+            }
+        }
         if (Ring()) {
             t.lse_out = vp.outTensors.at(1).deviceData;
             if (t.lse_out == nullptr) {
@@ -217,6 +322,7 @@ private:
     std::vector<DtypeComb> combs_;
     atb_b200_pa_plan *plan_ = nullptr;
     atb_b200_pa_desc desc_{};
+    std::vector<int32_t> tokenLens_, btRows_, maskRows_; // CALC_TYPE_SPEC: one entry per query token
 };
 
 } // namespace
@@ -253,10 +359,15 @@ template <> Status CreateOperation(const infer::MultiLatentAttentionParam &opPar
         opParam.maskUseStatusType >= Param::MASK_USE_STATUS_TYPE_MAX) {
         return ERROR_INVALID_PARAM;
     }
-    if ((opParam.calcType != Param::CALC_TYPE_UNDEFINED && opParam.calcType != Param::CALC_TYPE_RING) ||
-        opParam.maskType != Param::UNDEFINED ||
-        opParam.cacheMode != Param::KROPE_CTKV || opParam.maskUseStatusType != Param::MASK_USE_STATUS_TYPE_UNDEFINED) {
-        ATB_B200_LOG(ERROR, "MultiLatentAttention: parallel decoding, prefill, masks and the NZ / int8 "
+    const bool spec = opParam.calcType == Param::CALC_TYPE_SPEC || opParam.calcType == Param::CALC_TYPE_SPEC_AND_RING;
+    if (!spec && opParam.maskType != Param::UNDEFINED) {
+        ATB_B200_LOG(ERROR, "MultiLatentAttention: only mtp(CALC_TYPE_SPEC) support mask");
+        return ERROR_INVALID_PARAM;
+    }
+    if (opParam.calcType == Param::CALC_TYPE_PREFILL || opParam.maskType == Param::MASK_TYPE_CAUSAL_MASK ||
+        opParam.maskType == Param::MASK_TYPE_SWA_NORM || opParam.cacheMode != Param::KROPE_CTKV ||
+        opParam.maskUseStatusType != Param::MASK_USE_STATUS_TYPE_UNDEFINED) {
+        ATB_B200_LOG(ERROR, "MultiLatentAttention: prefill, the CAUSAL_MASK / SWA_NORM masks, maskUseStatus and the NZ / int8 "
                             "caches are not supported by this build");
         return ERROR_INVALID_PARAM;
     }

@@ -395,6 +395,9 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
         (t->mask == nullptr || t->mask_tokens < h.max_context || t->mask_batch_stride < 0 || t->mask_head_stride < 0)) {
         return kErrInvalidParam; // no mask, or one shorter than the longest context
     }
+    if ((h.desc.score_mods & ATB_B200_SCORE_MASK) != 0 && h.kernel == ATB_B200_KERNEL_MLA_TC5 && t->mask_head_stride != 0) {
+        return kErrInvalidParam; // the MLA kernel adds one mask row to all heads
+    }
     if ((h.desc.score_mods & ATB_B200_SCORE_LOGN) != 0 && t->logn == nullptr) {
         return kErrInvalidParam;
     }

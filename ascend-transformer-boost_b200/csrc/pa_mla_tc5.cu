@@ -142,7 +142,9 @@ __host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t b_mn_ma
 
 enum Bar { kQFull = 0, kQEmpty, kKvFull0, kKvFull1, kKvFull2, kKvEmpty0, kKvEmpty1, kKvEmpty2, kSFull0, kSFull1, kSEmpty0, kSEmpty1, kPFull, kPvDone };
 
-template <typename T>
+// kMask: the variant that adds a per-token mask row to the scores (parallel decoding with MASK_TYPE_SPEC); the plain
+// variant carries none of that code.  Both follow bt_rows when the plan gives every query token its block-table row.
+template <typename T, bool kMask>
 __global__ void __launch_bounds__(kThreads, 1)
 pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap rmap, const PaArgs a)
 {
@@ -225,7 +227,7 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         for (int it = item_begin, i = 0; it < item_end && alive; ++it, ++i) {
             const PaItem item = a.plan.items[it];
             const int n_st = (item.tok_end - item.tok_begin + kTok - 1) / kTok;
-            const int32_t *bt = a.block_tables + (int64_t)item.seq * a.max_blocks;
+            const int32_t *bt = a.block_tables + (int64_t)(a.bt_rows != nullptr ? a.bt_rows[item.seq] : item.seq) * a.max_blocks;
             for (int st0 = 0; st0 < n_st && alive; st0 += 32) {
                 int blk = 0;
                 if (st0 + lane < n_st) {
@@ -377,6 +379,11 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 }
             }
             float m_used = -INFINITY, l = 0.f;
+            const T *mrow = nullptr; // this token's mask row, at the first token of the range
+            if (kMask) {
+                mrow = static_cast<const T *>(a.mask) +
+                       (int64_t)(a.mask_rows != nullptr ? a.mask_rows[item.seq] : item.seq) * a.mask_bs + item.tok_begin;
+            }
             for (int st = 0; st < n_st && alive; ++st, ++g) {
                 const int sb = g & 1;
                 const int valid = min(kTok, item.tok_end - (item.tok_begin + st * kTok));
@@ -403,6 +410,17 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 for (int j = 0; j < 32; ++j) {
                     float v0 = __uint_as_float(r0[j]) * a.scale_log2;
                     float v1 = __uint_as_float(r1[j]) * a.scale_log2;
+                    if (kMask) {
+                        // the same mask value for every head (row); -inf is kept finite so that a fully masked
+                        // start of a range cannot make the running maximum -inf.  Tokens past the end are not read.
+                        constexpr float kLog2e = 1.4426950408889634f;
+                        if (j < valid) {
+                            v0 = fmaxf(v0 + kLog2e * Elem<T>::to_float(mrow[st * kTok + j]), -1e30f);
+                        }
+                        if (j + 32 < valid) {
+                            v1 = fmaxf(v1 + kLog2e * Elem<T>::to_float(mrow[st * kTok + j + 32]), -1e30f);
+                        }
+                    }
                     v0 = (j < valid) ? v0 : -INFINITY;
                     v1 = (j + 32 < valid) ? v1 : -INFINITY;
                     r0[j] = __float_as_uint(v0);
@@ -580,8 +598,10 @@ EncodeFn get_encode_fn()
 template <typename T>
 cudaError_t launch_typed(const PaArgs &args, const CUtensorMap &km, const CUtensorMap &rm, cudaStream_t s)
 {
-    auto kern = pa_mla_tc5_kernel<T>;
-    static bool configured[64] = {};
+    const bool masked = args.mask != nullptr;
+    auto kern = masked ? pa_mla_tc5_kernel<T, true> : pa_mla_tc5_kernel<T, false>;
+    static bool configured_plain[64] = {}, configured_masked[64] = {};
+    bool *configured = masked ? configured_masked : configured_plain;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {

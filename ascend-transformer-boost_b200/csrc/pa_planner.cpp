@@ -63,15 +63,17 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
         kernel = ATB_B200_KERNEL_MLA_TC5;
     }
     if (d.score_mods != 0) {
-        // masks and logN scaling live in the fp16 / bf16 D = 128 kernel and in the CUDA-core kernel
-        if ((d.score_mods & ~(ATB_B200_SCORE_MASK | ATB_B200_SCORE_LOGN | ATB_B200_SCORE_ROWS)) != 0 || d.rope_dim != 0) {
+        // masks, logN scaling and per-token rows live in the fp16 / bf16 D = 128 kernel and in the CUDA-core kernel;
+        // the MLA kernel takes per-token rows and a mask without a head stride, no logN
+        if ((d.score_mods & ~(ATB_B200_SCORE_MASK | ATB_B200_SCORE_LOGN | ATB_B200_SCORE_ROWS)) != 0) {
             return kErrInvalidParam;
         }
         const bool tma_plain = tma_ok && d.kv_dtype != kInt8;
+        const bool mla_mods = mla_ok && (d.score_mods & ATB_B200_SCORE_LOGN) == 0;
         if (kernel == ATB_B200_KERNEL_AUTO) {
-            kernel = tma_plain ? ATB_B200_KERNEL_TMA_MMA : ATB_B200_KERNEL_GENERIC;
+            kernel = tma_plain ? ATB_B200_KERNEL_TMA_MMA : (mla_mods ? ATB_B200_KERNEL_MLA_TC5 : ATB_B200_KERNEL_GENERIC);
         }
-        if (kernel == ATB_B200_KERNEL_MLA_TC5 || (kernel == ATB_B200_KERNEL_TMA_MMA && !tma_plain)) {
+        if ((kernel == ATB_B200_KERNEL_MLA_TC5 && !mla_mods) || (kernel == ATB_B200_KERNEL_TMA_MMA && !tma_plain)) {
             return kErrInvalidTensorDim;
         }
     }

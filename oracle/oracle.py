@@ -137,12 +137,12 @@ def _from_f32(a, dtype):
     return a.astype(np.float16)
 
 
-def attention_lse(q, k_cache, block_tables, context_lens, scale, q_dtype):
+def attention_lse(q, k_cache, block_tables, context_lens, scale, q_dtype, mask=None):
     """Natural-log log-sum-exp of the scaled scores of every (token, head), rounded to the query dtype: the second
     output of MultiLatentAttention with CALC_TYPE_RING.  Follows softmax_numpy (row_max + log(row_sum), fp32) and the
     cast in ref_masked_attention of tests/apitest/kernelstest/mix/test_paged_attention_mla_split.py:124-132, 171-175
     of the reference.  q [B, H, Dk] and k_cache [blocks, block_size, kv_heads, Dk] in this module's encodings;
-    sequences of length 0 keep 0."""
+    sequences of length 0 keep 0.  mask: optional fp32 [B, 1, T], added to the scaled scores of every head."""
     qf, kf = _to_f32(q, q_dtype), _to_f32(k_cache, q_dtype)
     B, H, _ = qf.shape
     kvh, bs = kf.shape[2], kf.shape[1]
@@ -155,19 +155,24 @@ def attention_lse(q, k_cache, block_tables, context_lens, scale, q_dtype):
         keys = np.stack(rows, axis=0)                                       # [n, kv_heads, Dk]
         for h in range(H):
             s = (keys[:, h // (H // kvh), :] @ qf[b, h]).astype(np.float32) * np.float32(scale)
+            if mask is not None:
+                s = s + mask[b, 0, :n]
             mx = s.max()
             out[b, h, 0] = mx + np.log(np.exp(s - mx).sum(dtype=np.float32))
     return _from_f32(out, q_dtype)
 
 
 def paged_attention_spec(q, k_cache, v_cache, block_tables, q_lens, context_lens, scale, q_dtype, mask, mask_rows_are_tokens,
-                         nthreads=0):
+                         nthreads=0, dv=None, want_lse=False):
     """Parallel decoding (PagedAttentionParam::CALC_TYPE_SPEC): sequence b owns q_lens[b] consecutive query tokens,
     each of which attends to all context_lens[b] cached tokens of that sequence plus a row of `mask` (fp32):
     row = the token's index for MASK_TYPE_SPEC ([tokens, T]; `mask_rows_are_tokens`), row = ctx - q_len + j of the
     square causal mask [T, T] for MASK_TYPE_NORM.  Restates ref_single_query_cached_kv_attention of
     tests/apitest/kernelstest/mix/test_paged_attention_lookahead.py:97-140 by expanding every query token into a
-    sequence of its own (its sequence's block-table row and length, its mask row) for `paged_attention`."""
+    sequence of its own (its sequence's block-table row and length, its mask row) for `paged_attention`.
+    mask=None: every token sees its sequence's whole context.  v_cache=None with dv: the MLA combined cache
+    (V = K[..., :dv]); want_lse also returns the log-sum-exp [tokens, heads, 1] as
+    tests/apitest/kernelstest/mix/test_paged_attention_mla_mtp_split.py:85-122 does (fp32, rounded to the query dtype)."""
     q_lens = np.asarray(q_lens, dtype=np.int64)
     context_lens = np.asarray(context_lens, dtype=np.int32)
     tokens = int(q_lens.sum())
@@ -175,12 +180,17 @@ def paged_attention_spec(q, k_cache, v_cache, block_tables, q_lens, context_lens
     owner = np.repeat(np.arange(len(q_lens)), q_lens)
     within = np.arange(tokens) - np.repeat(np.cumsum(q_lens) - q_lens, q_lens)
     lens = context_lens[owner]
-    mask = np.asarray(mask, dtype=np.float32)
-    rows = np.arange(tokens) if mask_rows_are_tokens else lens.astype(np.int64) - q_lens[owner] + within
-    assert rows.min(initial=0) >= 0 and rows.max(initial=0) < mask.shape[0]
-    per_token = np.ascontiguousarray(mask[rows][:, None, :])                     # [tokens, 1, T]
-    return paged_attention(q, k_cache, v_cache, np.ascontiguousarray(block_tables[owner]), lens, scale, q_dtype,
-                           nthreads=nthreads, mask=per_token)
+    per_token = None
+    if mask is not None:
+        mask = np.asarray(mask, dtype=np.float32)
+        rows = np.arange(tokens) if mask_rows_are_tokens else lens.astype(np.int64) - q_lens[owner] + within
+        assert rows.min(initial=0) >= 0 and rows.max(initial=0) < mask.shape[0]
+        per_token = np.ascontiguousarray(mask[rows][:, None, :])                 # [tokens, 1, T]
+    tables = np.ascontiguousarray(block_tables[owner])
+    out = paged_attention(q, k_cache, v_cache, tables, lens, scale, q_dtype, nthreads=nthreads, mask=per_token, dv=dv)
+    if not want_lse:
+        return out
+    return out, attention_lse(q, k_cache, tables, lens, scale, q_dtype, mask=per_token)
 
 
 def multi_latent_attention(q_nope, q_rope, ct_kv, k_rope, block_tables, context_lens, scale, q_dtype, **kw):

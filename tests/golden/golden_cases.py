@@ -208,6 +208,38 @@ GOLDEN_PA_SPEC_CASES = [
 ]
 
 
+GOLDEN_MLA_MTP_CASES = [
+    dict(case=Case("mla_mtp_spec_mask_bf16", batch=3, heads=8, kv_heads=1, dk=576, dv=512, q_dtype="bf16", mla=True,
+                   ctx=("list", [140, 90, 257]), seed=141), q_lens=[2, 2, 3], mask="spec"),
+    dict(case=Case("mla_mtp_no_mask_fp16", batch=2, heads=16, kv_heads=1, dk=576, dv=512, q_dtype="fp16", mla=True,
+                   ctx=("list", [129, 60]), seed=142), q_lens=[2, 1], mask=None),
+]
+
+
+def mla_mtp_inputs(spec):
+    """Inputs of an MLA parallel-decoding case (combined 576-wide rows; the tests split them [512, 64]): cache, block
+    tables and context lengths of `case`, a query with sum(q_lens) tokens, and for MASK_TYPE_SPEC the mask
+    [tokens, max_ctx] with every sequence's causal triangle in columns [ctx - q_len, ctx), as the reference test
+    builds it (tests/apitest/kernelstest/mix/test_paged_attention_mla_mtp_split.py:246-257)."""
+    case = spec["case"]
+    d = _wl.make_host_inputs(case)
+    q_lens = np.asarray(spec["q_lens"], dtype=np.int32)
+    tokens, T = int(q_lens.sum()), int(d["context_lens"].max())
+    rng = np.random.default_rng(case.seed + 31)
+    d["q"] = _wl.encode(rng.standard_normal((tokens, case.heads, case.dk)).astype(np.float32), case.q_dtype)
+    d["q_lens"] = q_lens
+    if spec["mask"] == "spec":
+        m = np.zeros((tokens, T), dtype=np.float32)
+        pre = 0
+        for n, k in zip(q_lens, d["context_lens"]):
+            m[pre:pre + n, k - n:k] = np.triu(np.ones((n, n), dtype=np.float32), 1) * -10000.0
+            pre += n
+        d["mask"] = _wl.encode(m, case.q_dtype)
+    for k in ("v_cache", "new_v"):
+        d.pop(k, None)
+    return d
+
+
 def spec_inputs(spec):
     """Inputs of a parallel-decoding case: the caches, block tables and context lengths of `case` (one row per
     sequence), a query with sum(q_lens) tokens, and the mask built like the reference test builds it

@@ -32,8 +32,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, HERE)
 
-from golden_cases import (GOLDEN_BLOCKCOPY_CASES, GOLDEN_PA_CASES, GOLDEN_KVCACHE_CASES, GOLDEN_PA_FEATURE_CASES, GOLDEN_PA_SPEC_CASES, GOLDEN_PCL_CASES,  # noqa: E402
-                          GOLDEN_NRR_CASES, GOLDEN_RAC_CASES, blockcopy_inputs, load_workloads, nrr_inputs, kvcache_inputs, pa_mask, spec_inputs,
+from golden_cases import (GOLDEN_BLOCKCOPY_CASES, GOLDEN_PA_CASES, GOLDEN_KVCACHE_CASES, GOLDEN_MLA_MTP_CASES, GOLDEN_PA_FEATURE_CASES, GOLDEN_PA_SPEC_CASES, GOLDEN_PCL_CASES,  # noqa: E402
+                          GOLDEN_NRR_CASES, GOLDEN_RAC_CASES, blockcopy_inputs, load_workloads, nrr_inputs, kvcache_inputs, mla_mtp_inputs, pa_mask, spec_inputs,
                           pcl_inputs, rac_inputs)
 
 wl = load_workloads()
@@ -254,6 +254,25 @@ def run_mla_lse_case(mla_split, case):
     return {"lse": from_torch(lse, case.q_dtype), "input_sha256": np.frombuffer(digest(d).encode(), dtype=np.uint8)}
 
 
+def run_mla_mtp_case(mtp, spec):
+    """MLA parallel decoding (output and log-sum-exp) through the golden of the reference's MTP split-cache kernel test;
+    mask_type 3 = MASK_TYPE_SPEC rows per token, 0 = no mask."""
+    case = spec["case"]
+    d = mla_mtp_inputs(spec)
+    tdt = {"fp16": torch.float16, "bf16": torch.bfloat16}[case.q_dtype]
+    t = mtp.TestUnpadPagedAttention()
+    t.post_mask_factor = 1.0
+    q, kc = to_torch(d["q"], case.q_dtype), to_torch(d["k_cache"], case.q_dtype)
+    tokens = q.shape[0]
+    out, out_high = torch.zeros((tokens, case.heads, case.dv), dtype=tdt), torch.zeros((tokens, case.heads, case.dv))
+    lse, lse_high = torch.zeros((tokens, case.heads, 1), dtype=tdt), torch.zeros((tokens, case.heads, 1))
+    mask = to_torch(d["mask"], case.q_dtype) if spec["mask"] else None
+    t.ref_single_query_cached_kv_attention(out, out_high, lse, lse_high, q, kc, kc[..., :case.dv], d["block_tables"].tolist(),
+                                           d["q_lens"].tolist(), d["context_lens"].tolist(), mask, 3 if spec["mask"] else 0)
+    return {"out": from_torch(out, case.q_dtype), "lse": from_torch(lse, case.q_dtype),
+            "input_sha256": np.frombuffer(digest(d).encode(), dtype=np.uint8)}
+
+
 def run_kvcache_case(mod, spec):
     """KvCache through golden_calc of the reference's kernel test (values as that test holds them: fp16 / int8 numpy;
     bf16 as float32 numpy, exact)."""
@@ -308,6 +327,7 @@ def main():
     nrrbf = _load(os.path.join(kt, "mix/test_rms_norm_and_rope_and_reshape_and_cache_bf16.py"), "ref_nrr_bf16")
     kvcache = _load(os.path.join(kt, "mix/test_kvcache.py"), "ref_kvcache")
     mla_split = _load(os.path.join(kt, "mix/test_paged_attention_mla_split.py"), "ref_pa_mla_split")
+    mtp = _load(os.path.join(kt, "mix/test_paged_attention_mla_mtp_split.py"), "ref_pa_mla_mtp")
     lookahead = _load(os.path.join(kt, "mix/test_paged_attention_lookahead.py"), "ref_pa_lookahead")
     os.chdir(cwd)
     for spec in GOLDEN_PA_SPEC_CASES:
@@ -318,6 +338,9 @@ def main():
         if case.mla:
             np.savez_compressed(os.path.join(HERE, f"mla_lse_{case.name}.npz"), **run_mla_lse_case(mla_split, case))
             print("wrote mla_lse", case.name)
+    for spec in GOLDEN_MLA_MTP_CASES:
+        np.savez_compressed(os.path.join(HERE, f"pa_{spec['case'].name}.npz"), **run_mla_mtp_case(mtp, spec))
+        print("wrote", spec["case"].name)
     for spec in GOLDEN_KVCACHE_CASES:
         np.savez_compressed(os.path.join(HERE, f"kvcache_{spec['name']}.npz"), **run_kvcache_case(kvcache, spec))
         print("wrote kvcache", spec["name"])

@@ -356,9 +356,10 @@ def test_multi_latent_attention_param_checks():
     assert (op.name, op.input_num, op.output_num) == ("MultiLatentAttentionOperation", 6, 1)
     for bad in (dict(qkScale=0.0), dict(qkScale=1.5), dict(headNum=24), dict(kvHeadNum=2), dict(cacheMode=0),
                 dict(cacheMode=9), dict(maskType=7), dict(calcType=9),
+                dict(maskType=1), dict(maskType=2, calcType=2),            # only mtp (CALC_TYPE_SPEC) supports masks
                 # forms of the reference this build does not carry
-                dict(calcType=1), dict(calcType=3), dict(calcType=4), dict(maskType=1, calcType=1),
-                dict(cacheMode=2), dict(cacheMode=3), dict(maskUseStatusType=1)):
+                dict(calcType=4), dict(maskType=3, calcType=1), dict(maskType=4, calcType=1, windowSize=8),
+                dict(cacheMode=2), dict(cacheMode=3), dict(maskUseStatusType=1, calcType=3)):
         _expect(capi.ERROR_INVALID_PARAM, capi.Operation, _mla_param(**bad))
     p = _mla_param()
     p.rsv[31] = 1
@@ -399,6 +400,32 @@ def test_multi_latent_attention_setup_checks(monkeypatch):
     _expect(capi.ERROR_INVALID_TENSOR_DIM, ring.setup, ins, outs + [T(dtype=bf, shape=(3, 128, 512), device_ptr=0x1000)], ctx)
     _expect(capi.ERROR_INVALID_TENSOR_INI_MATCH, ring.setup, ins,
             outs + [T(dtype=capi.ACL_FLOAT, shape=(3, 128, 1), device_ptr=0x1000)], ctx)
+    # CALC_TYPE_SPEC (MTP): qSeqLens as host data after the optional mask; one planned row per query token
+    qlens = np.array([2, 1, 2], dtype=np.int32)
+    spec_ins = [T(dtype=bf, shape=(5, 128, 512), device_ptr=0x1000), T(dtype=bf, shape=(5, 128, 64), device_ptr=0x1000)] + ins[2:]
+    spec_outs = [T(dtype=bf, shape=(5, 128, 512), device_ptr=0x1000)]
+    ql = T(dtype=capi.ACL_INT32, shape=(3,), device_ptr=0x1000, host=qlens)
+    nomask = capi.Operation(_mla_param(calcType=1))
+    assert nomask.input_num == 7
+    assert nomask.setup(spec_ins + [ql], spec_outs, ctx) >= 256
+    _expect(capi.ERROR_INVALID_PARAM, nomask.setup, spec_ins + [T(dtype=capi.ACL_INT32, shape=(3,), device_ptr=0x1000)],
+            spec_outs, ctx)                                                                              # no host qSeqLens
+    _expect(capi.ERROR_INVALID_PARAM, nomask.setup,
+            spec_ins + [T(dtype=capi.ACL_INT32, shape=(3,), device_ptr=0x1000, host=np.array([2, 2, 2], dtype=np.int32))],
+            spec_outs, ctx)                                                                              # sum != tokens
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, nomask.setup, spec_ins + [T(dtype=capi.ACL_INT32, shape=(2,), device_ptr=0x1000,
+                                                                      host=qlens)], spec_outs, ctx)
+    masked = capi.Operation(_mla_param(calcType=3, maskType=1))                                          # SPEC_AND_RING + spec mask
+    assert (masked.input_num, masked.output_num) == (8, 2)
+    m_ok = T(dtype=bf, shape=(5, 400), device_ptr=0x1000)
+    lse5 = T(dtype=bf, shape=(5, 128, 1), device_ptr=0x1000)
+    assert masked.setup(spec_ins + [m_ok, ql], spec_outs + [lse5], ctx) >= 256
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, masked.setup, spec_ins + [T(dtype=bf, shape=(4, 400), device_ptr=0x1000), ql],
+            spec_outs + [lse5], ctx)                                                                     # a row per token
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, masked.setup, spec_ins + [T(dtype=bf, shape=(5, 399), device_ptr=0x1000), ql],
+            spec_outs + [lse5], ctx)                                                                     # shorter than a context
+    free = capi.Operation(_mla_param(calcType=1, maskType=2))                                            # MASK_FREE: causal
+    assert free.setup(spec_ins + [T(dtype=bf, shape=(129, 128), device_ptr=0x1000), ql], spec_outs, ctx) >= 256
     # execute before a successful setup of these tensors is refused without touching the device
     op2 = capi.Operation(_mla_param())
     _expect(capi.ERROR_INVALID_PARAM, op2.execute, ins, outs, 0x1000, 1 << 20, ctx)
@@ -464,9 +491,11 @@ def test_planner_routes_score_modifiers():
     assert plan(kernel=capi.KERNEL_GENERIC) == capi.KERNEL_GENERIC
     _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, kv="int8", kernel=capi.KERNEL_TMA_MMA)
     _expect(capi.ERROR_INVALID_PARAM, plan, mods=8)
-    with pytest.raises(capi.AtbError):                                     # no mask on the split MLA cache
-        capi.PaPlan(capi.make_desc(2, 8, 1, 576, 512, 128, 64, 8, "bf16", sm_count=148, v_row_dim=512, rope_dim=64,
-                                   score_mods=1), lens)
+    mla = lambda mods: capi.PaPlan(capi.make_desc(2, 8, 1, 576, 512, 128, 64, 8, "bf16", sm_count=148, v_row_dim=512,
+                                                  rope_dim=64, score_mods=mods), lens).info.kernel
+    assert mla(capi.SCORE_MASK | capi.SCORE_ROWS) == capi.KERNEL_MLA_TC5    # per-token mask rows on the split MLA cache
+    with pytest.raises(capi.AtbError):                                     # no logN scaling in the MLA kernel
+        mla(capi.SCORE_LOGN)
 
 
 def test_launch_refuses_missing_or_short_mask_before_touching_the_device():

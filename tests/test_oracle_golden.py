@@ -211,3 +211,24 @@ def test_oracle_lse_matches_reference_golden(case):
     assert got.shape == (case.batch, case.heads, 1)
     assert np.all(np.abs(got - ref) <= ulp(case.q_dtype) * np.maximum(np.abs(ref), 1.0))
     assert np.mean(got == ref) > 0.9
+
+
+from golden_cases import GOLDEN_MLA_MTP_CASES, mla_mtp_inputs  # noqa: E402
+
+
+@pytest.mark.parametrize("spec", GOLDEN_MLA_MTP_CASES, ids=lambda s: s["case"].name)
+def test_oracle_mla_parallel_decoding_matches_reference_golden(spec):
+    """MultiLatentAttention with CALC_TYPE_SPEC(_AND_RING): output and log-sum-exp of every query token against the
+    golden of the reference's MTP split-cache kernel test (fp32 arithmetic like the oracle's)."""
+    case = spec["case"]
+    fx = np.load(os.path.join(HERE, f"pa_{case.name}.npz"))
+    d = mla_mtp_inputs(spec)
+    assert _digest(d) == bytes(fx["input_sha256"]).decode(), "seeded inputs changed; regenerate the fixtures"
+    mask = wl.to_f32(d["mask"], case.q_dtype) if spec["mask"] else None
+    out, lse = oracle.paged_attention_spec(d["q"], d["k_cache"], None, d["block_tables"], d["q_lens"], d["context_lens"],
+                                           case.qk_scale, case.q_dtype, mask, mask_rows_are_tokens=True, dv=case.dv,
+                                           want_lse=True)
+    got, ref = wl.to_f32(out, case.q_dtype), wl.to_f32(fx["out"], case.q_dtype)
+    assert np.all(np.abs(got - ref) <= 2 * ulp(case.q_dtype) * np.maximum(np.abs(ref), 2.0 ** -6))
+    gl, rl = wl.to_f32(lse, case.q_dtype), wl.to_f32(fx["lse"], case.q_dtype)
+    assert np.all(np.abs(gl - rl) <= ulp(case.q_dtype) * np.maximum(np.abs(rl), 1.0))

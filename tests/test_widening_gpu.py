@@ -570,3 +570,70 @@ def test_kv_cache_large_rows_keep_the_rest_of_the_cache():
     torch.cuda.synchronize()
     got = past.view(torch.int16).cpu().numpy().view(np.uint16)
     assert np.array_equal(got, want)
+
+
+# ------------------------------------------------------------------ MultiLatentAttention, parallel decoding (MTP)
+
+from golden_cases import GOLDEN_MLA_MTP_CASES, mla_mtp_inputs  # noqa: E402
+
+
+def _run_mla_mtp(case, d, mask_type, ring, mask=None):
+    dt = case.q_dtype
+    T = capi.atb_tensor
+    q, kc = to_dev(d["q"], dt), to_dev(d["k_cache"], dt)
+    q_nope, q_rope = q[..., :512].contiguous(), q[..., 512:].contiguous()
+    ct_kv, k_rope = kc[..., :512].contiguous(), kc[..., 512:].contiguous()
+    bt = torch.from_numpy(d["block_tables"]).cuda()
+    lens_dev, ql_dev = torch.from_numpy(d["context_lens"]).cuda(), torch.from_numpy(d["q_lens"]).cuda()
+    out = torch.full((q.shape[0], case.heads, 512), 7.0, dtype=q.dtype, device="cuda")
+    lse = torch.full((q.shape[0], case.heads, 1), 7.0, dtype=q.dtype, device="cuda")
+    ins = [T(q_nope), T(q_rope), T(ct_kv), T(k_rope), T(bt), T(lens_dev, host=d["context_lens"])]
+    keep = []
+    if mask_type:
+        keep.append(to_dev(mask, dt))
+        ins.append(T(keep[-1]))
+    ins.append(T(ql_dev, host=d["q_lens"]))
+    outs = [T(out)] + ([T(lse)] if ring else [])
+    op = capi.Operation(capi.MultiLatentAttentionParam(headNum=case.heads, kvHeadNum=1, qkScale=case.qk_scale, cacheMode=1,
+                                                       calcType=3 if ring else 1, maskType=mask_type))
+    assert op.input_num == len(ins) and op.output_num == len(outs)
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    ctx = capi.Context(stream.cuda_stream)
+    ws_bytes = op.setup(ins, outs, ctx)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device="cuda")
+    op.execute(ins, outs, ws.data_ptr(), ws_bytes, ctx)
+    torch.cuda.synchronize()
+    return wl.torch_to_host(out, dt), wl.torch_to_host(lse, dt)
+
+
+@pytest.mark.parametrize("spec", GOLDEN_MLA_MTP_CASES, ids=lambda s: s["case"].name)
+def test_mla_parallel_decoding_matches_reference_golden(spec):
+    case = spec["case"]
+    dt = case.q_dtype
+    fx = np.load(os.path.join(GOLDEN_DIR, f"pa_{case.name}.npz"))
+    d = mla_mtp_inputs(spec)
+    got, lse = _run_mla_mtp(case, d, 1 if spec["mask"] else 0, ring=True, mask=d.get("mask"))
+    assert max_abs_err(got, fx["out"], dt) <= tol_for(case)
+    unit = 2.0 ** (-10 if dt == "fp16" else -7)
+    gl, rl = wl.to_f32(lse, dt), wl.to_f32(fx["lse"], dt)
+    assert np.all(np.abs(gl - rl) <= 2 * unit * np.maximum(np.abs(rl), 1.0))
+    if spec["mask"]:
+        # MASK_FREE is the same causal rule without reading a mask: same result up to the masked terms' exp(-10000) = 0
+        free, _ = _run_mla_mtp(case, d, 2, ring=False, mask=np.zeros((8, 128), dtype=d["mask"].dtype))
+        assert max_abs_err(free, fx["out"], dt) <= tol_for(case)
+
+
+def test_mla_parallel_decoding_long_sequences():
+    """128 heads (two CTAs per range), sequences long enough to be split and merged, three tokens per sequence."""
+    case = wl.Case("mla_mtp_long", batch=3, heads=128, kv_heads=1, dk=576, dv=512, q_dtype="bf16", mla=True,
+                   ctx=("list", [3000, 77, 1500]), seed=93)
+    spec = dict(case=case, q_lens=[3, 1, 2], mask="spec")
+    d = mla_mtp_inputs(spec)
+    got, lse = _run_mla_mtp(case, d, 1, ring=True, mask=d["mask"])
+    ref, ref_lse = oracle.paged_attention_spec(d["q"], d["k_cache"], None, d["block_tables"], d["q_lens"], d["context_lens"],
+                                               case.qk_scale, "bf16", wl.to_f32(d["mask"], "bf16"), mask_rows_are_tokens=True,
+                                               dv=512, want_lse=True)
+    assert max_abs_err(got, ref, "bf16") <= tol_for(case)
+    gl, rl = wl.to_f32(lse, "bf16"), wl.to_f32(ref_lse, "bf16")
+    assert np.all(np.abs(gl - rl) <= 2 * 2.0 ** -7 * np.maximum(np.abs(rl), 1.0))
