@@ -189,6 +189,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
                     help="N>1: attention stores into every rank's gathered buffer (p2p) or a separate NCCL all-gather")
+    ap.add_argument("--variant", default="plain", choices=["plain", "alibi", "mtp2"],
+                    help="single-GPU side measurements of the attention kernel's other forms: an alibi mask shared by all "
+                         "sequences; two query tokens per sequence (parallel decoding, causal)")
     ap.add_argument("--op", default="decode", choices=["decode", "block_copy", "paged_cache_load", "norm_rope_reshape"],
                     help="decode (default): the hot path; the others time one cache-management kernel on 1 GPU")
     args = ap.parse_args()
@@ -198,6 +201,9 @@ def main():
     wl, capi = pkg.workloads, pkg.capi
     if args.op != "decode":
         run_cache_op_bench(args, capi)
+        return
+    if args.variant != "plain":
+        run_variant_bench(args, wl, capi)
         return
     case = wl.CONFIGS[args.config]
     if args.impl == "reference":
@@ -388,6 +394,79 @@ def main():
         exchange.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_variant_bench(args, wl, capi):
+    """Attention kernel alone on one GPU in one of its other forms, on the chosen configuration's cache: `alibi` adds
+    a [heads, 1, tokens] mask; `mtp2` runs two query tokens per sequence (the second sees the whole context, the first
+    one token less), planned as one row per token.  KV bytes are counted once per sequence, so `mtp2` shows what the
+    second read of a sequence's cache costs."""
+    import torch
+    case = wl.CONFIGS[args.config]
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    capi.lib()
+    d = wl.make_device_inputs(case, dev)
+    lens = d["context_lens_host"]
+    q_per_seq = 2 if args.variant == "mtp2" else 1
+    tokens = case.batch * q_per_seq
+    q = d["q"].repeat_interleave(q_per_seq, dim=0).contiguous()
+    out = torch.zeros((tokens, case.heads, case.dv), dtype=q.dtype, device=dev)
+    mods, mask, strides, mask_tokens, plan_lens = 0, None, (0, 0), 0, lens
+    if args.variant == "alibi":
+        if case.mla:
+            raise SystemExit("the MLA kernel takes no per-head mask")
+        mask_tokens = int(lens.max())
+        slopes = torch.exp2(-8.0 * (torch.arange(case.heads, device=dev) + 1) / case.heads)
+        mask = (slopes[:, None, None] * (torch.arange(mask_tokens, device=dev) - mask_tokens + 1)[None, None, :]).to(q.dtype)
+        mods, strides = capi.SCORE_MASK, (0, mask_tokens)
+    else:
+        mods = capi.SCORE_ROWS
+        plan_lens = np.stack([np.maximum(lens - 1, 1), lens], axis=1).reshape(-1).astype(np.int32)
+    desc = capi.make_desc(tokens, case.heads, case.kv_heads, case.dk, case.dv, case.block_size, d["num_blocks"],
+                          d["block_tables"].shape[1], case.q_dtype, case.kvd, case.qk_scale,
+                          v_row_dim=case.dk if case.mla else case.dv, score_mods=mods)
+    plan = capi.PaPlan(desc, plan_lens)
+    if args.variant == "mtp2":
+        plan.set_rows(np.repeat(np.arange(case.batch, dtype=np.int32), 2), case.batch)
+    info = plan.info
+    ws = torch.empty(max(int(info.workspace_bytes), 256), dtype=torch.uint8, device=dev)
+    tens = capi.pa_tensors(q, d["k_cache"], d["v_cache"], d["block_tables"], out, d.get("k_descale"), d.get("v_descale"),
+                           mask=mask, mask_strides=strides, mask_tokens=mask_tokens)
+    stream = torch.cuda.Stream()
+    steps = min(args.steps, 500)
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            plan.launch(tens, ws.data_ptr(), ws.numel(), stream.cuda_stream)
+        torch.cuda.synchronize()
+        sampler = ClockSampler(0)
+        sampler.start()
+        time.sleep(0.25)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            plan.launch(tens, ws.data_ptr(), ws.numel(), stream.cuda_stream)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        clocks = sampler.stop()
+    if plan.device_status(ws.data_ptr(), stream.cuda_stream) != 0:
+        raise RuntimeError("device status")
+    peak, peak_kind = measured_peak_gbs()
+    kv = wl.kv_bytes(case, lens)
+    value = kv / (ms * 1e-3) / 1e9
+    print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": steps, "warmup": max(args.warmup, 3),
+                      "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                      "dtype": case.q_dtype if case.kvd != "int8" else "int8/" + case.q_dtype, "data": "synthetic",
+                      "config": {"workload": case.name, "variant": args.variant, "query_tokens": tokens,
+                                 "kv_bytes_per_step": kv, "step": "attention launch alone (with its in-stream plan upload)",
+                                 "l2": "KV cache (%.0f MB) %s the 126 MB L2" % (kv / 1e6, "is larger than" if kv > 2 * L2_BYTES
+                                                                               else "is not well above"),
+                                 "kernel": {1: "generic", 2: "tma_mma", 3: "mla_tc5"}.get(info.kernel, "?"),
+                                 "ctas": info.num_ctas, "partials": info.num_partials},
+                      "gpu_launches": info.kernels_per_launch * steps, "clocks": clocks,
+                      "roofline": {"bound": "hbm", "achieved": value, "peak": peak, "unit": UNIT, "frac": value / peak,
+                                   "peak_kind": "of " + peak_kind, "traffic": None}}))
 
 
 def run_cache_op_bench(args, capi):

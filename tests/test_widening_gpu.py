@@ -637,3 +637,32 @@ def test_mla_parallel_decoding_long_sequences():
     assert max_abs_err(got, ref, "bf16") <= tol_for(case)
     gl, rl = wl.to_f32(lse, "bf16"), wl.to_f32(ref_lse, "bf16")
     assert np.all(np.abs(gl - rl) <= 2 * 2.0 ** -7 * np.maximum(np.abs(rl), 1.0))
+
+
+def test_mla_combined_cache_with_norm_mask():
+    """PagedAttention over the MLA combined cache (mlaVHeadSize) with a plain mask [batch, 1, tokens]: the mask variant
+    of the MLA kernel without per-token rows."""
+    case = [c for c in wl.SMALL_CASES if c.name == "mla_8h_bf16"][0]
+    h = wl.make_host_inputs(case)
+    dt, lens = case.q_dtype, h["context_lens"]
+    tmax = int(lens.max())
+    rng = np.random.default_rng(3)
+    mask = np.where(rng.random((case.batch, 1, tmax)) < 0.3, -10000.0, 0.0).astype(np.float32)
+    mask[:, 0, 0] = 0.0                                                   # every sequence keeps a visible token
+    d = host_inputs_to_device(case, h)
+    T = capi.atb_tensor
+    out = torch.full((case.batch, case.heads, case.dv), 7.0, dtype=d["q"].dtype, device="cuda")
+    lens_dev, mask_dev = torch.from_numpy(lens).cuda(), to_dev(wl.encode(mask, dt), dt)
+    ins = [T(d["q"]), T(d["k_cache"]), T(d["block_tables"]), T(lens_dev, host=lens), T(mask_dev)]
+    outs = [T(out)]
+    op = capi.Operation(capi.PagedAttentionParam(headNum=case.heads, kvHeadNum=1, qkScale=case.qk_scale, mlaVHeadSize=case.dv,
+                                                 maskType=1))
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    ctx = capi.Context(stream.cuda_stream)
+    ws_bytes = op.setup(ins, outs, ctx)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device="cuda")
+    op.execute(ins, outs, ws.data_ptr(), ws_bytes, ctx)
+    torch.cuda.synchronize()
+    ref = oracle.paged_attention(h["q"], h["k_cache"], None, h["block_tables"], lens, case.qk_scale, dt, dv=case.dv, mask=mask)
+    assert max_abs_err(wl.torch_to_host(out, dt), ref, dt) <= tol_for(case)
