@@ -36,7 +36,7 @@ class PaDesc(ctypes.Structure):
                 ("block_size", ctypes.c_int32), ("num_blocks", ctypes.c_int32),
                 ("max_blocks_per_seq", ctypes.c_int32), ("q_dtype", ctypes.c_int32), ("kv_dtype", ctypes.c_int32),
                 ("qk_scale", ctypes.c_float), ("kernel", ctypes.c_int32), ("sm_count", ctypes.c_int32),
-                ("rope_dim", ctypes.c_int32), ("score_mods", ctypes.c_int32), ("kv_layout", ctypes.c_int32), ("reserved", ctypes.c_int32 * 1)]
+                ("rope_dim", ctypes.c_int32), ("score_mods", ctypes.c_int32), ("kv_layout", ctypes.c_int32), ("q_per_seq", ctypes.c_int32)]
 
 
 class PaTensors(ctypes.Structure):
@@ -45,7 +45,8 @@ class PaTensors(ctypes.Structure):
                 ("k_offset", ctypes.c_void_p), ("v_offset", ctypes.c_void_p), ("out", ctypes.c_void_p),
                 ("q_rope", ctypes.c_void_p), ("k_rope_cache", ctypes.c_void_p),
                 ("mask", ctypes.c_void_p), ("mask_batch_stride", ctypes.c_int64), ("mask_head_stride", ctypes.c_int64),
-                ("mask_tokens", ctypes.c_int64), ("logn", ctypes.c_void_p), ("lse_out", ctypes.c_void_p)]
+                ("mask_tokens", ctypes.c_int64), ("mask_q_stride", ctypes.c_int64), ("logn", ctypes.c_void_p),
+                ("lse_out", ctypes.c_void_p)]
 
 
 SCORE_MASK, SCORE_LOGN, SCORE_ROWS = 1, 2, 4
@@ -237,8 +238,9 @@ def _check(rc, what):
 # ------------------------------------------------------------------ kernel level
 
 def make_desc(batch, num_heads, kv_heads, dk, dv, block_size, num_blocks, max_blocks, q_dtype, kv_dtype=None,
-              qk_scale=1.0, v_row_dim=None, kernel=KERNEL_AUTO, sm_count=0, rope_dim=0, score_mods=0, kv_layout=0):
+              qk_scale=1.0, v_row_dim=None, kernel=KERNEL_AUTO, sm_count=0, rope_dim=0, score_mods=0, kv_layout=0, q_per_seq=0):
     d = PaDesc()
+    d.q_per_seq = q_per_seq
     d.rope_dim, d.score_mods, d.kv_layout = rope_dim, score_mods, kv_layout
     d.batch, d.num_heads, d.kv_heads = batch, num_heads, kv_heads
     d.head_dim_k, d.head_dim_v, d.v_row_dim = dk, dv, (v_row_dim or dv)
@@ -343,10 +345,11 @@ def torch_stream_ptr():
 
 
 def pa_tensors(q, k_cache, v_cache, block_tables, out, k_descale=None, v_descale=None, k_offset=None, v_offset=None,
-               q_rope=None, k_rope_cache=None, mask=None, mask_strides=(0, 0), mask_tokens=0, logn=None, lse_out=None):
+               q_rope=None, k_rope_cache=None, mask=None, mask_strides=(0, 0), mask_tokens=0, logn=None, lse_out=None, mask_q_stride=0):
     """`mask_strides` = (batch, head) element strides of the additive mask, `mask_tokens` its last dimension."""
     t = PaTensors()
     t.mask, t.logn, t.lse_out = _ptr(mask), _ptr(logn), _ptr(lse_out)
+    t.mask_q_stride = int(mask_q_stride)
     t.mask_batch_stride, t.mask_head_stride, t.mask_tokens = int(mask_strides[0]), int(mask_strides[1]), int(mask_tokens)
     t.q_rope, t.k_rope_cache = _ptr(q_rope), _ptr(k_rope_cache)
     t.q, t.k_cache = _ptr(q), _ptr(k_cache)

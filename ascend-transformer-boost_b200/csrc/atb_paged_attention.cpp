@@ -487,6 +487,51 @@ protected:
                 ATB_B200_LOG(ERROR, "PagedAttention: the sum of qSeqLens should equal the query tokens");
                 return ERROR_INVALID_PARAM;
             }
+            // The same number n of query tokens for every sequence (MTP): one planned row per SEQUENCE whose CTA
+            // columns are the n x heads-per-kv-head (token, head) pairs, so the cache is read once.  Tried first; a shape
+            // the fused form does not cover (more than 8 pairs, head size, int8) falls back to one row per token.
+            int32_t n = batch > 0 ? qLens[0] : 0;
+            for (int64_t b = 1; b < batch; ++b) {
+                n = qLens[b] == n ? n : 0;
+            }
+            fusedTokens_ = 0;
+            if (n > 1 && !fusedRefused_ && std::getenv("ATB_B200_SPEC_EXPAND") == nullptr) {
+                atb_b200_pa_desc f = d;
+                f.batch = static_cast<int32_t>(batch);
+                f.num_heads = n * param_.headNum;
+                f.q_per_seq = n;
+                f.score_mods = ATB_B200_SCORE_MASK | (normMask ? ATB_B200_SCORE_ROWS : 0);
+                const int64_t maskLen = vp.inTensors.at(MaskPos()).desc.shape.dims[1];
+                for (int64_t b = 0; b < batch; ++b) {
+                    if (lens[b] > maskLen) {
+                        ATB_B200_LOG(ERROR, "PagedAttention: the mask is shorter than a sequence's context");
+                        return ERROR_INVALID_TENSOR_DIM;
+                    }
+                }
+                int rc = MakePlan(f, lens);
+                if (rc == 0 && normMask) {
+                    // row of a sequence's first query token in the square mask; block-table rows are the identity
+                    btRows_.resize(batch);
+                    maskRows_.resize(batch);
+                    for (int64_t b = 0; b < batch; ++b) {
+                        btRows_[b] = static_cast<int32_t>(b);
+                        maskRows_[b] = lens[b] - n;
+                    }
+                    rc = atb_b200_pa_plan_set_rows(plan_, btRows_.data(), static_cast<int32_t>(batch), maskRows_.data(),
+                                                   vp.inTensors.at(MaskPos()).desc.shape.dims[0]);
+                }
+                if (rc == 0) {
+                    fusedTokens_ = n;
+                    atb_b200_pa_plan_info info{};
+                    atb_b200_pa_plan_get_info(plan_, &info);
+                    workspaceSize = info.workspace_bytes + 256;
+                    return NO_ERROR;
+                }
+                if (rc != ERROR_INVALID_TENSOR_DIM) {
+                    return rc;
+                }
+                fusedRefused_ = true; // these shapes have no fused form: do not try again on later Setups
+            }
             lens = effectiveLens_.data();
         }
         if (HasMask()) {
@@ -518,17 +563,7 @@ protected:
             }
             lens = effectiveLens_.data();
         }
-        int rc;
-        if (plan_ != nullptr && SameDesc(d)) {
-            rc = atb_b200_pa_plan_update(plan_, lens);
-        } else {
-            if (plan_ != nullptr) {
-                atb_b200_pa_plan_destroy(plan_);
-                plan_ = nullptr;
-            }
-            rc = atb_b200_pa_plan_create(&d, lens, &plan_);
-            desc_ = d;
-        }
+        int rc = MakePlan(d, lens);
         if (rc != 0) {
             return rc;
         }
@@ -585,6 +620,14 @@ protected:
             t.mask = m.deviceData;
             (void)MaskLayout(m.desc.shape, vp.inTensors.at(0).desc.shape.dims[0], &t.mask_batch_stride,
                              &t.mask_head_stride, &t.mask_tokens);
+            if (fusedTokens_ > 1) {
+                // fused parallel decoding: consecutive tokens of a sequence are consecutive mask rows; with the spec mask
+                // a sequence's first row is sequence x tokens-per-sequence (the norm mask's comes from the plan's rows)
+                t.mask_q_stride = t.mask_tokens;
+                if (param_.maskType == Param::MASK_TYPE_SPEC) {
+                    t.mask_batch_stride = fusedTokens_ * t.mask_tokens;
+                }
+            }
         }
         if (param_.scaleType == Param::SCALE_TYPE_LOGN) {
             t.logn = static_cast<const float *>(vp.inTensors.at(vp.inTensors.size() - 1).deviceData);
@@ -601,6 +644,20 @@ protected:
     }
 
 private:
+    // Re-plans in place when only the lengths changed, else builds a new plan for `d`.
+    int MakePlan(const atb_b200_pa_desc &d, const int32_t *lens)
+    {
+        if (plan_ != nullptr && SameDesc(d)) {
+            return atb_b200_pa_plan_update(plan_, lens);
+        }
+        if (plan_ != nullptr) {
+            atb_b200_pa_plan_destroy(plan_);
+            plan_ = nullptr;
+        }
+        desc_ = d;
+        return atb_b200_pa_plan_create(&d, lens, &plan_);
+    }
+
     bool SameDesc(const atb_b200_pa_desc &d) const
     {
         return d.batch == desc_.batch && d.num_heads == desc_.num_heads && d.kv_heads == desc_.kv_heads &&
@@ -608,7 +665,7 @@ private:
                d.block_size == desc_.block_size && d.num_blocks == desc_.num_blocks &&
                d.max_blocks_per_seq == desc_.max_blocks_per_seq && d.q_dtype == desc_.q_dtype &&
                d.kv_dtype == desc_.kv_dtype && d.qk_scale == desc_.qk_scale && d.kernel == desc_.kernel &&
-               d.score_mods == desc_.score_mods && d.kv_layout == desc_.kv_layout;
+               d.score_mods == desc_.score_mods && d.kv_layout == desc_.kv_layout && d.q_per_seq == desc_.q_per_seq;
     }
     // fp32 scales are used in place; the int64-packed and fp16 encodings are converted once per
     // launch into a small device buffer owned by the operation.
@@ -620,6 +677,8 @@ private:
     atb_b200_pa_plan *plan_ = nullptr;
     // contextLens with the sequences batchRunStatus switches off set to 0; with CALC_TYPE_SPEC one entry per query token
     std::vector<int32_t> effectiveLens_;
+    bool fusedRefused_ = false;
+    int32_t fusedTokens_ = 0;                // CALC_TYPE_SPEC planned per sequence: query tokens per sequence (else 0)
     std::vector<int32_t> btRows_, maskRows_; // CALC_TYPE_SPEC: block-table row and mask row of every query token
     atb_b200_pa_desc desc_{};
     void *scratch_[2] = {nullptr, nullptr};

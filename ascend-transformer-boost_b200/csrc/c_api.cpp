@@ -369,7 +369,7 @@ int atb_b200_pa_launch(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, voi
 int atb_b200_pa_launch_gathered(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, const atb_b200_pa_peers *peers,
                                 void *workspace, uint64_t workspace_bytes, void *stream_v)
 {
-    if (plan == nullptr || peers == nullptr || peers->world < 1 || peers->world > 8 || peers->rank < 0 ||
+    if (plan == nullptr || peers == nullptr || plan->hp.desc.q_per_seq > 1 || peers->world < 1 || peers->world > 8 || peers->rank < 0 ||
         peers->rank >= peers->world || plan->hp.kernel != ATB_B200_KERNEL_TMA_MMA ||
         peers->head_offset < 0 || peers->head_offset + plan->hp.desc.num_heads > peers->total_heads) {
         return kErrInvalidParam;
@@ -452,9 +452,11 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
         a.mask = t->mask;
         a.mask_bs = t->mask_batch_stride;
         a.mask_hs = t->mask_head_stride;
+        a.mask_qs = d.q_per_seq > 1 ? t->mask_q_stride : 0;
     }
     a.logn = (d.score_mods & ATB_B200_SCORE_LOGN) != 0 ? t->logn : nullptr;
     a.kv_bnsd = d.kv_layout == ATB_B200_KV_BNSD ? 1 : 0;
+    a.q_per_seq = d.q_per_seq > 1 ? d.q_per_seq : 1;
     if (t->lse_out != nullptr && h.kernel != ATB_B200_KERNEL_MLA_TC5) {
         return kErrInvalidParam; // only the MLA kernel writes the log-sum-exp
     }

@@ -74,7 +74,8 @@ struct PaArgs {
     // additive mask in the query dtype (score(b, h, t) += mask[b * mask_bs + h * mask_hs + t]) and per-sequence
     // factors of the scale; both null on the plain path
     const void *mask;
-    int64_t mask_bs, mask_hs;
+    int64_t mask_bs, mask_hs, mask_qs; // mask_qs: between the rows of a sequence's consecutive query tokens
+    int32_t q_per_seq;                 // > 1: a CTA's columns are (query token, head) pairs of one sequence
     const float *logn;
     // parallel decoding: the block-table row and the mask row of every query token (null: the token's own index)
     const int32_t *bt_rows;

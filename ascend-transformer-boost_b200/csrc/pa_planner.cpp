@@ -39,10 +39,9 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
         d.max_blocks_per_seq <= 0) {
         return kErrInvalidParam;
     }
-    for (int r : d.reserved) {
-        if (r != 0) {
-            return kErrInvalidParam;
-        }
+    if (d.q_per_seq < 0 || (d.q_per_seq > 1 && (d.num_heads % d.q_per_seq != 0 ||
+                                                (d.num_heads / d.q_per_seq) % d.kv_heads != 0))) {
+        return kErrInvalidParam;
     }
     const int group = d.num_heads / d.kv_heads;
     const bool tma_ok = pa_tma_mma_supported(d.head_dim_k, d.head_dim_v, d.v_row_dim, d.block_size, group, d.q_dtype,
@@ -88,6 +87,15 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
         if (kernel == ATB_B200_KERNEL_MLA_TC5) {
             return kErrInvalidTensorDim;
         }
+    }
+    if (d.q_per_seq > 1) {
+        // (token, head) pairs as the columns of one CTA: the fp16 / bf16 D = 128 kernel only, at most 8 pairs per kv head
+        // (which is what its head limit already says about num_heads / kv_heads)
+        if (!tma_ok || d.kv_dtype == kInt8 || d.rope_dim != 0 ||
+            (kernel != ATB_B200_KERNEL_AUTO && kernel != ATB_B200_KERNEL_TMA_MMA)) {
+            return kErrInvalidTensorDim;
+        }
+        kernel = ATB_B200_KERNEL_TMA_MMA;
     }
     if (kernel == ATB_B200_KERNEL_AUTO) {
         kernel = tma_ok ? ATB_B200_KERNEL_TMA_MMA : (mla_ok ? ATB_B200_KERNEL_MLA_TC5 : ATB_B200_KERNEL_GENERIC);

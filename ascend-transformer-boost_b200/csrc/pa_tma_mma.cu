@@ -157,13 +157,19 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     const T *q = static_cast<const T *>(a.q);
     const uint32_t stages_u32 = smem_u32(stages);
     const int group = a.group;
+    // Column x of this CTA (0..7) -> head index in the [.., num_heads, 128] tensors.  With q_per_seq query tokens per
+    // sequence those tensors hold q_per_seq x real-heads rows per sequence and a column is a (token, head) pair:
+    // token x / gr, head kvh * gr + x % gr, gr = real heads per kv head.
+    const int qps = kMods ? a.q_per_seq : 1;
+    const int gr = group / qps, heads_real = a.num_heads / qps;
+    auto head_of = [&](int x) { return qps > 1 ? (x / gr) * heads_real + kvh * gr + x % gr : kvh * group + x; };
 
     for (int it = item_begin; it < item_end; ++it) {
         const PaItem item = a.plan.items[it];
         uint32_t qf[8][2];
         {
             const bool valid = g < group;
-            const T *qp = q + ((int64_t)item.seq * a.num_heads + kvh * group + (valid ? g : 0)) * 128;
+            const T *qp = q + ((int64_t)item.seq * a.num_heads + head_of(valid ? g : 0)) * 128;
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
                 qf[ks][0] = valid ? *reinterpret_cast<const uint32_t *>(qp + ks * 16 + 2 * c) : 0u;
@@ -186,8 +192,9 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             if (a.mask != nullptr) {
                 const T *mb = static_cast<const T *>(a.mask) +
                               (int64_t)(a.mask_rows != nullptr ? a.mask_rows[item.seq] : item.seq) * a.mask_bs;
-                mrow0 = mb + (int64_t)(kvh * group + min(2 * c, group - 1)) * a.mask_hs;     // padding heads read
-                mrow1 = mb + (int64_t)(kvh * group + min(2 * c + 1, group - 1)) * a.mask_hs; // a real head's row
+                const int x0 = min(2 * c, group - 1), x1 = min(2 * c + 1, group - 1); // padding columns read a real one's row
+                mrow0 = mb + (int64_t)(x0 / gr) * a.mask_qs + (int64_t)(kvh * gr + x0 % gr) * a.mask_hs;
+                mrow1 = mb + (int64_t)(x1 / gr) * a.mask_qs + (int64_t)(kvh * gr + x1 % gr) * a.mask_hs;
             }
         }
         const int n_st = (item.tok_end - item.tok_begin + kStageTokens - 1) / kStageTokens;
@@ -399,7 +406,7 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 const float *src = xbuf1 + hl * kFinalStride + d0;
                 const float4 va = *reinterpret_cast<const float4 *>(src);
                 const float4 vb = *reinterpret_cast<const float4 *>(src + 4);
-                const int h = kvh * group + hl;
+                const int h = head_of(hl);
                 if (item.slot < 0) {
                     uint4 pk;
                     pk.x = Elem<T>::pack2(va.x, va.y);
@@ -443,7 +450,7 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 const int hl = threadIdx.x >> 4;
                 const int d0 = (threadIdx.x & 15) * 8;
                 if (hl < group) {
-                    const int h = kvh * group + hl;
+                    const int h = head_of(hl);
                     const int pbase = a.plan.seq_part_base[item.seq];
                     const float *lse = a.plan.part_lse + (int64_t)pbase * a.num_heads + h;
                     float mx = -INFINITY;
@@ -541,7 +548,7 @@ bool encode_cache_map(CUtensorMap *map, const void *base, int elem_dtype, int kv
 
 template <typename T> cudaError_t launch_typed(const PaArgs &args, const CUtensorMap &km, const CUtensorMap &vm, cudaStream_t s)
 {
-    const bool mods = args.mask != nullptr || args.logn != nullptr || args.bt_rows != nullptr;
+    const bool mods = args.mask != nullptr || args.logn != nullptr || args.bt_rows != nullptr || args.q_per_seq > 1;
     auto kern = mods ? pa_tma_mma_kernel<T, true> : pa_tma_mma_kernel<T, false>;
     static bool configured_plain[64] = {}, configured_mods[64] = {};
     bool *configured = mods ? configured_mods : configured_plain;

@@ -189,9 +189,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
                     help="N>1: attention stores into every rank's gathered buffer (p2p) or a separate NCCL all-gather")
-    ap.add_argument("--variant", default="plain", choices=["plain", "alibi", "mtp2"],
+    ap.add_argument("--variant", default="plain", choices=["plain", "alibi", "mtp2", "mtp2_rows"],
                     help="single-GPU side measurements of the attention kernel's other forms: an alibi mask shared by all "
-                         "sequences; two query tokens per sequence (parallel decoding, causal)")
+                         "sequences; two query tokens per sequence (parallel decoding, causal) planned per sequence "
+                         "(mtp2: one read of the cache) or per token (mtp2_rows)")
     ap.add_argument("--op", default="decode", choices=["decode", "block_copy", "paged_cache_load", "norm_rope_reshape"],
                     help="decode (default): the hot path; the others time one cache-management kernel on 1 GPU")
     args = ap.parse_args()
@@ -398,9 +399,10 @@ def main():
 
 def run_variant_bench(args, wl, capi):
     """Attention kernel alone on one GPU in one of its other forms, on the chosen configuration's cache: `alibi` adds
-    a [heads, 1, tokens] mask; `mtp2` runs two query tokens per sequence (the second sees the whole context, the first
-    one token less), planned as one row per token.  KV bytes are counted once per sequence, so `mtp2` shows what the
-    second read of a sequence's cache costs."""
+    a [heads, 1, tokens] mask; `mtp2` / `mtp2_rows` run two query tokens per sequence (the second sees the whole context,
+    the first one token less): `mtp2` as one planned row per sequence whose CTA columns are the (token, head) pairs,
+    with the causal rule given as a [tokens, max_ctx] mask; `mtp2_rows` as one planned row per token (the form the MLA
+    kernel and ragged token counts use).  KV bytes are counted once per sequence."""
     import torch
     case = wl.CONFIGS[args.config]
     dev = torch.device("cuda", 0)
@@ -408,11 +410,11 @@ def run_variant_bench(args, wl, capi):
     capi.lib()
     d = wl.make_device_inputs(case, dev)
     lens = d["context_lens_host"]
-    q_per_seq = 2 if args.variant == "mtp2" else 1
+    q_per_seq = 2 if args.variant.startswith("mtp2") else 1
     tokens = case.batch * q_per_seq
     q = d["q"].repeat_interleave(q_per_seq, dim=0).contiguous()
     out = torch.zeros((tokens, case.heads, case.dv), dtype=q.dtype, device=dev)
-    mods, mask, strides, mask_tokens, plan_lens = 0, None, (0, 0), 0, lens
+    mods, mask, strides, mask_tokens, plan_lens, fused, planned_rows, heads = 0, None, (0, 0), 0, lens, 0, tokens, case.heads
     if args.variant == "alibi":
         if case.mla:
             raise SystemExit("the MLA kernel takes no per-head mask")
@@ -420,19 +422,27 @@ def run_variant_bench(args, wl, capi):
         slopes = torch.exp2(-8.0 * (torch.arange(case.heads, device=dev) + 1) / case.heads)
         mask = (slopes[:, None, None] * (torch.arange(mask_tokens, device=dev) - mask_tokens + 1)[None, None, :]).to(q.dtype)
         mods, strides = capi.SCORE_MASK, (0, mask_tokens)
+    elif args.variant == "mtp2":
+        if case.mla:
+            raise SystemExit("the MLA kernel plans parallel decoding per token: use --variant mtp2_rows")
+        mask_tokens = int(lens.max())
+        mask = torch.zeros((tokens, mask_tokens), dtype=q.dtype, device=dev)
+        first = torch.arange(case.batch, device=dev) * 2                 # a sequence's first token does not see the last key
+        mask[first, torch.from_numpy(lens.astype(np.int64) - 1).to(dev)] = -10000.0
+        mods, strides, fused, planned_rows, heads = capi.SCORE_MASK, (2 * mask_tokens, 0), 2, case.batch, 2 * case.heads
     else:
         mods = capi.SCORE_ROWS
         plan_lens = np.stack([np.maximum(lens - 1, 1), lens], axis=1).reshape(-1).astype(np.int32)
-    desc = capi.make_desc(tokens, case.heads, case.kv_heads, case.dk, case.dv, case.block_size, d["num_blocks"],
+    desc = capi.make_desc(planned_rows, heads, case.kv_heads, case.dk, case.dv, case.block_size, d["num_blocks"],
                           d["block_tables"].shape[1], case.q_dtype, case.kvd, case.qk_scale,
-                          v_row_dim=case.dk if case.mla else case.dv, score_mods=mods)
+                          v_row_dim=case.dk if case.mla else case.dv, score_mods=mods, q_per_seq=fused)
     plan = capi.PaPlan(desc, plan_lens)
-    if args.variant == "mtp2":
+    if args.variant == "mtp2_rows":
         plan.set_rows(np.repeat(np.arange(case.batch, dtype=np.int32), 2), case.batch)
     info = plan.info
     ws = torch.empty(max(int(info.workspace_bytes), 256), dtype=torch.uint8, device=dev)
     tens = capi.pa_tensors(q, d["k_cache"], d["v_cache"], d["block_tables"], out, d.get("k_descale"), d.get("v_descale"),
-                           mask=mask, mask_strides=strides, mask_tokens=mask_tokens)
+                           mask=mask, mask_strides=strides, mask_tokens=mask_tokens, mask_q_stride=mask_tokens if fused else 0)
     stream = torch.cuda.Stream()
     steps = min(args.steps, 500)
     with torch.cuda.stream(stream):

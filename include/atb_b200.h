@@ -62,7 +62,12 @@ typedef struct atb_b200_pa_desc {
     int32_t kv_layout;      /* ATB_B200_KV_BSND (0): caches [num_blocks, block_size, kv_heads, dim];
                                ATB_B200_KV_BNSD (1): [num_blocks, kv_heads, block_size, dim] (inputLayout TYPE_BNSD of
                                the reference; fp16 / bf16 caches, no split MLA cache) */
-    int32_t reserved[1];    /* must be 0 */
+    int32_t q_per_seq;      /* 0 / 1: one query token per planned row.  n > 1 (parallel decoding with the same number of
+                               query tokens for every sequence): batch = sequences, q and out hold n consecutive tokens
+                               per sequence ([batch * n, heads, dim]), num_heads = n x the real head count, and one CTA
+                               serves the n x heads-per-kv-head (token, head) pairs of a kv head from one read of the
+                               cache (at most 8 pairs; fp16 / bf16, head_dim 128).  A mask is indexed per (sequence,
+                               token): see mask_q_stride */
 } atb_b200_pa_desc;
 
 enum { ATB_B200_KV_BSND = 0, ATB_B200_KV_BNSD = 1 };
@@ -97,6 +102,9 @@ typedef struct atb_b200_pa_tensors {
     int64_t mask_batch_stride;
     int64_t mask_head_stride;
     int64_t mask_tokens;
+    int64_t mask_q_stride;      /* q_per_seq > 1 only: elements between the mask rows of consecutive query tokens of a
+                                   sequence; token j of sequence b reads mask[row(b) * mask_batch_stride + j *
+                                   mask_q_stride + h * mask_head_stride + t], row(b) = b or mask_rows[b] */
     const float *logn;          /* ATB_B200_SCORE_LOGN only: [batch] fp32 */
     void *lse_out;              /* optional, MLA kernel only: [batch, num_heads] in q_dtype, the natural-log
                                    log-sum-exp of the scaled scores of every (token, head) (the second output of

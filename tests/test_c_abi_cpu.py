@@ -114,7 +114,7 @@ def test_plan_rejects_bad_arguments():
         capi.PaPlan(d, lens)
     assert e.value.code == capi.ERROR_INVALID_PARAM
     d = capi.make_desc(case.batch, 32, 8, 128, 128, 128, 1000, 32, "bf16", sm_count=148)
-    d.reserved[0] = 7
+    d.q_per_seq = -1
     with pytest.raises(capi.AtbError):
         capi.PaPlan(d, lens)
     # a kernel that does not support the shape
@@ -592,3 +592,36 @@ def test_plan_rows_contract():
     _expect(capi.ERROR_INVALID_PARAM, plain.set_rows, [0, 0, 0, 1, 1], 2)                          # not a SCORE_ROWS plan
     plan.update(lens + 1)                                                                          # rows survive a re-plan
     assert plan.info.plan_bytes > plain.info.plan_bytes - 256
+
+
+def test_fused_parallel_decoding_plan_rules(monkeypatch):
+    """q_per_seq > 1: one planned row per sequence whose CTA columns are (token, head) pairs - the D = 128 fp16 / bf16
+    kernel only, at most 8 pairs per kv head."""
+    lens = np.array([100, 900], dtype=np.int32)
+
+    def plan(heads=16, kvh=4, n=2, dk=128, kv="bf16", kernel=0):
+        d = capi.make_desc(2, heads, kvh, dk, dk, 128, 64, 8, "bf16", kv, sm_count=148, score_mods=capi.SCORE_MASK,
+                           q_per_seq=n, kernel=kernel)
+        return capi.PaPlan(d, lens).info.kernel
+    assert plan() == capi.KERNEL_TMA_MMA                                   # 2 tokens x 2 heads per kv head
+    assert plan(heads=32, kvh=4, n=2) == capi.KERNEL_TMA_MMA               # 8 pairs
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, heads=48, kvh=4, n=3)     # 12 pairs
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, dk=64)
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, kv="int8")
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, kernel=capi.KERNEL_GENERIC)
+    _expect(capi.ERROR_INVALID_PARAM, plan, heads=18, kvh=2, n=4)          # heads not a multiple of the token count
+    # the operator plans uniform qSeqLens this way and falls back to one row per token where it cannot
+    monkeypatch.setenv("ATB_B200_SM_COUNT", "148")
+    T = capi.atb_tensor
+    f16, i32, fake = capi.ACL_FLOAT16, capi.ACL_INT32, 0x1000
+    ctx = capi.Context()
+    qlens = np.array([2, 2], dtype=np.int32)
+    for d, expect_ws in ((128, None), (96, None)):
+        ins = [T(dtype=f16, shape=(4, 8, d), device_ptr=fake), T(dtype=f16, shape=(16, 128, 2, d), device_ptr=fake),
+               T(dtype=f16, shape=(16, 128, 2, d), device_ptr=fake), T(dtype=i32, shape=(2, 8), device_ptr=fake),
+               T(dtype=i32, shape=(2,), device_ptr=fake, host=lens), T(dtype=f16, shape=(4, 900), device_ptr=fake),
+               T(dtype=i32, shape=(2,), device_ptr=fake, host=qlens)]
+        outs = [T(dtype=f16, shape=(4, 8, d), device_ptr=fake)]
+        op = capi.Operation(_pa_param(calcType=1, maskType=3))
+        assert op.setup(ins, outs, ctx) >= 256
+        assert op.setup(ins, outs, ctx) >= 256                              # second Setup re-plans in place

@@ -666,3 +666,29 @@ def test_mla_combined_cache_with_norm_mask():
     torch.cuda.synchronize()
     ref = oracle.paged_attention(h["q"], h["k_cache"], None, h["block_tables"], lens, case.qk_scale, dt, dv=case.dv, mask=mask)
     assert max_abs_err(wl.torch_to_host(out, dt), ref, dt) <= tol_for(case)
+
+
+# ------------------------------------------------------------------ parallel decoding planned per sequence (uniform q_len)
+
+@pytest.mark.parametrize("mask_kind", ["spec", "norm"])
+@pytest.mark.parametrize("heads,kv_heads,q_len,dtype", [(8, 2, 2, "bf16"), (8, 4, 4, "fp16"), (4, 4, 3, "fp16"), (16, 2, 1, "bf16")])
+def test_parallel_decoding_same_token_count_per_sequence(heads, kv_heads, q_len, dtype, mask_kind, monkeypatch):
+    """Every sequence has q_len query tokens: the operator plans one row per sequence whose CTA columns are the (token,
+    head) pairs (the cache is read once) when q_len x heads-per-kv-head <= 8, else one row per token.  Both must give
+    the oracle's result, and the per-sequence form the same as the per-token form (forced through the environment)."""
+    case = wl.Case(f"mtp_{heads}_{kv_heads}_{q_len}_{dtype}", batch=5, heads=heads, kv_heads=kv_heads, q_dtype=dtype,
+                   ctx=("list", [3000, 37, 640, 1, 129 if q_len < 4 else 200]), seed=97)
+    spec = dict(case=case, q_lens=[q_len] * 5, mask=mask_kind)
+    d = spec_inputs(spec)
+    lens = d["context_lens"].copy()
+    if mask_kind == "norm":
+        lens = np.maximum(lens, q_len).astype(np.int32)                   # the square mask needs ctx >= q_len
+        d["context_lens"] = lens
+    ref = oracle.paged_attention_spec(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], d["q_lens"], lens, case.qk_scale,
+                                      dtype, wl.to_f32(d["mask"], dtype), mask_rows_are_tokens=mask_kind == "spec")
+    got = _run_spec_op(case, d, mask_kind, d["q_lens"], lens)
+    assert max_abs_err(got, ref, dtype) <= tol_for(case)
+    monkeypatch.setenv("ATB_B200_SPEC_EXPAND", "1")
+    per_token = _run_spec_op(case, d, mask_kind, d["q_lens"], lens)
+    assert max_abs_err(per_token, ref, dtype) <= tol_for(case)
+    assert max_abs_err(got, per_token, dtype) <= tol_for(case)
