@@ -49,7 +49,7 @@ class PaTensors(ctypes.Structure):
                 ("lse_out", ctypes.c_void_p)]
 
 
-SCORE_MASK, SCORE_LOGN, SCORE_ROWS = 1, 2, 4
+SCORE_MASK, SCORE_LOGN, SCORE_ROWS, SCORE_CAUSAL = 1, 2, 4, 8
 
 
 class PaPlanInfo(ctypes.Structure):

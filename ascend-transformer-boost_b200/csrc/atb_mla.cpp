@@ -237,8 +237,22 @@ protected:
                 ATB_B200_LOG(ERROR, "MultiLatentAttention: the sum of qSeqlen should equal the query tokens");
                 return ERROR_INVALID_PARAM;
             }
-            lens = tokenLens_.data();
-            d.score_mods = ATB_B200_SCORE_ROWS | (specMask ? ATB_B200_SCORE_MASK : 0);
+            // The same number n of query tokens for every sequence (the usual MTP batch): one planned row per SEQUENCE,
+            // the kernel's rows are the n x heads (token, head) pairs and the cache is read once per 64 of them.
+            int32_t n = batch > 0 ? qLens[0] : 0;
+            for (int64_t b = 1; b < batch; ++b) {
+                n = qLens[b] == n ? n : 0;
+            }
+            fusedTokens_ = (n > 1 && std::getenv("ATB_B200_SPEC_EXPAND") == nullptr) ? n : 0;
+            if (fusedTokens_ > 1) {
+                d.batch = static_cast<int32_t>(batch);
+                d.num_heads = n * param_.headNum;
+                d.q_per_seq = n;
+                d.score_mods = (specMask ? ATB_B200_SCORE_MASK : 0) | (causal ? ATB_B200_SCORE_CAUSAL : 0);
+            } else {
+                lens = tokenLens_.data();
+                d.score_mods = ATB_B200_SCORE_ROWS | (specMask ? ATB_B200_SCORE_MASK : 0);
+            }
             if (specMask) {
                 const int64_t maskLen = vp.inTensors.at(MaskPos()).desc.shape.dims[1];
                 for (int32_t t = 0; t < d.batch; ++t) {
@@ -252,7 +266,7 @@ protected:
         int rc;
         if (plan_ != nullptr && d.batch == desc_.batch && d.num_blocks == desc_.num_blocks &&
             d.max_blocks_per_seq == desc_.max_blocks_per_seq && d.q_dtype == desc_.q_dtype && d.sm_count == desc_.sm_count &&
-            d.score_mods == desc_.score_mods) {
+            d.score_mods == desc_.score_mods && d.num_heads == desc_.num_heads && d.q_per_seq == desc_.q_per_seq) {
             rc = atb_b200_pa_plan_update(plan_, lens);
         } else {
             if (plan_ != nullptr) {
@@ -265,7 +279,7 @@ protected:
         if (rc != 0) {
             return rc;
         }
-        if (Spec()) {
+        if (Spec() && fusedTokens_ <= 1) {
             rc = atb_b200_pa_plan_set_rows(plan_, btRows_.data(), static_cast<int32_t>(cl.desc.shape.dims[0]),
                                            specMask ? maskRows_.data() : nullptr,
                                            specMask ? vp.inTensors.at(MaskPos()).desc.shape.dims[0] : 0);
@@ -294,7 +308,9 @@ protected:
         if (Spec() && param_.maskType == Param::MASK_TYPE_SPEC) {
             const Tensor &m = vp.inTensors.at(MaskPos());
             t.mask = m.deviceData;
-            t.mask_batch_stride = m.desc.shape.dims[1];
+            // one mask row per query token; planned per sequence, a sequence's rows are fusedTokens_ consecutive ones
+            t.mask_batch_stride = m.desc.shape.dims[1] * (fusedTokens_ > 1 ? fusedTokens_ : 1);
+            t.mask_q_stride = fusedTokens_ > 1 ? m.desc.shape.dims[1] : 0;
             t.mask_head_stride = 0;
             t.mask_tokens = m.desc.shape.dims[1];
             if (t.mask == nullptr) {
@@ -323,6 +339,7 @@ private:
     atb_b200_pa_plan *plan_ = nullptr;
     atb_b200_pa_desc desc_{};
     std::vector<int32_t> tokenLens_, btRows_, maskRows_; // CALC_TYPE_SPEC: one entry per query token
+    int32_t fusedTokens_ = 0; // CALC_TYPE_SPEC planned per sequence: query tokens per sequence (else 0)
 };
 
 } // namespace

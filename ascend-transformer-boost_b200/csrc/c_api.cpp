@@ -457,6 +457,7 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
     a.logn = (d.score_mods & ATB_B200_SCORE_LOGN) != 0 ? t->logn : nullptr;
     a.kv_bnsd = d.kv_layout == ATB_B200_KV_BNSD ? 1 : 0;
     a.q_per_seq = d.q_per_seq > 1 ? d.q_per_seq : 1;
+    a.seq_lens = (d.score_mods & ATB_B200_SCORE_CAUSAL) != 0 ? reinterpret_cast<const int32_t *>(blob + h.off_lens) : nullptr;
     if (t->lse_out != nullptr && h.kernel != ATB_B200_KERNEL_MLA_TC5) {
         return kErrInvalidParam; // only the MLA kernel writes the log-sum-exp
     }

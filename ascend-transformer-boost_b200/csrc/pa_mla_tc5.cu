@@ -142,8 +142,10 @@ __host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t b_mn_ma
 
 enum Bar { kQFull = 0, kQEmpty, kKvFull0, kKvFull1, kKvFull2, kKvEmpty0, kKvEmpty1, kKvEmpty2, kSFull0, kSFull1, kSEmpty0, kSEmpty1, kPFull, kPvDone };
 
-// kMask: the variant that adds a per-token mask row to the scores (parallel decoding with MASK_TYPE_SPEC); the plain
-// variant carries none of that code.  Both follow bt_rows when the plan gives every query token its block-table row.
+// kMask: the variant for parallel decoding with a mask or the causal rule: it adds the query token's mask row to the
+// scores (MASK_TYPE_SPEC) and / or hides the tokens behind the query token (q_per_seq > 1: the rows of a CTA are (token,
+// head) pairs, row r belongs to query token (head0 + r) / real heads).  The plain variant carries none of that code.
+// Both follow bt_rows when the plan gives every query token its block-table row.
 template <typename T, bool kMask>
 __global__ void __launch_bounds__(kThreads, 1)
 pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap rmap, const PaArgs a)
@@ -379,10 +381,18 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 }
             }
             float m_used = -INFINITY, l = 0.f;
-            const T *mrow = nullptr; // this token's mask row, at the first token of the range
+            const T *mrow = nullptr; // this row's mask row, at the first token of the range
+            int row_limit = 0x7fffffff; // first token of the range this row does not see (causal rule)
             if (kMask) {
-                mrow = static_cast<const T *>(a.mask) +
-                       (int64_t)(a.mask_rows != nullptr ? a.mask_rows[item.seq] : item.seq) * a.mask_bs + item.tok_begin;
+                const int jq = a.q_per_seq > 1 ? min(head0 + row, a.num_heads - 1) / (a.num_heads / a.q_per_seq) : 0;
+                if (a.mask != nullptr) {
+                    mrow = static_cast<const T *>(a.mask) +
+                           (int64_t)(a.mask_rows != nullptr ? a.mask_rows[item.seq] : item.seq) * a.mask_bs +
+                           (int64_t)jq * a.mask_qs + item.tok_begin;
+                }
+                if (a.seq_lens != nullptr) {
+                    row_limit = a.seq_lens[item.seq] - (a.q_per_seq - 1 - jq) - item.tok_begin;
+                }
             }
             for (int st = 0; st < n_st && alive; ++st, ++g) {
                 const int sb = g & 1;
@@ -414,12 +424,17 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         // the same mask value for every head (row); -inf is kept finite so that a fully masked
                         // start of a range cannot make the running maximum -inf.  Tokens past the end are not read.
                         constexpr float kLog2e = 1.4426950408889634f;
-                        if (j < valid) {
-                            v0 = fmaxf(v0 + kLog2e * Elem<T>::to_float(mrow[st * kTok + j]), -1e30f);
+                        if (mrow != nullptr) {
+                            if (j < valid) {
+                                v0 = fmaxf(v0 + kLog2e * Elem<T>::to_float(mrow[st * kTok + j]), -1e30f);
+                            }
+                            if (j + 32 < valid) {
+                                v1 = fmaxf(v1 + kLog2e * Elem<T>::to_float(mrow[st * kTok + j + 32]), -1e30f);
+                            }
                         }
-                        if (j + 32 < valid) {
-                            v1 = fmaxf(v1 + kLog2e * Elem<T>::to_float(mrow[st * kTok + j + 32]), -1e30f);
-                        }
+                        // hidden by the causal rule: finite like a mask of -inf (a range may hold nothing else)
+                        v0 = (st * kTok + j < row_limit) ? v0 : -1e30f;
+                        v1 = (st * kTok + j + 32 < row_limit) ? v1 : -1e30f;
                     }
                     v0 = (j < valid) ? v0 : -INFINITY;
                     v1 = (j + 32 < valid) ? v1 : -INFINITY;
@@ -598,7 +613,7 @@ EncodeFn get_encode_fn()
 template <typename T>
 cudaError_t launch_typed(const PaArgs &args, const CUtensorMap &km, const CUtensorMap &rm, cudaStream_t s)
 {
-    const bool masked = args.mask != nullptr;
+    const bool masked = args.mask != nullptr || args.seq_lens != nullptr;
     auto kern = masked ? pa_mla_tc5_kernel<T, true> : pa_mla_tc5_kernel<T, false>;
     static bool configured_plain[64] = {}, configured_masked[64] = {};
     bool *configured = masked ? configured_masked : configured_plain;

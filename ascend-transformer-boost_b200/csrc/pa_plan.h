@@ -75,6 +75,7 @@ struct PaArgs {
     // factors of the scale; both null on the plain path
     const void *mask;
     int64_t mask_bs, mask_hs, mask_qs; // mask_qs: between the rows of a sequence's consecutive query tokens
+    const int32_t *seq_lens;           // causal parallel decoding: context length of every sequence (else null)
     int32_t q_per_seq;                 // > 1: a CTA's columns are (query token, head) pairs of one sequence
     const float *logn;
     // parallel decoding: the block-table row and the mask row of every query token (null: the token's own index)

@@ -23,6 +23,9 @@ void HostPlan::write_blob(uint8_t *dst) const
     if (!combine_seqs.empty()) {
         std::memcpy(dst + off_combine, combine_seqs.data(), combine_seqs.size() * sizeof(int32_t));
     }
+    if (!seq_lens.empty()) {
+        std::memcpy(dst + off_lens, seq_lens.data(), seq_lens.size() * sizeof(int32_t));
+    }
     if (!bt_rows.empty()) {
         std::memcpy(dst + off_rows, bt_rows.data(), bt_rows.size() * sizeof(int32_t));
         std::memcpy(dst + off_rows + bt_rows.size() * sizeof(int32_t), mask_rows.data(), mask_rows.size() * sizeof(int32_t));
@@ -64,7 +67,8 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
     if (d.score_mods != 0) {
         // masks, logN scaling and per-token rows live in the fp16 / bf16 D = 128 kernel and in the CUDA-core kernel;
         // the MLA kernel takes per-token rows and a mask without a head stride, no logN
-        if ((d.score_mods & ~(ATB_B200_SCORE_MASK | ATB_B200_SCORE_LOGN | ATB_B200_SCORE_ROWS)) != 0) {
+        if ((d.score_mods & ~(ATB_B200_SCORE_MASK | ATB_B200_SCORE_LOGN | ATB_B200_SCORE_ROWS | ATB_B200_SCORE_CAUSAL)) != 0 ||
+            ((d.score_mods & ATB_B200_SCORE_CAUSAL) != 0 && d.q_per_seq <= 1)) {
             return kErrInvalidParam;
         }
         const bool tma_plain = tma_ok && d.kv_dtype != kInt8;
@@ -89,13 +93,15 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
         }
     }
     if (d.q_per_seq > 1) {
-        // (token, head) pairs as the columns of one CTA: the fp16 / bf16 D = 128 kernel only, at most 8 pairs per kv head
-        // (which is what its head limit already says about num_heads / kv_heads)
-        if (!tma_ok || d.kv_dtype == kInt8 || d.rope_dim != 0 ||
-            (kernel != ATB_B200_KERNEL_AUTO && kernel != ATB_B200_KERNEL_TMA_MMA)) {
+        // (token, head) pairs as the columns of one CTA of the fp16 / bf16 D = 128 kernel (at most 8 pairs per kv head,
+        // which is what its head limit already says about num_heads / kv_heads), or as the rows of the MLA kernel
+        const bool tma_pairs = tma_ok && d.kv_dtype != kInt8 && d.rope_dim == 0;
+        const int want = tma_pairs ? ATB_B200_KERNEL_TMA_MMA : ATB_B200_KERNEL_MLA_TC5;
+        if ((!tma_pairs && !mla_ok) || (d.score_mods & ATB_B200_SCORE_LOGN) != 0 ||
+            (kernel != ATB_B200_KERNEL_AUTO && kernel != want)) {
             return kErrInvalidTensorDim;
         }
-        kernel = ATB_B200_KERNEL_TMA_MMA;
+        kernel = want;
     }
     if (kernel == ATB_B200_KERNEL_AUTO) {
         kernel = tma_ok ? ATB_B200_KERNEL_TMA_MMA : (mla_ok ? ATB_B200_KERNEL_MLA_TC5 : ATB_B200_KERNEL_GENERIC);
@@ -235,6 +241,13 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
     p->off_counters = off;
     if (p->fused_combine && p->n_partials > 0) {
         off = align_up(off + (uint64_t)d.batch * p->cols * sizeof(int32_t), 16);
+    }
+    if ((d.score_mods & ATB_B200_SCORE_CAUSAL) != 0) {
+        p->seq_lens.assign(context_lens, context_lens + d.batch);
+        p->off_lens = off;
+        off = align_up(off + (uint64_t)d.batch * sizeof(int32_t), 16);
+    } else {
+        p->seq_lens.clear();
     }
     if ((d.score_mods & ATB_B200_SCORE_ROWS) != 0) {
         // rows set for this batch size stay; otherwise token b reads row b

@@ -26,11 +26,13 @@ struct HostPlan {
     std::vector<int32_t> seq_nparts;    // batch
     std::vector<int32_t> combine_seqs;
     std::vector<int32_t> bt_rows, mask_rows; // per query token, ATB_B200_SCORE_ROWS only (else empty)
+    std::vector<int32_t> seq_lens;           // context lengths, ATB_B200_SCORE_CAUSAL only (else empty)
 
     // Byte offsets inside the workspace (all 256-byte aligned).
     uint64_t off_group_begin = 0, off_items = 0, off_part_base = 0, off_nparts = 0, off_combine = 0;
     uint64_t off_done = 0;        // finished-CTA counter (zeroed by every upload)
     uint64_t off_counters = 0;    // arrival counters of the in-kernel merge (zeroed by every upload)
+    uint64_t off_lens = 0;        // seq_lens (batch entries), ATB_B200_SCORE_CAUSAL only
     uint64_t off_rows = 0;        // bt_rows then mask_rows (batch entries each), ATB_B200_SCORE_ROWS only
     bool fused_combine = false;   // the attention kernel merges split sequences itself
     uint64_t blob_bytes = 0;      // uploaded per launch

@@ -197,6 +197,13 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 mrow1 = mb + (int64_t)(x1 / gr) * a.mask_qs + (int64_t)(kvh * gr + x1 % gr) * a.mask_hs;
             }
         }
+        // causal parallel decoding: the query token of column x sees the sequence's first len - (qps - 1 - x / gr) tokens
+        int lim0 = 0x7fffffff, lim1 = 0x7fffffff;
+        if (kMods && a.seq_lens != nullptr) {
+            const int len = a.seq_lens[item.seq];
+            lim0 = len - (qps - 1 - min(2 * c, group - 1) / gr);
+            lim1 = len - (qps - 1 - min(2 * c + 1, group - 1) / gr);
+        }
         const int n_st = (item.tok_end - item.tok_begin + kStageTokens - 1) / kStageTokens;
         for (int st = 0; st < n_st; ++st) {
             const int valid_tokens = item.tok_end - (item.tok_begin + st * kStageTokens + warp * 16);
@@ -259,6 +266,14 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         s[2] = fmaxf(s[2] + kLog2e * Elem<T>::to_float(mrow0[t0 + 8]), -1e30f);
                         s[3] = fmaxf(s[3] + kLog2e * Elem<T>::to_float(mrow1[t0 + 8]), -1e30f);
                     }
+                }
+                if (kMods && a.seq_lens != nullptr) {
+                    // finite, like a mask of -inf: a range may hold nothing but tokens this column does not see
+                    const int t0 = item.tok_begin + st * kStageTokens + warp * 16 + g;
+                    s[0] = t0 < lim0 ? s[0] : -1e30f;
+                    s[1] = t0 < lim1 ? s[1] : -1e30f;
+                    s[2] = t0 + 8 < lim0 ? s[2] : -1e30f;
+                    s[3] = t0 + 8 < lim1 ? s[3] : -1e30f;
                 }
                 if (g >= valid_tokens) {
                     s[0] = s[1] = -INFINITY;
@@ -548,7 +563,8 @@ bool encode_cache_map(CUtensorMap *map, const void *base, int elem_dtype, int kv
 
 template <typename T> cudaError_t launch_typed(const PaArgs &args, const CUtensorMap &km, const CUtensorMap &vm, cudaStream_t s)
 {
-    const bool mods = args.mask != nullptr || args.logn != nullptr || args.bt_rows != nullptr || args.q_per_seq > 1;
+    const bool mods = args.mask != nullptr || args.logn != nullptr || args.bt_rows != nullptr || args.q_per_seq > 1 ||
+                      args.seq_lens != nullptr;
     auto kern = mods ? pa_tma_mma_kernel<T, true> : pa_tma_mma_kernel<T, false>;
     static bool configured_plain[64] = {}, configured_mods[64] = {};
     bool *configured = mods ? configured_mods : configured_plain;

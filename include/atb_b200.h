@@ -66,8 +66,9 @@ typedef struct atb_b200_pa_desc {
                                query tokens for every sequence): batch = sequences, q and out hold n consecutive tokens
                                per sequence ([batch * n, heads, dim]), num_heads = n x the real head count, and one CTA
                                serves the n x heads-per-kv-head (token, head) pairs of a kv head from one read of the
-                               cache (at most 8 pairs; fp16 / bf16, head_dim 128).  A mask is indexed per (sequence,
-                               token): see mask_q_stride */
+                               cache (at most 8 pairs; fp16 / bf16, head_dim 128); the MLA kernel takes any n: its
+                               rows are the n x heads (token, head) pairs.  A mask is indexed per (sequence, token):
+                               see mask_q_stride */
 } atb_b200_pa_desc;
 
 enum { ATB_B200_KV_BSND = 0, ATB_B200_KV_BNSD = 1 };
@@ -75,6 +76,9 @@ enum { ATB_B200_KV_BSND = 0, ATB_B200_KV_BNSD = 1 };
 enum {
     ATB_B200_SCORE_MASK = 1, /* score(b, h, t) += mask[b * mask_batch_stride + h * mask_head_stride + t] */
     ATB_B200_SCORE_LOGN = 2, /* the scale of sequence b is qk_scale * logn[b] */
+    ATB_B200_SCORE_CAUSAL = 8, /* q_per_seq = n > 1 only: query token j of a sequence sees its first context_len - (n - 1 - j)
+                                  cached tokens (the causal rule of parallel decoding, MASK_TYPE_MASK_FREE of the
+                                  reference's MultiLatentAttention) without reading a mask */
     ATB_B200_SCORE_ROWS = 4  /* query token b reads row bt_rows[b] of block_tables and (with a mask) row mask_rows[b]
                                 of the mask instead of row b: parallel decoding (CALC_TYPE_SPEC of the reference),
                                 where several query tokens share one sequence's cache.  The rows are set with

@@ -610,6 +610,13 @@ def test_fused_parallel_decoding_plan_rules(monkeypatch):
     _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, kv="int8")
     _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, kernel=capi.KERNEL_GENERIC)
     _expect(capi.ERROR_INVALID_PARAM, plan, heads=18, kvh=2, n=4)          # heads not a multiple of the token count
+    # the causal rule needs several query tokens per sequence; the MLA kernel takes any number of (token, head) rows
+    _expect(capi.ERROR_INVALID_PARAM, capi.PaPlan,
+            capi.make_desc(2, 8, 2, 128, 128, 128, 64, 8, "bf16", sm_count=148, score_mods=capi.SCORE_CAUSAL), lens)
+    mla = capi.make_desc(2, 3 * 128, 1, 576, 512, 128, 64, 8, "bf16", sm_count=148, v_row_dim=512, rope_dim=64,
+                         score_mods=capi.SCORE_CAUSAL, q_per_seq=3)
+    info = capi.PaPlan(mla, lens).info
+    assert info.kernel == capi.KERNEL_MLA_TC5 and info.num_ctas % 6 == 0       # 384 rows = 6 CTAs per token range
     # the operator plans uniform qSeqLens this way and falls back to one row per token where it cannot
     monkeypatch.setenv("ATB_B200_SM_COUNT", "148")
     T = capi.atb_tensor

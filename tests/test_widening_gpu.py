@@ -692,3 +692,28 @@ def test_parallel_decoding_same_token_count_per_sequence(heads, kv_heads, q_len,
     per_token = _run_spec_op(case, d, mask_kind, d["q_lens"], lens)
     assert max_abs_err(per_token, ref, dtype) <= tol_for(case)
     assert max_abs_err(got, per_token, dtype) <= tol_for(case)
+
+
+@pytest.mark.parametrize("mask_type", [0, 1, 2], ids=["no_mask", "spec_mask", "mask_free"])
+@pytest.mark.parametrize("heads,q_len,dtype", [(16, 2, "bf16"), (8, 3, "fp16"), (128, 2, "bf16")])
+def test_mla_parallel_decoding_same_token_count_per_sequence(heads, q_len, dtype, mask_type, monkeypatch):
+    """MTP with q_len tokens for every sequence: planned per sequence (the MLA kernel's rows are the (token, head) pairs,
+    64 per CTA) and, forced through the environment, per token; both against the oracle, with the log-sum-exp."""
+    case = wl.Case(f"mla_mtp_{heads}_{q_len}_{dtype}", batch=4, heads=heads, kv_heads=1, dk=576, dv=512, q_dtype=dtype, mla=True,
+                   ctx=("list", [1500, 64, 130, q_len]), seed=99)
+    spec = dict(case=case, q_lens=[q_len] * 4, mask="spec")
+    d = mla_mtp_inputs(spec)
+    lens = d["context_lens"]
+    mask_f32 = wl.to_f32(d["mask"], dtype)                                # the causal triangle in columns [ctx - q_len, ctx)
+    ref, ref_lse = oracle.paged_attention_spec(d["q"], d["k_cache"], None, d["block_tables"], d["q_lens"], lens, case.qk_scale,
+                                               dtype, None if mask_type == 0 else mask_f32, mask_rows_are_tokens=True, dv=512,
+                                               want_lse=True)
+    given = {0: None, 1: d["mask"], 2: np.zeros((8, 128), dtype=d["mask"].dtype)}[mask_type]
+    unit = 2.0 ** (-10 if dtype == "fp16" else -7)
+    for expand in (False, True):
+        if expand:
+            monkeypatch.setenv("ATB_B200_SPEC_EXPAND", "1")
+        got, lse = _run_mla_mtp(case, d, mask_type, ring=True, mask=given)
+        assert max_abs_err(got, ref, dtype) <= tol_for(case)
+        gl, rl = wl.to_f32(lse, dtype), wl.to_f32(ref_lse, dtype)
+        assert np.all(np.abs(gl - rl) <= 2 * unit * np.maximum(np.abs(rl), 1.0))
