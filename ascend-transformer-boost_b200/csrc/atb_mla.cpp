@@ -243,7 +243,14 @@ protected:
             for (int64_t b = 1; b < batch; ++b) {
                 n = qLens[b] == n ? n : 0;
             }
-            fusedTokens_ = (n > 1 && std::getenv("ATB_B200_SPEC_EXPAND") == nullptr) ? n : 0;
+            // Worth it when the pairs fill the kernel's 64 rows better than the heads alone do (16 or 32 heads per GPU
+            // under tensor parallelism); with 64 or 128 heads the per-token plan is as good (measured: 269 vs 280 us
+            // on the 128-head benchmark configuration).  The environment can force either form.
+            const int64_t H = param_.headNum;
+            const bool packs = n > 1 && (n * H + 63) / 64 < n * ((H + 63) / 64);
+            const bool fuse = std::getenv("ATB_B200_SPEC_FUSE") != nullptr ||
+                              (packs && std::getenv("ATB_B200_SPEC_EXPAND") == nullptr);
+            fusedTokens_ = (n > 1 && fuse) ? n : 0;
             if (fusedTokens_ > 1) {
                 d.batch = static_cast<int32_t>(batch);
                 d.num_heads = n * param_.headNum;

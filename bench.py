@@ -401,8 +401,8 @@ def run_variant_bench(args, wl, capi):
     """Attention kernel alone on one GPU in one of its other forms, on the chosen configuration's cache: `alibi` adds
     a [heads, 1, tokens] mask; `mtp2` / `mtp2_rows` run two query tokens per sequence (the second sees the whole context,
     the first one token less): `mtp2` as one planned row per sequence whose CTA columns are the (token, head) pairs,
-    with the causal rule given as a [tokens, max_ctx] mask; `mtp2_rows` as one planned row per token (the form the MLA
-    kernel and ragged token counts use).  KV bytes are counted once per sequence."""
+    with the causal rule given as a [tokens, max_ctx] mask (MLA: as the kernel's own rule); `mtp2_rows` as one planned row
+    per token (the form ragged token counts use).  KV bytes are counted once per sequence."""
     import torch
     case = wl.CONFIGS[args.config]
     dev = torch.device("cuda", 0)
@@ -422,9 +422,10 @@ def run_variant_bench(args, wl, capi):
         slopes = torch.exp2(-8.0 * (torch.arange(case.heads, device=dev) + 1) / case.heads)
         mask = (slopes[:, None, None] * (torch.arange(mask_tokens, device=dev) - mask_tokens + 1)[None, None, :]).to(q.dtype)
         mods, strides = capi.SCORE_MASK, (0, mask_tokens)
+    elif args.variant == "mtp2" and case.mla:
+        # the MLA kernel's rows are the (token, head) pairs; the causal rule needs no mask
+        mods, fused, planned_rows, heads = capi.SCORE_CAUSAL, 2, case.batch, 2 * case.heads
     elif args.variant == "mtp2":
-        if case.mla:
-            raise SystemExit("the MLA kernel plans parallel decoding per token: use --variant mtp2_rows")
         mask_tokens = int(lens.max())
         mask = torch.zeros((tokens, mask_tokens), dtype=q.dtype, device=dev)
         first = torch.arange(case.batch, device=dev) * 2                 # a sequence's first token does not see the last key

@@ -710,9 +710,11 @@ def test_mla_parallel_decoding_same_token_count_per_sequence(heads, q_len, dtype
                                                want_lse=True)
     given = {0: None, 1: d["mask"], 2: np.zeros((8, 128), dtype=d["mask"].dtype)}[mask_type]
     unit = 2.0 ** (-10 if dtype == "fp16" else -7)
-    for expand in (False, True):
-        if expand:
-            monkeypatch.setenv("ATB_B200_SPEC_EXPAND", "1")
+    for form in ("ATB_B200_SPEC_FUSE", "ATB_B200_SPEC_EXPAND", None):    # per sequence, per token, the operator's choice
+        monkeypatch.delenv("ATB_B200_SPEC_FUSE", raising=False)
+        monkeypatch.delenv("ATB_B200_SPEC_EXPAND", raising=False)
+        if form:
+            monkeypatch.setenv(form, "1")
         got, lse = _run_mla_mtp(case, d, mask_type, ring=True, mask=given)
         assert max_abs_err(got, ref, dtype) <= tol_for(case)
         gl, rl = wl.to_f32(lse, dtype), wl.to_f32(ref_lse, dtype)
