@@ -632,3 +632,26 @@ def test_fused_parallel_decoding_plan_rules(monkeypatch):
         op = capi.Operation(_pa_param(calcType=1, maskType=3))
         assert op.setup(ins, outs, ctx) >= 256
         assert op.setup(ins, outs, ctx) >= 256                              # second Setup re-plans in place
+
+
+def test_ctypes_mirror_matches_the_c_header(tmp_path):
+    """The header is plain C: compile a probe against it and compare sizes and field offsets with the ctypes mirror."""
+    import subprocess
+    fields = {"atb_b200_pa_desc": (capi.PaDesc, ["qk_scale", "rope_dim", "score_mods", "kv_layout", "q_per_seq"]),
+              "atb_b200_pa_tensors": (capi.PaTensors, ["out", "q_rope", "mask", "mask_tokens", "mask_q_stride", "logn", "lse_out"]),
+              "atb_b200_pa_plan_info": (capi.PaPlanInfo, ["workspace_bytes", "kernels_per_launch"]),
+              "atb_b200_pa_peers": (capi.PaPeers, ["peer_out", "peer_flags", "epoch"])}
+    lines = []
+    for name, (_, names) in fields.items():
+        lines.append(f'printf("%zu", sizeof({name}));')
+        lines += [f'printf(" %zu", offsetof({name}, {f}));' for f in names]
+        lines.append('printf("\\n");')
+    src = tmp_path / "probe.c"
+    src.write_text('#include <stddef.h>\n#include <stdio.h>\n#include "atb_b200.h"\nint main(void) {\n' + "\n".join(lines) +
+                   "\nreturn 0;\n}\n")
+    exe = tmp_path / "probe"
+    subprocess.check_call(["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)])
+    out = subprocess.check_output([str(exe)], text=True).strip().splitlines()
+    for line, (name, (cls, names)) in zip(out, fields.items()):
+        want = [ctypes.sizeof(cls)] + [getattr(cls, f).offset for f in names]
+        assert [int(x) for x in line.split()] == want, name
