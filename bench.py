@@ -193,7 +193,7 @@ def main():
                     help="single-GPU side measurements of the attention kernel's other forms: an alibi mask shared by all "
                          "sequences; two query tokens per sequence (parallel decoding, causal) planned per sequence "
                          "(mtp2: one read of the cache) or per token (mtp2_rows)")
-    ap.add_argument("--op", default="decode", choices=["decode", "block_copy", "paged_cache_load", "norm_rope_reshape"],
+    ap.add_argument("--op", default="decode", choices=["decode", "block_copy", "paged_cache_load", "norm_rope_reshape", "kv_cache"],
                     help="decode (default): the hot path; the others time one cache-management kernel on 1 GPU")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -521,6 +521,18 @@ def run_cache_op_bench(args, capi):
 
         def step():
             capi.paged_cache_load(kc, vc, tables, cu, key, value, cumulative=True, stream_ptr=stream.cuda_stream)
+    elif args.op == "kv_cache":
+        layers, batch, max_seqlen, hidden = 2, 64, 4096, 1024          # a prefill: 64 sequences x ~3072 new rows of 2 KB
+        lens_h = rng.integers(2048, 4097, size=batch).astype(np.int32)
+        seq_len, token_offset = torch.from_numpy(lens_h).to(dev), torch.from_numpy(lens_h).to(dev)
+        layer_id = torch.tensor([1], dtype=torch.int32, device=dev)
+        new_kv = torch.empty((int(lens_h.sum()), hidden), dtype=torch.bfloat16, device=dev).normal_()
+        past = torch.zeros((layers, batch, max_seqlen, hidden), dtype=torch.bfloat16, device=dev)
+        moved = 2 * new_kv.numel() * new_kv.element_size()
+        workload = f"{batch} sequences x 2048..4096 new rows of {hidden} bf16 into layer 1 of a [{layers}, {batch}, {max_seqlen}, {hidden}] cache"
+
+        def step():
+            capi.kv_cache(new_kv, layer_id, past, token_offset, seq_len, stream_ptr=stream.cuda_stream)
     else:
         tokens, dx, dr, nb = 4096, 512, 64, 4096       # a prefill-sized batch of new tokens: decode is latency-bound
         x = torch.empty((tokens, 1, dx), dtype=torch.bfloat16, device=dev).normal_()
