@@ -218,7 +218,10 @@ int atb_b200_kv_cache(const void *new_kv, const int32_t *layer_id, void *past, c
     a.n_tokens = num_tokens;
     // the longest run a sequence can have: every row of new_kv, or a full cache row
     const int64_t longest = (num_tokens < max_seqlen ? num_tokens : (int64_t)max_seqlen) * row_bytes;
-    a.chunks = chunks_for(longest);
+    // a sequence's run can be megabytes (prefill): cut it into ~32 KB chunks, up to 1024 per sequence, so that the
+    // grid has enough CTAs in flight; chunks past the end of a shorter run return at once
+    const int64_t want = (longest + kChunkBytes - 1) / kChunkBytes;
+    a.chunks = (int32_t)(want < 1 ? 1 : (want > 1024 ? 1024 : want));
     a.vec16 = aligned16(new_kv) && aligned16(past) && row_bytes % 16 == 0;
     const int64_t ctas = (int64_t)batch * a.chunks;
     if (ctas > 0x7fffffff) {
