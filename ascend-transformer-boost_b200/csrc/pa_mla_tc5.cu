@@ -192,6 +192,13 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     // launched with programmatic stream serialisation: the set-up above overlapped the tail of the
     // previous kernel in the stream; wait for it (and its memory) before reading any input
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // probe with CTA selector 255: every CTA records when it started and ended (global nanosecond timer) instead of
+    // one CTA recording its events
+    const bool time_all = a.trace != nullptr && (a.trace_cap >> 24) == 255u && 2 * gridDim.x + 2 <= (a.trace_cap & 0xffffffu);
+    unsigned long long t_start = 0;
+    if (time_all && threadIdx.x == 0) {
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_start));
+    }
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_o = tmem_base;                 // lanes 0-15 of every quadrant, columns 0..511
     const uint32_t tmem_s = tmem_base + (16u << 16);   // lanes 16-31 of every quadrant, columns 0..127
@@ -585,6 +592,12 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 
     tc_fence_before();
     __syncthreads();
+    if (time_all && threadIdx.x == 0) {
+        unsigned long long t_end;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_end));
+        a.trace[1 + 2 * blockIdx.x] = t_start;
+        a.trace[2 + 2 * blockIdx.x] = t_end;
+    }
     if (warp == 5) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);

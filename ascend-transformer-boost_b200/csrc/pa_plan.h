@@ -92,7 +92,7 @@ struct PaArgs {
 __device__ __forceinline__ void probe(const PaArgs &a, unsigned tag, unsigned idx)
 {
 #ifdef __CUDA_ARCH__
-    if (a.trace != nullptr && blockIdx.x == (a.trace_cap >> 24)) {
+    if (a.trace != nullptr && (a.trace_cap >> 24) != 255u && blockIdx.x == (a.trace_cap >> 24)) {
         const unsigned long long n = atomicAdd(a.trace, 1ull);
         if (n + 1 < (a.trace_cap & 0xffffffu)) {
             a.trace[n + 1] = ((unsigned long long)tag << 56) | ((unsigned long long)(idx & 0xffffu) << 40) |

@@ -232,7 +232,9 @@ int atb_b200_pa_plan_device_status(atb_b200_pa_plan *plan, void *workspace, void
 /* Optional event probe for kernel tuning (the role of the reference's Probe hooks,
  * src/atb/utils/probe.h:19-58): `device_events` is a zeroed device array of (capacity & 0xffffff) uint64;
  * CTA number (capacity >> 24) of the MLA kernel appends (tag << 56 | index << 40 | SM cycle counter) records,
- * element 0 counts them.  NULL switches it off. */
+ * element 0 counts them.  CTA number 255 selects the other form: every CTA b of the MLA kernel stores the global
+ * nanosecond timer at its start and at its end in elements 1 + 2b and 2 + 2b (capacity >= 2 * grid + 2), which shows how
+ * evenly the plan loads the SMs.  NULL switches it off. */
 int atb_b200_pa_plan_set_trace(atb_b200_pa_plan *plan, void *device_events, uint32_t capacity);
 
 /* Optional timing of the attention kernel alone: when enabled, every launch records a pair of

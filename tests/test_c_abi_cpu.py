@@ -655,3 +655,21 @@ def test_ctypes_mirror_matches_the_c_header(tmp_path):
     for line, (name, (cls, names)) in zip(out, fields.items()):
         want = [ctypes.sizeof(cls)] + [getattr(cls, f).offset for f in names]
         assert [int(x) for x in line.split()] == want, name
+
+
+def test_mla_plan_weighs_token_ranges():
+    """The MLA kernel pays for every token range it starts about as much as for six tiles; its plan packs
+    cost = tiles + 6 x ranges evenly, so groups that straddle a sequence boundary get fewer tiles."""
+    case = wl.CONFIGS[4]
+    plan, lens = _plan(case)
+    info = plan.info
+    assert info.kernel == capi.KERNEL_MLA_TC5
+    items, groups = plan.dump()
+    n_groups = info.num_ctas // 2
+    tiles = np.array([sum((e - b + 63) // 64 for _, b, e, _ in items[groups[g]:groups[g + 1]]) for g in range(n_groups)])
+    ranges = np.array([groups[g + 1] - groups[g] for g in range(n_groups)])
+    cost = tiles + 6 * ranges
+    total = int(((lens.astype(np.int64) + 63) // 64).sum())
+    assert tiles.sum() == total
+    assert cost.max() <= (total + 6 * len(items)) / n_groups + 7           # within one range of the mean cost
+    assert tiles[ranges == 2].max() < tiles[ranges == 1].max()            # two ranges -> fewer tiles

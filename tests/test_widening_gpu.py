@@ -719,3 +719,36 @@ def test_mla_parallel_decoding_same_token_count_per_sequence(heads, q_len, dtype
         assert max_abs_err(got, ref, dtype) <= tol_for(case)
         gl, rl = wl.to_f32(lse, dtype), wl.to_f32(ref_lse, dtype)
         assert np.all(np.abs(gl - rl) <= 2 * unit * np.maximum(np.abs(rl), 1.0))
+
+
+def test_mla_plan_balances_ranges_and_every_cta_reports_its_time():
+    """The MLA plan weighs every token range it starts like six tiles, so CTAs that hold two ranges get fewer tiles; the
+    all-CTA form of the probe (CTA selector 255) shows the result: every CTA's end is after its start and the CTAs that
+    work end close together."""
+    case = wl.Case("mla_plan_balance", batch=6, heads=128, kv_heads=1, dk=576, dv=512, q_dtype="bf16", mla=True,
+                   ctx=("list", [9000, 7000, 8000, 6000, 9500, 5000]), seed=95)
+    h = wl.make_host_inputs(case)
+    d = host_inputs_to_device(case, h)
+    out = torch.zeros((case.batch, case.heads, case.dv), dtype=d["q"].dtype, device="cuda")
+    desc = capi.make_desc(case.batch, case.heads, 1, 576, 512, case.block_size, d["k_cache"].shape[0], d["block_tables"].shape[1],
+                          "bf16", qk_scale=case.qk_scale, v_row_dim=576)
+    plan = capi.PaPlan(desc, h["context_lens"])
+    info = plan.info
+    items, groups = plan.dump()
+    n_groups = info.num_ctas // 2
+    cost = np.array([sum((e - b + 63) // 64 for _, b, e, _ in items[groups[g]:groups[g + 1]]) + 6 * (groups[g + 1] - groups[g])
+                     for g in range(n_groups)])
+    assert cost.max() <= np.sort(cost)[n_groups // 2] + 7                  # greedy packing: full groups differ by < one range
+    ws = torch.empty(max(int(info.workspace_bytes), 256), dtype=torch.uint8, device="cuda")
+    tens = capi.pa_tensors(d["q"], d["k_cache"], None, d["block_tables"], out)
+    trace = torch.zeros(4096, dtype=torch.int64, device="cuda")
+    plan.set_trace(trace.data_ptr(), 4096 | (255 << 24))
+    plan.launch(tens, ws.data_ptr(), ws.numel(), capi.torch_stream_ptr())
+    torch.cuda.synchronize()
+    plan.set_trace(0, 0)
+    assert plan.device_status(ws.data_ptr(), capi.torch_stream_ptr()) == 0
+    t = trace.cpu().numpy()
+    start, end = t[1:1 + 2 * info.num_ctas:2], t[2:2 + 2 * info.num_ctas:2]
+    assert np.all(end > start) and np.all(start > 0)
+    ref = oracle.paged_attention(h["q"], h["k_cache"], None, h["block_tables"], h["context_lens"], case.qk_scale, "bf16", dv=512)
+    assert max_abs_err(wl.torch_to_host(out, "bf16"), ref, "bf16") <= tol_for(case)
