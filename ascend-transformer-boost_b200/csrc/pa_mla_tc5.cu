@@ -366,19 +366,40 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 const uint4 *qrow = reinterpret_cast<const uint4 *>(static_cast<const T *>(a.q) + qidx * (split ? kDv : kDk));
                 const uint4 *qrope = split ? reinterpret_cast<const uint4 *>(static_cast<const T *>(a.q_rope) + qidx * (kDk - kDv))
                                            : qrow + kDv / 8;
+                // 64 elements = 128 B = 32 columns per atom; three atoms' loads are in flight together (this runs
+                // between two token ranges with the pipeline drained: every exposed load latency is kernel time)
+                static_assert(kAtoms % 3 == 0, "the Q block is stored three atoms at a time");
 #pragma unroll 1
-                for (int c = 0; c < kAtoms; ++c) { // 64 elements = 128 B = 32 columns per step
-                    const uint4 *src = c < kAtoms - 1 ? qrow + c * 8 : qrope;
-                    uint32_t t[32];
+                for (int c0 = 0; c0 < kAtoms; c0 += 3) {
+                    uint32_t t[3][32];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const uint4 v = has_row ? __ldg(src + j) : make_uint4(0, 0, 0, 0);
-                        t[4 * j] = v.x;
-                        t[4 * j + 1] = v.y;
-                        t[4 * j + 2] = v.z;
-                        t[4 * j + 3] = v.w;
+                    for (int u = 0; u < 3; ++u) {
+                        const uint4 *src = c0 + u < kAtoms - 1 ? qrow + (c0 + u) * 8 : qrope;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const uint4 v = has_row ? __ldg(src + j) : make_uint4(0, 0, 0, 0);
+                            t[u][4 * j] = v.x;
+                            t[u][4 * j + 1] = v.y;
+                            t[u][4 * j + 2] = v.z;
+                            t[u][4 * j + 3] = v.w;
+                        }
                     }
-                    tmem_st32(tmem_base + lane_base + kQCol + c * 32, t);
+#pragma unroll
+                    for (int u = 0; u < 3; ++u) {
+                        tmem_st32(tmem_base + lane_base + kQCol + (c0 + u) * 32, t[u]);
+                    }
+                }
+                if (has_row && it + 1 < item_end) {
+                    // the next range's Q rows: into L2 now, so that its range start finds them there
+                    const int64_t nidx = (int64_t)a.plan.items[it + 1].seq * a.num_heads + head0 + row;
+                    const char *nrow = reinterpret_cast<const char *>(static_cast<const T *>(a.q) + nidx * (split ? kDv : kDk));
+                    const int lines = split ? kDv / 64 : kDk / 64;
+                    for (int c = 0; c < lines; ++c) {
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(nrow + c * 128));
+                    }
+                    if (split) {
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const T *>(a.q_rope) + nidx * (kDk - kDv)));
+                    }
                 }
                 tmem_wait_st();
                 tc_fence_before();
