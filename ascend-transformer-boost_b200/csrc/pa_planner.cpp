@@ -207,7 +207,8 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
             }
             return groups;
         };
-        int64_t lo = kItemTiles + 1, hi = total_tiles + kItemTiles;
+        // one group that holds every range is always feasible: that is the upper end of the search
+        int64_t lo = kItemTiles + 1, hi = total_tiles + kItemTiles * (int64_t)d.batch;
         while (lo < hi) {
             const int64_t mid = (lo + hi) / 2;
             if (pack(mid, nullptr) <= n_groups) {
