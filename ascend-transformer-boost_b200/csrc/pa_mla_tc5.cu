@@ -142,6 +142,14 @@ __host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t b_mn_ma
 
 enum Bar { kQFull = 0, kQEmpty, kKvFull0, kKvFull1, kKvFull2, kKvEmpty0, kKvEmpty1, kKvEmpty2, kSFull0, kSFull1, kSEmpty0, kSEmpty1, kPFull, kPvDone };
 
+// One 256-bit store (eight 32-bit words) to a 32-byte aligned global address.
+__device__ __forceinline__ void st_global_v8(void *p, const uint32_t *w)
+{
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+                 "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                 : "memory");
+}
+
 // kMask: the variant for parallel decoding with a mask or the causal rule: it adds the query token's mask row to the
 // scores (MASK_TYPE_SPEC) and / or hides the tokens behind the query token (q_per_seq > 1: the rows of a CTA are (token,
 // head) pairs, row r belongs to query token (head0 + r) / real heads).  The plain variant carries none of that code.
@@ -571,6 +579,7 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             const int h = head0 + row;
             const bool writer = !s_lane && row < nh;
             T *out_row = static_cast<T *>(a.out) + ((int64_t)item.seq * a.num_heads + h) * kDv;
+            const bool out_wide = (reinterpret_cast<uintptr_t>(a.out) & 31u) == 0; // rows are 1 KB: all are aligned then
             float *part_row = a.plan.part_o + ((int64_t)(item.slot < 0 ? 0 : item.slot) * a.num_heads + h) * kDv;
 #pragma unroll 1
             for (int c0 = 0; c0 < kDv; c0 += 32) {
@@ -578,22 +587,32 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 tmem_ld32(tmem_base + lane_base + c0, t);
                 tmem_wait_ld();
                 if (writer) {
+                    // 32-byte stores: a lane writes whole sectors of its row (the rows of a warp are 1 or 2 KB apart,
+                    // so no two lanes share a line)
                     if (item.slot < 0) {
+                        uint32_t w[16];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            uint4 v;
-                            v.x = Elem<T>::pack2(__uint_as_float(t[8 * j]) * inv, __uint_as_float(t[8 * j + 1]) * inv);
-                            v.y = Elem<T>::pack2(__uint_as_float(t[8 * j + 2]) * inv, __uint_as_float(t[8 * j + 3]) * inv);
-                            v.z = Elem<T>::pack2(__uint_as_float(t[8 * j + 4]) * inv, __uint_as_float(t[8 * j + 5]) * inv);
-                            v.w = Elem<T>::pack2(__uint_as_float(t[8 * j + 6]) * inv, __uint_as_float(t[8 * j + 7]) * inv);
-                            *reinterpret_cast<uint4 *>(out_row + c0 + 8 * j) = v;
+                        for (int j = 0; j < 16; ++j) {
+                            w[j] = Elem<T>::pack2(__uint_as_float(t[2 * j]) * inv, __uint_as_float(t[2 * j + 1]) * inv);
+                        }
+                        if (out_wide) {
+                            st_global_v8(out_row + c0, w);
+                            st_global_v8(out_row + c0 + 16, w + 8);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                *reinterpret_cast<uint4 *>(out_row + c0 + 8 * j) =
+                                    make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+                            }
                         }
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            *reinterpret_cast<float4 *>(part_row + c0 + 4 * j) =
-                                make_float4(__uint_as_float(t[4 * j]) * inv, __uint_as_float(t[4 * j + 1]) * inv,
-                                            __uint_as_float(t[4 * j + 2]) * inv, __uint_as_float(t[4 * j + 3]) * inv);
+                        for (int j = 0; j < 32; ++j) {
+                            t[j] = __float_as_uint(__uint_as_float(t[j]) * inv);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            st_global_v8(part_row + c0 + 8 * j, t + 8 * j); // the workspace is 256-byte aligned
                         }
                     }
                 }
