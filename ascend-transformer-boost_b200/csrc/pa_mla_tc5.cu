@@ -142,6 +142,14 @@ __host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t b_mn_ma
 
 enum Bar { kQFull = 0, kQEmpty, kKvFull0, kKvFull1, kKvFull2, kKvEmpty0, kKvEmpty1, kKvEmpty2, kSFull0, kSFull1, kSEmpty0, kSEmpty1, kPFull, kPvDone };
 
+// One 256-bit read-only load from a 32-byte aligned global address.
+__device__ __forceinline__ void ld_global_nc_v8(const void *p, uint32_t *w)
+{
+    asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+                 : "l"(p));
+}
+
 // One 256-bit store (eight 32-bit words) to a 32-byte aligned global address.
 __device__ __forceinline__ void st_global_v8(void *p, const uint32_t *w)
 {
@@ -371,6 +379,8 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 const int64_t qidx = (int64_t)item.seq * a.num_heads + head0 + (has_row ? row : 0);
                 // combined rows: 576 elements; split cache: 512 latent elements here, 64 rope elements in q_rope
                 const bool split = a.q_rope != nullptr;
+                // rows are 1152 / 1024 / 128 bytes: with 32-byte aligned tensors every atom of every row is aligned too
+                const bool q_wide = ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.q_rope)) & 31u) == 0;
                 const uint4 *qrow = reinterpret_cast<const uint4 *>(static_cast<const T *>(a.q) + qidx * (split ? kDv : kDk));
                 const uint4 *qrope = split ? reinterpret_cast<const uint4 *>(static_cast<const T *>(a.q_rope) + qidx * (kDk - kDv))
                                            : qrow + kDv / 8;
@@ -383,13 +393,28 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 #pragma unroll
                     for (int u = 0; u < 3; ++u) {
                         const uint4 *src = c0 + u < kAtoms - 1 ? qrow + (c0 + u) * 8 : qrope;
+                        if (q_wide) {
+                            // 32-byte loads: four per 128-byte atom of the row
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const uint4 v = has_row ? __ldg(src + j) : make_uint4(0, 0, 0, 0);
-                            t[u][4 * j] = v.x;
-                            t[u][4 * j + 1] = v.y;
-                            t[u][4 * j + 2] = v.z;
-                            t[u][4 * j + 3] = v.w;
+                            for (int j = 0; j < 4; ++j) {
+                                if (has_row) {
+                                    ld_global_nc_v8(src + 2 * j, &t[u][8 * j]);
+                                } else {
+#pragma unroll
+                                    for (int k = 0; k < 8; ++k) {
+                                        t[u][8 * j + k] = 0u;
+                                    }
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const uint4 v = has_row ? __ldg(src + j) : make_uint4(0, 0, 0, 0);
+                                t[u][4 * j] = v.x;
+                                t[u][4 * j + 1] = v.y;
+                                t[u][4 * j + 2] = v.z;
+                                t[u][4 * j + 3] = v.w;
+                            }
                         }
                     }
 #pragma unroll
