@@ -1,5 +1,6 @@
 #include "pa_planner.h"
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include "kernels.h"
 
@@ -183,7 +184,13 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
         // range against 2.4 us per tile on a B200.  A group that straddles a sequence boundary holds two ranges, and
         // with equal tile counts those groups end last.  So balance cost = tiles + kItemTiles x ranges instead: the
         // smallest cap T for which a greedy left-to-right packing needs no more than n_groups groups.
-        constexpr int64_t kItemTiles = 6;
+        int64_t kItemTiles = 6;
+        if (const char *env = std::getenv("ATB_B200_MLA_RANGE_TILES")) { // tuning knob: the weight of a range start
+            const long v = std::strtol(env, nullptr, 10);
+            if (v >= 0 && v <= 64) {
+                kItemTiles = v;
+            }
+        }
         auto pack = [&](int64_t cap, std::vector<int64_t> *cuts) {
             int64_t groups = 1, cost = 0, pos = 0;
             if (cuts != nullptr) {
