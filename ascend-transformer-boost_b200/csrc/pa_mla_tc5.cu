@@ -307,14 +307,16 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         tc_fence_after();
                         const int s = gp % kStages;
                         const uint32_t vb = kv_addr + s * kTileBytes;
+                        const uint64_t da0 = smem_desc(p_addr, 16, 1024);
+                        // V^T operand: 64-element boxes along N are 8192 B apart, 8-token groups 1024 B apart
+                        const uint64_t dv0 = smem_desc(vb, kAtomBytes, 1024);
+                        const bool acc = next_pv != 0;
 #pragma unroll
                         for (int half = 0; half < 2; ++half) {
 #pragma unroll
                             for (int ks = 0; ks < 4; ++ks) {
-                                const uint64_t da = smem_desc(p_addr + ks * 32, 16, 1024);
-                                // V^T operand: 64-element boxes along N are 8192 B apart, 8-token groups 1024 B apart
-                                const uint64_t db = smem_desc(vb + (4 * half) * kAtomBytes + ks * 2048, kAtomBytes, 1024);
-                                tc_mma(tmem_o + half * 256, da, db, idesc_pv, next_pv != 0 || ks != 0);
+                                tc_mma(tmem_o + half * 256, da0 + ((ks * 32) >> 4),
+                                       dv0 + (((4 * half) * kAtomBytes + ks * 2048) >> 4), idesc_pv, acc || ks != 0);
                             }
                         }
                         tc_commit(&bars[kKvEmpty0 + s]);
@@ -328,13 +330,18 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         tc_fence_after();
                         const int s = gq & 1;                                   // S buffer
                         const uint32_t kb = kv_addr + (gq % kStages) * kTileBytes; // K tile slot
-#pragma unroll 1
+                        // The issuing thread is the bottleneck of a tile: all 36 MMAs unrolled, one descriptor built and
+                        // the others derived by adding to its address field (16-byte units; shared memory addresses stay
+                        // below the field's 256 KB range, so nothing carries into the next field).
+                        const uint64_t db0 = smem_desc(kb, 16, 1024);
+                        const uint32_t ds = tmem_s + s * 64;
+#pragma unroll
                         for (int at = 0; at < kAtoms; ++at) {
 #pragma unroll
                             for (int ks = 0; ks < 4; ++ks) {
                                 // 16 elements of Q = 8 TMEM columns (two 16-bit values per column)
-                                const uint64_t db = smem_desc(kb + at * kAtomBytes + ks * 32, 16, 1024);
-                                tc_mma_ts(tmem_s + s * 64, tmem_q + at * 32 + ks * 8, db, idesc_qk, (at | ks) != 0);
+                                tc_mma_ts(ds, tmem_q + at * 32 + ks * 8, db0 + ((at * kAtomBytes + ks * 32) >> 4), idesc_qk,
+                                          (at | ks) != 0);
                             }
                         }
                         tc_commit(&bars[kSFull0 + s]);
