@@ -63,7 +63,7 @@ class PaPlanInfo(ctypes.Structure):
 class PaPeers(ctypes.Structure):
     _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("total_heads", ctypes.c_int32),
                 ("head_offset", ctypes.c_int32), ("peer_out", ctypes.c_void_p * 8),
-                ("peer_flags", ctypes.c_void_p * 8), ("epoch", ctypes.c_uint32), ("reserved", ctypes.c_uint32)]
+                ("peer_flags", ctypes.c_void_p * 8), ("epoch", ctypes.c_uint32), ("poll_limit", ctypes.c_uint32)]
 
 
 class AtbTensor(ctypes.Structure):
@@ -157,7 +157,7 @@ EXPORTS = [
     "atb_b200_reshape_and_cache_strided", "atb_b200_operation_create_reshape_and_cache_with_stride",
     "atb_b200_norm_rope_reshape", "atb_b200_operation_create_norm_rope_reshape",
     "atb_b200_operation_create_multi_latent_attention",
-    "atb_b200_kv_cache", "atb_b200_operation_create_kv_cache",
+    "atb_b200_kv_cache", "atb_b200_operation_create_kv_cache", "atb_b200_context_set_gather",
 ]
 
 _lib = None
@@ -209,6 +209,7 @@ def lib():
         L.atb_b200_version.restype = ctypes.c_char_p
         L.atb_b200_pa_decode_static_scratch.argtypes = [P(PaDesc), vp, P(PaTensors), vp]
         L.atb_b200_pa_launch_gathered.argtypes = [vp, P(PaTensors), P(PaPeers), vp, u64, vp]
+        L.atb_b200_context_set_gather.argtypes = [vp, P(PaPeers)]
         L.atb_b200_peer_buffer_create.argtypes = [u64, P(vp), ctypes.c_char_p]
         L.atb_b200_peer_buffer_open.argtypes = [ctypes.c_char_p, P(vp)]
         L.atb_b200_peer_buffer_close.argtypes = [vp]
@@ -561,6 +562,11 @@ class Context:
 
     def set_stream(self, stream_ptr):
         _check(lib().atb_b200_context_set_stream(self.handle, stream_ptr), "atb_b200_context_set_stream")
+
+    def set_gather(self, peers):
+        """Sharded heads: the PaPeers of the next PagedAttention Execute on this context (None switches it off)."""
+        _check(lib().atb_b200_context_set_gather(self.handle, None if peers is None else ctypes.byref(peers)),
+               "atb_b200_context_set_gather")
 
     def __del__(self):
         try:

@@ -3,6 +3,7 @@
 #include <cstring>
 #include "../../include/atb_b200.h"
 #include "atb/atb_infer.h"
+#include "atb_operation_base.h"
 
 namespace {
 using namespace atb;
@@ -56,6 +57,19 @@ int atb_b200_context_set_stream(void *context, void *stream)
         return ERROR_INVALID_PARAM;
     }
     return static_cast<Context *>(context)->SetExecuteStream(stream);
+}
+
+int atb_b200_context_set_gather(void *context, const atb_b200_pa_peers *peers)
+{
+    ContextImpl *ci = dynamic_cast<ContextImpl *>(static_cast<Context *>(context));
+    if (ci == nullptr) {
+        return ERROR_INVALID_PARAM;
+    }
+    if (peers != nullptr && (peers->world < 1 || peers->world > 8 || peers->rank < 0 || peers->rank >= peers->world)) {
+        return ERROR_INVALID_PARAM;
+    }
+    ci->SetGatherPeers(peers);
+    return NO_ERROR;
 }
 
 int atb_b200_context_destroy(void *context) { return DestroyContext(static_cast<Context *>(context)); }

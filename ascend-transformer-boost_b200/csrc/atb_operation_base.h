@@ -9,6 +9,7 @@
 #include <string>
 #include <vector>
 #include "atb/atb_infer.h"
+#include "../../include/atb_b200.h"
 
 namespace atb {
 
@@ -24,8 +25,20 @@ public:
     ExecuteType GetExecuteType() override;
     Status SetLaunchMode(LaunchMode mode) override;
     LaunchMode GetLaunchMode() override;
+    // Extension (atb_b200_context_set_gather): the ranks' gathered output buffers for the next
+    // PagedAttention Execute calls on this context, or none.
+    void SetGatherPeers(const atb_b200_pa_peers *peers)
+    {
+        hasPeers_ = peers != nullptr;
+        if (hasPeers_) {
+            peers_ = *peers;
+        }
+    }
+    const atb_b200_pa_peers *GatherPeers() const { return hasPeers_ ? &peers_ : nullptr; }
 
 private:
+    atb_b200_pa_peers peers_{};
+    bool hasPeers_ = false;
     std::vector<aclrtStream> streams_{nullptr};
     bool asyncTilingCopy_ = false;
     LaunchMode mode_ = KERNEL_LAUNCH_MODE;
@@ -58,6 +71,8 @@ protected:
     // Enqueue on `stream` with the device pointers of this call.
     virtual Status LaunchImpl(const VariantPack &variantPack, uint8_t *workspace, uint64_t workspaceSize,
                               aclrtStream stream) = 0;
+    // The context of the last successful Setup (the one Execute insists on).
+    Context *SetupContext() const { return context_; }
 
 private:
     Status CheckVariantPack(const VariantPack &variantPack) const;

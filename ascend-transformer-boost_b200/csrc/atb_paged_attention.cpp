@@ -2,9 +2,10 @@
 // Parameter rules, tensor order and shape checks follow
 // src/ops/ops_infer/paged_attention/paged_attention_operation.cpp of the reference
 // (CreateOperation :92-143, *ParamCheck :145-365, GetInputNum :408-444, InferShapeImpl :451-472,
-//  SetupCheckImpl :492-525, KVCacheDimCheck910B :585-632, SetupDimCheck :926-963); features that
-// need other inputs (masks, batchRunStatus, parallel decoding, logN, head compression, QKV
-// quantisation, BNSD layout) are rejected at CreateOperation with ERROR_INVALID_PARAM.
+//  SetupCheckImpl :492-525, KVCacheDimCheck910B :585-632, SetupDimCheck :926-963).  Built: NORM / ALIBI / SPEC
+// masks, batchRunStatus, parallel decoding (CALC_TYPE_SPEC), logN scaling, qScale, the BNSD cache layout,
+// int8 caches with per-channel dequantisation.  Head compression, MASK_TYPE_MASK_FREE and the NZ layouts
+// (other SoC classes) are rejected at CreateOperation with ERROR_INVALID_PARAM.
 #include <cmath>
 #include <cstdlib>
 #include <new>
@@ -639,7 +640,12 @@ protected:
         }
         uint8_t *ws = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255));
         const uint64_t usable = workspaceSize - static_cast<uint64_t>(ws - workspace);
-        const int rc = atb_b200_pa_launch(plan_, &t, ws, usable, stream);
+        // kv heads sharded over the GPUs of a node: the context carries the ranks' gathered buffers and the kernel
+        // stores this rank's heads into all of them (attnOut itself is then left untouched)
+        const ContextImpl *ci = dynamic_cast<const ContextImpl *>(SetupContext());
+        const atb_b200_pa_peers *peers = ci != nullptr ? ci->GatherPeers() : nullptr;
+        const int rc = peers != nullptr ? atb_b200_pa_launch_gathered(plan_, &t, peers, ws, usable, stream)
+                                        : atb_b200_pa_launch(plan_, &t, ws, usable, stream);
         return rc == 0 ? NO_ERROR : (rc == ERROR_INVALID_PARAM ? ERROR_INVALID_PARAM : ERROR_RT_FAIL);
     }
 
@@ -655,7 +661,19 @@ private:
             plan_ = nullptr;
         }
         desc_ = d;
-        return atb_b200_pa_plan_create(&d, lens, &plan_);
+        const int rc = atb_b200_pa_plan_create(&d, lens, &plan_);
+        if (rc == 0) {
+            // once per plan shape: say when a shape misses the tiled kernels (the CUDA-core kernel is a
+            // correctness path, far from the memory roofline)
+            atb_b200_pa_plan_info info{};
+            if (atb_b200_pa_plan_get_info(plan_, &info) == 0 && info.kernel == ATB_B200_KERNEL_GENERIC) {
+                ATB_B200_LOG(INFO, "PagedAttentionOperation: this shape (heads per kv head " +
+                                       std::to_string(d.num_heads / d.kv_heads) + ", head dims " +
+                                       std::to_string(d.head_dim_k) + "/" + std::to_string(d.head_dim_v) + ", block size " +
+                                       std::to_string(d.block_size) + ") runs on the untuned CUDA-core kernel");
+            }
+        }
+        return rc;
     }
 
     bool SameDesc(const atb_b200_pa_desc &d) const

@@ -39,6 +39,9 @@ struct atb_b200_pa_plan {
     void *prefetch_stream = nullptr; // the stream that was made to wait for the prefetched copy
     uint64_t prefetches = 0;
     const int32_t *last_status_ptr = nullptr;
+    // status word of the last launch, read back when the device copy it lived in had to be freed
+    int32_t saved_status = 0;
+    bool has_saved_status = false;
     unsigned long long *trace = nullptr; // optional device event buffer (probe)
     uint32_t trace_cap = 0;
     // optional timing of the attention kernel: a ring of event pairs, one pair per launch
@@ -319,6 +322,15 @@ int atb_b200_pa_plan_prefetch(atb_b200_pa_plan *plan, void *stream_v)
         }
         cudaStreamSynchronize(plan->copy_stream);
         if (plan->dev_blob != nullptr) {
+            // the status word of the last launch may live in the copy about to be freed (its readers have
+            // completed: see the waits above): keep its value for atb_b200_pa_plan_device_status
+            const uint8_t *lo = plan->dev_blob, *hi = plan->dev_blob + plan->dev_cap * kRing;
+            const uint8_t *sp = reinterpret_cast<const uint8_t *>(plan->last_status_ptr);
+            if (sp != nullptr && sp >= lo && sp < hi) {
+                plan->has_saved_status =
+                    cudaMemcpy(&plan->saved_status, sp, sizeof(int32_t), cudaMemcpyDeviceToHost) == cudaSuccess;
+                plan->last_status_ptr = nullptr;
+            }
             cudaFree(plan->dev_blob);
             plan->dev_blob = nullptr;
         }
@@ -477,6 +489,7 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
     a.plan.done_ctas = reinterpret_cast<int32_t *>(blob + h.off_done);
     a.plan.counters = (h.fused_combine && h.n_partials > 0) ? reinterpret_cast<int32_t *>(blob + h.off_counters) : nullptr;
     plan->last_status_ptr = a.plan.status;
+    plan->has_saved_status = false;
     a.plan.n_cta_groups = h.n_cta_groups;
     a.plan.cols = h.cols;
     a.batch = d.batch;
@@ -504,6 +517,7 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
         }
         a.xchg_rank = peers->rank;
         a.xchg_epoch = peers->epoch;
+        a.xchg_poll_limit = peers->poll_limit;
     }
 
     const int prof_i = (int)(plan->launches % atb_b200_pa_plan::kProfRing);
@@ -550,6 +564,13 @@ int atb_b200_pa_plan_device_status(atb_b200_pa_plan *plan, void *workspace, void
     if (plan->status_host == nullptr &&
         cudaHostAlloc(reinterpret_cast<void **>(&plan->status_host), 64, cudaHostAllocDefault) != cudaSuccess) {
         return kErrOutOfHostMemory;
+    }
+    if (plan->last_status_ptr == nullptr && plan->has_saved_status) {
+        if (cudaStreamSynchronize(stream) != cudaSuccess) {
+            return kErrRtFail;
+        }
+        *status = plan->saved_status;
+        return ATB_B200_OK;
     }
     const uint8_t *ws = static_cast<const uint8_t *>(workspace);
     const void *src = plan->last_status_ptr != nullptr ? static_cast<const void *>(plan->last_status_ptr)

@@ -17,7 +17,7 @@ bool pa_generic_supported(int dk, int dv, int q_dtype, int kv_dtype);
 int pa_generic_heads_per_cta(int dk, int dv);
 cudaError_t launch_pa_generic(const PaArgs &args, int q_dtype, int kv_dtype, cudaStream_t stream);
 
-// TMA page gather + mma.sync tiles: D = 128, block_size = 128, up to 8 query heads per kv head.
+// TMA page gather + mma.sync tiles: D = 128, block_size 16 / 32 / 64 / 128 / 256, fp16 / bf16 cache.
 bool pa_tma_mma_supported(int dk, int dv, int v_row_dim, int block_size, int group, int q_dtype, int kv_dtype);
 cudaError_t launch_pa_tma_mma(const PaArgs &args, int q_dtype, int kv_dtype, int num_blocks, cudaStream_t stream);
 

@@ -31,6 +31,7 @@
 #include <type_traits>
 #include "common.cuh"
 #include "kernels.h"
+#include "tma_encode.h"
 
 namespace atb_b200 {
 namespace {
@@ -162,7 +163,9 @@ __device__ __forceinline__ void st_global_v8(void *p, const uint32_t *w)
 // scores (MASK_TYPE_SPEC) and / or hides the tokens behind the query token (q_per_seq > 1: the rows of a CTA are (token,
 // head) pairs, row r belongs to query token (head0 + r) / real heads).  The plain variant carries none of that code.
 // Both follow bt_rows when the plan gives every query token its block-table row.
-template <typename T, bool kMask>
+// kTrace: the build that carries the event probe (atb_b200_pa_plan_set_trace); the product build has none of it in
+// the issuing thread's loop.
+template <typename T, bool kMask, bool kTrace>
 __global__ void __launch_bounds__(kThreads, 1)
 pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap rmap, const PaArgs a)
 {
@@ -210,7 +213,7 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     asm volatile("griddepcontrol.wait;" ::: "memory");
     // probe with CTA selector 255: every CTA records when it started and ended (global nanosecond timer) instead of
     // one CTA recording its events
-    const bool time_all = a.trace != nullptr && (a.trace_cap >> 24) == 255u && 2 * gridDim.x + 2 <= (a.trace_cap & 0xffffffu);
+    const bool time_all = kTrace && a.trace != nullptr && (a.trace_cap >> 24) == 255u && 2 * gridDim.x + 2 <= (a.trace_cap & 0xffffffu);
     unsigned long long t_start = 0;
     if (time_all && threadIdx.x == 0) {
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_start));
@@ -257,6 +260,11 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 int blk = 0;
                 if (st0 + lane < n_st) {
                     blk = bt[(item.tok_begin + (st0 + lane) * kTok) / a.block_size];
+                    if ((unsigned)blk >= (unsigned)a.num_blocks) {
+                        // a caller error: report it, and load a zero tile instead of whatever lies there
+                        atomicExch(a.plan.status, kStatusBadBlockId);
+                        blk = -1;
+                    }
                 }
                 const int cnt = min(32, n_st - st0);
                 for (int j = 0; j < cnt && alive; ++j, ++g) {
@@ -268,7 +276,9 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         } else {
                             const int tok_in_blk = (item.tok_begin + (st0 + j) * kTok) % a.block_size;
                             uint8_t *dst = kv_smem + s * kTileBytes;
-                            probe(a, 1, g);
+                            if constexpr (kTrace) {
+                                probe(a, 1, g);
+                            }
                             mbar_expect_tx(&bars[kKvFull0 + s], kTileBytes);
                             for (int at = 0; at < kAtoms - 1; ++at) {
                                 tma_load_4d(dst + at * kAtomBytes, &kmap, &bars[kKvFull0 + s], at * 64, 0, tok_in_blk, b);
@@ -303,7 +313,9 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 while (next_pv < n_st) {
                     const uint32_t gp = g + next_pv, gq = g + next_qk;
                     if (next_pv < next_qk && ready(kPFull, gp & 1)) {
-                        probe(a, 3, gp);
+                        if constexpr (kTrace) {
+                            probe(a, 3, gp);
+                        }
                         tc_fence_after();
                         const int s = gp % kStages;
                         const uint32_t vb = kv_addr + s * kTileBytes;
@@ -326,7 +338,9 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     } else if (next_qk < n_st && next_qk < next_pv + 2 &&
                                ready(kKvFull0 + (gq % kStages), (gq / kStages) & 1) &&
                                ready(kSEmpty0 + (gq & 1), ((gq >> 1) & 1) ^ 1u)) {
-                        probe(a, 2, gq);
+                        if constexpr (kTrace) {
+                            probe(a, 2, gq);
+                        }
                         tc_fence_after();
                         const int s = gq & 1;                                   // S buffer
                         const uint32_t kb = kv_addr + (gq % kStages) * kTileBytes; // K tile slot
@@ -470,7 +484,9 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     break;
                 }
                 if (threadIdx.x == 16) {
-                    probe(a, 4, g);
+                    if constexpr (kTrace) {
+                        probe(a, 4, g);
+                    }
                 }
                 tc_fence_after();
                 uint32_t r0[32], r1[32];
@@ -533,7 +549,9 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 }
                 l += lsum;
                 if (threadIdx.x == 16) {
-                    probe(a, 5, g);
+                    if constexpr (kTrace) {
+                        probe(a, 5, g);
+                    }
                 }
                 // P(g) overwrites P(g-1) and a rescale touches O: both need P.V(g-1) to have finished
                 if (g > 0 && !wait(kPvDone, (g - 1) & 1)) {
@@ -541,7 +559,9 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     break;
                 }
                 if (threadIdx.x == 16) {
-                    probe(a, 6, g);
+                    if constexpr (kTrace) {
+                        probe(a, 6, g);
+                    }
                 }
                 if (rescale_any) {
                     // O rows live in lanes 0..15; the multiplier comes from the row's S lane.  The S lanes
@@ -593,7 +613,9 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     mbar_arrive(&bars[kPFull]);
                 }
                 if (threadIdx.x == 16) {
-                    probe(a, 7, g);
+                    if constexpr (kTrace) {
+                        probe(a, 7, g);
+                    }
                 }
             }
             if (!alive) {
@@ -676,32 +698,16 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     }
 }
 
-using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn get_encode_fn()
-{
-    static EncodeFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess) {
-            fn = reinterpret_cast<EncodeFn>(p);
-        }
-    });
-    return fn;
-}
 
 template <typename T>
 cudaError_t launch_typed(const PaArgs &args, const CUtensorMap &km, const CUtensorMap &rm, cudaStream_t s)
 {
     const bool masked = args.mask != nullptr || args.seq_lens != nullptr;
-    auto kern = masked ? pa_mla_tc5_kernel<T, true> : pa_mla_tc5_kernel<T, false>;
-    static bool configured_plain[64] = {}, configured_masked[64] = {};
-    bool *configured = masked ? configured_masked : configured_plain;
+    const bool traced = args.trace != nullptr;
+    auto kern = traced ? (masked ? pa_mla_tc5_kernel<T, true, true> : pa_mla_tc5_kernel<T, false, true>)
+                       : (masked ? pa_mla_tc5_kernel<T, true, false> : pa_mla_tc5_kernel<T, false, false>);
+    static bool configured_all[4][64] = {};
+    bool *configured = configured_all[(traced ? 2 : 0) + (masked ? 1 : 0)];
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
@@ -739,7 +745,7 @@ bool pa_mla_tc5_supported(int dk, int dv, int v_row_dim, int rope_dim, int block
 
 cudaError_t launch_pa_mla_tc5(const PaArgs &args, int q_dtype, int num_blocks, cudaStream_t stream)
 {
-    EncodeFn fn = get_encode_fn();
+    TmaEncodeFn fn = tma_encode_fn();
     if (fn == nullptr) {
         return cudaErrorInvalidValue;
     }

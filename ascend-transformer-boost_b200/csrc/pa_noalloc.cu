@@ -19,9 +19,21 @@
 // Device address of the scratch: inside host code the array's name is only a handle, not something
 // a kernel may dereference, so the first call on each device asks the runtime for the real address
 // with cudaGetSymbolAddress while that device is current and caches it.  That first call per device
-// therefore does a little extra work and should be made before any stream capture begins.
+// therefore does a little extra work and should be made before any stream capture begins.  Later calls
+// read the cached address with one atomic load (no lock).
+//
+// The plan travels to the device by cudaMemcpyAsync from the (pageable) stack buffer: the runtime
+// stages such a copy before the call returns, which may make the host wait until the stream has
+// reached the copy.  For the same reason a call on a stream that is being captured is refused
+// (ERROR_INVALID_PARAM): a captured copy node would keep the address of a dead stack frame, and the
+// split would stay frozen at the lengths seen at capture time.
+//
+// Device-side status (a bounded wait that gave up, a block id outside the cache) is written into the
+// scratch and not reported by this entry point; callers that need it use the planned entry points
+// and atb_b200_pa_plan_device_status.
 #include <cuda_runtime.h>
 #include <algorithm>
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -50,26 +62,30 @@ constexpr int kErrRtFail = 4;
 constexpr int kErrInvalidTensorDim = 8;
 
 std::mutex g_setup_mutex;
-unsigned char *g_scratch_ptr[64] = {};
+std::atomic<unsigned char *> g_scratch_ptr[64];
 
-// Device address of g_static_scratch on the current device (looked up once per device).
+// Device address of g_static_scratch on the current device.  Looked up once per device under a
+// mutex; every later call takes the cached pointer with a single atomic load.
 int scratch_address(unsigned char **out)
 {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
         return kErrRtFail;
     }
-    std::lock_guard<std::mutex> lock(g_setup_mutex);
-    if (g_scratch_ptr[dev] == nullptr) {
-        unsigned char *ptr = nullptr;
-        const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_static_scratch);
-        if (e != cudaSuccess || ptr == nullptr) {
-            std::fprintf(stderr, "[atb][ERROR] static scratch: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
-            return kErrRtFail;
+    unsigned char *ptr = g_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
+        std::lock_guard<std::mutex> lock(g_setup_mutex);
+        ptr = g_scratch_ptr[dev].load(std::memory_order_relaxed);
+        if (ptr == nullptr) {
+            const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_static_scratch);
+            if (e != cudaSuccess || ptr == nullptr) {
+                std::fprintf(stderr, "[atb][ERROR] static scratch: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+                return kErrRtFail;
+            }
+            g_scratch_ptr[dev].store(ptr, std::memory_order_release);
         }
-        g_scratch_ptr[dev] = ptr;
     }
-    *out = g_scratch_ptr[dev];
+    *out = ptr;
     return 0;
 }
 
@@ -107,9 +123,23 @@ extern "C" int atb_b200_pa_decode_static_scratch(const atb_b200_pa_desc *desc, c
     if (d.batch > kMaxBatch) {
         return refuse("batch", d.batch, kMaxBatch);
     }
+    {
+        // a copy from this call's stack frame must not become a node of a captured graph
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(static_cast<cudaStream_t>(stream_v), &cap) != cudaSuccess) {
+            return kErrRtFail;
+        }
+        if (cap != cudaStreamCaptureStatusNone) {
+            std::fprintf(stderr, "[atb][ERROR] atb_b200_pa_decode_static_scratch: the stream is being captured; this entry "
+                                 "point uploads its plan from the caller's stack and cannot be part of a graph\n");
+            return kErrInvalidParam;
+        }
+    }
     const int group = d.num_heads / d.kv_heads;
-    const bool tma_ok = pa_tma_mma_supported(d.head_dim_k, d.head_dim_v, d.v_row_dim, d.block_size, group, d.q_dtype,
-                                             d.kv_dtype);
+    const bool tma_i8 = pa_tma_mma_i8_supported(d.head_dim_k, d.head_dim_v, d.v_row_dim, d.block_size, group, d.q_dtype,
+                                                d.kv_dtype);
+    const bool tma_ok = tma_i8 || pa_tma_mma_supported(d.head_dim_k, d.head_dim_v, d.v_row_dim, d.block_size, group,
+                                                       d.q_dtype, d.kv_dtype);
     const bool gen_ok = pa_generic_supported(d.head_dim_k, d.head_dim_v, d.q_dtype, d.kv_dtype);
     int kernel = d.kernel == ATB_B200_KERNEL_AUTO ? (tma_ok ? ATB_B200_KERNEL_TMA_MMA : ATB_B200_KERNEL_GENERIC) : d.kernel;
     if ((kernel == ATB_B200_KERNEL_TMA_MMA && !tma_ok) || (kernel == ATB_B200_KERNEL_GENERIC && !gen_ok) ||
@@ -284,8 +314,13 @@ extern "C" int atb_b200_pa_decode_static_scratch(const atb_b200_pa_desc *desc, c
     a.heads_per_cta = heads_per_cta;
     a.chunks_per_kvh = chunks_per_kvh;
     a.scale_log2 = d.qk_scale * 1.4426950408889634f;
-    cudaError_t e = kernel == ATB_B200_KERNEL_TMA_MMA ? launch_pa_tma_mma(a, d.q_dtype, d.kv_dtype, d.num_blocks, stream)
-                                                      : launch_pa_generic(a, d.q_dtype, d.kv_dtype, stream);
+    cudaError_t e;
+    if (kernel == ATB_B200_KERNEL_TMA_MMA) {
+        e = tma_i8 ? launch_pa_tma_mma_i8(a, d.q_dtype, d.num_blocks, stream)
+                   : launch_pa_tma_mma(a, d.q_dtype, d.kv_dtype, d.num_blocks, stream);
+    } else {
+        e = launch_pa_generic(a, d.q_dtype, d.kv_dtype, stream);
+    }
     if (e != cudaSuccess) {
         return kErrRtFail;
     }

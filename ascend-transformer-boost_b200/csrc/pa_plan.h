@@ -68,6 +68,7 @@ struct PaArgs {
     uint32_t *peer_flags[8];
     int32_t xchg_rank;
     uint32_t xchg_epoch;
+    uint32_t xchg_poll_limit; // polls before the wait for the peers gives up (0 = 2^22)
     // split MLA cache: rope parts of the query rows and of the cache rows (null = combined rows)
     const void *q_rope;
     const void *k_rope;

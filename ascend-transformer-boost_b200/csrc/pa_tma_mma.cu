@@ -20,6 +20,7 @@
 #include <mutex>
 #include "common.cuh"
 #include "kernels.h"
+#include "tma_encode.h"
 #include "pa_exchange.cuh"
 
 namespace atb_b200 {
@@ -112,6 +113,11 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     const int tok = item.tok_begin + (st0 + lane / bps) * kStageTokens + (lane % bps) * box_tok;
                     if (tok < item.tok_end) {
                         blk = bt[tok / a.block_size];
+                        if ((unsigned)blk >= (unsigned)a.num_blocks) {
+                            // a caller error: report it, and load a zero tile instead of whatever lies there
+                            atomicExch(a.plan.status, kStatusBadBlockId);
+                            blk = -1;
+                        }
                     }
                 }
                 const int cnt = min(st_per_batch, n_st - st0);
@@ -512,31 +518,13 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     }
 }
 
-using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn get_encode_fn()
-{
-    static EncodeFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess) {
-            fn = reinterpret_cast<EncodeFn>(p);
-        }
-    });
-    return fn;
-}
 
 // 4-D view [num_blocks][block_size][kv_heads][128] of a cache; one box = 64 tokens x 64 elements
 // of one kv head (128-byte rows, 128-byte swizzle).
 bool encode_cache_map(CUtensorMap *map, const void *base, int elem_dtype, int kv_heads, int block_size, int num_blocks,
                       bool bnsd)
 {
-    EncodeFn fn = get_encode_fn();
+    TmaEncodeFn fn = tma_encode_fn();
     if (fn == nullptr) {
         return false;
     }

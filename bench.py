@@ -3,12 +3,15 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--config i]
 
 One step = one decode step over the whole batch: scatter the step's new K/V tokens into the paged
-cache, then attention of every sequence's query token over its cached context.  The workload is
-benchmark configuration 2 (GQA decode, Llama-3-8B attention shape: bf16, batch 64, 32 q / 8 kv
-heads, head_dim 128, block_size 128, context_lens uniform in [2048,4096]) with seeded synthetic
-tensors.  With N > 1 the kv heads are sharded over the ranks (strong scaling, one process per GPU)
-and the per-shard outputs are gathered; the MLA configuration has a single kv head and is sharded by
-sequence instead (contiguous chunks of the batch per rank).
+cache, then attention of every sequence's query token over its cached context.  The headline workload is
+benchmark configuration 4, the largest one a single GPU holds (skewed long-context GQA decode: bf16,
+batch 256, 64 q / 8 kv heads, head_dim 128, block_size 128, context_lens lognormal(7.6, 1.0) clipped to
+[16, 32768], 3.4 GB of KV per step) with seeded synthetic tensors; on one GPU the other four
+configurations are measured in the same process and reported in the line's `configs` array (`--only`
+leaves them out, `--config i` picks another headline).  With N > 1 the kv heads are sharded over the ranks
+(strong scaling, one process per GPU) and the per-shard outputs are gathered; the MLA configuration has
+a single kv head and is sharded by sequence instead (contiguous chunks of the batch per rank).  At every
+N the output is checked against the CPU oracle (`max_abs_err_vs_oracle`).
 
 `--op block_copy | paged_cache_load | norm_rope_reshape` times one of the cache-management kernels instead
 (1 GPU, its own JSON line with the achieved HBM bandwidth); the default is the decode hot path.
@@ -36,6 +39,8 @@ import __graft_entry__ as entry  # noqa: E402
 L2_BYTES = 126 * 1000 * 1000
 METRIC = "paged_decode_kv_bandwidth"
 UNIT = "GB/s"
+HEADLINE_CONFIG = 3          # configuration 4 (skewed long-context GQA): the largest one a single GPU holds
+TOLERANCE = {"fp16": 2e-3, "bf16": 8e-3, "int8": 1e-2}   # max-abs error allowed against the oracle
 
 
 def measured_peak_gbs():
@@ -110,6 +115,15 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def host_threads():
+    """Host threads the CPU arms use: all of the box's cores, stated explicitly because a launcher may
+    export OMP_NUM_THREADS=1 (torch.distributed.run does), which OpenMP's default would follow."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def run_reference_arm(args, case, wl):
     """The reference's own CPU implementation of the path = its Python/torch golden, restated in C with
     OpenMP (oracle/pa_oracle.c) because the reference's C++ cannot be built without CANN; timed on
@@ -119,9 +133,9 @@ def run_reference_arm(args, case, wl):
     if rank != 0:
         return
     oracle.build()
-    threads = oracle.num_threads()
+    threads = host_threads()
     lens = wl.context_lens(case)
-    # bounded sample: the first sequences of the batch, at most ~64k tokens, so a step stays ~1 s
+    # bounded sample: the first sequences of the batch, at most ~256k tokens, so a step stays well under a second
     budget, take = 65536 * 4, 0
     while take < case.batch and lens[:take + 1].sum() <= budget:
         take += 1
@@ -136,7 +150,7 @@ def run_reference_arm(args, case, wl):
         oracle.reshape_and_cache(h["new_k"], h["new_v"], h["k_cache"], h["v_cache"], h["slot_mapping"])
         oracle.paged_attention(h["q"], h["k_cache"], h["v_cache"], h["block_tables"], h["context_lens"],
                                sub.qk_scale, sub.q_dtype, kv_dtype=sub.kvd, dv=sub.dv,
-                               k_descale=h.get("k_descale"), v_descale=h.get("v_descale"))
+                               k_descale=h.get("k_descale"), v_descale=h.get("v_descale"), nthreads=threads)
 
     for _ in range(args.warmup):
         step()
@@ -156,71 +170,52 @@ def run_reference_arm(args, case, wl):
     print(json.dumps(line))
 
 
-def cpu_baseline(case, wl, d, lens):
-    """The CPU oracle on the host cores over the whole workload (a few seconds), inputs from the GPU run."""
+def oracle_on_device_inputs(case, wl, d, lens, threads):
+    """The CPU oracle on the tensors the GPU run used (copied back from the device, so the cache holds what
+    ReshapeAndCache wrote).  Returns (output in the host encoding, seconds)."""
     import oracle
-    threads = oracle.num_threads()
     hk = wl.torch_to_host(d["k_cache"], case.kvd)
     hv = None if case.mla else wl.torch_to_host(d["v_cache"], case.kvd)
     hq = wl.torch_to_host(d["q"], case.q_dtype)
     kd = d["k_descale"].cpu().numpy() if "k_descale" in d else None
     vd = d["v_descale"].cpu().numpy() if "v_descale" in d else None
-    bt = d["block_tables_host"]
-    reps, t_total = 0, 0.0
-    out = None
-    while reps < 3 or (t_total < 10.0 and reps < 20):
-        t0 = time.perf_counter()
-        out = oracle.paged_attention(hq, hk, hv, bt, lens, case.qk_scale, case.q_dtype, kv_dtype=case.kvd, dv=case.dv,
-                                     k_descale=kd, v_descale=vd)
-        t_total += time.perf_counter() - t0
-        reps += 1
-    dt = t_total / reps
-    return {"value": wl.kv_bytes(case, lens) / dt / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": f"whole workload, mean of {reps} runs ({dt * 1e3:.0f} ms each)"}, out
+    t0 = time.perf_counter()
+    out = oracle.paged_attention(hq, hk, hv, d["block_tables_host"], lens, case.qk_scale, case.q_dtype, kv_dtype=case.kvd,
+                                 dv=case.dv, k_descale=kd, v_descale=vd, nthreads=threads)
+    dt = time.perf_counter() - t0
+
+    def again():
+        t1 = time.perf_counter()
+        oracle.paged_attention(hq, hk, hv, d["block_tables_host"], lens, case.qk_scale, case.q_dtype, kv_dtype=case.kvd,
+                               dv=case.dv, k_descale=kd, v_descale=vd, nthreads=threads)
+        return time.perf_counter() - t1
+    return out, dt, again
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=3000)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="b200")
-    ap.add_argument("--config", type=int, default=1, help="index into the benchmark configurations (default 1)")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
-                    help="N>1: attention stores into every rank's gathered buffer (p2p) or a separate NCCL all-gather")
-    ap.add_argument("--variant", default="plain", choices=["plain", "alibi", "mtp2", "mtp2_rows"],
-                    help="single-GPU side measurements of the attention kernel's other forms: an alibi mask shared by all "
-                         "sequences; two query tokens per sequence (parallel decoding, causal) planned per sequence "
-                         "(mtp2: one read of the cache) or per token (mtp2_rows)")
-    ap.add_argument("--op", default="decode", choices=["decode", "block_copy", "paged_cache_load", "norm_rope_reshape", "kv_cache"],
-                    help="decode (default): the hot path; the others time one cache-management kernel on 1 GPU")
-    args = ap.parse_args()
-    args.warmup = max(args.warmup, 3)
+class L2Flusher:
+    """Empties the L2 between timed steps when a GPU's share of the cache is not well above it: writes a
+    256 MB buffer, then reads another one, so that the step starts from a cold L2 that holds clean lines
+    (after the write alone it would hold ~126 MB of dirty lines whose write-back the step would pay for)."""
 
-    pkg = entry.load_package()
-    wl, capi = pkg.workloads, pkg.capi
-    if args.op != "decode":
-        run_cache_op_bench(args, capi)
-        return
-    if args.variant != "plain":
-        run_variant_bench(args, wl, capi)
-        return
-    case = wl.CONFIGS[args.config]
-    if args.impl == "reference":
-        run_reference_arm(args, case, wl)
-        return
+    def __init__(self, dev):
+        import torch
+        self.w = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        self.r = torch.zeros(64 << 20, dtype=torch.int32, device=dev)
 
+    def __call__(self):
+        self.w.zero_()
+        self.r.sum()
+
+
+def measure_decode(args, case, rt, steps, with_cpu_baseline):
+    """Times one configuration on this process's GPU (its shard of it when the job has several ranks):
+    device-timed steps with resident inputs, the attention kernel's own time from event pairs inside the same
+    steps, the end-to-end step through the operator API with host buffers, and the check against the CPU
+    oracle.  Returns the result dictionary on rank 0, None elsewhere."""
+    import ctypes
     import torch
     import torch.distributed as dist
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    capi.lib()
+    wl, capi, dev, world, rank = rt["wl"], rt["capi"], rt["dev"], rt["world"], rt["rank"]
 
     # kv heads are sharded over the ranks; the MLA cache has one kv head and is sharded by sequence
     by_sequence = world > 1 and case.kv_heads % world != 0
@@ -256,7 +251,6 @@ def main():
 
     # The timed loop calls the C ABI with pre-built arguments: at N = 8 a step lasts tens of
     # microseconds and per-call Python marshalling would otherwise bound the measurement.
-    import ctypes
     L = capi.lib()
     vp = ctypes.c_void_p
     rac_args = (vp(d["new_k"].data_ptr()), vp(d["new_v"].data_ptr()) if d["new_v"] is not None else None,
@@ -269,12 +263,13 @@ def main():
     plan_handle = plan.handle
     gathered_flat = gathered.view(-1) if gathered is not None else None
     out_flat = out.view(-1)
+    last_gathered = [None]
 
     def step():
         rc = L.atb_b200_pa_plan_prefetch(plan_handle, stream_ptr)      # plan upload leaves the critical stream
         rc |= L.atb_b200_reshape_and_cache(*rac_args)
         if p2p:
-            peers, _ = exchange.peers()
+            peers, last_gathered[0] = exchange.peers()
             rc |= L.atb_b200_pa_launch_gathered(plan_handle, tens_ref, ctypes.byref(peers), ws_ptr, ws_bytes, stream_ptr)
         else:
             rc |= L.atb_b200_pa_launch(plan_handle, tens_ref, ws_ptr, ws_bytes, stream_ptr)
@@ -288,53 +283,45 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # A step re-reads the same cache.  When this GPU's share of it is not well above the 126 MB L2
+    # (small configurations, or kv heads sharded over many GPUs) the L2 is flushed before every step
+    # and the steps are timed one by one so that the flush stays outside.
+    flush_l2 = wl.kv_bytes(shard, lens) < 2 * L2_BYTES
+    flush = L2Flusher(dev) if flush_l2 else None
+    n_prof = min(steps, 256)
     with torch.cuda.stream(stream):
-        plan.set_profiling(False)
+        # value, ms_per_step and the attention kernel's own time all come from the SAME steps: every launch carries a
+        # CUDA-event pair around the attention kernel (atb_b200_pa_plan_set_profiling)
+        plan.set_profiling(True)
         for _ in range(args.warmup):
             step()
         barrier()
-        sampler = ClockSampler(local_rank)
+        sampler = ClockSampler(rt["local_rank"])
         if rank == 0:
             sampler.start()
             time.sleep(0.25)
-        # A step re-reads the same cache.  When this GPU's share of it is not well above the 126 MB L2
-        # (small configurations, or kv heads sharded over many GPUs) the L2 is flushed before every step by
-        # writing a 256 MB buffer, and the steps are timed one by one so that the flush stays outside.
-        flush_l2 = wl.kv_bytes(shard, lens) < 2 * L2_BYTES
         if flush_l2:
-            flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-            n_timed = min(args.steps, 500)
-            evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_timed)]
+            evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
             barrier()
             for a0, a1 in evs:
-                flush_buf.zero_()
+                flush()
                 a0.record(stream)
                 step()
                 a1.record(stream)
             barrier()
-            ms = sum(a0.elapsed_time(a1) for a0, a1 in evs) / n_timed
-            args.steps = n_timed
+            ms = sum(a0.elapsed_time(a1) for a0, a1 in evs) / steps
         else:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             barrier()
             e0.record(stream)
-            for _ in range(args.steps):
+            for _ in range(steps):
                 step()
             e1.record(stream)
             barrier()
-            ms = e0.elapsed_time(e1) / args.steps
-        # second pass over the same steps with a CUDA-event pair around the attention kernel of every
-        # launch (kept out of the first pass: an event record between ReshapeAndCache and the
-        # attention kernel would defeat their programmatic dependent launch)
-        plan.set_profiling(True)
-        n_prof = min(args.steps, 256)
-        for _ in range(n_prof):
-            if flush_l2:
-                flush_buf.zero_()
-            step()
-        barrier()
+            ms = e0.elapsed_time(e1) / steps
         kernel_ms = float(np.mean([plan.kernel_ms(i) for i in range(n_prof)]))
         clocks = sampler.stop() if rank == 0 else None
+        plan.set_profiling(False)
     status = plan.device_status(ws.data_ptr(), stream.cuda_stream)
     if status != 0:
         raise RuntimeError(f"device status {status}")
@@ -344,55 +331,179 @@ def main():
         ms, kernel_ms = float(t[0]), float(t[1])
 
     # ---- end to end through the operator API with host buffers (rank-local shard, same step)
-    e2e = run_e2e(args, shard, wl, capi, d, lens, dev, world, gathered)
+    e2e = run_e2e(args, case, shard, rt, d, lens, gathered, steps, p2p)
     if world > 1:
         t = torch.tensor([e2e["ms"]], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e["ms"] = float(t[0])
 
+    # ---- parity: every rank runs the CPU oracle on its own shard's tensors; the per-rank references are
+    # all-gathered into the unsharded reference and every rank compares the WHOLE gathered output it holds
+    threads = max(1, host_threads() // world)
+    with torch.cuda.stream(stream):
+        step()
+        barrier()
+    ref_local, oracle_s, oracle_again = oracle_on_device_inputs(shard, wl, d, lens, threads)
+    if world == 1:
+        got = wl.torch_to_host(out, case.q_dtype)
+        err = float(np.abs(wl.to_f32(got, case.q_dtype) - wl.to_f32(ref_local, case.q_dtype)).max()) if got.size else 0.0
+    else:
+        ref_t = torch.from_numpy(ref_local.view(np.int16) if case.q_dtype == "bf16" else ref_local).to(dev)
+        ref_all = torch.empty((world,) + tuple(ref_t.shape), dtype=ref_t.dtype, device=dev)
+        dist.all_gather_into_tensor(ref_all.view(-1), ref_t.contiguous().view(-1))
+        if p2p:
+            mine = exchange.local_tensor(last_gathered[0], (case.batch, case.heads, Dv), d["q"].dtype)
+        elif by_sequence:
+            mine = gathered.reshape(case.batch, case.heads, Dv)
+        else:
+            mine = gathered.permute(1, 0, 2, 3).reshape(case.batch, case.heads, Dv)
+        if by_sequence:
+            ref_full = ref_all.reshape(case.batch, case.heads, Dv)
+        else:
+            ref_full = ref_all.permute(1, 0, 2, 3).reshape(case.batch, case.heads, Dv)
+        ref_full = ref_full.view(d["q"].dtype) if ref_full.dtype != d["q"].dtype else ref_full
+        e = (mine.float() - ref_full.float()).abs().max().reshape(1)
+        dist.all_reduce(e, op=dist.ReduceOp.MAX)
+        err = float(e[0])
+
+    res = None
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
         value = kv_bytes_global / (ms * 1e-3) / 1e9
         achieved = wl.kv_bytes(shard, lens) / (kernel_ms * 1e-3) / 1e9
-        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-                "vs_baseline": None, "dtype": case.q_dtype if case.kvd != "int8" else "int8/" + case.q_dtype,
-                "data": "synthetic",
-                "config": {"workload": case.name, "batch": case.batch, "q_heads": case.heads,
-                           "kv_heads": case.kv_heads, "head_dim": case.dk, "block_size": case.block_size,
-                           "context_tokens": int(global_lens.sum()), "kv_bytes_per_step": kv_bytes_global,
-                           "parallelism": ((f"sequence shard x{world} (one kv head: contiguous chunks of the batch per "
-                                            "rank), outputs gathered by NCCL all-gather") if by_sequence else
-                                           (f"kv-head shard x{world}, outputs gathered by " +
-                                            ("peer stores from the attention kernel" if p2p else "NCCL all-gather")))
-                           if world > 1 else "single GPU",
-                           "l2": ("KV cache per GPU (%.0f MB): L2 flushed before every step by a 256 MB write, steps "
-                                  "timed one by one" if flush_l2 else
-                                  "KV cache per GPU (%.0f MB) is larger than the 126 MB L2") %
-                                 (wl.kv_bytes(shard, lens) / 1e6),
-                           "kernel": {1: "generic", 2: "tma_mma", 3: "mla_tc5"}.get(info.kernel, "?"),
-                           "ctas": info.num_ctas, "partials": info.num_partials},
-                "tokens_per_s": case.batch / (ms * 1e-3),
-                "pct_of_8000_gbs": 100.0 * value / (8000.0 * world),
-                "pct_of_measured_peak": 100.0 * value / (peak * world),
-                "gpu_launches": launches_per_step * args.steps,
-                "clocks": clocks,
-                "e2e": {"value": kv_bytes_global / (e2e["ms"] * 1e-3) / 1e9, "unit": UNIT,
-                        "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
-                        "ms_per_step": e2e["ms"], "tokens_per_s": case.batch / (e2e["ms"] * 1e-3)},
-                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT,
-                             "frac": achieved / peak, "peak_kind": "of " + peak_kind,
-                             "kernel": "pa attention kernel, per GPU", "kernel_ms": kernel_ms,
-                             "traffic": ncu_traffic_bytes(case.name) if world == 1 else None}}
-        if world == 1 and not args.no_cpu_baseline:
-            base, ref_out = cpu_baseline(case, wl, d, lens)
-            line["cpu_baseline"] = base
-            err = np.abs(wl.to_f32(wl.torch_to_host(out, case.q_dtype), case.q_dtype) -
-                         wl.to_f32(ref_out, case.q_dtype)).max()
-            line["max_abs_err_vs_oracle"] = float(err)
-        print(json.dumps(line))
+        sm_mhz = clocks.get("sm_mhz") if clocks else None
+        res = {"workload": case.name, "value": value, "ms_per_step": ms, "steps": steps,
+               "dtype": case.q_dtype if case.kvd != "int8" else "int8/" + case.q_dtype,
+               "config": {"workload": case.name, "batch": case.batch, "q_heads": case.heads,
+                          "kv_heads": case.kv_heads, "head_dim": case.dk, "block_size": case.block_size,
+                          "context_tokens": int(global_lens.sum()), "kv_bytes_per_step": kv_bytes_global,
+                          "parallelism": ((f"sequence shard x{world} (one kv head: contiguous chunks of the batch per "
+                                           "rank), outputs gathered by NCCL all-gather") if by_sequence else
+                                          (f"kv-head shard x{world}, outputs gathered by " +
+                                           ("peer stores from the attention kernel" if p2p else "NCCL all-gather")))
+                          if world > 1 else "single GPU",
+                          "l2": ("KV cache per GPU (%.0f MB): L2 flushed before every step (256 MB written, then 256 MB "
+                                 "read so that no dirty lines remain), steps timed one by one" if flush_l2 else
+                                 "KV cache per GPU (%.0f MB) is larger than the 126 MB L2") %
+                                (wl.kv_bytes(shard, lens) / 1e6),
+                          "kernel": {1: "generic", 2: "tma_mma", 3: "mla_tc5"}.get(info.kernel, "?"),
+                          "ctas": info.num_ctas, "partials": info.num_partials},
+               "tokens_per_s": case.batch / (ms * 1e-3),
+               "pct_of_8000_gbs": 100.0 * value / (8000.0 * world),
+               "pct_of_measured_peak": 100.0 * value / (peak * world),
+               "gpu_launches": launches_per_step * steps,
+               "clocks": clocks,
+               "e2e": {"value": kv_bytes_global / (e2e["ms"] * 1e-3) / 1e9, "unit": UNIT,
+                       "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                       "ms_per_step": e2e["ms"], "tokens_per_s": case.batch / (e2e["ms"] * 1e-3),
+                       "gather": e2e["gather"]},
+               "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT,
+                            "frac": achieved / peak, "peak_kind": "of " + peak_kind,
+                            "kernel": "pa attention kernel, per GPU", "kernel_ms": kernel_ms,
+                            "kernel_ms_x_sm_mhz": kernel_ms * sm_mhz if sm_mhz else None,
+                            "traffic": ncu_traffic_bytes(case.name) if world == 1 else None},
+               "max_abs_err_vs_oracle": err,
+               "oracle_check": ("whole workload; every rank compares the gathered output it holds with the all-gathered "
+                                "per-shard oracle results, maximum over ranks") if world > 1 else "whole workload"}
+        if case.mla:
+            flops = wl.attn_flops(shard, lens)
+            res["roofline"]["tensor_tflops"] = flops / (kernel_ms * 1e-3) / 1e12
+        if with_cpu_baseline and world == 1:
+            reps, t_total = 1, oracle_s
+            while reps < 3 or (t_total < 10.0 and reps < 20):
+                t_total += oracle_again()
+                reps += 1
+            dt = t_total / reps
+            res["cpu_baseline"] = {"value": wl.kv_bytes(case, lens) / dt / 1e9, "unit": UNIT, "cores": threads,
+                                   "kind": "port", "sample": f"whole workload, mean of {reps} runs ({dt * 1e3:.0f} ms each)"}
+        elif world == 1:
+            res["cpu_baseline"] = {"value": wl.kv_bytes(case, lens) / oracle_s / 1e9, "unit": UNIT, "cores": threads,
+                                   "kind": "port", "sample": f"whole workload, one run ({oracle_s * 1e3:.0f} ms)"}
     if exchange is not None:
         exchange.close()
+    del d, out, gathered, ws, plan
+    torch.cuda.empty_cache()
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--config", type=int, default=HEADLINE_CONFIG,
+                    help="index into the benchmark configurations (default: the largest single-GPU one)")
+    ap.add_argument("--only", action="store_true", help="measure the chosen configuration alone (no `configs` array)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
+                    help="N>1: attention stores into every rank's gathered buffer (p2p) or a separate NCCL all-gather")
+    ap.add_argument("--variant", default="plain", choices=["plain", "alibi", "mtp2", "mtp2_rows"],
+                    help="single-GPU side measurements of the attention kernel's other forms: an alibi mask shared by all "
+                         "sequences; two query tokens per sequence (parallel decoding, causal) planned per sequence "
+                         "(mtp2: one read of the cache) or per token (mtp2_rows)")
+    ap.add_argument("--op", default="decode", choices=["decode", "block_copy", "paged_cache_load", "norm_rope_reshape", "kv_cache"],
+                    help="decode (default): the hot path; the others time one cache-management kernel on 1 GPU")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    pkg = entry.load_package()
+    wl, capi = pkg.workloads, pkg.capi
+    if args.op != "decode":
+        run_cache_op_bench(args, capi)
+        return
+    if args.variant != "plain":
+        run_variant_bench(args, wl, capi)
+        return
+    case = wl.CONFIGS[args.config]
+    if args.impl == "reference":
+        run_reference_arm(args, case, wl)
+        return
+
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    capi.lib()
+    rt = {"wl": wl, "capi": capi, "dev": dev, "world": world, "rank": rank, "local_rank": local_rank}
+
+    res = measure_decode(args, case, rt, args.steps, with_cpu_baseline=not args.no_cpu_baseline)
+    # the other configurations, measured in the same process (fewer steps; their CPU figure is the one oracle
+    # run that checks them)
+    others = []
+    if world == 1 and not args.only:
+        for i, c in enumerate(wl.CONFIGS):
+            if i == args.config:
+                continue
+            r = measure_decode(args, c, rt, min(args.steps, 200), with_cpu_baseline=False)
+            others.append({"workload": r["workload"], "value": r["value"], "ms_per_step": r["ms_per_step"],
+                           "kernel_ms": r["roofline"]["kernel_ms"], "dtype": r["dtype"],
+                           "roofline": {k: r["roofline"][k] for k in ("achieved", "frac", "kernel_ms", "kernel_ms_x_sm_mhz",
+                                                                       "traffic", "tensor_tflops") if k in r["roofline"]},
+                           "e2e": r["e2e"], "max_abs_err_vs_oracle": r["max_abs_err_vs_oracle"],
+                           "tolerance": TOLERANCE["int8" if c.kvd == "int8" else c.q_dtype],
+                           "tokens_per_s": r["tokens_per_s"], "cpu_baseline": r["cpu_baseline"],
+                           "clocks": r["clocks"], "l2": r["config"]["l2"], "kernel": r["config"]["kernel"]})
+    if rank == 0:
+        line = {"metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": world, "steps": res["steps"],
+                "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": res["dtype"], "data": "synthetic", "config": res["config"],
+                "tokens_per_s": res["tokens_per_s"], "pct_of_8000_gbs": res["pct_of_8000_gbs"],
+                "pct_of_measured_peak": res["pct_of_measured_peak"], "gpu_launches": res["gpu_launches"],
+                "clocks": res["clocks"], "e2e": res["e2e"], "roofline": res["roofline"],
+                "max_abs_err_vs_oracle": res["max_abs_err_vs_oracle"],
+                "tolerance": TOLERANCE["int8" if case.kvd == "int8" else case.q_dtype],
+                "oracle_check": res["oracle_check"]}
+        if "cpu_baseline" in res:
+            line["cpu_baseline"] = res["cpu_baseline"]
+        if others:
+            line["configs"] = others
+        print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
@@ -578,16 +689,19 @@ def run_cache_op_bench(args, capi):
                                    "peak_kind": "of " + peak_kind, "kernel": args.op, "kernel_ms": ms, "traffic": None}}))
 
 
-def run_e2e(args, case, wl, capi, d, lens, dev, world, gathered):
+def run_e2e(args, full_case, case, rt, d, lens, gathered, steps, p2p):
     """The same step through atb::Operation Setup/Execute with HOST buffers: every step copies the
     query, the new K/V tokens, slot_mapping, block_tables and context_lens from pinned host memory
     (packed in one staging area, one H2D copy), re-plans from the host context_lens, runs
     ReshapeAndCache + PagedAttention and reads the output back to pinned host memory, then waits for
     it.  The KV cache itself is the path's resident state and stays in HBM.  The operator calls use
-    pre-built tensor records (a C++ caller builds its VariantPack once, too)."""
+    pre-built tensor records (a C++ caller builds its VariantPack once, too).  `case` is this rank's
+    shard of `full_case`; with sharded heads the operator stores into every rank's gathered buffer
+    (atb_b200_context_set_gather) and the step reads the whole gathered output back."""
     import ctypes
     import torch
     import torch.distributed as dist
+    wl, capi, dev, world, rank = rt["wl"], rt["capi"], rt["dev"], rt["world"], rt["rank"]
     T = capi.atb_tensor
     stream = torch.cuda.Stream()
     names = ["q", "new_k", "block_tables", "slot_mapping", "context_lens"] + ([] if case.mla else ["new_v"])
@@ -607,7 +721,16 @@ def run_e2e(args, case, wl, capi, d, lens, dev, world, gathered):
     lens_off = offs["context_lens"]
     lens_host = host_pack[lens_off:lens_off + 4 * case.batch].view(torch.int32).numpy()
     out = torch.zeros((case.batch, case.heads, case.dv), dtype=d["q"].dtype, device=dev)
-    out_host = torch.empty_like(out, device="cpu").pin_memory()
+    exchange = None
+    if p2p:
+        exchange = capi.PeerExchange(case.batch * full_case.heads * case.dv * out.element_size(), full_case.heads,
+                                     rank * case.heads)
+        result_shape = (case.batch, full_case.heads, case.dv)
+    elif world > 1:
+        result_shape = tuple(gathered.shape)
+    else:
+        result_shape = tuple(out.shape)
+    out_host = torch.empty(result_shape, dtype=out.dtype).pin_memory()
     ctx = capi.Context(stream.cuda_stream)
     rac_param = capi.ReshapeAndCacheParam()
     rac_param.kvCacheCfg = 1 if case.mla else 0
@@ -632,7 +755,7 @@ def run_e2e(args, case, wl, capi, d, lens, dev, world, gathered):
     pa_out = [T(out)]
     ws_bytes = pa.setup(pa_in, pa_out, ctx)
     ws = torch.empty(max(ws_bytes * 2, 256), dtype=torch.uint8, device=dev)
-    d2h = out.numel() * out.element_size()
+    d2h = out_host.numel() * out_host.element_size()
 
     L = capi.lib()
     arr = capi.Operation._arr
@@ -641,6 +764,7 @@ def run_e2e(args, case, wl, capi, d, lens, dev, world, gathered):
     need = ctypes.c_uint64(0)
     ws_ptr, ws_len = ctypes.c_void_p(ws.data_ptr()), ws.numel()
     gathered_flat = gathered.view(-1) if gathered is not None else None
+    gathered_views = {}
 
     def step():
         dev_pack.copy_(host_pack, non_blocking=True)
@@ -649,12 +773,21 @@ def run_e2e(args, case, wl, capi, d, lens, dev, world, gathered):
         rc = L.atb_b200_operation_setup(rac.handle, rac_i, n_ri, rac_o, n_ro, ctypes.byref(need), ctx.handle)
         rc |= L.atb_b200_operation_setup(pa.handle, pa_i, n_pi, pa_o, n_po, ctypes.byref(need), ctx.handle)
         rc |= L.atb_b200_operation_execute(rac.handle, rac_i, n_ri, rac_o, n_ro, None, 0, ctx.handle)
+        if p2p:
+            peers, local_ptr = exchange.peers()
+            rc |= L.atb_b200_context_set_gather(ctx.handle, ctypes.byref(peers))
         rc |= L.atb_b200_operation_execute(pa.handle, pa_i, n_pi, pa_o, n_po, ws_ptr, ws_len, ctx.handle)
         if rc != 0 or need.value > ws_len:
             raise RuntimeError(f"operator call failed ({rc})")
-        if world > 1:
+        if p2p:
+            if local_ptr not in gathered_views:
+                gathered_views[local_ptr] = exchange.local_tensor(local_ptr, result_shape, out.dtype)
+            out_host.copy_(gathered_views[local_ptr], non_blocking=True)
+        elif world > 1:
             dist.all_gather_into_tensor(gathered_flat, out.view(-1))
-        out_host.copy_(out, non_blocking=True)
+            out_host.copy_(gathered, non_blocking=True)
+        else:
+            out_host.copy_(out, non_blocking=True)
         stream.synchronize()                          # the caller consumes the result every step
 
     torch.cuda.synchronize()
@@ -666,22 +799,26 @@ def run_e2e(args, case, wl, capi, d, lens, dev, world, gathered):
         torch.cuda.synchronize()
         if wl.kv_bytes(case, lens) < 2 * L2_BYTES:
             # this GPU's cache is not well above the L2: flush it before every step, outside the step's clock
-            flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+            flush = L2Flusher(dev)
             total = 0.0
-            for _ in range(args.steps):
-                flush_buf.zero_()
+            for _ in range(steps):
+                flush()
                 torch.cuda.synchronize()
                 t0 = time.perf_counter()
                 step()
                 total += time.perf_counter() - t0
-            ms = total * 1e3 / args.steps
+            ms = total * 1e3 / steps
         else:
             t0 = time.perf_counter()
-            for _ in range(args.steps):
+            for _ in range(steps):
                 step()
             torch.cuda.synchronize()
-            ms = (time.perf_counter() - t0) * 1e3 / args.steps
-    return {"ms": ms, "h2d": h2d, "d2h": d2h}
+            ms = (time.perf_counter() - t0) * 1e3 / steps
+    if exchange is not None:
+        exchange.close()
+    how = "single GPU" if world == 1 else ("peer stores from the attention kernel (operator-level gather)" if p2p
+                                           else "NCCL all-gather")
+    return {"ms": ms, "h2d": h2d, "d2h": d2h, "gather": how}
 
 
 if __name__ == "__main__":

@@ -189,8 +189,9 @@ int atb_b200_pa_plan_prefetch(atb_b200_pa_plan *plan, void *stream);
  * first call) as mapped in THIS process (atb_b200_peer_buffer_*).  `epoch` starts at 1 and grows by
  * one per call on every rank.  A rank may run one step ahead of a slow peer, so alternate between
  * two gathered buffers from call to call.  The wait is bounded; a peer that never arrives sets the
- * status word (atb_b200_pa_plan_device_status) instead of hanging the GPU.  Only the TMA kernels
- * (head_dim 128) support this path.
+ * status word instead of hanging the GPU, and the call has still returned ATB_B200_OK (it only enqueues):
+ * read atb_b200_pa_plan_device_status before trusting the gathered buffer whenever a rank may have
+ * stalled (status 1 = the buffer is incomplete).  Only the TMA kernels (head_dim 128) support this path.
  */
 typedef struct atb_b200_pa_peers {
     int32_t world;        /* ranks, 1..8 */
@@ -200,7 +201,9 @@ typedef struct atb_b200_pa_peers {
     void *peer_out[8];
     uint32_t *peer_flags[8];
     uint32_t epoch;
-    uint32_t reserved;
+    uint32_t poll_limit;  /* polls (about 0.2 us each) before the wait for the peers gives up; 0 = 2^22 (about a second).
+                             Match it to the host skew between the ranks: a rank that enqueues its kernel later than
+                             this makes every other rank give up. */
 } atb_b200_pa_peers;
 
 int atb_b200_pa_launch_gathered(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *tensors,
@@ -287,6 +290,12 @@ typedef struct atb_b200_tensor {
 int atb_b200_context_create(void **context);
 int atb_b200_context_set_stream(void *context, void *stream);
 int atb_b200_context_destroy(void *context);
+/* Extension with no counterpart in the reference (there a model graph runs AllGatherOperation after attention,
+ * src/ops/ops_infer/all_gather/all_gather_operation.cpp:79-89): while `peers` is set on a context, every
+ * PagedAttention Execute on it takes the atb_b200_pa_launch_gathered path - the kernel stores this rank's heads
+ * into every rank's gathered buffer and attnOut is left untouched.  The struct is copied; set it again before
+ * every Execute (the epoch grows by one per step and the gathered buffers alternate), NULL switches it off. */
+int atb_b200_context_set_gather(void *context, const atb_b200_pa_peers *peers);
 
 /* `param` points at an atb::infer::PagedAttentionParam (120 bytes) / ReshapeAndCacheParam (24 bytes). */
 int atb_b200_operation_create_paged_attention(const void *param, uint64_t param_bytes, void **operation);

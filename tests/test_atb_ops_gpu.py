@@ -155,3 +155,46 @@ def test_paged_attention_op_mla_and_qscale():
                                      mlaVHeadSize=512)
     out = _run_pa_op(case, h, param)
     assert max_abs_err(out, oracle_out(case, h), case.q_dtype) <= tol_for(case)
+
+
+def test_paged_attention_operation_stores_into_the_gathered_buffer():
+    """Heads sharded over the GPUs of a node, driven through the operator: with gather peers set on the context the
+    Execute stores this rank's heads into the gathered [tokens, all heads, Dv] buffer and leaves attnOut alone.
+    One GPU stands for a world of one here (the 2-GPU form is in test_multi_gpu.py)."""
+    case = wl.Case("op_gather", batch=5, heads=16, kv_heads=4, q_dtype="bf16", ctx=("uniform", 100, 2500), seed=91)
+    h = wl.make_host_inputs(case)
+    d = host_inputs_to_device(case, h)
+    T = capi.atb_tensor
+    total_heads, offset = 48, 16                         # this rank owns heads 16..31 of a 48-head model
+    out = torch.full((case.batch, case.heads, case.dv), 7.0, dtype=torch.bfloat16, device="cuda")
+    gathered = torch.zeros((case.batch, total_heads, case.dv), dtype=torch.bfloat16, device="cuda")
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    lens_dev = torch.from_numpy(h["context_lens"]).cuda()
+    ins = [T(d["q"]), T(d["k_cache"]), T(d["v_cache"]), T(d["block_tables"]), T(lens_dev, host=h["context_lens"])]
+    outs = [T(out)]
+    op = capi.Operation(capi.PagedAttentionParam(headNum=case.heads, kvHeadNum=case.kv_heads, qkScale=case.qk_scale))
+    ctx = _new_ctx()
+    peers = capi.PaPeers()
+    peers.world, peers.rank, peers.total_heads, peers.head_offset = 1, 0, total_heads, offset
+    peers.peer_out[0], peers.peer_flags[0] = gathered.data_ptr(), flags.data_ptr()
+    ref = oracle_out(case, h)
+    for step in (1, 2):
+        peers.epoch = step
+        ctx.set_gather(peers)
+        ws_bytes = op.setup(ins, outs, ctx)
+        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device="cuda")
+        op.execute(ins, outs, ws.data_ptr(), ws_bytes, ctx)
+        torch.cuda.synchronize()
+        got = wl.torch_to_host(gathered[:, offset:offset + case.heads].contiguous(), case.q_dtype)
+        assert max_abs_err(got, ref, case.q_dtype) <= tol_for(case)
+        assert float(gathered[:, :offset].float().abs().max()) == 0.0
+        assert float(out.float().min()) == 7.0 and float(out.float().max()) == 7.0
+        assert int(flags[0]) == step
+        gathered.zero_()
+    # switched off again: the ordinary output
+    ctx.set_gather(None)
+    ws_bytes = op.setup(ins, outs, ctx)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device="cuda")
+    op.execute(ins, outs, ws.data_ptr(), ws_bytes, ctx)
+    torch.cuda.synchronize()
+    assert max_abs_err(wl.torch_to_host(out, case.q_dtype), ref, case.q_dtype) <= tol_for(case)

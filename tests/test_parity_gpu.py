@@ -192,7 +192,7 @@ def test_plan_reuse_over_decode_steps():
 
 def test_bad_block_id_is_reported_not_faulted():
     """A block id outside the cache (a caller bug) must not fault the GPU: the generic kernel skips the
-    token and sets the status word; the TMA kernels read zeros (out-of-bounds TMA fill)."""
+    token, the TMA kernels load a zero tile in its place, and all of them set the status word to 2."""
     case = wl.Case("badblk", batch=2, heads=8, kv_heads=2, dk=96, dv=96, block_size=16, q_dtype="fp16",
                    ctx=("list", [40, 33]), seed=71)
     h = wl.make_host_inputs(case)
@@ -209,10 +209,28 @@ def test_bad_block_id_is_reported_not_faulted():
     h2["block_tables"] = h2["block_tables"].copy()
     h2["block_tables"][0, 1] = -1
     d2 = host_inputs_to_device(case2, h2)
-    out2 = capi.paged_attention(d2["q"], d2["k_cache"], d2["v_cache"], d2["block_tables"], h2["context_lens"],
-                                case2.qk_scale)
+    out2, plan2, ws2 = capi.paged_attention(d2["q"], d2["k_cache"], d2["v_cache"], d2["block_tables"], h2["context_lens"],
+                                            case2.qk_scale, return_plan=True)
     torch.cuda.synchronize()
+    assert plan2.info.kernel == capi.KERNEL_TMA_MMA
+    assert plan2.device_status(ws2.data_ptr(), capi.torch_stream_ptr()) == 2
     assert torch.isfinite(out2.float()).all()
+    # the int8 and the MLA kernels report the same caller error
+    for case3 in (wl.Case("badblk_i8", batch=2, heads=8, kv_heads=2, q_dtype="fp16", kv_dtype="int8",
+                          ctx=("list", [300, 200]), seed=73),
+                  wl.Case("badblk_mla", batch=2, heads=16, kv_heads=1, dk=576, dv=512, q_dtype="bf16", mla=True,
+                          ctx=("list", [300, 200]), seed=74)):
+        h3 = wl.make_host_inputs(case3)
+        h3["block_tables"] = h3["block_tables"].copy()
+        h3["block_tables"][1, 0] = h3["num_blocks"]
+        d3 = host_inputs_to_device(case3, h3)
+        out3, plan3, ws3 = capi.paged_attention(d3["q"], d3["k_cache"], d3["v_cache"], d3["block_tables"],
+                                                h3["context_lens"], case3.qk_scale, dv=case3.dv,
+                                                k_descale=d3["k_descale"], v_descale=d3["v_descale"], return_plan=True)
+        torch.cuda.synchronize()
+        assert plan3.info.kernel != capi.KERNEL_GENERIC, case3.name
+        assert plan3.device_status(ws3.data_ptr(), capi.torch_stream_ptr()) == 2, case3.name
+        assert torch.isfinite(out3.float()).all(), case3.name
 
 
 def _random_cases(n, seed, block_sizes=(128,)):
