@@ -681,6 +681,73 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             // the next range's first P.V overwrites O: all reads of O must be done first.  It cannot start
             // before the next P tile is signalled by these same warps, which orders it after this point.
             tc_fence_before();
+            if (item.slot >= 0 && a.plan.counters != nullptr) {
+                // In-kernel merge, warp by warp (no CTA-wide barrier): warp w of every range writes head rows
+                // 16w..16w+15 of its partial; the warp that arrives last on the (sequence, 64-head column, w) counter
+                // finds all of them written (fence + counter, nobody spins) and combines them with their
+                // log-sum-exp weights, as the separate combine kernel would.
+                __threadfence();
+                __syncwarp();
+                const int n_parts = a.plan.seq_nparts[item.seq];
+                int last = 0;
+                if (lane == 0) {
+                    last = atomicAdd(&a.plan.counters[(item.seq * cols + col) * 4 + warp], 1) == n_parts - 1 ? 1 : 0;
+                }
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __threadfence();
+                    const int pbase = a.plan.seq_part_base[item.seq];
+                    // a lane per 16 consecutive dims of one head row: every load and store is contiguous
+                    for (int r = warp * 16; r < min(warp * 16 + 16, nh); ++r) {
+                        const int hh = head0 + r;
+                        const float *lse = a.plan.part_lse + (int64_t)pbase * a.num_heads + hh;
+                        float mx = -INFINITY;
+                        for (int i = 0; i < n_parts; ++i) {
+                            mx = fmaxf(mx, __ldcg(lse + (int64_t)i * a.num_heads));
+                        }
+                        float wsum = 0.f;
+                        for (int i = 0; i < n_parts; ++i) {
+                            wsum += exp2f(__ldcg(lse + (int64_t)i * a.num_heads) - mx);
+                        }
+                        const float inv_w = 1.f / wsum;
+                        float acc[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            acc[j] = 0.f;
+                        }
+                        const float *po = a.plan.part_o + ((int64_t)pbase * a.num_heads + hh) * kDv + lane * 16;
+                        for (int i = 0; i < n_parts; ++i) {
+                            const float w = exp2f(__ldcg(lse + (int64_t)i * a.num_heads) - mx) * inv_w;
+                            const float4 *src = reinterpret_cast<const float4 *>(po + (int64_t)i * a.num_heads * kDv);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float4 v = __ldcg(src + j);
+                                acc[4 * j] = fmaf(w, v.x, acc[4 * j]);
+                                acc[4 * j + 1] = fmaf(w, v.y, acc[4 * j + 1]);
+                                acc[4 * j + 2] = fmaf(w, v.z, acc[4 * j + 2]);
+                                acc[4 * j + 3] = fmaf(w, v.w, acc[4 * j + 3]);
+                            }
+                        }
+                        uint32_t w8[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            w8[j] = Elem<T>::pack2(acc[2 * j], acc[2 * j + 1]);
+                        }
+                        T *dst = static_cast<T *>(a.out) + ((int64_t)item.seq * a.num_heads + hh) * kDv + lane * 16;
+                        if (out_wide) {
+                            st_global_v8(dst, w8);
+                        } else {
+                            *reinterpret_cast<uint4 *>(dst) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
+                            *reinterpret_cast<uint4 *>(dst + 8) = make_uint4(w8[4], w8[5], w8[6], w8[7]);
+                        }
+                        if (lane == 0 && a.lse_out != nullptr) {
+                            // log-sum-exp of the whole sequence from its ranges' (log2 domain), as a natural log
+                            static_cast<T *>(a.lse_out)[(int64_t)item.seq * a.num_heads + hh] =
+                                Elem<T>::from_float((mx + log2f(wsum)) * 0.6931471805599453f);
+                        }
+                    }
+                }
+            }
         }
     }
 
