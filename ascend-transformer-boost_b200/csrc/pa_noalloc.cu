@@ -162,7 +162,7 @@ extern "C" int atb_b200_pa_decode_static_scratch(const atb_b200_pa_desc *desc, c
 
     // ---- work split on the stack: same balanced cut as the regular planner, fixed capacity
     const int heads_per_cta = kernel == ATB_B200_KERNEL_TMA_MMA ? 8 : pa_generic_heads_per_cta(d.head_dim_k, d.head_dim_v);
-    const int chunks_per_kvh = kernel == ATB_B200_KERNEL_TMA_MMA ? 1 : (group + heads_per_cta - 1) / heads_per_cta;
+    const int chunks_per_kvh = (group + heads_per_cta - 1) / heads_per_cta;
     const int ctas_per_sm = kernel == ATB_B200_KERNEL_TMA_MMA ? 2 : 4;
     const int cols = d.kv_heads * chunks_per_kvh;
     const int64_t max_ctx = (int64_t)d.max_blocks_per_seq * d.block_size;

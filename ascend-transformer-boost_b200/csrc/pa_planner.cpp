@@ -96,7 +96,7 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
     if (d.q_per_seq > 1) {
         // (token, head) pairs as the columns of one CTA of the fp16 / bf16 D = 128 kernel (at most 8 pairs per kv head,
         // which is what its head limit already says about num_heads / kv_heads), or as the rows of the MLA kernel
-        const bool tma_pairs = tma_ok && d.kv_dtype != kInt8 && d.rope_dim == 0;
+        const bool tma_pairs = tma_ok && d.kv_dtype != kInt8 && d.rope_dim == 0 && group <= 8;
         const int want = tma_pairs ? ATB_B200_KERNEL_TMA_MMA : ATB_B200_KERNEL_MLA_TC5;
         if ((!tma_pairs && !mla_ok) || (d.score_mods & ATB_B200_SCORE_LOGN) != 0 ||
             (kernel != ATB_B200_KERNEL_AUTO && kernel != want)) {
@@ -118,7 +118,7 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
     p->sm_count = sm_count;
     if (kernel == ATB_B200_KERNEL_TMA_MMA) {
         p->heads_per_cta = 8;
-        p->chunks_per_kvh = 1;
+        p->chunks_per_kvh = (group + 7) / 8; // more than 8 heads per kv head: several columns over the same K/V tiles
         p->ctas_per_sm = 2;
     } else if (kernel == ATB_B200_KERNEL_MLA_TC5) {
         p->heads_per_cta = 64;

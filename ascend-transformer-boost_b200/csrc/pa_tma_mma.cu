@@ -71,7 +71,11 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int cols = a.plan.cols;
     const int grp = blockIdx.x / cols;
-    const int kvh = blockIdx.x - grp * cols;
+    // a column is (kv head, chunk of 8 query heads): groups of more than 8 heads per kv head take several
+    // columns, whose CTAs read the same K/V tiles at about the same time (once from HBM, again from L2)
+    const int col = blockIdx.x - grp * cols;
+    const int kvh = col / a.chunks_per_kvh;
+    const int chunk0 = (col - kvh * a.chunks_per_kvh) * 8; // first head of this CTA within its kv head's group
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -162,13 +166,14 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     const int g = lane >> 2, c = lane & 3;
     const T *q = static_cast<const T *>(a.q);
     const uint32_t stages_u32 = smem_u32(stages);
-    const int group = a.group;
+    const int group = min(8, a.group - chunk0); // query heads (columns) of this CTA
     // Column x of this CTA (0..7) -> head index in the [.., num_heads, 128] tensors.  With q_per_seq query tokens per
     // sequence those tensors hold q_per_seq x real-heads rows per sequence and a column is a (token, head) pair:
-    // token x / gr, head kvh * gr + x % gr, gr = real heads per kv head.
+    // token x / gr, head kvh * gr + x % gr, gr = real heads per kv head (at most 8 pairs: one chunk).
     const int qps = kMods ? a.q_per_seq : 1;
-    const int gr = group / qps, heads_real = a.num_heads / qps;
-    auto head_of = [&](int x) { return qps > 1 ? (x / gr) * heads_real + kvh * gr + x % gr : kvh * group + x; };
+    const int gr = a.group / qps, heads_real = a.num_heads / qps;
+    const int hbase = kvh * gr + chunk0;
+    auto head_of = [&](int x) { return qps > 1 ? (x / gr) * heads_real + hbase + x % gr : hbase + x; };
 
     for (int it = item_begin; it < item_end; ++it) {
         const PaItem item = a.plan.items[it];
@@ -199,8 +204,8 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 const T *mb = static_cast<const T *>(a.mask) +
                               (int64_t)(a.mask_rows != nullptr ? a.mask_rows[item.seq] : item.seq) * a.mask_bs;
                 const int x0 = min(2 * c, group - 1), x1 = min(2 * c + 1, group - 1); // padding columns read a real one's row
-                mrow0 = mb + (int64_t)(x0 / gr) * a.mask_qs + (int64_t)(kvh * gr + x0 % gr) * a.mask_hs;
-                mrow1 = mb + (int64_t)(x1 / gr) * a.mask_qs + (int64_t)(kvh * gr + x1 % gr) * a.mask_hs;
+                mrow0 = mb + (int64_t)(x0 / gr) * a.mask_qs + (int64_t)(hbase + x0 % gr) * a.mask_hs;
+                mrow1 = mb + (int64_t)(x1 / gr) * a.mask_qs + (int64_t)(hbase + x1 % gr) * a.mask_hs;
             }
         }
         // causal parallel decoding: the query token of column x sees the sequence's first len - (qps - 1 - x / gr) tokens
@@ -461,7 +466,7 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             named_bar_sync(1, kConsumerWarps * 32);
             const int n_parts = a.plan.seq_nparts[item.seq];
             if (threadIdx.x == 0) {
-                const int old = atomicAdd(&a.plan.counters[item.seq * cols + kvh], 1);
+                const int old = atomicAdd(&a.plan.counters[item.seq * cols + col], 1);
                 sm_l[0] = (old == n_parts - 1) ? 1.f : 0.f;
             }
             named_bar_sync(1, kConsumerWarps * 32);
@@ -585,7 +590,7 @@ template <typename T> cudaError_t launch_typed(const PaArgs &args, const CUtenso
 
 bool pa_tma_mma_supported(int dk, int dv, int v_row_dim, int block_size, int group, int q_dtype, int kv_dtype)
 {
-    return dk == 128 && dv == 128 && v_row_dim == 128 && (block_size == 16 || block_size == 32 || block_size == 64 || block_size == 128 || block_size == 256) && group >= 1 && group <= 8 &&
+    return dk == 128 && dv == 128 && v_row_dim == 128 && (block_size == 16 || block_size == 32 || block_size == 64 || block_size == 128 || block_size == 256) && group >= 1 &&
            (q_dtype == kFp16 || q_dtype == kBf16) && kv_dtype == q_dtype;
 }
 

@@ -10,7 +10,9 @@
 //     change the softmax; Q is pre-scaled by kDescale once per token range.  Likewise
 //     out_d = vDescale_d * (sum_t p_t v_td / l + vOffset_d), applied when the range is written;
 //   * int8 -> fp16 is exact and done with byte permutes: (x ^ 0x80) placed in the mantissa of
-//     1024.0 gives 1152 + x, minus 1152.  ldmatrix moves byte pairs, so the k index of Q.K^T and
+//     1024.0 gives 1152 + x; the bias is never subtracted from the operands (three ALU instructions
+//     per four cache bytes): it cancels in the softmax for K and is taken out of the accumulated
+//     output once per token range for V.  ldmatrix moves byte pairs, so the k index of Q.K^T and
 //     the row index of V^T.P^T are permuted consistently between the two operands;
 //   * the tensor-core tiles run in fp16 for both fp16 and bf16 queries (P in fp16 is at least as
 //     precise as the golden's rounding of P to the query dtype).
@@ -39,26 +41,27 @@ constexpr int kXbufFloats = 32 * 32;                // one warp's O fragments
 constexpr int kFinalStride = 132;                   // padded [head][dim] row (floats)
 constexpr int kSmemBytes = kStages * kStageBytes + (kXbufFloats + 8 * kFinalStride + 64) * 4 + 2 * kStages * 8 + 1024;
 
-// Four int8 in a register -> two half2.  (x ^ 0x80) is x + 128 as an unsigned byte; placed under the
-// high byte 0x64 it reads as the half 1024 + 128 + x, and subtracting 1152 leaves x exactly.
-__device__ __forceinline__ uint32_t h2_minus_1152(uint32_t v)
-{
-    const __half2 r = __hsub2(*reinterpret_cast<const __half2 *>(&v), __half2half2(__ushort_as_half((unsigned short)0x6480)));
-    return *reinterpret_cast<const uint32_t *>(&r);
-}
+// Four int8 in a register -> two half2 holding 1152 + x.  (x ^ 0x80) is x + 128 as an unsigned byte; placed under
+// the high byte 0x64 it reads as the half 1024 + 128 + x, exactly.  The 1152 is never subtracted from the operands:
+//   * in Q.K^T it adds 1152 * sum_d q_d to every score of a head, the same for every token, which the softmax
+//     cancels (like the kOffset term);
+//   * in P.V it adds 1152 * sum_t p_t to every output dim of a head; the kernel keeps that sum of the ROUNDED
+//     probabilities (the values the tensor cores multiply) and subtracts it once per token range.
+// Products of two 11-bit significands are exact in the fp32 accumulators, so nothing is lost but ~4 of their 24 bits.
+constexpr float kI8Bias = 1152.f;
 // lo = (byte0, byte1), hi = (byte2, byte3)
 __device__ __forceinline__ void i8x4_to_h2x2(uint32_t w, uint32_t &lo, uint32_t &hi)
 {
     const uint32_t x = w ^ 0x80808080u;
-    lo = h2_minus_1152(__byte_perm(x, 0x64646464u, 0x4140));
-    hi = h2_minus_1152(__byte_perm(x, 0x64646464u, 0x4342));
+    lo = __byte_perm(x, 0x64646464u, 0x4140);
+    hi = __byte_perm(x, 0x64646464u, 0x4342);
 }
 // even = (byte0, byte2), odd = (byte1, byte3)
 __device__ __forceinline__ void i8x4_to_h2x2_even_odd(uint32_t w, uint32_t &even, uint32_t &odd)
 {
     const uint32_t x = w ^ 0x80808080u;
-    even = h2_minus_1152(__byte_perm(x, 0x64646464u, 0x4240));
-    odd = h2_minus_1152(__byte_perm(x, 0x64646464u, 0x4341));
+    even = __byte_perm(x, 0x64646464u, 0x4240);
+    odd = __byte_perm(x, 0x64646464u, 0x4341);
 }
 
 // Writes 8 output elements of (sequence, local head h) to the output tensor - or, when the heads are
@@ -94,7 +97,11 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int cols = a.plan.cols;
     const int grp = blockIdx.x / cols;
-    const int kvh = blockIdx.x - grp * cols;
+    // a column is (kv head, chunk of 8 query heads): groups of more than 8 heads per kv head take several
+    // columns, whose CTAs read the same K/V tiles at about the same time (once from HBM, again from L2)
+    const int col = blockIdx.x - grp * cols;
+    const int kvh = col / a.chunks_per_kvh;
+    const int head0 = kvh * a.group + (col - kvh * a.chunks_per_kvh) * 8; // first query head of this CTA
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -180,7 +187,7 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
     const int g = lane >> 2, c = lane & 3;
     const T *q = static_cast<const T *>(a.q);
     const uint32_t stages_u32 = smem_u32(stages);
-    const int group = a.group;
+    const int group = min(8, kvh * a.group + a.group - head0); // query heads of this CTA
 
     for (int it = item_begin; it < item_end; ++it) {
         const PaItem item = a.plan.items[it];
@@ -190,7 +197,7 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
         uint32_t qf[8][2];
         {
             const bool valid = g < group;
-            const T *qp = q + ((int64_t)item.seq * a.num_heads + kvh * group + (valid ? g : 0)) * 128;
+            const T *qp = q + ((int64_t)item.seq * a.num_heads + head0 + (valid ? g : 0)) * 128;
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
                 float f[4] = {0.f, 0.f, 0.f, 0.f};
@@ -214,6 +221,7 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
             o[mt][0] = o[mt][1] = o[mt][2] = o[mt][3] = 0.f;
         }
         float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+        float lr0 = 0.f, lr1 = 0.f; // sums of the probabilities as rounded for the tensor cores (bias of V)
 
         const int n_st = (item.tok_end - item.tok_begin + kStageTokens - 1) / kStageTokens;
         for (int st = 0; st < n_st; ++st) {
@@ -286,6 +294,12 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
                 l1 = l1 * corr1 + p1 + p3;
                 m0 = mn0;
                 m1 = mn1;
+                const uint32_t pk01 = Elem<__half>::pack2(p0, p1), pk23 = Elem<__half>::pack2(p2, p3);
+                {
+                    const float2 r01 = Elem<__half>::unpack2(pk01), r23 = Elem<__half>::unpack2(pk23);
+                    lr0 = lr0 * corr0 + r01.x + r23.x;
+                    lr1 = lr1 * corr1 + r01.y + r23.y;
+                }
                 if (__any_sync(0xffffffffu, corr0 != 1.f || corr1 != 1.f)) {
 #pragma unroll
                     for (int mt = 0; mt < 8; ++mt) {
@@ -295,8 +309,8 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
                         o[mt][3] *= corr1;
                     }
                 }
-                const uint32_t b0 = movmatrix_trans(Elem<__half>::pack2(p0, p1));
-                const uint32_t b1 = movmatrix_trans(Elem<__half>::pack2(p2, p3));
+                const uint32_t b0 = movmatrix_trans(pk01);
+                const uint32_t b1 = movmatrix_trans(pk23);
                 // ---- O^T += V^T . P^T  (128 dims x 8 heads, k = 16 tokens)
                 {
                     // one ldmatrix.x4.trans = 16 tokens x 32 int8 dims = two 16-dim row tiles.  A thread
@@ -335,6 +349,16 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
         for (int off = 4; off <= 16; off <<= 1) {
             l0 += __shfl_xor_sync(0xffffffffu, l0, off);
             l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+            lr0 += __shfl_xor_sync(0xffffffffu, lr0, off);
+            lr1 += __shfl_xor_sync(0xffffffffu, lr1, off);
+        }
+        // take the bias of the V operand out of this warp's accumulators: 1152 x (sum of its rounded probabilities)
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+            o[mt][0] = fmaf(-kI8Bias, lr0, o[mt][0]);
+            o[mt][1] = fmaf(-kI8Bias, lr1, o[mt][1]);
+            o[mt][2] = fmaf(-kI8Bias, lr0, o[mt][2]);
+            o[mt][3] = fmaf(-kI8Bias, lr1, o[mt][3]);
         }
         if (g == 0) {
             sm_m[warp * 8 + 2 * c] = m0;
@@ -432,7 +456,7 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
                     va.x *= sa.x; va.y *= sa.y; va.z *= sa.z; va.w *= sa.w;
                     vb.x *= sb.x; vb.y *= sb.y; vb.z *= sb.z; vb.w *= sb.w;
                 }
-                const int h = kvh * group + hl;
+                const int h = head0 + hl;
                 if (item.slot < 0) {
                     uint4 pk;
                     pk.x = Elem<T>::pack2(va.x, va.y);
@@ -466,7 +490,7 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
             named_bar_sync(1, kConsumerWarps * 32);
             const int n_parts = a.plan.seq_nparts[item.seq];
             if (threadIdx.x == 0) {
-                const int old = atomicAdd(&a.plan.counters[item.seq * cols + kvh], 1);
+                const int old = atomicAdd(&a.plan.counters[item.seq * cols + col], 1);
                 sm_l[0] = (old == n_parts - 1) ? 1.f : 0.f;
             }
             named_bar_sync(1, kConsumerWarps * 32);
@@ -476,7 +500,7 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
                 const int hl = threadIdx.x >> 4;
                 const int d0 = (threadIdx.x & 15) * 8;
                 if (hl < group) {
-                    const int h = kvh * group + hl;
+                    const int h = head0 + hl;
                     const int pbase = a.plan.seq_part_base[item.seq];
                     const float *lse = a.plan.part_lse + (int64_t)pbase * a.num_heads + h;
                     float mx = -INFINITY;
@@ -575,7 +599,7 @@ template <typename T> cudaError_t launch_typed(const PaArgs &args, const CUtenso
 
 bool pa_tma_mma_i8_supported(int dk, int dv, int v_row_dim, int block_size, int group, int q_dtype, int kv_dtype)
 {
-    return dk == 128 && dv == 128 && v_row_dim == 128 && (block_size == 16 || block_size == 32 || block_size == 64 || block_size == 128 || block_size == 256) && group >= 1 && group <= 8 &&
+    return dk == 128 && dv == 128 && v_row_dim == 128 && (block_size == 16 || block_size == 32 || block_size == 64 || block_size == 128 || block_size == 256) && group >= 1 &&
            (q_dtype == kFp16 || q_dtype == kBf16) && kv_dtype == kInt8;
 }
 

@@ -70,7 +70,7 @@ def test_plan_covers_every_token_exactly_once(case):
 
 def _cols(case, info):
     if info.kernel == capi.KERNEL_TMA_MMA:
-        return case.kv_heads
+        return case.kv_heads * ((case.heads // case.kv_heads + 7) // 8)   # a column per 8 query heads of a kv head
     if info.kernel == capi.KERNEL_MLA_TC5:
         return (case.heads + 63) // 64
     dmax = max(case.dk, case.dv)
@@ -129,7 +129,10 @@ def test_kernel_selection():
     assert _plan(wl.CONFIGS[0])[0].info.kernel == capi.KERNEL_TMA_MMA
     small = {c.name: c for c in wl.SMALL_CASES}
     assert _plan(small["ragged_d96_bs16_fp16"])[0].info.kernel == capi.KERNEL_GENERIC
-    assert _plan(small["gqa127_fp16"])[0].info.kernel == capi.KERNEL_GENERIC
+    # more than 8 query heads per kv head: the tiled kernel, a CTA column per chunk of 8 heads
+    p127 = _plan(small["gqa127_fp16"])[0].info
+    assert p127.kernel == capi.KERNEL_TMA_MMA and p127.num_ctas % 16 == 0
+    assert _plan(small["gqa15_fp16"])[0].info.kernel == capi.KERNEL_TMA_MMA
     assert _plan(small["mla_128h_bf16"])[0].info.kernel == capi.KERNEL_MLA_TC5
     assert _plan(wl.CONFIGS[2])[0].info.kernel == capi.KERNEL_TMA_MMA      # int8 cache
     assert _plan(wl.CONFIGS[4])[0].info.kernel == capi.KERNEL_MLA_TC5
