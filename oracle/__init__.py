@@ -7,5 +7,6 @@ tests/apitest/kernelstest/mix/test_reshape_and_cache.py:45-68 of the reference) 
 against outputs of those Python functions stored under tests/golden/.
 """
 from .oracle import (attention_lse, build, load, multi_latent_attention, num_threads, paged_attention,  # noqa: F401
+                     paged_attention_qkv_quant,
                      paged_attention_spec, reshape_and_cache)
 from . import cache_ops  # noqa: F401

@@ -36,6 +36,8 @@ def load():
         lib.oracle_reshape_and_cache.restype = ctypes.c_int
         lib.oracle_reshape_and_cache.argtypes = [vp] * 5 + [i32, i64, i64, i64]
         lib.oracle_num_threads.restype = ctypes.c_int
+        lib.oracle_paged_attention_qkv_quant.restype = ctypes.c_int
+        lib.oracle_paged_attention_qkv_quant.argtypes = [vp] * 9 + [i32] * 7 + [f32] + [i32] * 3
         _LIB = lib
     return _LIB
 
@@ -104,6 +106,31 @@ def paged_attention(q, k_cache, v_cache, block_tables, context_lens, scale, q_dt
     if rc != 0:
         raise ValueError("oracle_paged_attention rejected its arguments")
     return (out, high) if want_high else out
+
+
+def paged_attention_qkv_quant(q, k_cache, v_cache, block_tables, context_lens, k_descale, v_descale, scale, out_dtype,
+                              p_scale=None, tile_tokens=128, split_tokens=1 << 30, nthreads=0):
+    """Decode attention golden for int8 Q, K and V (TYPE_QUANT_QKV_ONLINE; with `p_scale` OFFLINE).
+
+    q [B,H,D] int8, caches [NB,BS,Hkv,D] int8, k_descale / v_descale / p_scale [H] fp32.  P is quantised to int8 per
+    tile of `tile_tokens` inside splits of `split_tokens` (the golden's block_size_calc and kv_split_per_core).
+    Returns out [B,H,D] in `out_dtype` ('fp16' as float16, 'bf16' as uint16 bits); rows of empty sequences are zero."""
+    lib = load()
+    B, H, D = q.shape
+    NB, BS, Hkv, _ = k_cache.shape
+    assert q.dtype == np.int8 and k_cache.dtype == np.int8 and v_cache.dtype == np.int8
+    block_tables = np.ascontiguousarray(block_tables, dtype=np.int32)
+    context_lens = np.ascontiguousarray(context_lens, dtype=np.int32)
+    out = np.zeros((B, H, D), dtype=np.float16 if out_dtype == "fp16" else np.uint16)
+    f32 = lambda a: None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+    kd, vd, ps = f32(k_descale), f32(v_descale), f32(p_scale)
+    rc = lib.oracle_paged_attention_qkv_quant(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(context_lens),
+                                              _ptr(kd), _ptr(vd), _ptr(ps), _ptr(out), B, H, Hkv, D, BS,
+                                              block_tables.shape[1], _DT[out_dtype], float(scale), int(tile_tokens),
+                                              int(min(split_tokens, 1 << 30)), int(nthreads))
+    if rc != 0:
+        raise ValueError("oracle_paged_attention_qkv_quant rejected its arguments")
+    return out
 
 
 def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping):

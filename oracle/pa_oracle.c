@@ -375,3 +375,163 @@ int oracle_num_threads(void)
     return 1;
 #endif
 }
+
+/*
+ * Decode attention with int8 Q, K, V (quantType TYPE_QUANT_QKV_ONLINE / OFFLINE): restates
+ * tests/apitest/kernelstest/mix/test_paged_attention_common.py of the reference:
+ *   group_mm_torch :104-110 (int32 matmuls, then * de_scale[head]), softmax_quant_numpy :142-166 (running
+ *   maximum per tile, P quantised to int8 per tile: online with the tile's own maximum / 127, offline with
+ *   the per-head pScale; both round through fp16 first), softmax_quant_numpy_online :169-227 (tiles of
+ *   `tile_tokens` = its block_size_calc inside splits of `split_tokens` = its kv_split_per_core, the
+ *   splits merged by their log-sum-exp), ref_masked_attention :256-265.
+ * k_descale, v_descale, p_scale: [H] fp32 (p_scale NULL = online).  Output in `out_dtype`.
+ * The result depends (slightly) on where the tiles fall, so the tile and split sizes are arguments.
+ */
+int oracle_paged_attention_qkv_quant(const int8_t *q, const int8_t *k_cache, const int8_t *v_cache,
+                                     const int32_t *block_tables, const int32_t *context_lens, const float *k_descale,
+                                     const float *v_descale, const float *p_scale, void *out, int32_t B, int32_t H,
+                                     int32_t Hkv, int32_t D, int32_t block_size, int32_t max_blocks, int32_t out_dtype,
+                                     float scale, int32_t tile_tokens, int32_t split_tokens, int32_t nthreads)
+{
+    if (B < 0 || H <= 0 || Hkv <= 0 || H % Hkv != 0 || D <= 0 || block_size <= 0 || tile_tokens <= 0 ||
+        split_tokens <= 0 || (out_dtype != ORACLE_FP16 && out_dtype != ORACLE_BF16)) {
+        return 1;
+    }
+    ensure_lut();
+#ifdef _OPENMP
+    if (nthreads > 0) {
+        omp_set_num_threads(nthreads);
+    }
+#else
+    (void)nthreads;
+#endif
+    const int group = H / Hkv;
+    int failed = 0;
+#pragma omp parallel for schedule(dynamic, 1) collapse(2)
+    for (int b = 0; b < B; ++b) {
+        for (int h = 0; h < H; ++h) {
+            const int len = context_lens[b];
+            if (len <= 0) {
+                continue;
+            }
+            const int hk = h / group;
+            const int n_split = (int)(((int64_t)len + split_tokens - 1) / split_tokens);
+            float *sim = (float *)malloc(sizeof(float) * (size_t)tile_tokens);
+            int8_t *pq = (int8_t *)malloc((size_t)tile_tokens);
+            int32_t *acc = (int32_t *)malloc(sizeof(int32_t) * (size_t)D);
+            float *go = (float *)malloc(sizeof(float) * (size_t)D);
+            float *po = (float *)malloc(sizeof(float) * (size_t)D * (size_t)n_split);
+            float *pl = (float *)malloc(sizeof(float) * (size_t)n_split);
+            if (!sim || !pq || !acc || !go || !po || !pl) {
+                failed = 1;
+                free(sim); free(pq); free(acc); free(go); free(po); free(pl);
+                continue;
+            }
+            const int8_t *qrow = q + ((int64_t)b * H + h) * D;
+            for (int si = 0; si < n_split; ++si) {
+                const int s_begin = si * split_tokens;
+                const int s_end = len < s_begin + split_tokens ? len : s_begin + split_tokens;
+                float gm = -3.4028234663852886e38f, gl = 0.f;
+                for (int t0 = s_begin, first = 1; t0 < s_end; t0 += tile_tokens, first = 0) {
+                    const int n = s_end - t0 < tile_tokens ? s_end - t0 : tile_tokens;
+                    float lm = -INFINITY;
+                    for (int t = 0; t < n; ++t) {
+                        const int tok = t0 + t;
+                        const int blk = block_tables[(int64_t)b * max_blocks + tok / block_size];
+                        const int8_t *krow = k_cache + (((int64_t)blk * block_size + tok % block_size) * Hkv + hk) * D;
+                        int32_t dot = 0;
+                        for (int d = 0; d < D; ++d) {
+                            dot += (int32_t)qrow[d] * (int32_t)krow[d];
+                        }
+                        const float s = ((float)dot * k_descale[h]) * scale;
+                        sim[t] = s;
+                        lm = s > lm ? s : lm;
+                    }
+                    float hm, dm;
+                    if (first) {
+                        hm = lm;
+                        dm = 0.f;
+                    } else {
+                        hm = gm > lm ? gm : lm;
+                        dm = gm - hm;
+                    }
+                    gm = hm;
+                    float row_sum = 0.f, row_maxp = 0.f;
+                    for (int t = 0; t < n; ++t) {
+                        sim[t] = expf(sim[t] - hm);
+                        row_sum += sim[t];
+                        row_maxp = sim[t] > row_maxp ? sim[t] : row_maxp;
+                    }
+                    float dsv;
+                    if (p_scale == NULL) {
+                        const float sc = row_maxp / 127.0f;
+                        for (int t = 0; t < n; ++t) {
+                            const float v16 = g_half_lut[float_to_half_bits(sim[t] / sc)];
+                            pq[t] = (int8_t)rintf(v16);
+                        }
+                        dsv = v_descale[h] * row_maxp / 127.f;
+                    } else {
+                        for (int t = 0; t < n; ++t) {
+                            const float v16 = g_half_lut[float_to_half_bits(sim[t] * p_scale[h])];
+                            pq[t] = (int8_t)rintf(v16);
+                        }
+                        dsv = v_descale[h];
+                    }
+                    memset(acc, 0, sizeof(int32_t) * (size_t)D);
+                    for (int t = 0; t < n; ++t) {
+                        const int tok = t0 + t;
+                        const int blk = block_tables[(int64_t)b * max_blocks + tok / block_size];
+                        const int8_t *vrow = v_cache + (((int64_t)blk * block_size + tok % block_size) * Hkv + hk) * D;
+                        const int32_t p = pq[t];
+                        for (int d = 0; d < D; ++d) {
+                            acc[d] += p * (int32_t)vrow[d];
+                        }
+                    }
+                    if (first) {
+                        gl = row_sum;
+                        for (int d = 0; d < D; ++d) {
+                            go[d] = (float)acc[d] * dsv;
+                        }
+                    } else {
+                        const float e = expf(dm);
+                        gl = gl * e + row_sum;
+                        for (int d = 0; d < D; ++d) {
+                            go[d] = go[d] * e + (float)acc[d] * dsv;
+                        }
+                    }
+                }
+                for (int d = 0; d < D; ++d) {
+                    po[(size_t)si * D + d] = go[d] / gl;
+                }
+                pl[si] = logf(gl) + gm;
+            }
+            if (n_split > 1) {
+                float lmax = -INFINITY, lsum = 0.f;
+                for (int si = 0; si < n_split; ++si) {
+                    lmax = pl[si] > lmax ? pl[si] : lmax;
+                }
+                for (int si = 0; si < n_split; ++si) {
+                    lsum += expf(pl[si] - lmax);
+                }
+                const float logsum = logf(lsum) + lmax;
+                for (int d = 0; d < D; ++d) {
+                    go[d] = 0.f;
+                }
+                for (int si = 0; si < n_split; ++si) {
+                    const float w = expf(pl[si] - logsum);
+                    for (int d = 0; d < D; ++d) {
+                        go[d] += po[(size_t)si * D + d] * w;
+                    }
+                }
+            } else {
+                memcpy(go, po, sizeof(float) * (size_t)D);
+            }
+            uint16_t *orow = (uint16_t *)out + ((int64_t)b * H + h) * D;
+            for (int d = 0; d < D; ++d) {
+                orow[d] = out_dtype == ORACLE_BF16 ? float_to_bf16_bits(go[d]) : float_to_half_bits(go[d]);
+            }
+            free(sim); free(pq); free(acc); free(go); free(po); free(pl);
+        }
+    }
+    return failed;
+}

@@ -198,6 +198,45 @@ def pa_mask(spec):
     return _wl.encode(m, case.q_dtype)
 
 
+# ------------------------------------------------------------------ PagedAttention with int8 Q, K and V (QUANT_QKV)
+
+GOLDEN_PA_QUANT_CASES = [
+    dict(name="quant_online_fp16", batch=3, heads=8, kv_heads=8, out_dtype="fp16", lens=[70, 300, 129], offline=False,
+         tile=128, split=1 << 30, seed=131),
+    dict(name="quant_online_bf16_gqa_split", batch=2, heads=8, kv_heads=2, out_dtype="bf16", lens=[700, 257], offline=False,
+         tile=128, split=256, seed=132),
+    dict(name="quant_offline_fp16_gqa", batch=3, heads=8, kv_heads=1, out_dtype="fp16", lens=[33, 260, 128], offline=True,
+         tile=128, split=1 << 30, seed=133),
+]
+
+
+def quant_inputs(spec):
+    """Seeded inputs of a QUANT_QKV case with the value ranges of the reference test
+    (tests/apitest/kernelstest/mix/test_paged_attention_common.py:444-450, 540-543): int8 query and caches
+    in [-5, 5]; one dequantisation scale per query head for Q.K^T and one for P.V (the reference draws them from
+    (-5/127, 5/127); here (0.2/127, 1/127), positive, so that no head's scores flip sign as a whole); for the
+    offline form one P scale per head (the reference: (0, 127); here (20, 127), away from the degenerate 0)."""
+    rng = np.random.default_rng(spec["seed"])
+    bs, d = 128, 128
+    lens = np.asarray(spec["lens"], dtype=np.int32)
+    need = (lens + bs - 1) // bs
+    pool = int(2 * need.sum())
+    perm = rng.permutation(pool).astype(np.int32)
+    bt = np.full((spec["batch"], int(need.max())), -1, dtype=np.int32)
+    pos = 0
+    for b in range(spec["batch"]):
+        bt[b, :need[b]] = perm[pos:pos + need[b]]
+        pos += need[b]
+    out = {"context_lens": lens, "block_tables": bt, "num_blocks": pool}
+    out["q"] = rng.integers(-5, 6, size=(spec["batch"], spec["heads"], d), dtype=np.int8)
+    out["k_cache"] = rng.integers(-5, 6, size=(pool, bs, spec["kv_heads"], d), dtype=np.int8)
+    out["v_cache"] = rng.integers(-5, 6, size=(pool, bs, spec["kv_heads"], d), dtype=np.int8)
+    out["k_descale"] = rng.uniform(0.2 / 127, 1.0 / 127, spec["heads"]).astype(np.float32)
+    out["v_descale"] = rng.uniform(0.2 / 127, 1.0 / 127, spec["heads"]).astype(np.float32)
+    out["p_scale"] = rng.uniform(20.0, 127.0, spec["heads"]).astype(np.float32) if spec["offline"] else None
+    return out
+
+
 # ------------------------------------------------------------------ PagedAttention, parallel decoding (CALC_TYPE_SPEC)
 
 GOLDEN_PA_SPEC_CASES = [

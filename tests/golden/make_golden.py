@@ -32,6 +32,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, HERE)
 
+from golden_cases import GOLDEN_PA_QUANT_CASES, quant_inputs  # noqa: E402
 from golden_cases import (GOLDEN_BLOCKCOPY_CASES, GOLDEN_PA_CASES, GOLDEN_KVCACHE_CASES, GOLDEN_MLA_MTP_CASES, GOLDEN_PA_FEATURE_CASES, GOLDEN_PA_SPEC_CASES, GOLDEN_PCL_CASES,  # noqa: E402
                           GOLDEN_NRR_CASES, GOLDEN_RAC_CASES, blockcopy_inputs, load_workloads, nrr_inputs, kvcache_inputs, mla_mtp_inputs, pa_mask, spec_inputs,
                           pcl_inputs, rac_inputs)
@@ -184,6 +185,40 @@ def run_pa_feature_case(common, spec):
     return res
 
 
+def run_pa_quant_case(common, spec):
+    """int8 Q, K and V (QUANT_QKV online / offline) through the reference golden: the int32 matmuls, the per-tile
+    quantisation of P and the log-sum-exp merge of the splits are all the reference's code; only the tile size
+    (its block_size_calc) and the split length (its kv_split_per_core) are set here instead of derived from the
+    core count of an Ascend SoC."""
+    d = quant_inputs(spec)
+    t = common.TestPagedAttention()
+    t.compressHead = False
+    t.is_int8_flag = False
+    t.is_quant_flag = 1
+    t.is_quant_offiline = 1 if spec["offline"] else 0
+    t.has_bias = False
+    t.scaleType = 0
+    t.num_heads, t.kv_heads, t.num_tokens, t.head_size = spec["heads"], spec["kv_heads"], spec["batch"], 128
+    t.block_size = 128
+    t.block_size_calc = spec["tile"]
+    max_len = int(d["context_lens"].max())
+    t.kv_split_per_core = min(spec["split"], max_len)
+    t.kvsplit = (max_len + t.kv_split_per_core - 1) // t.kv_split_per_core
+    t.de_scale1_fp32 = torch.from_numpy(d["k_descale"])
+    t.de_scale2_fp32 = torch.from_numpy(d["v_descale"])
+    if spec["offline"]:
+        t.scale = torch.from_numpy(d["p_scale"])
+    tdt = {"fp16": torch.float16, "bf16": torch.bfloat16}[spec["out_dtype"]]
+    out = torch.zeros((spec["batch"], spec["heads"], 128), dtype=torch.float32)
+    high = torch.zeros_like(out)
+    t.ref_single_query_cached_kv_attention(out, high, torch.from_numpy(d["q"]), torch.from_numpy(d["k_cache"]),
+                                           torch.from_numpy(d["v_cache"]), d["block_tables"].tolist(),
+                                           d["context_lens"].tolist(), None, None, False, mask_dim=0, mask_data_type=tdt)
+    dig = {k: v for k, v in d.items() if isinstance(v, np.ndarray)}
+    return {"out": from_torch(out, spec["out_dtype"]), "out_f32": out.numpy(),
+            "input_sha256": np.frombuffer(digest(dig).encode(), dtype=np.uint8)}
+
+
 def run_pa_spec_case(lookahead, spec):
     """Parallel decoding through the golden function of the reference's lookahead test (numpy, fp16; mask_type 3 =
     MASK_TYPE_SPEC rows per token, 0 = rows of the square causal mask)."""
@@ -330,6 +365,12 @@ def main():
     mtp = _load(os.path.join(kt, "mix/test_paged_attention_mla_mtp_split.py"), "ref_pa_mla_mtp")
     lookahead = _load(os.path.join(kt, "mix/test_paged_attention_lookahead.py"), "ref_pa_lookahead")
     os.chdir(cwd)
+    for spec in GOLDEN_PA_QUANT_CASES:
+        res = run_pa_quant_case(common, spec)
+        np.savez_compressed(os.path.join(HERE, f"pa_{spec['name']}.npz"), **res)
+        print("wrote", spec["name"], res["out"].shape)
+    if "--quant-only" in sys.argv:
+        return
     for spec in GOLDEN_PA_SPEC_CASES:
         res = run_pa_spec_case(lookahead, spec)
         np.savez_compressed(os.path.join(HERE, f"pa_{spec['case'].name}.npz"), **res)

@@ -232,3 +232,32 @@ def test_oracle_mla_parallel_decoding_matches_reference_golden(spec):
     assert np.all(np.abs(got - ref) <= 2 * ulp(case.q_dtype) * np.maximum(np.abs(ref), 2.0 ** -6))
     gl, rl = wl.to_f32(lse, case.q_dtype), wl.to_f32(fx["lse"], case.q_dtype)
     assert np.all(np.abs(gl - rl) <= ulp(case.q_dtype) * np.maximum(np.abs(rl), 1.0))
+
+
+# ------------------------------------------------------------------ int8 Q, K and V (QUANT_QKV online / offline)
+
+from golden_cases import GOLDEN_PA_QUANT_CASES, quant_inputs  # noqa: E402
+
+
+@pytest.mark.parametrize("spec", GOLDEN_PA_QUANT_CASES, ids=lambda s: s["name"])
+def test_oracle_qkv_quant_matches_reference_golden(spec):
+    """The restated int32 matmuls, per-tile quantisation of P and split merge against the reference's own golden
+    (test_paged_attention_common.py:104-110, 142-227), run with the same tile and split sizes."""
+    fx = np.load(os.path.join(HERE, f"pa_{spec['name']}.npz"))
+    d = quant_inputs(spec)
+    dig = {k: v for k, v in d.items() if isinstance(v, np.ndarray)}
+    assert _digest(dig) == bytes(fx["input_sha256"]).decode(), "seeded inputs changed; regenerate the fixtures"
+    dt = spec["out_dtype"]
+    out = oracle.paged_attention_qkv_quant(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], d["context_lens"],
+                                           d["k_descale"], d["v_descale"], 1.0 / np.sqrt(128.0), dt, p_scale=d["p_scale"],
+                                           tile_tokens=spec["tile"], split_tokens=spec["split"])
+    got, ref = wl.to_f32(out, dt), wl.to_f32(fx["out"], dt)
+    scale = max(float(np.abs(ref).max()), 1e-6)
+    assert np.abs(got - ref).max() <= 2 * ulp(dt) * scale
+    assert (got == ref).mean() >= 0.95
+    # the quantisation of P is not a no-op: another tile size moves the result (a little)
+    other = oracle.paged_attention_qkv_quant(d["q"], d["k_cache"], d["v_cache"], d["block_tables"], d["context_lens"],
+                                             d["k_descale"], d["v_descale"], 1.0 / np.sqrt(128.0), dt, p_scale=d["p_scale"],
+                                             tile_tokens=16, split_tokens=spec["split"])
+    diff = np.abs(wl.to_f32(other, dt) - ref).max()
+    assert 0 < diff <= 1e-2 * scale
