@@ -36,7 +36,8 @@ class PaDesc(ctypes.Structure):
                 ("block_size", ctypes.c_int32), ("num_blocks", ctypes.c_int32),
                 ("max_blocks_per_seq", ctypes.c_int32), ("q_dtype", ctypes.c_int32), ("kv_dtype", ctypes.c_int32),
                 ("qk_scale", ctypes.c_float), ("kernel", ctypes.c_int32), ("sm_count", ctypes.c_int32),
-                ("rope_dim", ctypes.c_int32), ("score_mods", ctypes.c_int32), ("kv_layout", ctypes.c_int32), ("q_per_seq", ctypes.c_int32)]
+                ("rope_dim", ctypes.c_int32), ("score_mods", ctypes.c_int32), ("kv_layout", ctypes.c_int32), ("q_per_seq", ctypes.c_int32),
+                ("qkv_quant", ctypes.c_int32), ("out_dtype", ctypes.c_int32)]
 
 
 class PaTensors(ctypes.Structure):
@@ -46,9 +47,10 @@ class PaTensors(ctypes.Structure):
                 ("q_rope", ctypes.c_void_p), ("k_rope_cache", ctypes.c_void_p),
                 ("mask", ctypes.c_void_p), ("mask_batch_stride", ctypes.c_int64), ("mask_head_stride", ctypes.c_int64),
                 ("mask_tokens", ctypes.c_int64), ("mask_q_stride", ctypes.c_int64), ("logn", ctypes.c_void_p),
-                ("lse_out", ctypes.c_void_p)]
+                ("lse_out", ctypes.c_void_p), ("p_scale", ctypes.c_void_p)]
 
 
+QUANT_ONLINE, QUANT_OFFLINE = 1, 2
 SCORE_MASK, SCORE_LOGN, SCORE_ROWS, SCORE_CAUSAL = 1, 2, 4, 8
 
 
@@ -239,9 +241,12 @@ def _check(rc, what):
 # ------------------------------------------------------------------ kernel level
 
 def make_desc(batch, num_heads, kv_heads, dk, dv, block_size, num_blocks, max_blocks, q_dtype, kv_dtype=None,
-              qk_scale=1.0, v_row_dim=None, kernel=KERNEL_AUTO, sm_count=0, rope_dim=0, score_mods=0, kv_layout=0, q_per_seq=0):
+              qk_scale=1.0, v_row_dim=None, kernel=KERNEL_AUTO, sm_count=0, rope_dim=0, score_mods=0, kv_layout=0, q_per_seq=0,
+              qkv_quant=0, out_dtype=None):
     d = PaDesc()
     d.q_per_seq = q_per_seq
+    d.qkv_quant = qkv_quant
+    d.out_dtype = 0 if out_dtype is None else (DTYPE_CODE[out_dtype] if isinstance(out_dtype, str) else out_dtype)
     d.rope_dim, d.score_mods, d.kv_layout = rope_dim, score_mods, kv_layout
     d.batch, d.num_heads, d.kv_heads = batch, num_heads, kv_heads
     d.head_dim_k, d.head_dim_v, d.v_row_dim = dk, dv, (v_row_dim or dv)
@@ -315,7 +320,8 @@ class PaPlan:
         _check(lib().atb_b200_pa_plan_set_trace(self.handle, device_ptr, capacity), "atb_b200_pa_plan_set_trace")
 
     def set_profiling(self, on=True):
-        _check(lib().atb_b200_pa_plan_set_profiling(self.handle, 1 if on else 0), "atb_b200_pa_plan_set_profiling")
+        """on: False / True (every launch) or a stride n (every n-th launch carries the event pair)."""
+        _check(lib().atb_b200_pa_plan_set_profiling(self.handle, int(on)), "atb_b200_pa_plan_set_profiling")
 
     def kernel_ms(self, launches_back=0):
         """Duration of the attention kernel `launches_back` launches ago (profiling must be on)."""
@@ -346,9 +352,11 @@ def torch_stream_ptr():
 
 
 def pa_tensors(q, k_cache, v_cache, block_tables, out, k_descale=None, v_descale=None, k_offset=None, v_offset=None,
-               q_rope=None, k_rope_cache=None, mask=None, mask_strides=(0, 0), mask_tokens=0, logn=None, lse_out=None, mask_q_stride=0):
+               q_rope=None, k_rope_cache=None, mask=None, mask_strides=(0, 0), mask_tokens=0, logn=None, lse_out=None, mask_q_stride=0,
+               p_scale=None):
     """`mask_strides` = (batch, head) element strides of the additive mask, `mask_tokens` its last dimension."""
     t = PaTensors()
+    t.p_scale = _ptr(p_scale)
     t.mask, t.logn, t.lse_out = _ptr(mask), _ptr(logn), _ptr(lse_out)
     t.mask_q_stride = int(mask_q_stride)
     t.mask_batch_stride, t.mask_head_stride, t.mask_tokens = int(mask_strides[0]), int(mask_strides[1]), int(mask_tokens)

@@ -4,7 +4,8 @@
 // (CreateOperation :92-143, *ParamCheck :145-365, GetInputNum :408-444, InferShapeImpl :451-472,
 //  SetupCheckImpl :492-525, KVCacheDimCheck910B :585-632, SetupDimCheck :926-963).  Built: NORM / ALIBI / SPEC
 // masks, batchRunStatus, parallel decoding (CALC_TYPE_SPEC), logN scaling, qScale, the BNSD cache layout,
-// int8 caches with per-channel dequantisation.  Head compression, MASK_TYPE_MASK_FREE and the NZ layouts
+// int8 caches with per-channel dequantisation, int8 Q / K / V (TYPE_QUANT_QKV_ONLINE / OFFLINE, without a mask).
+// Head compression, MASK_TYPE_MASK_FREE and the NZ layouts
 // (other SoC classes) are rejected at CreateOperation with ERROR_INVALID_PARAM.
 #include <cmath>
 #include <cstdlib>
@@ -94,13 +95,34 @@ bool ParamCheck(const Param &p)
         ATB_B200_LOG(ERROR, "MASK_TYPE_SPEC needs calcType CALC_TYPE_SPEC");
         return false;
     }
+    const bool qkvQuant = p.quantType == Param::TYPE_QUANT_QKV_OFFLINE || p.quantType == Param::TYPE_QUANT_QKV_ONLINE;
+    if (qkvQuant) {
+        // QuantParamCheck of the reference (paged_attention_operation.cpp:249-276)
+        if (p.outDataType != ACL_FLOAT16 && p.outDataType != ACL_BF16) {
+            ATB_B200_LOG(ERROR, "outDataType only support ACL_FLOAT16 and ACL_BF16");
+            return false;
+        }
+        if (p.hasQuantOffset) {
+            ATB_B200_LOG(ERROR, "QKVQuant only support when hasQuantOffset is False");
+            return false;
+        }
+        if (p.calcType != Param::CALC_TYPE_UNDEFINED) {
+            ATB_B200_LOG(ERROR, "QKVQuant only support when calcType is CALC_TYPE_UNDEFINED");
+            return false;
+        }
+        if (p.maskType != Param::UNDEFINED || p.batchRunStatusEnable || p.mlaVHeadSize > 0 ||
+            p.inputLayout != infer::TYPE_BSND) {
+            ATB_B200_LOG(ERROR, "PagedAttention: QKVQuant with a mask, batchRunStatus, mla or BNSD is not supported by "
+                                "this build");
+            return false;
+        }
+    }
     // Features outside the decode path of this build.
     if ((p.maskType != Param::UNDEFINED && p.maskType != Param::MASK_TYPE_NORM && p.maskType != Param::MASK_TYPE_ALIBI &&
          p.maskType != Param::MASK_TYPE_SPEC) ||
         p.compressType != Param::COMPRESS_TYPE_UNDEFINED ||
-        (p.quantType != Param::TYPE_QUANT_UNQUANT && p.quantType != Param::TYPE_DEQUANT_FUSION)) {
-        ATB_B200_LOG(ERROR, "PagedAttention: MASK_FREE / NORM_COMPRESS masks, compress and QKV-quant "
-                            "are not supported by this build");
+        (p.quantType != Param::TYPE_QUANT_UNQUANT && p.quantType != Param::TYPE_DEQUANT_FUSION && !qkvQuant)) {
+        ATB_B200_LOG(ERROR, "PagedAttention: MASK_FREE / NORM_COMPRESS masks and compress are not supported by this build");
         return false;
     }
     return true;
@@ -127,7 +149,18 @@ public:
         const bool mla = p.mlaVHeadSize > 0;
         const aclDataType halfs[2] = {ACL_FLOAT16, ACL_BF16};
         for (aclDataType h : halfs) {
-            if (p.quantType == Param::TYPE_DEQUANT_FUSION) {
+            if (QkvQuant()) {
+                // int8 query and caches, fp32 scales per head, output of the type the param names
+                if (h != p.outDataType) {
+                    continue;
+                }
+                DtypeComb c = {ACL_INT8, ACL_INT8, ACL_INT8, ACL_INT32, ACL_INT32, ACL_FLOAT, ACL_FLOAT};
+                if (p.quantType == Param::TYPE_QUANT_QKV_OFFLINE) {
+                    c.push_back(ACL_FLOAT); // pScale
+                }
+                c.push_back(h);
+                combs_.push_back(c);
+            } else if (p.quantType == Param::TYPE_DEQUANT_FUSION) {
                 // descale tensors: fp32, the int64-packed fp32 encoding, or (extension) fp16
                 for (aclDataType sc : {ACL_FLOAT, ACL_INT64, ACL_FLOAT16}) {
                     DtypeComb c = {h, ACL_INT8, ACL_INT8, ACL_INT32, ACL_INT32};
@@ -200,6 +233,9 @@ public:
         if (param_.quantType == Param::TYPE_DEQUANT_FUSION) {
             n += param_.hasQuantOffset ? 4 : 2;
         }
+        if (QkvQuant()) {
+            n += param_.quantType == Param::TYPE_QUANT_QKV_OFFLINE ? 3 : 2; // kDescale, vDescale, [pScale]
+        }
         if (param_.mlaVHeadSize > 0) {
             n -= 1; // no valueCache
         }
@@ -210,6 +246,10 @@ public:
 protected:
     // optional inputs follow contextLens in the reference's order: mask, batchRunStatus, kDescale ..., logN (last)
     bool HasMask() const { return param_.maskType != Param::UNDEFINED; }
+    bool QkvQuant() const
+    {
+        return param_.quantType == Param::TYPE_QUANT_QKV_OFFLINE || param_.quantType == Param::TYPE_QUANT_QKV_ONLINE;
+    }
     size_t ClPos() const { return param_.mlaVHeadSize > 0 ? 3 : 4; }
     size_t MaskPos() const { return ClPos() + 1; }
     size_t StatusPos() const { return ClPos() + 1 + (HasMask() ? 1 : 0); }
@@ -348,7 +388,19 @@ protected:
             ATB_B200_LOG(ERROR, "PagedAttention: headSize of keyCache and query should be same");
             return ERROR_INVALID_TENSOR_DIM;
         }
-        if (param_.quantType == Param::TYPE_DEQUANT_FUSION) {
+        if (QkvQuant()) {
+            if (headSize != in.at(2).shape.dims[3] || headSize > 256 || headSize * blockSize > 128 * 128) {
+                ATB_B200_LOG(ERROR, "PagedAttention: QKVQuant needs equal head sizes <= 256 and block_size * head_size <= 128*128");
+                return ERROR_INVALID_TENSOR_DIM;
+            }
+            const size_t n = param_.quantType == Param::TYPE_QUANT_QKV_OFFLINE ? 3u : 2u;
+            for (size_t i = ScalePos(); i < ScalePos() + n; ++i) {
+                if (in.at(i).shape.dimNum != 1 || in.at(i).shape.dims[0] != param_.headNum) {
+                    ATB_B200_LOG(ERROR, "PagedAttention: QKVQuant scales should have headNum elements");
+                    return ERROR_INVALID_TENSOR_DIM;
+                }
+            }
+        } else if (param_.quantType == Param::TYPE_DEQUANT_FUSION) {
             if (headSize != in.at(2).shape.dims[3]) {
                 return ERROR_INVALID_TENSOR_DIM;
             }
@@ -390,6 +442,9 @@ protected:
     {
         out.at(0) = in.at(0);
         out.at(0).shape.dims[2] = param_.mlaVHeadSize > 0 ? param_.mlaVHeadSize : in.at(2).shape.dims[3];
+        if (QkvQuant()) {
+            out.at(0).dtype = param_.outDataType; // the query is int8 here
+        }
         return NO_ERROR;
     }
 
@@ -447,6 +502,10 @@ protected:
             scale *= param_.qScale; // the reference multiplies Q by qScale in a separate node
         }
         d.qk_scale = scale;
+        if (QkvQuant()) {
+            d.qkv_quant = param_.quantType == Param::TYPE_QUANT_QKV_OFFLINE ? ATB_B200_QUANT_OFFLINE : ATB_B200_QUANT_ONLINE;
+            d.out_dtype = ToKernelDtype(param_.outDataType);
+        }
         d.kernel = ATB_B200_KERNEL_AUTO;
         if (const char *force = std::getenv("ATB_B200_FORCE_KERNEL")) {
             d.kernel = std::atoi(force);
@@ -616,6 +675,18 @@ protected:
             t.k_offset = ko ? static_cast<const int32_t *>(ko->deviceData) : nullptr;
             t.v_offset = vo ? static_cast<const int32_t *>(vo->deviceData) : nullptr;
         }
+        if (QkvQuant()) {
+            size_t i = ScalePos();
+            t.k_descale = static_cast<const float *>(vp.inTensors.at(i++).deviceData);
+            t.v_descale = static_cast<const float *>(vp.inTensors.at(i++).deviceData);
+            if (param_.quantType == Param::TYPE_QUANT_QKV_OFFLINE) {
+                t.p_scale = static_cast<const float *>(vp.inTensors.at(i++).deviceData);
+            }
+            if (t.k_descale == nullptr || t.v_descale == nullptr ||
+                (param_.quantType == Param::TYPE_QUANT_QKV_OFFLINE && t.p_scale == nullptr)) {
+                return ERROR_INVALID_PARAM;
+            }
+        }
         if (HasMask()) {
             const Tensor &m = vp.inTensors.at(MaskPos());
             t.mask = m.deviceData;
@@ -683,7 +754,8 @@ private:
                d.block_size == desc_.block_size && d.num_blocks == desc_.num_blocks &&
                d.max_blocks_per_seq == desc_.max_blocks_per_seq && d.q_dtype == desc_.q_dtype &&
                d.kv_dtype == desc_.kv_dtype && d.qk_scale == desc_.qk_scale && d.kernel == desc_.kernel &&
-               d.score_mods == desc_.score_mods && d.kv_layout == desc_.kv_layout && d.q_per_seq == desc_.q_per_seq;
+               d.score_mods == desc_.score_mods && d.kv_layout == desc_.kv_layout && d.q_per_seq == desc_.q_per_seq &&
+               d.qkv_quant == desc_.qkv_quant && d.out_dtype == desc_.out_dtype;
     }
     // fp32 scales are used in place; the int64-packed and fp16 encodings are converted once per
     // launch into a small device buffer owned by the operation.

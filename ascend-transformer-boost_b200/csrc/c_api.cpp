@@ -46,9 +46,10 @@ struct atb_b200_pa_plan {
     uint32_t trace_cap = 0;
     // optional timing of the attention kernel: a ring of event pairs, one pair per launch
     static constexpr int kProfRing = 256;
-    bool profile = false;
+    int profile_every = 0; // 0 = off, n = every n-th launch carries an event pair
     cudaEvent_t ev0[kProfRing] = {}, ev1[kProfRing] = {};
-    uint64_t launches = 0;
+    uint64_t launches = 0;  // launches that recorded an event pair
+    uint64_t launch_seq = 0; // all launches since profiling was switched on
     int32_t *status_host = nullptr;
 };
 
@@ -235,8 +236,9 @@ int atb_b200_pa_plan_set_profiling(atb_b200_pa_plan *plan, int enable)
             }
         }
     }
-    plan->profile = enable != 0;
+    plan->profile_every = enable > 0 ? enable : 0;
     plan->launches = 0;
+    plan->launch_seq = 0;
     return ATB_B200_OK;
 }
 
@@ -454,6 +456,11 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
     a.v_descale = t->v_descale;
     a.k_offset = t->k_offset;
     a.v_offset = t->v_offset;
+    a.p_scale = d.qkv_quant == ATB_B200_QUANT_OFFLINE ? t->p_scale : nullptr;
+    if (d.qkv_quant != 0 && (t->k_descale == nullptr || t->v_descale == nullptr ||
+                             (d.qkv_quant == ATB_B200_QUANT_OFFLINE && t->p_scale == nullptr))) {
+        return kErrInvalidParam;
+    }
     a.out = t->out;
     a.q_rope = d.rope_dim != 0 ? t->q_rope : nullptr;
     a.k_rope = d.rope_dim != 0 ? t->k_rope_cache : nullptr;
@@ -521,19 +528,21 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
     }
 
     const int prof_i = (int)(plan->launches % atb_b200_pa_plan::kProfRing);
-    if (plan->profile) {
+    const bool profiled = plan->profile_every > 0 && (plan->launch_seq++ % (uint64_t)plan->profile_every) == 0;
+    if (profiled) {
         cudaEventRecord(plan->ev0[prof_i], stream);
     }
     cudaError_t e;
     if (h.kernel == ATB_B200_KERNEL_TMA_MMA) {
-        e = d.kv_dtype == kInt8 ? launch_pa_tma_mma_i8(a, d.q_dtype, d.num_blocks, stream)
-                                : launch_pa_tma_mma(a, d.q_dtype, d.kv_dtype, d.num_blocks, stream);
+        e = d.qkv_quant != 0 ? launch_pa_tma_mma_q8(a, d.out_dtype, d.num_blocks, stream)
+            : d.kv_dtype == kInt8 ? launch_pa_tma_mma_i8(a, d.q_dtype, d.num_blocks, stream)
+                                  : launch_pa_tma_mma(a, d.q_dtype, d.kv_dtype, d.num_blocks, stream);
     } else if (h.kernel == ATB_B200_KERNEL_MLA_TC5) {
         e = launch_pa_mla_tc5(a, d.q_dtype, d.num_blocks, stream);
     } else {
         e = launch_pa_generic(a, d.q_dtype, d.kv_dtype, stream);
     }
-    if (plan->profile) {
+    if (profiled) {
         cudaEventRecord(plan->ev1[prof_i], stream);
         plan->launches++;
     }

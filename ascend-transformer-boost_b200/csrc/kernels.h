@@ -25,6 +25,11 @@ cudaError_t launch_pa_tma_mma(const PaArgs &args, int q_dtype, int kv_dtype, int
 bool pa_tma_mma_i8_supported(int dk, int dv, int v_row_dim, int block_size, int group, int q_dtype, int kv_dtype);
 cudaError_t launch_pa_tma_mma_i8(const PaArgs &args, int q_dtype, int num_blocks, cudaStream_t stream);
 
+// int8 query, int8 cache (QKV quantisation): both contractions on the integer tensor cores; k_descale, v_descale
+// (and p_scale for the offline form) hold one fp32 value per query head.  `out_dtype` is fp16 or bf16.
+bool pa_tma_mma_q8_supported(int dk, int dv, int v_row_dim, int block_size, int group, int out_dtype);
+cudaError_t launch_pa_tma_mma_q8(const PaArgs &args, int out_dtype, int num_blocks, cudaStream_t stream);
+
 // MLA combined cache (Dk 576, Dv 512, one kv head): TMA + tcgen05/TMEM, 64 query heads per CTA.
 bool pa_mla_tc5_supported(int dk, int dv, int v_row_dim, int rope_dim, int block_size, int kv_heads, int q_dtype,
                           int kv_dtype);

@@ -116,7 +116,7 @@ extern "C" int atb_b200_pa_decode_static_scratch(const atb_b200_pa_desc *desc, c
         d.max_blocks_per_seq <= 0) {
         return kErrInvalidParam;
     }
-    if (d.rope_dim != 0 || d.score_mods != 0 || d.kv_layout != 0 || d.q_per_seq > 1) {
+    if (d.rope_dim != 0 || d.score_mods != 0 || d.kv_layout != 0 || d.q_per_seq > 1 || d.qkv_quant != 0) {
         return kErrInvalidTensorDim; // the split latent / rope cache, masks, logN scaling and the heads-major
                                      // cache layout are served by the planned entry points only
     }

@@ -56,6 +56,7 @@ struct PaArgs {
     const float *v_descale;
     const int32_t *k_offset;
     const int32_t *v_offset;
+    const float *p_scale; // int8 query, offline quantisation of P: one scale per query head (else null)
     void *out;
     PaDevPlan plan;
     int32_t batch, num_heads, kv_heads, group; // group = num_heads / kv_heads

@@ -48,7 +48,21 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
         return kErrInvalidParam;
     }
     const int group = d.num_heads / d.kv_heads;
-    const bool tma_ok = pa_tma_mma_supported(d.head_dim_k, d.head_dim_v, d.v_row_dim, d.block_size, group, d.q_dtype,
+    if (d.qkv_quant != 0) {
+        // int8 query and cache: the integer tensor-core variant of the tiled kernel only, plain scores
+        if ((d.qkv_quant != ATB_B200_QUANT_ONLINE && d.qkv_quant != ATB_B200_QUANT_OFFLINE) || d.q_dtype != kInt8 ||
+            d.kv_dtype != kInt8 || d.score_mods != 0 || d.rope_dim != 0 || d.kv_layout != ATB_B200_KV_BSND ||
+            d.q_per_seq > 1) {
+            return kErrInvalidParam;
+        }
+        if (!pa_tma_mma_q8_supported(d.head_dim_k, d.head_dim_v, d.v_row_dim, d.block_size, group, d.out_dtype) ||
+            (d.kernel != ATB_B200_KERNEL_AUTO && d.kernel != ATB_B200_KERNEL_TMA_MMA)) {
+            return kErrInvalidTensorDim;
+        }
+    } else if (d.q_dtype == kInt8) {
+        return kErrInvalidParam;
+    }
+    const bool tma_ok = d.qkv_quant != 0 || pa_tma_mma_supported(d.head_dim_k, d.head_dim_v, d.v_row_dim, d.block_size, group, d.q_dtype,
                                              d.kv_dtype) ||
                         pa_tma_mma_i8_supported(d.head_dim_k, d.head_dim_v, d.v_row_dim, d.block_size, group, d.q_dtype,
                                                 d.kv_dtype);

@@ -17,6 +17,15 @@
 //   * the tensor-core tiles run in fp16 for both fp16 and bf16 queries (P in fp16 is at least as
 //     precise as the golden's rounding of P to the query dtype).
 //
+// kQ8 (quantType TYPE_QUANT_QKV_ONLINE / OFFLINE: the query is int8 too) runs both contractions on the integer
+// tensor cores: S^T = K . Q^T as mma m16n8k32 s8 x s8 -> s32 straight from the ldmatrix registers (no conversion
+// at all), the probabilities of a warp's 16 tokens quantised to int8 - online: 127 * 2^(s - max of those 16),
+// i.e. relative to the tile's own maximum, weight 2^(tile max - running max) applied to the tile's int32 P.V
+// result; offline: p * pScale[head] - and O^T += V^T . P^T as m16n8k16 s8 (one byte permute per cache register).
+// One dequantisation scale per query head for each contraction, applied to the scores and to the output row.
+// Follows the golden of tests/apitest/kernelstest/mix/test_paged_attention_common.py:104-110, 142-227, whose
+// tiles are 128 tokens or more where these are 16: the results differ by the quantisation noise of P only.
+//
 // The reference dequantises K/V to fp16/bf16 through a global-memory scratch before its matmuls
 // (DequantKV, src/kernels/mixkernels/pagedattention/op_kernel/paged_attention_decoder_nd_common.cce:8306-8420);
 // its golden computes (float(x) + offset) * scale in fp32
@@ -64,6 +73,21 @@ __device__ __forceinline__ void i8x4_to_h2x2_even_odd(uint32_t w, uint32_t &even
     odd = __byte_perm(x, 0x64646464u, 0x4341);
 }
 
+__device__ __forceinline__ void mma_s8_16832(int32_t (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_s8_16816(int32_t (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(b0));
+}
+// rint(fp16(x)) as the golden rounds a probability before it becomes an int8
+__device__ __forceinline__ int32_t quant_p(float x) { return __half2int_rn(__float2half_rn(x)); }
+
 // Writes 8 output elements of (sequence, local head h) to the output tensor - or, when the heads are
 // sharded over several GPUs, into the gathered [tokens, all heads, 128] buffer of every rank.
 template <typename T>
@@ -80,7 +104,8 @@ __device__ __forceinline__ void store_out_row(const PaArgs &a, int seq, int h, i
     }
 }
 
-template <typename T>
+// T: query / output type; kQ8: the query is int8 as well (T is the output type only), see the file comment.
+template <typename T, bool kQ8>
 __global__ void __launch_bounds__(kThreads, 2)
 pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const PaArgs a)
 {
@@ -193,9 +218,26 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
         const PaItem item = a.plan.items[it];
         // B fragments of Q^T, pre-multiplied by kDescale.  ldmatrix hands a thread the 4 consecutive
         // int8 dims 4c..4c+3 of each 16-dim chunk, so those dims take the mma's k slots
-        // {2c, 2c+1, 2c+8, 2c+9} for both operands.
+        // {2c, 2c+1, 2c+8, 2c+9} for both operands.  (kQ8: the int8 query bytes themselves, 4 dims per register.)
         uint32_t qf[8][2];
-        {
+        float kd0 = 0.f, kd1 = 0.f;   // kQ8: score scale of this thread's two heads (columns 2c, 2c + 1), log2 domain
+        float ps0 = 127.f, ps1 = 127.f; // kQ8 offline: their pScale
+        if constexpr (kQ8) {
+            const bool valid = g < group;
+            const int8_t *qp = static_cast<const int8_t *>(a.q) + ((int64_t)item.seq * a.num_heads + head0 + (valid ? g : 0)) * 128;
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                qf[2 * kk][0] = valid ? *reinterpret_cast<const uint32_t *>(qp + kk * 32 + 4 * c) : 0u;
+                qf[2 * kk][1] = valid ? *reinterpret_cast<const uint32_t *>(qp + kk * 32 + 16 + 4 * c) : 0u;
+            }
+            const int h0 = head0 + min(2 * c, group - 1), h1 = head0 + min(2 * c + 1, group - 1);
+            kd0 = a.k_descale[h0] * a.scale_log2;
+            kd1 = a.k_descale[h1] * a.scale_log2;
+            if (a.p_scale != nullptr) {
+                ps0 = a.p_scale[h0];
+                ps1 = a.p_scale[h1];
+            }
+        } else {
             const bool valid = g < group;
             const T *qp = q + ((int64_t)item.seq * a.num_heads + head0 + (valid ? g : 0)) * 128;
 #pragma unroll
@@ -235,9 +277,9 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
             if (valid_tokens > 0) {
                 const uint32_t kbase = stages_u32 + stage * kStageBytes;
                 const uint32_t vbase = kbase + kTileBytes;
-                if (valid_tokens < 16) {
+                if (!kQ8 && valid_tokens < 16) {
                     // rows past the end of the sequence may hold anything (even NaN bit patterns):
-                    // clear this warp's unused V rows so that 0 * V stays 0
+                    // clear this warp's unused V rows so that 0 * V stays 0 (integer products need no such care)
                     uint8_t *vs = stages + stage * kStageBytes + kTileBytes;
                     const int rows = 16 - valid_tokens;
                     for (int i = lane; i < rows * 8; i += 32) { // 8 x 16-byte chunks per 128-byte row
@@ -248,8 +290,26 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
                     __syncwarp();
                 }
                 // ---- S^T = K . Q^T  (16 tokens x 8 heads, k = 128)
-                float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-                {
+                float s[4];
+                if constexpr (kQ8) {
+                    int32_t si[4] = {0, 0, 0, 0};
+                    const int t = warp * 16 + (lane & 15);
+                    const uint32_t row_addr = kbase + t * 128;
+                    const int sw = t & 7;
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        // one ldmatrix.x4 = 16 tokens x 32 int8 dims = the A fragment of one k = 32 step as it is
+                        const int ch = kk * 2 + (lane >> 4);
+                        uint32_t r[4];
+                        ldmatrix_x4(r, row_addr + ((ch ^ sw) << 4));
+                        mma_s8_16832(si, r, qf[2 * kk][0], qf[2 * kk][1]);
+                    }
+                    s[0] = (float)si[0] * kd0;
+                    s[1] = (float)si[1] * kd1;
+                    s[2] = (float)si[2] * kd0;
+                    s[3] = (float)si[3] * kd1;
+                } else {
+                    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
                     // one ldmatrix.x4 = 16 tokens x 32 int8 dims = two k steps:
                     // r[0] (token g, chunk 2kk), r[1] (token g+8, chunk 2kk), r[2], r[3] the same for chunk 2kk+1
                     const int t = warp * 16 + (lane & 15);
@@ -268,11 +328,10 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
                         i8x4_to_h2x2(r[3], af[1], af[3]);
                         mma_16816<__half>(s1, af, qf[2 * kk + 1][0], qf[2 * kk + 1][1]);
                     }
-                }
-                float s[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    s[i] = (s0[i] + s1[i]) * a.scale_log2;
+                    for (int i = 0; i < 4; ++i) {
+                        s[i] = (s0[i] + s1[i]) * a.scale_log2;
+                    }
                 }
                 if (g >= valid_tokens) {
                     s[0] = s[1] = -INFINITY;
@@ -288,34 +347,37 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
                 }
                 const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1); // finite: token 0 of the slice is valid
                 const float corr0 = fast_exp2(m0 - mn0), corr1 = fast_exp2(m1 - mn1);
-                const float p0 = fast_exp2(s[0] - mn0), p1 = fast_exp2(s[1] - mn1);
-                const float p2 = fast_exp2(s[2] - mn0), p3 = fast_exp2(s[3] - mn1);
-                l0 = l0 * corr0 + p0 + p2;
-                l1 = l1 * corr1 + p1 + p3;
-                m0 = mn0;
-                m1 = mn1;
-                const uint32_t pk01 = Elem<__half>::pack2(p0, p1), pk23 = Elem<__half>::pack2(p2, p3);
-                {
-                    const float2 r01 = Elem<__half>::unpack2(pk01), r23 = Elem<__half>::unpack2(pk23);
-                    lr0 = lr0 * corr0 + r01.x + r23.x;
-                    lr1 = lr1 * corr1 + r01.y + r23.y;
-                }
-                if (__any_sync(0xffffffffu, corr0 != 1.f || corr1 != 1.f)) {
+                if constexpr (kQ8) {
+                    // weight of this tile against the running maximum, and the probabilities against the tile's own
+                    const float w0 = fast_exp2(mx0 - mn0), w1 = fast_exp2(mx1 - mn1);
+                    const float e0 = fast_exp2(s[0] - mx0), e1 = fast_exp2(s[1] - mx1);
+                    const float e2 = fast_exp2(s[2] - mx0), e3 = fast_exp2(s[3] - mx1);
+                    l0 = l0 * corr0 + (e0 + e2) * w0;
+                    l1 = l1 * corr1 + (e1 + e3) * w1;
+                    m0 = mn0;
+                    m1 = mn1;
+                    const bool offline = a.p_scale != nullptr;
+                    // online: 127 * 2^(s - tile max), weight w on the tile's result; offline: p * pScale, weight 1
+                    const float f0 = offline ? w0 * ps0 : 127.f, f1 = offline ? w1 * ps1 : 127.f;
+                    const float u0 = offline ? 1.f : w0, u1 = offline ? 1.f : w1;
+                    const int32_t q0 = quant_p(e0 * f0), q1 = quant_p(e1 * f1), q2 = quant_p(e2 * f0), q3 = quant_p(e3 * f1);
+                    if (__any_sync(0xffffffffu, corr0 != 1.f || corr1 != 1.f)) {
 #pragma unroll
-                    for (int mt = 0; mt < 8; ++mt) {
-                        o[mt][0] *= corr0;
-                        o[mt][1] *= corr1;
-                        o[mt][2] *= corr0;
-                        o[mt][3] *= corr1;
+                        for (int mt = 0; mt < 8; ++mt) {
+                            o[mt][0] *= corr0;
+                            o[mt][1] *= corr1;
+                            o[mt][2] *= corr0;
+                            o[mt][3] *= corr1;
+                        }
                     }
-                }
-                const uint32_t b0 = movmatrix_trans(pk01);
-                const uint32_t b1 = movmatrix_trans(pk23);
-                // ---- O^T += V^T . P^T  (128 dims x 8 heads, k = 16 tokens)
-                {
-                    // one ldmatrix.x4.trans = 16 tokens x 32 int8 dims = two 16-dim row tiles.  A thread
-                    // receives (token 2c, dims 2g,2g+1 | token 2c+1, dims 2g,2g+1) per 8-token matrix, so
-                    // within a row tile the mma row g holds dim 2g and the row g+8 holds dim 2g+1.
+                    // P^T as the B operand: after the transposes a thread holds, for head g, tokens 2c, 2c+1 (and
+                    // 8+2c, 9+2c) in 16-bit slots; their low bytes are the operand's k slots 4c..4c+3
+                    const uint32_t ta = movmatrix_trans((uint32_t)q0 | ((uint32_t)q1 << 16));
+                    const uint32_t tb = movmatrix_trans((uint32_t)q2 | ((uint32_t)q3 << 16));
+                    const uint32_t bq = __byte_perm(ta, tb, 0x6420);
+                    // ---- O^T += w * (V^T . P^T)  (128 dims x 8 heads, k = 16 tokens; the thread's registers hold
+                    // tokens {2c, 2c+1} / {8+2c, 9+2c} x dims {2g, 2g+1}: even bytes are dim 2g = mma row g, odd
+                    // bytes dim 2g+1 = row g+8, the same row order as the float path)
                     const int t = warp * 16 + (lane & 15);
                     const uint32_t row_addr = vbase + t * 128;
                     const int sw = t & 7;
@@ -324,16 +386,66 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
                         const int ch = mm * 2 + (lane >> 4);
                         uint32_t r[4];
                         ldmatrix_x4_trans(r, row_addr + ((ch ^ sw) << 4));
-                        uint32_t af[4];
-                        i8x4_to_h2x2_even_odd(r[0], af[0], af[1]);
-                        i8x4_to_h2x2_even_odd(r[1], af[2], af[3]);
-                        mma_16816<__half>(o[2 * mm], af, b0, b1);
-                        i8x4_to_h2x2_even_odd(r[2], af[0], af[1]);
-                        i8x4_to_h2x2_even_odd(r[3], af[2], af[3]);
-                        mma_16816<__half>(o[2 * mm + 1], af, b0, b1);
+#pragma unroll
+                        for (int hf = 0; hf < 2; ++hf) {
+                            int32_t d[4] = {0, 0, 0, 0};
+                            mma_s8_16816(d, __byte_perm(r[2 * hf], r[2 * hf + 1], 0x6420),
+                                         __byte_perm(r[2 * hf], r[2 * hf + 1], 0x7531), bq);
+                            float *oo = o[2 * mm + hf];
+                            oo[0] = fmaf((float)d[0], u0, oo[0]);
+                            oo[1] = fmaf((float)d[1], u1, oo[1]);
+                            oo[2] = fmaf((float)d[2], u0, oo[2]);
+                            oo[3] = fmaf((float)d[3], u1, oo[3]);
+                        }
+                    }
+                } else {
+                    const float p0 = fast_exp2(s[0] - mn0), p1 = fast_exp2(s[1] - mn1);
+                    const float p2 = fast_exp2(s[2] - mn0), p3 = fast_exp2(s[3] - mn1);
+                    l0 = l0 * corr0 + p0 + p2;
+                    l1 = l1 * corr1 + p1 + p3;
+                    m0 = mn0;
+                    m1 = mn1;
+                    const uint32_t pk01 = Elem<__half>::pack2(p0, p1), pk23 = Elem<__half>::pack2(p2, p3);
+                    {
+                        const float2 r01 = Elem<__half>::unpack2(pk01), r23 = Elem<__half>::unpack2(pk23);
+                        lr0 = lr0 * corr0 + r01.x + r23.x;
+                        lr1 = lr1 * corr1 + r01.y + r23.y;
+                    }
+                    if (__any_sync(0xffffffffu, corr0 != 1.f || corr1 != 1.f)) {
+    #pragma unroll
+                        for (int mt = 0; mt < 8; ++mt) {
+                            o[mt][0] *= corr0;
+                            o[mt][1] *= corr1;
+                            o[mt][2] *= corr0;
+                            o[mt][3] *= corr1;
+                        }
+                    }
+                    const uint32_t b0 = movmatrix_trans(pk01);
+                    const uint32_t b1 = movmatrix_trans(pk23);
+                    // ---- O^T += V^T . P^T  (128 dims x 8 heads, k = 16 tokens)
+                    {
+                        // one ldmatrix.x4.trans = 16 tokens x 32 int8 dims = two 16-dim row tiles.  A thread
+                        // receives (token 2c, dims 2g,2g+1 | token 2c+1, dims 2g,2g+1) per 8-token matrix, so
+                        // within a row tile the mma row g holds dim 2g and the row g+8 holds dim 2g+1.
+                        const int t = warp * 16 + (lane & 15);
+                        const uint32_t row_addr = vbase + t * 128;
+                        const int sw = t & 7;
+    #pragma unroll
+                        for (int mm = 0; mm < 4; ++mm) {
+                            const int ch = mm * 2 + (lane >> 4);
+                            uint32_t r[4];
+                            ldmatrix_x4_trans(r, row_addr + ((ch ^ sw) << 4));
+                            uint32_t af[4];
+                            i8x4_to_h2x2_even_odd(r[0], af[0], af[1]);
+                            i8x4_to_h2x2_even_odd(r[1], af[2], af[3]);
+                            mma_16816<__half>(o[2 * mm], af, b0, b1);
+                            i8x4_to_h2x2_even_odd(r[2], af[0], af[1]);
+                            i8x4_to_h2x2_even_odd(r[3], af[2], af[3]);
+                            mma_16816<__half>(o[2 * mm + 1], af, b0, b1);
+                        }
                     }
                 }
-            }
+                }
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(&empty[stage]);
@@ -354,7 +466,7 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
         }
         // take the bias of the V operand out of this warp's accumulators: 1152 x (sum of its rounded probabilities)
 #pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
+        for (int mt = 0; mt < (kQ8 ? 0 : 8); ++mt) {
             o[mt][0] = fmaf(-kI8Bias, lr0, o[mt][0]);
             o[mt][1] = fmaf(-kI8Bias, lr1, o[mt][1]);
             o[mt][2] = fmaf(-kI8Bias, lr0, o[mt][2]);
@@ -444,13 +556,19 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
                 const float *src = xbuf1 + hl * kFinalStride + d0;
                 float4 va = *reinterpret_cast<const float4 *>(src);
                 float4 vb = *reinterpret_cast<const float4 *>(src + 4);
-                if (a.v_offset != nullptr) {
+                if constexpr (kQ8) {
+                    // one P.V scale per query head; online quantisation put 127 into every probability
+                    const float sc = a.v_descale[head0 + hl] * (a.p_scale != nullptr ? 1.f : 1.f / 127.f);
+                    va.x *= sc; va.y *= sc; va.z *= sc; va.w *= sc;
+                    vb.x *= sc; vb.y *= sc; vb.z *= sc; vb.w *= sc;
+                }
+                if (!kQ8 && a.v_offset != nullptr) {
                     const int4 oa = *reinterpret_cast<const int4 *>(a.v_offset + kvh * 128 + d0);
                     const int4 ob = *reinterpret_cast<const int4 *>(a.v_offset + kvh * 128 + d0 + 4);
                     va.x += (float)oa.x; va.y += (float)oa.y; va.z += (float)oa.z; va.w += (float)oa.w;
                     vb.x += (float)ob.x; vb.y += (float)ob.y; vb.z += (float)ob.z; vb.w += (float)ob.w;
                 }
-                if (a.v_descale != nullptr) {
+                if (!kQ8 && a.v_descale != nullptr) {
                     const float4 sa = *reinterpret_cast<const float4 *>(a.v_descale + kvh * 128 + d0);
                     const float4 sb = *reinterpret_cast<const float4 *>(a.v_descale + kvh * 128 + d0 + 4);
                     va.x *= sa.x; va.y *= sa.y; va.z *= sa.z; va.w *= sa.w;
@@ -566,9 +684,10 @@ bool encode_cache_map(CUtensorMap *map, const void *base, int kv_heads, int bloc
     return r == CUDA_SUCCESS;
 }
 
-template <typename T> cudaError_t launch_typed(const PaArgs &args, const CUtensorMap &km, const CUtensorMap &vm, cudaStream_t s)
+template <typename T, bool kQ8>
+cudaError_t launch_typed(const PaArgs &args, const CUtensorMap &km, const CUtensorMap &vm, cudaStream_t s)
 {
-    auto kern = pa_tma_mma_i8_kernel<T>;
+    auto kern = pa_tma_mma_i8_kernel<T, kQ8>;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -610,7 +729,25 @@ cudaError_t launch_pa_tma_mma_i8(const PaArgs &args, int q_dtype, int num_blocks
         !encode_cache_map(&vm, args.v_cache, args.kv_heads, args.block_size, num_blocks)) {
         return cudaErrorInvalidValue;
     }
-    return q_dtype == kFp16 ? launch_typed<__half>(args, km, vm, stream) : launch_typed<__nv_bfloat16>(args, km, vm, stream);
+    return q_dtype == kFp16 ? launch_typed<__half, false>(args, km, vm, stream)
+                            : launch_typed<__nv_bfloat16, false>(args, km, vm, stream);
+}
+
+bool pa_tma_mma_q8_supported(int dk, int dv, int v_row_dim, int block_size, int group, int out_dtype)
+{
+    return pa_tma_mma_i8_supported(dk, dv, v_row_dim, block_size, group, out_dtype, kInt8);
+}
+
+cudaError_t launch_pa_tma_mma_q8(const PaArgs &args, int out_dtype, int num_blocks, cudaStream_t stream)
+{
+    CUtensorMap km, vm;
+    if (args.k_descale == nullptr || args.v_descale == nullptr ||
+        !encode_cache_map(&km, args.k_cache, args.kv_heads, args.block_size, num_blocks) ||
+        !encode_cache_map(&vm, args.v_cache, args.kv_heads, args.block_size, num_blocks)) {
+        return cudaErrorInvalidValue;
+    }
+    return out_dtype == kFp16 ? launch_typed<__half, true>(args, km, vm, stream)
+                              : launch_typed<__nv_bfloat16, true>(args, km, vm, stream);
 }
 
 } // namespace atb_b200

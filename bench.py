@@ -288,11 +288,12 @@ def measure_decode(args, case, rt, steps, with_cpu_baseline):
     # and the steps are timed one by one so that the flush stays outside.
     flush_l2 = wl.kv_bytes(shard, lens) < 2 * L2_BYTES
     flush = L2Flusher(dev) if flush_l2 else None
-    n_prof = min(steps, 256)
     with torch.cuda.stream(stream):
-        # value, ms_per_step and the attention kernel's own time all come from the SAME steps: every launch carries a
-        # CUDA-event pair around the attention kernel (atb_b200_pa_plan_set_profiling)
-        plan.set_profiling(True)
+        # value, ms_per_step and the attention kernel's own time all come from the SAME steps: every prof_stride-th
+        # launch carries a CUDA-event pair around the attention kernel (atb_b200_pa_plan_set_profiling; an event
+        # between ReshapeAndCache and attention costs their programmatic overlap, hence not every launch)
+        prof_stride = 8 if steps >= 100 else (4 if steps >= 12 else 1)
+        plan.set_profiling(prof_stride)
         for _ in range(args.warmup):
             step()
         barrier()
@@ -319,6 +320,7 @@ def measure_decode(args, case, rt, steps, with_cpu_baseline):
             e1.record(stream)
             barrier()
             ms = e0.elapsed_time(e1) / steps
+        n_prof = max(1, min((steps + prof_stride - 1) // prof_stride, 256))
         kernel_ms = float(np.mean([plan.kernel_ms(i) for i in range(n_prof)]))
         clocks = sampler.stop() if rank == 0 else None
         plan.set_profiling(False)
@@ -400,6 +402,7 @@ def measure_decode(args, case, rt, steps, with_cpu_baseline):
                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT,
                             "frac": achieved / peak, "peak_kind": "of " + peak_kind,
                             "kernel": "pa attention kernel, per GPU", "kernel_ms": kernel_ms,
+                            "kernel_samples": n_prof,
                             "kernel_ms_x_sm_mhz": kernel_ms * sm_mhz if sm_mhz else None,
                             "traffic": ncu_traffic_bytes(case.name) if world == 1 else None},
                "max_abs_err_vs_oracle": err,

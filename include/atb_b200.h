@@ -48,7 +48,7 @@ typedef struct atb_b200_pa_desc {
     int32_t block_size;     /* tokens per cache block */
     int32_t num_blocks;     /* blocks in the cache */
     int32_t max_blocks_per_seq; /* row length of block_tables */
-    int32_t q_dtype;        /* ATB_B200_FP16 | ATB_B200_BF16; also the output type */
+    int32_t q_dtype;        /* ATB_B200_FP16 | ATB_B200_BF16; also the output type (ATB_B200_INT8 with qkv_quant) */
     int32_t kv_dtype;       /* same as q_dtype, or ATB_B200_INT8 */
     float qk_scale;         /* multiplies Q*K^T */
     int32_t kernel;         /* ATB_B200_KERNEL_*; AUTO unless forcing a path */
@@ -69,7 +69,15 @@ typedef struct atb_b200_pa_desc {
                                cache (at most 8 pairs; fp16 / bf16, head_dim 128); the MLA kernel takes any n: its
                                rows are the n x heads (token, head) pairs.  A mask is indexed per (sequence, token):
                                see mask_q_stride */
+    int32_t qkv_quant;      /* 0, or ATB_B200_QUANT_ONLINE / ATB_B200_QUANT_OFFLINE (quantType TYPE_QUANT_QKV_ONLINE /
+                               OFFLINE of the reference): q_dtype and kv_dtype are ATB_B200_INT8, k_descale and v_descale
+                               hold ONE fp32 scale per query head ([num_heads]: of Q.K^T and of P.V), the probabilities
+                               are quantised to int8 - online against each tile's own maximum, offline with p_scale
+                               [num_heads] - and both contractions run on the integer tensor cores; head_dim 128 */
+    int32_t out_dtype;      /* qkv_quant only: ATB_B200_FP16 | ATB_B200_BF16, the type of `out` */
 } atb_b200_pa_desc;
+
+enum { ATB_B200_QUANT_ONLINE = 1, ATB_B200_QUANT_OFFLINE = 2 };
 
 enum { ATB_B200_KV_BSND = 0, ATB_B200_KV_BNSD = 1 };
 
@@ -113,6 +121,7 @@ typedef struct atb_b200_pa_tensors {
     void *lse_out;              /* optional, MLA kernel only: [batch, num_heads] in q_dtype, the natural-log
                                    log-sum-exp of the scaled scores of every (token, head) (the second output of
                                    MultiLatentAttention with CALC_TYPE_RING); NULL = not wanted */
+    const float *p_scale;       /* ATB_B200_QUANT_OFFLINE only: [num_heads] fp32 */
 } atb_b200_pa_tensors;
 
 typedef struct atb_b200_pa_plan atb_b200_pa_plan; /* opaque */
@@ -240,10 +249,11 @@ int atb_b200_pa_plan_device_status(atb_b200_pa_plan *plan, void *workspace, void
  * evenly the plan loads the SMs.  NULL switches it off. */
 int atb_b200_pa_plan_set_trace(atb_b200_pa_plan *plan, void *device_events, uint32_t capacity);
 
-/* Optional timing of the attention kernel alone: when enabled, every launch records a pair of
- * CUDA events on the launch stream around that kernel (a ring of 256 pairs).  kernel_ms returns
- * the duration of the launch `launches_back` launches ago (0 = the latest) and synchronises on
- * its second event. */
+/* Optional timing of the attention kernel alone: with enable = n > 0 every n-th launch (the first one included)
+ * records a pair of CUDA events on the launch stream around that kernel (a ring of 256 pairs); 0 switches it
+ * off.  An event between ReshapeAndCache and the attention kernel costs their programmatic overlap, so a
+ * stride above 1 keeps the timed steps close to untimed ones.  kernel_ms returns the duration of the timed
+ * launch `launches_back` timed launches ago (0 = the latest) and synchronises on its second event. */
 int atb_b200_pa_plan_set_profiling(atb_b200_pa_plan *plan, int enable);
 int atb_b200_pa_plan_kernel_ms(atb_b200_pa_plan *plan, int32_t launches_back, float *ms);
 
