@@ -681,138 +681,6 @@ pa_mla_tc5_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             // the next range's first P.V overwrites O: all reads of O must be done first.  It cannot start
             // before the next P tile is signalled by these same warps, which orders it after this point.
             tc_fence_before();
-            if (item.slot >= 0 && a.plan.counters != nullptr) {
-                // In-kernel merge, warp by warp (no CTA-wide barrier): warp w of every range writes head rows
-                // 16w..16w+15 of its partial; the warp that arrives last on the (sequence, 64-head column, w) counter
-                // finds all of them written (fence + counter, nobody spins) and combines them with their
-                // log-sum-exp weights, as the separate combine kernel would.
-                __threadfence();
-                __syncwarp();
-                const int n_parts = a.plan.seq_nparts[item.seq];
-                int last = 0;
-                if (lane == 0) {
-                    last = atomicAdd(&a.plan.counters[(item.seq * cols + col) * 4 + warp], 1) == n_parts - 1 ? 1 : 0;
-                }
-                last = __shfl_sync(0xffffffffu, last, 0);
-                if (last) {
-                    __threadfence();
-                    const int pbase = a.plan.seq_part_base[item.seq];
-                    const int r_begin = warp * 16, r_end = min(warp * 16 + 16, nh);
-                    // Every load below hits L2 with ~1 us of latency, so the loop is built for loads in flight, not
-                    // for instruction count.  Phase 1: lane r owns head row r_begin + r and turns the row's
-                    // log-sum-exps into merge weights (kept in registers for up to kMergeRegParts ranges).
-                    constexpr int kMergeRegParts = 8;
-                    float wreg[kMergeRegParts];
-                    float mx = -INFINITY, wsum = 0.f;
-                    const bool own = lane < r_end - r_begin;
-                    const float *lse = a.plan.part_lse + (int64_t)pbase * a.num_heads + head0 + r_begin + (own ? lane : 0);
-#pragma unroll
-                    for (int i = 0; i < kMergeRegParts; ++i) {
-                        wreg[i] = (own && i < n_parts) ? __ldcg(lse + (int64_t)i * a.num_heads) : -INFINITY;
-                        mx = fmaxf(mx, wreg[i]);
-                    }
-                    for (int i = kMergeRegParts; i < n_parts; ++i) {
-                        mx = fmaxf(mx, own ? __ldcg(lse + (int64_t)i * a.num_heads) : -INFINITY);
-                    }
-#pragma unroll
-                    for (int i = 0; i < kMergeRegParts; ++i) {
-                        wreg[i] = exp2f(wreg[i] - mx); // 0 for the ranges that do not exist
-                        wsum += wreg[i];
-                    }
-                    for (int i = kMergeRegParts; i < n_parts; ++i) {
-                        wsum += own ? exp2f(__ldcg(lse + (int64_t)i * a.num_heads) - mx) : 0.f;
-                    }
-                    const float inv_w = own ? 1.f / wsum : 0.f;
-                    if (own && a.lse_out != nullptr) {
-                        // log-sum-exp of the whole sequence from its ranges' (log2 domain), as a natural log
-                        static_cast<T *>(a.lse_out)[(int64_t)item.seq * a.num_heads + head0 + r_begin + lane] =
-                            Elem<T>::from_float((mx + log2f(wsum)) * 0.6931471805599453f);
-                    }
-                    // Phase 2: two head rows at a time, a lane per 16 consecutive dims of each (contiguous 2 KB per
-                    // row and range), all loads of a step issued before the first is used.
-                    const int64_t part_stride = (int64_t)a.num_heads * kDv;
-                    for (int r = r_begin; r < r_end; r += 2) {
-                        const bool two = r + 1 < r_end;
-                        const float *po0 = a.plan.part_o + ((int64_t)pbase * a.num_heads + head0 + r) * kDv + lane * 16;
-                        const float *po1 = po0 + (two ? kDv : 0);
-                        float acc0[16], acc1[16];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            acc0[j] = acc1[j] = 0.f;
-                        }
-                        const float inv0 = __shfl_sync(0xffffffffu, inv_w, r - r_begin);
-                        const float inv1 = __shfl_sync(0xffffffffu, inv_w, min(r + 1 - r_begin, 15));
-                        const float mx0 = __shfl_sync(0xffffffffu, mx, r - r_begin);
-                        const float mx1 = __shfl_sync(0xffffffffu, mx, min(r + 1 - r_begin, 15));
-                        for (int i0 = 0; i0 < n_parts; i0 += 2) {
-                            // two ranges x two rows = 16 float4 loads in flight per lane
-                            const bool second = i0 + 1 < n_parts;
-                            float4 v[2][2][4];
-#pragma unroll
-                            for (int u = 0; u < 2; ++u) {
-                                const int64_t off = (int64_t)(i0 + ((u == 1 && second) ? 1 : 0)) * part_stride;
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    v[u][0][j] = __ldcg(reinterpret_cast<const float4 *>(po0 + off) + j);
-                                    v[u][1][j] = __ldcg(reinterpret_cast<const float4 *>(po1 + off) + j);
-                                }
-                            }
-#pragma unroll
-                            for (int u = 0; u < 2; ++u) {
-                                const int i = i0 + u;
-                                float w0, w1;
-                                if (i < kMergeRegParts) {
-                                    // the weights live in the owning lanes' registers: fetch part i0 + u of both rows
-                                    float mine = 0.f;
-#pragma unroll
-                                    for (int k = 0; k < kMergeRegParts; ++k) {
-                                        mine = (k == i) ? wreg[k] : mine;
-                                    }
-                                    w0 = __shfl_sync(0xffffffffu, mine, r - r_begin) * inv0;
-                                    w1 = __shfl_sync(0xffffffffu, mine, min(r + 1 - r_begin, 15)) * inv1;
-                                } else {
-                                    const float *l0p = a.plan.part_lse + (int64_t)(pbase + min(i, n_parts - 1)) * a.num_heads + head0 + r;
-                                    w0 = exp2f(__ldcg(l0p) - mx0) * inv0;
-                                    w1 = exp2f(__ldcg(l0p + (two ? 1 : 0)) - mx1) * inv1;
-                                }
-                                if (u == 1 && !second) {
-                                    w0 = w1 = 0.f;
-                                }
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    acc0[4 * j] = fmaf(w0, v[u][0][j].x, acc0[4 * j]);
-                                    acc0[4 * j + 1] = fmaf(w0, v[u][0][j].y, acc0[4 * j + 1]);
-                                    acc0[4 * j + 2] = fmaf(w0, v[u][0][j].z, acc0[4 * j + 2]);
-                                    acc0[4 * j + 3] = fmaf(w0, v[u][0][j].w, acc0[4 * j + 3]);
-                                    acc1[4 * j] = fmaf(w1, v[u][1][j].x, acc1[4 * j]);
-                                    acc1[4 * j + 1] = fmaf(w1, v[u][1][j].y, acc1[4 * j + 1]);
-                                    acc1[4 * j + 2] = fmaf(w1, v[u][1][j].z, acc1[4 * j + 2]);
-                                    acc1[4 * j + 3] = fmaf(w1, v[u][1][j].w, acc1[4 * j + 3]);
-                                }
-                            }
-                        }
-#pragma unroll
-                        for (int rr = 0; rr < 2; ++rr) {
-                            if (rr == 1 && !two) {
-                                break;
-                            }
-                            const float *acc = rr == 0 ? acc0 : acc1;
-                            uint32_t w8[8];
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                w8[j] = Elem<T>::pack2(acc[2 * j], acc[2 * j + 1]);
-                            }
-                            T *dst = static_cast<T *>(a.out) + ((int64_t)item.seq * a.num_heads + head0 + r + rr) * kDv + lane * 16;
-                            if (out_wide) {
-                                st_global_v8(dst, w8);
-                            } else {
-                                *reinterpret_cast<uint4 *>(dst) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
-                                *reinterpret_cast<uint4 *>(dst + 8) = make_uint4(w8[4], w8[5], w8[6], w8[7]);
-                            }
-                        }
-                    }
-                }
-            }
         }
     }
 

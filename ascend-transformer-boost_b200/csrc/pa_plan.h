@@ -6,7 +6,7 @@
 // balance).  All columns of a group walk the same token ranges, so the 8 kv-head slices of one
 // cache page are read at about the same time.  A sequence cut into several ranges yields one fp32
 // partial result per range; the range that finishes last merges them with their log-sum-exp weights
-// (the CUDA-core kernel leaves that to the combine kernel).
+// (the CUDA-core and the MLA kernels leave that to the combine kernel).
 //
 // Stands in for the core-split / split-KV tiling of the reference
 // (src/kernels/mixkernels/pagedattention/tiling/paged_attention_tiling_dependency.cpp:186-212, 406-521).
@@ -37,8 +37,7 @@ struct PaDevPlan {
     float *part_o;                // [n_partials, num_heads, dv] normalised partial outputs
     float *part_lse;              // [n_partials, num_heads] log2-domain log-sum-exp
     int32_t *status;              // device status word (0 = ok)
-    int32_t *counters;            // [batch * cols] arrivals per (sequence, column) ([batch * cols * 4], one per
-                                  // softmax warp, in the MLA kernel), zero before the launch;
+    int32_t *counters;            // [batch * cols] arrivals per (sequence, column), zero before the launch;
                                   // non-null = the last range to finish merges the partials itself
     int32_t *done_ctas;           // CTAs that have finished (zero before the launch); used by the
                                   // cross-GPU completion exchange

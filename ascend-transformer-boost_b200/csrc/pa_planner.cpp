@@ -304,12 +304,10 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
     p->off_status = off; // zeroed by every upload
     p->off_done = off + 4;
     off += 16;
-    p->fused_combine = kernel == ATB_B200_KERNEL_TMA_MMA || kernel == ATB_B200_KERNEL_MLA_TC5;
+    p->fused_combine = kernel == ATB_B200_KERNEL_TMA_MMA;
     p->off_counters = off;
     if (p->fused_combine && p->n_partials > 0) {
-        // one arrival counter per (sequence, column); the MLA kernel counts each of its four softmax warps apart
-        const uint64_t per_col = kernel == ATB_B200_KERNEL_MLA_TC5 ? 4 : 1;
-        off = align_up(off + (uint64_t)d.batch * p->cols * per_col * sizeof(int32_t), 16);
+        off = align_up(off + (uint64_t)d.batch * p->cols * sizeof(int32_t), 16);
     }
     if ((d.score_mods & ATB_B200_SCORE_CAUSAL) != 0) {
         p->seq_lens.assign(context_lens, context_lens + d.batch);

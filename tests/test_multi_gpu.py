@@ -1,6 +1,9 @@
-"""Head-sharded decode on 2 GPUs: each rank's attention kernel stores its heads into every rank's
-gathered output through peer memory; both ranks must end up with the unsharded oracle result.
-Runs as child processes (one per GPU); skipped when fewer than 2 GPUs are visible."""
+"""Decode on 2 GPUs, as child processes (one per GPU); skipped when fewer than 2 GPUs are visible.
+
+Head-sharded: each rank's attention kernel stores its heads into every rank's gathered output through peer
+memory; both ranks must end up with the unsharded oracle result.  Sequence-sharded (the MLA cache has one kv
+head): each rank runs its contiguous share of the batch and the outputs are all-gathered along the first
+dimension (NCCL); the result must equal the unsharded oracle result too."""
 import os
 import socket
 import sys
@@ -86,3 +89,53 @@ def test_peer_store_gather_matches_oracle(case_kw, tmp_path):
         for step in range(got.shape[0]):
             g = got[step].view(ref.dtype) if got.dtype != ref.dtype else got[step]
             assert max_abs_err(g, ref, case.q_dtype) <= tol_for(case), (rank, step)
+
+
+def _mla_rank_main(rank, world, port, case_kw, result_dir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    wl, sh, capi = pkg.workloads, pkg.sharding, pkg.capi
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from helpers import to_dev
+    case = wl.Case(**case_kw)
+    h = wl.make_host_inputs(case)
+    mine = sh.shard_host_inputs_by_sequence(case, h, rank, world)
+    q = to_dev(mine["q"], case.q_dtype)
+    kc = to_dev(mine["k_cache"], case.kvd)
+    bt = torch.from_numpy(mine["block_tables"]).cuda()
+    nk = to_dev(mine["new_k"], case.kvd)
+    slots = torch.from_numpy(mine["slot_mapping"]).cuda()
+    capi.reshape_and_cache(nk, None, kc, None, slots)
+    out = capi.paged_attention(q, kc, None, bt, mine["context_lens"], case.qk_scale, dv=case.dv)
+    gathered = sh.all_gather_outputs(out)
+    torch.cuda.synchronize()
+    full = sh.gathered_sequences_to_full(gathered)
+    np.save(os.path.join(result_dir, f"mla_full_{rank}.npy"), wl.torch_to_host(full, case.q_dtype))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_sequence_sharded_mla_matches_oracle(tmp_path):
+    sys.path.insert(0, ROOT)
+    import oracle
+    from helpers import max_abs_err, tol_for, wl
+    case_kw = dict(name="seqshard_mla", batch=6, heads=128, kv_heads=1, dk=576, dv=512, q_dtype="bf16", mla=True,
+                   ctx=("list", [700, 64, 1500, 129, 3000, 257]), seed=63)
+    world = 2
+    mp.spawn(_mla_rank_main, args=(world, _free_port(), case_kw, str(tmp_path)), nprocs=world, join=True)
+    case = wl.Case(**case_kw)
+    h = wl.make_host_inputs(case)
+    oracle.reshape_and_cache(h["new_k"], None, h["k_cache"], None, h["slot_mapping"])
+    ref = oracle.paged_attention(h["q"], h["k_cache"], None, h["block_tables"], h["context_lens"], case.qk_scale,
+                                 case.q_dtype, dv=case.dv)
+    for rank in range(world):
+        got = np.load(os.path.join(str(tmp_path), f"mla_full_{rank}.npy"))
+        g = got.view(ref.dtype) if got.dtype != ref.dtype else got
+        assert max_abs_err(g, ref, case.q_dtype) <= tol_for(case), rank
