@@ -163,7 +163,7 @@ extern "C" int atb_b200_pa_decode_static_scratch(const atb_b200_pa_desc *desc, c
     // ---- work split on the stack: same balanced cut as the regular planner, fixed capacity
     const int heads_per_cta = kernel == ATB_B200_KERNEL_TMA_MMA ? 8 : pa_generic_heads_per_cta(d.head_dim_k, d.head_dim_v);
     const int chunks_per_kvh = (group + heads_per_cta - 1) / heads_per_cta;
-    const int ctas_per_sm = kernel == ATB_B200_KERNEL_TMA_MMA ? 2 : 4;
+    const int ctas_per_sm = kernel == ATB_B200_KERNEL_TMA_MMA ? (d.head_dim_k > 128 ? 1 : 2) : 4;
     const int cols = d.kv_heads * chunks_per_kvh;
     const int64_t max_ctx = (int64_t)d.max_blocks_per_seq * d.block_size;
     int64_t seq_start[kMaxBatch + 1];

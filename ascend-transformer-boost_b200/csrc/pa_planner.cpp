@@ -133,7 +133,7 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
     if (kernel == ATB_B200_KERNEL_TMA_MMA) {
         p->heads_per_cta = 8;
         p->chunks_per_kvh = (group + 7) / 8; // more than 8 heads per kv head: several columns over the same K/V tiles
-        p->ctas_per_sm = 2;
+        p->ctas_per_sm = d.head_dim_k > 128 ? 1 : 2; // the 3-stage ring of 256-wide rows takes 192 KB of shared memory
     } else if (kernel == ATB_B200_KERNEL_MLA_TC5) {
         p->heads_per_cta = 64;
         p->chunks_per_kvh = (group + 63) / 64;

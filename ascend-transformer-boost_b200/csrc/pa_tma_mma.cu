@@ -1,5 +1,5 @@
-// Paged decode attention for head_dim 128 / block_size 16, 32, 64, 128 or 256 and up to 8 query heads per kv head
-// (MHA and GQA, fp16 / bf16 cache): the HBM-bound hot kernel.
+// Paged decode attention for head_dim 64, 128 or 256 / block_size 16, 32, 64, 128 or 256 (MHA and GQA, fp16 / bf16
+// cache; 8 query heads of one kv head per CTA, larger groups as several CTA columns): the HBM-bound hot kernel.
 //
 // One CTA per (CTA group, kv head), two CTAs per SM.  A producer warp walks the CTA's token ranges,
 // looks the physical block of every 64-token stage up in block_tables and issues TMA tile loads
@@ -27,24 +27,33 @@ namespace atb_b200 {
 namespace {
 
 constexpr int kStageTokens = 64;
-constexpr int kStages = 3;
 constexpr int kConsumerWarps = 4;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
-constexpr int kHalfBytes = kStageTokens * 128;      // 64 tokens x 64 elements x 2 B
-constexpr int kStageBytes = 4 * kHalfBytes;         // K lo, K hi, V lo, V hi
-constexpr int kXbufFloats = 32 * 32;                // one warp's O fragments
-constexpr int kFinalStride = 132;                   // padded [head][dim] row (floats)
-constexpr int kSmemBytes = kStages * kStageBytes + (kXbufFloats + 8 * kFinalStride + 64) * 4 + 2 * kStages * 8 + 1024;
+constexpr int kHalfBytes = kStageTokens * 128;      // 64 tokens x 64 elements x 2 B: one TMA box
+
+// Sizes that follow from the head dimension kD (64, 128 or 256).  A row is kD / 64 boxes of 64 elements.
+template <int kD> struct Geo {
+    static_assert(kD == 64 || kD == 128 || kD == 256, "head dimensions of the tiled kernel");
+    static constexpr int kHalves = kD / 64;                       // boxes per K (or V) row
+    static constexpr int kStageBytes = 2 * kHalves * kHalfBytes;  // K boxes, then V boxes
+    static constexpr int kStages = kD == 64 ? 6 : 3;              // 96 KB (two CTAs per SM); 192 KB at kD = 256 (one)
+    static constexpr int kSteps = kD / 16;                        // k steps of Q.K^T = row tiles of V^T.P^T
+    static constexpr int kXbufFloats = kSteps * 4 * 32;           // one warp's O fragments
+    static constexpr int kFinalStride = kD + 4;                   // padded [head][dim] row (floats)
+    static constexpr int kSmemBytes =
+        kStages * kStageBytes + (kXbufFloats + 8 * kFinalStride + 64) * 4 + 2 * kStages * 8 + 1024;
+    static constexpr int kCtasPerSm = kD == 256 ? 1 : 2;
+};
 
 // Writes 8 output elements of (sequence, local head h) to the output tensor - or, when the heads are
 // sharded over several GPUs, into the gathered [tokens, all heads, 128] buffer of every rank.
-template <typename T>
+template <typename T, int kD>
 __device__ __forceinline__ void store_out_row(const PaArgs &a, int seq, int h, int d0, const uint4 &pk)
 {
     if (a.n_out_peers == 0) {
-        *reinterpret_cast<uint4 *>(static_cast<T *>(a.out) + ((int64_t)seq * a.num_heads + h) * 128 + d0) = pk;
+        *reinterpret_cast<uint4 *>(static_cast<T *>(a.out) + ((int64_t)seq * a.num_heads + h) * kD + d0) = pk;
     } else {
-        const int64_t off = ((int64_t)seq * a.out_total_heads + a.out_head_offset + h) * 128 + d0;
+        const int64_t off = ((int64_t)seq * a.out_total_heads + a.out_head_offset + h) * kD + d0;
 #pragma unroll 1
         for (int r = 0; r < a.n_out_peers; ++r) {
             *reinterpret_cast<uint4 *>(static_cast<T *>(a.out_peers[r]) + off) = pk;
@@ -54,15 +63,17 @@ __device__ __forceinline__ void store_out_row(const PaArgs &a, int seq, int h, i
 
 // kMods: the variant that applies an additive mask and / or per-sequence logN factors to the scores; the plain
 // variant carries none of that code.
-template <typename T, bool kMods>
-__global__ void __launch_bounds__(kThreads, 2)
+template <typename T, bool kMods, int kD>
+__global__ void __launch_bounds__(kThreads, Geo<kD>::kCtasPerSm)
 pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const PaArgs a)
 {
+    constexpr int kHalves = Geo<kD>::kHalves, kStageBytes = Geo<kD>::kStageBytes, kStages = Geo<kD>::kStages;
+    constexpr int kSteps = Geo<kD>::kSteps, kXbufFloats = Geo<kD>::kXbufFloats, kFinalStride = Geo<kD>::kFinalStride;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *stages = base;
     float *xbuf0 = reinterpret_cast<float *>(base + kStages * kStageBytes);
-    float *xbuf1 = xbuf0 + kXbufFloats; // also the final [8][132] tile
+    float *xbuf1 = xbuf0 + kXbufFloats; // also the final [8][kD + 4] tile
     float *sm_m = xbuf1 + 8 * kFinalStride;
     float *sm_l = sm_m + 32;
     uint64_t *full = reinterpret_cast<uint64_t *>(sm_l + 32);
@@ -146,10 +157,14 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             // a block id outside the cache makes the tile out of bounds: TMA fills zeros
                             // coordinates (dim, kv head, token, block); heads-major blocks swap the middle two
                             const int c1 = a.kv_bnsd ? tok_in_blk : kvh, c2 = a.kv_bnsd ? kvh : tok_in_blk;
-                            tma_load_4d(dst, &kmap, &full[stage], 0, c1, c2, b);
-                            tma_load_4d(dst + kHalfBytes, &kmap, &full[stage], 64, c1, c2, b);
-                            tma_load_4d(dst + 2 * kHalfBytes, &vmap, &full[stage], 0, c1, c2, b);
-                            tma_load_4d(dst + 3 * kHalfBytes, &vmap, &full[stage], 64, c1, c2, b);
+#pragma unroll
+                            for (int hf = 0; hf < kHalves; ++hf) {
+                                tma_load_4d(dst + hf * kHalfBytes, &kmap, &full[stage], 64 * hf, c1, c2, b);
+                            }
+#pragma unroll
+                            for (int hf = 0; hf < kHalves; ++hf) {
+                                tma_load_4d(dst + (kHalves + hf) * kHalfBytes, &vmap, &full[stage], 64 * hf, c1, c2, b);
+                            }
                         }
                     }
                     if (++stage == kStages) {
@@ -177,19 +192,19 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 
     for (int it = item_begin; it < item_end; ++it) {
         const PaItem item = a.plan.items[it];
-        uint32_t qf[8][2];
+        uint32_t qf[kSteps][2];
         {
             const bool valid = g < group;
-            const T *qp = q + ((int64_t)item.seq * a.num_heads + head_of(valid ? g : 0)) * 128;
+            const T *qp = q + ((int64_t)item.seq * a.num_heads + head_of(valid ? g : 0)) * kD;
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
+            for (int ks = 0; ks < kSteps; ++ks) {
                 qf[ks][0] = valid ? *reinterpret_cast<const uint32_t *>(qp + ks * 16 + 2 * c) : 0u;
                 qf[ks][1] = valid ? *reinterpret_cast<const uint32_t *>(qp + ks * 16 + 8 + 2 * c) : 0u;
             }
         }
-        float o[8][4];
+        float o[kSteps][4];
 #pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
+        for (int mt = 0; mt < kSteps; ++mt) {
             o[mt][0] = o[mt][1] = o[mt][2] = o[mt][3] = 0.f;
         }
         float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
@@ -226,29 +241,30 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             }
             if (valid_tokens > 0) {
                 const uint32_t kbase = stages_u32 + stage * kStageBytes;
-                const uint32_t vbase = kbase + 2 * kHalfBytes;
+                const uint32_t vbase = kbase + kHalves * kHalfBytes;
                 if (valid_tokens < 16) {
                     // rows past the end of the sequence may hold anything (even NaN bit patterns):
                     // clear this warp's unused V rows so that 0 * V stays 0
-                    uint8_t *vs = stages + stage * kStageBytes + 2 * kHalfBytes;
+                    uint8_t *vs = stages + stage * kStageBytes + kHalves * kHalfBytes;
                     const int rows = 16 - valid_tokens;
-                    for (int i = lane; i < rows * 16; i += 32) { // 16 x 16-byte chunks per row (2 halves x 8)
-                        const int r = warp * 16 + valid_tokens + (i >> 4);
-                        const int ch = i & 15;
+                    constexpr int kRowChunks = kD / 8; // 16-byte chunks per row (8 per box)
+                    for (int i = lane; i < rows * kRowChunks; i += 32) {
+                        const int r = warp * 16 + valid_tokens + i / kRowChunks;
+                        const int ch = i % kRowChunks;
                         *reinterpret_cast<uint4 *>(vs + (ch >> 3) * kHalfBytes + r * 128 + ((ch & 7) << 4)) =
                             make_uint4(0, 0, 0, 0);
                     }
                     fence_proxy_async();
                     __syncwarp();
                 }
-                // ---- S^T = K . Q^T  (16 tokens x 8 heads, k = 128)
+                // ---- S^T = K . Q^T  (16 tokens x 8 heads, k = kD)
                 float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
                 {
                     const int t = warp * 16 + (lane & 15);
                     const uint32_t row_addr = kbase + t * 128;
                     const int sw = t & 7;
 #pragma unroll
-                    for (int ks = 0; ks < 8; ++ks) {
+                    for (int ks = 0; ks < kSteps; ++ks) {
                         const int ch = ks * 2 + (lane >> 4);
                         uint32_t af[4];
                         ldmatrix_x4(af, row_addr + (ch >> 3) * kHalfBytes + (((ch & 7) ^ sw) << 4));
@@ -308,7 +324,7 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 m1 = mn1;
                 if (__any_sync(0xffffffffu, corr0 != 1.f || corr1 != 1.f)) {
 #pragma unroll
-                    for (int mt = 0; mt < 8; ++mt) {
+                    for (int mt = 0; mt < kSteps; ++mt) {
                         o[mt][0] *= corr0;
                         o[mt][1] *= corr1;
                         o[mt][2] *= corr0;
@@ -317,14 +333,14 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 }
                 const uint32_t b0 = movmatrix_trans(Elem<T>::pack2(p0, p1));
                 const uint32_t b1 = movmatrix_trans(Elem<T>::pack2(p2, p3));
-                // ---- O^T += V^T . P^T  (128 dims x 8 heads, k = 16 tokens)
+                // ---- O^T += V^T . P^T  (kD dims x 8 heads, k = 16 tokens)
                 {
                     const int j = lane >> 3;
                     const int tok = warp * 16 + (j >> 1) * 8 + (lane & 7);
                     const uint32_t row_addr = vbase + tok * 128;
                     const int sw = tok & 7;
 #pragma unroll
-                    for (int mt = 0; mt < 8; ++mt) {
+                    for (int mt = 0; mt < kSteps; ++mt) {
                         const int ch = mt * 2 + (j & 1);
                         uint32_t af[4];
                         ldmatrix_x4_trans(af, row_addr + (ch >> 3) * kHalfBytes + (((ch & 7) ^ sw) << 4));
@@ -373,7 +389,7 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             f1 = exp2f(m1 - M1) / L1;
         }
 #pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
+        for (int mt = 0; mt < kSteps; ++mt) {
             o[mt][0] *= f0;
             o[mt][1] *= f1;
             o[mt][2] *= f0;
@@ -382,7 +398,7 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         if (warp >= 2) {
             float *xb = (warp == 2) ? xbuf0 : xbuf1;
 #pragma unroll
-            for (int mt = 0; mt < 8; ++mt) {
+            for (int mt = 0; mt < kSteps; ++mt) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     xb[(mt * 4 + i) * 32 + lane] = o[mt][i];
@@ -393,7 +409,7 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         if (warp < 2) {
             const float *xb = (warp == 0) ? xbuf0 : xbuf1;
 #pragma unroll
-            for (int mt = 0; mt < 8; ++mt) {
+            for (int mt = 0; mt < kSteps; ++mt) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     o[mt][i] += xb[(mt * 4 + i) * 32 + lane];
@@ -403,7 +419,7 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         named_bar_sync(1, kConsumerWarps * 32);
         if (warp == 1) {
 #pragma unroll
-            for (int mt = 0; mt < 8; ++mt) {
+            for (int mt = 0; mt < kSteps; ++mt) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     xbuf0[(mt * 4 + i) * 32 + lane] = o[mt][i];
@@ -413,7 +429,7 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         named_bar_sync(1, kConsumerWarps * 32);
         if (warp == 0) {
 #pragma unroll
-            for (int mt = 0; mt < 8; ++mt) {
+            for (int mt = 0; mt < kSteps; ++mt) {
                 const float v0 = o[mt][0] + xbuf0[(mt * 4 + 0) * 32 + lane];
                 const float v1 = o[mt][1] + xbuf0[(mt * 4 + 1) * 32 + lane];
                 const float v2 = o[mt][2] + xbuf0[(mt * 4 + 2) * 32 + lane];
@@ -425,9 +441,10 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             }
         }
         named_bar_sync(1, kConsumerWarps * 32);
-        {
-            const int hl = threadIdx.x >> 4;       // head within the group
-            const int d0 = (threadIdx.x & 15) * 8; // 8 consecutive dims
+        // kD / 8 chunks of 8 dims per head row, 8 head rows: a thread per chunk (two at kD = 256, half the threads at 64)
+        for (int idx = threadIdx.x; idx < kD; idx += kConsumerWarps * 32) {
+            const int hl = idx / (kD / 8);       // head within the group
+            const int d0 = (idx % (kD / 8)) * 8; // 8 consecutive dims
             if (hl < group) {
                 const float *src = xbuf1 + hl * kFinalStride + d0;
                 const float4 va = *reinterpret_cast<const float4 *>(src);
@@ -439,9 +456,9 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     pk.y = Elem<T>::pack2(va.z, va.w);
                     pk.z = Elem<T>::pack2(vb.x, vb.y);
                     pk.w = Elem<T>::pack2(vb.z, vb.w);
-                    store_out_row<T>(a, item.seq, h, d0, pk);
+                    store_out_row<T, kD>(a, item.seq, h, d0, pk);
                 } else {
-                    float *dst = a.plan.part_o + ((int64_t)item.slot * a.num_heads + h) * 128 + d0;
+                    float *dst = a.plan.part_o + ((int64_t)item.slot * a.num_heads + h) * kD + d0;
                     *reinterpret_cast<float4 *>(dst) = va;
                     *reinterpret_cast<float4 *>(dst + 4) = vb;
                     if (d0 == 0) {
@@ -473,9 +490,12 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             const bool last = sm_l[0] != 0.f;
             if (last) {
                 __threadfence();
-                const int hl = threadIdx.x >> 4;
-                const int d0 = (threadIdx.x & 15) * 8;
-                if (hl < group) {
+                for (int idx = threadIdx.x; idx < kD; idx += kConsumerWarps * 32) {
+                    const int hl = idx / (kD / 8);
+                    const int d0 = (idx % (kD / 8)) * 8;
+                    if (hl >= group) {
+                        continue;
+                    }
                     const int h = head_of(hl);
                     const int pbase = a.plan.seq_part_base[item.seq];
                     const float *lse = a.plan.part_lse + (int64_t)pbase * a.num_heads + h;
@@ -485,12 +505,12 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     }
                     float wsum = 0.f;
                     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                    const float *po = a.plan.part_o + ((int64_t)pbase * a.num_heads + h) * 128 + d0;
+                    const float *po = a.plan.part_o + ((int64_t)pbase * a.num_heads + h) * kD + d0;
                     for (int i = 0; i < n_parts; ++i) {
                         const float w = exp2f(__ldcg(lse + (int64_t)i * a.num_heads) - mx);
                         wsum += w;
-                        const float4 pa = __ldcg(reinterpret_cast<const float4 *>(po + (int64_t)i * a.num_heads * 128));
-                        const float4 pb = __ldcg(reinterpret_cast<const float4 *>(po + (int64_t)i * a.num_heads * 128 + 4));
+                        const float4 pa = __ldcg(reinterpret_cast<const float4 *>(po + (int64_t)i * a.num_heads * kD));
+                        const float4 pb = __ldcg(reinterpret_cast<const float4 *>(po + (int64_t)i * a.num_heads * kD + 4));
                         acc[0] = fmaf(w, pa.x, acc[0]);
                         acc[1] = fmaf(w, pa.y, acc[1]);
                         acc[2] = fmaf(w, pa.z, acc[2]);
@@ -506,7 +526,7 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     pk.y = Elem<T>::pack2(acc[2] * inv, acc[3] * inv);
                     pk.z = Elem<T>::pack2(acc[4] * inv, acc[5] * inv);
                     pk.w = Elem<T>::pack2(acc[6] * inv, acc[7] * inv);
-                    store_out_row<T>(a, item.seq, h, d0, pk);
+                    store_out_row<T, kD>(a, item.seq, h, d0, pk);
                 }
             }
         }
@@ -524,26 +544,27 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 }
 
 
-// 4-D view [num_blocks][block_size][kv_heads][128] of a cache; one box = 64 tokens x 64 elements
+// 4-D view [num_blocks][block_size][kv_heads][dim] of a cache; one box = 64 tokens x 64 elements
 // of one kv head (128-byte rows, 128-byte swizzle).
 bool encode_cache_map(CUtensorMap *map, const void *base, int elem_dtype, int kv_heads, int block_size, int num_blocks,
-                      bool bnsd)
+                      bool bnsd, int dim)
 {
     TmaEncodeFn fn = tma_encode_fn();
     if (fn == nullptr) {
         return false;
     }
     const cuuint64_t es = 2;
-    cuuint64_t dims[4] = {128, (cuuint64_t)kv_heads, (cuuint64_t)block_size, (cuuint64_t)num_blocks};
-    cuuint64_t strides[3] = {128 * es, (cuuint64_t)kv_heads * 128 * es, (cuuint64_t)block_size * kv_heads * 128 * es};
+    const cuuint64_t D = (cuuint64_t)dim;
+    cuuint64_t dims[4] = {D, (cuuint64_t)kv_heads, (cuuint64_t)block_size, (cuuint64_t)num_blocks};
+    cuuint64_t strides[3] = {D * es, (cuuint64_t)kv_heads * D * es, (cuuint64_t)block_size * kv_heads * D * es};
     cuuint32_t box[4] = {64, 1, (cuuint32_t)(block_size < kStageTokens ? block_size : kStageTokens), 1};
     if (bnsd) {
         // [num_blocks][kv_heads][block_size][128]: coordinates (dim, token, kv head, block), strides still ascending;
         // a box is the same 64-element x box_tokens tile in shared memory
         dims[1] = (cuuint64_t)block_size;
         dims[2] = (cuuint64_t)kv_heads;
-        strides[0] = 128 * es;
-        strides[1] = (cuuint64_t)block_size * 128 * es;
+        strides[0] = D * es;
+        strides[1] = (cuuint64_t)block_size * D * es;
         box[1] = box[2];
         box[2] = 1;
     }
@@ -554,11 +575,13 @@ bool encode_cache_map(CUtensorMap *map, const void *base, int elem_dtype, int kv
     return r == CUDA_SUCCESS;
 }
 
-template <typename T> cudaError_t launch_typed(const PaArgs &args, const CUtensorMap &km, const CUtensorMap &vm, cudaStream_t s)
+template <typename T, int kD>
+cudaError_t launch_typed(const PaArgs &args, const CUtensorMap &km, const CUtensorMap &vm, cudaStream_t s)
 {
+    constexpr int kSmemBytes = Geo<kD>::kSmemBytes;
     const bool mods = args.mask != nullptr || args.logn != nullptr || args.bt_rows != nullptr || args.q_per_seq > 1 ||
                       args.seq_lens != nullptr;
-    auto kern = mods ? pa_tma_mma_kernel<T, true> : pa_tma_mma_kernel<T, false>;
+    auto kern = mods ? pa_tma_mma_kernel<T, true, kD> : pa_tma_mma_kernel<T, false, kD>;
     static bool configured_plain[64] = {}, configured_mods[64] = {};
     bool *configured = mods ? configured_mods : configured_plain;
     int dev = 0;
@@ -590,7 +613,7 @@ template <typename T> cudaError_t launch_typed(const PaArgs &args, const CUtenso
 
 bool pa_tma_mma_supported(int dk, int dv, int v_row_dim, int block_size, int group, int q_dtype, int kv_dtype)
 {
-    return dk == 128 && dv == 128 && v_row_dim == 128 && (block_size == 16 || block_size == 32 || block_size == 64 || block_size == 128 || block_size == 256) && group >= 1 &&
+    return (dk == 64 || dk == 128 || dk == 256) && dv == dk && v_row_dim == dk && (block_size == 16 || block_size == 32 || block_size == 64 || block_size == 128 || block_size == 256) && group >= 1 &&
            (q_dtype == kFp16 || q_dtype == kBf16) && kv_dtype == q_dtype;
 }
 
@@ -598,11 +621,21 @@ cudaError_t launch_pa_tma_mma(const PaArgs &args, int q_dtype, int kv_dtype, int
 {
     (void)kv_dtype;
     CUtensorMap km, vm;
-    if (!encode_cache_map(&km, args.k_cache, q_dtype, args.kv_heads, args.block_size, num_blocks, args.kv_bnsd != 0) ||
-        !encode_cache_map(&vm, args.v_cache, q_dtype, args.kv_heads, args.block_size, num_blocks, args.kv_bnsd != 0)) {
+    if (!encode_cache_map(&km, args.k_cache, q_dtype, args.kv_heads, args.block_size, num_blocks, args.kv_bnsd != 0, args.dk) ||
+        !encode_cache_map(&vm, args.v_cache, q_dtype, args.kv_heads, args.block_size, num_blocks, args.kv_bnsd != 0, args.dk)) {
         return cudaErrorInvalidValue;
     }
-    return q_dtype == kFp16 ? launch_typed<__half>(args, km, vm, stream) : launch_typed<__nv_bfloat16>(args, km, vm, stream);
+    const bool f16 = q_dtype == kFp16;
+    switch (args.dk) {
+        case 64:
+            return f16 ? launch_typed<__half, 64>(args, km, vm, stream) : launch_typed<__nv_bfloat16, 64>(args, km, vm, stream);
+        case 128:
+            return f16 ? launch_typed<__half, 128>(args, km, vm, stream) : launch_typed<__nv_bfloat16, 128>(args, km, vm, stream);
+        case 256:
+            return f16 ? launch_typed<__half, 256>(args, km, vm, stream) : launch_typed<__nv_bfloat16, 256>(args, km, vm, stream);
+        default:
+            return cudaErrorInvalidValue;
+    }
 }
 
 } // namespace atb_b200

@@ -489,7 +489,8 @@ def test_planner_routes_score_modifiers():
         return capi.PaPlan(d, lens).info.kernel
     assert plan() == capi.KERNEL_TMA_MMA
     assert plan(mods=capi.SCORE_LOGN | capi.SCORE_MASK) == capi.KERNEL_TMA_MMA
-    assert plan(dk=64) == capi.KERNEL_GENERIC
+    assert plan(dk=64) == capi.KERNEL_TMA_MMA and plan(dk=256) == capi.KERNEL_TMA_MMA
+    assert plan(dk=96) == capi.KERNEL_GENERIC
     assert plan(kv="int8") == capi.KERNEL_GENERIC                          # the int8 TMA kernel carries no mask code
     assert plan(kernel=capi.KERNEL_GENERIC) == capi.KERNEL_GENERIC
     _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, kv="int8", kernel=capi.KERNEL_TMA_MMA)

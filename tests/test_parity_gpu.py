@@ -20,9 +20,8 @@ torch = pytest.importorskip("torch")
 
 def _kernels_for(case):
     ks = [capi.KERNEL_AUTO]
-    group = case.heads // case.kv_heads
-    if case.dk == 128 and case.dv == 128 and case.block_size in (16, 32, 64, 128, 256) and group <= 8 and not case.mla:
-        ks.append(capi.KERNEL_GENERIC)
+    if case.dk == case.dv and case.dk in (64, 128, 256) and case.block_size in (16, 32, 64, 128, 256) and not case.mla:
+        ks.append(capi.KERNEL_GENERIC)                 # the tiled kernel runs these: check the CUDA-core one too
     if case.mla and case.batch * case.heads <= 4096:
         ks.append(capi.KERNEL_GENERIC)
     return ks
@@ -281,3 +280,37 @@ def test_randomized_mla_shapes_match_oracle(heads, lens):
     out, info = run_gpu_case(case, h)
     assert info.kernel == capi.KERNEL_MLA_TC5
     assert max_abs_err(out, ref, "bf16") <= 8e-3
+
+
+# Shapes the tiled kernel took over from the CUDA-core one: head sizes 64 and 256 (one, two or four 64-element TMA
+# boxes per row) and more than 8 query heads per kv head (one CTA column per 8 heads), down to the reference's own
+# regression shapes (tests/apitest/kernelstest/mix/test_paged_attention_common.py:1928 gqa_2 127 / 1, :1977 gqa_3
+# 30 / 2 of the reference), with split sequences, small blocks and empty sequences.
+_WIDE_CASES = [
+    wl.Case("d64_mha_fp16", batch=5, heads=8, kv_heads=8, dk=64, dv=64, q_dtype="fp16", ctx=("list", [1, 63, 64, 700, 3000]), seed=301),
+    wl.Case("d64_gqa4_bf16_bs16", batch=4, heads=16, kv_heads=4, dk=64, dv=64, block_size=16, q_dtype="bf16",
+            ctx=("list", [17, 0, 5000, 129]), seed=302),
+    wl.Case("d256_mha_bf16_bs64", batch=4, heads=4, kv_heads=4, dk=256, dv=256, block_size=64, q_dtype="bf16",
+            ctx=("list", [1, 65, 2500, 640]), seed=303),
+    wl.Case("d256_gqa8_fp16_bs32_split", batch=2, heads=16, kv_heads=2, dk=256, dv=256, block_size=32, q_dtype="fp16",
+            ctx=("list", [9000, 31]), seed=304),
+    wl.Case("gqa16_bf16_split", batch=3, heads=32, kv_heads=2, q_dtype="bf16", ctx=("list", [12000, 64, 300]), seed=305),
+    wl.Case("gqa15_fp16_long", batch=4, heads=30, kv_heads=2, q_dtype="fp16", ctx=("list", [88, 4000, 0, 1025]), seed=306),
+    wl.Case("gqa127_fp16_long", batch=3, heads=127, kv_heads=1, q_dtype="fp16", ctx=("list", [88, 2000, 130]), seed=307),
+    wl.Case("gqa12_int8_fp16", batch=3, heads=24, kv_heads=2, q_dtype="fp16", kv_dtype="int8", offsets=True,
+            ctx=("list", [300, 5000, 64]), seed=308),
+    wl.Case("gqa9_d64_bf16", batch=2, heads=18, kv_heads=2, dk=64, dv=64, q_dtype="bf16", ctx=("list", [513, 77]), seed=309),
+]
+
+
+@pytest.mark.parametrize("case", _WIDE_CASES, ids=lambda c: c.name)
+def test_head_sizes_and_large_groups_run_on_the_tiled_kernel(case):
+    h = wl.make_host_inputs(case)
+    out, info = run_gpu_case(case, h, out_fill=3.0)
+    assert info.kernel == capi.KERNEL_TMA_MMA
+    ref = oracle_out(case, h, out=wl.encode(np.full((case.batch, case.heads, case.dv), 3.0, dtype=np.float32), case.q_dtype))
+    assert max_abs_err(out, ref, case.q_dtype) <= tol_for(case)
+    # and the CUDA-core kernel agrees on the same inputs
+    out_g, info_g = run_gpu_case(case, h, kernel=capi.KERNEL_GENERIC, out_fill=3.0)
+    assert info_g.kernel == capi.KERNEL_GENERIC
+    assert max_abs_err(out_g, ref, case.q_dtype) <= tol_for(case)
