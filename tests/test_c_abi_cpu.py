@@ -610,7 +610,8 @@ def test_fused_parallel_decoding_plan_rules(monkeypatch):
     assert plan() == capi.KERNEL_TMA_MMA                                   # 2 tokens x 2 heads per kv head
     assert plan(heads=32, kvh=4, n=2) == capi.KERNEL_TMA_MMA               # 8 pairs
     _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, heads=48, kvh=4, n=3)     # 12 pairs
-    _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, dk=64)
+    assert plan(dk=64) == capi.KERNEL_TMA_MMA                              # head sizes 64 / 128 / 256
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, dk=96)
     _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, kv="int8")
     _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, kernel=capi.KERNEL_GENERIC)
     _expect(capi.ERROR_INVALID_PARAM, plan, heads=18, kvh=2, n=4)          # heads not a multiple of the token count
