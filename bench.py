@@ -350,9 +350,11 @@ def measure_decode(args, case, rt, steps, with_cpu_baseline):
         got = wl.torch_to_host(out, case.q_dtype)
         err = float(np.abs(wl.to_f32(got, case.q_dtype) - wl.to_f32(ref_local, case.q_dtype)).max()) if got.size else 0.0
     else:
-        ref_t = torch.from_numpy(ref_local.view(np.int16) if case.q_dtype == "bf16" else ref_local).to(dev)
-        ref_all = torch.empty((world,) + tuple(ref_t.shape), dtype=ref_t.dtype, device=dev)
-        dist.all_gather_into_tensor(ref_all.view(-1), ref_t.contiguous().view(-1))
+        # as raw bytes: NCCL moves uint8 whatever the element type
+        ref_t = torch.from_numpy(np.ascontiguousarray(ref_local).view(np.uint8).reshape(-1)).to(dev)
+        ref_all = torch.empty((world, ref_t.numel()), dtype=torch.uint8, device=dev)
+        dist.all_gather_into_tensor(ref_all.view(-1), ref_t)
+        ref_all = ref_all.view(d["q"].dtype).view(world, B, H_local, Dv)
         if p2p:
             mine = exchange.local_tensor(last_gathered[0], (case.batch, case.heads, Dv), d["q"].dtype)
         elif by_sequence:
@@ -363,7 +365,6 @@ def measure_decode(args, case, rt, steps, with_cpu_baseline):
             ref_full = ref_all.reshape(case.batch, case.heads, Dv)
         else:
             ref_full = ref_all.permute(1, 0, 2, 3).reshape(case.batch, case.heads, Dv)
-        ref_full = ref_full.view(d["q"].dtype) if ref_full.dtype != d["q"].dtype else ref_full
         e = (mine.float() - ref_full.float()).abs().max().reshape(1)
         dist.all_reduce(e, op=dist.ReduceOp.MAX)
         err = float(e[0])
