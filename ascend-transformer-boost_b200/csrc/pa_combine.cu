@@ -24,12 +24,29 @@ __global__ void __launch_bounds__(160) pa_combine_kernel(const PaArgs a)
     const int base = a.plan.seq_part_base[seq];
     const int n = a.plan.seq_nparts[seq];
     const float *lse = a.plan.part_lse + (int64_t)base * a.num_heads + h;
+    // Every load here is an L2 hit with ~1 us of latency and the kernel is nothing but such loads: they are issued in
+    // batches (all log-sum-exps of up to kRegParts ranges at once, then four partial rows at once), never one by one.
+    constexpr int kRegParts = 8;
+    float lr[kRegParts];
     float mx = -INFINITY;
-    for (int i = 0; i < n; ++i) {
+#pragma unroll
+    for (int i = 0; i < kRegParts; ++i) {
+        lr[i] = i < n ? lse[(int64_t)i * a.num_heads] : -INFINITY;
+    }
+#pragma unroll
+    for (int i = 0; i < kRegParts; ++i) {
+        mx = fmaxf(mx, lr[i]);
+    }
+    for (int i = kRegParts; i < n; ++i) {
         mx = fmaxf(mx, lse[(int64_t)i * a.num_heads]);
     }
     float sum = 0.f;
-    for (int i = 0; i < n; ++i) {
+#pragma unroll
+    for (int i = 0; i < kRegParts; ++i) {
+        lr[i] = exp2f(lr[i] - mx); // 0 for the ranges that do not exist
+        sum += lr[i];
+    }
+    for (int i = kRegParts; i < n; ++i) {
         sum += exp2f(lse[(int64_t)i * a.num_heads] - mx);
     }
     const float inv = 1.f / sum;
@@ -40,7 +57,13 @@ __global__ void __launch_bounds__(160) pa_combine_kernel(const PaArgs a)
     }
     const bool use_shared = n <= kMaxPartsShared;
     if (use_shared) {
-        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+#pragma unroll
+        for (int i = 0; i < kRegParts; ++i) {
+            if (threadIdx.x == 0 && i < n) {
+                w[i] = lr[i] * inv;
+            }
+        }
+        for (int i = kRegParts + threadIdx.x; i < n; i += blockDim.x) {
             w[i] = exp2f(lse[(int64_t)i * a.num_heads] - mx) * inv;
         }
         __syncthreads();
@@ -50,13 +73,24 @@ __global__ void __launch_bounds__(160) pa_combine_kernel(const PaArgs a)
     const int64_t stride = (int64_t)a.num_heads * a.dv;
     for (int d = threadIdx.x * 4; d < a.dv; d += blockDim.x * 4) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int i = 0; i < n; ++i) {
-            const float wi = use_shared ? w[i] : exp2f(lse[(int64_t)i * a.num_heads] - mx) * inv;
-            const float4 v = *reinterpret_cast<const float4 *>(po + i * stride + d);
-            acc.x = fmaf(wi, v.x, acc.x);
-            acc.y = fmaf(wi, v.y, acc.y);
-            acc.z = fmaf(wi, v.z, acc.z);
-            acc.w = fmaf(wi, v.w, acc.w);
+        for (int i0 = 0; i0 < n; i0 += 4) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                v[u] = *reinterpret_cast<const float4 *>(po + (int64_t)min(i0 + u, n - 1) * stride + d);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u;
+                float wi = 0.f;
+                if (i < n) {
+                    wi = use_shared ? w[i] : exp2f(lse[(int64_t)i * a.num_heads] - mx) * inv;
+                }
+                acc.x = fmaf(wi, v[u].x, acc.x);
+                acc.y = fmaf(wi, v[u].y, acc.y);
+                acc.z = fmaf(wi, v[u].z, acc.z);
+                acc.w = fmaf(wi, v[u].w, acc.w);
+            }
         }
         uint2 pk;
         pk.x = Elem<TQ>::pack2(acc.x, acc.y);
