@@ -138,7 +138,7 @@ int atb_b200_pa_plan_get_info(const atb_b200_pa_plan *plan, atb_b200_pa_plan_inf
     }
     const HostPlan &h = plan->hp;
     info->kernel = h.kernel;
-    info->num_ctas = h.n_cta_groups * h.cols;
+    info->num_ctas = h.n_cta_groups * h.cols * (h.mla_split ? 2 : 1);
     info->num_items = (int32_t)h.items.size();
     info->num_partials = h.n_partials;
     info->num_combine_seqs = (int32_t)h.combine_seqs.size();
@@ -538,7 +538,7 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
             : d.kv_dtype == kInt8 ? launch_pa_tma_mma_i8(a, d.q_dtype, d.num_blocks, stream)
                                   : launch_pa_tma_mma(a, d.q_dtype, d.kv_dtype, d.num_blocks, stream);
     } else if (h.kernel == ATB_B200_KERNEL_MLA_TC5) {
-        e = launch_pa_mla_tc5(a, d.q_dtype, d.num_blocks, stream);
+        e = h.mla_split ? launch_pa_mla_split(a, d.num_blocks, stream) : launch_pa_mla_tc5(a, d.q_dtype, d.num_blocks, stream);
     } else {
         e = launch_pa_generic(a, d.q_dtype, d.kv_dtype, stream);
     }

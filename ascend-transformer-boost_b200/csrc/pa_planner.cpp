@@ -130,6 +130,7 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
     p->desc = d;
     p->kernel = kernel;
     p->sm_count = sm_count;
+    p->mla_split = false;
     if (kernel == ATB_B200_KERNEL_TMA_MMA) {
         p->heads_per_cta = 8;
         p->chunks_per_kvh = (group + 7) / 8; // more than 8 heads per kv head: several columns over the same K/V tiles
@@ -138,6 +139,12 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
         p->heads_per_cta = 64;
         p->chunks_per_kvh = (group + 63) / 64;
         p->ctas_per_sm = 1;
+        // bf16 without a mask, the causal rule or fused query tokens: CTA pairs that split the dims
+        const char *env = std::getenv("ATB_B200_MLA_SPLIT");
+        p->mla_split = (env != nullptr && env[0] == '1') && d.q_per_seq <= 1 &&
+                       (d.score_mods & (ATB_B200_SCORE_MASK | ATB_B200_SCORE_CAUSAL)) == 0 &&
+                       pa_mla_split_supported(d.head_dim_k, d.head_dim_v, d.v_row_dim, d.rope_dim, d.block_size, d.kv_heads,
+                                              d.q_dtype, d.kv_dtype);
     } else {
         p->heads_per_cta = pa_generic_heads_per_cta(d.head_dim_k, d.head_dim_v);
         p->chunks_per_kvh = (group + p->heads_per_cta - 1) / p->heads_per_cta;
@@ -158,7 +165,7 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
     }
     p->max_context = longest;
     const int slots = sm_count * p->ctas_per_sm;
-    int64_t n_groups = std::max<int64_t>(1, slots / p->cols);
+    int64_t n_groups = std::max<int64_t>(1, slots / (p->cols * (p->mla_split ? 2 : 1)));
     if (n_groups < 4) {
         n_groups = 4; // many columns: still cut long sequences a little for balance
     }
