@@ -74,6 +74,9 @@ int atb_b200_pa_plan_create(const atb_b200_pa_desc *desc, const int32_t *context
     if (p == nullptr) {
         return kErrOutOfHostMemory;
     }
+    if (desc->sm_count <= 0 && desc->head_dim_k == 576) {
+        p->hp.cta_pairs = pa_mla_split_max_pairs(); // planned for the current device: how many CTA pairs it can hold
+    }
     int rc;
     try {
         rc = plan_paged_attention(*desc, context_lens_host, sm, &p->hp);

@@ -552,6 +552,40 @@ bool pa_mla_split_supported(int dk, int dv, int v_row_dim, int rope_dim, int blo
            block_size <= 256 && q_dtype == kBf16 && kv_dtype == kBf16;
 }
 
+// CTA pairs that can be resident at once on the current device (pairs are placed within a GPC, so this may be less
+// than SMs / 2); 0 if the query fails.  Cached per device.
+int pa_mla_split_max_pairs()
+{
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        return 0;
+    }
+    if (cached[dev] == 0) {
+        if (cudaFuncSetAttribute(pa_mla_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
+            return 0;
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * 148);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = kSmemBytes;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, pa_mla_split_kernel, &cfg) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            return 0;
+        }
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 cudaError_t launch_pa_mla_split(const PaArgs &args, int num_blocks, cudaStream_t stream)
 {
     TmaEncodeFn fn = tma_encode_fn();

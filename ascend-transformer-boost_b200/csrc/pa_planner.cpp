@@ -165,7 +165,12 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
     }
     p->max_context = longest;
     const int slots = sm_count * p->ctas_per_sm;
-    int64_t n_groups = std::max<int64_t>(1, slots / (p->cols * (p->mla_split ? 2 : 1)));
+    int64_t n_groups = std::max<int64_t>(1, slots / p->cols);
+    if (p->mla_split) {
+        // one CTA pair per (group, column), all pairs resident at once
+        const int pairs = p->cta_pairs > 0 ? p->cta_pairs : sm_count / 2;
+        n_groups = std::max<int64_t>(1, pairs / p->cols);
+    }
     if (n_groups < 4) {
         n_groups = 4; // many columns: still cut long sequences a little for balance
     }

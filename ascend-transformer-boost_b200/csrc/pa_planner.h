@@ -17,6 +17,7 @@ struct HostPlan {
     int chunks_per_kvh = 1;
     int ctas_per_sm = 2;
     int sm_count = 148;
+    int cta_pairs = 0;     // CTA pairs of the split MLA kernel resident at once (0: assume sm_count / 2)
     int n_cta_groups = 0;
     int n_partials = 0;
     int64_t max_context = 0; // longest context of the planned batch (tokens)
@@ -45,6 +46,7 @@ struct HostPlan {
 };
 
 // Returns 0 or an atb::ErrorType value.  `sm_count` must be > 0.
+// `plan->cta_pairs`, when set beforehand, bounds the grid of the split MLA kernel.
 int plan_paged_attention(const atb_b200_pa_desc &desc, const int32_t *context_lens, int sm_count, HostPlan *plan);
 
 } // namespace atb_b200
