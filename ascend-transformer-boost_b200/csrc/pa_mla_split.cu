@@ -63,6 +63,7 @@ struct Small {
     uint64_t bars[24];
     uint32_t tmem_slot;
     int abort_flag;
+    int v_clean;               // rank 1: warps that have cleared the stale V rows, 4 per tile, counted over the kernel
     float mref[2][kHeads];     // reference score per head, log2 domain (double-buffered over ranges)
     float wsum[2][4][kHeads];  // per-warp row sums of a range (double-buffered over ranges)
     float linv[2][kHeads];     // 1 / row sum (both ranks), double-buffered over ranges
@@ -107,7 +108,11 @@ pa_mla_split_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
             mbar_init(&bars[kSFull0 + s], 1);
             mbar_init(&bars[kSEmpty0 + s], 4);
         }
-        mbar_init(&bars[kPFull], rank == 0 ? 4 : 8); // rank 1: its own four warps (V rows cleared) + rank 0's four (P^T written)
+        // P^T of a tile is written by rank 0's four warps (into both CTAs).  Rank 1's own warps report their cleared V rows
+        // on a plain counter (v_clean): they run up to two tiles ahead of the P.V that needs them, which the parity of an
+        // mbarrier cannot express
+        mbar_init(&bars[kPFull], 4);
+        sm->v_clean = 0;
         mbar_init(&bars[kPvDone], 1);
         mbar_init(&bars[kPvDonePeer], 1);
         mbar_init(&bars[kRecvFull], 4);
@@ -240,6 +245,7 @@ pa_mla_split_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
                 while (next_pv < n_tiles) {
                     const uint32_t gp = g + next_pv, gq = g + next_qk;
                     if (next_pv < next_qk && mbar_test_wait_cluster(&bars[kPFull], gp & 1) &&
+                        (rank == 0 || *reinterpret_cast<volatile int *>(&sm->v_clean) >= 4 * (int)(gp + 1)) &&
                         (o_free || next_pv > 0 || ready(kOFree, (i & 1) ^ 1u))) {
                         // the first P.V of a range overwrites O^T: the previous range's read-out must be over
                         o_free = true;
@@ -362,7 +368,8 @@ pa_mla_split_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
                     __syncwarp();
                     if (lane == 0) {
                         mbar_arrive_cluster(peer_bar(kRecvFull));
-                        mbar_arrive(&bars[kPFull]);          // this warp's V rows are clean
+                        __threadfence_block();
+                        atomicAdd(&sm->v_clean, 1);          // this warp's V rows of tile g are clean
                     }
                     // relay "P.V of the previous tile has completed here" so that rank 0 may overwrite P^T
                     if (warp == 0 && g > 0) {
