@@ -45,7 +45,9 @@ constexpr int kQAtomBytes = kHeads * 128;      // 64 heads x 64 dims: 8 KB
 constexpr int kMaxAtoms = 5;
 constexpr int kStages = 2;
 constexpr int kPBytes = kTile * 128;           // P^T: 128 tokens x 64 heads, bf16
-constexpr int kRecvBytes = kTile * kHeads * 4; // rank 0: the peer's partial S^T, [head][token] fp32
+constexpr int kRecvStride = kHeads + 4;        // floats per token row of the receive buffer: 272 B, so that the 16-byte
+                                               // accesses of a quarter warp (8 rows) fall into 8 different bank groups
+constexpr int kRecvBytes = kTile * kRecvStride * 4; // rank 0: the peer's partial S^T, [token][head] fp32
 constexpr int kBigBytes = kMaxAtoms * kQAtomBytes + kStages * kMaxAtoms * kAtomBytes + kPBytes; // 216 KB (rank 1)
 static_assert(4 * kQAtomBytes + kStages * 4 * kAtomBytes + kPBytes + kRecvBytes <= kBigBytes, "rank 0 fits the same area");
 constexpr int kSmallBytes = 4096;              // barriers, tmem slot, flags, reference scores, row-sum scratch
@@ -56,21 +58,26 @@ constexpr float kMaxExponent = 100.f;
 
 enum Bar {
     kQFull = 0, kQEmpty, kStFull0, kStFull1, kStEmpty0, kStEmpty1, kSFull0, kSFull1, kSEmpty0, kSEmpty1,
-    kPFull, kPvDone, kPvDonePeer, kRecvFull, kRecvEmpty, kMref, kWsum, kLinv, kOFree, kNumBars
+    kPFull, kPvDone, kPHalf0, kPHalf1, kPHalfPeer0, kPHalfPeer1, kRecvFull0, kRecvFull1, kRecvFull2, kRecvFull3,
+    kRecvEmpty0, kRecvEmpty1, kRecvEmpty2, kRecvEmpty3, kMref, kWsum, kLinv, kOFree, kNumBars
 };
 
 struct Small {
-    uint64_t bars[24];
+    uint64_t bars[32];
     uint32_t tmem_slot;
     int abort_flag;
     int v_clean;               // rank 1: warps that have cleared the stale V rows, 4 per tile, counted over the kernel
-    float mref[2][kHeads];     // reference score per head, log2 domain (double-buffered over ranges)
+    alignas(16) float mref[2][kHeads]; // (read 16 bytes at a time) reference score per head, log2 domain (double-buffered over ranges)
     float wsum[2][4][kHeads];  // per-warp row sums of a range (double-buffered over ranges)
     float linv[2][kHeads];     // 1 / row sum (both ranks), double-buffered over ranges
     float lfull[2][kHeads];    // row sum (rank 0), for the log-sum-exp
 };
 static_assert(sizeof(Small) <= kSmallBytes, "small shared-memory area");
 
+// kTrace: the build with the timing probe (atb_b200_pa_plan_set_trace with CTA selector 255): every CTA stores the
+// global timer at its start and end in trace[1 + 2b], trace[2 + 2b], and 16 cycle counters of its issuing thread and of
+// thread 0 from trace[2 + 2 * grid + 16b] on.  The product build carries none of it.
+template <bool kTrace>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 pa_mla_split_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap rmap,
                     const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap qrmap, const PaArgs a)
@@ -114,9 +121,14 @@ pa_mla_split_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
         mbar_init(&bars[kPFull], 4);
         sm->v_clean = 0;
         mbar_init(&bars[kPvDone], 1);
-        mbar_init(&bars[kPvDonePeer], 1);
-        mbar_init(&bars[kRecvFull], 4);
-        mbar_init(&bars[kRecvEmpty], 4);
+        for (int k = 0; k < 2; ++k) {
+            mbar_init(&bars[kPHalf0 + k], 1);     // P.V has consumed tokens 64k..64k+63 of P^T (this CTA)
+            mbar_init(&bars[kPHalfPeer0 + k], 1); // the same on the peer, relayed
+        }
+        for (int w = 0; w < 4; ++w) {
+            mbar_init(&bars[kRecvFull0 + w], 1);  // rank 0: warp w of rank 1 has sent its 32 token rows
+            mbar_init(&bars[kRecvEmpty0 + w], 1); // rank 1: warp w of rank 0 has read them
+        }
         mbar_init(&bars[kMref], 1);
         mbar_init(&bars[kWsum], 4);
         mbar_init(&bars[kLinv], 2);
@@ -136,6 +148,15 @@ pa_mla_split_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const uint32_t tmem_base = sm->tmem_slot;
+    const bool tracing = kTrace && a.trace != nullptr && (a.trace_cap >> 24) == 255u &&
+                         2 + 18 * gridDim.x <= (a.trace_cap & 0xffffffu);
+    unsigned long long t_start = 0;
+    if (tracing && threadIdx.x == 0) {
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_start));
+    }
+    unsigned long long *acct = tracing ? a.trace + 2 + 2 * gridDim.x + 16 * blockIdx.x : nullptr;
+    long long acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    auto tick = [&]() -> long long { return kTrace ? clock64() : 0; };
     const int item_begin = a.plan.group_begin[grp], item_end = a.plan.group_begin[grp + 1];
 
     // bounded waits; `cluster` = the barrier is arrived on by the peer CTA
@@ -249,26 +270,35 @@ pa_mla_split_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
                         (o_free || next_pv > 0 || ready(kOFree, (i & 1) ^ 1u))) {
                         // the first P.V of a range overwrites O^T: the previous range's read-out must be over
                         o_free = true;
+                        const long long t0 = tick();
                         tc_fence_after();
                         fence_proxy_async_all(); // P^T was written by ordinary stores (on rank 1: by the peer CTA's)
                         const uint32_t vb = st_addr + (gp & 1) * n_atoms * kAtomBytes;
                         const uint64_t dp0 = smem_desc(p_addr, kAtomBytes, 1024);
+                        // tokens 0..63 first, then 64..127: each half of P^T is handed back to the softmax warps as soon as
+                        // its MMAs have completed
 #pragma unroll
-                        for (int mb = 0; mb < 2; ++mb) {
-                            // V^T rows of 128 dims = two atoms kAtomBytes apart; 8-token groups 1024 B apart
-                            const uint64_t dv0 = smem_desc(vb + 2 * mb * kAtomBytes, kAtomBytes, 1024);
+                        for (int half = 0; half < 2; ++half) {
 #pragma unroll
-                            for (int ks = 0; ks < kTile / 16; ++ks) {
-                                tc_mma(tmem_base + 128 + mb * 64, dv0 + ((ks * 2048) >> 4), dp0 + ((ks * 2048) >> 4), idesc_pv,
-                                       next_pv != 0 || ks != 0);
+                            for (int mb = 0; mb < 2; ++mb) {
+                                // V^T rows of 128 dims = two atoms kAtomBytes apart; 8-token groups 1024 B apart
+                                const uint64_t dv0 = smem_desc(vb + 2 * mb * kAtomBytes, kAtomBytes, 1024);
+#pragma unroll
+                                for (int ks = 4 * half; ks < 4 * half + 4; ++ks) {
+                                    tc_mma(tmem_base + 128 + mb * 64, dv0 + ((ks * 2048) >> 4), dp0 + ((ks * 2048) >> 4), idesc_pv,
+                                           next_pv != 0 || ks != 0);
+                                }
                             }
+                            tc_commit(&bars[kPHalf0 + half]);
                         }
                         tc_commit(&bars[kStEmpty0 + (gp & 1)]);
                         tc_commit(&bars[kPvDone]);
                         ++next_pv;
                         idle = 0;
+                        acc[1] += tick() - t0;
                     } else if (next_qk < n_tiles && next_qk < next_pv + 2 &&
                                ready(kStFull0 + (gq & 1), (gq >> 1) & 1) && ready(kSEmpty0 + (gq & 1), ((gq >> 1) & 1) ^ 1u)) {
+                        const long long t0 = tick();
                         tc_fence_after();
                         const uint32_t kb = st_addr + (gq & 1) * n_atoms * kAtomBytes;
                         const uint32_t ds = tmem_base + (gq & 1) * 64;
@@ -286,7 +316,18 @@ pa_mla_split_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
                         }
                         ++next_qk;
                         idle = 0;
+                        acc[0] += tick() - t0;
                     } else {
+                        if (kTrace) {
+                            // why nothing could be issued: 3 look-ahead exhausted (P^T missing), 4 K tile missing, 5 S^T buffer busy
+                            if (!(next_qk < n_tiles && next_qk < next_pv + 2)) {
+                                acc[3]++;
+                            } else if (!ready(kStFull0 + (gq & 1), (gq >> 1) & 1)) {
+                                acc[4]++;
+                            } else {
+                                acc[5]++;
+                            }
+                        }
                         ++idle;
                         if (idle > (1u << 22) || *abort_flag) {
                             *abort_flag = 1;
@@ -297,6 +338,11 @@ pa_mla_split_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
                     }
                 }
                 g += n_tiles;
+            }
+            if (tracing) {
+                for (int k = 0; k < 8; ++k) {
+                    acct[k] = (unsigned long long)acc[k];
+                }
             }
         }
     } else {
@@ -318,10 +364,13 @@ pa_mla_split_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
             for (int t = 0; t < n_tiles && alive; ++t, ++g) {
                 const int sb = g & 1;
                 const int valid = min(kTile, item.tok_end - (item.tok_begin + t * kTile));
+                long long t0 = tick();
                 if (!wait(kSFull0 + sb, (g >> 1) & 1, false)) {
                     alive = false;
                     break;
                 }
+                acc[0] += tick() - t0;
+                t0 = tick();
                 tc_fence_after();
                 uint32_t sv[kHeads];
 #pragma unroll
@@ -353,56 +402,75 @@ pa_mla_split_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
                     }
                     fence_proxy_async();
                 }
+                const int half = warp >> 1;                       // which 64 tokens of the tile this warp owns
                 if (rank == 1) {
-                    // ---- forward the partial scores to rank 0: recv[head][token], one row of 32 tokens per store
-                    if (!wait(kRecvEmpty, (g & 1) ^ 1u, true)) {
+                    // ---- forward the partial scores to rank 0: recv[token][head], the thread's own row, 16 bytes per store
+                    acc[2] += tick() - t0;
+                    t0 = tick();
+                    if (!wait(kRecvEmpty0 + warp, (g & 1) ^ 1u, true)) {
                         alive = false;
                         break;
                     }
+                    acc[1] += tick() - t0;
+                    t0 = tick();
                     // rank 0 keeps 4 atoms, so its receive buffer lies at another offset than this CTA's layout suggests
-                    const uint32_t dst = map_to_cta(smem_u32(base + 4 * kQAtomBytes + kStages * 4 * kAtomBytes + kPBytes), 0) + tok_l * 4;
+                    const uint32_t dst = map_to_cta(smem_u32(base + 4 * kQAtomBytes + kStages * 4 * kAtomBytes + kPBytes), 0) +
+                                         tok_l * (kRecvStride * 4);
 #pragma unroll
-                    for (int h = 0; h < kHeads; ++h) {
-                        st_cluster_f32(dst + h * kTile * 4, __uint_as_float(sv[h]));
+                    for (int c = 0; c < kHeads / 4; ++c) {
+                        st_cluster_v4(dst + c * 16, sv[4 * c], sv[4 * c + 1], sv[4 * c + 2], sv[4 * c + 3]);
                     }
                     __syncwarp();
                     if (lane == 0) {
-                        mbar_arrive_cluster(peer_bar(kRecvFull));
+                        mbar_arrive_cluster(peer_bar(kRecvFull0 + warp));
                         __threadfence_block();
                         atomicAdd(&sm->v_clean, 1);          // this warp's V rows of tile g are clean
                     }
-                    // relay "P.V of the previous tile has completed here" so that rank 0 may overwrite P^T
-                    if (warp == 0 && g > 0) {
-                        if (!wait(kPvDone, (g - 1) & 1, false)) {
+                    acc[4] += tick() - t0;
+                    t0 = tick();
+                    // relay "P.V of the previous tile has consumed this half of P^T here" so that rank 0 may overwrite it
+                    if ((warp & 1) == 0 && g > 0) {
+                        if (!wait(kPHalf0 + half, (g - 1) & 1, false)) {
                             alive = false;
                             break;
                         }
                         if (lane == 0) {
-                            mbar_arrive_cluster(peer_bar(kPvDonePeer));
+                            mbar_arrive_cluster(peer_bar(kPHalfPeer0 + half));
                         }
                     }
+                    acc[3] += tick() - t0;
                     continue;
                 }
                 // ---- rank 0: add the peer's partial, scale, reference, exponentials
-                if (!wait(kRecvFull, g & 1, true)) {
+                acc[2] += tick() - t0;
+                t0 = tick();
+                if (!wait(kRecvFull0 + warp, g & 1, true)) {
                     alive = false;
                     break;
                 }
-                float v[kHeads];
+                acc[1] += tick() - t0;
+                t0 = tick();
+                {
+                    const float4 *row = reinterpret_cast<const float4 *>(recv + tok_l * kRecvStride);
 #pragma unroll
-                for (int h = 0; h < kHeads; ++h) {
-                    v[h] = (__uint_as_float(sv[h]) + recv[h * kTile + tok_l]) * a.scale_log2;
+                    for (int c = 0; c < kHeads / 4; ++c) {
+                        const float4 r = row[c];
+                        sv[4 * c] = __float_as_uint(__uint_as_float(sv[4 * c]) + r.x);
+                        sv[4 * c + 1] = __float_as_uint(__uint_as_float(sv[4 * c + 1]) + r.y);
+                        sv[4 * c + 2] = __float_as_uint(__uint_as_float(sv[4 * c + 2]) + r.z);
+                        sv[4 * c + 3] = __float_as_uint(__uint_as_float(sv[4 * c + 3]) + r.w);
+                    }
                 }
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive_cluster(peer_bar(kRecvEmpty));
+                    mbar_arrive_cluster(peer_bar(kRecvEmpty0 + warp));
                 }
                 float *mref = sm->mref[i & 1];
                 if (t == 0) {
                     if (threadIdx.x == 0) {
 #pragma unroll
                         for (int h = 0; h < kHeads; ++h) {
-                            mref[h] = v[h];
+                            mref[h] = __uint_as_float(sv[h]) * a.scale_log2;
                         }
                         mbar_arrive(&bars[kMref]);
                     }
@@ -414,18 +482,28 @@ pa_mla_split_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
                 const bool live = tok_l < valid;
                 uint32_t pk[kHeads / 2];
 #pragma unroll
-                for (int h = 0; h < kHeads; h += 2) {
-                    const float p0 = live ? fast_exp2(fminf(v[h] - mref[h], kMaxExponent)) : 0.f;
-                    const float p1 = live ? fast_exp2(fminf(v[h + 1] - mref[h + 1], kMaxExponent)) : 0.f;
-                    lsum[h] += p0;
-                    lsum[h + 1] += p1;
-                    pk[h >> 1] = Elem<T>::pack2(p0, p1);
+                for (int c = 0; c < kHeads / 4; ++c) {
+                    const float4 m = reinterpret_cast<const float4 *>(mref)[c];
+                    const float p0 = live ? fast_exp2(fminf(fmaf(__uint_as_float(sv[4 * c]), a.scale_log2, -m.x), kMaxExponent)) : 0.f;
+                    const float p1 = live ? fast_exp2(fminf(fmaf(__uint_as_float(sv[4 * c + 1]), a.scale_log2, -m.y), kMaxExponent)) : 0.f;
+                    const float p2 = live ? fast_exp2(fminf(fmaf(__uint_as_float(sv[4 * c + 2]), a.scale_log2, -m.z), kMaxExponent)) : 0.f;
+                    const float p3 = live ? fast_exp2(fminf(fmaf(__uint_as_float(sv[4 * c + 3]), a.scale_log2, -m.w), kMaxExponent)) : 0.f;
+                    lsum[4 * c] += p0;
+                    lsum[4 * c + 1] += p1;
+                    lsum[4 * c + 2] += p2;
+                    lsum[4 * c + 3] += p3;
+                    pk[2 * c] = Elem<T>::pack2(p0, p1);
+                    pk[2 * c + 1] = Elem<T>::pack2(p2, p3);
                 }
-                // P^T(g) overwrites P^T(g-1): both CTAs' P.V(g-1) must have completed
-                if (g > 0 && (!wait(kPvDone, (g - 1) & 1, false) || !wait(kPvDonePeer, (g - 1) & 1, true))) {
+                // this half of P^T(g) overwrites that of P^T(g-1): both CTAs' P.V(g-1) must have consumed it
+                acc[2] += tick() - t0;
+                t0 = tick();
+                if (g > 0 && (!wait(kPHalf0 + half, (g - 1) & 1, false) || !wait(kPHalfPeer0 + half, (g - 1) & 1, true))) {
                     alive = false;
                     break;
                 }
+                acc[3] += tick() - t0;
+                t0 = tick();
                 {
                     // row of P^T: 64 heads = 8 chunks of 16 B, 128-byte swizzle; the same row into the peer's buffer
                     uint8_t *prow = p_smem + tok_l * 128;
@@ -445,11 +523,14 @@ pa_mla_split_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
                     mbar_arrive(&bars[kPFull]);
                     mbar_arrive_cluster(peer_bar(kPFull));
                 }
+                acc[4] += tick() - t0;
+                acc[6]++;
             }
             if (!alive) {
                 break;
             }
             // ---- end of the token range: row sums -> 1 / l for both CTAs, then O^T / l -> output row or partial
+            const long long t_ep = tick();
             float *linv = sm->linv[i & 1];
             if (rank == 0) {
 #pragma unroll
@@ -536,11 +617,24 @@ pa_mla_split_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
             if (lane == 0) {
                 mbar_arrive(&bars[kOFree]);
             }
+            acc[5] += tick() - t_ep;
+            acc[7]++;
+        }
+        if (tracing && threadIdx.x == 0) {
+            for (int k = 0; k < 8; ++k) {
+                acct[8 + k] = (unsigned long long)acc[k];
+            }
         }
     }
 
     tc_fence_before();
     __syncthreads();
+    if (tracing && threadIdx.x == 0) {
+        unsigned long long t_end;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_end));
+        a.trace[1 + 2 * blockIdx.x] = t_start;
+        a.trace[2 + 2 * blockIdx.x] = t_end;
+    }
     if (warp == 5) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
@@ -569,7 +663,7 @@ int pa_mla_split_max_pairs()
         return 0;
     }
     if (cached[dev] == 0) {
-        if (cudaFuncSetAttribute(pa_mla_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
+        if (cudaFuncSetAttribute(pa_mla_split_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
             return 0;
         }
         cudaLaunchConfig_t cfg = {};
@@ -584,7 +678,7 @@ int pa_mla_split_max_pairs()
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, pa_mla_split_kernel, &cfg) != cudaSuccess || n <= 0) {
+        if (cudaOccupancyMaxActiveClusters(&n, pa_mla_split_kernel<false>, &cfg) != cudaSuccess || n <= 0) {
             cudaGetLastError();
             return 0;
         }
@@ -628,11 +722,14 @@ cudaError_t launch_pa_mla_split(const PaArgs &args, int num_blocks, cudaStream_t
         !encode_q(&qrm, split ? args.q_rope : args.q, split ? kDk - kDv : kDk)) {
         return cudaErrorInvalidValue;
     }
-    static bool configured[64] = {};
+    const bool traced = args.trace != nullptr;
+    auto kern = traced ? pa_mla_split_kernel<true> : pa_mla_split_kernel<false>;
+    static bool configured_all[2][64] = {};
+    bool *configured = configured_all[traced ? 1 : 0];
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(pa_mla_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) {
             return e;
         }
@@ -650,7 +747,7 @@ cudaError_t launch_pa_mla_split(const PaArgs &args, int num_blocks, cudaStream_t
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, pa_mla_split_kernel, km, rm, qm, qrm, args);
+    return cudaLaunchKernelEx(&cfg, kern, km, rm, qm, qrm, args);
 }
 
 } // namespace atb_b200
