@@ -145,6 +145,12 @@ __device__ __forceinline__ void tma_load_4d(void *smem_dst, const void *tmap, ui
                  "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
                  : "memory");
 }
+// The same tile into L2 only (no shared-memory destination, nothing to wait for).
+__device__ __forceinline__ void tma_prefetch_4d(const void *tmap, int c0, int c1, int c2, int c3)
+{
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const void *tmap)
 {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");

@@ -26,6 +26,14 @@ __device__ __forceinline__ void tc_commit(uint64_t *bar)
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
 }
+// The same, arriving on the barrier at this shared-memory offset in BOTH CTAs of a cluster of two.
+__device__ __forceinline__ void tc_commit_pair(uint64_t *bar)
+{
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)),
+                 "h"(mask)
+                 : "memory");
+}
 __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate)
 {
     asm volatile("{\n\t.reg .pred p;\n\t"
@@ -90,6 +98,18 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
     return d;
 }
 
+// The same with the 64-byte swizzle (rows of 64 bytes, 8-row groups 512 B apart).
+__device__ __forceinline__ uint64_t smem_desc_sw64(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3fffu);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
+    d |= (uint64_t)1 << 46; // descriptor version of this architecture
+    d |= (uint64_t)4 << 61; // SWIZZLE_64B
+    return d;
+}
+
 // Instruction descriptor of kind::f16: fp32 accumulate, A/B format (0 fp16, 1 bf16), majors, N, M.
 __host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t b_mn_major, uint32_t n, uint32_t m)
 {
@@ -140,6 +160,19 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint32_t a,
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
 {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// The same without ordering: for a signal that publishes no data of the arriving thread.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// 16-byte store into a CTA of the cluster that counts its bytes on an mbarrier of the SAME CTA when it has landed
+// (complete_tx): the receiver expects the bytes and waits; the sender neither fences nor arrives.
+__device__ __forceinline__ void st_async_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t cluster_mbar)
+{
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(cluster_addr),
+                 "r"(a), "r"(b), "r"(c), "r"(d), "r"(cluster_mbar)
+                 : "memory");
 }
 // try_wait on an own mbarrier that a peer CTA may arrive on (acquire at cluster scope).
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity)
