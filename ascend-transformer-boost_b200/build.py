@@ -9,7 +9,7 @@ CSRC = os.path.join(PKG, "csrc")
 OUT = os.path.join(PKG, "libatb_b200.so")
 
 CU_SOURCES = ["reshape_and_cache.cu", "pa_generic.cu", "pa_combine.cu", "pa_tma_mma.cu", "atb_scale_convert.cu",
-              "pa_noalloc.cu", "pa_tma_mma_i8.cu", "pa_mla_tc5.cu", "pa_mla_split.cu", "pa_exchange.cu", "cache_ops.cu", "norm_rope_cache.cu"]
+              "pa_noalloc.cu", "pa_tma_mma_i8.cu", "pa_mla_tc5.cu", "pa_mla_pair.cu", "pa_exchange.cu", "cache_ops.cu", "norm_rope_cache.cu"]
 CPP_SOURCES = ["tma_encode.cpp", "pa_planner.cpp", "c_api.cpp", "atb_operation_base.cpp", "atb_paged_attention.cpp",
                "atb_reshape_and_cache.cpp", "atb_c_wrappers.cpp", "atb_cache_ops.cpp", "atb_mla.cpp"]
 

@@ -75,7 +75,7 @@ int atb_b200_pa_plan_create(const atb_b200_pa_desc *desc, const int32_t *context
         return kErrOutOfHostMemory;
     }
     if (desc->sm_count <= 0 && desc->head_dim_k == 576) {
-        p->hp.cta_pairs = pa_mla_split_max_pairs(); // planned for the current device: how many CTA pairs it can hold
+        p->hp.cta_pairs = pa_mla_pair_max_pairs(); // planned for the current device: how many CTA pairs it can hold
     }
     int rc;
     try {
@@ -141,7 +141,7 @@ int atb_b200_pa_plan_get_info(const atb_b200_pa_plan *plan, atb_b200_pa_plan_inf
     }
     const HostPlan &h = plan->hp;
     info->kernel = h.kernel;
-    info->num_ctas = h.n_cta_groups * h.cols * (h.mla_split ? 2 : 1);
+    info->num_ctas = h.n_cta_groups * h.cols * (h.mla_pair ? 2 : 1);
     info->num_items = (int32_t)h.items.size();
     info->num_partials = h.n_partials;
     info->num_combine_seqs = (int32_t)h.combine_seqs.size();
@@ -541,7 +541,7 @@ static int pa_launch_impl(atb_b200_pa_plan *plan, const atb_b200_pa_tensors *t, 
             : d.kv_dtype == kInt8 ? launch_pa_tma_mma_i8(a, d.q_dtype, d.num_blocks, stream)
                                   : launch_pa_tma_mma(a, d.q_dtype, d.kv_dtype, d.num_blocks, stream);
     } else if (h.kernel == ATB_B200_KERNEL_MLA_TC5) {
-        e = h.mla_split ? launch_pa_mla_split(a, d.num_blocks, stream) : launch_pa_mla_tc5(a, d.q_dtype, d.num_blocks, stream);
+        e = h.mla_pair ? launch_pa_mla_pair(a, d.num_blocks, stream) : launch_pa_mla_tc5(a, d.q_dtype, d.num_blocks, stream);
     } else {
         e = launch_pa_generic(a, d.q_dtype, d.kv_dtype, stream);
     }

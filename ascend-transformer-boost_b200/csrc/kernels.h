@@ -35,12 +35,11 @@ bool pa_mla_tc5_supported(int dk, int dv, int v_row_dim, int rope_dim, int block
                           int kv_dtype);
 cudaError_t launch_pa_mla_tc5(const PaArgs &args, int q_dtype, int num_blocks, cudaStream_t stream);
 
-// The same cache as a cluster of two CTAs per 64 heads that split the 576 dims (bf16, no mask): both contractions with
-// the tokens in M; the grid is 2 x n_cta_groups x cols CTAs.
-bool pa_mla_split_supported(int dk, int dv, int v_row_dim, int rope_dim, int block_size, int kv_heads, int q_dtype,
-                            int kv_dtype);
-cudaError_t launch_pa_mla_split(const PaArgs &args, int num_blocks, cudaStream_t stream);
-int pa_mla_split_max_pairs(); // CTA pairs resident at once on the current device (0: unknown)
+// The same cache as a cluster of two CTAs per 128 heads that split the 576 dims (bf16, no mask): heads in M, Q and P in
+// tensor memory; the grid is 2 x n_cta_groups x cols CTAs.
+bool pa_mla_pair_supported(int dk, int dv, int v_row_dim, int rope_dim, int block_size, int kv_heads, int q_dtype, int kv_dtype);
+cudaError_t launch_pa_mla_pair(const PaArgs &args, int num_blocks, cudaStream_t stream);
+int pa_mla_pair_max_pairs(); // CTA pairs resident at once on the current device (0: unknown)
 
 // Merges the split-KV partials of every split sequence into the output.
 cudaError_t launch_pa_combine(const PaArgs &args, int n_combine_seqs, int q_dtype, cudaStream_t stream);

@@ -130,7 +130,7 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
     p->desc = d;
     p->kernel = kernel;
     p->sm_count = sm_count;
-    p->mla_split = false;
+    p->mla_pair = false;
     if (kernel == ATB_B200_KERNEL_TMA_MMA) {
         p->heads_per_cta = 8;
         p->chunks_per_kvh = (group + 7) / 8; // more than 8 heads per kv head: several columns over the same K/V tiles
@@ -139,12 +139,15 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
         p->heads_per_cta = 64;
         p->chunks_per_kvh = (group + 63) / 64;
         p->ctas_per_sm = 1;
-        // bf16 without a mask, the causal rule or fused query tokens: CTA pairs that split the dims
-        const char *env = std::getenv("ATB_B200_MLA_SPLIT");
-        p->mla_split = (env != nullptr && env[0] == '1') && d.q_per_seq <= 1 &&
-                       (d.score_mods & (ATB_B200_SCORE_MASK | ATB_B200_SCORE_CAUSAL)) == 0 &&
-                       pa_mla_split_supported(d.head_dim_k, d.head_dim_v, d.v_row_dim, d.rope_dim, d.block_size, d.kv_heads,
-                                              d.q_dtype, d.kv_dtype);
+        // opt-in (ATB_B200_MLA_PAIR=1), bf16 without a mask, the causal rule or fused query tokens: CTA pairs that split the
+        // dims, 128 heads per pair
+        const char *env = std::getenv("ATB_B200_MLA_PAIR");
+        if (env != nullptr && env[0] == '1' && d.q_per_seq <= 1 && (d.score_mods & (ATB_B200_SCORE_MASK | ATB_B200_SCORE_CAUSAL)) == 0 &&
+            pa_mla_pair_supported(d.head_dim_k, d.head_dim_v, d.v_row_dim, d.rope_dim, d.block_size, d.kv_heads, d.q_dtype, d.kv_dtype)) {
+            p->mla_pair = true;
+            p->heads_per_cta = 128;   // per pair
+            p->chunks_per_kvh = (group + 127) / 128;
+        }
     } else {
         p->heads_per_cta = pa_generic_heads_per_cta(d.head_dim_k, d.head_dim_v);
         p->chunks_per_kvh = (group + p->heads_per_cta - 1) / p->heads_per_cta;
@@ -166,7 +169,7 @@ int plan_paged_attention(const atb_b200_pa_desc &d, const int32_t *context_lens,
     p->max_context = longest;
     const int slots = sm_count * p->ctas_per_sm;
     int64_t n_groups = std::max<int64_t>(1, slots / p->cols);
-    if (p->mla_split) {
+    if (p->mla_pair) {
         // one CTA pair per (group, column), all pairs resident at once
         const int pairs = p->cta_pairs > 0 ? p->cta_pairs : sm_count / 2;
         n_groups = std::max<int64_t>(1, pairs / p->cols);

@@ -36,7 +36,7 @@ struct HostPlan {
     uint64_t off_lens = 0;        // seq_lens (batch entries), ATB_B200_SCORE_CAUSAL only
     uint64_t off_rows = 0;        // bt_rows then mask_rows (batch entries each), ATB_B200_SCORE_ROWS only
     bool fused_combine = false;   // the attention kernel merges split sequences itself
-    bool mla_split = false;       // MLA on CTA pairs that split the dims (pa_mla_split.cu); grid = 2 x groups x cols
+    bool mla_pair = false;        // MLA on CTA pairs that split the dims, 128 heads per pair (pa_mla_pair.cu); grid = 2 x groups x cols
     uint64_t blob_bytes = 0;      // uploaded per launch
     uint64_t off_status = 0, off_lse = 0, off_part_o = 0;
     uint64_t workspace_bytes = 0;

@@ -1,10 +1,10 @@
-"""The opt-in MLA kernel that runs a token range on a pair of CTAs (ATB_B200_MLA_SPLIT=1): parity with the oracle.
+"""The opt-in MLA kernel that runs a token range on a pair of CTAs (ATB_B200_MLA_PAIR=1): parity with the oracle.
 
 The variable is read when a plan is made, so each test sets it for its own plans only.  The default MLA kernel is
 covered by test_parity_gpu.py; the cases here are the ones that exercise what differs in the pair kernel: a single tile,
-ragged tails (rows of V past the end of a range), more than one token range per pair, 128 heads (two head columns),
-split sequences merged by the combine kernel, a block size of one TMA box, the split latent / rope cache, and a block
-table that points outside the cache.  Golden: multi-latent attention of the reference's Python test
+ragged tails (rows of V past the end of a range), more than one token range per pair, fewer heads than the 128 rows of a
+pair, 128 and 160 heads (one and two head columns), split sequences merged by the combine kernel, a block size of one
+TMA box, the split latent / rope cache, and a block table that points outside the cache.  Golden: multi-latent attention of the reference's Python test
 (tests/apitest/kernelstest/mix/test_paged_attention_common.py:229-366 of the reference) through the oracle.
 """
 import numpy as np
@@ -26,6 +26,8 @@ _CASES = [
             seed=4),
     wl.Case("pair_16h_bs64", batch=3, heads=16, kv_heads=1, dk=576, dv=512, block_size=64, q_dtype="bf16", mla=True,
             ctx=("list", [500, 63, 2000]), seed=5),
+    wl.Case("pair_160h_two_columns", batch=2, heads=160, kv_heads=1, dk=576, dv=512, q_dtype="bf16", mla=True, ctx=("list", [1500, 333]),
+            seed=7),
     wl.Case("pair_40h_empty_seq", batch=4, heads=40, kv_heads=1, dk=576, dv=512, q_dtype="bf16", mla=True, ctx=("list", [0, 257, 0, 31]),
             seed=6),
 ]
@@ -33,7 +35,7 @@ _CASES = [
 
 @pytest.fixture
 def pair_kernel(monkeypatch):
-    monkeypatch.setenv("ATB_B200_MLA_SPLIT", "1")
+    monkeypatch.setenv("ATB_B200_MLA_PAIR", "1")
 
 
 def _run(case, h, d):
@@ -63,9 +65,9 @@ def test_pair_kernel_is_deterministic_and_matches_default_kernel(monkeypatch):
     case = _CASES[3]
     h = wl.make_host_inputs(case)
     d = host_inputs_to_device(case, h)
-    monkeypatch.delenv("ATB_B200_MLA_SPLIT", raising=False)
+    monkeypatch.delenv("ATB_B200_MLA_PAIR", raising=False)
     base, plan0, st0 = _run(case, h, d)
-    monkeypatch.setenv("ATB_B200_MLA_SPLIT", "1")
+    monkeypatch.setenv("ATB_B200_MLA_PAIR", "1")
     a, plan1, st1 = _run(case, h, d)
     b, _, st2 = _run(case, h, d)
     assert st0 == 0 and st1 == 0 and st2 == 0
