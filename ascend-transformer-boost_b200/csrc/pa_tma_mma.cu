@@ -31,7 +31,10 @@ constexpr int kConsumerWarps = 4;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kHalfBytes = kStageTokens * 128;      // 64 tokens x 64 elements x 2 B: one TMA box
 
-// Sizes that follow from the head dimension kD (64, 128 or 256).  A row is kD / 64 boxes of 64 elements.
+// Sizes that follow from the head dimension kD (64, 128 or 256).  A row is kD / 64 boxes of 64 elements.  Other head
+// sizes (multiples of 16 below 256) run the next larger geometry: the part of a box past the end of the cache row is out
+// of the tensor's bounds, which TMA fills with zeros without fetching anything, the query's missing dims are set to
+// zero, and only the real dims of the output are written (kPad: global rows are a.dk elements, not kD).
 template <int kD> struct Geo {
     static_assert(kD == 64 || kD == 128 || kD == 256, "head dimensions of the tiled kernel");
     static constexpr int kHalves = kD / 64;                       // boxes per K (or V) row
@@ -47,13 +50,13 @@ template <int kD> struct Geo {
 
 // Writes 8 output elements of (sequence, local head h) to the output tensor - or, when the heads are
 // sharded over several GPUs, into the gathered [tokens, all heads, 128] buffer of every rank.
-template <typename T, int kD>
-__device__ __forceinline__ void store_out_row(const PaArgs &a, int seq, int h, int d0, const uint4 &pk)
+template <typename T>
+__device__ __forceinline__ void store_out_row(const PaArgs &a, int row_dim, int seq, int h, int d0, const uint4 &pk)
 {
     if (a.n_out_peers == 0) {
-        *reinterpret_cast<uint4 *>(static_cast<T *>(a.out) + ((int64_t)seq * a.num_heads + h) * kD + d0) = pk;
+        *reinterpret_cast<uint4 *>(static_cast<T *>(a.out) + ((int64_t)seq * a.num_heads + h) * row_dim + d0) = pk;
     } else {
-        const int64_t off = ((int64_t)seq * a.out_total_heads + a.out_head_offset + h) * kD + d0;
+        const int64_t off = ((int64_t)seq * a.out_total_heads + a.out_head_offset + h) * row_dim + d0;
 #pragma unroll 1
         for (int r = 0; r < a.n_out_peers; ++r) {
             *reinterpret_cast<uint4 *>(static_cast<T *>(a.out_peers[r]) + off) = pk;
@@ -63,7 +66,7 @@ __device__ __forceinline__ void store_out_row(const PaArgs &a, int seq, int h, i
 
 // kMods: the variant that applies an additive mask and / or per-sequence logN factors to the scores; the plain
 // variant carries none of that code.
-template <typename T, bool kMods, int kD>
+template <typename T, bool kMods, int kD, bool kPad>
 __global__ void __launch_bounds__(kThreads, Geo<kD>::kCtasPerSm)
 pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const PaArgs a)
 {
@@ -74,6 +77,7 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     uint8_t *stages = base;
     float *xbuf0 = reinterpret_cast<float *>(base + kStages * kStageBytes);
     float *xbuf1 = xbuf0 + kXbufFloats; // also the final [8][kD + 4] tile
+    const int dr = kPad ? a.dk : kD;    // elements per row of the query, the output and the partials
     float *sm_m = xbuf1 + 8 * kFinalStride;
     float *sm_l = sm_m + 32;
     uint64_t *full = reinterpret_cast<uint64_t *>(sm_l + 32);
@@ -195,11 +199,12 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         uint32_t qf[kSteps][2];
         {
             const bool valid = g < group;
-            const T *qp = q + ((int64_t)item.seq * a.num_heads + head_of(valid ? g : 0)) * kD;
+            const T *qp = q + ((int64_t)item.seq * a.num_heads + head_of(valid ? g : 0)) * dr;
 #pragma unroll
             for (int ks = 0; ks < kSteps; ++ks) {
-                qf[ks][0] = valid ? *reinterpret_cast<const uint32_t *>(qp + ks * 16 + 2 * c) : 0u;
-                qf[ks][1] = valid ? *reinterpret_cast<const uint32_t *>(qp + ks * 16 + 8 + 2 * c) : 0u;
+                const bool in = valid && (!kPad || ks * 16 < dr);   // dr is a multiple of 16
+                qf[ks][0] = in ? *reinterpret_cast<const uint32_t *>(qp + ks * 16 + 2 * c) : 0u;
+                qf[ks][1] = in ? *reinterpret_cast<const uint32_t *>(qp + ks * 16 + 8 + 2 * c) : 0u;
             }
         }
         float o[kSteps][4];
@@ -442,9 +447,9 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         }
         named_bar_sync(1, kConsumerWarps * 32);
         // kD / 8 chunks of 8 dims per head row, 8 head rows: a thread per chunk (two at kD = 256, half the threads at 64)
-        for (int idx = threadIdx.x; idx < kD; idx += kConsumerWarps * 32) {
-            const int hl = idx / (kD / 8);       // head within the group
-            const int d0 = (idx % (kD / 8)) * 8; // 8 consecutive dims
+        for (int idx = threadIdx.x; idx < dr; idx += kConsumerWarps * 32) {
+            const int hl = idx / (dr / 8);       // head within the group
+            const int d0 = (idx % (dr / 8)) * 8; // 8 consecutive dims
             if (hl < group) {
                 const float *src = xbuf1 + hl * kFinalStride + d0;
                 const float4 va = *reinterpret_cast<const float4 *>(src);
@@ -456,9 +461,9 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     pk.y = Elem<T>::pack2(va.z, va.w);
                     pk.z = Elem<T>::pack2(vb.x, vb.y);
                     pk.w = Elem<T>::pack2(vb.z, vb.w);
-                    store_out_row<T, kD>(a, item.seq, h, d0, pk);
+                    store_out_row<T>(a, dr, item.seq, h, d0, pk);
                 } else {
-                    float *dst = a.plan.part_o + ((int64_t)item.slot * a.num_heads + h) * kD + d0;
+                    float *dst = a.plan.part_o + ((int64_t)item.slot * a.num_heads + h) * dr + d0;
                     *reinterpret_cast<float4 *>(dst) = va;
                     *reinterpret_cast<float4 *>(dst + 4) = vb;
                     if (d0 == 0) {
@@ -490,9 +495,9 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             const bool last = sm_l[0] != 0.f;
             if (last) {
                 __threadfence();
-                for (int idx = threadIdx.x; idx < kD; idx += kConsumerWarps * 32) {
-                    const int hl = idx / (kD / 8);
-                    const int d0 = (idx % (kD / 8)) * 8;
+                for (int idx = threadIdx.x; idx < dr; idx += kConsumerWarps * 32) {
+                    const int hl = idx / (dr / 8);
+                    const int d0 = (idx % (dr / 8)) * 8;
                     if (hl >= group) {
                         continue;
                     }
@@ -505,12 +510,12 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     }
                     float wsum = 0.f;
                     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                    const float *po = a.plan.part_o + ((int64_t)pbase * a.num_heads + h) * kD + d0;
+                    const float *po = a.plan.part_o + ((int64_t)pbase * a.num_heads + h) * dr + d0;
                     for (int i = 0; i < n_parts; ++i) {
                         const float w = exp2f(__ldcg(lse + (int64_t)i * a.num_heads) - mx);
                         wsum += w;
-                        const float4 pa = __ldcg(reinterpret_cast<const float4 *>(po + (int64_t)i * a.num_heads * kD));
-                        const float4 pb = __ldcg(reinterpret_cast<const float4 *>(po + (int64_t)i * a.num_heads * kD + 4));
+                        const float4 pa = __ldcg(reinterpret_cast<const float4 *>(po + (int64_t)i * a.num_heads * dr));
+                        const float4 pb = __ldcg(reinterpret_cast<const float4 *>(po + (int64_t)i * a.num_heads * dr + 4));
                         acc[0] = fmaf(w, pa.x, acc[0]);
                         acc[1] = fmaf(w, pa.y, acc[1]);
                         acc[2] = fmaf(w, pa.z, acc[2]);
@@ -526,7 +531,7 @@ pa_tma_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     pk.y = Elem<T>::pack2(acc[2] * inv, acc[3] * inv);
                     pk.z = Elem<T>::pack2(acc[4] * inv, acc[5] * inv);
                     pk.w = Elem<T>::pack2(acc[6] * inv, acc[7] * inv);
-                    store_out_row<T, kD>(a, item.seq, h, d0, pk);
+                    store_out_row<T>(a, dr, item.seq, h, d0, pk);
                 }
             }
         }
@@ -575,13 +580,13 @@ bool encode_cache_map(CUtensorMap *map, const void *base, int elem_dtype, int kv
     return r == CUDA_SUCCESS;
 }
 
-template <typename T, int kD>
+template <typename T, int kD, bool kPad>
 cudaError_t launch_typed(const PaArgs &args, const CUtensorMap &km, const CUtensorMap &vm, cudaStream_t s)
 {
     constexpr int kSmemBytes = Geo<kD>::kSmemBytes;
     const bool mods = args.mask != nullptr || args.logn != nullptr || args.bt_rows != nullptr || args.q_per_seq > 1 ||
                       args.seq_lens != nullptr;
-    auto kern = mods ? pa_tma_mma_kernel<T, true, kD> : pa_tma_mma_kernel<T, false, kD>;
+    auto kern = mods ? pa_tma_mma_kernel<T, true, kD, kPad> : pa_tma_mma_kernel<T, false, kD, kPad>;
     static bool configured_plain[64] = {}, configured_mods[64] = {};
     bool *configured = mods ? configured_mods : configured_plain;
     int dev = 0;
@@ -611,9 +616,18 @@ cudaError_t launch_typed(const PaArgs &args, const CUtensorMap &km, const CUtens
 
 } // namespace
 
+// The geometry (64, 128 or 256) a head size runs on; 0 if the tiled kernel has none for it.
+static int tiled_geometry(int dk)
+{
+    if (dk < 16 || dk > 256 || dk % 16 != 0) {
+        return 0;
+    }
+    return dk <= 64 ? 64 : dk <= 128 ? 128 : 256;
+}
+
 bool pa_tma_mma_supported(int dk, int dv, int v_row_dim, int block_size, int group, int q_dtype, int kv_dtype)
 {
-    return (dk == 64 || dk == 128 || dk == 256) && dv == dk && v_row_dim == dk && (block_size == 16 || block_size == 32 || block_size == 64 || block_size == 128 || block_size == 256) && group >= 1 &&
+    return tiled_geometry(dk) != 0 && dv == dk && v_row_dim == dk && (block_size == 16 || block_size == 32 || block_size == 64 || block_size == 128 || block_size == 256) && group >= 1 &&
            (q_dtype == kFp16 || q_dtype == kBf16) && kv_dtype == q_dtype;
 }
 
@@ -626,16 +640,22 @@ cudaError_t launch_pa_tma_mma(const PaArgs &args, int q_dtype, int kv_dtype, int
         return cudaErrorInvalidValue;
     }
     const bool f16 = q_dtype == kFp16;
-    switch (args.dk) {
+    const int geo = tiled_geometry(args.dk);
+    const bool pad = geo != args.dk;
+#define ATB_B200_LAUNCH_TILED(D)                                                                                              \
+    (pad ? (f16 ? launch_typed<__half, D, true>(args, km, vm, stream) : launch_typed<__nv_bfloat16, D, true>(args, km, vm, stream)) \
+         : (f16 ? launch_typed<__half, D, false>(args, km, vm, stream) : launch_typed<__nv_bfloat16, D, false>(args, km, vm, stream)))
+    switch (geo) {
         case 64:
-            return f16 ? launch_typed<__half, 64>(args, km, vm, stream) : launch_typed<__nv_bfloat16, 64>(args, km, vm, stream);
+            return ATB_B200_LAUNCH_TILED(64);
         case 128:
-            return f16 ? launch_typed<__half, 128>(args, km, vm, stream) : launch_typed<__nv_bfloat16, 128>(args, km, vm, stream);
+            return ATB_B200_LAUNCH_TILED(128);
         case 256:
-            return f16 ? launch_typed<__half, 256>(args, km, vm, stream) : launch_typed<__nv_bfloat16, 256>(args, km, vm, stream);
+            return ATB_B200_LAUNCH_TILED(256);
         default:
             return cudaErrorInvalidValue;
     }
+#undef ATB_B200_LAUNCH_TILED
 }
 
 } // namespace atb_b200

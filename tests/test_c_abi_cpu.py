@@ -118,7 +118,7 @@ def test_plan_rejects_bad_arguments():
     with pytest.raises(capi.AtbError):
         capi.PaPlan(d, lens)
     # a kernel that does not support the shape
-    d = capi.make_desc(4, 8, 8, 96, 96, 16, 1000, 64, "fp16", kernel=capi.KERNEL_TMA_MMA, sm_count=148)
+    d = capi.make_desc(4, 8, 8, 72, 72, 16, 1000, 64, "fp16", kernel=capi.KERNEL_TMA_MMA, sm_count=148)
     with pytest.raises(capi.AtbError) as e:
         capi.PaPlan(d, np.array([5, 6, 7, 8], dtype=np.int32))
     assert e.value.code == capi.ERROR_INVALID_TENSOR_DIM
@@ -128,7 +128,7 @@ def test_kernel_selection():
     assert _plan(wl.CONFIGS[1])[0].info.kernel == capi.KERNEL_TMA_MMA
     assert _plan(wl.CONFIGS[0])[0].info.kernel == capi.KERNEL_TMA_MMA
     small = {c.name: c for c in wl.SMALL_CASES}
-    assert _plan(small["ragged_d96_bs16_fp16"])[0].info.kernel == capi.KERNEL_GENERIC
+    assert _plan(small["ragged_d96_bs16_fp16"])[0].info.kernel == capi.KERNEL_TMA_MMA     # 96 runs padded on the 128 geometry
     # more than 8 query heads per kv head: the tiled kernel, a CTA column per chunk of 8 heads
     p127 = _plan(small["gqa127_fp16"])[0].info
     assert p127.kernel == capi.KERNEL_TMA_MMA and p127.num_ctas % 16 == 0
@@ -490,7 +490,8 @@ def test_planner_routes_score_modifiers():
     assert plan() == capi.KERNEL_TMA_MMA
     assert plan(mods=capi.SCORE_LOGN | capi.SCORE_MASK) == capi.KERNEL_TMA_MMA
     assert plan(dk=64) == capi.KERNEL_TMA_MMA and plan(dk=256) == capi.KERNEL_TMA_MMA
-    assert plan(dk=96) == capi.KERNEL_GENERIC
+    assert plan(dk=96) == capi.KERNEL_TMA_MMA and plan(dk=192) == capi.KERNEL_TMA_MMA   # multiples of 16: padded geometry
+    assert plan(dk=72) == capi.KERNEL_GENERIC
     assert plan(kv="int8") == capi.KERNEL_GENERIC                          # the int8 TMA kernel carries no mask code
     assert plan(kernel=capi.KERNEL_GENERIC) == capi.KERNEL_GENERIC
     _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, kv="int8", kernel=capi.KERNEL_TMA_MMA)
@@ -537,7 +538,7 @@ def test_bnsd_layout_rules(monkeypatch):
     # kernel level: heads-major blocks exist for fp16 / bf16 caches without the split MLA cache
     d = capi.make_desc(3, 8, 2, 128, 128, 64, 16, 8, "fp16", sm_count=148, kv_layout=1)
     assert capi.PaPlan(d, lens).info.kernel == capi.KERNEL_TMA_MMA
-    assert capi.PaPlan(capi.make_desc(3, 8, 2, 96, 96, 64, 16, 8, "fp16", sm_count=148, kv_layout=1),
+    assert capi.PaPlan(capi.make_desc(3, 8, 2, 72, 72, 64, 16, 8, "fp16", sm_count=148, kv_layout=1),
                        lens).info.kernel == capi.KERNEL_GENERIC
     _expect(capi.ERROR_INVALID_PARAM, capi.PaPlan, capi.make_desc(3, 8, 2, 128, 128, 64, 16, 8, "fp16", "int8", sm_count=148,
                                                                    kv_layout=1), lens)
@@ -611,7 +612,8 @@ def test_fused_parallel_decoding_plan_rules(monkeypatch):
     assert plan(heads=32, kvh=4, n=2) == capi.KERNEL_TMA_MMA               # 8 pairs
     _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, heads=48, kvh=4, n=3)     # 12 pairs
     assert plan(dk=64) == capi.KERNEL_TMA_MMA                              # head sizes 64 / 128 / 256
-    _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, dk=96)
+    assert plan(dk=96) == capi.KERNEL_TMA_MMA                              # padded on the 128 geometry
+    _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, dk=72)
     _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, kv="int8")
     _expect(capi.ERROR_INVALID_TENSOR_DIM, plan, kernel=capi.KERNEL_GENERIC)
     _expect(capi.ERROR_INVALID_PARAM, plan, heads=18, kvh=2, n=4)          # heads not a multiple of the token count

@@ -300,6 +300,21 @@ _WIDE_CASES = [
     wl.Case("gqa12_int8_fp16", batch=3, heads=24, kv_heads=2, q_dtype="fp16", kv_dtype="int8", offsets=True,
             ctx=("list", [300, 5000, 64]), seed=308),
     wl.Case("gqa9_d64_bf16", batch=2, heads=18, kv_heads=2, dk=64, dv=64, q_dtype="bf16", ctx=("list", [513, 77]), seed=309),
+    # head sizes between the geometries: multiples of 16 run padded (TMA zero-fills the part of a box past the row)
+    wl.Case("d96_gqa4_bf16_split", batch=3, heads=16, kv_heads=4, dk=96, dv=96, q_dtype="bf16", ctx=("list", [9000, 1, 700]), seed=310),
+    wl.Case("d96_mha_fp16_bs16", batch=4, heads=6, kv_heads=6, dk=96, dv=96, block_size=16, q_dtype="fp16",
+            ctx=("list", [15, 16, 17, 1200]), seed=311),
+    wl.Case("d80_gqa2_fp16", batch=3, heads=8, kv_heads=4, dk=80, dv=80, q_dtype="fp16", ctx=("list", [333, 64, 2049]), seed=312),
+    wl.Case("d112_gqa8_bf16_bs32", batch=2, heads=16, kv_heads=2, dk=112, dv=112, block_size=32, q_dtype="bf16",
+            ctx=("list", [5000, 90]), seed=313),
+    wl.Case("d32_mha_fp16", batch=3, heads=4, kv_heads=4, dk=32, dv=32, q_dtype="fp16", ctx=("list", [70, 1, 900]), seed=314),
+    wl.Case("d48_gqa3_bf16_bs64", batch=2, heads=6, kv_heads=2, dk=48, dv=48, block_size=64, q_dtype="bf16", ctx=("list", [640, 65]),
+            seed=315),
+    wl.Case("d160_mha_bf16", batch=3, heads=4, kv_heads=4, dk=160, dv=160, q_dtype="bf16", ctx=("list", [2, 1500, 129]), seed=316),
+    wl.Case("d192_gqa4_fp16_bs64_split", batch=2, heads=8, kv_heads=2, dk=192, dv=192, block_size=64, q_dtype="fp16",
+            ctx=("list", [7000, 300]), seed=317),
+    wl.Case("d240_mha_fp16_bs16", batch=2, heads=3, kv_heads=3, dk=240, dv=240, block_size=16, q_dtype="fp16", ctx=("list", [47, 800]),
+            seed=318),
 ]
 
 
