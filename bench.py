@@ -334,7 +334,11 @@ def measure_decode(args, case, rt, steps, with_cpu_baseline):
         ms, kernel_ms = float(t[0]), float(t[1])
 
     # ---- end to end through the operator API with host buffers (rank-local shard, same step)
-    e2e = run_e2e(args, case, shard, rt, d, lens, gathered, steps, p2p)
+    chunks = e2e_chunks(wl, shard, lens, world, args.e2e_chunks)
+    if len(chunks) > 1:
+        e2e = run_e2e_pipelined(args, shard, rt, d, lens, steps, chunks, out)
+    else:
+        e2e = run_e2e(args, case, shard, rt, d, lens, gathered, steps, p2p)
     if world > 1:
         t = torch.tensor([e2e["ms"]], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -400,7 +404,7 @@ def measure_decode(args, case, rt, steps, with_cpu_baseline):
                "e2e": {"value": kv_bytes_global / (e2e["ms"] * 1e-3) / 1e9, "unit": UNIT,
                        "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
                        "ms_per_step": e2e["ms"], "tokens_per_s": case.batch / (e2e["ms"] * 1e-3),
-                       "gather": e2e["gather"]},
+                       "gather": e2e["gather"], **{k: e2e[k] for k in ("pipeline", "max_abs_diff_vs_kernel_level_path") if k in e2e}},
                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT,
                             "frac": achieved / peak, "peak_kind": "of " + peak_kind,
                             "kernel": "pa attention kernel, per GPU", "kernel_ms": kernel_ms,
@@ -441,6 +445,8 @@ def main():
                     help="index into the benchmark configurations (default: the largest single-GPU one)")
     ap.add_argument("--only", action="store_true", help="measure the chosen configuration alone (no `configs` array)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-chunks", type=int, default=0,
+                    help="sub-batches of the pipelined end-to-end step on one GPU (0: chosen from the cache size; 1: no pipelining)")
     ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
                     help="N>1: attention stores into every rank's gathered buffer (p2p) or a separate NCCL all-gather")
     ap.add_argument("--variant", default="plain", choices=["plain", "alibi", "mtp2", "mtp2_rows"],
@@ -694,6 +700,125 @@ def run_cache_op_bench(args, capi):
                       "gpu_launches": steps, "clocks": clocks,
                       "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
                                    "peak_kind": "of " + peak_kind, "kernel": args.op, "kernel_ms": ms, "traffic": None}}))
+
+
+E2E_CHUNK_BYTES = 600e6   # a sub-batch of the pipelined end-to-end step reads at least this much cache
+
+
+def e2e_chunks(wl, case, lens, world, forced=0):
+    """Sub-batches of the end-to-end step on one GPU: contiguous slices of the batch with about equal context tokens
+    (equal kernel time), at most four, none smaller than E2E_CHUNK_BYTES of cache (smaller kernels lose more than the
+    overlap gains).  [(b0, b1)]; one slice = the whole batch = no pipelining."""
+    n = 1 if world > 1 else int(max(1, min(4, wl.kv_bytes(case, lens) // E2E_CHUNK_BYTES)))
+    if forced > 0 and world == 1:
+        n = min(forced, case.batch)
+    csum = np.concatenate([[0], np.cumsum(np.asarray(lens, dtype=np.int64))])
+    cuts = [0]
+    for j in range(1, n):
+        b = int(np.searchsorted(csum, csum[-1] * j / n))
+        cuts.append(min(max(b, cuts[-1] + 1), case.batch - (n - j)))
+    cuts.append(case.batch)
+    return [(cuts[j], cuts[j + 1]) for j in range(n)]
+
+
+def run_e2e_pipelined(args, case, rt, d, lens, steps, chunks, check_out):
+    """The end-to-end step of run_e2e on one GPU, as sub-batches in a pipeline: each sub-batch has its inputs packed in
+    one pinned staging area (one H2D copy on a copy stream), its own ReshapeAndCache and PagedAttention operations
+    (Setup re-plans from its host context_lens every step, Execute on the compute stream once its copy has landed) and
+    its slice of the output read back on a third stream.  The copies of one sub-batch overlap the kernels of another;
+    a step ends when the whole output is in pinned host memory.  The result of the last step is compared with
+    `check_out` (the output of the kernel-level path on the same inputs)."""
+    import ctypes
+    import torch
+    wl, capi, dev = rt["wl"], rt["capi"], rt["dev"]
+    T = capi.atb_tensor
+    s_h2d, s_run, s_d2h = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    names = ["q", "new_k", "block_tables", "slot_mapping", "context_lens"] + ([] if case.mla else ["new_v"])
+    out = torch.zeros((case.batch, case.heads, case.dv), dtype=d["q"].dtype, device=dev)
+    out_host = torch.empty(tuple(out.shape), dtype=out.dtype).pin_memory()
+    ctx = capi.Context(s_run.cuda_stream)
+    L = capi.lib()
+    arr = capi.Operation._arr
+    need = ctypes.c_uint64(0)
+    parts, h2d = [], 0
+    for b0, b1 in chunks:
+        offs, total = {}, 0
+        for k in names:
+            offs[k] = total
+            total += (d[k][b0:b1].numel() * d[k].element_size() + 255) // 256 * 256
+        host_pack = torch.empty(total, dtype=torch.uint8).pin_memory()
+        dev_pack = torch.empty(total, dtype=torch.uint8, device=dev)
+        devb = {}
+        for k in names:
+            src = d[k][b0:b1]
+            n = src.numel() * src.element_size()
+            host_pack[offs[k]:offs[k] + n] = src.cpu().contiguous().view(torch.uint8).view(-1)
+            devb[k] = dev_pack[offs[k]:offs[k] + n].view(src.dtype).view(src.shape)
+            h2d += n
+        lens_host = host_pack[offs["context_lens"]:offs["context_lens"] + 4 * (b1 - b0)].view(torch.int32).numpy()
+        rac_param = capi.ReshapeAndCacheParam()
+        rac_param.kvCacheCfg = 1 if case.mla else 0
+        rac = capi.Operation(rac_param)
+        pa_kw = dict(headNum=case.heads, kvHeadNum=case.kv_heads, qkScale=case.qk_scale)
+        if case.kvd == "int8":
+            pa_kw["quantType"] = 1
+        if case.mla:
+            pa_kw["mlaVHeadSize"] = case.dv
+        pa = capi.Operation(capi.PagedAttentionParam(**pa_kw))
+        if case.mla:
+            rac_in = [T(devb["new_k"]), T(d["k_cache"]), T(devb["slot_mapping"])]
+            rac_out = [T(d["k_cache"])]
+            pa_in = [T(devb["q"]), T(d["k_cache"]), T(devb["block_tables"]), T(devb["context_lens"], host=lens_host)]
+        else:
+            rac_in = [T(devb["new_k"]), T(devb["new_v"]), T(d["k_cache"]), T(d["v_cache"]), T(devb["slot_mapping"])]
+            rac_out = [T(d["k_cache"]), T(d["v_cache"])]
+            pa_in = [T(devb["q"]), T(d["k_cache"]), T(d["v_cache"]), T(devb["block_tables"]),
+                     T(devb["context_lens"], host=lens_host)]
+        if case.kvd == "int8":
+            pa_in += [T(d["k_descale"]), T(d["v_descale"])]
+        pa_out = [T(out[b0:b1])]
+        ws_bytes = pa.setup(pa_in, pa_out, ctx)
+        ws = torch.empty(max(ws_bytes * 2, 256), dtype=torch.uint8, device=dev)
+        parts.append(dict(host_pack=host_pack, dev_pack=dev_pack, rac=rac, pa=pa, keep=(rac_in, rac_out, pa_in, pa_out, devb, ws),
+                          rac_i=arr(rac_in), n_ri=len(rac_in), rac_o=arr(rac_out), n_ro=len(rac_out), pa_i=arr(pa_in), n_pi=len(pa_in),
+                          pa_o=arr(pa_out), n_po=len(pa_out), ws_ptr=ctypes.c_void_p(ws.data_ptr()), ws_len=ws.numel(),
+                          out_dev=out[b0:b1], out_host=out_host[b0:b1], ev_in=torch.cuda.Event(), ev_done=torch.cuda.Event()))
+    d2h = out_host.numel() * out_host.element_size()
+
+    def step():
+        for p in parts:
+            with torch.cuda.stream(s_h2d):
+                p["dev_pack"].copy_(p["host_pack"], non_blocking=True)
+                p["ev_in"].record(s_h2d)
+        for p in parts:
+            s_run.wait_event(p["ev_in"])
+            rc = L.atb_b200_operation_setup(p["rac"].handle, p["rac_i"], p["n_ri"], p["rac_o"], p["n_ro"], ctypes.byref(need), ctx.handle)
+            rc |= L.atb_b200_operation_setup(p["pa"].handle, p["pa_i"], p["n_pi"], p["pa_o"], p["n_po"], ctypes.byref(need), ctx.handle)
+            rc |= L.atb_b200_operation_execute(p["rac"].handle, p["rac_i"], p["n_ri"], p["rac_o"], p["n_ro"], None, 0, ctx.handle)
+            rc |= L.atb_b200_operation_execute(p["pa"].handle, p["pa_i"], p["n_pi"], p["pa_o"], p["n_po"], p["ws_ptr"], p["ws_len"], ctx.handle)
+            if rc != 0 or need.value > p["ws_len"]:
+                raise RuntimeError(f"operator call failed ({rc})")
+            p["ev_done"].record(s_run)
+            s_d2h.wait_event(p["ev_done"])
+            with torch.cuda.stream(s_d2h):
+                p["out_host"].copy_(p["out_dev"], non_blocking=True)
+        s_d2h.synchronize()                           # the caller consumes the result every step
+
+    torch.cuda.synchronize()
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    torch.cuda.synchronize()
+    ms = (time.perf_counter() - t0) * 1e3 / steps
+    diff = float((out_host.float() - check_out.detach().cpu().float()).abs().max())
+    if not diff <= TOLERANCE[case.q_dtype if case.kvd != "int8" else "int8"]:
+        raise RuntimeError(f"pipelined end-to-end output differs from the kernel-level path by {diff}")
+    return {"ms": ms, "h2d": h2d, "d2h": d2h, "gather": "single GPU",
+            "pipeline": f"{len(chunks)} sub-batches of about equal context tokens; the copies of one overlap the kernels of another",
+            "max_abs_diff_vs_kernel_level_path": diff}
 
 
 def run_e2e(args, full_case, case, rt, d, lens, gathered, steps, p2p):
