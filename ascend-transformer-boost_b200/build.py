@@ -56,7 +56,7 @@ def build(force=False, verbose=False):
         failed |= p.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    subprocess.check_call([nvcc, "-shared", "-Wno-deprecated-gpu-targets", "-o", OUT] + objs + ["-cudart", "shared" if os.environ.get("ATB_B200_SHARED_CUDART") else "static"])
+    subprocess.check_call([nvcc, "-shared", "-Wno-deprecated-gpu-targets", "-o", OUT] + objs + ["-cudart", "shared" if os.environ.get("ATB_B200_SHARED_CUDART") else "static", "-ldl"])
     return OUT
 
 

@@ -4,6 +4,8 @@
 #include <cstring>
 #include <limits>
 #include <new>
+#include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 
 namespace atb {
 
@@ -283,8 +285,27 @@ Status OperationBase::CheckVariantPack(const VariantPack &variantPack) const
     return NO_ERROR;
 }
 
+namespace {
+// A named range around Setup / Execute for timeline tools (NVTX is header-only and costs a few nanoseconds when no tool
+// is attached).
+struct TraceRange {
+    explicit TraceRange(const std::string &name) { nvtxRangePushA(name.c_str()); }
+    ~TraceRange() { nvtxRangePop(); }
+};
+
+// ATB_STREAM_SYNC_EVERY_OPERATION_ENABLE=1, as in the reference (src/atb/utils/config.cpp:36,
+// src/atb/operation/operation_base.cpp:1059-1062): wait for the execute stream after every Execute, so that a device
+// failure is reported by the operation that caused it.  Read at every call: a test can switch it.
+bool StreamSyncEveryOperation()
+{
+    const char *e = std::getenv("ATB_STREAM_SYNC_EVERY_OPERATION_ENABLE");
+    return e != nullptr && std::strcmp(e, "1") == 0;
+}
+} // namespace
+
 Status OperationBase::Setup(const VariantPack &variantPack, uint64_t &workspaceSize, Context *context)
 {
+    TraceRange range(name_ + "::Setup");
     setupSuccess_ = false;
     try {
         Status st = CheckVariantPack(variantPack);
@@ -328,6 +349,7 @@ Status OperationBase::Setup(const VariantPack &variantPack, uint64_t &workspaceS
 Status OperationBase::Execute(const VariantPack &variantPack, uint8_t *workspace, uint64_t workspaceSize,
                               Context *context)
 {
+    TraceRange range(name_ + "::Execute");
     try {
         if (!setupSuccess_) {
             ATB_B200_LOG(ERROR, name_ + ": Execute without a successful Setup");
@@ -360,7 +382,14 @@ Status OperationBase::Execute(const VariantPack &variantPack, uint8_t *workspace
                 return ERROR_INVALID_PARAM;
             }
         }
-        return LaunchImpl(variantPack, workspace, workspaceSize, stream);
+        const Status st = LaunchImpl(variantPack, workspace, workspaceSize, stream);
+        if (StreamSyncEveryOperation()) {
+            const cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+            if (e != cudaSuccess) {
+                ATB_B200_LOG(ERROR, name_ + ": stream sync fail: " + cudaGetErrorString(e));
+            }
+        }
+        return st;
     } catch (...) {
         return ERROR_RT_FAIL;
     }

@@ -198,3 +198,31 @@ def test_paged_attention_operation_stores_into_the_gathered_buffer():
     op.execute(ins, outs, ws.data_ptr(), ws_bytes, ctx)
     torch.cuda.synchronize()
     assert max_abs_err(wl.torch_to_host(out, case.q_dtype), ref, case.q_dtype) <= tol_for(case)
+
+
+def test_stream_sync_every_operation(monkeypatch):
+    """ATB_STREAM_SYNC_EVERY_OPERATION_ENABLE=1 (src/atb/utils/config.cpp:36 and
+    src/atb/operation/operation_base.cpp:1059-1062 of the reference): Execute returns with its stream drained."""
+    case = wl.CONFIGS[1]                                   # ~130 us of kernel time: not done by the time a launch returns
+    h = wl.make_host_inputs(case)
+    d = host_inputs_to_device(case, h)
+    T = capi.atb_tensor
+    out = torch.zeros((case.batch, case.heads, case.dv), dtype=wl.torch_dtype(case.q_dtype), device="cuda")
+    lens_dev = torch.from_numpy(h["context_lens"]).cuda()
+    ins = [T(d["q"]), T(d["k_cache"]), T(d["v_cache"]), T(d["block_tables"]), T(lens_dev, host=h["context_lens"])]
+    outs = [T(out)]
+    op = capi.Operation(capi.PagedAttentionParam(headNum=case.heads, kvHeadNum=case.kv_heads, qkScale=case.qk_scale))
+    ctx = _new_ctx()
+    stream = _STREAMS[-1]
+    ws_bytes = op.setup(ins, outs, ctx)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device="cuda")
+    monkeypatch.setenv("ATB_STREAM_SYNC_EVERY_OPERATION_ENABLE", "1")
+    for _ in range(3):
+        op.setup(ins, outs, ctx)
+        op.execute(ins, outs, ws.data_ptr(), ws_bytes, ctx)
+        assert stream.query()                              # nothing left in flight
+    monkeypatch.setenv("ATB_STREAM_SYNC_EVERY_OPERATION_ENABLE", "0")
+    op.setup(ins, outs, ctx)
+    op.execute(ins, outs, ws.data_ptr(), ws_bytes, ctx)
+    torch.cuda.synchronize()
+    assert max_abs_err(wl.torch_to_host(out, case.q_dtype), oracle_out(case, h), case.q_dtype) <= tol_for(case)
