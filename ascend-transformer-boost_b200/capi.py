@@ -151,7 +151,7 @@ EXPORTS = [
     "atb_b200_operation_create_paged_attention", "atb_b200_operation_create_reshape_and_cache",
     "atb_b200_operation_input_num", "atb_b200_operation_output_num", "atb_b200_operation_infer_shape",
     "atb_b200_operation_setup", "atb_b200_operation_execute", "atb_b200_operation_destroy", "atb_b200_version",
-    "atb_b200_pa_decode_static_scratch", "atb_b200_pa_launch_gathered", "atb_b200_peer_buffer_create",
+    "atb_b200_pa_decode_static_scratch", "atb_b200_pa_static_scratch_status", "atb_b200_pa_launch_gathered", "atb_b200_peer_buffer_create",
     "atb_b200_peer_buffer_open", "atb_b200_peer_buffer_close", "atb_b200_peer_buffer_destroy",
     "atb_b200_pa_plan_set_trace", "atb_b200_pa_plan_prefetch", "atb_b200_operation_name",
     "atb_b200_block_copy", "atb_b200_paged_cache_load", "atb_b200_paged_cache_load_workspace_bytes",
@@ -210,6 +210,7 @@ def lib():
         L.atb_b200_operation_name.argtypes = [vp, ctypes.c_char_p, u64]
         L.atb_b200_version.restype = ctypes.c_char_p
         L.atb_b200_pa_decode_static_scratch.argtypes = [P(PaDesc), vp, P(PaTensors), vp]
+        L.atb_b200_pa_static_scratch_status.argtypes = [vp, P(ctypes.c_int32)]
         L.atb_b200_pa_launch_gathered.argtypes = [vp, P(PaTensors), P(PaPeers), vp, u64, vp]
         L.atb_b200_context_set_gather.argtypes = [vp, P(PaPeers)]
         L.atb_b200_peer_buffer_create.argtypes = [u64, P(vp), ctypes.c_char_p]

@@ -29,8 +29,8 @@
 // split would stay frozen at the lengths seen at capture time.
 //
 // Device-side status (a bounded wait that gave up, a block id outside the cache) is written into the
-// scratch and not reported by this entry point; callers that need it use the planned entry points
-// and atb_b200_pa_plan_device_status.
+// first word of the scratch (cleared by every call's plan upload); atb_b200_pa_static_scratch_status
+// copies it back on the caller's stream, also without allocating.
 #include <cuda_runtime.h>
 #include <algorithm>
 #include <atomic>
@@ -188,7 +188,8 @@ extern "C" int atb_b200_pa_decode_static_scratch(const atb_b200_pa_desc *desc, c
     const int64_t snap = (total_tiles / n_groups >= 8) ? 1 : 0;
 
     alignas(16) unsigned char blob[kBlobCap];
-    uint64_t off = 0;
+    const uint64_t off_status = 0;          // fixed place: atb_b200_pa_static_scratch_status reads it
+    uint64_t off = 16;
     const uint64_t off_group_begin = off;
     off = align_up(off + (uint64_t)(n_groups + 1) * sizeof(int32_t), 16);
     const uint64_t off_items = off;
@@ -199,8 +200,6 @@ extern "C" int atb_b200_pa_decode_static_scratch(const atb_b200_pa_desc *desc, c
     off = align_up(off + (uint64_t)d.batch * sizeof(int32_t), 16);
     const uint64_t off_combine = off;
     off = align_up(off + (uint64_t)d.batch * sizeof(int32_t), 16);
-    const uint64_t off_status = off;
-    off += 16;
     const uint64_t blob_bytes = align_up(off, 256);
     if (blob_bytes > kBlobCap) {
         return refuse("plan bytes", (long long)blob_bytes, (long long)kBlobCap);
@@ -326,4 +325,27 @@ extern "C" int atb_b200_pa_decode_static_scratch(const atb_b200_pa_desc *desc, c
     }
     e = launch_pa_combine(a, n_combine, d.q_dtype, stream);
     return e == cudaSuccess ? ATB_B200_OK : kErrRtFail;
+}
+
+extern "C" int atb_b200_pa_static_scratch_status(void *stream, int32_t *status_out)
+{
+    if (status_out == nullptr) {
+        return atb_b200::kErrInvalidParam;
+    }
+    unsigned char *scratch = nullptr;
+    const int rc = atb_b200::scratch_address(&scratch);
+    if (rc != 0) {
+        return rc;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+        return atb_b200::kErrInvalidParam;
+    }
+    // the status word is the first word of the scratch; the destination may be pageable: the call waits for the copy
+    if (cudaMemcpyAsync(status_out, scratch, sizeof(int32_t), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaStreamSynchronize(s) != cudaSuccess) {
+        return atb_b200::kErrRtFail;
+    }
+    return ATB_B200_OK;
 }

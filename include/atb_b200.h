@@ -284,6 +284,12 @@ int atb_b200_pa_plan_kernel_ms(atb_b200_pa_plan *plan, int32_t launches_back, fl
 int atb_b200_pa_decode_static_scratch(const atb_b200_pa_desc *desc, const int32_t *context_lens_host,
                                       const atb_b200_pa_tensors *tensors, void *stream);
 
+/* Device status of the last atb_b200_pa_decode_static_scratch call on this GPU whose kernels have run: 0, 1 (a bounded
+ * wait gave up) or 2 (a block id outside the cache), as atb_b200_pa_plan_device_status reports for the planned entry
+ * points.  Copies the word from the scratch on `stream` and waits for that stream; allocates nothing; refused on a
+ * capturing stream.  Like the entry point itself it has no counterpart in the reference. */
+int atb_b200_pa_static_scratch_status(void *stream, int32_t *status_out);
+
 /* ---------------------------------------------------------------- operator level */
 
 /* Mirrors atb::Tensor (include/atb/types.h:118-127 of the reference). */

@@ -33,6 +33,12 @@ def _static_scratch_call(case, h, d, out):
                                                         capi.torch_stream_ptr())
 
 
+def _scratch_status():
+    st = ctypes.c_int32(-1)
+    assert capi.lib().atb_b200_pa_static_scratch_status(capi.torch_stream_ptr(), ctypes.byref(st)) == 0
+    return st.value
+
+
 @pytest.mark.parametrize("case", [
     wl.Case("noalloc_gqa4_bf16", batch=12, heads=32, kv_heads=8, q_dtype="bf16", ctx=("uniform", 500, 6000), seed=41),
     wl.Case("noalloc_gqa15_fp16", batch=6, heads=30, kv_heads=2, q_dtype="fp16", ctx=("uniform", 88, 4000), seed=42),
@@ -52,6 +58,7 @@ def test_static_scratch_matches_workspace_entry_point(case):
         out = torch.zeros_like(ref)
         rc = _static_scratch_call(case, h, d, out)
         assert rc == 0, rc
+        assert _scratch_status() == 0
         torch.cuda.synchronize()
         err = np.abs(out.float().cpu().numpy() - ref_f).max()
         assert err <= tol_for(case), (call, err)
@@ -65,6 +72,25 @@ def test_static_scratch_matches_workspace_entry_point(case):
     torch.cuda.synchronize()
     assert np.abs(out2.float().cpu().numpy() - ref2.float().cpu().numpy()).max() <= tol_for(case)
     assert max_abs_err(wl.torch_to_host(out2, case.q_dtype), oracle_out(case, h2), case.q_dtype) <= tol_for(case)
+
+
+def test_static_scratch_reports_a_block_id_outside_the_cache():
+    """The status word of the scratch: 2 after a call whose block table points outside the cache (the tile is replaced
+    by zeros, nothing faults), 0 again after the next clean call."""
+    case = wl.Case("noalloc_bad_block", batch=4, heads=16, kv_heads=4, q_dtype="bf16", ctx=("list", [300, 1000, 64, 129]), seed=44)
+    h = wl.make_host_inputs(case)
+    bad = dict(h, block_tables=h["block_tables"].copy())
+    bad["block_tables"][1, 3] = h["num_blocks"] + 5
+    d_bad = host_inputs_to_device(case, bad)
+    out = torch.zeros((case.batch, case.heads, case.dv), dtype=torch.bfloat16, device="cuda")
+    assert _static_scratch_call(case, bad, d_bad, out) == 0
+    assert _scratch_status() == 2
+    assert torch.isfinite(out.float()).all()
+    d = host_inputs_to_device(case, h)
+    assert _static_scratch_call(case, h, d, out) == 0
+    assert _scratch_status() == 0
+    assert max_abs_err(wl.torch_to_host(out, "bf16"), oracle_out(case, h), "bf16") <= tol_for(case)
+    assert capi.lib().atb_b200_pa_static_scratch_status(capi.torch_stream_ptr(), None) == capi.ERROR_INVALID_PARAM
 
 
 def test_static_scratch_refuses_a_stream_under_capture():
