@@ -257,6 +257,13 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
                 qf[ks][1] = Elem<__half>::pack2(f[2], f[3]);
             }
         }
+        if (!kQ8 && it + 1 < item_end && warp == 0 && c == 0 && g < group) {
+            // the next range's query row of this head: on its way into L2 while this range streams
+            const char *nq = reinterpret_cast<const char *>(q) + ((int64_t)a.plan.items[it + 1].seq * a.num_heads + head0 + g) * 128 * (int64_t)sizeof(*q);
+            for (int b = 0; b < 128 * (int)sizeof(*q); b += 128) {
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(nq + b));
+            }
+        }
         float o[8][4];
 #pragma unroll
         for (int mt = 0; mt < 8; ++mt) {
@@ -621,26 +628,47 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
                     const int h = head0 + hl;
                     const int pbase = a.plan.seq_part_base[item.seq];
                     const float *lse = a.plan.part_lse + (int64_t)pbase * a.num_heads + h;
+                    // the partials come from L2: loads in batches of independent requests, or their latencies add up
+                    const float *po = a.plan.part_o + ((int64_t)pbase * a.num_heads + h) * 128 + d0;
+                    const int64_t lstride = a.num_heads, ostride = (int64_t)a.num_heads * 128;
                     float mx = -INFINITY;
-                    for (int i = 0; i < n_parts; ++i) {
-                        mx = fmaxf(mx, __ldcg(lse + (int64_t)i * a.num_heads));
+                    for (int i0 = 0; i0 < n_parts; i0 += 8) {
+                        float v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            v[j] = i0 + j < n_parts ? __ldcg(lse + (i0 + j) * lstride) : -INFINITY;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            mx = fmaxf(mx, v[j]);
+                        }
                     }
                     float wsum = 0.f;
                     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                    const float *po = a.plan.part_o + ((int64_t)pbase * a.num_heads + h) * 128 + d0;
-                    for (int i = 0; i < n_parts; ++i) {
-                        const float w = exp2f(__ldcg(lse + (int64_t)i * a.num_heads) - mx);
-                        wsum += w;
-                        const float4 pa = __ldcg(reinterpret_cast<const float4 *>(po + (int64_t)i * a.num_heads * 128));
-                        const float4 pb = __ldcg(reinterpret_cast<const float4 *>(po + (int64_t)i * a.num_heads * 128 + 4));
-                        acc[0] = fmaf(w, pa.x, acc[0]);
-                        acc[1] = fmaf(w, pa.y, acc[1]);
-                        acc[2] = fmaf(w, pa.z, acc[2]);
-                        acc[3] = fmaf(w, pa.w, acc[3]);
-                        acc[4] = fmaf(w, pb.x, acc[4]);
-                        acc[5] = fmaf(w, pb.y, acc[5]);
-                        acc[6] = fmaf(w, pb.z, acc[6]);
-                        acc[7] = fmaf(w, pb.w, acc[7]);
+                    for (int i0 = 0; i0 < n_parts; i0 += 4) {
+                        float w[4];
+                        float4 pa[4], pb[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const bool in = i0 + j < n_parts;
+                            const int i = in ? i0 + j : i0;
+                            w[j] = __ldcg(lse + i * lstride);
+                            pa[j] = __ldcg(reinterpret_cast<const float4 *>(po + i * ostride));
+                            pb[j] = __ldcg(reinterpret_cast<const float4 *>(po + i * ostride + 4));
+                            w[j] = in ? exp2f(w[j] - mx) : 0.f;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            wsum += w[j];
+                            acc[0] = fmaf(w[j], pa[j].x, acc[0]);
+                            acc[1] = fmaf(w[j], pa[j].y, acc[1]);
+                            acc[2] = fmaf(w[j], pa[j].z, acc[2]);
+                            acc[3] = fmaf(w[j], pa[j].w, acc[3]);
+                            acc[4] = fmaf(w[j], pb[j].x, acc[4]);
+                            acc[5] = fmaf(w[j], pb[j].y, acc[5]);
+                            acc[6] = fmaf(w[j], pb[j].z, acc[6]);
+                            acc[7] = fmaf(w[j], pb[j].w, acc[7]);
+                        }
                     }
                     const float inv = 1.f / wsum;
                     uint4 pk;
