@@ -6,6 +6,8 @@
 #include <new>
 #include <cuda_runtime.h>
 #include <nvtx3/nvToolsExt.h>
+#include <sys/stat.h>
+#include <vector>
 
 namespace atb {
 
@@ -296,6 +298,60 @@ struct TraceRange {
 // ATB_STREAM_SYNC_EVERY_OPERATION_ENABLE=1, as in the reference (src/atb/utils/config.cpp:36,
 // src/atb/operation/operation_base.cpp:1059-1062): wait for the execute stream after every Execute, so that a device
 // failure is reported by the operation that caused it.  Read at every call: a test can switch it.
+// ATB_SAVE_TENSOR_DIR=<dir>: every Execute writes its input and output tensors before and after the launch, for parity
+// triage, as the reference's Probe hooks do (src/atb/runner/runner.cpp:102-135, store_util.cpp:57-73):
+//   <dir>/<execute count>_<operation name>/{before,after}/{intensor,outtensor}<i>.bin
+// A file is one text line "dtype=<aclDataType> format=<aclFormat> dims=<d0,d1,..> bytes=<n>" and then the n raw bytes.
+// The stream is synchronised around the launch while this is on.
+void MakeDirs(const std::string &path)
+{
+    for (size_t i = 1; i <= path.size(); ++i) {
+        if (i == path.size() || path[i] == '/') {
+            ::mkdir(path.substr(0, i).c_str(), 0755);
+        }
+    }
+}
+
+void SaveTensors(const SVector<Tensor> &tensors, const std::string &dir, const char *stem)
+{
+    std::vector<unsigned char> host;
+    for (size_t i = 0; i < tensors.size(); ++i) {
+        const Tensor &t = tensors.at(i);
+        const unsigned char *src = static_cast<const unsigned char *>(t.hostData);
+        if (t.deviceData != nullptr) {
+            host.resize(t.dataSize);
+            if (cudaMemcpy(host.data(), t.deviceData, t.dataSize, cudaMemcpyDeviceToHost) != cudaSuccess) {
+                cudaGetLastError();
+                continue;
+            }
+            src = host.data();
+        }
+        if (src == nullptr) {
+            continue;
+        }
+        FILE *f = std::fopen((dir + "/" + stem + std::to_string(i) + ".bin").c_str(), "wb");
+        if (f == nullptr) {
+            continue;
+        }
+        std::string dims;
+        for (uint64_t k = 0; k < t.desc.shape.dimNum; ++k) {
+            dims += (k ? "," : "") + std::to_string(t.desc.shape.dims[k]);
+        }
+        std::fprintf(f, "dtype=%d format=%d dims=%s bytes=%llu\n", static_cast<int>(t.desc.dtype), static_cast<int>(t.desc.format),
+                     dims.c_str(), static_cast<unsigned long long>(t.dataSize));
+        std::fwrite(src, 1, t.dataSize, f);
+        std::fclose(f);
+    }
+}
+
+void SaveVariantPack(const VariantPack &pack, cudaStream_t stream, const std::string &dir)
+{
+    cudaStreamSynchronize(stream);
+    MakeDirs(dir);
+    SaveTensors(pack.inTensors, dir, "intensor");
+    SaveTensors(pack.outTensors, dir, "outtensor");
+}
+
 bool StreamSyncEveryOperation()
 {
     const char *e = std::getenv("ATB_STREAM_SYNC_EVERY_OPERATION_ENABLE");
@@ -382,7 +438,17 @@ Status OperationBase::Execute(const VariantPack &variantPack, uint8_t *workspace
                 return ERROR_INVALID_PARAM;
             }
         }
+        const char *dumpDir = std::getenv("ATB_SAVE_TENSOR_DIR");
+        std::string dumpBase;
+        if (dumpDir != nullptr && dumpDir[0] != '\0') {
+            dumpBase = std::string(dumpDir) + "/" + std::to_string(executeCount_) + "_" + name_;
+            SaveVariantPack(variantPack, static_cast<cudaStream_t>(stream), dumpBase + "/before");
+        }
         const Status st = LaunchImpl(variantPack, workspace, workspaceSize, stream);
+        ++executeCount_;
+        if (!dumpBase.empty()) {
+            SaveVariantPack(variantPack, static_cast<cudaStream_t>(stream), dumpBase + "/after");
+        }
         if (StreamSyncEveryOperation()) {
             const cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
             if (e != cudaSuccess) {

@@ -82,6 +82,7 @@ private:
     std::atomic<bool> setupSuccess_{false};
     Context *context_ = nullptr;
     uint64_t workspaceSize_ = 0;
+    uint64_t executeCount_ = 0;   // names the tensor-dump directories (ATB_SAVE_TENSOR_DIR)
     std::vector<TensorDesc> setupInDescs_, setupOutDescs_;
 };
 

@@ -226,3 +226,48 @@ def test_stream_sync_every_operation(monkeypatch):
     op.execute(ins, outs, ws.data_ptr(), ws_bytes, ctx)
     torch.cuda.synchronize()
     assert max_abs_err(wl.torch_to_host(out, case.q_dtype), oracle_out(case, h), case.q_dtype) <= tol_for(case)
+
+
+def test_tensor_dump_before_and_after_execute(monkeypatch, tmp_path):
+    """ATB_SAVE_TENSOR_DIR: every Execute writes its tensors before and after the launch (the reference's Probe hooks,
+    src/atb/runner/runner.cpp:102-135): intensor<i>.bin / outtensor<i>.bin, one text header line and the raw bytes."""
+    case = wl.CONFIGS[0]
+    h = wl.make_host_inputs(case)
+    d = host_inputs_to_device(case, h)
+    T = capi.atb_tensor
+    nk, nv = to_dev(h["new_k"], case.kvd), to_dev(h["new_v"], case.kvd)
+    slots = torch.from_numpy(h["slot_mapping"]).cuda()
+    rac = capi.Operation(capi.ReshapeAndCacheParam())
+    ctx = _new_ctx()
+    ins = [T(nk), T(nv), T(d["k_cache"]), T(d["v_cache"]), T(slots)]
+    outs = [T(d["k_cache"]), T(d["v_cache"])]
+    k_before = wl.torch_to_host(d["k_cache"], case.kvd).copy()
+    monkeypatch.setenv("ATB_SAVE_TENSOR_DIR", str(tmp_path))
+    assert rac.setup(ins, outs, ctx) == 0
+    rac.execute(ins, outs, None, 0, ctx)
+    monkeypatch.delenv("ATB_SAVE_TENSOR_DIR")
+    torch.cuda.synchronize()
+    dirs = sorted(p.name for p in tmp_path.iterdir())
+    assert len(dirs) == 1 and dirs[0].startswith("0_") and "ReshapeAndCache" in dirs[0]
+
+    def load(path):
+        raw = path.read_bytes()
+        head, body = raw.split(b"\n", 1)
+        f = dict(kv.split("=") for kv in head.decode().split())
+        assert int(f["bytes"]) == len(body)
+        return f, body
+
+    base = tmp_path / dirs[0]
+    assert sorted(p.name for p in (base / "before").iterdir()) == ["intensor0.bin", "intensor1.bin", "intensor2.bin", "intensor3.bin",
+                                                                    "intensor4.bin", "outtensor0.bin", "outtensor1.bin"]
+    f, body = load(base / "before" / "intensor0.bin")
+    assert f["dims"] == ",".join(str(x) for x in h["new_k"].shape) and int(f["dtype"]) == capi.ACL_FLOAT16
+    assert body == h["new_k"].tobytes()
+    _, cache_before = load(base / "before" / "outtensor0.bin")
+    _, cache_after = load(base / "after" / "outtensor0.bin")
+    assert cache_before == k_before.tobytes()
+    kc, vc = h["k_cache"].copy(), h["v_cache"].copy()
+    oracle.reshape_and_cache(h["new_k"], h["new_v"], kc, vc, h["slot_mapping"])
+    assert cache_after == kc.tobytes() and cache_after != cache_before
+    _, slots_bytes = load(base / "after" / "intensor4.bin")
+    assert slots_bytes == h["slot_mapping"].tobytes()
