@@ -786,11 +786,11 @@ def run_e2e_pipelined(args, case, rt, d, lens, steps, chunks, check_out):
     d2h = out_host.numel() * out_host.element_size()
 
     def step():
+        # sub-batch by sub-batch: the first one's kernels are submitted before the others' copies are even queued
         for p in parts:
             with torch.cuda.stream(s_h2d):
                 p["dev_pack"].copy_(p["host_pack"], non_blocking=True)
                 p["ev_in"].record(s_h2d)
-        for p in parts:
             s_run.wait_event(p["ev_in"])
             rc = L.atb_b200_operation_setup(p["rac"].handle, p["rac_i"], p["n_ri"], p["rac_o"], p["n_ro"], ctypes.byref(need), ctx.handle)
             rc |= L.atb_b200_operation_setup(p["pa"].handle, p["pa_i"], p["n_pi"], p["pa_o"], p["n_po"], ctypes.byref(need), ctx.handle)
