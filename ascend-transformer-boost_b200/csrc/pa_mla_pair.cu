@@ -25,7 +25,9 @@
 // exponent at +100: bf16 has the exponent range of fp32, so P keeps its relative precision wherever the reference
 // lies, the first token contributes exactly 1 to the row sum (never 0), and a score more than 2^100 times above the
 // reference - which no softmax input reaches - would only be weighted as 2^100.  No rescaling of O, no cross-thread
-// reduction per tile; row sums are kept per thread and added up once per range.
+// reduction per tile; row sums are kept per thread and added up once per range.  They add up P as rounded to bf16, the
+// values P.V multiplies with: the weights of a row then sum to one exactly, and the rounding of a dominant P (which,
+// unlike with a running maximum, is not 1.0 here) cancels between numerator and denominator.
 //
 // Tensor memory (512 columns): Q 0..127 (256 dims as bf16 pairs), S 128..255 (P over its first 64), O 256..511.  S has
 // one buffer: per tile the MMA thread issues Q.K^T, waits for P, issues P.V and goes on to the next tile's Q.K^T, which
@@ -602,8 +604,9 @@ pa_mla_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
                             for (int k = 0; k < 8; ++k) {
                                 const float p0 = fast_exp2(fminf(fmaf(s[2 * k], a.scale_log2, -mref), kMaxExponent));
                                 const float p1 = fast_exp2(fminf(fmaf(s[2 * k + 1], a.scale_log2, -mref), kMaxExponent));
-                                lsum += p0 + p1;
                                 pk[8 * c + k] = Elem<T>::pack2(p0, p1);
+                                const float2 pr = Elem<T>::unpack2(pk[8 * c + k]);   // the row sum of P as P.V sees it
+                                lsum += pr.x + pr.y;
                             }
                         } else {
                             // the ragged end of a range: tokens past it get probability 0 whatever their scores are
@@ -617,8 +620,9 @@ pa_mla_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
                                 if (tok_first + 16 * c + 2 * k + 1 >= valid) {
                                     p1 = 0.f;
                                 }
-                                lsum += p0 + p1;
                                 pk[8 * c + k] = Elem<T>::pack2(p0, p1);
+                                const float2 pr = Elem<T>::unpack2(pk[8 * c + k]);
+                                lsum += pr.x + pr.y;
                             }
                         }
                         if (c == 0) {
