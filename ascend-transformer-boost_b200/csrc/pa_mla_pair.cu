@@ -66,6 +66,11 @@ constexpr int kBigBytes = kStages * kStageBytes + kQRopeBytes + kRecvSBytes + kR
 constexpr int kSmallBytes = 6144;              // barriers, tmem slot, flags, reference scores, row-sum scratch
 constexpr int kSmemBytes = kBigBytes + kSmallBytes + 1024;
 constexpr int kSoftmaxWarps = 16;
+constexpr int kParts = 2;                      // a tile's tokens go through Q.K^T, softmax and P.V in this many parts, each
+                                               // with its own S / P columns and barriers, pipelined against one another
+constexpr int kPartTok = kTile / kParts;       // tokens per part = N of a Q.K^T MMA
+constexpr int kCgPerPart = 4 / kParts;         // a warp holds 32 tokens of a tile: warps (per lane quarter) per part
+static_assert(kParts == 2 || kParts == 4, "a part is one or two warps' tokens");
 constexpr int kThreads = (kSoftmaxWarps + 2) * 32;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kQCol = 0, kSCol = 128, kOCol = 256;
@@ -74,9 +79,11 @@ static_assert(kStageBytes % 1024 == 0 && (kFullAtoms * kAtomBytes) % 1024 == 0 &
               "swizzle atoms stay aligned");
 
 enum Bar {
-    kQFull = 0, kQTmem, kQEmpty, kStEmpty0, kStEmpty1, kSFull0, kSFull1, kPFull0, kPFull1, kPvDone, kWsum, kLinv, kOFree,
-    kQuadS0,                                   // 8: the two warps of a lane quarter and tile half have read their part of S
-    kQuadM0 = kQuadS0 + 8,                     // 4: the reference scores of a quarter's heads are in shared memory
+    kQFull = 0, kQTmem, kQEmpty, kStEmpty0, kStEmpty1, kPvDone, kWsum, kLinv, kOFree,
+    kSFull0,                                   // per part: its S is complete
+    kPFull0 = kSFull0 + kParts,                // per part: P of all 128 heads is in tensor memory
+    kQuadS0 = kPFull0 + kParts,                // per lane quarter and part: its warps have read their S
+    kQuadM0 = kQuadS0 + 4 * kParts,            // 4: the reference scores of a quarter's heads are in shared memory
     kStFull0 = kQuadM0 + 4,                    // one per stage and atom (the rope half last): kStFull0 + 5 s + k
     kXSFull0 = kStFull0 + 2 * (kFullAtoms + 1), // per warp and 16 tokens (kXSFull0 + 16 c + w): partial scores from the peer's
                                                // warp of the same number have landed
@@ -154,16 +161,16 @@ pa_mla_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
             }
             mbar_init(&bars[kStEmpty0 + s], 1);
         }
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < kParts; ++h) {
             mbar_init(&bars[kSFull0 + h], 1);
-            mbar_init(&bars[kPFull0 + h], kSoftmaxWarps / 2);
+            mbar_init(&bars[kPFull0 + h], kSoftmaxWarps / kParts);
         }
         mbar_init(&bars[kPvDone], 1);
         mbar_init(&bars[kWsum], kSoftmaxWarps / 2);
         mbar_init(&bars[kLinv], 4);               // two warps here, two in the peer
         mbar_init(&bars[kOFree], kSoftmaxWarps);
-        for (int k = 0; k < 8; ++k) {
-            mbar_init(&bars[kQuadS0 + k], 2);
+        for (int k = 0; k < 4 * kParts; ++k) {
+            mbar_init(&bars[kQuadS0 + k], kCgPerPart);
         }
         for (int k = 0; k < 4; ++k) {
             mbar_init(&bars[kQuadM0 + k], 1);
@@ -315,7 +322,7 @@ pa_mla_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
     } else if (warp == kSoftmaxWarps + 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc_qk = instr_desc_ab(1, 0, 0, kTile / 2, kHeads); // B = half a K tile, K-major, N = 64 tokens
+            constexpr uint32_t idesc_qk = instr_desc_ab(1, 0, 0, kPartTok, kHeads);  // B = a part of a K tile, K-major
             constexpr uint32_t idesc_pv = instr_desc_ab(1, 0, 1, 256, kHeads);    // B = V, MN-major, N = 256 dims
             const uint32_t st_addr = smem_u32(st_smem);
             const uint64_t dqr = smem_desc_sw64(smem_u32(qr_smem), 16, 512);
@@ -327,20 +334,20 @@ pa_mla_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
                 if (!wait(kQFull, i & 1, false) || !wait(kQTmem, i & 1, false)) {
                     break;
                 }
-                // S = Q . K^T of one half (64 tokens) of tile gg.  Each half of S has one buffer: the softmax warps are done
-                // with the previous tile's (they have delivered its P), and P.V of that half runs before this in issue order
+                // S = Q . K^T of one part of tile gg.  Each part of S has one buffer: the softmax warps are done with the
+                // previous tile's (they have delivered its P), and P.V of that part runs before this in issue order
                 auto qk = [&](uint32_t gg, int h, bool last) -> bool {
                     const int stg = gg & 1;
                     const uint32_t ph = (gg >> 1) & 1;
-                    const uint32_t kb = st_addr + stg * kStageBytes + h * 64 * 128;   // rows 64h.. of every atom
+                    const uint32_t kb = st_addr + stg * kStageBytes + h * kPartTok * 128;   // the part's rows of every atom
                     const uint64_t db0 = smem_desc(kb, 16, 1024);
-                    const uint32_t ds = tmem_base + kSCol + 64 * h;
+                    const uint32_t ds = tmem_base + kSCol + kPartTok * h;
                     if (h == 0) {
                         mark(gg, 2);
                     }
 #pragma unroll
                     for (int at = 0; at <= kFullAtoms; ++at) {
-                        // atom by atom as the atoms land (the second half finds them there)
+                        // atom by atom as the atoms land (the later parts find them there)
                         if (h == 0 && !wait(kStFull0 + 5 * stg + at, ph, false)) {
                             return false;
                         }
@@ -354,7 +361,7 @@ pa_mla_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
                             }
                         } else {
                             // the 32 rope dims, both operands from shared memory: rows of 64 bytes, 64-byte swizzle
-                            const uint64_t dkr = smem_desc_sw64(st_addr + stg * kStageBytes + kFullAtoms * kAtomBytes + h * 64 * 64, 16, 512);
+                            const uint64_t dkr = smem_desc_sw64(st_addr + stg * kStageBytes + kFullAtoms * kAtomBytes + h * kPartTok * 64, 16, 512);
 #pragma unroll
                             for (int ks = 0; ks < 2; ++ks) {
                                 tc_mma(ds, dqr + ((ks * 32) >> 4), dkr + ((ks * 32) >> 4), idesc_qk, true);
@@ -365,15 +372,15 @@ pa_mla_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
                     if (h == 0) {
                         mark(gg, 1);   // (overwrites the producer's mark) first half issued
                     }
-                    if (last && h == 1) {
+                    if (last && h == kParts - 1) {
                         tc_commit(&bars[kQEmpty]); // the query block of this range is no longer needed
                     }
-                    if (h == 1) {
+                    if (h == kParts - 1) {
                         mark(gg, 3);
                     }
                     return true;
                 };
-                // O += P . V of one half, once P of all 128 heads for its 64 tokens is in tensor memory
+                // O += P . V of one part, once P of all 128 heads for its tokens is in tensor memory
                 auto pv = [&](uint32_t gg, int h, bool first) -> bool {
                     if (!wait(kPFull0 + h, gg & 1, false)) {
                         return false;
@@ -388,23 +395,29 @@ pa_mla_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
                     tc_fence_after();
                     const int stg = gg & 1;
                     // V: 64-dim atoms kAtomBytes apart along N, 8-token groups 1024 B apart; 16 tokens of P = 8 TMEM columns
-                    const uint64_t dv0 = smem_desc(st_addr + stg * kStageBytes + h * 64 * 128, kAtomBytes, 1024);
+                    const uint64_t dv0 = smem_desc(st_addr + stg * kStageBytes + h * kPartTok * 128, kAtomBytes, 1024);
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        tc_mma_ts(tmem_base + kOCol, tmem_base + kSCol + 64 * h + ks * 8, dv0 + ((ks * 2048) >> 4), idesc_pv,
+                    for (int ks = 0; ks < kPartTok / 16; ++ks) {
+                        tc_mma_ts(tmem_base + kOCol, tmem_base + kSCol + kPartTok * h + ks * 8, dv0 + ((ks * 2048) >> 4), idesc_pv,
                                   !(first && h == 0) || ks != 0);
                     }
-                    if (h == 1) {
+                    if (h == kParts - 1) {
                         tc_commit(&bars[kStEmpty0 + stg]);
                         tc_commit(&bars[kPvDone]);
                         mark(gg, 7);
                     }
                     return true;
                 };
-                alive = qk(g, 0, n_tiles == 1) && qk(g, 1, n_tiles == 1);
+#pragma unroll
+                for (int h = 0; h < kParts; ++h) {
+                    alive = alive && qk(g, h, n_tiles == 1);
+                }
                 for (int t = 0; t < n_tiles && alive; ++t, ++g) {
                     const bool more = t + 1 < n_tiles, last = t + 2 == n_tiles;
-                    alive = pv(g, 0, t == 0) && (!more || qk(g + 1, 0, last)) && pv(g, 1, t == 0) && (!more || qk(g + 1, 1, last));
+#pragma unroll
+                    for (int h = 0; h < kParts; ++h) {
+                        alive = alive && pv(g, h, t == 0) && (!more || qk(g + 1, h, last));
+                    }
                 }
                 if (!alive) {
                     *abort_flag = 1;
@@ -416,7 +429,7 @@ pa_mla_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
         // tile's tokens per thread
         const int q4 = warp & 3;                                       // TMEM lane quarter this warp may access
         const int cg = warp >> 2;                                      // which 32 tokens of a tile
-        const int hf = cg >> 1;                                        // which half of the tile: it has its own S, P and barriers
+        const int part = cg / kCgPerPart;                              // which part of the tile: it has its own S, P and barriers
         const int head = q4 * 32 + lane;                               // row of S, P and O
         const bool own = (uint32_t)(q4 >> 1) == rank;                  // this CTA computes the softmax of this quarter's heads
         const int hidx = (q4 & 1) * 32 + lane;                         // index among the 64 heads of their owner
@@ -481,7 +494,7 @@ pa_mla_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
             float *mref_s = sm->mref[i & 1];
             for (int t = 0; t < n_tiles && alive; ++t, ++g) {
                 const int valid = min(kTile, item.tok_end - (item.tok_begin + t * kTile));
-                if (!wait(kSFull0 + hf, g & 1, false)) {
+                if (!wait(kSFull0 + part, g & 1, false)) {
                     alive = false;
                     break;
                 }
@@ -497,17 +510,17 @@ pa_mla_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
                 }
                 tc_fence_before();
                 __syncwarp();
-                // P goes over S: nothing of it may be written before both warps of this quarter and half have read their parts
+                // P goes over S: nothing of it may be written before the warps of this quarter and part have read their S
                 if (lane == 0) {
-                    mbar_arrive(&bars[kQuadS0 + 2 * q4 + hf]);
+                    mbar_arrive(&bars[kQuadS0 + kParts * q4 + part]);
                 }
                 // rows of V past the end of the range may hold anything: clear them (0 * NaN != 0); the K rows only feed the
                 // scores of those tokens, which get probability 0 below
                 if (valid < kTile) {
                     uint8_t *stg = st_smem + (g & 1) * kStageBytes;
-                    // the 256 threads of this half: its 64 rows of the four atoms
-                    const int idx = ((cg & 1) * 4 + q4) * 32 + lane;
-                    const int row = 64 * hf + (idx & 63), at = idx >> 6;
+                    // the threads of this part: its rows of the four atoms
+                    const int idx = ((cg % kCgPerPart) * 4 + q4) * 32 + lane;
+                    const int row = kPartTok * part + (idx % kPartTok), at = idx / kPartTok;
                     if (row >= valid) {
 #pragma unroll
                         for (int ch = 0; ch < 8; ++ch) {
@@ -653,7 +666,7 @@ pa_mla_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
                     }
                 }
                 // ---- P into this thread's lane of tensor memory, over the first half of S
-                if (!wait(kQuadS0 + 2 * q4 + hf, g & 1, false)) {
+                if (!wait(kQuadS0 + kParts * q4 + part, g & 1, false)) {
                     alive = false;
                     break;
                 }
@@ -661,12 +674,12 @@ pa_mla_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
                     mark(g, 12);
                 }
                 tc_fence_after();
-                tmem_st16(tmem_base + lane_base + kSCol + 64 * hf + 16 * (cg & 1), pk);
+                tmem_st16(tmem_base + lane_base + kSCol + kPartTok * part + 16 * (cg % kCgPerPart), pk);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(&bars[kPFull0 + hf]);
+                    mbar_arrive(&bars[kPFull0 + part]);
                     if (!own) {
                         mbar_arrive_cluster_relaxed(peer_bar(kXPEmpty0 + warp));   // the received P has been read
                     }
