@@ -334,7 +334,7 @@ def measure_decode(args, case, rt, steps, with_cpu_baseline):
         ms, kernel_ms = float(t[0]), float(t[1])
 
     # ---- end to end through the operator API with host buffers (rank-local shard, same step)
-    chunks = e2e_chunks(wl, shard, lens, world, args.e2e_chunks)
+    chunks = e2e_chunks(shard, lens, world, ms, args.e2e_chunks)
     if len(chunks) > 1:
         e2e = run_e2e_pipelined(args, shard, rt, d, lens, steps, chunks, out)
     else:
@@ -446,7 +446,7 @@ def main():
     ap.add_argument("--only", action="store_true", help="measure the chosen configuration alone (no `configs` array)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-chunks", type=int, default=0,
-                    help="sub-batches of the pipelined end-to-end step on one GPU (0: chosen from the cache size; 1: no pipelining)")
+                    help="sub-batches of the pipelined end-to-end step on one GPU (0: chosen from the step's copy and kernel times; 1: no pipelining)")
     ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
                     help="N>1: attention stores into every rank's gathered buffer (p2p) or a separate NCCL all-gather")
     ap.add_argument("--variant", default="plain", choices=["plain", "alibi", "mtp2", "mtp2_rows"],
@@ -702,16 +702,23 @@ def run_cache_op_bench(args, capi):
                                    "peak_kind": "of " + peak_kind, "kernel": args.op, "kernel_ms": ms, "traffic": None}}))
 
 
-E2E_CHUNK_BYTES = 600e6   # a sub-batch of the pipelined end-to-end step reads at least this much cache
+PCIE_GBS = 50.0   # what a pinned copy reaches on these hosts, for choosing the sub-batches of the end-to-end step only
 
 
-def e2e_chunks(wl, case, lens, world, forced=0):
+def e2e_chunks(case, lens, world, step_ms, forced=0):
     """Sub-batches of the end-to-end step on one GPU: contiguous slices of the batch with about equal context tokens
-    (equal kernel time), at most four, none smaller than E2E_CHUNK_BYTES of cache (smaller kernels lose more than the
-    overlap gains).  [(b0, b1)]; one slice = the whole batch = no pipelining."""
-    n = 1 if world > 1 else int(max(1, min(4, wl.kv_bytes(case, lens) // E2E_CHUNK_BYTES)))
+    (equal kernel time).  Pipelining pays where the step's copies (query and new tokens in, output back) are a good part
+    of its kernel time: two sub-batches then, four for steps above 300 us (smaller kernels lose more than the overlap
+    gains).  [(b0, b1)]; one slice = the whole batch = no pipelining."""
+    esz = 2
+    io_bytes = case.batch * case.heads * (case.dk + case.dv) * esz          # queries in, outputs back
+    copy_us = io_bytes / (PCIE_GBS * 1e3)
+    n = 1
+    if world == 1 and copy_us >= 0.25 * step_ms * 1e3:
+        n = 4 if step_ms > 0.3 else 2
     if forced > 0 and world == 1:
-        n = min(forced, case.batch)
+        n = forced
+    n = max(1, min(n, case.batch // 2))
     csum = np.concatenate([[0], np.cumsum(np.asarray(lens, dtype=np.int64))])
     cuts = [0]
     for j in range(1, n):
@@ -808,11 +815,23 @@ def run_e2e_pipelined(args, case, rt, d, lens, steps, chunks, check_out):
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        step()
-    torch.cuda.synchronize()
-    ms = (time.perf_counter() - t0) * 1e3 / steps
+    if wl.kv_bytes(case, lens) < 2 * L2_BYTES:
+        # the cache is not well above the L2: flush it before every step, outside the step's clock (as run_e2e does)
+        flush = L2Flusher(dev)
+        total = 0.0
+        for _ in range(steps):
+            flush()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            step()
+            total += time.perf_counter() - t0
+        ms = total * 1e3 / steps
+    else:
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step()
+        torch.cuda.synchronize()
+        ms = (time.perf_counter() - t0) * 1e3 / steps
     diff = float((out_host.float() - check_out.detach().cpu().float()).abs().max())
     if not diff <= TOLERANCE[case.q_dtype if case.kvd != "int8" else "int8"]:
         raise RuntimeError(f"pipelined end-to-end output differs from the kernel-level path by {diff}")
