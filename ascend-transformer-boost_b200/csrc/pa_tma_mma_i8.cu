@@ -34,6 +34,7 @@
 #include <mutex>
 #include "common.cuh"
 #include "kernels.h"
+#include "pa_merge.cuh"
 #include "tma_encode.h"
 #include "pa_exchange.cuh"
 
@@ -627,55 +628,7 @@ pa_tma_mma_i8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
                 if (hl < group) {
                     const int h = head0 + hl;
                     const int pbase = a.plan.seq_part_base[item.seq];
-                    const float *lse = a.plan.part_lse + (int64_t)pbase * a.num_heads + h;
-                    // the partials come from L2: loads in batches of independent requests, or their latencies add up
-                    const float *po = a.plan.part_o + ((int64_t)pbase * a.num_heads + h) * 128 + d0;
-                    const int64_t lstride = a.num_heads, ostride = (int64_t)a.num_heads * 128;
-                    float mx = -INFINITY;
-                    for (int i0 = 0; i0 < n_parts; i0 += 8) {
-                        float v[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            v[j] = i0 + j < n_parts ? __ldcg(lse + (i0 + j) * lstride) : -INFINITY;
-                        }
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            mx = fmaxf(mx, v[j]);
-                        }
-                    }
-                    float wsum = 0.f;
-                    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                    for (int i0 = 0; i0 < n_parts; i0 += 4) {
-                        float w[4];
-                        float4 pa[4], pb[4];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const bool in = i0 + j < n_parts;
-                            const int i = in ? i0 + j : i0;
-                            w[j] = __ldcg(lse + i * lstride);
-                            pa[j] = __ldcg(reinterpret_cast<const float4 *>(po + i * ostride));
-                            pb[j] = __ldcg(reinterpret_cast<const float4 *>(po + i * ostride + 4));
-                            w[j] = in ? exp2f(w[j] - mx) : 0.f;
-                        }
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            wsum += w[j];
-                            acc[0] = fmaf(w[j], pa[j].x, acc[0]);
-                            acc[1] = fmaf(w[j], pa[j].y, acc[1]);
-                            acc[2] = fmaf(w[j], pa[j].z, acc[2]);
-                            acc[3] = fmaf(w[j], pa[j].w, acc[3]);
-                            acc[4] = fmaf(w[j], pb[j].x, acc[4]);
-                            acc[5] = fmaf(w[j], pb[j].y, acc[5]);
-                            acc[6] = fmaf(w[j], pb[j].z, acc[6]);
-                            acc[7] = fmaf(w[j], pb[j].w, acc[7]);
-                        }
-                    }
-                    const float inv = 1.f / wsum;
-                    uint4 pk;
-                    pk.x = Elem<T>::pack2(acc[0] * inv, acc[1] * inv);
-                    pk.y = Elem<T>::pack2(acc[2] * inv, acc[3] * inv);
-                    pk.z = Elem<T>::pack2(acc[4] * inv, acc[5] * inv);
-                    pk.w = Elem<T>::pack2(acc[6] * inv, acc[7] * inv);
+                    const uint4 pk = merge_partials8<T>(a, pbase, h, d0, 128, n_parts);
                     store_out_row<T>(a, item.seq, h, d0, pk);
                 }
             }
