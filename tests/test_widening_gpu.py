@@ -394,12 +394,13 @@ def test_mask_and_logn_match_reference_golden(spec, kernel, monkeypatch):
     assert max_abs_err(got, fx["out"], case.q_dtype) <= tol_for(case)
 
 
+@pytest.mark.parametrize("dim", [128, 96], ids=["d128", "d96_padded"])
 @pytest.mark.parametrize("dtype", ["fp16", "bf16"])
-def test_shared_alibi_rows_split_sequences_and_masked_out_prefix(dtype):
+def test_shared_alibi_rows_split_sequences_and_masked_out_prefix(dtype, dim):
     """Long sequences (split over several CTAs and merged), the alibi mask given once for all sequences
     ([heads, 1, tokens]), logN factors, and - in a second run - a norm mask that removes a whole prefix with -inf,
     longer than one CTA's first tile, which must neither produce NaN nor let the removed tokens through."""
-    case = wl.Case(f"feat_long_{dtype}", batch=5, heads=16, kv_heads=4, q_dtype=dtype,
+    case = wl.Case(f"feat_long_{dtype}_{dim}", batch=5, heads=16, kv_heads=4, dk=dim, dv=dim, q_dtype=dtype,
                    ctx=("list", [4000, 37, 2100, 640, 1]), seed=77)
     h = wl.make_host_inputs(case)
     lens = h["context_lens"]
@@ -671,13 +672,14 @@ def test_mla_combined_cache_with_norm_mask():
 # ------------------------------------------------------------------ parallel decoding planned per sequence (uniform q_len)
 
 @pytest.mark.parametrize("mask_kind", ["spec", "norm"])
-@pytest.mark.parametrize("heads,kv_heads,q_len,dtype", [(8, 2, 2, "bf16"), (8, 4, 4, "fp16"), (4, 4, 3, "fp16"), (16, 2, 1, "bf16")])
-def test_parallel_decoding_same_token_count_per_sequence(heads, kv_heads, q_len, dtype, mask_kind, monkeypatch):
+@pytest.mark.parametrize("heads,kv_heads,q_len,dtype,dim", [(8, 2, 2, "bf16", 128), (8, 4, 4, "fp16", 128), (4, 4, 3, "fp16", 128),
+                                                            (16, 2, 1, "bf16", 128), (8, 2, 2, "bf16", 80), (4, 4, 3, "fp16", 192)])
+def test_parallel_decoding_same_token_count_per_sequence(heads, kv_heads, q_len, dtype, dim, mask_kind, monkeypatch):
     """Every sequence has q_len query tokens: the operator plans one row per sequence whose CTA columns are the (token,
     head) pairs (the cache is read once) when q_len x heads-per-kv-head <= 8, else one row per token.  Both must give
     the oracle's result, and the per-sequence form the same as the per-token form (forced through the environment)."""
-    case = wl.Case(f"mtp_{heads}_{kv_heads}_{q_len}_{dtype}", batch=5, heads=heads, kv_heads=kv_heads, q_dtype=dtype,
-                   ctx=("list", [3000, 37, 640, 1, 129 if q_len < 4 else 200]), seed=97)
+    case = wl.Case(f"mtp_{heads}_{kv_heads}_{q_len}_{dtype}_{dim}", batch=5, heads=heads, kv_heads=kv_heads, dk=dim, dv=dim,
+                   q_dtype=dtype, ctx=("list", [3000, 37, 640, 1, 129 if q_len < 4 else 200]), seed=97)
     spec = dict(case=case, q_lens=[q_len] * 5, mask=mask_kind)
     d = spec_inputs(spec)
     lens = d["context_lens"].copy()
