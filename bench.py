@@ -402,7 +402,8 @@ def measure_decode(args, case, rt, steps, with_cpu_baseline):
                "gpu_launches": launches_per_step * steps,
                "clocks": clocks,
                "e2e": {"value": kv_bytes_global / (e2e["ms"] * 1e-3) / 1e9, "unit": UNIT,
-                       "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                       # at N > 1: summed over the ranks (every rank copies its shard's inputs in and 1/N of the result out)
+                       "h2d_bytes_per_step": e2e["h2d"] * world, "d2h_bytes_per_step": e2e["d2h"] * world,
                        "ms_per_step": e2e["ms"], "tokens_per_s": case.batch / (e2e["ms"] * 1e-3),
                        "gather": e2e["gather"], **{k: e2e[k] for k in ("pipeline", "max_abs_diff_vs_kernel_level_path") if k in e2e}},
                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT,
@@ -848,7 +849,8 @@ def run_e2e(args, full_case, case, rt, d, lens, gathered, steps, p2p):
     it.  The KV cache itself is the path's resident state and stays in HBM.  The operator calls use
     pre-built tensor records (a C++ caller builds its VariantPack once, too).  `case` is this rank's
     shard of `full_case`; with sharded heads the operator stores into every rank's gathered buffer
-    (atb_b200_context_set_gather) and the step reads the whole gathered output back."""
+    (atb_b200_context_set_gather); the gathered result is read back once by the ranks' hosts between them, rank r taking
+    its r-th contiguous 1/N (d2h_bytes_per_step is this rank's share)."""
     import ctypes
     import torch
     import torch.distributed as dist
@@ -881,7 +883,11 @@ def run_e2e(args, full_case, case, rt, d, lens, gathered, steps, p2p):
         result_shape = tuple(gathered.shape)
     else:
         result_shape = tuple(out.shape)
-    out_host = torch.empty(result_shape, dtype=out.dtype).pin_memory()
+    # Every rank holds the whole gathered result on its GPU; the ranks' hosts read it back once between them: rank r its
+    # r-th contiguous 1/N of the buffer (at N = 1 the whole output)
+    n_result = int(np.prod(result_shape))
+    r0, r1 = rank * n_result // world, (rank + 1) * n_result // world
+    out_host = torch.empty(r1 - r0, dtype=out.dtype).pin_memory()
     ctx = capi.Context(stream.cuda_stream)
     rac_param = capi.ReshapeAndCacheParam()
     rac_param.kvCacheCfg = 1 if case.mla else 0
@@ -932,13 +938,13 @@ def run_e2e(args, full_case, case, rt, d, lens, gathered, steps, p2p):
             raise RuntimeError(f"operator call failed ({rc})")
         if p2p:
             if local_ptr not in gathered_views:
-                gathered_views[local_ptr] = exchange.local_tensor(local_ptr, result_shape, out.dtype)
+                gathered_views[local_ptr] = exchange.local_tensor(local_ptr, result_shape, out.dtype).view(-1)[r0:r1]
             out_host.copy_(gathered_views[local_ptr], non_blocking=True)
         elif world > 1:
             dist.all_gather_into_tensor(gathered_flat, out.view(-1))
-            out_host.copy_(gathered, non_blocking=True)
+            out_host.copy_(gathered_flat[r0:r1], non_blocking=True)
         else:
-            out_host.copy_(out, non_blocking=True)
+            out_host.copy_(out.view(-1), non_blocking=True)
         stream.synchronize()                          # the caller consumes the result every step
 
     torch.cuda.synchronize()
@@ -967,8 +973,8 @@ def run_e2e(args, full_case, case, rt, d, lens, gathered, steps, p2p):
             ms = (time.perf_counter() - t0) * 1e3 / steps
     if exchange is not None:
         exchange.close()
-    how = "single GPU" if world == 1 else ("peer stores from the attention kernel (operator-level gather)" if p2p
-                                           else "NCCL all-gather")
+    how = "single GPU" if world == 1 else (("peer stores from the attention kernel (operator-level gather)" if p2p
+                                            else "NCCL all-gather") + f"; each rank's host reads 1/{world} of the gathered result")
     return {"ms": ms, "h2d": h2d, "d2h": d2h, "gather": how}
 
 
