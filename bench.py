@@ -305,8 +305,13 @@ def measure_decode(args, case, rt, steps, with_cpu_baseline):
         if flush_l2:
             evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
             barrier()
+            align = torch.zeros(1, device=dev) if world > 1 else None
             for a0, a1 in evs:
                 flush()
+                if world > 1:
+                    # the ranks flush on their own clocks: line them up again (a collective on this stream, outside the
+                    # timed region), or a step's wait for its peers would include their flushes
+                    dist.all_reduce(align)
                 a0.record(stream)
                 step()
                 a1.record(stream)
@@ -961,6 +966,8 @@ def run_e2e(args, full_case, case, rt, d, lens, gathered, steps, p2p):
             for _ in range(steps):
                 flush()
                 torch.cuda.synchronize()
+                if world > 1:
+                    dist.barrier()                    # the ranks flush on their own clocks: start the step together
                 t0 = time.perf_counter()
                 step()
                 total += time.perf_counter() - t0
